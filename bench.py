@@ -1,0 +1,285 @@
+"""Headline benchmark: Q4_0 x Q8_0 decode GEMV over the Llama-7B-shaped layers.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" is one decode pass over the four layer shapes (4096x4096, 11008x4096,
+4096x11008, 32000x4096), batch 1: four GEMV launches.  Weights rotate over distinct copies
+whose total size is several times the 126 MB L2, so every launch streams from HBM.  The
+metric is algorithmic bytes (weights once + activations + outputs) per second.  The GEMV
+does not shard: with N > 1 every rank runs an independent replica (weak scaling) and
+`value` is the sum over ranks divided by the slowest rank's time.
+
+`--impl reference` times the CPU oracle (the restatement of the reference's scalar
+semantics; the reference's own generated code needs an RVV toolchain) on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+import __graft_entry__ as entry  # noqa: E402
+
+SHAPES = [(4096, 4096), (11008, 4096), (4096, 11008), (32000, 4096)]  # (N rows, K)
+METRIC = "q4_0_q8_0_decode_gemv_hbm_gbs"
+UNIT = "GB/s"
+WORKLOAD = "q4_0_q8_0_gemv_llama7b_layers_batch1"
+ROTATION_BYTES = 640 << 20  # weight copies per shape cover at least this much (5x L2)
+
+
+def gemv_bytes(nr: int, k: int, batch: int) -> int:
+    nb = k // 32
+    return nr * nb * 18 + batch * nb * 34 + 4 * batch * nr
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f), "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.thread.join(timeout=2)
+        sm, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx = float(parts[1])
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------- CPU arm
+
+
+def cpu_sample(threads: int, target_seconds: float = 5.0):
+    """Times the oracle's Q4_0 x Q8_0 GEMV on a bounded sample: the first `rows` rows of each
+    layer shape, batch 1, all `threads` host threads.  Returns (GB/s, description)."""
+    O = entry.load_oracle()
+    rows = 2048
+    total_bytes, total_time = 0, 0.0
+    while True:
+        total_bytes, total_time = 0, 0.0
+        for nr, k in SHAPES:
+            r = min(rows, nr)
+            w = O.quantize_q4_0(O.fill_normal(r * k, 900 + k, 0.0, 0.02).reshape(r, k))
+            x = O.quantize_q8_0(O.fill_normal(k, 901 + k).reshape(1, k))
+            O.gemm(w[:64], x, threads=threads)  # warm caches / page in
+            t0 = time.perf_counter()
+            O.gemm(w, x, threads=threads)
+            total_time += time.perf_counter() - t0
+            total_bytes += gemv_bytes(r, k, 1)
+        if total_time >= target_seconds / 4 or rows >= 32000:
+            break
+        rows *= 4
+    return total_bytes / total_time / 1e9, f"first {rows} rows (or all) of each of the 4 layer shapes, batch 1, one pass"
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    O = entry.load_oracle()
+    O.build()
+    for _ in range(args.warmup):
+        cpu_sample(threads, 0.5)
+    t_total, b_total = 0.0, 0.0
+    desc = ""
+    for _ in range(args.steps):
+        gbs, desc = cpu_sample(threads, 2.0)
+        b_total += gbs
+        t_total += 1
+    value = b_total / max(t_total, 1)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": None, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "int8 products, int32 block sums, fp32 fold",
+        "data": "synthetic", "config": {"workload": WORKLOAD},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": desc},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "CPU oracle (restatement of the reference's scalar kernel); the reference's generated RVV C "
+                "cannot be built on this host",
+    }
+    print(json.dumps(line))
+
+
+# ------------------------------------------------------------------------- GPU arm
+
+
+def run_ours(args):
+    import torch
+
+    pkg = entry.load_package()
+    pkg.lib()  # fails loudly when the CUDA library is missing
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    # ---- inputs: fp32 weights ~ N(0, 0.02) quantised on the GPU, x ~ N(0, 1) -> Q8_0
+    gen = torch.Generator(device="cuda").manual_seed(1234 + rank)
+    layers = []
+    for nr, k in SHAPES:
+        wf = torch.randn((nr, k), generator=gen, device="cuda") * 0.02
+        w = pkg.quantize_q4_0(wf)
+        del wf
+        ncopies = max(2, -(-ROTATION_BYTES // w.numel()))
+        copies = [w] + [w.clone() for _ in range(ncopies - 1)]
+        x = pkg.quantize_q8_0(torch.randn((1, k), generator=gen, device="cuda"))
+        y = torch.empty((nr, 1), dtype=torch.float32, device="cuda")
+        layers.append({"nr": nr, "k": k, "w": copies, "x": x, "y": y, "bytes": gemv_bytes(nr, k, 1)})
+    step_bytes = sum(l["bytes"] for l in layers)
+    launches_per_step = len(layers)
+    counter = {"launches": 0}
+
+    def step(i: int):
+        for l in layers:
+            pkg.gemv(l["w"][i % len(l["w"])], l["x"], out=l["y"])
+        counter["launches"] += launches_per_step
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for i in range(args.warmup):
+        step(i)
+    pkg.check_device_errors()
+    sync_all()
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    counter["launches"] = 0
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for i in range(args.steps):
+        step(args.warmup + i)
+    stop.record()
+    sync_all()
+    elapsed_ms = start.elapsed_time(stop)
+    launches = counter["launches"]
+    clocks = sampler.stop() if rank == 0 else None
+    pkg.check_device_errors()
+    if dist is not None:
+        t = torch.tensor([elapsed_ms], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        elapsed_ms = float(t.item())
+
+    # ---- per-shape timing (explains the aggregate; same rotation, events on this stream)
+    per_shape = []
+    for l in layers:
+        reps = max(20, args.steps // 2)
+        for i in range(5):
+            pkg.gemv(l["w"][i % len(l["w"])], l["x"], out=l["y"])
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for i in range(reps):
+            pkg.gemv(l["w"][i % len(l["w"])], l["x"], out=l["y"])
+        b.record()
+        torch.cuda.synchronize()
+        us = a.elapsed_time(b) * 1e3 / reps
+        per_shape.append({"shape": f"{l['nr']}x{l['k']}", "us": round(us, 3), "gbs": round(l["bytes"] / us / 1e3, 1)})
+
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    peaks, peak_kind = measured_peaks()
+    value = step_bytes * args.steps * world / (elapsed_ms * 1e-3) / 1e9
+    per_gpu = value / world
+    big = per_shape[-1]
+    line = {
+        "metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(elapsed_ms / args.steps, 6), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "int8 products, int32 block sums, fp32 fold",
+        "data": "synthetic",
+        "config": {"workload": WORKLOAD, "shapes": [f"{n}x{k}" for n, k in SHAPES], "batch": 1,
+                   "l2": f"weights rotate over distinct copies >= {ROTATION_BYTES >> 20} MiB per shape",
+                   "parallelism": "replicas only" if world > 1 else "single GPU"},
+        "roofline": {"bound": "hbm", "achieved": round(per_gpu, 2), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(per_gpu / peaks["hbm_gbs"], 4), "traffic": None, "peak_kind": f"of {peak_kind}",
+                     "kernel": "gemv_stream_kernel<q4_0, 1 column>", "largest_shape": big},
+        "per_shape": per_shape,
+        "gpu_launches": launches,
+        "clocks": clocks,
+    }
+    print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

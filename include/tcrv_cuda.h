@@ -1,0 +1,128 @@
+/*
+ * tcrv_cuda.h -- C ABI of the sm_100a provider for the ggml-style Q8_0 / Q4_0 block path.
+ *
+ * Each entry point replaces one kernel that the TianChen-RV compiler emits as RISC-V
+ * Vector C (`extern "C" void tcrv_emitc_<kernel>_<variant>(...)`); the parameter lists keep
+ * the reference's runtime-ABI order (the declaration order of the fixture's
+ * `tcrv_rvv.runtime_abi_value` ops) and add a trailing CUDA stream.  All buffer pointers of
+ * the `tcrv_cuda_*` functions are DEVICE pointers owned by the caller
+ * (ownership "target-export-abi-owned": the library never frees or keeps them); calls are
+ * asynchronous on `stream` and return 0 or a negative tcrv_cuda_status.  Nothing here falls
+ * back to the CPU.
+ *
+ * Citations are paths inside the reference project (zzyu5/TianChen-RV).
+ */
+#ifndef TCRV_CUDA_H
+#define TCRV_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void *tcrv_cuda_stream; /* a cudaStream_t; NULL is the legacy default stream */
+
+typedef enum {
+  TCRV_CUDA_OK = 0,
+  TCRV_CUDA_ERR_INVALID_ARGUMENT = -1, /* null pointer, n % 32 != 0, stride too small, ... */
+  TCRV_CUDA_ERR_UNSUPPORTED = -2,      /* facts this provider has no kernel for */
+  TCRV_CUDA_ERR_CUDA = -3,             /* a CUDA runtime call failed (see tcrv_cuda_last_error_text) */
+  TCRV_CUDA_ERR_DEVICE_TIMEOUT = -4,   /* a bounded device-side wait gave up */
+  TCRV_CUDA_ERR_WORKSPACE = -5         /* workspace missing or too small */
+} tcrv_cuda_status;
+
+/* Block-format facts (include/TianChenRV/Dialect/RVV/IR/RVVOps.td:3837-3841, :8359-8361). */
+#define TCRV_QK 32
+#define TCRV_Q4_0_BLOCK_BYTES 18
+#define TCRV_Q8_0_BLOCK_BYTES 34
+
+/* flags for the GEMV / GEMM entry points */
+#define TCRV_CUDA_FLAG_NONE 0u
+/* fold every row's blocks in strict ascending order (bit-identical to the sequential
+ * scalar kernel with the fused fold); slower, meant for verification */
+#define TCRV_CUDA_FLAG_STRICT_ORDER 1u
+
+const char *tcrv_cuda_status_string(int status);
+/* Text of the last CUDA runtime error seen by the calling thread ("" if none). */
+const char *tcrv_cuda_last_error_text(void);
+/* Library/ABI version, bumped when a signature changes. */
+int tcrv_cuda_abi_version(void);
+/* Synchronises `stream`, then returns and clears the device-side error word
+ * (0, or TCRV_CUDA_ERR_DEVICE_TIMEOUT if a bounded wait in a kernel expired). */
+int tcrv_cuda_check_device_errors(tcrv_cuda_stream stream);
+
+/* ---- elementwise ------------------------------------------------------------------ */
+
+/* out[i] = lhs[i] + rhs[i].  Replaces the `tcrv_rvv.binary {kind = "add"}` body
+ * (lib/Conversion/RVV/RVVToEmitC.cpp:1873-1910; ABI order lhs, rhs, out, n:
+ * test/Conversion/RVV/rvv-to-emitc-add-cpp-golden.mlir:15-18). */
+int tcrv_cuda_add_f32(const float *lhs, const float *rhs, float *out, size_t n, tcrv_cuda_stream stream);
+int tcrv_cuda_add_i32(const int32_t *lhs, const int32_t *rhs, int32_t *out, size_t n, tcrv_cuda_stream stream);
+
+/* out[i] = (float)lhs[i] * scale.  Replaces `tcrv_rvv.dequantize {kind = "i32_to_f32_scaled"}`
+ * (lib/Conversion/RVV/RVVToEmitC.cpp:3347-3394; ABI lhs, scale, out, n:
+ * test/Conversion/RVV/rvv-to-emitc-dequantize-i32-to-f32.mlir:21-24). */
+int tcrv_cuda_dequantize_i32_f32(const int32_t *lhs, float scale, float *out, size_t n, tcrv_cuda_stream stream);
+
+/* Block dequantisation y = d * q over n elements (n % 32 == 0), i.e. the dequantize math
+ * above with the scale read from each block header.  vx holds n/32 blocks. */
+int tcrv_cuda_dequantize_row_q8_0(const uint8_t *vx, float *y, size_t n, tcrv_cuda_stream stream);
+int tcrv_cuda_dequantize_row_q4_0(const uint8_t *vx, float *y, size_t n, tcrv_cuda_stream stream);
+
+/* f32 -> block_q8_0.  Replaces `tcrv_rvv.quantize_row_q8_0`
+ * (lib/Conversion/RVV/RVVToEmitCForwardElementwise.cpp:751-958; ABI n, x, vy:
+ * test/Conversion/RVV/rvv-to-emitc-ggml-quantize-row-q8-0.mlir:27-29). */
+int tcrv_cuda_quantize_row_q8_0(size_t n, const float *x, uint8_t *vy, tcrv_cuda_stream stream);
+/* f32 -> block_q4_0 (weight preparation; the reference has no such op, the format is the one
+ * its verifier pins: include/TianChenRV/Dialect/RVV/IR/RVVOps.td:3837-3841). */
+int tcrv_cuda_quantize_row_q4_0(size_t n, const float *x, uint8_t *vx, tcrv_cuda_stream stream);
+
+/* ---- block dots --------------------------------------------------------------------- */
+
+/* *s = sum over blocks of ((float)sumi * d_x) * d_y.  Replaces `tcrv_rvv.q4_0_q8_0_block_dot`
+ * (lib/Conversion/RVV/RVVToEmitCBlockQuantLinear.cpp:29-470); ggml vec_dot ABI order
+ * n, s, bs, vx, bx, vy, by, nrc (test/Conversion/RVV/rvv-to-emitc-q4-0-q8-0-block-dot.mlir:24-31);
+ * as in the reference only n, s, vx, vy are consumed. */
+int tcrv_cuda_vec_dot_q4_0_q8_0(size_t n, float *s, size_t bs, const uint8_t *vx, size_t bx,
+                                const uint8_t *vy, size_t by, int32_t nrc, tcrv_cuda_stream stream);
+
+/* *s = sum over blocks of (float)sumi * (d_x * d_y).  Replaces `tcrv_rvv.q8_0_q8_0_block_dot`
+ * (lib/Conversion/RVV/RVVToEmitCBlockQuantLinear.cpp:7264-7671; ABI n, s, vx, vy:
+ * test/Conversion/RVV/rvv-to-emitc-q8-0-q8-0-block-dot.mlir:17-20). */
+int tcrv_cuda_vec_dot_q8_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy,
+                                tcrv_cuda_stream stream);
+
+/* ---- GEMV / GEMM ------------------------------------------------------------------ */
+
+/* s[ir*bs + col] = block dot of weight row ir (vx + ir*bx) with activation column col
+ * (vy + col*by), for ir < nr, col < nc.  Replaces `tcrv_rvv.q4_0_q8_0_gemm`
+ * (lib/Conversion/RVV/RVVToEmitCBlockQuantLinear.cpp:1691-2120; ABI n, s, vx, vy, by, nr, nc,
+ * bx, bs: test/Conversion/RVV/rvv-to-emitc-q4-0-q8-0-gemm.mlir:24-32).  bx and by are byte
+ * strides, bs counts floats.
+ *
+ * `tcrv_cuda_gemv_*` is the decode path (nc <= 8, HBM-bound weight streaming);
+ * `tcrv_cuda_gemm_*` is the prefill path (int8 tensor-core contraction, needs a workspace).
+ * The GEMV folds each row in 32 lane partials (lane l owns block pairs l, l+32, ... in
+ * ascending order) that are combined by a butterfly; TCRV_CUDA_FLAG_STRICT_ORDER selects
+ * the sequential fold.  The GEMM folds every output element in strict ascending block
+ * order.  Both use the fused form fma((float)sumi * d_x, d_y, sumf). */
+int tcrv_cuda_gemv_q4_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by,
+                             size_t nr, size_t nc, size_t bx, size_t bs, unsigned flags,
+                             tcrv_cuda_stream stream);
+/* The same loop over the Q8_0 x Q8_0 block dot (fold fma((float)sumi, d_x*d_y, sumf)). */
+int tcrv_cuda_gemv_q8_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by,
+                             size_t nr, size_t nc, size_t bx, size_t bs, unsigned flags,
+                             tcrv_cuda_stream stream);
+
+/* Debug variant of the integer stage: sumi[(ir*nc + col)*(n/32) + ib], bit-exact int32. */
+int tcrv_cuda_block_sums_q4_0_q8_0(size_t n, int32_t *sumi, const uint8_t *vx, const uint8_t *vy,
+                                   size_t by, size_t nr, size_t nc, size_t bx, tcrv_cuda_stream stream);
+int tcrv_cuda_block_sums_q8_0_q8_0(size_t n, int32_t *sumi, const uint8_t *vx, const uint8_t *vy,
+                                   size_t by, size_t nr, size_t nc, size_t bx, tcrv_cuda_stream stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TCRV_CUDA_H */

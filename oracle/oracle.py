@@ -1,0 +1,243 @@
+"""ctypes front-end to the CPU oracle (``oracle/tcrv_oracle.c``).
+
+TEST INFRASTRUCTURE ONLY: imported by ``tests/``, by ``__graft_entry__.smoke()`` and by the
+``cpu_baseline`` / ``--impl reference`` legs of ``bench.py``.  The product path never touches
+it.  Parity is unpinned by reference data (the reference ships no golden vectors for the
+quantized path); see the header of ``tcrv_oracle.h``.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.path.join(_HERE, "_build", "libtcrv_oracle.so")
+
+QK = 32
+Q4_0_BLOCK = 18
+Q8_0_BLOCK = 34
+FOLD_NOFMA = 0
+FOLD_FMA = 1
+
+
+def build(force: bool = False) -> str:
+    """Compile the oracle with the committed Makefile; returns the library path."""
+    src = os.path.join(_HERE, "tcrv_oracle.c")
+    hdr = os.path.join(_HERE, "tcrv_oracle.h")
+    stale = (
+        force
+        or not os.path.exists(_LIB_PATH)
+        or os.path.getmtime(_LIB_PATH) < max(os.path.getmtime(src), os.path.getmtime(hdr))
+    )
+    if stale:
+        subprocess.run(["make", "-C", _HERE, "-B" if force else "-s"], check=True)
+    return _LIB_PATH
+
+
+_lib = None
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        _lib = ctypes.CDLL(build())
+        _declare(_lib)
+    return _lib
+
+
+_sz = ctypes.c_size_t
+_p = ctypes.c_void_p
+
+
+def _declare(L: ctypes.CDLL) -> None:
+    L.tcrv_oracle_fp16_to_fp32.argtypes = [ctypes.c_uint16]
+    L.tcrv_oracle_fp16_to_fp32.restype = ctypes.c_float
+    L.tcrv_oracle_fp32_to_fp16.argtypes = [ctypes.c_float]
+    L.tcrv_oracle_fp32_to_fp16.restype = ctypes.c_uint16
+    L.tcrv_oracle_fill_uniform.argtypes = [_p, _sz, ctypes.c_uint64, ctypes.c_float, ctypes.c_float]
+    L.tcrv_oracle_fill_normal.argtypes = [_p, _sz, ctypes.c_uint64, ctypes.c_float, ctypes.c_float]
+    L.tcrv_oracle_add_f32.argtypes = [_p, _p, _p, _sz]
+    L.tcrv_oracle_add_i32.argtypes = [_p, _p, _p, _sz]
+    L.tcrv_oracle_dequantize_i32_f32.argtypes = [_p, ctypes.c_float, _p, _sz]
+    L.tcrv_oracle_quantize_row_q8_0.argtypes = [_p, _p, _sz]
+    L.tcrv_oracle_quantize_row_q4_0.argtypes = [_p, _p, _sz]
+    L.tcrv_oracle_dequantize_row_q8_0.argtypes = [_p, _p, _sz]
+    L.tcrv_oracle_dequantize_row_q4_0.argtypes = [_p, _p, _sz]
+    L.tcrv_oracle_decode_nibbles.argtypes = [ctypes.c_uint8, _p, _p]
+    L.tcrv_oracle_block_sums_q4_0_q8_0.argtypes = [_sz, _p, _p, _p]
+    L.tcrv_oracle_block_sums_q8_0_q8_0.argtypes = [_sz, _p, _p, _p]
+    L.tcrv_oracle_vec_dot_q4_0_q8_0.argtypes = [_sz, _p, _sz, _p, _sz, _p, _sz, ctypes.c_int32, ctypes.c_int]
+    L.tcrv_oracle_vec_dot_q8_0_q8_0.argtypes = [_sz, _p, _p, _p, ctypes.c_int]
+    gemm = [_sz, _p, _p, _p, _sz, _sz, _sz, _sz, _sz, ctypes.c_int, ctypes.c_int]
+    L.tcrv_oracle_gemm_q4_0_q8_0.argtypes = gemm
+    L.tcrv_oracle_gemm_q8_0_q8_0.argtypes = gemm
+    L.tcrv_oracle_gemv_lane_order.argtypes = [_sz, _p, _p, _p, _sz, _sz, _sz, _sz, _sz, ctypes.c_int]
+    L.tcrv_oracle_gemm_abs_terms.argtypes = [_sz, _p, _p, _p, _sz, _sz, _sz, _sz, _sz, ctypes.c_int]
+
+
+def _ptr(a: np.ndarray) -> int:
+    assert a.flags["C_CONTIGUOUS"]
+    return a.ctypes.data
+
+
+# ----------------------------------------------------------------- generators
+
+
+def fill_uniform(n: int, seed: int, lo: float = -1.0, hi: float = 1.0) -> np.ndarray:
+    out = np.empty(n, dtype=np.float32)
+    lib().tcrv_oracle_fill_uniform(_ptr(out), n, seed, lo, hi)
+    return out
+
+
+def fill_normal(n: int, seed: int, mean: float = 0.0, std: float = 1.0) -> np.ndarray:
+    out = np.empty(n, dtype=np.float32)
+    lib().tcrv_oracle_fill_normal(_ptr(out), n, seed, mean, std)
+    return out
+
+
+# ---------------------------------------------------------------- elementwise
+
+
+def fp16_to_fp32(h: int) -> float:
+    return float(lib().tcrv_oracle_fp16_to_fp32(h))
+
+
+def fp32_to_fp16(f: float) -> int:
+    return int(lib().tcrv_oracle_fp32_to_fp16(f))
+
+
+def add_f32(a: np.ndarray, b: np.ndarray) -> np.ndarray:
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    b = np.ascontiguousarray(b, dtype=np.float32)
+    out = np.empty_like(a)
+    lib().tcrv_oracle_add_f32(_ptr(a), _ptr(b), _ptr(out), a.size)
+    return out
+
+
+def add_i32(a: np.ndarray, b: np.ndarray) -> np.ndarray:
+    a = np.ascontiguousarray(a, dtype=np.int32)
+    b = np.ascontiguousarray(b, dtype=np.int32)
+    out = np.empty_like(a)
+    lib().tcrv_oracle_add_i32(_ptr(a), _ptr(b), _ptr(out), a.size)
+    return out
+
+
+def dequantize_i32_f32(v: np.ndarray, scale: float) -> np.ndarray:
+    v = np.ascontiguousarray(v, dtype=np.int32)
+    out = np.empty(v.shape, dtype=np.float32)
+    lib().tcrv_oracle_dequantize_i32_f32(_ptr(v), scale, _ptr(out), v.size)
+    return out
+
+
+# ----------------------------------------------------------------- quantizers
+
+
+def quantize_q8_0(x: np.ndarray) -> np.ndarray:
+    """fp32 (..., K) -> uint8 (..., K/32*34); blocks run along the last axis."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    assert x.shape[-1] % QK == 0
+    out = np.empty(x.shape[:-1] + (x.shape[-1] // QK * Q8_0_BLOCK,), dtype=np.uint8)
+    lib().tcrv_oracle_quantize_row_q8_0(_ptr(x), _ptr(out), x.size)
+    return out
+
+
+def quantize_q4_0(x: np.ndarray) -> np.ndarray:
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    assert x.shape[-1] % QK == 0
+    out = np.empty(x.shape[:-1] + (x.shape[-1] // QK * Q4_0_BLOCK,), dtype=np.uint8)
+    lib().tcrv_oracle_quantize_row_q4_0(_ptr(x), _ptr(out), x.size)
+    return out
+
+
+def dequantize_q8_0(q: np.ndarray) -> np.ndarray:
+    q = np.ascontiguousarray(q, dtype=np.uint8)
+    assert q.shape[-1] % Q8_0_BLOCK == 0
+    out = np.empty(q.shape[:-1] + (q.shape[-1] // Q8_0_BLOCK * QK,), dtype=np.float32)
+    lib().tcrv_oracle_dequantize_row_q8_0(_ptr(q), _ptr(out), out.size)
+    return out
+
+
+def dequantize_q4_0(q: np.ndarray) -> np.ndarray:
+    q = np.ascontiguousarray(q, dtype=np.uint8)
+    assert q.shape[-1] % Q4_0_BLOCK == 0
+    out = np.empty(q.shape[:-1] + (q.shape[-1] // Q4_0_BLOCK * QK,), dtype=np.float32)
+    lib().tcrv_oracle_dequantize_row_q4_0(_ptr(q), _ptr(out), out.size)
+    return out
+
+
+def decode_nibbles(byte: int) -> tuple[int, int]:
+    lo = ctypes.c_int8()
+    hi = ctypes.c_int8()
+    lib().tcrv_oracle_decode_nibbles(byte, ctypes.byref(lo), ctypes.byref(hi))
+    return lo.value, hi.value
+
+
+# ----------------------------------------------------------------- block dots
+
+
+def _wblock(q8_weights: bool) -> int:
+    return Q8_0_BLOCK if q8_weights else Q4_0_BLOCK
+
+
+def block_sums(w: np.ndarray, x: np.ndarray, q8_weights: bool = False) -> np.ndarray:
+    """Per-block int32 sums, shape (nr, nc, K/32), for weights (nr, rowbytes) and
+    activations (nc, K/32*34)."""
+    w = np.ascontiguousarray(w, dtype=np.uint8)
+    x = np.ascontiguousarray(x, dtype=np.uint8)
+    nb = x.shape[-1] // Q8_0_BLOCK
+    assert w.shape[-1] == nb * _wblock(q8_weights)
+    out = np.empty((w.shape[0], x.shape[0], nb), dtype=np.int32)
+    fn = lib().tcrv_oracle_block_sums_q8_0_q8_0 if q8_weights else lib().tcrv_oracle_block_sums_q4_0_q8_0
+    for r in range(w.shape[0]):
+        for c in range(x.shape[0]):
+            fn(nb * QK, _ptr(out[r, c]), _ptr(w[r]), _ptr(x[c]))
+    return out
+
+
+def vec_dot_q4_0_q8_0(w_row: np.ndarray, x_row: np.ndarray, fold: int = FOLD_FMA) -> np.float32:
+    w_row = np.ascontiguousarray(w_row, dtype=np.uint8)
+    x_row = np.ascontiguousarray(x_row, dtype=np.uint8)
+    n = x_row.size // Q8_0_BLOCK * QK
+    s = np.zeros(1, dtype=np.float32)
+    lib().tcrv_oracle_vec_dot_q4_0_q8_0(n, _ptr(s), 0, _ptr(w_row), 0, _ptr(x_row), 0, 1, fold)
+    return s[0]
+
+
+def vec_dot_q8_0_q8_0(w_row: np.ndarray, x_row: np.ndarray, fold: int = FOLD_FMA) -> np.float32:
+    w_row = np.ascontiguousarray(w_row, dtype=np.uint8)
+    x_row = np.ascontiguousarray(x_row, dtype=np.uint8)
+    n = x_row.size // Q8_0_BLOCK * QK
+    s = np.zeros(1, dtype=np.float32)
+    lib().tcrv_oracle_vec_dot_q8_0_q8_0(n, _ptr(s), _ptr(w_row), _ptr(x_row), fold)
+    return s[0]
+
+
+def _gemm_like(fn, w, x, extra) -> np.ndarray:
+    w = np.ascontiguousarray(w, dtype=np.uint8)
+    x = np.ascontiguousarray(x, dtype=np.uint8)
+    nr, bx = w.shape
+    nc, by = x.shape
+    n = by // Q8_0_BLOCK * QK
+    out = np.empty((nr, nc), dtype=np.float32)
+    fn(n, _ptr(out), _ptr(w), _ptr(x), by, nr, nc, bx, nc, *extra)
+    return out
+
+
+def gemm(w: np.ndarray, x: np.ndarray, q8_weights: bool = False, fold: int = FOLD_FMA,
+         threads: int = 1) -> np.ndarray:
+    """out[row, col] = block dot of weight row `row` with activation column `col`
+    (the reference's N-major output), sequential ascending block order."""
+    fn = lib().tcrv_oracle_gemm_q8_0_q8_0 if q8_weights else lib().tcrv_oracle_gemm_q4_0_q8_0
+    return _gemm_like(fn, w, x, (fold, threads))
+
+
+def gemv_lane_order(w: np.ndarray, x: np.ndarray, q8_weights: bool = False) -> np.ndarray:
+    """The CUDA GEMV's fp32 order restated on the CPU (lane partials + butterfly)."""
+    return _gemm_like(lib().tcrv_oracle_gemv_lane_order, w, x, (1 if q8_weights else 0,))
+
+
+def abs_terms(w: np.ndarray, x: np.ndarray, q8_weights: bool = False) -> np.ndarray:
+    return _gemm_like(lib().tcrv_oracle_gemm_abs_terms, w, x, (1 if q8_weights else 0,))

@@ -1,0 +1,443 @@
+/*
+ * CPU oracle (test infrastructure only; parity unpinned by reference data -- see
+ * tcrv_oracle.h).  Build with `-O2 -ffp-contract=off` so every C operator below rounds
+ * exactly once; the fused fold is spelled with fmaf() where it is wanted.
+ */
+#include "tcrv_oracle.h"
+
+#include <math.h>
+#include <pthread.h>
+#include <stdlib.h>
+#include <string.h>
+
+/* ------------------------------------------------------------------ fp16 */
+
+float tcrv_oracle_fp16_to_fp32(uint16_t h) {
+  uint32_t sign = (uint32_t)(h & 0x8000u) << 16;
+  uint32_t exp = (h >> 10) & 0x1fu;
+  uint32_t man = h & 0x3ffu;
+  uint32_t bits;
+  if (exp == 0) {
+    if (man == 0) {
+      bits = sign;
+    } else {
+      /* subnormal half: renormalise */
+      int shift = 0;
+      while ((man & 0x400u) == 0) {
+        man <<= 1;
+        ++shift;
+      }
+      man &= 0x3ffu;
+      bits = sign | ((uint32_t)(127 - 15 - shift + 1) << 23) | (man << 13);
+    }
+  } else if (exp == 31) {
+    bits = sign | 0x7f800000u | (man << 13);
+  } else {
+    bits = sign | ((exp + 127 - 15) << 23) | (man << 13);
+  }
+  float f;
+  memcpy(&f, &bits, sizeof f);
+  return f;
+}
+
+uint16_t tcrv_oracle_fp32_to_fp16(float f) {
+  uint32_t x;
+  memcpy(&x, &f, sizeof x);
+  uint16_t sign = (uint16_t)((x >> 16) & 0x8000u);
+  uint32_t absx = x & 0x7fffffffu;
+  if (absx >= 0x7f800000u) { /* inf / nan */
+    if (absx > 0x7f800000u)
+      return (uint16_t)(sign | 0x7e00u | ((absx >> 13) & 0x3ffu));
+    return (uint16_t)(sign | 0x7c00u);
+  }
+  if (absx >= 0x477ff000u) /* >= 65520 rounds to inf */
+    return (uint16_t)(sign | 0x7c00u);
+  if (absx < 0x33000001u) /* <= 2^-25 rounds to zero (tie goes to even = 0) */
+    return sign;
+  int32_t e = (int32_t)(absx >> 23) - 127;
+  uint32_t man = (absx & 0x7fffffu) | 0x800000u; /* 24-bit significand */
+  uint32_t shift;
+  uint32_t half_exp;
+  if (e < -14) { /* subnormal half */
+    shift = (uint32_t)(13 + (-14 - e));
+    half_exp = 0;
+  } else {
+    shift = 13;
+    half_exp = (uint32_t)(e + 15);
+  }
+  uint32_t kept = man >> shift;
+  uint32_t rem = man & ((1u << shift) - 1u);
+  uint32_t halfway = 1u << (shift - 1);
+  if (rem > halfway || (rem == halfway && (kept & 1u)))
+    ++kept;
+  uint32_t out;
+  if (half_exp == 0) {
+    out = kept; /* a carry into bit 10 lands on the smallest normal, as it should */
+  } else {
+    out = ((half_exp - 1) << 10) + kept; /* kept has the implicit bit at 0x400 */
+  }
+  return (uint16_t)(sign | out);
+}
+
+static inline float block_scale(const uint8_t *block) {
+  uint16_t h = (uint16_t)(block[0] | ((uint16_t)block[1] << 8));
+  return tcrv_oracle_fp16_to_fp32(h);
+}
+
+/* ------------------------------------------------------------ generators */
+
+static inline uint64_t splitmix64(uint64_t z) {
+  z += 0x9e3779b97f4a7c15ull;
+  z = (z ^ (z >> 30)) * 0xbf58476d1ce4e5b9ull;
+  z = (z ^ (z >> 27)) * 0x94d049bb133111ebull;
+  return z ^ (z >> 31);
+}
+
+static inline double unit_open(uint64_t seed, uint64_t counter) {
+  uint64_t r = splitmix64(seed * 0x2545f4914f6cdd1dull + counter);
+  return ((double)(r >> 11) + 0.5) * (1.0 / 9007199254740992.0); /* (0,1) */
+}
+
+void tcrv_oracle_fill_uniform(float *out, size_t n, uint64_t seed, float lo, float hi) {
+  for (size_t i = 0; i < n; ++i)
+    out[i] = (float)((double)lo + ((double)hi - (double)lo) * unit_open(seed, i));
+}
+
+void tcrv_oracle_fill_normal(float *out, size_t n, uint64_t seed, float mean, float stddev) {
+  for (size_t i = 0; i < n; i += 2) {
+    double u1 = unit_open(seed, i);
+    double u2 = unit_open(seed, i + 1);
+    double r = sqrt(-2.0 * log(u1));
+    double a = 6.283185307179586476925286766559 * u2;
+    out[i] = (float)((double)mean + (double)stddev * r * cos(a));
+    if (i + 1 < n)
+      out[i + 1] = (float)((double)mean + (double)stddev * r * sin(a));
+  }
+}
+
+/* ------------------------------------------------------------ elementwise */
+
+void tcrv_oracle_add_f32(const float *lhs, const float *rhs, float *out, size_t n) {
+  for (size_t i = 0; i < n; ++i)
+    out[i] = lhs[i] + rhs[i];
+}
+
+void tcrv_oracle_add_i32(const int32_t *lhs, const int32_t *rhs, int32_t *out, size_t n) {
+  for (size_t i = 0; i < n; ++i)
+    out[i] = (int32_t)((uint32_t)lhs[i] + (uint32_t)rhs[i]); /* vadd wraps */
+}
+
+void tcrv_oracle_dequantize_i32_f32(const int32_t *lhs, float scale, float *out, size_t n) {
+  for (size_t i = 0; i < n; ++i)
+    out[i] = (float)lhs[i] * scale; /* vfcvt_f_x_v then vfmul_vf */
+}
+
+/* ------------------------------------------------------------- quantizers */
+
+void tcrv_oracle_quantize_row_q8_0(const float *x, uint8_t *vy, size_t n) {
+  size_t nb = n / TCRV_QK;
+  for (size_t ib = 0; ib < nb; ++ib) {
+    const float *xb = x + ib * TCRV_QK;
+    uint8_t *yb = vy + ib * TCRV_Q8_0_BLOCK_BYTES;
+    float amax = 0.0f; /* vfredmax seeded with 0.0f over vfabs */
+    for (int j = 0; j < TCRV_QK; ++j) {
+      float a = fabsf(xb[j]);
+      if (a > amax)
+        amax = a;
+    }
+    float d = amax / 127.0f;
+    float id = 0.0f;
+    if (d != 0.0f)
+      id = 1.0f / d;
+    uint16_t dh = tcrv_oracle_fp32_to_fp16(d);
+    yb[0] = (uint8_t)(dh & 0xff);
+    yb[1] = (uint8_t)(dh >> 8);
+    for (int j = 0; j < TCRV_QK; ++j) {
+      float x0 = xb[j] * id;
+      /* vfncvt_x_f_w (f32 -> i16, round-to-nearest-even, saturating) */
+      float r = nearbyintf(x0); /* default rounding mode is to-nearest-even */
+      int32_t i16;
+      if (r >= 32767.0f)
+        i16 = 32767;
+      else if (r <= -32768.0f)
+        i16 = -32768;
+      else if (r != r)
+        i16 = 32767; /* RVV converts NaN to the maximum */
+      else
+        i16 = (int32_t)r;
+      /* vncvt_x_x_w (i16 -> i8) keeps the low byte */
+      yb[2 + j] = (uint8_t)(i16 & 0xff);
+    }
+  }
+}
+
+void tcrv_oracle_quantize_row_q4_0(const float *x, uint8_t *vx, size_t n) {
+  size_t nb = n / TCRV_QK;
+  for (size_t ib = 0; ib < nb; ++ib) {
+    const float *xb = x + ib * TCRV_QK;
+    uint8_t *wb = vx + ib * TCRV_Q4_0_BLOCK_BYTES;
+    float amax = 0.0f, vmax = 0.0f;
+    for (int j = 0; j < TCRV_QK; ++j) {
+      float a = fabsf(xb[j]);
+      if (a > amax) {
+        amax = a;
+        vmax = xb[j];
+      }
+    }
+    float d = vmax / -8.0f;
+    float id = 0.0f;
+    if (d != 0.0f)
+      id = 1.0f / d;
+    uint16_t dh = tcrv_oracle_fp32_to_fp16(d);
+    wb[0] = (uint8_t)(dh & 0xff);
+    wb[1] = (uint8_t)(dh >> 8);
+    for (int j = 0; j < TCRV_QK / 2; ++j) {
+      float x0 = xb[j] * id;
+      float x1 = xb[j + TCRV_QK / 2] * id;
+      int32_t q0 = (int32_t)(int8_t)(x0 + 8.5f);
+      int32_t q1 = (int32_t)(int8_t)(x1 + 8.5f);
+      if (q0 > 15)
+        q0 = 15;
+      if (q1 > 15)
+        q1 = 15;
+      wb[2 + j] = (uint8_t)(q0 | (q1 << 4));
+    }
+  }
+}
+
+/* ------------------------------------------------------------- dequantize */
+
+void tcrv_oracle_decode_nibbles(uint8_t byte, int8_t *lo, int8_t *hi) {
+  uint8_t t = (uint8_t)(byte ^ 0x88u);
+  int8_t shifted = (int8_t)(uint8_t)(t << 4);
+  *lo = (int8_t)(shifted >> 4); /* arithmetic shift on a signed byte */
+  *hi = (int8_t)((int8_t)t >> 4);
+}
+
+void tcrv_oracle_dequantize_row_q8_0(const uint8_t *vx, float *y, size_t n) {
+  size_t nb = n / TCRV_QK;
+  for (size_t ib = 0; ib < nb; ++ib) {
+    const uint8_t *b = vx + ib * TCRV_Q8_0_BLOCK_BYTES;
+    float d = block_scale(b);
+    for (int j = 0; j < TCRV_QK; ++j)
+      y[ib * TCRV_QK + j] = (float)(int32_t)(int8_t)b[2 + j] * d;
+  }
+}
+
+void tcrv_oracle_dequantize_row_q4_0(const uint8_t *vx, float *y, size_t n) {
+  size_t nb = n / TCRV_QK;
+  for (size_t ib = 0; ib < nb; ++ib) {
+    const uint8_t *b = vx + ib * TCRV_Q4_0_BLOCK_BYTES;
+    float d = block_scale(b);
+    for (int j = 0; j < TCRV_QK / 2; ++j) {
+      int8_t lo, hi;
+      tcrv_oracle_decode_nibbles(b[2 + j], &lo, &hi);
+      y[ib * TCRV_QK + j] = (float)(int32_t)lo * d;
+      y[ib * TCRV_QK + j + TCRV_QK / 2] = (float)(int32_t)hi * d;
+    }
+  }
+}
+
+/* --------------------------------------------------------------- block dots */
+
+static inline int32_t block_sum_q4_0_q8_0(const uint8_t *xb, const uint8_t *yb) {
+  int32_t sumi = 0;
+  for (int j = 0; j < TCRV_QK / 2; ++j) {
+    int8_t lo, hi;
+    tcrv_oracle_decode_nibbles(xb[2 + j], &lo, &hi);
+    sumi += (int32_t)lo * (int32_t)(int8_t)yb[2 + j];
+    sumi += (int32_t)hi * (int32_t)(int8_t)yb[2 + j + TCRV_QK / 2];
+  }
+  return sumi;
+}
+
+static inline int32_t block_sum_q8_0_q8_0(const uint8_t *xb, const uint8_t *yb) {
+  int32_t sumi = 0;
+  for (int j = 0; j < TCRV_QK; ++j)
+    sumi += (int32_t)(int8_t)xb[2 + j] * (int32_t)(int8_t)yb[2 + j];
+  return sumi;
+}
+
+void tcrv_oracle_block_sums_q4_0_q8_0(size_t n, int32_t *sumi, const uint8_t *vx, const uint8_t *vy) {
+  size_t nb = n / TCRV_QK;
+  for (size_t ib = 0; ib < nb; ++ib)
+    sumi[ib] = block_sum_q4_0_q8_0(vx + ib * TCRV_Q4_0_BLOCK_BYTES, vy + ib * TCRV_Q8_0_BLOCK_BYTES);
+}
+
+void tcrv_oracle_block_sums_q8_0_q8_0(size_t n, int32_t *sumi, const uint8_t *vx, const uint8_t *vy) {
+  size_t nb = n / TCRV_QK;
+  for (size_t ib = 0; ib < nb; ++ib)
+    sumi[ib] = block_sum_q8_0_q8_0(vx + ib * TCRV_Q8_0_BLOCK_BYTES, vy + ib * TCRV_Q8_0_BLOCK_BYTES);
+}
+
+static inline float fold_q4(float sumf, int32_t sumi, float dx, float dy, int fold) {
+  float t = (float)sumi * dx;
+  if (fold == TCRV_FOLD_FMA)
+    return fmaf(t, dy, sumf);
+  float term = t * dy;
+  return sumf + term;
+}
+
+static inline float fold_q8(float sumf, int32_t sumi, float dx, float dy, int fold) {
+  float scale = dx * dy;
+  if (fold == TCRV_FOLD_FMA)
+    return fmaf((float)sumi, scale, sumf);
+  float term = (float)sumi * scale;
+  return sumf + term;
+}
+
+static float dot_q4_0_q8_0(size_t n, const uint8_t *vx, const uint8_t *vy, int fold) {
+  size_t nb = n / TCRV_QK;
+  float sumf = 0.0f;
+  for (size_t ib = 0; ib < nb; ++ib) {
+    const uint8_t *xb = vx + ib * TCRV_Q4_0_BLOCK_BYTES;
+    const uint8_t *yb = vy + ib * TCRV_Q8_0_BLOCK_BYTES;
+    sumf = fold_q4(sumf, block_sum_q4_0_q8_0(xb, yb), block_scale(xb), block_scale(yb), fold);
+  }
+  return sumf;
+}
+
+static float dot_q8_0_q8_0(size_t n, const uint8_t *vx, const uint8_t *vy, int fold) {
+  size_t nb = n / TCRV_QK;
+  float sumf = 0.0f;
+  for (size_t ib = 0; ib < nb; ++ib) {
+    const uint8_t *xb = vx + ib * TCRV_Q8_0_BLOCK_BYTES;
+    const uint8_t *yb = vy + ib * TCRV_Q8_0_BLOCK_BYTES;
+    sumf = fold_q8(sumf, block_sum_q8_0_q8_0(xb, yb), block_scale(xb), block_scale(yb), fold);
+  }
+  return sumf;
+}
+
+void tcrv_oracle_vec_dot_q4_0_q8_0(size_t n, float *s, size_t bs, const uint8_t *vx, size_t bx,
+                                   const uint8_t *vy, size_t by, int32_t nrc, int fold) {
+  (void)bs;
+  (void)bx;
+  (void)by;
+  (void)nrc; /* only n, s, vx, vy are consumed by the reference kernel */
+  *s = dot_q4_0_q8_0(n, vx, vy, fold);
+}
+
+void tcrv_oracle_vec_dot_q8_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, int fold) {
+  *s = dot_q8_0_q8_0(n, vx, vy, fold);
+}
+
+/* --------------------------------------------------------------------- GEMM */
+
+typedef struct {
+  size_t n;
+  float *s;
+  const uint8_t *vx;
+  const uint8_t *vy;
+  size_t by, nr_begin, nr_end, nc, bx, bs;
+  int fold;
+  int q8_weights;
+} gemm_job;
+
+static void *gemm_worker(void *arg) {
+  const gemm_job *j = (const gemm_job *)arg;
+  for (size_t ir = j->nr_begin; ir < j->nr_end; ++ir) {
+    const uint8_t *xr = j->vx + ir * j->bx;
+    float *sr = j->s + ir * j->bs;
+    for (size_t col = 0; col < j->nc; ++col) {
+      const uint8_t *yc = j->vy + col * j->by;
+      sr[col] = j->q8_weights ? dot_q8_0_q8_0(j->n, xr, yc, j->fold) : dot_q4_0_q8_0(j->n, xr, yc, j->fold);
+    }
+  }
+  return NULL;
+}
+
+static void gemm_run(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by, size_t nr,
+                     size_t nc, size_t bx, size_t bs, int fold, int threads, int q8_weights) {
+  if (threads < 1)
+    threads = 1;
+  if ((size_t)threads > nr)
+    threads = nr ? (int)nr : 1;
+  gemm_job *jobs = (gemm_job *)malloc(sizeof(gemm_job) * (size_t)threads);
+  pthread_t *tids = (pthread_t *)malloc(sizeof(pthread_t) * (size_t)threads);
+  size_t per = (nr + (size_t)threads - 1) / (size_t)threads;
+  for (int t = 0; t < threads; ++t) {
+    size_t b = (size_t)t * per, e = b + per;
+    if (b > nr)
+      b = nr;
+    if (e > nr)
+      e = nr;
+    gemm_job j = {n, s, vx, vy, by, b, e, nc, bx, bs, fold, q8_weights};
+    jobs[t] = j;
+  }
+  if (threads == 1) {
+    gemm_worker(&jobs[0]);
+  } else {
+    for (int t = 0; t < threads; ++t)
+      pthread_create(&tids[t], NULL, gemm_worker, &jobs[t]);
+    for (int t = 0; t < threads; ++t)
+      pthread_join(tids[t], NULL);
+  }
+  free(jobs);
+  free(tids);
+}
+
+void tcrv_oracle_gemm_q4_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by,
+                                size_t nr, size_t nc, size_t bx, size_t bs, int fold, int threads) {
+  gemm_run(n, s, vx, vy, by, nr, nc, bx, bs, fold, threads, 0);
+}
+
+void tcrv_oracle_gemm_q8_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by,
+                                size_t nr, size_t nc, size_t bx, size_t bs, int fold, int threads) {
+  gemm_run(n, s, vx, vy, by, nr, nc, bx, bs, fold, threads, 1);
+}
+
+/* ------------------------------------------------- CUDA GEMV order restated */
+
+void tcrv_oracle_gemv_lane_order(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by,
+                                 size_t nr, size_t nc, size_t bx, size_t bs, int q8_weights) {
+  size_t nb = n / TCRV_QK;
+  size_t wstride = q8_weights ? TCRV_Q8_0_BLOCK_BYTES : TCRV_Q4_0_BLOCK_BYTES;
+  for (size_t ir = 0; ir < nr; ++ir) {
+    const uint8_t *xr = vx + ir * bx;
+    for (size_t col = 0; col < nc; ++col) {
+      const uint8_t *yc = vy + col * by;
+      float lane[32];
+      for (int l = 0; l < 32; ++l) {
+        float acc = 0.0f;
+        /* lane l owns block pairs l, l+32, ...: blocks 64i+2l and 64i+2l+1 */
+        for (size_t k = 0; 2 * ((size_t)l + 32 * (k / 2)) + (k & 1) < nb; ++k) {
+          size_t ib = 2 * ((size_t)l + 32 * (k / 2)) + (k & 1);
+          const uint8_t *xb = xr + ib * wstride;
+          const uint8_t *yb = yc + ib * TCRV_Q8_0_BLOCK_BYTES;
+          if (q8_weights)
+            acc = fold_q8(acc, block_sum_q8_0_q8_0(xb, yb), block_scale(xb), block_scale(yb), TCRV_FOLD_FMA);
+          else
+            acc = fold_q4(acc, block_sum_q4_0_q8_0(xb, yb), block_scale(xb), block_scale(yb), TCRV_FOLD_FMA);
+        }
+        lane[l] = acc;
+      }
+      for (int off = 16; off >= 1; off >>= 1) {
+        float next[32];
+        for (int l = 0; l < 32; ++l)
+          next[l] = lane[l] + lane[l ^ off];
+        memcpy(lane, next, sizeof lane);
+      }
+      s[ir * bs + col] = lane[0];
+    }
+  }
+}
+
+void tcrv_oracle_gemm_abs_terms(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by,
+                                size_t nr, size_t nc, size_t bx, size_t bs, int q8_weights) {
+  size_t nb = n / TCRV_QK;
+  size_t wstride = q8_weights ? TCRV_Q8_0_BLOCK_BYTES : TCRV_Q4_0_BLOCK_BYTES;
+  for (size_t ir = 0; ir < nr; ++ir) {
+    const uint8_t *xr = vx + ir * bx;
+    for (size_t col = 0; col < nc; ++col) {
+      const uint8_t *yc = vy + col * by;
+      double acc = 0.0;
+      for (size_t ib = 0; ib < nb; ++ib) {
+        const uint8_t *xb = xr + ib * wstride;
+        const uint8_t *yb = yc + ib * TCRV_Q8_0_BLOCK_BYTES;
+        int32_t si = q8_weights ? block_sum_q8_0_q8_0(xb, yb) : block_sum_q4_0_q8_0(xb, yb);
+        acc += fabs((double)si * (double)block_scale(xb) * (double)block_scale(yb));
+      }
+      s[ir * bs + col] = (float)acc;
+    }
+  }
+}

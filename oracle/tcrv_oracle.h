@@ -1,0 +1,116 @@
+/*
+ * CPU oracle for the ggml-style Q8_0 / Q4_0 block path that TianChen-RV compiles.
+ *
+ * TEST INFRASTRUCTURE ONLY.  This is a plain-C restatement of the arithmetic the
+ * reference's emitters state; it exists to check the CUDA kernels and to be timed
+ * as the reported CPU baseline.  Nothing on the product path may call it.
+ *
+ * PARITY UNPINNED: the reference ships no golden vectors or known-answer tests for
+ * the quantized path (its lit tests pin IR structure and the fp32 fold expression
+ * tree, not numbers), and neither the reference compiler (needs LLVM/MLIR 20) nor
+ * its generated RVV C (needs <riscv_vector.h> + qemu) can be built on a host.  The
+ * only numeric fixture in the reference is the i32 `add` harness
+ * (examples/qemu/harness_add.cpp:15-33), which tests/ replays.  Everything else is
+ * pinned by the stated semantics cited per function below plus hand-computed cases.
+ *
+ * fp32 fold modes (`fold` argument):
+ *   TCRV_FOLD_NOFMA  every C operator rounds separately (-ffp-contract=off reading)
+ *   TCRV_FOLD_FMA    the final `sumf + t * d` is one fused multiply-add, which is what
+ *                    the single-expression fold compiles to on the reference's RVV
+ *                    build (lib/Conversion/RVV/RVVToEmitCBlockQuantLinear.cpp:322-328)
+ */
+#ifndef TCRV_ORACLE_H
+#define TCRV_ORACLE_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TCRV_QK 32
+#define TCRV_Q4_0_BLOCK_BYTES 18
+#define TCRV_Q8_0_BLOCK_BYTES 34
+
+#define TCRV_FOLD_NOFMA 0
+#define TCRV_FOLD_FMA 1
+
+/* IEEE binary16 <-> binary32, bit exact, narrowing is round-to-nearest-even. */
+float tcrv_oracle_fp16_to_fp32(uint16_t h);
+uint16_t tcrv_oracle_fp32_to_fp16(float f);
+
+/* Seeded input generators (splitmix64 counter stream; Box-Muller for normals). */
+void tcrv_oracle_fill_uniform(float *out, size_t n, uint64_t seed, float lo, float hi);
+void tcrv_oracle_fill_normal(float *out, size_t n, uint64_t seed, float mean, float stddev);
+
+/* tcrv_rvv.binary{kind="add"}: lib/Conversion/RVV/RVVToEmitC.cpp:1873-1910. */
+void tcrv_oracle_add_f32(const float *lhs, const float *rhs, float *out, size_t n);
+void tcrv_oracle_add_i32(const int32_t *lhs, const int32_t *rhs, int32_t *out, size_t n);
+
+/* tcrv_rvv.dequantize i32 -> f32 with one runtime scale:
+ * lib/Conversion/RVV/RVVToEmitC.cpp:3347-3394. */
+void tcrv_oracle_dequantize_i32_f32(const int32_t *lhs, float scale, float *out, size_t n);
+
+/* tcrv_rvv.quantize_row_q8_0:
+ * lib/Conversion/RVV/RVVToEmitCForwardElementwise.cpp:751-958,
+ * include/TianChenRV/Dialect/RVV/IR/RVVOps.td:8363-8389. */
+void tcrv_oracle_quantize_row_q8_0(const float *x, uint8_t *vy, size_t n);
+
+/* Q4_0 weight quantizer.  The reference has none; this follows the block format its
+ * verifier pins (include/TianChenRV/Dialect/RVV/IR/RVVOps.td:3837-3841): d = the
+ * signed max-magnitude element / -8 stored as fp16, nibble = trunc(x/d + 8.5) clamped
+ * to 15, element j in the low nibble of byte j and element j+16 in the high nibble. */
+void tcrv_oracle_quantize_row_q4_0(const float *x, uint8_t *vx, size_t n);
+
+/* Block dequantisation y = d * q.  Per element this is the i32->f32 dequantize math
+ * (RVVToEmitC.cpp:3347-3394) with d read from the block header. */
+void tcrv_oracle_dequantize_row_q8_0(const uint8_t *vx, float *y, size_t n);
+void tcrv_oracle_dequantize_row_q4_0(const uint8_t *vx, float *y, size_t n);
+
+/* Offset-binary nibble decode, one byte -> two signed values in [-8,7]:
+ * lib/Conversion/RVV/RVVToEmitC.cpp:2524-2589 (t = b ^ 0x88; lo = (int8)(t<<4)>>4;
+ * hi = (int8)t >> 4). */
+void tcrv_oracle_decode_nibbles(uint8_t byte, int8_t *lo, int8_t *hi);
+
+/* Per-block int32 sums (the integer stage of both block dots). */
+void tcrv_oracle_block_sums_q4_0_q8_0(size_t n, int32_t *sumi, const uint8_t *vx, const uint8_t *vy);
+void tcrv_oracle_block_sums_q8_0_q8_0(size_t n, int32_t *sumi, const uint8_t *vx, const uint8_t *vy);
+
+/* tcrv_rvv.q4_0_q8_0_block_dot, ggml vec_dot ABI order:
+ * lib/Conversion/RVV/RVVToEmitCBlockQuantLinear.cpp:29-470 (fold :329-356).
+ * sumf = sumf + ((float)sumi * d_x) * d_y, ascending block order. */
+void tcrv_oracle_vec_dot_q4_0_q8_0(size_t n, float *s, size_t bs, const uint8_t *vx, size_t bx,
+                                   const uint8_t *vy, size_t by, int32_t nrc, int fold);
+
+/* tcrv_rvv.q8_0_q8_0_block_dot:
+ * lib/Conversion/RVV/RVVToEmitCBlockQuantLinear.cpp:7264-7671 (fold :7545-7573).
+ * sumf = sumf + (float)sumi * (d_x * d_y), ascending block order. */
+void tcrv_oracle_vec_dot_q8_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, int fold);
+
+/* tcrv_rvv.q4_0_q8_0_gemm: lib/Conversion/RVV/RVVToEmitCBlockQuantLinear.cpp:1691-2120.
+ * s[ir*bs + col] = vec_dot(weight row ir at vx + ir*bx, activation column at vy + col*by).
+ * `threads` > 1 splits the weight rows across pthreads (results are identical). */
+void tcrv_oracle_gemm_q4_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by,
+                                size_t nr, size_t nc, size_t bx, size_t bs, int fold, int threads);
+
+/* The same row/column loop over the Q8_0 x Q8_0 block dot (the GEMV of a Q8_0 matrix). */
+void tcrv_oracle_gemm_q8_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by,
+                                size_t nr, size_t nc, size_t bx, size_t bs, int fold, int threads);
+
+/* Restatement of the CUDA GEMV's fp32 order, for bit-exact comparison of the fast
+ * kernels: lane l of a 32-lane group owns block pairs l, l+32, ... (blocks 64i+2l and
+ * 64i+2l+1) and folds them in ascending order from 0.0f with the fused form of the fold, then partials are combined by a butterfly
+ * (xor 16, 8, 4, 2, 1).  `q8_weights` selects the Q8_0 x Q8_0 association. */
+void tcrv_oracle_gemv_lane_order(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by,
+                                 size_t nr, size_t nc, size_t bx, size_t bs, int q8_weights);
+
+/* Sum over blocks of |term| for one (row, column): the cancellation scale tests use to
+ * judge a relative error on a row whose terms nearly cancel. */
+void tcrv_oracle_gemm_abs_terms(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by,
+                                size_t nr, size_t nc, size_t bx, size_t bs, int q8_weights);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TCRV_ORACLE_H */

@@ -1,0 +1,56 @@
+"""The C-ABI library loads without a GPU and exports every symbol the header declares."""
+import ctypes
+import os
+import re
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_functions():
+    names = []
+    for fname in sorted(os.listdir(os.path.join(ROOT, "include"))):
+        if not fname.endswith(".h"):
+            continue
+        text = open(os.path.join(ROOT, "include", fname)).read()
+        text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+        names += re.findall(r"\b(tcrv_(?:cuda|emitc)_\w+)\s*\(", text)
+    return sorted(set(names))
+
+
+def test_header_declares_entry_points():
+    names = declared_functions()
+    assert "tcrv_cuda_gemv_q4_0_q8_0" in names and "tcrv_cuda_add_f32" in names
+    assert len(names) >= 15
+
+
+def test_library_exports_every_declared_symbol(pkg):
+    pkg.build_library()
+    raw = ctypes.CDLL(pkg.LIB_PATH)
+    missing = [n for n in declared_functions() if not hasattr(raw, n)]
+    assert not missing, f"declared in include/*.h but not exported: {missing}"
+
+
+def test_python_binding_table_matches_header(pkg):
+    assert sorted(n for n in pkg.ABI if n.startswith("tcrv_cuda_")) == [
+        n for n in declared_functions() if n.startswith("tcrv_cuda_")
+    ]
+
+
+def test_status_strings_without_gpu(pkg):
+    L = pkg.lib()
+    assert L.tcrv_cuda_status_string(0) == b"ok"
+    assert L.tcrv_cuda_status_string(-1) == b"invalid argument"
+    assert L.tcrv_cuda_abi_version() >= 1
+
+
+def test_argument_validation_without_gpu(pkg):
+    # rejected before any CUDA call: n not a multiple of 32, null buffers, short strides
+    L = pkg.lib()
+    assert L.tcrv_cuda_dequantize_row_q8_0(None, None, 33, None) == -1
+    assert L.tcrv_cuda_quantize_row_q8_0(64, None, None, None) == -1
+    assert L.tcrv_cuda_gemv_q4_0_q8_0(4096, None, None, None, 0, 8, 1, 2304, 1, 0, None) == -1
+    assert L.tcrv_cuda_gemv_q4_0_q8_0(4100, 1, 1, 1, 4352, 8, 1, 2304, 1, 0, None) == -1
+    assert L.tcrv_cuda_gemv_q4_0_q8_0(4096, 1, 1, 1, 4352, 8, 1, 100, 1, 0, None) == -1  # bx < row bytes
+    assert L.tcrv_cuda_gemv_q4_0_q8_0(4096, 1, 1, 1, 100, 8, 2, 2304, 2, 0, None) == -1  # by < column bytes
+    assert L.tcrv_cuda_gemv_q4_0_q8_0(4096, 1, 1, 1, 4352, 8, 2, 2304, 1, 0, None) == -1  # bs < nc
+    assert L.tcrv_cuda_add_f32(None, None, None, 0, None) == 0  # empty input is a no-op

@@ -1,0 +1,145 @@
+"""GPU parity, decode GEMV: per-block int32 sums bit-exact, rows bit-exact against the
+oracle's restatement of the kernel's fp32 order, and within rel 1e-5 of the sequential
+oracle (rows whose terms cancel are judged against the sum of |terms|)."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+REL = 1e-5        # tolerance the path is specified to
+CANCEL = 1e-6     # |err| allowed per unit of sum(|terms|) on rows that nearly cancel
+
+
+def dev(torch, a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def make(O, nr, k, nc, q8w, seed):
+    wf = O.fill_normal(nr * k, seed, 0, 0.02).reshape(nr, k)
+    w = O.quantize_q8_0(wf) if q8w else O.quantize_q4_0(wf)
+    x = O.quantize_q8_0(O.fill_normal(nc * k, seed + 1).reshape(nc, k))
+    return w, x
+
+
+def check_rows(O, got, w, x, q8w):
+    assert np.array_equal(got.view(np.uint32), O.gemv_lane_order(w, x, q8w).view(np.uint32))
+    ref = O.gemm(w, x, q8_weights=q8w)
+    err = np.abs(got - ref)
+    ok = (err <= REL * np.abs(ref)) | (err <= CANCEL * O.abs_terms(w, x, q8w))
+    assert np.all(ok)
+    return float(np.mean(err <= REL * np.abs(ref)))
+
+
+@pytest.mark.parametrize("q8w", [False, True])
+@pytest.mark.parametrize("nr,k,nc", [(1, 256, 1), (8, 256, 1), (9, 512, 2), (300, 4096, 1), (300, 4096, 8),
+                                      (131, 11008, 1), (131, 11008, 5), (64, 2048, 3)])
+def test_stream_kernel_matches_oracle(cuda, pkg, O, q8w, nr, k, nc):
+    w, x = make(O, nr, k, nc, q8w, 100 + nr)
+    got = pkg.gemv(dev(cuda, w), dev(cuda, x), q8_weights=q8w).cpu().numpy()
+    pkg.check_device_errors()
+    check_rows(O, got, w, x, q8w)
+
+
+@pytest.mark.parametrize("q8w", [False, True])
+@pytest.mark.parametrize("nr,k,nc", [(5, 32, 1), (17, 96, 2), (3, 4128, 1), (40, 1056, 8)])
+def test_generic_kernel_ragged_shapes(cuda, pkg, O, q8w, nr, k, nc):
+    # block counts that are not a multiple of 8 cannot use 16-byte bulk copies
+    w, x = make(O, nr, k, nc, q8w, 200 + nr)
+    got = pkg.gemv(dev(cuda, w), dev(cuda, x), q8_weights=q8w).cpu().numpy()
+    check_rows(O, got, w, x, q8w)
+
+
+@pytest.mark.parametrize("q8w", [False, True])
+def test_strict_order_is_bit_exact_with_sequential_oracle(cuda, pkg, O, q8w):
+    w, x = make(O, 77, 4096, 3, q8w, 300)
+    got = pkg.gemv(dev(cuda, w), dev(cuda, x), q8_weights=q8w, flags=pkg.FLAG_STRICT_ORDER).cpu().numpy()
+    assert np.array_equal(got.view(np.uint32), O.gemm(w, x, q8_weights=q8w, fold=O.FOLD_FMA).view(np.uint32))
+
+
+@pytest.mark.parametrize("q8w", [False, True])
+def test_block_sums_bit_exact(cuda, pkg, O, q8w):
+    w, x = make(O, 24, 4096, 2, q8w, 400)
+    got = pkg.block_sums(dev(cuda, w), dev(cuda, x), q8_weights=q8w).cpu().numpy()
+    assert np.array_equal(got, O.block_sums(w, x, q8w))
+
+
+def test_block_sums_extreme_bytes(cuda, pkg, O):
+    # all-0x00 / all-0xff nibbles against +-127 / -128 activations: the int32 range corners
+    w = np.zeros((4, 18 * 8), dtype=np.uint8)
+    w[1, :] = 0xFF
+    w[2, :] = 0x0F
+    w[3, :] = 0xF0
+    w.reshape(4, 8, 18)[:, :, :2] = np.array([0x3C00], dtype=np.uint16).view(np.uint8)
+    x = np.zeros((3, 34 * 8), dtype=np.uint8)
+    x[0, :] = 0x7F
+    x[1, :] = 0x80
+    x[2, :] = 0x81
+    x.reshape(3, 8, 34)[:, :, :2] = np.array([0x3C00], dtype=np.uint16).view(np.uint8)
+    got = pkg.block_sums(dev(cuda, w), dev(cuda, x)).cpu().numpy()
+    want = O.block_sums(w, x)
+    assert np.array_equal(got, want) and want.min() == -8 * 127 * 32 and want.max() == 8 * 128 * 32
+    y = pkg.gemv(dev(cuda, w), dev(cuda, x)).cpu().numpy()
+    assert np.array_equal(y, O.gemv_lane_order(w, x))
+
+
+def test_vec_dot_entry_points(cuda, pkg, O):
+    for q8w, fn, ofn in ((False, pkg.vec_dot_q4_0_q8_0, O.vec_dot_q4_0_q8_0), (True, pkg.vec_dot_q8_0_q8_0, O.vec_dot_q8_0_q8_0)):
+        w, x = make(O, 1, 4096, 1, q8w, 500)
+        got = fn(dev(cuda, w[0]), dev(cuda, x[0])).cpu().numpy()[0]
+        assert got == ofn(w[0], x[0], O.FOLD_FMA)
+
+
+def test_padded_strides(cuda, pkg, O):
+    # bx / by / bs larger than the packed sizes (the ABI passes them explicitly)
+    w, x = make(O, 50, 2048, 4, False, 600)
+    wt = cuda.zeros((50, w.shape[1] + 48), dtype=cuda.uint8, device="cuda")
+    wt[:, : w.shape[1]] = dev(cuda, w)
+    xt = cuda.zeros((4, x.shape[1] + 6), dtype=cuda.uint8, device="cuda")
+    xt[:, : x.shape[1]] = dev(cuda, x)
+    out = cuda.full((50, 7), -1.0, dtype=cuda.float32, device="cuda")
+    L = pkg.lib()
+    st = L.tcrv_cuda_gemv_q4_0_q8_0(2048, out.data_ptr(), wt.data_ptr(), xt.data_ptr(), xt.stride(0), 50, 4,
+                                    wt.stride(0), 7, 0, cuda.cuda.current_stream().cuda_stream)
+    assert st == 0
+    pkg.check_device_errors()
+    res = out.cpu().numpy()
+    assert np.array_equal(res[:, :4], O.gemv_lane_order(w, x)) and np.all(res[:, 4:] == -1.0)
+
+
+@pytest.mark.parametrize("nr,k", [(4096, 4096), (11008, 4096), (4096, 11008), (32000, 4096)])
+@pytest.mark.parametrize("nc", [1, 8])
+def test_llama7b_shapes_q4_0(cuda, pkg, O, nr, k, nc):
+    # BASELINE config: Q4_0 x Q8_0 decode GEMV, batch 1 and 8, W ~ N(0, 0.02), x ~ N(0, 1).
+    # Weights are quantised on the GPU (that kernel is checked bit-exact elsewhere) and the
+    # oracle consumes the same bytes; a row subset keeps the CPU side to seconds.
+    gen = cuda.Generator(device="cuda").manual_seed(nr + k)
+    wf = cuda.randn((nr, k), generator=gen, device="cuda") * 0.02
+    wd = pkg.quantize_q4_0(wf)
+    x = O.quantize_q8_0(O.fill_normal(nc * k, 700 + nc).reshape(nc, k))
+    got = pkg.gemv(wd, dev(cuda, x)).cpu().numpy()
+    pkg.check_device_errors()
+    rows = np.unique(np.concatenate([np.arange(0, nr, 97), np.arange(nr - 40, nr), np.arange(40)]))
+    w = wd.cpu().numpy()[rows]
+    frac = check_rows(O, got[rows], w, x, False)
+    assert frac > 0.95  # nearly all rows meet the plain relative bound
+    # linearity of the integer stage in the activations' scale: doubling every activation
+    # scale doubles every row exactly (fp32 scaling by 2 is exact)
+    x2 = x.copy().reshape(nc, -1, 34)
+    d = x2[:, :, :2].copy().view(np.float16)
+    x2[:, :, :2] = (d * np.float16(2)).view(np.uint8)
+    got2 = pkg.gemv(wd, dev(cuda, x2.reshape(nc, -1))).cpu().numpy()
+    assert np.array_equal(got2, got * np.float32(2))
+
+
+def test_q8_0_gemv_config(cuda, pkg, O):
+    # BASELINE config: W 11008x4096 Q8_0, x 1x4096 ~ N(0,1): per-block int32 bit-exact, rows 1e-5
+    wf = O.fill_normal(11008 * 4096, 801, 0, 0.02).reshape(11008, 4096)
+    w = O.quantize_q8_0(wf)
+    x = O.quantize_q8_0(O.fill_normal(4096, 802).reshape(1, 4096))
+    wd, xd = dev(cuda, w), dev(cuda, x)
+    got = pkg.gemv(wd, xd, q8_weights=True).cpu().numpy()
+    pkg.check_device_errors()
+    rows = np.arange(0, 11008, 43)
+    check_rows(O, got[rows], w[rows], x, True)
+    sums = pkg.block_sums(wd[:64], xd, q8_weights=True).cpu().numpy()
+    assert np.array_equal(sums, O.block_sums(w[:64], x, True))

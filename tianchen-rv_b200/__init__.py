@@ -1,0 +1,251 @@
+"""tianchen-rv_b200: sm_100a provider for the ggml-style Q8_0 / Q4_0 block path.
+
+This module is the Python face of ``libtcrv_cuda.so`` (the C ABI declared in
+``include/tcrv_cuda.h``).  Functions take CUDA ``torch.Tensor`` operands (torch is used for
+device memory and streams only) and launch on torch's current stream.  There is no CPU
+path: importing works without a GPU, but every compute call needs the built library and a
+CUDA device and raises otherwise.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+from . import build as _build
+
+QK = 32
+Q4_0_BLOCK = 18
+Q8_0_BLOCK = 34
+FLAG_NONE = 0
+FLAG_STRICT_ORDER = 1
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libtcrv_cuda.so")
+
+_sz = ctypes.c_size_t
+_p = ctypes.c_void_p
+_i = ctypes.c_int
+
+# name -> argtypes; every function returns an int status unless noted in _RESTYPES
+ABI = {
+    "tcrv_cuda_status_string": [_i],
+    "tcrv_cuda_last_error_text": [],
+    "tcrv_cuda_abi_version": [],
+    "tcrv_cuda_check_device_errors": [_p],
+    "tcrv_cuda_add_f32": [_p, _p, _p, _sz, _p],
+    "tcrv_cuda_add_i32": [_p, _p, _p, _sz, _p],
+    "tcrv_cuda_dequantize_i32_f32": [_p, ctypes.c_float, _p, _sz, _p],
+    "tcrv_cuda_dequantize_row_q8_0": [_p, _p, _sz, _p],
+    "tcrv_cuda_dequantize_row_q4_0": [_p, _p, _sz, _p],
+    "tcrv_cuda_quantize_row_q8_0": [_sz, _p, _p, _p],
+    "tcrv_cuda_quantize_row_q4_0": [_sz, _p, _p, _p],
+    "tcrv_cuda_vec_dot_q4_0_q8_0": [_sz, _p, _sz, _p, _sz, _p, _sz, ctypes.c_int32, _p],
+    "tcrv_cuda_vec_dot_q8_0_q8_0": [_sz, _p, _p, _p, _p],
+    "tcrv_cuda_gemv_q4_0_q8_0": [_sz, _p, _p, _p, _sz, _sz, _sz, _sz, _sz, ctypes.c_uint, _p],
+    "tcrv_cuda_gemv_q8_0_q8_0": [_sz, _p, _p, _p, _sz, _sz, _sz, _sz, _sz, ctypes.c_uint, _p],
+    "tcrv_cuda_block_sums_q4_0_q8_0": [_sz, _p, _p, _p, _sz, _sz, _sz, _sz, _p],
+    "tcrv_cuda_block_sums_q8_0_q8_0": [_sz, _p, _p, _p, _sz, _sz, _sz, _sz, _p],
+}
+_RESTYPES = {"tcrv_cuda_status_string": ctypes.c_char_p, "tcrv_cuda_last_error_text": ctypes.c_char_p}
+
+_lib = None
+
+
+class TcrvCudaError(RuntimeError):
+    def __init__(self, status: int, where: str, detail: str = ""):
+        self.status = status
+        super().__init__(f"{where} failed with status {status}" + (f": {detail}" if detail else ""))
+
+
+def lib() -> ctypes.CDLL:
+    """The loaded C-ABI library.  Raises if it has not been built (no fallback exists)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -c 'import __graft_entry__ as g; g.build()'`; "
+                "this provider has no CPU or PyTorch fallback"
+            )
+        L = ctypes.CDLL(LIB_PATH)
+        for name, argtypes in ABI.items():
+            fn = getattr(L, name)
+            fn.argtypes = argtypes
+            fn.restype = _RESTYPES.get(name, ctypes.c_int)
+        _lib = L
+    return _lib
+
+
+def build_library(force: bool = False) -> str:
+    return _build.build_library(force=force)
+
+
+def _check(status: int, where: str) -> None:
+    if status != 0:
+        L = lib()
+        detail = L.tcrv_cuda_status_string(status).decode()
+        extra = L.tcrv_cuda_last_error_text().decode()
+        raise TcrvCudaError(status, where, detail + (f" [{extra}]" if extra and status == -3 else ""))
+
+
+def _stream() -> int:
+    import torch
+
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _dev(t, dtype=None):
+    import torch
+
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise TypeError("operands must be CUDA torch tensors (device pointers cross the C ABI)")
+    if dtype is not None and t.dtype != dtype:
+        raise TypeError(f"expected dtype {dtype}, got {t.dtype}")
+    if not t.is_contiguous():
+        raise ValueError("operands must be contiguous")
+    return t.data_ptr()
+
+
+def check_device_errors() -> None:
+    """Synchronise the current stream and raise if a kernel's bounded wait expired."""
+    _check(lib().tcrv_cuda_check_device_errors(_stream()), "tcrv_cuda_check_device_errors")
+
+
+# ------------------------------------------------------------------ elementwise
+
+
+def add(lhs, rhs, out=None):
+    import torch
+
+    if out is None:
+        out = torch.empty_like(lhs)
+    if lhs.dtype == torch.float32:
+        fn, name = lib().tcrv_cuda_add_f32, "tcrv_cuda_add_f32"
+    elif lhs.dtype == torch.int32:
+        fn, name = lib().tcrv_cuda_add_i32, "tcrv_cuda_add_i32"
+    else:
+        raise TypeError("add supports float32 and int32")
+    _check(fn(_dev(lhs), _dev(rhs, lhs.dtype), _dev(out, lhs.dtype), lhs.numel(), _stream()), name)
+    return out
+
+
+def dequantize_i32_f32(lhs, scale: float, out=None):
+    import torch
+
+    if out is None:
+        out = torch.empty(lhs.shape, dtype=torch.float32, device=lhs.device)
+    _check(
+        lib().tcrv_cuda_dequantize_i32_f32(_dev(lhs, torch.int32), scale, _dev(out, torch.float32), lhs.numel(), _stream()),
+        "tcrv_cuda_dequantize_i32_f32",
+    )
+    return out
+
+
+def _rows(t, block_bytes: int):
+    if t.shape[-1] % block_bytes != 0:
+        raise ValueError(f"last dimension {t.shape[-1]} is not a whole number of {block_bytes}-byte blocks")
+    return t.shape[-1] // block_bytes
+
+
+def dequantize_q8_0(vx, out=None):
+    import torch
+
+    nb = _rows(vx, Q8_0_BLOCK)
+    if out is None:
+        out = torch.empty(vx.shape[:-1] + (nb * QK,), dtype=torch.float32, device=vx.device)
+    _check(lib().tcrv_cuda_dequantize_row_q8_0(_dev(vx, torch.uint8), _dev(out, torch.float32), out.numel(), _stream()),
+           "tcrv_cuda_dequantize_row_q8_0")
+    return out
+
+
+def dequantize_q4_0(vx, out=None):
+    import torch
+
+    nb = _rows(vx, Q4_0_BLOCK)
+    if out is None:
+        out = torch.empty(vx.shape[:-1] + (nb * QK,), dtype=torch.float32, device=vx.device)
+    _check(lib().tcrv_cuda_dequantize_row_q4_0(_dev(vx, torch.uint8), _dev(out, torch.float32), out.numel(), _stream()),
+           "tcrv_cuda_dequantize_row_q4_0")
+    return out
+
+
+def quantize_q8_0(x, out=None):
+    import torch
+
+    if x.shape[-1] % QK != 0:
+        raise ValueError("last dimension must be a multiple of 32")
+    if out is None:
+        out = torch.empty(x.shape[:-1] + (x.shape[-1] // QK * Q8_0_BLOCK,), dtype=torch.uint8, device=x.device)
+    _check(lib().tcrv_cuda_quantize_row_q8_0(x.numel(), _dev(x, torch.float32), _dev(out, torch.uint8), _stream()),
+           "tcrv_cuda_quantize_row_q8_0")
+    return out
+
+
+def quantize_q4_0(x, out=None):
+    import torch
+
+    if x.shape[-1] % QK != 0:
+        raise ValueError("last dimension must be a multiple of 32")
+    if out is None:
+        out = torch.empty(x.shape[:-1] + (x.shape[-1] // QK * Q4_0_BLOCK,), dtype=torch.uint8, device=x.device)
+    _check(lib().tcrv_cuda_quantize_row_q4_0(x.numel(), _dev(x, torch.float32), _dev(out, torch.uint8), _stream()),
+           "tcrv_cuda_quantize_row_q4_0")
+    return out
+
+
+# ------------------------------------------------------------------- block dots
+
+
+def _matrix_args(w, x, wblock: int):
+    import torch
+
+    if w.dim() != 2 or x.dim() != 2:
+        raise ValueError("weights are (rows, row_bytes), activations are (columns, column_bytes)")
+    nb = _rows(x, Q8_0_BLOCK)
+    if _rows(w, wblock) != nb:
+        raise ValueError("weights and activations disagree on the number of blocks per row")
+    return nb * QK, w.shape[0], x.shape[0], w.stride(0), x.stride(0), torch
+
+
+def vec_dot_q4_0_q8_0(w_row, x_row):
+    """One Q4_0 x Q8_0 block dot (sequential fold); returns a 1-element float32 tensor."""
+    import torch
+
+    n = _rows(x_row, Q8_0_BLOCK) * QK
+    s = torch.empty(1, dtype=torch.float32, device=w_row.device)
+    _check(lib().tcrv_cuda_vec_dot_q4_0_q8_0(n, _dev(s), 0, _dev(w_row, torch.uint8), 0, _dev(x_row, torch.uint8), 0, 1,
+                                             _stream()), "tcrv_cuda_vec_dot_q4_0_q8_0")
+    return s
+
+
+def vec_dot_q8_0_q8_0(w_row, x_row):
+    import torch
+
+    n = _rows(x_row, Q8_0_BLOCK) * QK
+    s = torch.empty(1, dtype=torch.float32, device=w_row.device)
+    _check(lib().tcrv_cuda_vec_dot_q8_0_q8_0(n, _dev(s), _dev(w_row, torch.uint8), _dev(x_row, torch.uint8), _stream()),
+           "tcrv_cuda_vec_dot_q8_0_q8_0")
+    return s
+
+
+def gemv(w, x, q8_weights: bool = False, flags: int = FLAG_NONE, out=None):
+    """out[row, col] = block dot(weight row, activation column); x has at most 8 columns."""
+    wblock = Q8_0_BLOCK if q8_weights else Q4_0_BLOCK
+    n, nr, nc, bx, by, torch = _matrix_args(w, x, wblock)
+    if out is None:
+        out = torch.empty((nr, nc), dtype=torch.float32, device=w.device)
+    name = "tcrv_cuda_gemv_q8_0_q8_0" if q8_weights else "tcrv_cuda_gemv_q4_0_q8_0"
+    fn = getattr(lib(), name)
+    _check(fn(n, _dev(out, torch.float32), w.data_ptr(), x.data_ptr(), by, nr, nc, bx, out.stride(0), flags, _stream()),
+           name)
+    return out
+
+
+def block_sums(w, x, q8_weights: bool = False):
+    """Per-block int32 sums, shape (rows, columns, blocks): the integer stage, for parity."""
+    wblock = Q8_0_BLOCK if q8_weights else Q4_0_BLOCK
+    n, nr, nc, bx, by, torch = _matrix_args(w, x, wblock)
+    out = torch.empty((nr, nc, n // QK), dtype=torch.int32, device=w.device)
+    name = "tcrv_cuda_block_sums_q8_0_q8_0" if q8_weights else "tcrv_cuda_block_sums_q4_0_q8_0"
+    fn = getattr(lib(), name)
+    _check(fn(n, _dev(out), w.data_ptr(), x.data_ptr(), by, nr, nc, bx, _stream()), name)
+    return out

@@ -1,0 +1,196 @@
+// extern "C" surface of the provider: argument validation, status codes, error text and the
+// device-side error word.  Every function here takes device pointers and launches on the
+// caller's stream; none allocates, and none has a CPU fallback.
+#include <stdio.h>
+#include <string.h>
+
+#include "launchers.h"
+#include "tcrv_common.cuh"
+
+namespace tcrv {
+
+__device__ int g_device_error = 0;
+
+namespace {
+thread_local char t_error_text[256] = "";
+}
+
+int record_cuda_error(cudaError_t err, const char *what) {
+  snprintf(t_error_text, sizeof t_error_text, "%s: %s (%s)", what, cudaGetErrorName(err), cudaGetErrorString(err));
+  (void)cudaGetLastError();  // clear the sticky-free error state
+  return TCRV_CUDA_ERR_CUDA;
+}
+
+int sm_count() {
+  static int cached[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64)
+    return kNumSMsB200;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+      n = kNumSMsB200;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+namespace {
+
+inline cudaStream_t as_stream(tcrv_cuda_stream s) { return static_cast<cudaStream_t>(s); }
+
+// Shared checks of the GEMV/GEMM-shaped entry points.
+int check_matrix_args(size_t n, const void *out, const void *vx, const void *vy, size_t by, size_t nr, size_t nc,
+                      size_t bx, size_t out_stride, size_t weight_block_bytes) {
+  if (n % TCRV_QK != 0)
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  if (nr == 0 || nc == 0)
+    return TCRV_CUDA_OK;
+  if (!out || !vx || !vy)
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  const size_t nb = n / TCRV_QK;
+  if (nb > 0xffffffffull / 64 || nr > 0xffffffffull || nc > 0xffffffffull)
+    return TCRV_CUDA_ERR_UNSUPPORTED;
+  if (nr > 1 && bx < nb * weight_block_bytes)
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  if (nc > 1 && by < nb * TCRV_Q8_0_BLOCK_BYTES)
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  if (nr > 1 && out_stride < nc)
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  return TCRV_CUDA_OK;
+}
+
+}  // namespace
+}  // namespace tcrv
+
+using namespace tcrv;
+
+extern "C" {
+
+const char *tcrv_cuda_status_string(int status) {
+  switch (status) {
+    case TCRV_CUDA_OK:
+      return "ok";
+    case TCRV_CUDA_ERR_INVALID_ARGUMENT:
+      return "invalid argument";
+    case TCRV_CUDA_ERR_UNSUPPORTED:
+      return "unsupported facts";
+    case TCRV_CUDA_ERR_CUDA:
+      return "CUDA runtime error";
+    case TCRV_CUDA_ERR_DEVICE_TIMEOUT:
+      return "device-side wait timed out";
+    case TCRV_CUDA_ERR_WORKSPACE:
+      return "workspace missing or too small";
+    default:
+      return "unknown status";
+  }
+}
+
+const char *tcrv_cuda_last_error_text(void) { return t_error_text; }
+
+int tcrv_cuda_abi_version(void) { return 1; }
+
+int tcrv_cuda_check_device_errors(tcrv_cuda_stream stream) {
+  TCRV_CUDA_TRY(cudaStreamSynchronize(as_stream(stream)));
+  int word = 0;
+  TCRV_CUDA_TRY(cudaMemcpyFromSymbol(&word, g_device_error, sizeof word));
+  if (word != 0) {
+    const int zero = 0;
+    TCRV_CUDA_TRY(cudaMemcpyToSymbol(g_device_error, &zero, sizeof zero));
+    return TCRV_CUDA_ERR_DEVICE_TIMEOUT;
+  }
+  return TCRV_CUDA_OK;
+}
+
+int tcrv_cuda_add_f32(const float *lhs, const float *rhs, float *out, size_t n, tcrv_cuda_stream stream) {
+  if (n != 0 && (!lhs || !rhs || !out))
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  return launch_add_f32(lhs, rhs, out, n, as_stream(stream));
+}
+
+int tcrv_cuda_add_i32(const int32_t *lhs, const int32_t *rhs, int32_t *out, size_t n, tcrv_cuda_stream stream) {
+  if (n != 0 && (!lhs || !rhs || !out))
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  return launch_add_i32(lhs, rhs, out, n, as_stream(stream));
+}
+
+int tcrv_cuda_dequantize_i32_f32(const int32_t *lhs, float scale, float *out, size_t n, tcrv_cuda_stream stream) {
+  if (n != 0 && (!lhs || !out))
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  return launch_dequantize_i32_f32(lhs, scale, out, n, as_stream(stream));
+}
+
+int tcrv_cuda_dequantize_row_q8_0(const uint8_t *vx, float *y, size_t n, tcrv_cuda_stream stream) {
+  if (n % TCRV_QK != 0 || (n != 0 && (!vx || !y)))
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  return launch_dequantize_row_q8_0(vx, y, n, as_stream(stream));
+}
+
+int tcrv_cuda_dequantize_row_q4_0(const uint8_t *vx, float *y, size_t n, tcrv_cuda_stream stream) {
+  if (n % TCRV_QK != 0 || (n != 0 && (!vx || !y)))
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  return launch_dequantize_row_q4_0(vx, y, n, as_stream(stream));
+}
+
+int tcrv_cuda_quantize_row_q8_0(size_t n, const float *x, uint8_t *vy, tcrv_cuda_stream stream) {
+  if (n % TCRV_QK != 0 || (n != 0 && (!x || !vy)))
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  return launch_quantize_row_q8_0(n, x, vy, as_stream(stream));
+}
+
+int tcrv_cuda_quantize_row_q4_0(size_t n, const float *x, uint8_t *vx, tcrv_cuda_stream stream) {
+  if (n % TCRV_QK != 0 || (n != 0 && (!x || !vx)))
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  return launch_quantize_row_q4_0(n, x, vx, as_stream(stream));
+}
+
+int tcrv_cuda_vec_dot_q4_0_q8_0(size_t n, float *s, size_t bs, const uint8_t *vx, size_t bx, const uint8_t *vy,
+                                size_t by, int32_t nrc, tcrv_cuda_stream stream) {
+  (void)bs;
+  (void)bx;
+  (void)by;
+  (void)nrc;  // as in the reference kernel, only n, s, vx, vy are consumed
+  if (n % TCRV_QK != 0 || !s || (n != 0 && (!vx || !vy)))
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  return launch_gemv<false>(n, s, vx, vy, 0, 1, 1, 0, 1, TCRV_CUDA_FLAG_STRICT_ORDER, as_stream(stream));
+}
+
+int tcrv_cuda_vec_dot_q8_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, tcrv_cuda_stream stream) {
+  if (n % TCRV_QK != 0 || !s || (n != 0 && (!vx || !vy)))
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  return launch_gemv<true>(n, s, vx, vy, 0, 1, 1, 0, 1, TCRV_CUDA_FLAG_STRICT_ORDER, as_stream(stream));
+}
+
+int tcrv_cuda_gemv_q4_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by, size_t nr,
+                             size_t nc, size_t bx, size_t bs, unsigned flags, tcrv_cuda_stream stream) {
+  const int st = check_matrix_args(n, s, vx, vy, by, nr, nc, bx, bs, TCRV_Q4_0_BLOCK_BYTES);
+  if (st != TCRV_CUDA_OK)
+    return st;
+  return launch_gemv<false>(n, s, vx, vy, by, nr, nc, bx, bs, flags, as_stream(stream));
+}
+
+int tcrv_cuda_gemv_q8_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by, size_t nr,
+                             size_t nc, size_t bx, size_t bs, unsigned flags, tcrv_cuda_stream stream) {
+  const int st = check_matrix_args(n, s, vx, vy, by, nr, nc, bx, bs, TCRV_Q8_0_BLOCK_BYTES);
+  if (st != TCRV_CUDA_OK)
+    return st;
+  return launch_gemv<true>(n, s, vx, vy, by, nr, nc, bx, bs, flags, as_stream(stream));
+}
+
+int tcrv_cuda_block_sums_q4_0_q8_0(size_t n, int32_t *sumi, const uint8_t *vx, const uint8_t *vy, size_t by,
+                                   size_t nr, size_t nc, size_t bx, tcrv_cuda_stream stream) {
+  const int st = check_matrix_args(n, sumi, vx, vy, by, nr, nc, bx, nc, TCRV_Q4_0_BLOCK_BYTES);
+  if (st != TCRV_CUDA_OK)
+    return st;
+  return launch_block_sums<false>(n, sumi, vx, vy, by, nr, nc, bx, as_stream(stream));
+}
+
+int tcrv_cuda_block_sums_q8_0_q8_0(size_t n, int32_t *sumi, const uint8_t *vx, const uint8_t *vy, size_t by,
+                                   size_t nr, size_t nc, size_t bx, tcrv_cuda_stream stream) {
+  const int st = check_matrix_args(n, sumi, vx, vy, by, nr, nc, bx, nc, TCRV_Q8_0_BLOCK_BYTES);
+  if (st != TCRV_CUDA_OK)
+    return st;
+  return launch_block_sums<true>(n, sumi, vx, vy, by, nr, nc, bx, as_stream(stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,248 @@
+// GEMV launchers: the streaming kernel (gemv_stream.cuh) when the operands allow 16-byte
+// bulk copies, otherwise a generic warp-per-row kernel that accepts any alignment and any
+// block count and also implements the strict (sequential) fold order.  Plus the debug kernel
+// that exposes the integer stage (per-block int32 sums).
+#include "gemv_stream.cuh"
+
+namespace tcrv {
+
+namespace {
+
+// Integer stage of one block straight from global memory, byte-granular (no alignment
+// assumptions).
+template <bool kQ8W>
+__device__ __forceinline__ int block_sumi_bytes(const uint8_t *wb, const uint8_t *xb) {
+  uint32_t x[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j)
+    x[j] = load_u32_bytes(xb + 2 + 4 * j);
+  if constexpr (kQ8W) {
+    uint32_t w[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      w[j] = load_u32_bytes(wb + 2 + 4 * j);
+    return q8_0_q8_0_sumi(w, x);
+  } else {
+    uint32_t w[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      w[j] = load_u32_bytes(wb + 2 + 4 * j);
+    return q4_0_q8_0_sumi(w, x, 8 * sum_s8x32(x));
+  }
+}
+
+template <bool kQ8W>
+__device__ __forceinline__ float fold_any(float acc, int sumi, float dw, float dx) {
+  if constexpr (kQ8W)
+    return fold_q8(acc, sumi, dw, dx);
+  else
+    return fold_q4(acc, sumi, dw, dx);
+}
+
+// One warp per (row, column).  kStrict = false reproduces the streaming kernel's order
+// (lane l owns block pairs l, l+32, ...; butterfly); kStrict = true folds all blocks in
+// ascending order: every lane computes one block of a group of 32, then the 32 terms are
+// folded one after another (each lane repeats the same fold, so no broadcast is needed).
+template <bool kQ8W, bool kStrict>
+__global__ void __launch_bounds__(256) gemv_generic_kernel(const uint8_t *__restrict__ vx,
+                                                           const uint8_t *__restrict__ vy, float *__restrict__ s,
+                                                           size_t bx, size_t by, size_t bs, uint32_t nr, uint32_t nc,
+                                                           uint32_t nb) {
+  constexpr int WB = WeightFormat<kQ8W>::kBlockBytes;
+  const int lane = threadIdx.x & 31;
+  const size_t warp = (static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const size_t nwarps = (static_cast<size_t>(gridDim.x) * blockDim.x) >> 5;
+  const size_t total = static_cast<size_t>(nr) * nc;
+  for (size_t item = warp; item < total; item += nwarps) {
+    const size_t row = item / nc, col = item - row * nc;
+    const uint8_t *wr = vx + row * bx;
+    const uint8_t *xc = vy + col * by;
+    float acc = 0.0f;
+    if constexpr (kStrict) {
+      for (uint32_t base = 0; base < nb; base += 32) {
+        const uint32_t ib = base + lane;
+        float term_a = 0.0f, term_b = 0.0f;
+        if (ib < nb) {
+          const uint8_t *wb = wr + static_cast<size_t>(ib) * WB;
+          const uint8_t *xb = xc + static_cast<size_t>(ib) * kQ8Block;
+          const float dw = half_bits_to_float(load_u16(wb));
+          const float dx = half_bits_to_float(load_u16(xb));
+          const float fs = __int2float_rn(block_sumi_bytes<kQ8W>(wb, xb));
+          if constexpr (kQ8W) {
+            term_a = fs;
+            term_b = __fmul_rn(dw, dx);
+          } else {
+            term_a = __fmul_rn(fs, dw);
+            term_b = dx;
+          }
+        }
+        const uint32_t live = min(32u, nb - base);
+        for (uint32_t j = 0; j < live; ++j)
+          acc = __fmaf_rn(__shfl_sync(0xffffffffu, term_a, j), __shfl_sync(0xffffffffu, term_b, j), acc);
+      }
+    } else {
+      for (uint32_t p = lane; 2 * p < nb; p += 32) {
+#pragma unroll
+        for (uint32_t h = 0; h < 2; ++h) {
+          const uint32_t ib = 2 * p + h;
+          if (ib < nb) {
+            const uint8_t *wb = wr + static_cast<size_t>(ib) * WB;
+            const uint8_t *xb = xc + static_cast<size_t>(ib) * kQ8Block;
+            acc = fold_any<kQ8W>(acc, block_sumi_bytes<kQ8W>(wb, xb), half_bits_to_float(load_u16(wb)),
+                                 half_bits_to_float(load_u16(xb)));
+          }
+        }
+      }
+#pragma unroll
+      for (int off = 16; off >= 1; off >>= 1)
+        acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, off));
+    }
+    if (lane == 0)
+      s[row * bs + col] = acc;
+  }
+}
+
+template <bool kQ8W>
+__global__ void __launch_bounds__(256) block_sums_kernel(const uint8_t *__restrict__ vx,
+                                                         const uint8_t *__restrict__ vy, int32_t *__restrict__ sumi,
+                                                         size_t bx, size_t by, uint32_t nr, uint32_t nc, uint32_t nb) {
+  constexpr int WB = WeightFormat<kQ8W>::kBlockBytes;
+  const size_t total = static_cast<size_t>(nr) * nc * nb;
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const size_t ib = i % nb, rc = i / nb, col = rc % nc, row = rc / nc;
+    sumi[i] = block_sumi_bytes<kQ8W>(vx + row * bx + ib * WB, vy + col * by + ib * kQ8Block);
+  }
+}
+
+constexpr size_t kMaxDynamicSmem = 227 * 1024;
+
+template <bool kQ8W, int kCols, int kXRegPairs>
+int launch_stream_instance(const GemvArgs &args, int grid, size_t smem, cudaStream_t stream) {
+  auto kernel = gemv_stream_kernel<kQ8W, kCols, kXRegPairs>;
+  static bool configured[64] = {};
+  int dev = 0;
+  TCRV_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 64 && !configured[dev]) {
+    TCRV_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(kMaxDynamicSmem)));
+    configured[dev] = true;
+  }
+  kernel<<<grid, kGemvThreads, smem, stream>>>(args);
+  TCRV_CUDA_TRY(cudaGetLastError());
+  return TCRV_CUDA_OK;
+}
+
+template <bool kQ8W>
+int launch_stream(const GemvArgs &args, uint32_t nc, int grid, size_t smem, cudaStream_t stream) {
+  const uint32_t npairs = args.nb / 2;
+  switch (nc) {
+    case 1:
+      if (npairs <= 64)
+        return launch_stream_instance<kQ8W, 1, 2>(args, grid, smem, stream);
+      if (npairs <= 192)
+        return launch_stream_instance<kQ8W, 1, 6>(args, grid, smem, stream);
+      return launch_stream_instance<kQ8W, 1, 0>(args, grid, smem, stream);
+    case 2:
+      return launch_stream_instance<kQ8W, 2, 0>(args, grid, smem, stream);
+    case 3:
+      return launch_stream_instance<kQ8W, 3, 0>(args, grid, smem, stream);
+    case 4:
+      return launch_stream_instance<kQ8W, 4, 0>(args, grid, smem, stream);
+    case 5:
+      return launch_stream_instance<kQ8W, 5, 0>(args, grid, smem, stream);
+    case 6:
+      return launch_stream_instance<kQ8W, 6, 0>(args, grid, smem, stream);
+    case 7:
+      return launch_stream_instance<kQ8W, 7, 0>(args, grid, smem, stream);
+    case 8:
+      return launch_stream_instance<kQ8W, 8, 0>(args, grid, smem, stream);
+    default:
+      return TCRV_CUDA_ERR_UNSUPPORTED;
+  }
+}
+
+inline bool multiple_of(const void *p, uintptr_t m) { return reinterpret_cast<uintptr_t>(p) % m == 0; }
+
+}  // namespace
+
+template <bool kQ8W>
+int launch_gemv(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by, size_t nr, size_t nc,
+                size_t bx, size_t bs, unsigned flags, cudaStream_t stream) {
+  if (nr == 0 || nc == 0)
+    return TCRV_CUDA_OK;
+  constexpr int WB = WeightFormat<kQ8W>::kBlockBytes;
+  const uint32_t nb = static_cast<uint32_t>(n / kQK);
+  const bool strict = (flags & TCRV_CUDA_FLAG_STRICT_ORDER) != 0;
+  const size_t row_bytes = static_cast<size_t>(nb) * WB;
+
+  if (!strict && nb > 0 && nb % 8 == 0 && nc <= kGemvMaxCols && multiple_of(vx, 16) && bx % 16 == 0 &&
+      multiple_of(vy, 2) && by % 2 == 0) {
+    const size_t fixed = kGemvBarrierBytes + nc * static_cast<size_t>(gemv_xcol_bytes(nb));
+    const size_t stage = kGemvRowsPerChunk * row_bytes;
+    if (fixed + 2 * stage <= kMaxDynamicSmem) {
+      size_t ns = (kMaxDynamicSmem - fixed) / stage;
+      if (ns > kGemvMaxStages)
+        ns = kGemvMaxStages;
+      GemvArgs args;
+      args.vx = vx;
+      args.vy = vy;
+      args.s = s;
+      args.bx = bx;
+      args.by = by;
+      args.bs = bs;
+      args.nr = static_cast<uint32_t>(nr);
+      args.nb = nb;
+      args.row_bytes = static_cast<uint32_t>(row_bytes);
+      args.nstages = static_cast<uint32_t>(ns);
+      const size_t chunks = (nr + kGemvRowsPerChunk - 1) / kGemvRowsPerChunk;
+      const int sms = sm_count();
+      const int grid = static_cast<int>(chunks < static_cast<size_t>(sms) ? chunks : sms);
+      return launch_stream<kQ8W>(args, static_cast<uint32_t>(nc), grid, fixed + ns * stage, stream);
+    }
+  }
+
+  // generic path
+  const size_t items = nr * nc;
+  size_t blocks = (items + 7) / 8;
+  const size_t cap = static_cast<size_t>(sm_count()) * 8;
+  if (blocks > cap)
+    blocks = cap;
+  if (strict)
+    gemv_generic_kernel<kQ8W, true><<<static_cast<int>(blocks), 256, 0, stream>>>(
+        vx, vy, s, bx, by, bs, static_cast<uint32_t>(nr), static_cast<uint32_t>(nc), nb);
+  else
+    gemv_generic_kernel<kQ8W, false><<<static_cast<int>(blocks), 256, 0, stream>>>(
+        vx, vy, s, bx, by, bs, static_cast<uint32_t>(nr), static_cast<uint32_t>(nc), nb);
+  TCRV_CUDA_TRY(cudaGetLastError());
+  return TCRV_CUDA_OK;
+}
+
+template int launch_gemv<false>(size_t, float *, const uint8_t *, const uint8_t *, size_t, size_t, size_t, size_t,
+                                size_t, unsigned, cudaStream_t);
+template int launch_gemv<true>(size_t, float *, const uint8_t *, const uint8_t *, size_t, size_t, size_t, size_t,
+                               size_t, unsigned, cudaStream_t);
+
+template <bool kQ8W>
+int launch_block_sums(size_t n, int32_t *sumi, const uint8_t *vx, const uint8_t *vy, size_t by, size_t nr,
+                      size_t nc, size_t bx, cudaStream_t stream) {
+  const uint32_t nb = static_cast<uint32_t>(n / kQK);
+  const size_t total = nr * nc * nb;
+  if (total == 0)
+    return TCRV_CUDA_OK;
+  size_t blocks = (total + 255) / 256;
+  const size_t cap = static_cast<size_t>(sm_count()) * 8;
+  if (blocks > cap)
+    blocks = cap;
+  block_sums_kernel<kQ8W><<<static_cast<int>(blocks), 256, 0, stream>>>(
+      vx, vy, sumi, bx, by, static_cast<uint32_t>(nr), static_cast<uint32_t>(nc), nb);
+  TCRV_CUDA_TRY(cudaGetLastError());
+  return TCRV_CUDA_OK;
+}
+
+template int launch_block_sums<false>(size_t, int32_t *, const uint8_t *, const uint8_t *, size_t, size_t, size_t,
+                                      size_t, cudaStream_t);
+template int launch_block_sums<true>(size_t, int32_t *, const uint8_t *, const uint8_t *, size_t, size_t, size_t,
+                                     size_t, cudaStream_t);
+
+}  // namespace tcrv

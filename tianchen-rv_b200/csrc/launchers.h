@@ -1,0 +1,25 @@
+// Internal launch functions behind the C ABI (device pointers, already validated).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace tcrv {
+
+int launch_add_f32(const float *lhs, const float *rhs, float *out, size_t n, cudaStream_t stream);
+int launch_add_i32(const int32_t *lhs, const int32_t *rhs, int32_t *out, size_t n, cudaStream_t stream);
+int launch_dequantize_i32_f32(const int32_t *lhs, float scale, float *out, size_t n, cudaStream_t stream);
+int launch_dequantize_row_q8_0(const uint8_t *vx, float *y, size_t n, cudaStream_t stream);
+int launch_dequantize_row_q4_0(const uint8_t *vx, float *y, size_t n, cudaStream_t stream);
+int launch_quantize_row_q8_0(size_t n, const float *x, uint8_t *vy, cudaStream_t stream);
+int launch_quantize_row_q4_0(size_t n, const float *x, uint8_t *vx, cudaStream_t stream);
+
+template <bool kQ8W>
+int launch_gemv(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by, size_t nr, size_t nc,
+                size_t bx, size_t bs, unsigned flags, cudaStream_t stream);
+template <bool kQ8W>
+int launch_block_sums(size_t n, int32_t *sumi, const uint8_t *vx, const uint8_t *vy, size_t by, size_t nr,
+                      size_t nc, size_t bx, cudaStream_t stream);
+
+}  // namespace tcrv

@@ -1,0 +1,97 @@
+// Shared device/host helpers for the sm_100a kernels of the Q8_0 / Q4_0 block path.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#include "tcrv_cuda.h"
+
+namespace tcrv {
+
+constexpr int kQK = TCRV_QK;
+constexpr int kQ4Block = TCRV_Q4_0_BLOCK_BYTES;
+constexpr int kQ8Block = TCRV_Q8_0_BLOCK_BYTES;
+constexpr int kNumSMsB200 = 148;
+
+// Device-side error word: kernels with bounded waits OR a code into it when a wait
+// expires.  Read and cleared by tcrv_cuda_check_device_errors().
+extern __device__ int g_device_error;
+constexpr int kDevErrBarrierTimeout = 1;
+
+// Records a failing CUDA runtime call for tcrv_cuda_last_error_text().
+int record_cuda_error(cudaError_t err, const char *what);
+
+#define TCRV_CUDA_TRY(expr)                                      \
+  do {                                                           \
+    cudaError_t tcrv_err_ = (expr);                              \
+    if (tcrv_err_ != cudaSuccess)                                \
+      return ::tcrv::record_cuda_error(tcrv_err_, #expr);        \
+  } while (0)
+
+// Number of SMs of the current device (cached per device).
+int sm_count();
+
+__device__ __forceinline__ float half_bits_to_float(uint32_t bits16) {
+  return __half2float(__ushort_as_half(static_cast<unsigned short>(bits16)));
+}
+
+// Unaligned-safe little-endian reads from global or shared memory.
+__device__ __forceinline__ uint32_t load_u16(const uint8_t *p) {
+  return static_cast<uint32_t>(p[0]) | (static_cast<uint32_t>(p[1]) << 8);
+}
+__device__ __forceinline__ uint32_t load_u32_bytes(const uint8_t *p) {
+  return static_cast<uint32_t>(p[0]) | (static_cast<uint32_t>(p[1]) << 8) |
+         (static_cast<uint32_t>(p[2]) << 16) | (static_cast<uint32_t>(p[3]) << 24);
+}
+
+// Signed 4x int8 dot product with int32 accumulate.
+__device__ __forceinline__ int dp4a_s8(uint32_t a, uint32_t b, int c) {
+  return __dp4a(static_cast<int>(a), static_cast<int>(b), c);
+}
+
+// Sum of the 32 signed bytes held in eight 32-bit words.
+__device__ __forceinline__ int sum_s8x32(const uint32_t (&q)[8]) {
+  int s = 0;
+#pragma unroll
+  for (int j = 0; j < 8; ++j)
+    s = dp4a_s8(q[j], 0x01010101u, s);
+  return s;
+}
+
+// Integer stage of the Q4_0 x Q8_0 block dot.  w[j] holds weight bytes 4j..4j+3 (byte j:
+// element j in the low nibble, element j+16 in the high nibble); x[j] holds activation
+// elements 4j..4j+3.  Returns sum((nibble - 8) * x) exactly, using the identity
+// sum((nib-8)*x) = sum(nib*x) - 8*sum(x); `x_sum8` is 8*sum(x).
+__device__ __forceinline__ int q4_0_q8_0_sumi(const uint32_t (&w)[4], const uint32_t (&x)[8], int x_sum8) {
+  int s = 0;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    uint32_t lo = w[j] & 0x0f0f0f0fu;
+    uint32_t hi = (w[j] >> 4) & 0x0f0f0f0fu;
+    s = dp4a_s8(lo, x[j], s);
+    s = dp4a_s8(hi, x[4 + j], s);
+  }
+  return s - x_sum8;
+}
+
+__device__ __forceinline__ int q8_0_q8_0_sumi(const uint32_t (&w)[8], const uint32_t (&x)[8]) {
+  int s = 0;
+#pragma unroll
+  for (int j = 0; j < 8; ++j)
+    s = dp4a_s8(w[j], x[j], s);
+  return s;
+}
+
+// fp32 folds, fused form (one rounding for the multiply-add):
+//   Q4_0 x Q8_0: sumf = fma((float)sumi * d_x, d_y, sumf)
+//   Q8_0 x Q8_0: sumf = fma((float)sumi, d_x * d_y, sumf)
+__device__ __forceinline__ float fold_q4(float sumf, int sumi, float dx, float dy) {
+  return __fmaf_rn(__fmul_rn(__int2float_rn(sumi), dx), dy, sumf);
+}
+__device__ __forceinline__ float fold_q8(float sumf, int sumi, float dx, float dy) {
+  return __fmaf_rn(__int2float_rn(sumi), __fmul_rn(dx, dy), sumf);
+}
+
+}  // namespace tcrv
