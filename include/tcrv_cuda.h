@@ -116,6 +116,36 @@ int tcrv_cuda_gemv_q8_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_
                              size_t nr, size_t nc, size_t bx, size_t bs, unsigned flags,
                              tcrv_cuda_stream stream);
 
+/* ---- prefill GEMM (tensor cores) ---------------------------------------------------- */
+
+/* The tensor-core GEMM reads a planar copy of its operands (int8 values and fp32 scales in
+ * separate, TMA-friendly matrices).  That copy lives in caller-provided device memory:
+ *   tcrv_cuda_gemm_weights_bytes(n, nr)        bytes for the prepared weights
+ *   tcrv_cuda_gemm_acts_workspace_bytes(n, nc) bytes for the per-call activation copy
+ *   tcrv_cuda_gemm_workspace_bytes(n, nr, nc)  both, for the plain-format entry point
+ * Pointers must be 256-byte aligned.  Preparing static weights once is this provider's
+ * weight-layout contract, the counterpart of the reference's repacked-weight contract
+ * (lib/Plugin/RVV/RVVLowerQuantContraction.cpp:80-91). */
+size_t tcrv_cuda_gemm_weights_bytes(size_t n, size_t nr);
+size_t tcrv_cuda_gemm_acts_workspace_bytes(size_t n, size_t nc);
+size_t tcrv_cuda_gemm_workspace_bytes(size_t n, size_t nr, size_t nc);
+
+/* block_q4_0 rows (stride bx) -> prepared weights. */
+int tcrv_cuda_gemm_prepare_weights_q4_0(size_t n, const uint8_t *vx, size_t bx, size_t nr, void *prepared,
+                                        size_t prepared_bytes, tcrv_cuda_stream stream);
+
+/* Plain-format GEMM, same contract and ABI order as tcrv_cuda_gemv_q4_0_q8_0 (replaces
+ * `tcrv_rvv.q4_0_q8_0_gemm`, lib/Conversion/RVV/RVVToEmitCBlockQuantLinear.cpp:1691-2120) for
+ * any nc: prepares both operands into `workspace`, then runs the contraction. */
+int tcrv_cuda_gemm_q4_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by, size_t nr,
+                             size_t nc, size_t bx, size_t bs, void *workspace, size_t workspace_bytes,
+                             unsigned flags, tcrv_cuda_stream stream);
+
+/* The same with weights prepared beforehand; `workspace` only holds the activation copy. */
+int tcrv_cuda_gemm_q4_0_q8_0_prepared(size_t n, float *s, const void *prepared_weights, const uint8_t *vy,
+                                      size_t by, size_t nr, size_t nc, size_t bs, void *workspace,
+                                      size_t workspace_bytes, unsigned flags, tcrv_cuda_stream stream);
+
 /* Debug variant of the integer stage: sumi[(ir*nc + col)*(n/32) + ib], bit-exact int32. */
 int tcrv_cuda_block_sums_q4_0_q8_0(size_t n, int32_t *sumi, const uint8_t *vx, const uint8_t *vy,
                                    size_t by, size_t nr, size_t nc, size_t bx, tcrv_cuda_stream stream);

@@ -43,10 +43,22 @@ ABI = {
     "tcrv_cuda_vec_dot_q8_0_q8_0": [_sz, _p, _p, _p, _p],
     "tcrv_cuda_gemv_q4_0_q8_0": [_sz, _p, _p, _p, _sz, _sz, _sz, _sz, _sz, ctypes.c_uint, _p],
     "tcrv_cuda_gemv_q8_0_q8_0": [_sz, _p, _p, _p, _sz, _sz, _sz, _sz, _sz, ctypes.c_uint, _p],
+    "tcrv_cuda_gemm_weights_bytes": [_sz, _sz],
+    "tcrv_cuda_gemm_acts_workspace_bytes": [_sz, _sz],
+    "tcrv_cuda_gemm_workspace_bytes": [_sz, _sz, _sz],
+    "tcrv_cuda_gemm_prepare_weights_q4_0": [_sz, _p, _sz, _sz, _p, _sz, _p],
+    "tcrv_cuda_gemm_q4_0_q8_0": [_sz, _p, _p, _p, _sz, _sz, _sz, _sz, _sz, _p, _sz, ctypes.c_uint, _p],
+    "tcrv_cuda_gemm_q4_0_q8_0_prepared": [_sz, _p, _p, _p, _sz, _sz, _sz, _sz, _p, _sz, ctypes.c_uint, _p],
     "tcrv_cuda_block_sums_q4_0_q8_0": [_sz, _p, _p, _p, _sz, _sz, _sz, _sz, _p],
     "tcrv_cuda_block_sums_q8_0_q8_0": [_sz, _p, _p, _p, _sz, _sz, _sz, _sz, _p],
 }
-_RESTYPES = {"tcrv_cuda_status_string": ctypes.c_char_p, "tcrv_cuda_last_error_text": ctypes.c_char_p}
+_RESTYPES = {
+    "tcrv_cuda_status_string": ctypes.c_char_p,
+    "tcrv_cuda_last_error_text": ctypes.c_char_p,
+    "tcrv_cuda_gemm_weights_bytes": _sz,
+    "tcrv_cuda_gemm_acts_workspace_bytes": _sz,
+    "tcrv_cuda_gemm_workspace_bytes": _sz,
+}
 
 _lib = None
 
@@ -248,4 +260,58 @@ def block_sums(w, x, q8_weights: bool = False):
     name = "tcrv_cuda_block_sums_q8_0_q8_0" if q8_weights else "tcrv_cuda_block_sums_q4_0_q8_0"
     fn = getattr(lib(), name)
     _check(fn(n, _dev(out), w.data_ptr(), x.data_ptr(), by, nr, nc, bx, _stream()), name)
+    return out
+
+
+# ------------------------------------------------------------------ prefill GEMM
+
+
+def _workspace(nbytes: int, device):
+    import torch
+
+    return torch.empty(max(nbytes, 256), dtype=torch.uint8, device=device)  # torch allocations are 256-byte aligned
+
+
+class PreparedWeights:
+    """Q4_0 weights converted once into the GEMM's planar layout (the weight-layout contract)."""
+
+    def __init__(self, w):
+        import torch
+
+        n, nr = _rows(w, Q4_0_BLOCK) * QK, w.shape[0]
+        self.n, self.nr = n, nr
+        self.buffer = _workspace(lib().tcrv_cuda_gemm_weights_bytes(n, nr), w.device)
+        _check(lib().tcrv_cuda_gemm_prepare_weights_q4_0(n, _dev(w, torch.uint8) if w.is_contiguous() else w.data_ptr(),
+                                                         w.stride(0), nr, self.buffer.data_ptr(), self.buffer.numel(),
+                                                         _stream()), "tcrv_cuda_gemm_prepare_weights_q4_0")
+
+
+def gemm(w, x, out=None, workspace=None):
+    """out[row, col] = Q4_0 x Q8_0 block dot for any number of activation columns.
+
+    `w` is either a (rows, row_bytes) uint8 tensor of block_q4_0 rows or a PreparedWeights."""
+    import torch
+
+    if isinstance(w, PreparedWeights):
+        n, nr, nc, by = w.n, w.nr, x.shape[0], x.stride(0)
+        if _rows(x, Q8_0_BLOCK) * QK != n:
+            raise ValueError("weights and activations disagree on the number of blocks per row")
+        if out is None:
+            out = torch.empty((nr, nc), dtype=torch.float32, device=x.device)
+        need = lib().tcrv_cuda_gemm_acts_workspace_bytes(n, nc)
+        if workspace is None:
+            workspace = _workspace(need, x.device)
+        _check(lib().tcrv_cuda_gemm_q4_0_q8_0_prepared(n, _dev(out, torch.float32), w.buffer.data_ptr(), x.data_ptr(), by,
+                                                       nr, nc, out.stride(0), workspace.data_ptr(), workspace.numel(), 0,
+                                                       _stream()), "tcrv_cuda_gemm_q4_0_q8_0_prepared")
+        return out
+    n, nr, nc, bx, by, _ = _matrix_args(w, x, Q4_0_BLOCK)
+    if out is None:
+        out = torch.empty((nr, nc), dtype=torch.float32, device=w.device)
+    need = lib().tcrv_cuda_gemm_workspace_bytes(n, nr, nc)
+    if workspace is None:
+        workspace = _workspace(need, w.device)
+    _check(lib().tcrv_cuda_gemm_q4_0_q8_0(n, _dev(out, torch.float32), w.data_ptr(), x.data_ptr(), by, nr, nc, bx,
+                                          out.stride(0), workspace.data_ptr(), workspace.numel(), 0, _stream()),
+           "tcrv_cuda_gemm_q4_0_q8_0")
     return out

@@ -193,4 +193,69 @@ int tcrv_cuda_block_sums_q8_0_q8_0(size_t n, int32_t *sumi, const uint8_t *vx, c
   return launch_block_sums<true>(n, sumi, vx, vy, by, nr, nc, bx, as_stream(stream));
 }
 
+size_t tcrv_cuda_gemm_weights_bytes(size_t n, size_t nr) { return gemm_weights_bytes(n, nr); }
+
+size_t tcrv_cuda_gemm_acts_workspace_bytes(size_t n, size_t nc) { return gemm_acts_bytes(n, nc); }
+
+size_t tcrv_cuda_gemm_workspace_bytes(size_t n, size_t nr, size_t nc) {
+  return gemm_weights_bytes(n, nr) + gemm_acts_bytes(n, nc);
+}
+
+int tcrv_cuda_gemm_prepare_weights_q4_0(size_t n, const uint8_t *vx, size_t bx, size_t nr, void *prepared,
+                                        size_t prepared_bytes, tcrv_cuda_stream stream) {
+  if (n % TCRV_QK != 0 || (nr != 0 && n != 0 && (!vx || !prepared)))
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  if (nr > 1 && bx < n / TCRV_QK * TCRV_Q4_0_BLOCK_BYTES)
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  if (prepared_bytes < gemm_weights_bytes(n, nr) || reinterpret_cast<uintptr_t>(prepared) % 256 != 0)
+    return TCRV_CUDA_ERR_WORKSPACE;
+  return launch_gemm_prepare_weights_q4_0(n, vx, bx, nr, static_cast<uint8_t *>(prepared), as_stream(stream));
+}
+
+int tcrv_cuda_gemm_q4_0_q8_0_prepared(size_t n, float *s, const void *prepared_weights, const uint8_t *vy,
+                                      size_t by, size_t nr, size_t nc, size_t bs, void *workspace,
+                                      size_t workspace_bytes, unsigned flags, tcrv_cuda_stream stream) {
+  (void)flags;  // the GEMM always folds in strict ascending block order
+  const int st = check_matrix_args(n, s, prepared_weights, vy, by, nr, nc, static_cast<size_t>(-1), bs, 0);
+  if (st != TCRV_CUDA_OK)
+    return st;
+  if (nr == 0 || nc == 0 || n == 0) {
+    if (n == 0)
+      for (size_t r = 0; r < nr; ++r)
+        TCRV_CUDA_TRY(cudaMemsetAsync(s + r * bs, 0, nc * sizeof(float), as_stream(stream)));
+    return TCRV_CUDA_OK;
+  }
+  if (!workspace || workspace_bytes < gemm_acts_bytes(n, nc) || reinterpret_cast<uintptr_t>(workspace) % 256 != 0 ||
+      reinterpret_cast<uintptr_t>(prepared_weights) % 256 != 0)
+    return TCRV_CUDA_ERR_WORKSPACE;
+  uint8_t *acts = static_cast<uint8_t *>(workspace);
+  int rc = launch_gemm_prepare_acts_q8_0(n, vy, by, nc, acts, as_stream(stream));
+  if (rc != TCRV_CUDA_OK)
+    return rc;
+  return launch_gemm_prepared(n, s, static_cast<const uint8_t *>(prepared_weights), acts, nr, nc, bs,
+                              as_stream(stream));
+}
+
+int tcrv_cuda_gemm_q4_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by, size_t nr,
+                             size_t nc, size_t bx, size_t bs, void *workspace, size_t workspace_bytes,
+                             unsigned flags, tcrv_cuda_stream stream) {
+  const int st = check_matrix_args(n, s, vx, vy, by, nr, nc, bx, bs, TCRV_Q4_0_BLOCK_BYTES);
+  if (st != TCRV_CUDA_OK)
+    return st;
+  if (nr == 0 || nc == 0)
+    return TCRV_CUDA_OK;
+  const size_t wbytes = gemm_weights_bytes(n, nr);
+  if (n != 0 && (!workspace || workspace_bytes < wbytes + gemm_acts_bytes(n, nc) ||
+                 reinterpret_cast<uintptr_t>(workspace) % 256 != 0))
+    return TCRV_CUDA_ERR_WORKSPACE;
+  uint8_t *ws = static_cast<uint8_t *>(workspace);
+  if (n != 0) {
+    const int rc = launch_gemm_prepare_weights_q4_0(n, vx, bx, nr, ws, as_stream(stream));
+    if (rc != TCRV_CUDA_OK)
+      return rc;
+  }
+  return tcrv_cuda_gemm_q4_0_q8_0_prepared(n, s, ws, vy, by, nr, nc, bs, ws + wbytes, workspace_bytes - wbytes, flags,
+                                           stream);
+}
+
 }  // extern "C"

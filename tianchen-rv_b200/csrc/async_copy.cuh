@@ -45,17 +45,33 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
   return done != 0;
 }
 
-// Bounded wait for the phase with the given parity.  Each try_wait already blocks for a
-// hardware-defined interval, so the cap corresponds to seconds, far beyond any legitimate
-// wait of these kernels (microseconds).
-constexpr uint32_t kMbarMaxTries = 1u << 22;
+// Bounded wait for the phase with the given parity: gives up after kMbarTimeoutNs of wall
+// time (the global nanosecond timer is sampled every 256 polls), far beyond any legitimate
+// wait of these kernels (microseconds).  `abort_flag`, when given, is a shared-memory word
+// another role sets after its own wait failed, so that the whole CTA leaves promptly.
+constexpr uint64_t kMbarTimeoutNs = 2000000000ull;
 
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity) {
-  for (uint32_t i = 0; i < kMbarMaxTries; ++i) {
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity,
+                                                  volatile uint32_t *abort_flag = nullptr) {
+  if (mbar_try_wait(bar, parity))
+    return true;
+  const uint64_t start = global_timer_ns();
+  for (uint32_t i = 1;; ++i) {
     if (mbar_try_wait(bar, parity))
       return true;
+    if ((i & 255u) == 0) {
+      if (abort_flag != nullptr && *abort_flag != 0)
+        return false;
+      if (global_timer_ns() - start > kMbarTimeoutNs)
+        return false;
+    }
   }
-  return false;
 }
 
 // global -> shared bulk copy; dst, src and bytes must be multiples of 16.

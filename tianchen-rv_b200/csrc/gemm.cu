@@ -1,0 +1,252 @@
+// Prefill GEMM host side: the unpack ("prepare") kernels that turn plain block_q4_0 /
+// block_q8_0 rows into the planar layout the tensor-core kernel consumes, the TMA tensor
+// maps, and the launchers.
+//
+// Planar layout (all regions 256-byte aligned inside the caller's workspace):
+//   weights      int8 [nr][K]            value = nibble - 8
+//   weight scale fp32 [nr][nbp]          nbp = blocks per row rounded up to 4
+//   activations  int8 [nc][K]
+//   act. scale   fp32 [nb][ncp]          transposed; ncp = columns rounded up to 4
+#include <cuda.h>
+
+#include "gemm_tc.cuh"
+#include "launchers.h"
+
+namespace tcrv {
+
+namespace {
+
+constexpr size_t kAlign = 256;
+inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// ---------------------------------------------------------------- unpack kernels
+
+// One thread per (row, block): 18 bytes in, 32 int8 + one fp32 scale out.
+__global__ void __launch_bounds__(256) unpack_q4_0_kernel(const uint8_t *__restrict__ vx, size_t bx, uint32_t nr,
+                                                          uint32_t nb, uint32_t nbp, int8_t *__restrict__ w8,
+                                                          float *__restrict__ dw, bool aligned2) {
+  const size_t total = static_cast<size_t>(nr) * nb;
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const size_t row = i / nb, ib = i - row * nb;
+    const uint8_t *blk = vx + row * bx + ib * kQ4Block;
+    uint32_t d, q[4];
+    if (aligned2) {
+      const unsigned short *h = reinterpret_cast<const unsigned short *>(blk);
+      d = h[0];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        q[j] = static_cast<uint32_t>(h[1 + 2 * j]) | (static_cast<uint32_t>(h[2 + 2 * j]) << 16);
+    } else {
+      d = load_u16(blk);
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        q[j] = load_u32_bytes(blk + 2 + 4 * j);
+    }
+    uint32_t lo[4], hi[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      lo[j] = __vsub4(q[j] & 0x0f0f0f0fu, 0x08080808u);         // elements 4j..4j+3
+      hi[j] = __vsub4((q[j] >> 4) & 0x0f0f0f0fu, 0x08080808u);  // elements 16+4j..
+    }
+    uint4 *dst = reinterpret_cast<uint4 *>(w8 + (row * nb + ib) * kQK);
+    dst[0] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+    dst[1] = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+    dw[row * nbp + ib] = half_bits_to_float(d);
+  }
+}
+
+__global__ void __launch_bounds__(256) unpack_q8_0_kernel(const uint8_t *__restrict__ vy, size_t by, uint32_t nc,
+                                                          uint32_t nb, uint32_t ncp, int8_t *__restrict__ x8,
+                                                          float *__restrict__ dxt, bool aligned2) {
+  const size_t total = static_cast<size_t>(nc) * nb;
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const size_t col = i / nb, ib = i - col * nb;
+    const uint8_t *blk = vy + col * by + ib * kQ8Block;
+    uint32_t d, q[8];
+    if (aligned2) {
+      const unsigned short *h = reinterpret_cast<const unsigned short *>(blk);
+      d = h[0];
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        q[j] = static_cast<uint32_t>(h[1 + 2 * j]) | (static_cast<uint32_t>(h[2 + 2 * j]) << 16);
+    } else {
+      d = load_u16(blk);
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        q[j] = load_u32_bytes(blk + 2 + 4 * j);
+    }
+    uint4 *dst = reinterpret_cast<uint4 *>(x8 + (col * nb + ib) * kQK);
+    dst[0] = make_uint4(q[0], q[1], q[2], q[3]);
+    dst[1] = make_uint4(q[4], q[5], q[6], q[7]);
+    dxt[ib * ncp + col] = half_bits_to_float(d);
+  }
+}
+
+// ------------------------------------------------------------------- tensor maps
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+int get_encode_fn(EncodeTiledFn *out) {
+  static EncodeTiledFn cached = nullptr;
+  if (cached == nullptr) {
+    void *fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    TCRV_CUDA_TRY(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+    if (qres != cudaDriverEntryPointSuccess || fn == nullptr)
+      return record_cuda_error(cudaErrorNotSupported, "cuTensorMapEncodeTiled entry point");
+    cached = reinterpret_cast<EncodeTiledFn>(fn);
+  }
+  *out = cached;
+  return TCRV_CUDA_OK;
+}
+
+int make_map_2d(CUtensorMap *map, CUtensorMapDataType type, size_t elem_bytes, const void *base, uint64_t inner,
+                uint64_t outer, uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer,
+                CUtensorMapSwizzle swizzle) {
+  EncodeTiledFn encode;
+  const int st = get_encode_fn(&encode);
+  if (st != TCRV_CUDA_OK)
+    return st;
+  (void)elem_bytes;
+  const cuuint64_t dims[2] = {inner, outer};
+  const cuuint64_t strides[1] = {row_stride_bytes};
+  const cuuint32_t box[2] = {box_inner, box_outer};
+  const cuuint32_t elem_strides[2] = {1, 1};
+  const CUresult res = encode(map, type, 2, const_cast<void *>(base), dims, strides, box, elem_strides,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (res != CUDA_SUCCESS)
+    return record_cuda_error(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");
+  return TCRV_CUDA_OK;
+}
+
+struct PlanarSizes {
+  size_t nb, nbp, ncp, k;
+  size_t w8, dw, x8, dxt;  // region sizes (aligned)
+};
+
+PlanarSizes planar_sizes(size_t n, size_t nr, size_t nc) {
+  PlanarSizes p;
+  p.nb = n / kQK;
+  p.nbp = align_up(p.nb, 4);
+  p.ncp = align_up(nc, 4);
+  p.k = n;
+  p.w8 = align_up(nr * n, kAlign);
+  p.dw = align_up(nr * p.nbp * 4, kAlign);
+  p.x8 = align_up(nc * n, kAlign);
+  p.dxt = align_up(p.nb * p.ncp * 4, kAlign);
+  return p;
+}
+
+inline int blocks_for(size_t items) {
+  size_t b = (items + 255) / 256;
+  const size_t cap = static_cast<size_t>(sm_count()) * 16;
+  return static_cast<int>(b < cap ? (b ? b : 1) : cap);
+}
+
+int run_gemm(size_t n, float *s, const uint8_t *weights_planar, const uint8_t *acts_planar, size_t nr, size_t nc,
+             size_t bs, cudaStream_t stream) {
+  const PlanarSizes p = planar_sizes(n, nr, nc);
+  const int8_t *w8 = reinterpret_cast<const int8_t *>(weights_planar);
+  const float *dw = reinterpret_cast<const float *>(weights_planar + p.w8);
+  const int8_t *x8 = reinterpret_cast<const int8_t *>(acts_planar);
+  const float *dxt = reinterpret_cast<const float *>(acts_planar + p.x8);
+
+  CUtensorMap map_w, map_x, map_dw, map_dx;
+  int st = make_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w8, n, nr, n, kGemmStageBlocks * kQK, kGemmTileRows,
+                       CU_TENSOR_MAP_SWIZZLE_128B);
+  if (st == TCRV_CUDA_OK)
+    st = make_map_2d(&map_x, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, x8, n, nc, n, kGemmStageBlocks * kQK, kGemmTileCols,
+                     CU_TENSOR_MAP_SWIZZLE_128B);
+  if (st == TCRV_CUDA_OK)
+    st = make_map_2d(&map_dw, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, dw, p.nbp, nr, p.nbp * 4, kGemmStageBlocks,
+                     kGemmTileRows, CU_TENSOR_MAP_SWIZZLE_NONE);
+  if (st == TCRV_CUDA_OK)
+    st = make_map_2d(&map_dx, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, dxt, p.ncp, p.nb, p.ncp * 4, kGemmTileCols,
+                     kGemmStageBlocks, CU_TENSOR_MAP_SWIZZLE_NONE);
+  if (st != TCRV_CUDA_OK)
+    return st;
+
+  GemmArgs args;
+  args.s = s;
+  args.bs = bs;
+  args.nr = static_cast<uint32_t>(nr);
+  args.nc = static_cast<uint32_t>(nc);
+  args.nb = static_cast<uint32_t>(p.nb);
+  args.tiles_m = static_cast<uint32_t>((nc + kGemmTileCols - 1) / kGemmTileCols);
+  args.tiles = static_cast<uint32_t>((nr + kGemmTileRows - 1) / kGemmTileRows) * args.tiles_m;
+
+  static bool configured[64] = {};
+  int dev = 0;
+  TCRV_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 64 && !configured[dev]) {
+    TCRV_CUDA_TRY(cudaFuncSetAttribute(gemm_q4_0_q8_0_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(kGemmSmemBytes)));
+    configured[dev] = true;
+  }
+  const int sms = sm_count();
+  const int grid = static_cast<int>(args.tiles < static_cast<uint32_t>(sms) ? args.tiles : sms);
+  gemm_q4_0_q8_0_tc_kernel<<<grid, kGemmThreads, kGemmSmemBytes, stream>>>(map_w, map_x, map_dw, map_dx, args);
+  TCRV_CUDA_TRY(cudaGetLastError());
+  return TCRV_CUDA_OK;
+}
+
+}  // namespace
+
+size_t gemm_weights_bytes(size_t n, size_t nr) {
+  const PlanarSizes p = planar_sizes(n, nr, 0);
+  return p.w8 + p.dw;
+}
+
+size_t gemm_acts_bytes(size_t n, size_t nc) {
+  const PlanarSizes p = planar_sizes(n, 0, nc);
+  return p.x8 + p.dxt;
+}
+
+int launch_gemm_prepare_weights_q4_0(size_t n, const uint8_t *vx, size_t bx, size_t nr, uint8_t *prepared,
+                                     cudaStream_t stream) {
+  const PlanarSizes p = planar_sizes(n, nr, 0);
+  if (nr == 0 || p.nb == 0)
+    return TCRV_CUDA_OK;
+  const bool aligned2 = (reinterpret_cast<uintptr_t>(vx) % 2 == 0) && (bx % 2 == 0);
+  // padded scale columns must read as zero: the TMA box covers them
+  if (p.nbp != p.nb)
+    TCRV_CUDA_TRY(cudaMemsetAsync(prepared + p.w8, 0, nr * p.nbp * 4, stream));
+  unpack_q4_0_kernel<<<blocks_for(nr * p.nb), 256, 0, stream>>>(vx, bx, static_cast<uint32_t>(nr),
+                                                                static_cast<uint32_t>(p.nb),
+                                                                static_cast<uint32_t>(p.nbp),
+                                                                reinterpret_cast<int8_t *>(prepared),
+                                                                reinterpret_cast<float *>(prepared + p.w8), aligned2);
+  TCRV_CUDA_TRY(cudaGetLastError());
+  return TCRV_CUDA_OK;
+}
+
+int launch_gemm_prepare_acts_q8_0(size_t n, const uint8_t *vy, size_t by, size_t nc, uint8_t *prepared,
+                                  cudaStream_t stream) {
+  const PlanarSizes p = planar_sizes(n, 0, nc);
+  if (nc == 0 || p.nb == 0)
+    return TCRV_CUDA_OK;
+  const bool aligned2 = (reinterpret_cast<uintptr_t>(vy) % 2 == 0) && (by % 2 == 0);
+  if (p.ncp != nc)
+    TCRV_CUDA_TRY(cudaMemsetAsync(prepared + p.x8, 0, p.nb * p.ncp * 4, stream));
+  unpack_q8_0_kernel<<<blocks_for(nc * p.nb), 256, 0, stream>>>(vy, by, static_cast<uint32_t>(nc),
+                                                                static_cast<uint32_t>(p.nb),
+                                                                static_cast<uint32_t>(p.ncp),
+                                                                reinterpret_cast<int8_t *>(prepared),
+                                                                reinterpret_cast<float *>(prepared + p.x8), aligned2);
+  TCRV_CUDA_TRY(cudaGetLastError());
+  return TCRV_CUDA_OK;
+}
+
+int launch_gemm_prepared(size_t n, float *s, const uint8_t *weights_planar, const uint8_t *acts_planar, size_t nr,
+                         size_t nc, size_t bs, cudaStream_t stream) {
+  if (nr == 0 || nc == 0)
+    return TCRV_CUDA_OK;
+  return run_gemm(n, s, weights_planar, acts_planar, nr, nc, bs, stream);
+}
+
+}  // namespace tcrv

@@ -1,0 +1,321 @@
+// Prefill GEMM, Q4_0 weights x Q8_0 activations, on the 5th-generation tensor cores.
+//
+//   s[row*bs + col] = sum over blocks b of ((float)S_b[row,col] * d_w[row,b]) * d_x[col,b]
+//   S_b[row,col]    = int32 dot of the 32 int8 weight values and 32 int8 activation values
+//
+// Every ggml block (32 elements of K) has its own pair of fp16 scales, so the contraction
+// cannot accumulate across blocks in integer: each block is ONE tcgen05.mma (kind::i8,
+// M=128 weight rows, N=128 activation columns, K=32) into a fresh TMEM accumulator, and the
+// epilogue warps fold that int32 tile into fp32 register accumulators with the two scales
+// before the next block's tile arrives.  The fold runs in strict ascending block order per
+// output element, in the fused form fma((float)S * d_w, d_x, acc).
+//
+// Operands come from a planar ("prepared") layout written by the unpack kernels: int8
+// matrices [rows][K] and fp32 scale matrices, all fetched with tiled TMA loads (128-byte
+// swizzle for the int8 tiles).  Warp roles in a CTA of 10 warps:
+//   warps 0..7  epilogue: warp w reads TMEM lanes 32*(w%4).. (its weight rows) and columns
+//               64*(w/4).. of every accumulator tile
+//   warp 8      TMA producer (one lane)
+//   warp 9      TMEM allocation + MMA issue (one lane)
+// Pipelines: kSmemStages shared-memory stages of 4 blocks each (full/empty mbarriers) and
+// kTmemStages TMEM accumulator tiles of 128 columns (full/empty mbarriers).  Every wait is
+// bounded; a failed wait raises the device error word and the CTA winds down.
+#pragma once
+
+#include "tcgen05.cuh"
+#include "tcrv_common.cuh"
+
+namespace tcrv {
+
+constexpr int kGemmTileRows = 128;   // weight rows per tile  (MMA M, TMEM lanes)
+constexpr int kGemmTileCols = 128;   // activation columns per tile (MMA N, TMEM columns)
+constexpr int kGemmStageBlocks = 4;  // ggml blocks per shared-memory stage (128 bytes of K)
+constexpr int kGemmSmemStages = 5;
+constexpr int kGemmTmemStages = 4;
+constexpr int kGemmTmemCols = kGemmTmemStages * kGemmTileCols;  // 512
+constexpr int kGemmEpilogueWarps = 8;
+constexpr int kGemmThreads = (kGemmEpilogueWarps + 2) * 32;
+
+constexpr int kGemmABytes = kGemmTileRows * kGemmStageBlocks * kQK;           // 16384
+constexpr int kGemmBBytes = kGemmTileCols * kGemmStageBlocks * kQK;           // 16384
+constexpr int kGemmDwBytes = kGemmTileRows * kGemmStageBlocks * 4;            // [128][4] fp32
+constexpr int kGemmDxBytes = kGemmStageBlocks * kGemmTileCols * 4;            // [4][128] fp32
+constexpr int kGemmStageBytes = kGemmABytes + kGemmBBytes + kGemmDwBytes + kGemmDxBytes;
+constexpr int kGemmCtrlBytes = 1024;  // barriers, TMEM base, abort flag
+constexpr size_t kGemmSmemBytes = kGemmCtrlBytes + static_cast<size_t>(kGemmSmemStages) * kGemmStageBytes + 1024;
+
+struct GemmArgs {
+  float *s;
+  size_t bs;
+  uint32_t nr, nc, nb;
+  uint32_t tiles_m;  // column tiles
+  uint32_t tiles;    // row tiles * column tiles
+};
+
+// ---- packed fp32x2 arithmetic (two IEEE round-to-nearest operations per instruction)
+__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack_f32x2(uint64_t v, float &lo, float &hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t mul_f32x2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+
+struct PipeState {
+  uint32_t stage = 0, phase = 0;
+  __device__ __forceinline__ void advance(uint32_t nstages) {
+    if (++stage == nstages) {
+      stage = 0;
+      phase ^= 1;
+    }
+  }
+};
+
+__global__ void __launch_bounds__(kGemmThreads, 1)
+    gemm_q4_0_q8_0_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                             const __grid_constant__ CUtensorMap map_dw, const __grid_constant__ CUtensorMap map_dx,
+                             const GemmArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  // control block first, then stages on a 1024-byte boundary (required by the 128B swizzle)
+  uint8_t *ctrl = smem_raw;
+  uint64_t *smem_full = reinterpret_cast<uint64_t *>(ctrl);
+  uint64_t *smem_empty = smem_full + kGemmSmemStages;
+  uint64_t *tmem_full = smem_empty + kGemmSmemStages;
+  uint64_t *tmem_empty = tmem_full + kGemmTmemStages;
+  uint64_t *drain_bar = tmem_empty + kGemmTmemStages;
+  uint32_t *tmem_base_slot = reinterpret_cast<uint32_t *>(drain_bar + 1);
+  volatile uint32_t *abort_flag = tmem_base_slot + 1;
+  const uint32_t stage_base_addr = (smem_addr(smem_raw) + kGemmCtrlBytes + 1023u) & ~1023u;
+  uint8_t *stages = smem_raw + (stage_base_addr - smem_addr(smem_raw));
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t nkb = (a.nb + kGemmStageBlocks - 1) / kGemmStageBlocks;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kGemmSmemStages; ++i) {
+      mbar_init(&smem_full[i], 1);
+      mbar_init(&smem_empty[i], 1 + kGemmEpilogueWarps);  // MMA commit + every epilogue warp
+    }
+    for (int i = 0; i < kGemmTmemStages; ++i) {
+      mbar_init(&tmem_full[i], 1);
+      mbar_init(&tmem_empty[i], kGemmEpilogueWarps);
+    }
+    mbar_init(drain_bar, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == kGemmEpilogueWarps + 1) {
+    tmem_alloc(tmem_base_slot, kGemmTmemCols);
+    tmem_relinquish_alloc_permit();
+  }
+  tcgen05_fence_before_thread_sync();
+  __syncthreads();
+  tcgen05_fence_after_thread_sync();
+  const uint32_t tmem_base = *tmem_base_slot;
+
+  if (warp == kGemmEpilogueWarps) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      prefetch_tensormap(&map_w);
+      prefetch_tensormap(&map_x);
+      prefetch_tensormap(&map_dw);
+      prefetch_tensormap(&map_dx);
+      PipeState ps;
+      bool ok = true;
+      uint32_t issued = 0;
+      for (uint32_t t = blockIdx.x; t < a.tiles && ok; t += gridDim.x) {
+        const int n0 = static_cast<int>(t / a.tiles_m) * kGemmTileRows;
+        const int m0 = static_cast<int>(t % a.tiles_m) * kGemmTileCols;
+        for (uint32_t kb = 0; kb < nkb; ++kb) {
+          ok = mbar_wait_bounded(&smem_empty[ps.stage], ps.phase ^ 1, abort_flag);
+          if (!ok)
+            break;
+          uint8_t *st = stages + static_cast<size_t>(ps.stage) * kGemmStageBytes;
+          mbar_arrive_expect_tx(&smem_full[ps.stage], kGemmStageBytes);
+          const int kbyte = static_cast<int>(kb) * kGemmStageBlocks * kQK;
+          const int kblk = static_cast<int>(kb) * kGemmStageBlocks;
+          tma_load_2d(st, &map_w, kbyte, n0, &smem_full[ps.stage]);
+          tma_load_2d(st + kGemmABytes, &map_x, kbyte, m0, &smem_full[ps.stage]);
+          tma_load_2d(st + kGemmABytes + kGemmBBytes, &map_dw, kblk, n0, &smem_full[ps.stage]);
+          tma_load_2d(st + kGemmABytes + kGemmBBytes + kGemmDwBytes, &map_dx, m0, kblk, &smem_full[ps.stage]);
+          ps.advance(kGemmSmemStages);
+          ++issued;
+        }
+      }
+      if (!ok) {
+        *abort_flag = 1;
+        atomicOr(&g_device_error, kDevErrBarrierTimeout);
+      }
+      if (*abort_flag != 0) {
+        // winding down after a failed wait: let this CTA's own copies land before it exits
+        const uint32_t first = issued > kGemmSmemStages ? issued - kGemmSmemStages : 0;
+        for (uint32_t i = first; i < issued; ++i)
+          (void)mbar_wait_bounded(&smem_full[i % kGemmSmemStages], (i / kGemmSmemStages) & 1, nullptr);
+      }
+    }
+  } else if (warp == kGemmEpilogueWarps + 1) {
+    // ------------------------------ MMA issuer ------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_s8(kGemmTileRows, kGemmTileCols);
+      PipeState ps, ts;
+      bool ok = true;
+      for (uint32_t t = blockIdx.x; t < a.tiles && ok; t += gridDim.x) {
+        for (uint32_t kb = 0; kb < nkb && ok; ++kb) {
+          ok = mbar_wait_bounded(&smem_full[ps.stage], ps.phase, abort_flag);
+          if (!ok)
+            break;
+          tcgen05_fence_after_thread_sync();
+          const uint32_t a_addr = stage_base_addr + ps.stage * kGemmStageBytes;
+          const uint32_t b_addr = a_addr + kGemmABytes;
+          const uint32_t steps = min(static_cast<uint32_t>(kGemmStageBlocks), a.nb - kb * kGemmStageBlocks);
+          for (uint32_t kk = 0; kk < steps; ++kk) {
+            ok = mbar_wait_bounded(&tmem_empty[ts.stage], ts.phase ^ 1, abort_flag);
+            if (!ok)
+              break;
+            tcgen05_fence_after_thread_sync();
+            umma_s8_ss(tmem_base + ts.stage * kGemmTileCols, umma_desc_k_major_sw128(a_addr + kk * kQK),
+                       umma_desc_k_major_sw128(b_addr + kk * kQK), idesc, 0u);
+            umma_commit(&tmem_full[ts.stage]);
+            ts.advance(kGemmTmemStages);
+          }
+          if (ok)
+            umma_commit(&smem_empty[ps.stage]);
+          ps.advance(kGemmSmemStages);
+        }
+      }
+      if (!ok) {
+        *abort_flag = 1;
+        atomicOr(&g_device_error, kDevErrBarrierTimeout);
+      }
+      // every MMA issued above must have finished before TMEM is released
+      umma_commit(drain_bar);
+      (void)mbar_wait_bounded(drain_bar, 0, nullptr);
+    }
+  } else {
+    // ------------------------------ epilogue warps ------------------------------
+    const int quarter = warp & 3, half = warp >> 2;
+    const int row_local = quarter * 32 + lane;
+    const uint32_t lane_field = static_cast<uint32_t>(quarter * 32) << 16;
+    PipeState ps, ts;
+    bool ok = true;
+    for (uint32_t t = blockIdx.x; t < a.tiles && ok; t += gridDim.x) {
+      const uint32_t n0 = (t / a.tiles_m) * kGemmTileRows;
+      const uint32_t m0 = (t % a.tiles_m) * kGemmTileCols + half * 64;
+      uint64_t acc[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        acc[j] = 0ull;
+      for (uint32_t kb = 0; kb < nkb && ok; ++kb) {
+        ok = mbar_wait_bounded(&smem_full[ps.stage], ps.phase, abort_flag);
+        if (!ok)
+          break;
+        const uint8_t *st = stages + static_cast<size_t>(ps.stage) * kGemmStageBytes;
+        const float4 dw4 = reinterpret_cast<const float4 *>(st + kGemmABytes + kGemmBBytes)[row_local];
+        const float dws[4] = {dw4.x, dw4.y, dw4.z, dw4.w};
+        const uint8_t *dx_base = st + kGemmABytes + kGemmBBytes + kGemmDwBytes + half * 64 * 4;
+        const uint32_t steps = min(static_cast<uint32_t>(kGemmStageBlocks), a.nb - kb * kGemmStageBlocks);
+#pragma unroll
+        for (uint32_t kk = 0; kk < kGemmStageBlocks; ++kk) {
+          if (kk < steps && ok) {
+            ok = mbar_wait_bounded(&tmem_full[ts.stage], ts.phase, abort_flag);
+            if (ok) {
+              tcgen05_fence_after_thread_sync();
+              uint32_t v0[32], v1[32];
+              const uint32_t taddr = tmem_base + lane_field + ts.stage * kGemmTileCols + half * 64;
+              tmem_ld_32x32b_x32(taddr, v0);
+              tmem_ld_32x32b_x32(taddr + 32, v1);
+              tmem_ld_wait();
+              tcgen05_fence_before_thread_sync();
+              __syncwarp();
+              if (lane == 0)
+                mbar_arrive(&tmem_empty[ts.stage]);
+              ts.advance(kGemmTmemStages);
+              const uint64_t dw2 = pack_f32x2(dws[kk], dws[kk]);
+              const ulonglong2 *dx2 = reinterpret_cast<const ulonglong2 *>(dx_base + kk * kGemmTileCols * 4);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const ulonglong2 d = dx2[j];
+                const uint64_t t0 = mul_f32x2(
+                    pack_f32x2(__int2float_rn(static_cast<int>(v0[4 * j])), __int2float_rn(static_cast<int>(v0[4 * j + 1]))),
+                    dw2);
+                const uint64_t t1 = mul_f32x2(pack_f32x2(__int2float_rn(static_cast<int>(v0[4 * j + 2])),
+                                                         __int2float_rn(static_cast<int>(v0[4 * j + 3]))),
+                                              dw2);
+                acc[2 * j] = fma_f32x2(t0, d.x, acc[2 * j]);
+                acc[2 * j + 1] = fma_f32x2(t1, d.y, acc[2 * j + 1]);
+              }
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const ulonglong2 d = dx2[8 + j];
+                const uint64_t t0 = mul_f32x2(
+                    pack_f32x2(__int2float_rn(static_cast<int>(v1[4 * j])), __int2float_rn(static_cast<int>(v1[4 * j + 1]))),
+                    dw2);
+                const uint64_t t1 = mul_f32x2(pack_f32x2(__int2float_rn(static_cast<int>(v1[4 * j + 2])),
+                                                         __int2float_rn(static_cast<int>(v1[4 * j + 3]))),
+                                              dw2);
+                acc[16 + 2 * j] = fma_f32x2(t0, d.x, acc[16 + 2 * j]);
+                acc[16 + 2 * j + 1] = fma_f32x2(t1, d.y, acc[16 + 2 * j + 1]);
+              }
+            }
+          }
+        }
+        // this warp no longer needs the stage's scale tiles
+        __syncwarp();
+        if (lane == 0 && ok)
+          mbar_arrive(&smem_empty[ps.stage]);
+        ps.advance(kGemmSmemStages);
+      }
+      if (!ok)
+        break;
+      // ---- store: this thread owns 64 consecutive outputs of one weight row
+      const uint32_t row = n0 + row_local;
+      if (row < a.nr) {
+        float *dst = a.s + static_cast<size_t>(row) * a.bs + m0;
+        const bool vec = (a.bs % 4 == 0) && ((reinterpret_cast<uintptr_t>(a.s) & 15u) == 0) && (m0 + 64 <= a.nc);
+        if (vec) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            float4 o;
+            unpack_f32x2(acc[2 * j], o.x, o.y);
+            unpack_f32x2(acc[2 * j + 1], o.z, o.w);
+            reinterpret_cast<float4 *>(dst)[j] = o;
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            float lo, hi;
+            unpack_f32x2(acc[j], lo, hi);
+            if (m0 + 2 * j < a.nc)
+              dst[2 * j] = lo;
+            if (m0 + 2 * j + 1 < a.nc)
+              dst[2 * j + 1] = hi;
+          }
+        }
+      }
+    }
+    if (!ok && lane == 0) {
+      *abort_flag = 1;
+      atomicOr(&g_device_error, kDevErrBarrierTimeout);
+    }
+  }
+
+  tcgen05_fence_before_thread_sync();
+  __syncthreads();
+  if (warp == kGemmEpilogueWarps + 1) {
+    tcgen05_fence_after_thread_sync();
+    tmem_dealloc(tmem_base, kGemmTmemCols);
+  }
+}
+
+}  // namespace tcrv

@@ -23,3 +23,15 @@ int launch_block_sums(size_t n, int32_t *sumi, const uint8_t *vx, const uint8_t 
                       size_t nc, size_t bx, cudaStream_t stream);
 
 }  // namespace tcrv
+
+namespace tcrv {
+// Prefill GEMM: planar-layout sizes, the two prepare steps and the tensor-core launch.
+size_t gemm_weights_bytes(size_t n, size_t nr);
+size_t gemm_acts_bytes(size_t n, size_t nc);
+int launch_gemm_prepare_weights_q4_0(size_t n, const uint8_t *vx, size_t bx, size_t nr, uint8_t *prepared,
+                                     cudaStream_t stream);
+int launch_gemm_prepare_acts_q8_0(size_t n, const uint8_t *vy, size_t by, size_t nc, uint8_t *prepared,
+                                  cudaStream_t stream);
+int launch_gemm_prepared(size_t n, float *s, const uint8_t *weights_planar, const uint8_t *acts_planar, size_t nr,
+                         size_t nc, size_t bs, cudaStream_t stream);
+}  // namespace tcrv
