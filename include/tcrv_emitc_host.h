@@ -1,0 +1,71 @@
+/*
+ * tcrv_emitc_host.h -- host-pointer entry points of the sm_100a provider.
+ *
+ * The functions named `tcrv_emitc_<kernel>_<variant>` have the exact symbol names and
+ * parameter lists of the C functions the TianChen-RV compiler emits for the corresponding
+ * fixtures (entry naming: lib/Conversion/RVV/RVVToEmitC.cpp:165-172; parameters in
+ * runtime_abi_value declaration order: lib/Conversion/RVV/RVVToEmitC.cpp:133-145), so a
+ * harness written against the generated RVV kernel links against this library unchanged.
+ * All pointers are HOST pointers; a call returns when its output is in host memory.  Like
+ * the generated kernels they return void; a provider failure prints a message and aborts.
+ * The `tcrv_cuda_host_*` functions are the same operations returning a tcrv_cuda_status.
+ */
+#ifndef TCRV_EMITC_HOST_H
+#define TCRV_EMITC_HOST_H
+
+#include "tcrv_cuda.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Static weights: upload `bytes` at `host` once; later calls that pass the same host pointer
+ * as their weight operand use the resident device copy.  The caller keeps ownership of the
+ * host buffer and must not change it while registered. */
+int tcrv_cuda_host_register_weights(const void *host, size_t bytes);
+int tcrv_cuda_host_unregister_weights(const void *host);
+/* Frees every device allocation this front end made (arena and resident weights). */
+int tcrv_cuda_host_release(void);
+
+int tcrv_cuda_host_add_f32(const float *lhs, const float *rhs, float *out, size_t n);
+int tcrv_cuda_host_add_i32(const int32_t *lhs, const int32_t *rhs, int32_t *out, size_t n);
+int tcrv_cuda_host_dequantize_i32_f32(const int32_t *lhs, float scale, float *out, size_t n);
+int tcrv_cuda_host_quantize_row_q8_0(size_t n, const float *x, uint8_t *vy);
+/* nc <= 8 runs the decode GEMV, larger nc the tensor-core GEMM. */
+int tcrv_cuda_host_gemm_q4_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by, size_t nr,
+                                  size_t nc, size_t bx, size_t bs);
+/* Q8_0 weights: decode GEMV only (nc <= 8). */
+int tcrv_cuda_host_gemm_q8_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by, size_t nr,
+                                  size_t nc, size_t bx, size_t bs);
+
+/* test/Target/RVV/explicit-selected-body-artifact-add.mlir:68 (header artifact prototype);
+ * examples/qemu/harness_add.cpp:11-12 declares and calls exactly this symbol. */
+void tcrv_emitc_explicit_selected_body_add_kernel_explicit_selected_body_rvv_i32_add(const int32_t *lhs,
+                                                                                     const int32_t *rhs,
+                                                                                     int32_t *out, size_t n);
+/* The f32 form of the same slice (this repository's fixture; f32/m1 add is legal in the
+ * reference: lib/Dialect/RVV/IR/RVVDialect.cpp:2918-2933). */
+void tcrv_emitc_explicit_selected_body_add_f32_kernel_explicit_selected_body_cuda_f32_add(const float *lhs,
+                                                                                          const float *rhs,
+                                                                                          float *out, size_t n);
+/* test/Conversion/RVV/rvv-to-emitc-dequantize-i32-to-f32.mlir:44 */
+void tcrv_emitc_explicit_selected_body_dequantize_i32_to_f32_kernel_explicit_selected_body_rvv_dequantize_i32_to_f32(
+    const int32_t *lhs, float scale, float *out, size_t n);
+/* test/Conversion/RVV/rvv-to-emitc-ggml-quantize-row-q8-0.mlir:40 */
+void tcrv_emitc_quantize_row_q8_0_kernel_quantize_row_q8_0(size_t n, const float *x, uint8_t *vy);
+/* test/Conversion/RVV/rvv-to-emitc-q4-0-q8-0-block-dot.mlir:44 */
+void tcrv_emitc_ggml_vec_dot_q4_0_q8_0_kernel_ggml_vec_dot_q4_0_q8_0(size_t n, float *s, size_t bs, const uint8_t *vx,
+                                                                     size_t bx, const uint8_t *vy, size_t by,
+                                                                     int32_t nrc);
+/* test/Conversion/RVV/rvv-to-emitc-q8-0-q8-0-block-dot.mlir:30 */
+void tcrv_emitc_ggml_vec_dot_q8_0_q8_0_kernel_ggml_vec_dot_q8_0_q8_0(size_t n, float *s, const uint8_t *vx,
+                                                                     const uint8_t *vy);
+/* test/Conversion/RVV/rvv-to-emitc-q4-0-q8-0-gemm.mlir:44 */
+void tcrv_emitc_ggml_q4_0_q8_0_gemm_kernel_ggml_q4_0_q8_0_gemm(size_t n, float *s, const uint8_t *vx,
+                                                               const uint8_t *vy, size_t by, size_t nr, size_t nc,
+                                                               size_t bx, size_t bs);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TCRV_EMITC_HOST_H */

@@ -52,6 +52,19 @@ ABI = {
     "tcrv_cuda_block_sums_q4_0_q8_0": [_sz, _p, _p, _p, _sz, _sz, _sz, _sz, _p],
     "tcrv_cuda_block_sums_q8_0_q8_0": [_sz, _p, _p, _p, _sz, _sz, _sz, _sz, _p],
 }
+# host-pointer front end (include/tcrv_emitc_host.h)
+ABI.update({
+    "tcrv_cuda_host_register_weights": [_p, _sz],
+    "tcrv_cuda_host_unregister_weights": [_p],
+    "tcrv_cuda_host_release": [],
+    "tcrv_cuda_host_add_f32": [_p, _p, _p, _sz],
+    "tcrv_cuda_host_add_i32": [_p, _p, _p, _sz],
+    "tcrv_cuda_host_dequantize_i32_f32": [_p, ctypes.c_float, _p, _sz],
+    "tcrv_cuda_host_quantize_row_q8_0": [_sz, _p, _p],
+    "tcrv_cuda_host_gemm_q4_0_q8_0": [_sz, _p, _p, _p, _sz, _sz, _sz, _sz, _sz],
+    "tcrv_cuda_host_gemm_q8_0_q8_0": [_sz, _p, _p, _p, _sz, _sz, _sz, _sz, _sz],
+})
+
 _RESTYPES = {
     "tcrv_cuda_status_string": ctypes.c_char_p,
     "tcrv_cuda_last_error_text": ctypes.c_char_p,

@@ -1,0 +1,401 @@
+// Host-pointer front of the provider: entry points whose buffers live in HOST memory, with
+// the exact names and parameter lists of the kernels the reference compiler emits
+// (`tcrv_emitc_<kernel>_<variant>`), so a harness written for the generated RVV C links
+// against this library unchanged.  Each call stages its operands through a grow-only device
+// arena owned by the library, runs the same CUDA kernels as the device-pointer ABI, copies
+// the result back and returns when the output is in host memory.
+//
+// Weights are static: tcrv_cuda_host_register_weights() uploads a host weight buffer once and
+// later calls that pass the same host pointer use the resident copy (and, for the GEMM, its
+// prepared planar form).  Unregistered weights are uploaded on every call.
+#include <stdio.h>
+#include <stdlib.h>
+
+#include <map>
+#include <mutex>
+
+#include "launchers.h"
+#include "tcrv_common.cuh"
+#include "tcrv_emitc_host.h"
+
+namespace tcrv {
+namespace {
+
+struct ResidentWeights {
+  uint8_t *dev = nullptr;
+  size_t bytes = 0;
+  uint8_t *prepared = nullptr;  // GEMM planar form, built on first use
+  size_t prepared_n = 0, prepared_nr = 0, prepared_bx = 0;
+};
+
+struct HostContext {
+  std::mutex mu;
+  cudaStream_t stream = nullptr;
+  uint8_t *arena = nullptr;
+  size_t arena_cap = 0, arena_used = 0;
+  std::map<const void *, ResidentWeights> weights;
+};
+
+HostContext &ctx() {
+  static HostContext c;
+  return c;
+}
+
+inline size_t up256(size_t v) { return (v + 255) / 256 * 256; }
+
+int ensure_stream(HostContext &c) {
+  if (c.stream == nullptr)
+    TCRV_CUDA_TRY(cudaStreamCreateWithFlags(&c.stream, cudaStreamNonBlocking));
+  return TCRV_CUDA_OK;
+}
+
+// Makes room for `total` bytes and resets the bump pointer.  Growing frees the old arena,
+// so it must happen before any piece of the current call is carved.
+int arena_reserve(HostContext &c, size_t total) {
+  if (total > c.arena_cap) {
+    TCRV_CUDA_TRY(cudaStreamSynchronize(c.stream));
+    if (c.arena)
+      TCRV_CUDA_TRY(cudaFree(c.arena));
+    c.arena = nullptr;
+    c.arena_cap = 0;
+    const size_t want = up256(total + total / 4);
+    TCRV_CUDA_TRY(cudaMalloc(reinterpret_cast<void **>(&c.arena), want));
+    c.arena_cap = want;
+  }
+  c.arena_used = 0;
+  return TCRV_CUDA_OK;
+}
+
+uint8_t *arena_take(HostContext &c, size_t bytes) {
+  uint8_t *p = c.arena + c.arena_used;
+  c.arena_used += up256(bytes);
+  return p;
+}
+
+// rows x row_bytes, host stride -> packed device rows
+int upload_rows(HostContext &c, uint8_t *dst, const void *src, size_t rows, size_t row_bytes, size_t stride) {
+  if (rows == 0 || row_bytes == 0)
+    return TCRV_CUDA_OK;
+  if (rows == 1 || stride == row_bytes)
+    TCRV_CUDA_TRY(cudaMemcpyAsync(dst, src, rows * row_bytes, cudaMemcpyHostToDevice, c.stream));
+  else
+    TCRV_CUDA_TRY(cudaMemcpy2DAsync(dst, row_bytes, src, stride, row_bytes, rows, cudaMemcpyHostToDevice, c.stream));
+  return TCRV_CUDA_OK;
+}
+
+int finish(HostContext &c) {
+  TCRV_CUDA_TRY(cudaStreamSynchronize(c.stream));
+  return TCRV_CUDA_OK;
+}
+
+template <typename T, typename Launch>
+int host_binary(const T *lhs, const T *rhs, T *out, size_t n, Launch launch) {
+  if (n == 0)
+    return TCRV_CUDA_OK;
+  if (!lhs || !rhs || !out)
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  HostContext &c = ctx();
+  std::lock_guard<std::mutex> lock(c.mu);
+  int st = ensure_stream(c);
+  if (st == TCRV_CUDA_OK)
+    st = arena_reserve(c, 3 * up256(n * sizeof(T)));
+  if (st != TCRV_CUDA_OK)
+    return st;
+  T *dl = reinterpret_cast<T *>(arena_take(c, n * sizeof(T)));
+  T *dr = reinterpret_cast<T *>(arena_take(c, n * sizeof(T)));
+  T *dout = reinterpret_cast<T *>(arena_take(c, n * sizeof(T)));
+  TCRV_CUDA_TRY(cudaMemcpyAsync(dl, lhs, n * sizeof(T), cudaMemcpyHostToDevice, c.stream));
+  TCRV_CUDA_TRY(cudaMemcpyAsync(dr, rhs, n * sizeof(T), cudaMemcpyHostToDevice, c.stream));
+  st = launch(dl, dr, dout, n, c.stream);
+  if (st != TCRV_CUDA_OK)
+    return st;
+  TCRV_CUDA_TRY(cudaMemcpyAsync(out, dout, n * sizeof(T), cudaMemcpyDeviceToHost, c.stream));
+  return finish(c);
+}
+
+// s[ir*bs + col] for host operands; q8_weights selects the Q8_0 x Q8_0 block dot.
+int host_matmul(bool q8_weights, size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by, size_t nr,
+                size_t nc, size_t bx, size_t bs, unsigned flags = TCRV_CUDA_FLAG_NONE) {
+  if (n % kQK != 0)
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  if (nr == 0 || nc == 0)
+    return TCRV_CUDA_OK;
+  if (!s || !vx || !vy)
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  const size_t nb = n / kQK;
+  const size_t wrow = nb * (q8_weights ? kQ8Block : kQ4Block), xrow = nb * kQ8Block;
+  if ((nr > 1 && bx < wrow) || (nc > 1 && by < xrow) || (nr > 1 && bs < nc))
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  HostContext &c = ctx();
+  std::lock_guard<std::mutex> lock(c.mu);
+  int st = ensure_stream(c);
+  if (st != TCRV_CUDA_OK)
+    return st;
+
+  auto it = c.weights.find(vx);
+  ResidentWeights *res = it == c.weights.end() ? nullptr : &it->second;
+  const bool use_gemm = !q8_weights && nc > 8;
+  if (q8_weights && nc > 8)
+    return TCRV_CUDA_ERR_UNSUPPORTED;  // no Q8_0-weight prefill kernel
+  if (res && res->bytes < (nr - 1) * bx + wrow)
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+
+  const size_t w_dev_bytes = res ? 0 : nr * wrow;
+  const size_t prep_bytes = use_gemm && !(res && res->prepared) ? gemm_weights_bytes(n, nr) : 0;
+  const size_t acts_ws = use_gemm ? gemm_acts_bytes(n, nc) : 0;
+  // a resident weight keeps its prepared form outside the arena
+  const size_t arena_prep = res ? 0 : prep_bytes;
+  st = arena_reserve(c, up256(w_dev_bytes) + up256(arena_prep) + up256(acts_ws) + up256(nc * xrow) +
+                            up256(nr * nc * sizeof(float)) + 1024);
+  if (st != TCRV_CUDA_OK)
+    return st;
+
+  const uint8_t *dw;
+  size_t dbx;
+  if (res) {
+    dw = res->dev;
+    dbx = bx;
+  } else {
+    uint8_t *up = arena_take(c, w_dev_bytes);
+    st = upload_rows(c, up, vx, nr, wrow, bx);
+    if (st != TCRV_CUDA_OK)
+      return st;
+    dw = up;
+    dbx = wrow;
+  }
+  uint8_t *dx = arena_take(c, nc * xrow);
+  st = upload_rows(c, dx, vy, nc, xrow, by);
+  if (st != TCRV_CUDA_OK)
+    return st;
+  float *ds = reinterpret_cast<float *>(arena_take(c, nr * nc * sizeof(float)));
+
+  if (use_gemm) {
+    const uint8_t *prepared;
+    if (res) {
+      if (res->prepared && (res->prepared_n != n || res->prepared_nr != nr || res->prepared_bx != bx)) {
+        TCRV_CUDA_TRY(cudaStreamSynchronize(c.stream));
+        TCRV_CUDA_TRY(cudaFree(res->prepared));
+        res->prepared = nullptr;
+      }
+      if (!res->prepared) {
+        TCRV_CUDA_TRY(cudaMalloc(reinterpret_cast<void **>(&res->prepared), gemm_weights_bytes(n, nr)));
+        res->prepared_n = n, res->prepared_nr = nr, res->prepared_bx = bx;
+        st = launch_gemm_prepare_weights_q4_0(n, dw, dbx, nr, res->prepared, c.stream);
+        if (st != TCRV_CUDA_OK)
+          return st;
+      }
+      prepared = res->prepared;
+    } else {
+      uint8_t *p = arena_take(c, prep_bytes);
+      st = launch_gemm_prepare_weights_q4_0(n, dw, dbx, nr, p, c.stream);
+      if (st != TCRV_CUDA_OK)
+        return st;
+      prepared = p;
+    }
+    uint8_t *acts = arena_take(c, acts_ws);
+    st = launch_gemm_prepare_acts_q8_0(n, dx, xrow, nc, acts, c.stream);
+    if (st == TCRV_CUDA_OK)
+      st = launch_gemm_prepared(n, ds, prepared, acts, nr, nc, nc, c.stream);
+  } else if (q8_weights) {
+    st = launch_gemv<true>(n, ds, dw, dx, xrow, nr, nc, dbx, nc, flags, c.stream);
+  } else {
+    st = launch_gemv<false>(n, ds, dw, dx, xrow, nr, nc, dbx, nc, flags, c.stream);
+  }
+  if (st != TCRV_CUDA_OK)
+    return st;
+  if (nr == 1 || bs == nc)
+    TCRV_CUDA_TRY(cudaMemcpyAsync(s, ds, nr * nc * sizeof(float), cudaMemcpyDeviceToHost, c.stream));
+  else
+    TCRV_CUDA_TRY(cudaMemcpy2DAsync(s, bs * sizeof(float), ds, nc * sizeof(float), nc * sizeof(float), nr,
+                                    cudaMemcpyDeviceToHost, c.stream));
+  st = finish(c);
+  if (st != TCRV_CUDA_OK)
+    return st;
+  int word = 0;
+  TCRV_CUDA_TRY(cudaMemcpyFromSymbol(&word, g_device_error, sizeof word));
+  return word != 0 ? TCRV_CUDA_ERR_DEVICE_TIMEOUT : TCRV_CUDA_OK;
+}
+
+// The generated kernels return void and cannot fail; a provider error ends the process
+// with a message instead of returning garbage.
+void must(int status, const char *entry) {
+  if (status == TCRV_CUDA_OK)
+    return;
+  fprintf(stderr, "%s: %s [%s]\n", entry, tcrv_cuda_status_string(status), tcrv_cuda_last_error_text());
+  abort();
+}
+
+}  // namespace
+}  // namespace tcrv
+
+using namespace tcrv;
+
+extern "C" {
+
+int tcrv_cuda_host_register_weights(const void *host, size_t bytes) {
+  if (!host || bytes == 0)
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  HostContext &c = ctx();
+  std::lock_guard<std::mutex> lock(c.mu);
+  int st = ensure_stream(c);
+  if (st != TCRV_CUDA_OK)
+    return st;
+  ResidentWeights &r = c.weights[host];
+  if (r.dev) {
+    TCRV_CUDA_TRY(cudaStreamSynchronize(c.stream));
+    TCRV_CUDA_TRY(cudaFree(r.dev));
+    if (r.prepared)
+      TCRV_CUDA_TRY(cudaFree(r.prepared));
+    r = ResidentWeights();
+  }
+  TCRV_CUDA_TRY(cudaMalloc(reinterpret_cast<void **>(&r.dev), bytes));
+  r.bytes = bytes;
+  TCRV_CUDA_TRY(cudaMemcpyAsync(r.dev, host, bytes, cudaMemcpyHostToDevice, c.stream));
+  return finish(c);
+}
+
+int tcrv_cuda_host_unregister_weights(const void *host) {
+  HostContext &c = ctx();
+  std::lock_guard<std::mutex> lock(c.mu);
+  auto it = c.weights.find(host);
+  if (it == c.weights.end())
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  if (c.stream)
+    TCRV_CUDA_TRY(cudaStreamSynchronize(c.stream));
+  if (it->second.dev)
+    TCRV_CUDA_TRY(cudaFree(it->second.dev));
+  if (it->second.prepared)
+    TCRV_CUDA_TRY(cudaFree(it->second.prepared));
+  c.weights.erase(it);
+  return TCRV_CUDA_OK;
+}
+
+int tcrv_cuda_host_release(void) {
+  HostContext &c = ctx();
+  std::lock_guard<std::mutex> lock(c.mu);
+  if (c.stream)
+    TCRV_CUDA_TRY(cudaStreamSynchronize(c.stream));
+  for (auto &kv : c.weights) {
+    if (kv.second.dev)
+      (void)cudaFree(kv.second.dev);
+    if (kv.second.prepared)
+      (void)cudaFree(kv.second.prepared);
+  }
+  c.weights.clear();
+  if (c.arena)
+    (void)cudaFree(c.arena);
+  c.arena = nullptr;
+  c.arena_cap = c.arena_used = 0;
+  return TCRV_CUDA_OK;
+}
+
+int tcrv_cuda_host_add_f32(const float *lhs, const float *rhs, float *out, size_t n) {
+  return host_binary<float>(lhs, rhs, out, n, launch_add_f32);
+}
+
+int tcrv_cuda_host_add_i32(const int32_t *lhs, const int32_t *rhs, int32_t *out, size_t n) {
+  return host_binary<int32_t>(lhs, rhs, out, n, launch_add_i32);
+}
+
+int tcrv_cuda_host_dequantize_i32_f32(const int32_t *lhs, float scale, float *out, size_t n) {
+  if (n == 0)
+    return TCRV_CUDA_OK;
+  if (!lhs || !out)
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  HostContext &c = ctx();
+  std::lock_guard<std::mutex> lock(c.mu);
+  int st = ensure_stream(c);
+  if (st == TCRV_CUDA_OK)
+    st = arena_reserve(c, 2 * up256(n * 4));
+  if (st != TCRV_CUDA_OK)
+    return st;
+  int32_t *dl = reinterpret_cast<int32_t *>(arena_take(c, n * 4));
+  float *dout = reinterpret_cast<float *>(arena_take(c, n * 4));
+  TCRV_CUDA_TRY(cudaMemcpyAsync(dl, lhs, n * 4, cudaMemcpyHostToDevice, c.stream));
+  st = launch_dequantize_i32_f32(dl, scale, dout, n, c.stream);
+  if (st != TCRV_CUDA_OK)
+    return st;
+  TCRV_CUDA_TRY(cudaMemcpyAsync(out, dout, n * 4, cudaMemcpyDeviceToHost, c.stream));
+  return finish(c);
+}
+
+int tcrv_cuda_host_quantize_row_q8_0(size_t n, const float *x, uint8_t *vy) {
+  if (n % kQK != 0)
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  if (n == 0)
+    return TCRV_CUDA_OK;
+  if (!x || !vy)
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  HostContext &c = ctx();
+  std::lock_guard<std::mutex> lock(c.mu);
+  const size_t out_bytes = n / kQK * kQ8Block;
+  int st = ensure_stream(c);
+  if (st == TCRV_CUDA_OK)
+    st = arena_reserve(c, up256(n * 4) + up256(out_bytes));
+  if (st != TCRV_CUDA_OK)
+    return st;
+  float *dx = reinterpret_cast<float *>(arena_take(c, n * 4));
+  uint8_t *dy = arena_take(c, out_bytes);
+  TCRV_CUDA_TRY(cudaMemcpyAsync(dx, x, n * 4, cudaMemcpyHostToDevice, c.stream));
+  st = launch_quantize_row_q8_0(n, dx, dy, c.stream);
+  if (st != TCRV_CUDA_OK)
+    return st;
+  TCRV_CUDA_TRY(cudaMemcpyAsync(vy, dy, out_bytes, cudaMemcpyDeviceToHost, c.stream));
+  return finish(c);
+}
+
+int tcrv_cuda_host_gemm_q4_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by, size_t nr,
+                                  size_t nc, size_t bx, size_t bs) {
+  return host_matmul(false, n, s, vx, vy, by, nr, nc, bx, bs);
+}
+
+int tcrv_cuda_host_gemm_q8_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by, size_t nr,
+                                  size_t nc, size_t bx, size_t bs) {
+  return host_matmul(true, n, s, vx, vy, by, nr, nc, bx, bs);
+}
+
+// ---- reference-named entry points (fixture kernel symbol + variant symbol) ----
+
+void tcrv_emitc_explicit_selected_body_add_kernel_explicit_selected_body_rvv_i32_add(const int32_t *lhs,
+                                                                                     const int32_t *rhs,
+                                                                                     int32_t *out, size_t n) {
+  must(tcrv_cuda_host_add_i32(lhs, rhs, out, n), __func__);
+}
+
+void tcrv_emitc_explicit_selected_body_add_f32_kernel_explicit_selected_body_cuda_f32_add(const float *lhs,
+                                                                                          const float *rhs,
+                                                                                          float *out, size_t n) {
+  must(tcrv_cuda_host_add_f32(lhs, rhs, out, n), __func__);
+}
+
+void tcrv_emitc_explicit_selected_body_dequantize_i32_to_f32_kernel_explicit_selected_body_rvv_dequantize_i32_to_f32(
+    const int32_t *lhs, float scale, float *out, size_t n) {
+  must(tcrv_cuda_host_dequantize_i32_f32(lhs, scale, out, n), __func__);
+}
+
+void tcrv_emitc_quantize_row_q8_0_kernel_quantize_row_q8_0(size_t n, const float *x, uint8_t *vy) {
+  must(tcrv_cuda_host_quantize_row_q8_0(n, x, vy), __func__);
+}
+
+void tcrv_emitc_ggml_vec_dot_q4_0_q8_0_kernel_ggml_vec_dot_q4_0_q8_0(size_t n, float *s, size_t bs, const uint8_t *vx,
+                                                                     size_t bx, const uint8_t *vy, size_t by,
+                                                                     int32_t nrc) {
+  (void)bs;
+  (void)bx;
+  (void)by;
+  (void)nrc;
+  must(host_matmul(false, n, s, vx, vy, 0, 1, 1, 0, 1, TCRV_CUDA_FLAG_STRICT_ORDER), __func__);
+}
+
+void tcrv_emitc_ggml_vec_dot_q8_0_q8_0_kernel_ggml_vec_dot_q8_0_q8_0(size_t n, float *s, const uint8_t *vx,
+                                                                     const uint8_t *vy) {
+  must(host_matmul(true, n, s, vx, vy, 0, 1, 1, 0, 1, TCRV_CUDA_FLAG_STRICT_ORDER), __func__);
+}
+
+void tcrv_emitc_ggml_q4_0_q8_0_gemm_kernel_ggml_q4_0_q8_0_gemm(size_t n, float *s, const uint8_t *vx,
+                                                               const uint8_t *vy, size_t by, size_t nr, size_t nc,
+                                                               size_t bx, size_t bs) {
+  must(host_matmul(false, n, s, vx, vy, by, nr, nc, bx, bs), __func__);
+}
+
+}  // extern "C"
