@@ -128,7 +128,7 @@ int launch_stream_instance(const GemvArgs &args, int grid, size_t smem, cudaStre
                                        static_cast<int>(kMaxDynamicSmem)));
     configured[dev] = true;
   }
-  kernel<<<grid, kGemvThreads, smem, stream>>>(args);
+  kernel<<<grid, (args.nwarps + 1) * 32, smem, stream>>>(args);
   TCRV_CUDA_TRY(cudaGetLastError());
   return TCRV_CUDA_OK;
 }
@@ -140,8 +140,6 @@ int launch_stream(const GemvArgs &args, uint32_t nc, int grid, size_t smem, cuda
     case 1:
       if (npairs <= 64)
         return launch_stream_instance<kQ8W, 1, 2>(args, grid, smem, stream);
-      if (npairs <= 192)
-        return launch_stream_instance<kQ8W, 1, 6>(args, grid, smem, stream);
       return launch_stream_instance<kQ8W, 1, 0>(args, grid, smem, stream);
     case 2:
       return launch_stream_instance<kQ8W, 2, 0>(args, grid, smem, stream);
@@ -179,11 +177,19 @@ int launch_gemv(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t
   if (!strict && nb > 0 && nb % 8 == 0 && nc <= kGemvMaxCols && multiple_of(vx, 16) && bx % 16 == 0 &&
       multiple_of(vy, 2) && by % 2 == 0) {
     const size_t fixed = kGemvBarrierBytes + nc * static_cast<size_t>(gemv_xcol_bytes(nb));
-    const size_t stage = kGemvRowsPerChunk * row_bytes;
-    if (fixed + 2 * stage <= kMaxDynamicSmem) {
-      size_t ns = (kMaxDynamicSmem - fixed) / stage;
-      if (ns > kGemvMaxStages)
-        ns = kGemvMaxStages;
+    const size_t slot = kGemvRowsPerSlot * row_bytes;
+    if (fixed + 2 * slot <= kMaxDynamicSmem) {
+      const size_t total_slots = (kMaxDynamicSmem - fixed) / slot;
+      size_t nwarps, spw;
+      if (total_slots >= 2 * kGemvMaxConsumerWarps) {
+        nwarps = kGemvMaxConsumerWarps;
+        spw = total_slots / nwarps;
+        if (spw > kGemvMaxSlotsPerWarp)
+          spw = kGemvMaxSlotsPerWarp;
+      } else {
+        nwarps = total_slots / 2;
+        spw = 2;
+      }
       GemvArgs args;
       args.vx = vx;
       args.vy = vy;
@@ -194,11 +200,13 @@ int launch_gemv(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t
       args.nr = static_cast<uint32_t>(nr);
       args.nb = nb;
       args.row_bytes = static_cast<uint32_t>(row_bytes);
-      args.nstages = static_cast<uint32_t>(ns);
-      const size_t chunks = (nr + kGemvRowsPerChunk - 1) / kGemvRowsPerChunk;
+      args.nwarps = static_cast<uint32_t>(nwarps);
+      args.slots = static_cast<uint32_t>(spw);
+      args.contiguous = (bx == row_bytes) ? 1u : 0u;
+      const size_t pairs = (nr + kGemvRowsPerSlot - 1) / kGemvRowsPerSlot;
       const int sms = sm_count();
-      const int grid = static_cast<int>(chunks < static_cast<size_t>(sms) ? chunks : sms);
-      return launch_stream<kQ8W>(args, static_cast<uint32_t>(nc), grid, fixed + ns * stage, stream);
+      const int grid = static_cast<int>(pairs < static_cast<size_t>(sms) ? pairs : sms);
+      return launch_stream<kQ8W>(args, static_cast<uint32_t>(nc), grid, fixed + nwarps * spw * slot, stream);
     }
   }
 

@@ -1,15 +1,17 @@
 // Decode GEMV, streaming form: s[row*bs + col] = block dot(weight row, activation column),
 // for up to 8 activation columns.  HBM-bound: the weight matrix is read exactly once.
 //
-// One persistent CTA per SM owns a contiguous range of weight rows and walks it in chunks
-// of 8 rows.  A producer warp feeds a ring of shared-memory stages with the 1-D bulk copy
-// engine (one cp.async.bulk per row, completion counted on an mbarrier); eight consumer
-// warps each take one row of the chunk.  Rows stay in the plain 18-byte (Q4_0) or 34-byte
-// (Q8_0) block format.  A lane owns PAIRS of adjacent blocks: a pair is 36 or 68 bytes, i.e.
-// 9 or 17 aligned 32-bit words, and both strides are odd, so the 32 lanes of a warp read
-// shared memory without bank conflicts.  The fp16 scale of the even block sits in the low
-// half of word 0 and its quants straddle words (re-aligned with funnel shifts); the odd
-// block's scale is the high half of the middle word and its quants are word aligned.
+// One persistent CTA per SM owns a contiguous range of weight rows, taken two rows at a
+// time.  A producer warp feeds per-warp rings of shared-memory slots (one slot = two
+// adjacent rows) with the 1-D bulk copy engine (cp.async.bulk, completion counted on the
+// slot's mbarrier); up to 16 consumer warps each own a ring and work on both rows of a slot
+// at once, so that about 32 rows are in flight per SM -- the kernel is latency-bound below
+// that.  Rows stay in the plain 18-byte (Q4_0) or 34-byte (Q8_0) block format.  A lane owns
+// PAIRS of adjacent blocks: a pair is 36 or 68 bytes, i.e. 9 or 17 aligned 32-bit words,
+// and both strides are odd, so the 32 lanes of a warp read shared memory without bank
+// conflicts.  The fp16 scale of the even block sits in the low half of word 0 and its
+// quants straddle words (re-aligned with funnel shifts); the odd block's scale is the high
+// half of the middle word and its quants are word aligned.
 //
 // The activation columns are converted once per CTA into a lane-friendly layout: for every
 // block pair four 16-byte pieces (stored as four planes so that consecutive lanes read
@@ -26,11 +28,11 @@
 
 namespace tcrv {
 
-constexpr int kGemvConsumerWarps = 8;
-constexpr int kGemvRowsPerChunk = kGemvConsumerWarps;
-constexpr int kGemvThreads = (kGemvConsumerWarps + 1) * 32;
-constexpr int kGemvMaxStages = 8;
-constexpr int kGemvBarrierBytes = 128;
+constexpr int kGemvMaxConsumerWarps = 16;
+constexpr int kGemvMaxSlotsPerWarp = 8;
+constexpr int kGemvMaxThreads = (kGemvMaxConsumerWarps + 1) * 32;
+constexpr int kGemvRowsPerSlot = 2;
+constexpr int kGemvBarrierBytes = 2 * kGemvMaxConsumerWarps * kGemvMaxSlotsPerWarp * 8;  // full + empty
 constexpr int kGemvMaxCols = 8;
 
 struct GemvArgs {
@@ -41,7 +43,9 @@ struct GemvArgs {
   uint32_t nr;
   uint32_t nb;         // blocks per row
   uint32_t row_bytes;  // nb * block bytes
-  uint32_t nstages;
+  uint32_t nwarps;     // consumer warps (the producer is one more warp)
+  uint32_t slots;      // slots per consumer warp
+  uint32_t contiguous; // bx == row_bytes: both rows of a slot arrive in one copy
 };
 
 template <bool kQ8W>
@@ -97,37 +101,105 @@ __device__ __forceinline__ float fold_pair(float acc, const uint32_t *w, const X
   return acc;
 }
 
+// Folds all block pairs of `kRows` weight rows (kRows = 1 or 2, the rows of one slot) against
+// every activation column, then reduces over the warp and stores.
+template <bool kQ8W, int kCols, int kXRegPairs, int kRows>
+__device__ __forceinline__ void gemv_rows(const GemvArgs &a, const uint32_t *wrow0, const uint8_t *xsm,
+                                          uint32_t xcol_bytes, const XBlockPair *xr, uint32_t row, int lane) {
+  using F = WeightFormat<kQ8W>;
+  constexpr int PW = F::kPairWords;
+  const uint32_t nb = a.nb, npairs = nb / 2;
+  const uint32_t row_words = a.row_bytes / 4;
+  float acc[kRows][kCols];
+#pragma unroll
+  for (int r = 0; r < kRows; ++r)
+#pragma unroll
+    for (int b = 0; b < kCols; ++b)
+      acc[r][b] = 0.0f;
+  if constexpr (kXRegPairs > 0) {
+#pragma unroll
+    for (int i = 0; i < kXRegPairs; ++i) {
+      const uint32_t p = lane + 32u * i;
+      if (p < npairs) {
+        uint32_t w[kRows][PW];
+#pragma unroll
+        for (int r = 0; r < kRows; ++r)
+#pragma unroll
+          for (int j = 0; j < PW; ++j)
+            w[r][j] = wrow0[r * row_words + p * PW + j];
+#pragma unroll
+        for (int r = 0; r < kRows; ++r)
+          acc[r][0] = fold_pair<kQ8W>(acc[r][0], w[r], xr[i]);
+      }
+    }
+  } else {
+    for (uint32_t p = lane; p < npairs; p += 32) {
+      uint32_t w[kRows][PW];
+#pragma unroll
+      for (int r = 0; r < kRows; ++r)
+#pragma unroll
+        for (int j = 0; j < PW; ++j)
+          w[r][j] = wrow0[r * row_words + p * PW + j];
+#pragma unroll
+      for (int b = 0; b < kCols; ++b) {
+        XBlockPair x;
+        load_xpair(x, xsm + static_cast<size_t>(b) * xcol_bytes, npairs, nb, p);
+#pragma unroll
+        for (int r = 0; r < kRows; ++r)
+          acc[r][b] = fold_pair<kQ8W>(acc[r][b], w[r], x);
+      }
+    }
+  }
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1) {
+#pragma unroll
+    for (int r = 0; r < kRows; ++r)
+#pragma unroll
+      for (int b = 0; b < kCols; ++b)
+        acc[r][b] = __fadd_rn(acc[r][b], __shfl_xor_sync(0xffffffffu, acc[r][b], off));
+  }
+#pragma unroll
+  for (int r = 0; r < kRows; ++r) {
+    float mine = acc[r][0];
+#pragma unroll
+    for (int b = 1; b < kCols; ++b)
+      mine = lane == b ? acc[r][b] : mine;
+    if (lane < kCols)
+      a.s[static_cast<size_t>(row + r) * a.bs + lane] = mine;
+  }
+}
+
 // kCols: activation columns (1..8).  kXRegPairs: when > 0 (single column only) the lane keeps
 // its activation pairs in registers for the whole kernel; requires npairs <= 32*kXRegPairs.
 template <bool kQ8W, int kCols, int kXRegPairs>
-__global__ void __launch_bounds__(kGemvThreads, 1) gemv_stream_kernel(const GemvArgs a) {
-  using F = WeightFormat<kQ8W>;
-  constexpr int PW = F::kPairWords;
+__global__ void __launch_bounds__(kGemvMaxThreads, 1) gemv_stream_kernel(const GemvArgs a) {
   extern __shared__ __align__(128) uint8_t smem[];
   uint64_t *full = reinterpret_cast<uint64_t *>(smem);
-  uint64_t *empty = full + kGemvMaxStages;
+  uint64_t *empty = full + kGemvMaxConsumerWarps * kGemvMaxSlotsPerWarp;
   uint8_t *xsm = smem + kGemvBarrierBytes;
   const uint32_t nb = a.nb, npairs = nb / 2;
   const uint32_t xcol_bytes = gemv_xcol_bytes(nb);
-  uint8_t *stages = xsm + static_cast<size_t>(kCols) * xcol_bytes;
-  const uint32_t stage_bytes = kGemvRowsPerChunk * a.row_bytes;
-  const uint32_t ns = a.nstages;
+  uint8_t *slots = xsm + static_cast<size_t>(kCols) * xcol_bytes;
+  const uint32_t slot_bytes = kGemvRowsPerSlot * a.row_bytes;
+  const uint32_t nwarps = a.nwarps, spw = a.slots;
+  const uint32_t nthreads = (nwarps + 1) * 32;
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // contiguous, balanced row range of this CTA
+  const uint32_t warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  // contiguous, balanced row range of this CTA, walked two rows (one slot) at a time
   const uint32_t r0 = static_cast<uint32_t>(static_cast<uint64_t>(a.nr) * blockIdx.x / gridDim.x);
   const uint32_t r1 = static_cast<uint32_t>(static_cast<uint64_t>(a.nr) * (blockIdx.x + 1) / gridDim.x);
-  const uint32_t nchunks = (r1 - r0 + kGemvRowsPerChunk - 1) / kGemvRowsPerChunk;
+  const uint32_t nslots = (r1 - r0 + kGemvRowsPerSlot - 1) / kGemvRowsPerSlot;
 
   if (threadIdx.x == 0) {
-    for (uint32_t i = 0; i < ns; ++i) {
+    for (uint32_t i = 0; i < nwarps * spw; ++i) {
       mbar_init(&full[i], 1);
-      mbar_init(&empty[i], kGemvConsumerWarps);
+      mbar_init(&empty[i], 1);
     }
     mbar_fence_init();
   }
   // Convert the activation columns (plain block_q8_0, 2-byte aligned) into the lane layout.
-  for (uint32_t idx = threadIdx.x; idx < kCols * nb; idx += kGemvThreads) {
+  for (uint32_t idx = threadIdx.x; idx < kCols * nb; idx += nthreads) {
     const uint32_t col = idx / nb, ib = idx - col * nb;
     const uint8_t *src = a.vy + col * a.by + static_cast<size_t>(ib) * kQ8Block;
     const unsigned short *h = reinterpret_cast<const unsigned short *>(src);
@@ -145,36 +217,45 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_stream_kernel(const Gemv
   }
   __syncthreads();
 
-  if (warp == kGemvConsumerWarps) {
+  if (warp == nwarps) {
     // ---------------- producer: one lane issues the bulk copies ----------------
     if (lane == 0) {
       uint32_t issued = 0;
       bool ok = true;
-      for (uint32_t c = 0; c < nchunks && ok; ++c) {
-        const uint32_t st = c % ns, use = c / ns;
-        if (use > 0)
-          ok = mbar_wait_bounded(&empty[st], (use - 1) & 1);
-        if (!ok)
+      for (uint32_t j = 0; j < nslots; ++j) {
+        const uint32_t w = j % nwarps, t = j / nwarps;
+        const uint32_t bar = w * spw + t % spw, use = t / spw;
+        if (use > 0 && !mbar_wait_bounded(&empty[bar], (use - 1) & 1)) {
+          ok = false;
           break;
-        const uint32_t row = r0 + c * kGemvRowsPerChunk;
-        const uint32_t rows = min(static_cast<uint32_t>(kGemvRowsPerChunk), r1 - row);
-        mbar_arrive_expect_tx(&full[st], rows * a.row_bytes);
-        uint8_t *dst = stages + static_cast<size_t>(st) * stage_bytes;
-        for (uint32_t r = 0; r < rows; ++r)
-          bulk_copy_g2s(dst + r * a.row_bytes, a.vx + static_cast<size_t>(row + r) * a.bx, a.row_bytes, &full[st]);
-        issued = c + 1;
+        }
+        const uint32_t row = r0 + j * kGemvRowsPerSlot;
+        const uint32_t rows = min(static_cast<uint32_t>(kGemvRowsPerSlot), r1 - row);
+        mbar_arrive_expect_tx(&full[bar], rows * a.row_bytes);
+        uint8_t *dst = slots + static_cast<size_t>(bar) * slot_bytes;
+        const uint8_t *src = a.vx + static_cast<size_t>(row) * a.bx;
+        if (a.contiguous) {
+          bulk_copy_g2s(dst, src, rows * a.row_bytes, &full[bar]);
+        } else {
+          for (uint32_t r = 0; r < rows; ++r)
+            bulk_copy_g2s(dst + r * a.row_bytes, src + r * a.bx, a.row_bytes, &full[bar]);
+        }
+        issued = j + 1;
       }
       if (!ok)
         atomicOr(&g_device_error, kDevErrBarrierTimeout);
       // Do not leave while copies of this CTA may still be in flight.
-      const uint32_t first = issued > ns ? issued - ns : 0;
-      for (uint32_t c = first; c < issued; ++c)
-        (void)mbar_wait_bounded(&full[c % ns], (c / ns) & 1);
+      const uint32_t ring = nwarps * spw;
+      const uint32_t first = issued > ring ? issued - ring : 0;
+      for (uint32_t j = first; j < issued; ++j) {
+        const uint32_t w = j % nwarps, t = j / nwarps;
+        (void)mbar_wait_bounded(&full[w * spw + t % spw], (t / spw) & 1);
+      }
     }
     return;
   }
 
-  // ---------------- consumers: warp w takes row w of every chunk ----------------
+  // ---------------- consumers: warp w takes slots w, w + nwarps, ... ----------------
   XBlockPair xr[kXRegPairs > 0 ? kXRegPairs : 1];
   if constexpr (kXRegPairs > 0) {
 #pragma unroll
@@ -185,63 +266,22 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_stream_kernel(const Gemv
     }
   }
 
-  for (uint32_t c = 0; c < nchunks; ++c) {
-    const uint32_t st = c % ns;
-    if (!mbar_wait_bounded(&full[st], (c / ns) & 1)) {
+  for (uint32_t j = warp, t = 0; j < nslots; j += nwarps, ++t) {
+    const uint32_t bar = warp * spw + t % spw;
+    if (!mbar_wait_bounded(&full[bar], (t / spw) & 1)) {
       if (lane == 0)
         atomicOr(&g_device_error, kDevErrBarrierTimeout);
       return;
     }
-    const uint32_t row = r0 + c * kGemvRowsPerChunk + warp;
-    if (row < r1) {
-      const uint32_t *wrow =
-          reinterpret_cast<const uint32_t *>(stages + static_cast<size_t>(st) * stage_bytes + warp * a.row_bytes);
-      float acc[kCols];
-#pragma unroll
-      for (int b = 0; b < kCols; ++b)
-        acc[b] = 0.0f;
-      if constexpr (kXRegPairs > 0) {
-#pragma unroll
-        for (int i = 0; i < kXRegPairs; ++i) {
-          const uint32_t p = lane + 32u * i;
-          if (p < npairs) {
-            uint32_t w[PW];
-#pragma unroll
-            for (int j = 0; j < PW; ++j)
-              w[j] = wrow[p * PW + j];
-            acc[0] = fold_pair<kQ8W>(acc[0], w, xr[i]);
-          }
-        }
-      } else {
-        for (uint32_t p = lane; p < npairs; p += 32) {
-          uint32_t w[PW];
-#pragma unroll
-          for (int j = 0; j < PW; ++j)
-            w[j] = wrow[p * PW + j];
-#pragma unroll
-          for (int b = 0; b < kCols; ++b) {
-            XBlockPair x;
-            load_xpair(x, xsm + static_cast<size_t>(b) * xcol_bytes, npairs, nb, p);
-            acc[b] = fold_pair<kQ8W>(acc[b], w, x);
-          }
-        }
-      }
-#pragma unroll
-      for (int off = 16; off >= 1; off >>= 1) {
-#pragma unroll
-        for (int b = 0; b < kCols; ++b)
-          acc[b] = __fadd_rn(acc[b], __shfl_xor_sync(0xffffffffu, acc[b], off));
-      }
-      float mine = acc[0];
-#pragma unroll
-      for (int b = 1; b < kCols; ++b)
-        mine = lane == b ? acc[b] : mine;
-      if (lane < kCols)
-        a.s[static_cast<size_t>(row) * a.bs + lane] = mine;
-    }
+    const uint32_t row = r0 + j * kGemvRowsPerSlot;
+    const uint32_t *wrow = reinterpret_cast<const uint32_t *>(slots + static_cast<size_t>(bar) * slot_bytes);
+    if (row + 1 < r1)
+      gemv_rows<kQ8W, kCols, kXRegPairs, 2>(a, wrow, xsm, xcol_bytes, xr, row, lane);
+    else
+      gemv_rows<kQ8W, kCols, kXRegPairs, 1>(a, wrow, xsm, xcol_bytes, xr, row, lane);
     __syncwarp();
     if (lane == 0)
-      mbar_arrive(&empty[st]);
+      mbar_arrive(&empty[bar]);
   }
 }
 
