@@ -128,7 +128,7 @@ int launch_stream_instance(const GemvArgs &args, int grid, size_t smem, cudaStre
                                        static_cast<int>(kMaxDynamicSmem)));
     configured[dev] = true;
   }
-  kernel<<<grid, (args.nwarps + 1) * 32, smem, stream>>>(args);
+  kernel<<<grid, args.nwarps * 32, smem, stream>>>(args);
   TCRV_CUDA_TRY(cudaGetLastError());
   return TCRV_CUDA_OK;
 }

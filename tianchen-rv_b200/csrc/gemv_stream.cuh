@@ -2,16 +2,17 @@
 // for up to 8 activation columns.  HBM-bound: the weight matrix is read exactly once.
 //
 // One persistent CTA per SM owns a contiguous range of weight rows, taken two rows at a
-// time.  A producer warp feeds per-warp rings of shared-memory slots (one slot = two
-// adjacent rows) with the 1-D bulk copy engine (cp.async.bulk, completion counted on the
-// slot's mbarrier); up to 16 consumer warps each own a ring and work on both rows of a slot
-// at once, so that about 32 rows are in flight per SM -- the kernel is latency-bound below
-// that.  Rows stay in the plain 18-byte (Q4_0) or 34-byte (Q8_0) block format.  A lane owns
-// PAIRS of adjacent blocks: a pair is 36 or 68 bytes, i.e. 9 or 17 aligned 32-bit words,
-// and both strides are odd, so the 32 lanes of a warp read shared memory without bank
-// conflicts.  The fp16 scale of the even block sits in the low half of word 0 and its
-// quants straddle words (re-aligned with funnel shifts); the odd block's scale is the high
-// half of the middle word and its quants are word aligned.
+// time.  Up to 16 warps each own a private ring of shared-memory slots (one slot = two
+// adjacent rows) and keep it full themselves: lane 0 issues a 1-D bulk copy
+// (cp.async.bulk, completion counted on the slot's mbarrier) for the slot it has just
+// finished, so copy issue is spread over all warps and no warp waits for another.  Each warp
+// works on both rows of a slot at once; about 32 rows are in flight per SM, below that the
+// kernel is latency-bound.  Rows stay in the plain 18-byte (Q4_0) or 34-byte (Q8_0) block
+// format.  A lane owns PAIRS of adjacent blocks: a pair is 36 or 68 bytes, i.e. 9 or 17
+// aligned 32-bit words, and both strides are odd, so the 32 lanes of a warp read shared
+// memory without bank conflicts.  The fp16 scale of the even block sits in the low half of
+// word 0 and its quants straddle words (re-aligned with funnel shifts); the odd block's
+// scale is the high half of the middle word and its quants are word aligned.
 //
 // The activation columns are converted once per CTA into a lane-friendly layout: for every
 // block pair four 16-byte pieces (stored as four planes so that consecutive lanes read
@@ -30,9 +31,9 @@ namespace tcrv {
 
 constexpr int kGemvMaxConsumerWarps = 16;
 constexpr int kGemvMaxSlotsPerWarp = 8;
-constexpr int kGemvMaxThreads = (kGemvMaxConsumerWarps + 1) * 32;
+constexpr int kGemvMaxThreads = kGemvMaxConsumerWarps * 32;
 constexpr int kGemvRowsPerSlot = 2;
-constexpr int kGemvBarrierBytes = 2 * kGemvMaxConsumerWarps * kGemvMaxSlotsPerWarp * 8;  // full + empty
+constexpr int kGemvBarrierBytes = kGemvMaxConsumerWarps * kGemvMaxSlotsPerWarp * 8;  // one "full" barrier per slot
 constexpr int kGemvMaxCols = 8;
 
 struct GemvArgs {
@@ -43,7 +44,7 @@ struct GemvArgs {
   uint32_t nr;
   uint32_t nb;         // blocks per row
   uint32_t row_bytes;  // nb * block bytes
-  uint32_t nwarps;     // consumer warps (the producer is one more warp)
+  uint32_t nwarps;     // warps per CTA
   uint32_t slots;      // slots per consumer warp
   uint32_t contiguous; // bx == row_bytes: both rows of a slot arrive in one copy
 };
@@ -175,28 +176,46 @@ template <bool kQ8W, int kCols, int kXRegPairs>
 __global__ void __launch_bounds__(kGemvMaxThreads, 1) gemv_stream_kernel(const GemvArgs a) {
   extern __shared__ __align__(128) uint8_t smem[];
   uint64_t *full = reinterpret_cast<uint64_t *>(smem);
-  uint64_t *empty = full + kGemvMaxConsumerWarps * kGemvMaxSlotsPerWarp;
   uint8_t *xsm = smem + kGemvBarrierBytes;
   const uint32_t nb = a.nb, npairs = nb / 2;
   const uint32_t xcol_bytes = gemv_xcol_bytes(nb);
   uint8_t *slots = xsm + static_cast<size_t>(kCols) * xcol_bytes;
   const uint32_t slot_bytes = kGemvRowsPerSlot * a.row_bytes;
   const uint32_t nwarps = a.nwarps, spw = a.slots;
-  const uint32_t nthreads = (nwarps + 1) * 32;
+  const uint32_t nthreads = nwarps * 32;
 
   const uint32_t warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  // contiguous, balanced row range of this CTA, walked two rows (one slot) at a time
+  // contiguous, balanced row range of this CTA, walked two rows (one slot) at a time;
+  // warp w takes slots w, w + nwarps, ...
   const uint32_t r0 = static_cast<uint32_t>(static_cast<uint64_t>(a.nr) * blockIdx.x / gridDim.x);
   const uint32_t r1 = static_cast<uint32_t>(static_cast<uint64_t>(a.nr) * (blockIdx.x + 1) / gridDim.x);
   const uint32_t nslots = (r1 - r0 + kGemvRowsPerSlot - 1) / kGemvRowsPerSlot;
+  const uint32_t mine = warp < nslots ? (nslots - warp + nwarps - 1) / nwarps : 0;  // slots of this warp
 
-  if (threadIdx.x == 0) {
-    for (uint32_t i = 0; i < nwarps * spw; ++i) {
-      mbar_init(&full[i], 1);
-      mbar_init(&empty[i], 1);
+  // Issues the copy of this warp's t-th slot into ring position t % spw (one lane calls it).
+  auto issue = [&](uint32_t t) {
+    const uint32_t bar = warp * spw + t % spw;
+    const uint32_t row = r0 + (warp + t * nwarps) * kGemvRowsPerSlot;
+    const uint32_t rows = min(static_cast<uint32_t>(kGemvRowsPerSlot), r1 - row);
+    mbar_arrive_expect_tx(&full[bar], rows * a.row_bytes);
+    uint8_t *dst = slots + static_cast<size_t>(bar) * slot_bytes;
+    const uint8_t *src = a.vx + static_cast<size_t>(row) * a.bx;
+    if (a.contiguous) {
+      bulk_copy_g2s(dst, src, rows * a.row_bytes, &full[bar]);
+    } else {
+      for (uint32_t r = 0; r < rows; ++r)
+        bulk_copy_g2s(dst + r * a.row_bytes, src + r * a.bx, a.row_bytes, &full[bar]);
     }
+  };
+
+  if (lane == 0) {
+    for (uint32_t i = 0; i < spw; ++i)
+      mbar_init(&full[warp * spw + i], 1);
     mbar_fence_init();
+    // Start streaming weights right away; they do not depend on the activation staging.
+    for (uint32_t t = 0; t < min(spw, mine); ++t)
+      issue(t);
   }
   // Convert the activation columns (plain block_q8_0, 2-byte aligned) into the lane layout.
   for (uint32_t idx = threadIdx.x; idx < kCols * nb; idx += nthreads) {
@@ -217,45 +236,6 @@ __global__ void __launch_bounds__(kGemvMaxThreads, 1) gemv_stream_kernel(const G
   }
   __syncthreads();
 
-  if (warp == nwarps) {
-    // ---------------- producer: one lane issues the bulk copies ----------------
-    if (lane == 0) {
-      uint32_t issued = 0;
-      bool ok = true;
-      for (uint32_t j = 0; j < nslots; ++j) {
-        const uint32_t w = j % nwarps, t = j / nwarps;
-        const uint32_t bar = w * spw + t % spw, use = t / spw;
-        if (use > 0 && !mbar_wait_bounded(&empty[bar], (use - 1) & 1)) {
-          ok = false;
-          break;
-        }
-        const uint32_t row = r0 + j * kGemvRowsPerSlot;
-        const uint32_t rows = min(static_cast<uint32_t>(kGemvRowsPerSlot), r1 - row);
-        mbar_arrive_expect_tx(&full[bar], rows * a.row_bytes);
-        uint8_t *dst = slots + static_cast<size_t>(bar) * slot_bytes;
-        const uint8_t *src = a.vx + static_cast<size_t>(row) * a.bx;
-        if (a.contiguous) {
-          bulk_copy_g2s(dst, src, rows * a.row_bytes, &full[bar]);
-        } else {
-          for (uint32_t r = 0; r < rows; ++r)
-            bulk_copy_g2s(dst + r * a.row_bytes, src + r * a.bx, a.row_bytes, &full[bar]);
-        }
-        issued = j + 1;
-      }
-      if (!ok)
-        atomicOr(&g_device_error, kDevErrBarrierTimeout);
-      // Do not leave while copies of this CTA may still be in flight.
-      const uint32_t ring = nwarps * spw;
-      const uint32_t first = issued > ring ? issued - ring : 0;
-      for (uint32_t j = first; j < issued; ++j) {
-        const uint32_t w = j % nwarps, t = j / nwarps;
-        (void)mbar_wait_bounded(&full[w * spw + t % spw], (t / spw) & 1);
-      }
-    }
-    return;
-  }
-
-  // ---------------- consumers: warp w takes slots w, w + nwarps, ... ----------------
   XBlockPair xr[kXRegPairs > 0 ? kXRegPairs : 1];
   if constexpr (kXRegPairs > 0) {
 #pragma unroll
@@ -266,22 +246,30 @@ __global__ void __launch_bounds__(kGemvMaxThreads, 1) gemv_stream_kernel(const G
     }
   }
 
-  for (uint32_t j = warp, t = 0; j < nslots; j += nwarps, ++t) {
+  for (uint32_t t = 0; t < mine; ++t) {
     const uint32_t bar = warp * spw + t % spw;
     if (!mbar_wait_bounded(&full[bar], (t / spw) & 1)) {
-      if (lane == 0)
+      if (lane == 0) {
         atomicOr(&g_device_error, kDevErrBarrierTimeout);
+        // copies already issued for later slots must land before the CTA's memory goes away
+        for (uint32_t u = t + 1; u < min(mine, t + spw); ++u)
+          (void)mbar_wait_bounded(&full[warp * spw + u % spw], (u / spw) & 1);
+      }
       return;
     }
-    const uint32_t row = r0 + j * kGemvRowsPerSlot;
+    const uint32_t row = r0 + (warp + t * nwarps) * kGemvRowsPerSlot;
     const uint32_t *wrow = reinterpret_cast<const uint32_t *>(slots + static_cast<size_t>(bar) * slot_bytes);
     if (row + 1 < r1)
       gemv_rows<kQ8W, kCols, kXRegPairs, 2>(a, wrow, xsm, xcol_bytes, xr, row, lane);
     else
       gemv_rows<kQ8W, kCols, kXRegPairs, 1>(a, wrow, xsm, xcol_bytes, xr, row, lane);
+    // Every lane has consumed its words of the slot (their values fed the reduction above);
+    // order those reads before the copy engine overwrites the slot, then refill it.
     __syncwarp();
-    if (lane == 0)
-      mbar_arrive(&empty[bar]);
+    if (lane == 0 && t + spw < mine) {
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      issue(t + spw);
+    }
   }
 }
 

@@ -1,0 +1,185 @@
+// The CUDA provider: selects a hand-written sm_100a kernel for a typed tcrv_rvv body by op
+// identity and typed facts, validates the selected lowering boundary fail-closed, realizes
+// pre-realized bodies, and builds the emission plan that names the C-ABI launcher.
+//
+// Behaviour mirrored from the reference's RVV provider: readiness -> plan -> boundary
+// materialisation (lib/Plugin/RVV/RVVExtensionPlugin.cpp:536-712), pre-realized body
+// realization (lib/Plugin/RVV/RVVSelectedBodyRealization.cpp:214-244), and the pinned
+// block-format facts of the quantized ops (lib/Dialect/RVV/IR/RVVDialectWideningOps.cpp:993-1183).
+#include "tcrv/CUDAPlugin.h"
+
+#include <sstream>
+
+namespace tcrv {
+namespace cuda {
+
+const char *const kPluginName = "cuda-plugin";
+const char *const kCapabilityId = "cuda.sm_100a";
+const char *const kCapabilityKind = "accelerator";
+const char *const kProtocolAttr = "cuda_construction_protocol";
+const char *const kProtocolValue = "extension-family-construction-protocol.v1";
+const char *const kRouteId = "cuda-sm100a-typed-body-launch-route-family";
+const char *const kEmissionKind = "prebuilt-sm100a-kernel-c-abi-launch";
+const char *const kArtifactKind = "cuda-sm100a-launch-descriptor";
+const char *const kBoundaryOp = "tcrv_rvv.with_vl";
+const char *const kRuntimeABIKind = "plugin-owned-runtime-abi";
+const char *const kGlueRole = "cuda-c-abi-launch-runtime-glue";
+
+namespace {
+
+using Sig = std::vector<std::pair<std::string, std::string>>;  // (role, c_type) in ABI order
+
+const std::vector<Fact> kQ4Q8Facts = {
+    {"scale_model", false, "dual-fp16-per-block-d_x.d_y", 0}, {"qk", true, "", 32},
+    {"weight_block_stride", true, "", 18},                    {"activation_block_stride", true, "", 34},
+    {"quant_byte_offset", true, "", 2},                       {"activation_high_byte_offset", true, "", 16}};
+
+const std::vector<Fact> kQ8Q8Facts = {{"scale_model", false, "dual-fp16-per-block-d_x.d_y", 0},
+                                      {"qk", true, "", 32},
+                                      {"weight_block_stride", true, "", 34},
+                                      {"activation_block_stride", true, "", 34},
+                                      {"quant_byte_offset", true, "", 2}};
+
+std::vector<Fact> withKind(const char *kind, std::vector<Fact> rest) {
+  rest.insert(rest.begin(), Fact{"kind", false, kind, 0});
+  return rest;
+}
+
+std::vector<RouteEntry> buildTable() {
+  std::vector<RouteEntry> t;
+  const Sig addF32 = {{"lhs-input-buffer", "const float *"},
+                      {"rhs-input-buffer", "const float *"},
+                      {"output-buffer", "float *"},
+                      {"runtime-element-count", "size_t"}};
+  const Sig addI32 = {{"lhs-input-buffer", "const int32_t *"},
+                      {"rhs-input-buffer", "const int32_t *"},
+                      {"output-buffer", "int32_t *"},
+                      {"runtime-element-count", "size_t"}};
+  t.push_back({"tcrv_rvv.binary", withKind("add", {}), "f32", {"tcrv_rvv.load", "tcrv_rvv.load", "tcrv_rvv.binary", "tcrv_rvv.store"},
+               {}, addF32, "add", "cuda-generic-binary-add-f32-callable-c-abi.v1", "tcrv_cuda_add_f32",
+               "tcrv_cuda_host_add_f32", "streaming-elementwise", "hbm", ""});
+  t.push_back({"tcrv_rvv.binary", withKind("add", {}), "i32", {"tcrv_rvv.load", "tcrv_rvv.load", "tcrv_rvv.binary", "tcrv_rvv.store"},
+               {}, addI32, "add", "cuda-generic-binary-add-i32-callable-c-abi.v1", "tcrv_cuda_add_i32",
+               "tcrv_cuda_host_add_i32", "streaming-elementwise", "hbm", ""});
+  t.push_back({"tcrv_rvv.dequantize",
+               withKind("i32_to_f32_scaled", {{"dequant_relation", false, "signed-i32m1-to-f32m1-scale-f32", 0}}), "",
+               {"tcrv_rvv.load", "tcrv_rvv.dequantize", "tcrv_rvv.store"}, {},
+               {{"lhs-input-buffer", "const int32_t *"}, {"dequant-scale-value", "float"}, {"output-buffer", "float *"},
+                {"runtime-element-count", "size_t"}},
+               "dequantize_i32_to_f32", "cuda-generic-dequantize-i32-f32-callable-c-abi.v1",
+               "tcrv_cuda_dequantize_i32_f32", "tcrv_cuda_host_dequantize_i32_f32", "streaming-elementwise", "hbm", ""});
+  t.push_back({"tcrv_rvv.quantize_row_q8_0",
+               withKind("ggml_quantize_row_q8_0", {{"qk", true, "", 32}, {"block_stride", true, "", 34},
+                                                   {"scale_byte_offset", true, "", 0}, {"quant_byte_offset", true, "", 2}}),
+               "", {"tcrv_rvv.quantize_row_q8_0"},
+               {"lhs-input-buffer", "output-buffer", "runtime-element-count"},
+               {{"runtime-element-count", "size_t"}, {"lhs-input-buffer", "const float *"}, {"output-buffer", "uint8_t *"}},
+               "quantize_row_q8_0", "cuda-ggml-quantize-row-q8_0-callable-c-abi.v1", "tcrv_cuda_quantize_row_q8_0",
+               "tcrv_cuda_host_quantize_row_q8_0", "streaming-quantizer", "hbm", ""});
+  t.push_back({"tcrv_rvv.q4_0_q8_0_block_dot", withKind("ggml_q4_0_q8_0_block_dot", kQ4Q8Facts), "",
+               {"tcrv_rvv.q4_0_q8_0_block_dot"},
+               {"lhs-input-buffer", "rhs-input-buffer", "output-buffer", "runtime-element-count"},
+               {{"runtime-element-count", "size_t"}, {"output-buffer", "float *"}, {"output-stride", "size_t"},
+                {"lhs-input-buffer", "const uint8_t *"}, {"lhs-input-stride", "size_t"},
+                {"rhs-input-buffer", "const uint8_t *"}, {"rhs-input-stride", "size_t"},
+                {"rhs-scalar-value", "int32_t"}},
+               "q4_0_q8_0_block_dot", "cuda-ggml-q4_0-q8_0-block-dot-callable-c-abi.v1", "tcrv_cuda_vec_dot_q4_0_q8_0",
+               "tcrv_emitc_ggml_vec_dot_q4_0_q8_0_kernel_ggml_vec_dot_q4_0_q8_0", "block-dot-strict-order", "hbm",
+               "sumf = fma((float)sumi * d_x, d_y, sumf), ascending blocks"});
+  t.push_back({"tcrv_rvv.q8_0_q8_0_block_dot", withKind("ggml_q8_0_q8_0_block_dot", kQ8Q8Facts), "",
+               {"tcrv_rvv.q8_0_q8_0_block_dot"},
+               {"lhs-input-buffer", "rhs-input-buffer", "output-buffer", "runtime-element-count"},
+               {{"runtime-element-count", "size_t"}, {"output-buffer", "float *"},
+                {"lhs-input-buffer", "const uint8_t *"}, {"rhs-input-buffer", "const uint8_t *"}},
+               "q8_0_q8_0_block_dot", "cuda-ggml-q8_0-q8_0-block-dot-callable-c-abi.v1", "tcrv_cuda_vec_dot_q8_0_q8_0",
+               "tcrv_emitc_ggml_vec_dot_q8_0_q8_0_kernel_ggml_vec_dot_q8_0_q8_0", "block-dot-strict-order", "hbm",
+               "sumf = fma((float)sumi, d_x * d_y, sumf), ascending blocks"});
+  t.push_back({"tcrv_rvv.q4_0_q8_0_gemm", withKind("ggml_q4_0_q8_0_gemm", kQ4Q8Facts), "",
+               {"tcrv_rvv.q4_0_q8_0_gemm"},
+               {"lhs-input-buffer", "rhs-input-buffer", "rhs-input-stride", "output-buffer", "runtime-element-count",
+                "source-byte-stride", "destination-byte-stride", "lhs-input-stride", "output-stride"},
+               {{"runtime-element-count", "size_t"}, {"output-buffer", "float *"},
+                {"lhs-input-buffer", "const uint8_t *"}, {"rhs-input-buffer", "const uint8_t *"},
+                {"rhs-input-stride", "size_t"}, {"source-byte-stride", "size_t"},
+                {"destination-byte-stride", "size_t"}, {"lhs-input-stride", "size_t"}, {"output-stride", "size_t"}},
+               "q4_0_q8_0_gemm", "cuda-ggml-q4_0-q8_0-gemm-callable-c-abi.v1",
+               "tcrv_cuda_gemv_q4_0_q8_0|tcrv_cuda_gemm_q4_0_q8_0", "tcrv_cuda_host_gemm_q4_0_q8_0",
+               "decode-gemv-bulk-copy(nc<=8)|prefill-gemm-tcgen05-i8(nc>8)", "hbm|tensor",
+               "gemv: 32 lane partials + butterfly; gemm: ascending blocks per element; fused fold"});
+  return t;
+}
+
+// element type of `!tcrv_rvv.vector<f32, "m1">`
+std::string vectorElementType(const std::string &type) {
+  const std::string key = "!tcrv_rvv.vector<";
+  size_t b = type.find(key);
+  if (b == std::string::npos)
+    return {};
+  size_t e = type.find_first_of(",>", b + key.size());
+  return type.substr(b + key.size(), e - b - key.size());
+}
+
+const Op *boundaryOf(const Op &variant) { return variant.firstChild(kBoundaryOp); }
+
+const Op *computeOpOf(const Op &boundary) {
+  for (const auto &c : boundary.body)
+    if (c->name != "tcrv_rvv.load" && c->name != "tcrv_rvv.store")
+      return c.get();
+  return nullptr;
+}
+
+std::string factMismatch(const Op &op, const RouteEntry &e) {
+  for (const Fact &f : e.facts) {
+    if (f.isInteger) {
+      long long v = 0;
+      if (!op.intAttr(f.key, v))
+        return "missing integer attribute '" + f.key + "'";
+      if (v != f.integer)
+        return "'" + f.key + "' must be " + std::to_string(f.integer) + ", got " + std::to_string(v);
+    } else {
+      const Attr *a = op.attr(f.key);
+      if (!a || a->kind != Attr::String)
+        return "missing string attribute '" + f.key + "'";
+      if (a->str != f.str)
+        return "'" + f.key + "' must be \"" + f.str + "\", got \"" + a->str + "\"";
+    }
+  }
+  return {};
+}
+
+}  // namespace
+
+const std::vector<RouteEntry> &routeTable() {
+  static const std::vector<RouteEntry> table = buildTable();
+  return table;
+}
+
+// Finds the table entry for a compute op; `why` explains a miss.
+const RouteEntry *selectRoute(const Op &computeOp, std::string &why) {
+  std::string lastMismatch;
+  bool sawOp = false;
+  std::string elem;
+  if (!computeOp.resultTypes.empty())
+    elem = vectorElementType(computeOp.resultTypes[0]);
+  for (const RouteEntry &e : routeTable()) {
+    if (e.opName != computeOp.name)
+      continue;
+    sawOp = true;
+    std::string m = factMismatch(computeOp, e);
+    if (!m.empty()) {
+      lastMismatch = m;
+      continue;
+    }
+    if (!e.elementType.empty() && e.elementType != elem) {
+      lastMismatch = "no kernel for element type '" + elem + "'";
+      continue;
+    }
+    return &e;
+  }
+  why = sawOp ? "op " + computeOp.name + ": " + lastMismatch
+              : "the CUDA provider has no kernel for op '" + computeOp.name + "'";
+  return nullptr;
+}
+
+}  // namespace cuda
+}  // namespace tcrv
