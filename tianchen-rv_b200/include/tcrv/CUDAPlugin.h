@@ -1,0 +1,56 @@
+// The CUDA provider's public pieces: its constants, the route table entry type and the
+// factory.  One table entry = one hand-written sm_100a kernel family behind a C-ABI launcher,
+// keyed by typed facts (op mnemonic, pinned attribute values, element type, ABI signature).
+#pragma once
+
+#include <string>
+#include <utility>
+#include <vector>
+
+#include "tcrv/ExtensionPlugin.h"
+
+namespace tcrv {
+namespace cuda {
+
+extern const char *const kPluginName;       // "cuda-plugin"
+extern const char *const kCapabilityId;     // "cuda.sm_100a"
+extern const char *const kCapabilityKind;   // "accelerator"
+extern const char *const kProtocolAttr;     // boundary attribute naming the construction protocol
+extern const char *const kProtocolValue;
+extern const char *const kRouteId;
+extern const char *const kEmissionKind;
+extern const char *const kArtifactKind;
+extern const char *const kBoundaryOp;
+extern const char *const kRuntimeABIKind;
+extern const char *const kGlueRole;
+
+struct Fact {
+  std::string key;
+  bool isInteger;
+  std::string str;
+  long long integer;
+};
+
+struct RouteEntry {
+  std::string opName;                    // typed compute op, e.g. "tcrv_rvv.q4_0_q8_0_gemm"
+  std::vector<Fact> facts;               // attribute values the op must carry
+  std::string elementType;               // vector element type to match ("" = not applicable)
+  std::vector<std::string> bodyOps;      // ops inside the boundary, in order
+  std::vector<std::string> operandRoles; // ABI role of each compute-op operand ("" = not checked)
+  std::vector<std::pair<std::string, std::string>> abi;  // (role, c_type) in declaration order
+  std::string operation;                 // short operation name for the plan
+  std::string runtimeABIName;
+  std::string launcherSymbol;            // device-pointer C-ABI entry point(s)
+  std::string hostSymbol;                // host-pointer twin
+  std::string kernelFamily;
+  std::string rooflineBound;             // "hbm", "tensor" or both
+  std::string foldOrder;                 // fp32 fold convention ("" for non-dot kernels)
+};
+
+const std::vector<RouteEntry> &routeTable();
+const RouteEntry *selectRoute(const Op &computeOp, std::string &why);
+
+std::shared_ptr<const ExtensionPlugin> createCUDAExtensionPlugin();
+
+}  // namespace cuda
+}  // namespace tcrv

@@ -119,15 +119,6 @@ std::string vectorElementType(const std::string &type) {
   return type.substr(b + key.size(), e - b - key.size());
 }
 
-const Op *boundaryOf(const Op &variant) { return variant.firstChild(kBoundaryOp); }
-
-const Op *computeOpOf(const Op &boundary) {
-  for (const auto &c : boundary.body)
-    if (c->name != "tcrv_rvv.load" && c->name != "tcrv_rvv.store")
-      return c.get();
-  return nullptr;
-}
-
 std::string factMismatch(const Op &op, const RouteEntry &e) {
   for (const Fact &f : e.facts) {
     if (f.isInteger) {
