@@ -193,9 +193,6 @@ int tcrv_cuda_block_sums_q8_0_q8_0(size_t n, int32_t *sumi, const uint8_t *vx, c
   return launch_block_sums<true>(n, sumi, vx, vy, by, nr, nc, bx, as_stream(stream));
 }
 
-// Not part of the public header: selects the GEMM epilogue variant for A/B timing.
-void tcrv_cuda_debug_set_gemm_variant(int v) { set_gemm_variant(v); }
-
 size_t tcrv_cuda_gemm_weights_bytes(size_t n, size_t nr) { return gemm_weights_bytes(n, nr); }
 
 size_t tcrv_cuda_gemm_acts_workspace_bytes(size_t n, size_t nc) { return gemm_acts_bytes(n, nc); }

@@ -17,7 +17,6 @@ namespace tcrv {
 namespace {
 
 constexpr size_t kAlign = 256;
-int g_gemm_variant = 1;  // 0: convert in the epilogue, 1: bias pre-loaded in TMEM
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 // ---------------------------------------------------------------- unpack kernels
@@ -185,25 +184,18 @@ int run_gemm(size_t n, float *s, const uint8_t *weights_planar, const uint8_t *a
   int dev = 0;
   TCRV_CUDA_TRY(cudaGetDevice(&dev));
   if (dev < 64 && !configured[dev]) {
-    TCRV_CUDA_TRY(cudaFuncSetAttribute(gemm_q4_0_q8_0_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       static_cast<int>(kGemmSmemBytes)));
-    TCRV_CUDA_TRY(cudaFuncSetAttribute(gemm_q4_0_q8_0_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    TCRV_CUDA_TRY(cudaFuncSetAttribute(gemm_q4_0_q8_0_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(kGemmSmemBytes)));
     configured[dev] = true;
   }
   const int sms = sm_count();
   const int grid = static_cast<int>(args.tiles < static_cast<uint32_t>(sms) ? args.tiles : sms);
-  if (g_gemm_variant == 0)
-    gemm_q4_0_q8_0_tc_kernel<false><<<grid, kGemmThreads, kGemmSmemBytes, stream>>>(map_w, map_x, map_dw, map_dx, args);
-  else
-    gemm_q4_0_q8_0_tc_kernel<true><<<grid, kGemmThreads, kGemmSmemBytes, stream>>>(map_w, map_x, map_dw, map_dx, args);
+  gemm_q4_0_q8_0_tc_kernel<<<grid, kGemmThreads, kGemmSmemBytes, stream>>>(map_w, map_x, map_dw, map_dx, args);
   TCRV_CUDA_TRY(cudaGetLastError());
   return TCRV_CUDA_OK;
 }
 
 }  // namespace
-
-void set_gemm_variant(int v) { g_gemm_variant = v; }
 
 size_t gemm_weights_bytes(size_t n, size_t nr) {
   const PlanarSizes p = planar_sizes(n, nr, 0);

@@ -82,15 +82,6 @@ struct PipeState {
   }
 };
 
-// kBias: the accumulator tiles are pre-loaded with the bit pattern of 12582912.0f (1.5 * 2^23)
-// and the MMA accumulates onto it, so an accumulator word read as a float IS 12582912 + S
-// (|S| <= 32512 keeps it inside the binade whose ulp is 1).  The int->float conversion then
-// folds into the first scale multiply, t = fma(r, d_w, -12582912 * d_w) = round(S * d_w),
-// which is exact arithmetic followed by one rounding, i.e. bit-identical to (float)S * d_w.
-constexpr uint32_t kMagicBits = 0x4B400000u;
-constexpr float kMagic = 12582912.0f;
-
-template <bool kBias>
 __global__ void __launch_bounds__(kGemmThreads, 1)
     gemm_q4_0_q8_0_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                              const __grid_constant__ CUtensorMap map_dw, const __grid_constant__ CUtensorMap map_dx,
@@ -189,14 +180,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           const uint32_t b_addr = a_addr + kGemmABytes;
           const uint32_t steps = min(static_cast<uint32_t>(kGemmStageBlocks), a.nb - kb * kGemmStageBlocks);
           for (uint32_t kk = 0; kk < steps; ++kk) {
-            // with kBias the epilogue warps hand over every tile (also the first round) after
-            // writing the bias into it; without it the first round starts on untouched tiles
-            ok = mbar_wait_bounded(&tmem_empty[ts.stage], kBias ? ts.phase : ts.phase ^ 1, abort_flag);
+            ok = mbar_wait_bounded(&tmem_empty[ts.stage], ts.phase ^ 1, abort_flag);
             if (!ok)
               break;
             tcgen05_fence_after_thread_sync();
             umma_s8_ss(tmem_base + ts.stage * kGemmTileCols, umma_desc_k_major_sw128(a_addr + kk * kQK),
-                       umma_desc_k_major_sw128(b_addr + kk * kQK), idesc, kBias ? 1u : 0u);
+                       umma_desc_k_major_sw128(b_addr + kk * kQK), idesc, 0u);
             umma_commit(&tmem_full[ts.stage]);
             ts.advance(kGemmTmemStages);
           }
@@ -220,27 +209,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     const uint32_t lane_field = static_cast<uint32_t>(quarter * 32) << 16;
     PipeState ps, ts;
     bool ok = true;
-    uint32_t bias[16];
-#pragma unroll
-    for (int j = 0; j < 16; ++j)
-      bias[j] = kMagicBits;
-    // writes the bias into this warp's 32 lanes x 64 columns of one accumulator tile
-    auto store_bias = [&](uint32_t stage) {
-      const uint32_t taddr = tmem_base + lane_field + stage * kGemmTileCols + half * 64;
-#pragma unroll
-      for (int c = 0; c < 4; ++c)
-        tmem_st_32x32b_x16(taddr + 16 * c, bias);
-      tmem_st_wait();
-    };
-    if constexpr (kBias) {
-      for (uint32_t st = 0; st < kGemmTmemStages; ++st) {
-        store_bias(st);
-        tcgen05_fence_before_thread_sync();
-        __syncwarp();
-        if (lane == 0)
-          mbar_arrive(&tmem_empty[st]);
-      }
-    }
     for (uint32_t t = blockIdx.x; t < a.tiles && ok; t += gridDim.x) {
       const uint32_t n0 = (t / a.tiles_m) * kGemmTileRows;
       const uint32_t m0 = (t % a.tiles_m) * kGemmTileCols + half * 64;
@@ -268,37 +236,36 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
               tmem_ld_32x32b_x32(taddr, v0);
               tmem_ld_32x32b_x32(taddr + 32, v1);
               tmem_ld_wait();
-              if constexpr (kBias)
-                store_bias(ts.stage);
               tcgen05_fence_before_thread_sync();
               __syncwarp();
               if (lane == 0)
                 mbar_arrive(&tmem_empty[ts.stage]);
               ts.advance(kGemmTmemStages);
               const uint64_t dw2 = pack_f32x2(dws[kk], dws[kk]);
-              const float cneg = __fmul_rn(-kMagic, dws[kk]);  // exact: 2-bit x 11-bit significands
-              const uint64_t c2 = pack_f32x2(cneg, cneg);
               const ulonglong2 *dx2 = reinterpret_cast<const ulonglong2 *>(dx_base + kk * kGemmTileCols * 4);
-              // (float)S * d_w for two adjacent columns
-              auto scaled = [&](uint32_t lo, uint32_t hi) -> uint64_t {
-                if constexpr (kBias) {
-                  return fma_f32x2(pack_f32x2(__uint_as_float(lo), __uint_as_float(hi)), dw2, c2);
-                } else {
-                  return mul_f32x2(
-                      pack_f32x2(__int2float_rn(static_cast<int>(lo)), __int2float_rn(static_cast<int>(hi))), dw2);
-                }
-              };
 #pragma unroll
               for (int j = 0; j < 8; ++j) {
                 const ulonglong2 d = dx2[j];
-                acc[2 * j] = fma_f32x2(scaled(v0[4 * j], v0[4 * j + 1]), d.x, acc[2 * j]);
-                acc[2 * j + 1] = fma_f32x2(scaled(v0[4 * j + 2], v0[4 * j + 3]), d.y, acc[2 * j + 1]);
+                const uint64_t t0 = mul_f32x2(
+                    pack_f32x2(__int2float_rn(static_cast<int>(v0[4 * j])), __int2float_rn(static_cast<int>(v0[4 * j + 1]))),
+                    dw2);
+                const uint64_t t1 = mul_f32x2(pack_f32x2(__int2float_rn(static_cast<int>(v0[4 * j + 2])),
+                                                         __int2float_rn(static_cast<int>(v0[4 * j + 3]))),
+                                              dw2);
+                acc[2 * j] = fma_f32x2(t0, d.x, acc[2 * j]);
+                acc[2 * j + 1] = fma_f32x2(t1, d.y, acc[2 * j + 1]);
               }
 #pragma unroll
               for (int j = 0; j < 8; ++j) {
                 const ulonglong2 d = dx2[8 + j];
-                acc[16 + 2 * j] = fma_f32x2(scaled(v1[4 * j], v1[4 * j + 1]), d.x, acc[16 + 2 * j]);
-                acc[16 + 2 * j + 1] = fma_f32x2(scaled(v1[4 * j + 2], v1[4 * j + 3]), d.y, acc[16 + 2 * j + 1]);
+                const uint64_t t0 = mul_f32x2(
+                    pack_f32x2(__int2float_rn(static_cast<int>(v1[4 * j])), __int2float_rn(static_cast<int>(v1[4 * j + 1]))),
+                    dw2);
+                const uint64_t t1 = mul_f32x2(pack_f32x2(__int2float_rn(static_cast<int>(v1[4 * j + 2])),
+                                                         __int2float_rn(static_cast<int>(v1[4 * j + 3]))),
+                                              dw2);
+                acc[16 + 2 * j] = fma_f32x2(t0, d.x, acc[16 + 2 * j]);
+                acc[16 + 2 * j + 1] = fma_f32x2(t1, d.y, acc[16 + 2 * j + 1]);
               }
             }
           }

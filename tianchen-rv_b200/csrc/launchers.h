@@ -27,7 +27,6 @@ int launch_block_sums(size_t n, int32_t *sumi, const uint8_t *vx, const uint8_t 
 namespace tcrv {
 // Prefill GEMM: planar-layout sizes, the two prepare steps and the tensor-core launch.
 size_t gemm_weights_bytes(size_t n, size_t nr);
-void set_gemm_variant(int v);  // epilogue variant, for A/B timing
 size_t gemm_acts_bytes(size_t n, size_t nc);
 int launch_gemm_prepare_weights_q4_0(size_t n, const uint8_t *vx, size_t bx, size_t nr, uint8_t *prepared,
                                      cudaStream_t stream);
