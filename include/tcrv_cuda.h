@@ -146,6 +146,30 @@ int tcrv_cuda_gemm_q4_0_q8_0_prepared(size_t n, float *s, const void *prepared_w
                                       size_t by, size_t nr, size_t nc, size_t bs, void *workspace,
                                       size_t workspace_bytes, unsigned flags, tcrv_cuda_stream stream);
 
+/* The plain-format GEMM for callers that cannot allocate device memory.  No counterpart in
+ * the reference (its kernels take every buffer from the caller and need no scratch).
+ *
+ * Some hosts hand the whole GPU to their own allocator at start-up, or run under a fixed
+ * memory budget that is carved up before any kernel runs; a cudaMalloc from inside a
+ * library call then either fails or stalls the device, and such callers have nowhere to take
+ * a workspace from either.  For them the planar operand copies this GEMM needs live in a
+ * fixed array inside the library (TCRV_CUDA_STATIC_SCRATCH_BYTES, held by every GPU that
+ * loads the library until the process exits).  Inputs and the output are still the
+ * caller's.  The call performs no allocation of any kind.
+ *
+ * Limit: tcrv_cuda_gemm_workspace_bytes(n, nr, nc) must not exceed
+ * TCRV_CUDA_STATIC_SCRATCH_BYTES, otherwise TCRV_CUDA_ERR_WORKSPACE is returned and nothing
+ * runs (e.g. 4096 x 4096 weights with 512 columns fit; 11008 x 4096 do not).
+ * The first call on a device looks up the array's device address; make that call before
+ * starting any stream capture.  All calls share the one array and each call overwrites what
+ * the previous one left there (everything a call reads is written by that call first), so
+ * two calls whose kernels may overlap on the GPU -- different streams, or different host
+ * threads -- race; serialise them. */
+#define TCRV_CUDA_STATIC_SCRATCH_BYTES (32u << 20)
+int tcrv_cuda_gemm_q4_0_q8_0_static_scratch(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by,
+                                            size_t nr, size_t nc, size_t bx, size_t bs, unsigned flags,
+                                            tcrv_cuda_stream stream);
+
 /* Debug variant of the integer stage: sumi[(ir*nc + col)*(n/32) + ib], bit-exact int32. */
 int tcrv_cuda_block_sums_q4_0_q8_0(size_t n, int32_t *sumi, const uint8_t *vx, const uint8_t *vy,
                                    size_t by, size_t nr, size_t nc, size_t bx, tcrv_cuda_stream stream);

@@ -18,6 +18,7 @@ Q4_0_BLOCK = 18
 Q8_0_BLOCK = 34
 FLAG_NONE = 0
 FLAG_STRICT_ORDER = 1
+STATIC_SCRATCH_BYTES = 32 << 20
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libtcrv_cuda.so")
@@ -49,6 +50,7 @@ ABI = {
     "tcrv_cuda_gemm_prepare_weights_q4_0": [_sz, _p, _sz, _sz, _p, _sz, _p],
     "tcrv_cuda_gemm_q4_0_q8_0": [_sz, _p, _p, _p, _sz, _sz, _sz, _sz, _sz, _p, _sz, ctypes.c_uint, _p],
     "tcrv_cuda_gemm_q4_0_q8_0_prepared": [_sz, _p, _p, _p, _sz, _sz, _sz, _sz, _p, _sz, ctypes.c_uint, _p],
+    "tcrv_cuda_gemm_q4_0_q8_0_static_scratch": [_sz, _p, _p, _p, _sz, _sz, _sz, _sz, _sz, ctypes.c_uint, _p],
     "tcrv_cuda_block_sums_q4_0_q8_0": [_sz, _p, _p, _p, _sz, _sz, _sz, _sz, _p],
     "tcrv_cuda_block_sums_q8_0_q8_0": [_sz, _p, _p, _p, _sz, _sz, _sz, _sz, _p],
 }

@@ -258,4 +258,19 @@ int tcrv_cuda_gemm_q4_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_
                                            stream);
 }
 
+int tcrv_cuda_gemm_q4_0_q8_0_static_scratch(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by,
+                                            size_t nr, size_t nc, size_t bx, size_t bs, unsigned flags,
+                                            tcrv_cuda_stream stream) {
+  (void)flags;
+  const int st = check_matrix_args(n, s, vx, vy, by, nr, nc, bx, bs, TCRV_Q4_0_BLOCK_BYTES);
+  if (st != TCRV_CUDA_OK)
+    return st;
+  if (n == 0) {
+    for (size_t r = 0; r < nr; ++r)
+      TCRV_CUDA_TRY(cudaMemsetAsync(s + r * bs, 0, nc * sizeof(float), as_stream(stream)));
+    return TCRV_CUDA_OK;
+  }
+  return launch_gemm_static_scratch(n, s, vx, bx, vy, by, nr, nc, bs, as_stream(stream));
+}
+
 }  // extern "C"

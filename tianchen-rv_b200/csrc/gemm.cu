@@ -249,4 +249,40 @@ int launch_gemm_prepared(size_t n, float *s, const uint8_t *weights_planar, cons
   return run_gemm(n, s, weights_planar, acts_planar, nr, nc, bs, stream);
 }
 
+// ------------------------------------------------------------ allocation-free variant
+//
+// Scratch for callers that must not allocate device memory: the planar operand copies live
+// in this fixed array instead of a caller-provided workspace.  The array is part of the
+// library image, so every GPU that loads the library sets aside kStaticScratchBytes for it
+// until the process exits.  In host code the array's name only stands for the symbol; the
+// device address has to be asked for (once per device, with that device current).
+constexpr size_t kStaticScratchBytes = TCRV_CUDA_STATIC_SCRATCH_BYTES;
+static __device__ __align__(256) uint8_t g_static_scratch[kStaticScratchBytes];
+
+int launch_gemm_static_scratch(size_t n, float *s, const uint8_t *vx, size_t bx, const uint8_t *vy, size_t by,
+                               size_t nr, size_t nc, size_t bs, cudaStream_t stream) {
+  if (nr == 0 || nc == 0 || n == 0)
+    return TCRV_CUDA_OK;
+  const size_t wbytes = gemm_weights_bytes(n, nr), abytes = gemm_acts_bytes(n, nc);
+  if (wbytes + abytes > kStaticScratchBytes)
+    return TCRV_CUDA_ERR_WORKSPACE;
+  static uint8_t *base[64] = {};
+  int dev = 0;
+  TCRV_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64)
+    return TCRV_CUDA_ERR_UNSUPPORTED;
+  if (base[dev] == nullptr) {
+    void *addr = nullptr;
+    TCRV_CUDA_TRY(cudaGetSymbolAddress(&addr, g_static_scratch));
+    base[dev] = static_cast<uint8_t *>(addr);
+  }
+  uint8_t *weights = base[dev], *acts = base[dev] + wbytes;
+  int st = launch_gemm_prepare_weights_q4_0(n, vx, bx, nr, weights, stream);
+  if (st == TCRV_CUDA_OK)
+    st = launch_gemm_prepare_acts_q8_0(n, vy, by, nc, acts, stream);
+  if (st == TCRV_CUDA_OK)
+    st = run_gemm(n, s, weights, acts, nr, nc, bs, stream);
+  return st;
+}
+
 }  // namespace tcrv

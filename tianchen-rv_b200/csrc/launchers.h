@@ -32,6 +32,8 @@ int launch_gemm_prepare_weights_q4_0(size_t n, const uint8_t *vx, size_t bx, siz
                                      cudaStream_t stream);
 int launch_gemm_prepare_acts_q8_0(size_t n, const uint8_t *vy, size_t by, size_t nc, uint8_t *prepared,
                                   cudaStream_t stream);
+int launch_gemm_static_scratch(size_t n, float *s, const uint8_t *vx, size_t bx, const uint8_t *vy, size_t by,
+                               size_t nr, size_t nc, size_t bs, cudaStream_t stream);
 int launch_gemm_prepared(size_t n, float *s, const uint8_t *weights_planar, const uint8_t *acts_planar, size_t nr,
                          size_t nc, size_t bs, cudaStream_t stream);
 }  // namespace tcrv
