@@ -222,7 +222,7 @@ def run_ours(args):
     t_warm = time.perf_counter()
     warm_mark = len(sampler.lines)
     i = 0
-    while i < args.warmup or time.perf_counter() - t_warm < MIN_WARM_SECONDS:
+    while i < args.warmup or time.perf_counter() - t_warm < args.min_warm_seconds:
         step(i)
         i += 1
         if i % 64 == 0:
@@ -268,7 +268,7 @@ def run_ours(args):
 
     e2e = measure_e2e(pkg, torch, layers, max(10, min(args.steps, 50)), dist)
     try:
-        gemm = measure_gemm(pkg, torch, dist, rank, world)
+        gemm = None if args.skip_gemm else measure_gemm(pkg, torch, dist, rank, world)
     except Exception as exc:  # the headline line must still be printed
         gemm = {"error": f"{type(exc).__name__}: {exc}"}
 
@@ -381,12 +381,12 @@ def measure_gemm(pkg, torch, dist, rank, world):
     results = []
     for nr, k in GEMM_SHAPES:
         ops = 2.0 * GEMM_TOKENS * nr * k
-        rows = nr // world
+        first_row, rows = pkg.row_shard(nr, world, rank)
         wq = pkg.quantize_q4_0(torch.randn((rows, k), generator=gen, device="cuda") * 0.02)
         x = pkg.quantize_q8_0(torch.randn((GEMM_TOKENS, k), generator=gen, device="cuda"))
         pw = pkg.PreparedWeights(wq)
         full = torch.empty((nr, GEMM_TOKENS), dtype=torch.float32, device="cuda")
-        slab = full[rank * rows:(rank + 1) * rows]
+        slab = full[first_row:first_row + rows]
         ws = torch.empty(pkg.lib().tcrv_cuda_gemm_acts_workspace_bytes(k, GEMM_TOKENS), dtype=torch.uint8, device="cuda")
         ws_plain = torch.empty(pkg.lib().tcrv_cuda_gemm_workspace_bytes(k, rows, GEMM_TOKENS), dtype=torch.uint8,
                                device="cuda")
@@ -418,7 +418,7 @@ def measure_gemm(pkg, torch, dist, rank, world):
 
         def with_gather():
             pkg.gemm(pw, x, out=slab, workspace=ws)
-            dist.all_gather_into_tensor(full, slab)
+            pkg.gather_row_slabs(full, dist, rank, world)
 
         ms_c = timed(compute)
         ms_p = timed(compute_plain)
@@ -444,6 +444,9 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--min-warm-seconds", type=float, default=MIN_WARM_SECONDS,
+                    help="warm-up lasts at least this long (0 for a profiler's launch-list pass)")
+    ap.add_argument("--skip-gemm", action="store_true", help="leave out the prefill-GEMM section")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

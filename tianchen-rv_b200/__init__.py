@@ -330,3 +330,28 @@ def gemm(w, x, out=None, workspace=None):
                                           out.stride(0), workspace.data_ptr(), workspace.numel(), 0, _stream()),
            "tcrv_cuda_gemm_q4_0_q8_0")
     return out
+
+
+# ------------------------------------------------------------------ N-sharding (multi-GPU GEMM)
+
+
+def row_shard(nr: int, world: int, rank: int):
+    """Contiguous, equal shard of the weight rows for `rank`: (first_row, rows).
+
+    The GEMM output is N-major (one row of `nc` floats per weight row), so a row shard is a
+    contiguous slab of the output and equal shards map straight onto one all-gather.  `nr`
+    must divide evenly (11008 and 32000 do for 2, 4 and 8 ranks)."""
+    if world < 1 or not 0 <= rank < world:
+        raise ValueError("bad rank/world")
+    if nr % world != 0:
+        raise ValueError(f"{nr} weight rows do not split evenly over {world} ranks")
+    rows = nr // world
+    return rank * rows, rows
+
+
+def gather_row_slabs(full, dist, rank: int, world: int):
+    """All-gathers the per-rank output slabs in place: rank r has written rows
+    row_shard(nr, world, r) of `full` (shape (nr, nc)); afterwards every rank holds all rows."""
+    first, rows = row_shard(full.shape[0], world, rank)
+    dist.all_gather_into_tensor(full, full[first:first + rows])
+    return full
