@@ -143,3 +143,16 @@ def test_q8_0_gemv_config(cuda, pkg, O):
     check_rows(O, got[rows], w[rows], x, True)
     sums = pkg.block_sums(wd[:64], xd, q8_weights=True).cpu().numpy()
     assert np.array_equal(sums, O.block_sums(w[:64], x, True))
+
+
+@pytest.mark.parametrize("forced", [1, 2, 4])
+@pytest.mark.parametrize("q8w", [False, True])
+def test_rows_per_slot_choices_give_identical_rows(cuda, pkg, O, forced, q8w):
+    # the launcher picks 1, 2 or 4 rows per slot from the problem size; bits 8..11 of `flags`
+    # force a choice.  The per-row fp32 order does not depend on it, and ragged row counts
+    # exercise the 3-, 2- and 1-row tails of a 4-row slot.
+    for nr in (1003, 149, 7):
+        w, x = make(O, nr, 2048, 1, q8w, 900 + nr)
+        got = pkg.gemv(dev(cuda, w), dev(cuda, x), q8_weights=q8w, flags=forced << 8).cpu().numpy()
+        pkg.check_device_errors()
+        assert np.array_equal(got.view(np.uint32), O.gemv_lane_order(w, x, q8w).view(np.uint32))

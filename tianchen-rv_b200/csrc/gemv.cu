@@ -177,7 +177,18 @@ int launch_gemv(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t
   if (!strict && nb > 0 && nb % 8 == 0 && nc <= kGemvMaxCols && multiple_of(vx, 16) && bx % 16 == 0 &&
       multiple_of(vy, 2) && by % 2 == 0) {
     const size_t fixed = kGemvBarrierBytes + nc * static_cast<size_t>(gemv_xcol_bytes(nb));
-    const size_t slot = kGemvRowsPerSlot * row_bytes;
+    // Rows per slot: more rows per warp step give more independent work per warp (the
+    // kernel is issue/latency-bound), fewer rows give finer balance when a CTA only gets a
+    // few dozen rows.  flags bits 8..11 override the choice (tuning).
+    const int sms = sm_count();
+    const size_t rows_per_cta = (nr + sms - 1) / sms;
+    size_t rps = nc == 1 ? (rows_per_cta >= 160 ? 4 : rows_per_cta >= 48 ? 2 : 1) : (rows_per_cta >= 48 ? 2 : 1);
+    const unsigned forced = (flags >> 8) & 0xfu;
+    if (forced == 1 || forced == 2 || (forced == 4 && nc == 1))
+      rps = forced;
+    while (rps > 1 && fixed + 2 * rps * row_bytes > kMaxDynamicSmem)
+      rps /= 2;
+    const size_t slot = rps * row_bytes;
     if (fixed + 2 * slot <= kMaxDynamicSmem) {
       const size_t total_slots = (kMaxDynamicSmem - fixed) / slot;
       size_t nwarps, spw;
@@ -203,9 +214,9 @@ int launch_gemv(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t
       args.nwarps = static_cast<uint32_t>(nwarps);
       args.slots = static_cast<uint32_t>(spw);
       args.contiguous = (bx == row_bytes) ? 1u : 0u;
-      const size_t pairs = (nr + kGemvRowsPerSlot - 1) / kGemvRowsPerSlot;
-      const int sms = sm_count();
-      const int grid = static_cast<int>(pairs < static_cast<size_t>(sms) ? pairs : sms);
+      args.rps = static_cast<uint32_t>(rps);
+      const size_t nslots = (nr + rps - 1) / rps;
+      const int grid = static_cast<int>(nslots < static_cast<size_t>(sms) ? nslots : sms);
       return launch_stream<kQ8W>(args, static_cast<uint32_t>(nc), grid, fixed + nwarps * spw * slot, stream);
     }
   }

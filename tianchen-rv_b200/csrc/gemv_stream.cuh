@@ -2,8 +2,8 @@
 // for up to 8 activation columns.  HBM-bound: the weight matrix is read exactly once.
 //
 // One persistent CTA per SM owns a contiguous range of weight rows, taken two rows at a
-// time.  Up to 16 warps each own a private ring of shared-memory slots (one slot = two
-// adjacent rows) and keep it full themselves: lane 0 issues a 1-D bulk copy
+// time.  Up to 16 warps each own a private ring of shared-memory slots (one slot = 1, 2 or 4
+// adjacent rows, chosen by the launcher from the rows each CTA gets) and keep it full themselves: lane 0 issues a 1-D bulk copy
 // (cp.async.bulk, completion counted on the slot's mbarrier) for the slot it has just
 // finished, so copy issue is spread over all warps and no warp waits for another.  Each warp
 // works on both rows of a slot at once; about 32 rows are in flight per SM, below that the
@@ -32,7 +32,7 @@ namespace tcrv {
 constexpr int kGemvMaxConsumerWarps = 16;
 constexpr int kGemvMaxSlotsPerWarp = 8;
 constexpr int kGemvMaxThreads = kGemvMaxConsumerWarps * 32;
-constexpr int kGemvRowsPerSlot = 2;
+constexpr int kGemvMaxRowsPerSlot = 4;
 constexpr int kGemvBarrierBytes = kGemvMaxConsumerWarps * kGemvMaxSlotsPerWarp * 8;  // one "full" barrier per slot
 constexpr int kGemvMaxCols = 8;
 
@@ -46,7 +46,8 @@ struct GemvArgs {
   uint32_t row_bytes;  // nb * block bytes
   uint32_t nwarps;     // warps per CTA
   uint32_t slots;      // slots per consumer warp
-  uint32_t contiguous; // bx == row_bytes: both rows of a slot arrive in one copy
+  uint32_t contiguous; // bx == row_bytes: all rows of a slot arrive in one copy
+  uint32_t rps;        // rows per slot: 1, 2 or 4 (single column), 1 or 2 otherwise
 };
 
 template <bool kQ8W>
@@ -180,7 +181,8 @@ __global__ void __launch_bounds__(kGemvMaxThreads, 1) gemv_stream_kernel(const G
   const uint32_t nb = a.nb, npairs = nb / 2;
   const uint32_t xcol_bytes = gemv_xcol_bytes(nb);
   uint8_t *slots = xsm + static_cast<size_t>(kCols) * xcol_bytes;
-  const uint32_t slot_bytes = kGemvRowsPerSlot * a.row_bytes;
+  const uint32_t rps = a.rps;
+  const uint32_t slot_bytes = rps * a.row_bytes;
   const uint32_t nwarps = a.nwarps, spw = a.slots;
   const uint32_t nthreads = nwarps * 32;
 
@@ -190,14 +192,14 @@ __global__ void __launch_bounds__(kGemvMaxThreads, 1) gemv_stream_kernel(const G
   // warp w takes slots w, w + nwarps, ...
   const uint32_t r0 = static_cast<uint32_t>(static_cast<uint64_t>(a.nr) * blockIdx.x / gridDim.x);
   const uint32_t r1 = static_cast<uint32_t>(static_cast<uint64_t>(a.nr) * (blockIdx.x + 1) / gridDim.x);
-  const uint32_t nslots = (r1 - r0 + kGemvRowsPerSlot - 1) / kGemvRowsPerSlot;
+  const uint32_t nslots = (r1 - r0 + rps - 1) / rps;
   const uint32_t mine = warp < nslots ? (nslots - warp + nwarps - 1) / nwarps : 0;  // slots of this warp
 
   // Issues the copy of this warp's t-th slot into ring position t % spw (one lane calls it).
   auto issue = [&](uint32_t t) {
     const uint32_t bar = warp * spw + t % spw;
-    const uint32_t row = r0 + (warp + t * nwarps) * kGemvRowsPerSlot;
-    const uint32_t rows = min(static_cast<uint32_t>(kGemvRowsPerSlot), r1 - row);
+    const uint32_t row = r0 + (warp + t * nwarps) * rps;
+    const uint32_t rows = min(rps, r1 - row);
     mbar_arrive_expect_tx(&full[bar], rows * a.row_bytes);
     uint8_t *dst = slots + static_cast<size_t>(bar) * slot_bytes;
     const uint8_t *src = a.vx + static_cast<size_t>(row) * a.bx;
@@ -257,12 +259,21 @@ __global__ void __launch_bounds__(kGemvMaxThreads, 1) gemv_stream_kernel(const G
       }
       return;
     }
-    const uint32_t row = r0 + (warp + t * nwarps) * kGemvRowsPerSlot;
+    const uint32_t row = r0 + (warp + t * nwarps) * rps;
     const uint32_t *wrow = reinterpret_cast<const uint32_t *>(slots + static_cast<size_t>(bar) * slot_bytes);
-    if (row + 1 < r1)
+    const uint32_t rows = min(rps, r1 - row);
+    // all rows of the slot are folded together (independent accumulators hide latency)
+    if (rows == 4) {
+      if constexpr (kCols == 1)
+        gemv_rows<kQ8W, kCols, kXRegPairs, 4>(a, wrow, xsm, xcol_bytes, xr, row, lane);
+    } else if (rows == 3) {
+      if constexpr (kCols == 1)
+        gemv_rows<kQ8W, kCols, kXRegPairs, 3>(a, wrow, xsm, xcol_bytes, xr, row, lane);
+    } else if (rows == 2) {
       gemv_rows<kQ8W, kCols, kXRegPairs, 2>(a, wrow, xsm, xcol_bytes, xr, row, lane);
-    else
+    } else {
       gemv_rows<kQ8W, kCols, kXRegPairs, 1>(a, wrow, xsm, xcol_bytes, xr, row, lane);
+    }
     // Every lane has consumed its words of the slot (their values fed the reduction above);
     // order those reads before the copy engine overwrites the slot, then refill it.
     __syncwarp();
