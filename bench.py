@@ -34,6 +34,13 @@ ROTATION_SETS = 8       # distinct copies of every weight matrix; 8 x 134 MB, fa
 MIN_WARM_SECONDS = 1.5  # warm-up runs at least this long so that the clock sampler sees load
 
 
+# DRAM traffic per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures
+# summarised under profiles/: measured for two shapes, the other two scaled from the larger
+# one by their weight bytes (traffic grows in proportion to the rows streamed).
+NCU_TRAFFIC = {"32000x4096": 74_444_288, "4096x4096": 9_463_040}
+NCU_TRAFFIC_RATIO = 74_444_288 / 73_860_352  # traffic / algorithmic bytes of the measured launch
+
+
 def gemv_bytes(nr: int, k: int, batch: int) -> int:
     nb = k // 32
     return nr * nb * 18 + batch * nb * 34 + 4 * batch * nr
@@ -284,6 +291,7 @@ def run_ours(args):
         cpu = {"value": round(gbs, 3), "unit": UNIT, "cores": threads, "kind": "port", "sample": desc}
 
     peaks, peak_kind = measured_peaks()
+    step_traffic = sum(NCU_TRAFFIC.get(f"{l['nr']}x{l['k']}", l["bytes"] * NCU_TRAFFIC_RATIO) for l in layers)
     value = step_bytes * args.steps * world / (elapsed_ms * 1e-3) / 1e9
     per_gpu = value / world
     big = per_shape[-1]
@@ -297,7 +305,11 @@ def run_ours(args):
                    "launch": "one CUDA graph (4 GEMV kernels) per step",
                    "parallelism": "replicas only" if world > 1 else "single GPU"},
         "roofline": {"bound": "hbm", "achieved": round(per_gpu, 2), "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                     "frac": round(per_gpu / peaks["hbm_gbs"], 4), "traffic": None, "peak_kind": f"of {peak_kind}",
+                     "frac": round(per_gpu / peaks["hbm_gbs"], 4), "traffic": round(step_traffic / launches_per_step),
+                     "algorithmic_bytes_per_launch": round(step_bytes / launches_per_step),
+                     "traffic_source": "ncu dram bytes per launch, averaged over the step's 4 launches "
+                                       "(profiles/gemv_stream_q4_0_b1_32000x4096.md)",
+                     "peak_kind": f"of {peak_kind}",
                      "kernel": "gemv_stream_kernel<q4_0, 1 column>", "largest_shape": big},
         "e2e": e2e,
         "cpu_baseline": cpu,
