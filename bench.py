@@ -200,7 +200,7 @@ def run_ours(args):
 
     def launch_set(r: int):
         for l in layers:
-            pkg.gemv(l["w"][r], l["x"], out=l["y"])
+            pkg.gemv(l["w"][r], l["x"], out=l["y"], flags=pkg.FLAG_STATIC_WEIGHTS)
 
     # One CUDA graph per rotation set: a step is one graph launch (4 GEMV kernels), so the
     # host's per-call cost does not sit between the kernels.
@@ -259,7 +259,7 @@ def run_ours(args):
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g, stream=side):
             for r in range(ROTATION_SETS):
-                pkg.gemv(l["w"][r], l["x"], out=l["y"])
+                pkg.gemv(l["w"][r], l["x"], out=l["y"], flags=pkg.FLAG_STATIC_WEIGHTS)
         reps = max(5, args.steps // ROTATION_SETS)
         for _ in range(2):
             g.replay()

@@ -43,6 +43,10 @@ typedef enum {
 /* fold every row's blocks in strict ascending order (bit-identical to the sequential
  * scalar kernel with the fused fold); slower, meant for verification */
 #define TCRV_CUDA_FLAG_STRICT_ORDER 1u
+/* the weight buffer was not written by the work that immediately precedes this call on the
+ * stream (model weights are static): the decode GEMV may then start streaming weights while
+ * the preceding kernel is still draining; activations and outputs are always ordered */
+#define TCRV_CUDA_FLAG_STATIC_WEIGHTS 2u
 
 const char *tcrv_cuda_status_string(int status);
 /* Text of the last CUDA runtime error seen by the calling thread ("" if none). */

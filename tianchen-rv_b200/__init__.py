@@ -18,6 +18,7 @@ Q4_0_BLOCK = 18
 Q8_0_BLOCK = 34
 FLAG_NONE = 0
 FLAG_STRICT_ORDER = 1
+FLAG_STATIC_WEIGHTS = 2
 STATIC_SCRATCH_BYTES = 32 << 20
 
 _HERE = os.path.dirname(os.path.abspath(__file__))

@@ -128,7 +128,19 @@ int launch_stream_instance(const GemvArgs &args, int grid, size_t smem, cudaStre
                                        static_cast<int>(kMaxDynamicSmem)));
     configured[dev] = true;
   }
-  kernel<<<grid, args.nwarps * 32, smem, stream>>>(args);
+  // Launched with programmatic stream serialization so that its prologue can overlap the
+  // tail of the preceding kernel (the kernel itself waits before touching dependent data).
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(args.nwarps * 32);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  TCRV_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, args));
   TCRV_CUDA_TRY(cudaGetLastError());
   return TCRV_CUDA_OK;
 }
@@ -177,12 +189,12 @@ int launch_gemv(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t
   if (!strict && nb > 0 && nb % 8 == 0 && nc <= kGemvMaxCols && multiple_of(vx, 16) && bx % 16 == 0 &&
       multiple_of(vy, 2) && by % 2 == 0) {
     const size_t fixed = kGemvBarrierBytes + nc * static_cast<size_t>(gemv_xcol_bytes(nb));
-    // Rows per slot: more rows per warp step give more independent work per warp (the
-    // kernel is issue/latency-bound), fewer rows give finer balance when a CTA only gets a
-    // few dozen rows.  flags bits 8..11 override the choice (tuning).
+    // Rows per slot: a warp folds all rows of a slot together, and more independent rows per
+    // warp hide more latency (the kernel is issue/latency-bound); measured best is 4 rows for
+    // rows up to 4 KB and 2 rows beyond (registers), 2 rows with several activation columns.
+    // flags bits 8..11 override the choice (tuning).
     const int sms = sm_count();
-    const size_t rows_per_cta = (nr + sms - 1) / sms;
-    size_t rps = nc == 1 ? (rows_per_cta >= 160 ? 4 : rows_per_cta >= 48 ? 2 : 1) : (rows_per_cta >= 48 ? 2 : 1);
+    size_t rps = nc == 1 ? (row_bytes <= 4096 ? 4 : 2) : 2;
     const unsigned forced = (flags >> 8) & 0xfu;
     if (forced == 1 || forced == 2 || (forced == 4 && nc == 1))
       rps = forced;
@@ -215,6 +227,7 @@ int launch_gemv(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t
       args.slots = static_cast<uint32_t>(spw);
       args.contiguous = (bx == row_bytes) ? 1u : 0u;
       args.rps = static_cast<uint32_t>(rps);
+      args.static_weights = (flags & TCRV_CUDA_FLAG_STATIC_WEIGHTS) ? 1u : 0u;
       const size_t nslots = (nr + rps - 1) / rps;
       const int grid = static_cast<int>(nslots < static_cast<size_t>(sms) ? nslots : sms);
       return launch_stream<kQ8W>(args, static_cast<uint32_t>(nc), grid, fixed + nwarps * spw * slot, stream);

@@ -48,6 +48,7 @@ struct GemvArgs {
   uint32_t slots;      // slots per consumer warp
   uint32_t contiguous; // bx == row_bytes: all rows of a slot arrive in one copy
   uint32_t rps;        // rows per slot: 1, 2 or 4 (single column), 1 or 2 otherwise
+  uint32_t static_weights;  // weights may be fetched before the preceding kernel has finished
 };
 
 template <bool kQ8W>
@@ -211,6 +212,13 @@ __global__ void __launch_bounds__(kGemvMaxThreads, 1) gemv_stream_kernel(const G
     }
   };
 
+  // Programmatic dependent launch: let the next kernel of the stream start its own prologue
+  // as soon as SMs free up.  This kernel in turn may only touch data the preceding kernel
+  // could have written after griddepcontrol.wait.  Activations and outputs always wait; the
+  // weight stream starts before the wait when the caller declared the weights static.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  if (!a.static_weights)
+    asm volatile("griddepcontrol.wait;" ::: "memory");
   if (lane == 0) {
     for (uint32_t i = 0; i < spw; ++i)
       mbar_init(&full[warp * spw + i], 1);
@@ -219,6 +227,8 @@ __global__ void __launch_bounds__(kGemvMaxThreads, 1) gemv_stream_kernel(const G
     for (uint32_t t = 0; t < min(spw, mine); ++t)
       issue(t);
   }
+  if (a.static_weights)
+    asm volatile("griddepcontrol.wait;" ::: "memory");
   // Convert the activation columns (plain block_q8_0, 2-byte aligned) into the lane layout.
   for (uint32_t idx = threadIdx.x; idx < kCols * nb; idx += nthreads) {
     const uint32_t col = idx / nb, ib = idx - col * nb;
