@@ -275,6 +275,10 @@ def run_ours(args):
 
     e2e = measure_e2e(pkg, torch, layers, max(10, min(args.steps, 50)), dist)
     try:
+        others = measure_other_kernels(pkg, torch) if (rank == 0 and not args.skip_gemm) else None
+    except Exception as exc:
+        others = {"error": f"{type(exc).__name__}: {exc}"}
+    try:
         gemm = None if args.skip_gemm else measure_gemm(pkg, torch, dist, rank, world)
     except Exception as exc:  # the headline line must still be printed
         gemm = {"error": f"{type(exc).__name__}: {exc}"}
@@ -315,6 +319,7 @@ def run_ours(args):
         "cpu_baseline": cpu,
         "per_shape": per_shape,
         "gemm": gemm,
+        "other_kernels": others,
         "gpu_launches": launches,
         "clocks": clocks,
     }
@@ -378,6 +383,67 @@ def measure_e2e(pkg, torch, layers, steps, dist):
             "d2h_bytes_per_step": sum(int(y.numel()) * 4 for _, _, _, y in host),
             "ms_per_step": round(dt / steps * 1e3, 4), "steps": steps,
             "weights": "registered once (resident); activations and outputs cross PCIe every step"}
+
+
+def measure_other_kernels(pkg, torch):
+    """The remaining kernels of the path at their BASELINE sizes, device-resident, timed with
+    events over CUDA-graph replays on rotating buffers (> L2 in total): algorithmic GB/s."""
+    side = torch.cuda.Stream()
+    gen = torch.Generator(device="cuda").manual_seed(5)
+    out = []
+
+    def timed(name, fn_for_copy, ncopies, nbytes, note):
+        with torch.cuda.stream(side):
+            for c in range(ncopies):
+                fn_for_copy(c)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            for c in range(ncopies):
+                fn_for_copy(c)
+        for _ in range(2):
+            g.replay()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 10
+        a.record()
+        for _ in range(reps):
+            g.replay()
+        b.record()
+        torch.cuda.synchronize()
+        us = a.elapsed_time(b) * 1e3 / (reps * ncopies)
+        out.append({"kernel": name, "us": round(us, 3), "gbs": round(nbytes / us / 1e3, 1), "bytes": nbytes, "case": note})
+
+    # add f32, n = 1,048,576 (12.6 MB per launch; 24 buffer sets = 302 MB)
+    n = 1 << 20
+    sets = [(torch.rand(n, generator=gen, device="cuda") * 2 - 1, torch.rand(n, generator=gen, device="cuda") * 2 - 1,
+             torch.empty(n, device="cuda")) for _ in range(24)]
+    timed("add_f32", lambda c: pkg.add(sets[c][0], sets[c][1], out=sets[c][2]), 24, 12 * n, "n = 1,048,576")
+    del sets
+    # Q8_0 dequant 4096 x 4096 (84.9 MB per launch; 4 sets)
+    wf = torch.randn((4096, 4096), generator=gen, device="cuda") * 0.02
+    q8 = [pkg.quantize_q8_0(wf) for _ in range(4)]
+    q4 = [pkg.quantize_q4_0(wf) for _ in range(4)]
+    outs = [torch.empty((4096, 4096), device="cuda") for _ in range(4)]
+    nb = 4096 * 4096 // 32
+    timed("dequantize_row_q8_0", lambda c: pkg.dequantize_q8_0(q8[c], out=outs[c]), 4, nb * (34 + 128), "4096 x 4096")
+    timed("dequantize_row_q4_0", lambda c: pkg.dequantize_q4_0(q4[c], out=outs[c]), 4, nb * (18 + 128), "4096 x 4096")
+    timed("quantize_row_q8_0", lambda c: pkg.quantize_q8_0(outs[c], out=q8[c]), 4, nb * (34 + 128), "4096 x 4096")
+    del q4, outs, wf
+    # Q8_0 x Q8_0 GEMV 11008 x 4096 and Q4_0 x Q8_0 GEMV with 8 activation columns
+    w8 = [pkg.quantize_q8_0(torch.randn((11008, 4096), generator=gen, device="cuda") * 0.02) for _ in range(6)]
+    x1 = pkg.quantize_q8_0(torch.randn((1, 4096), generator=gen, device="cuda"))
+    y1 = torch.empty((11008, 1), device="cuda")
+    timed("gemv_q8_0_q8_0", lambda c: pkg.gemv(w8[c], x1, q8_weights=True, out=y1, flags=pkg.FLAG_STATIC_WEIGHTS), 6,
+          11008 * 128 * 34 + 128 * 34 + 4 * 11008, "11008 x 4096, batch 1")
+    del w8
+    w4 = [pkg.quantize_q4_0(torch.randn((32000, 4096), generator=gen, device="cuda") * 0.02) for _ in range(5)]
+    x8 = pkg.quantize_q8_0(torch.randn((8, 4096), generator=gen, device="cuda"))
+    y8 = torch.empty((32000, 8), device="cuda")
+    timed("gemv_q4_0_q8_0_batch8", lambda c: pkg.gemv(w4[c], x8, out=y8, flags=pkg.FLAG_STATIC_WEIGHTS), 5,
+          gemv_bytes(32000, 4096, 8), "32000 x 4096, batch 8")
+    pkg.check_device_errors()
+    return out
 
 
 GEMM_SHAPES = [(11008, 4096), (32000, 4096)]

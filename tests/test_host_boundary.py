@@ -235,3 +235,56 @@ def test_launch_stub_defines_the_reference_named_entry():
     c = subprocess.run(["g++", "-std=c++17", "-fsyntax-only", "-I", os.path.join(ROOT, "include"), "-x", "c++", "-"],
                        input=s.stdout, capture_output=True, text=True)
     assert c.returncode == 0, c.stderr
+
+
+# ---- abstract contraction request (tcrv_rvv.quant_contraction) -> provider picks the kernel
+
+LOWER = "--tcrv-cuda-lower-quant-contraction"
+
+
+def test_quant_contraction_decode_lowers_to_block_dot_with_audit():
+    src = fixture("cuda-quant-contraction-q4-0.mlir")
+    lowered = plan(src, [LOWER])
+    assert "tcrv_rvv.quant_contraction" not in lowered
+    assert "tcrv_rvv.q4_0_q8_0_block_dot %vx, %vy, %s, %n, %vl" in lowered  # the column count is dropped
+    for needle in ('kind = "ggml_q4_0_q8_0_block_dot"', 'tcrv_cuda.contraction_algorithm = "decode-gemv-bulk-copy"',
+                   'tcrv_cuda.path_selection_reason = "streaming-kept-q4_0-decode-hbm-bound"',
+                   'tcrv_cuda.weight_layout_contract = "plain"', "weight_block_stride = 18"):
+        assert needle in lowered, needle
+    for gone in ("m_regime", "weight_layout =", "min_vlen", 'quant = "q4_0"'):
+        assert gone not in lowered, gone
+    h = header(plan(src, [LOWER, *PLAN_PASSES]))
+    assert h.returncode == 0, h.stderr
+    assert "void tcrv_emitc_ggml_vec_dot_q4_0_q8_0_kernel_ggml_vec_dot_q4_0_q8_0(size_t n, float *s, size_t bs" in h.stdout
+    # lowering is idempotent; an unlowered request has no kernel
+    assert plan(lowered, [LOWER]) == lowered
+    r = run([OPT, "-", *PLAN_PASSES], src)
+    assert r.returncode != 0 and "no kernel for op 'tcrv_rvv.quant_contraction'" in r.stderr
+
+
+def test_quant_contraction_selection_matrix():
+    src = fixture("cuda-quant-contraction-q4-0.mlir")
+    prefill = plan(src.replace('m_regime = "decode"', 'm_regime = "prefill"'), [LOWER])
+    assert 'tcrv_cuda.contraction_algorithm = "prefill-gemm-tcgen05-i8"' in prefill
+    assert 'tcrv_cuda.path_selection_reason = "tensor-core-kept-q4_0-prefill"' in prefill
+    assert 'tcrv_cuda.weight_layout_contract = "planar-int8-fp32-scales"' in prefill
+    q8 = (src.replace('quant = "q4_0"', 'quant = "q8_0"').replace("weight_block_stride = 18", "weight_block_stride = 34")
+          .replace(", activation_high_byte_offset = 16 : i64", ""))
+    low = plan(q8, [LOWER])
+    assert "tcrv_rvv.q8_0_q8_0_block_dot" in low and "streaming-kept-q8_0-decode-hbm-bound" in low
+    low = plan(q8.replace('m_regime = "decode"', 'm_regime = "prefill"'), [LOWER])
+    assert "streaming-decline-q8_0-no-tensor-core-kernel" in low and 'weight_layout_contract = "plain"' in low
+
+
+@pytest.mark.parametrize("old,new,message", [
+    ('weight_layout = "plain"', 'weight_layout = "x16"', "takes plain weights"),
+    ('m_regime = "decode"', 'm_regime = "training"', "m_regime must be"),
+    ('quant = "q4_0"', 'quant = "q4_K"', "unsupported quant"),
+    ("weight_block_stride = 18", "weight_block_stride = 34", "needs weight_block_stride = 18"),
+    ("%n, %bs, %vl {quant", "%n, %vl {quant", "takes weight, activation, output, n, nc"),
+])
+def test_quant_contraction_negatives(old, new, message):
+    src = fixture("cuda-quant-contraction-q4-0.mlir")
+    assert old in src
+    r = run([OPT, "-", LOWER], src.replace(old, new))
+    assert r.returncode != 0 and message in r.stderr, r.stderr

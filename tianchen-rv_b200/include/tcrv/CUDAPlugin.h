@@ -54,3 +54,33 @@ std::shared_ptr<const ExtensionPlugin> createCUDAExtensionPlugin();
 
 }  // namespace cuda
 }  // namespace tcrv
+
+// ---- abstract contraction request -> concrete op (the provider picks HOW) ----
+namespace tcrv {
+namespace cuda {
+
+enum class QuantType { Q4_0, Q8_0 };
+enum class MRegime { Decode, Prefill };
+enum class ContractionAlgorithm {
+  StreamingGemv,   // plain-format weight streaming, dp4a, HBM-bound (decode)
+  TensorCoreGemm,  // tcgen05 kind::i8 over the prepared planar layout (prefill)
+};
+
+struct ContractionSelection {
+  ContractionAlgorithm algorithm;
+  const char *algorithmName;         // stamped as tcrv_cuda.contraction_algorithm
+  const char *reason;                // stamped as tcrv_cuda.path_selection_reason
+  const char *weightLayoutContract;  // stamped as tcrv_cuda.weight_layout_contract
+};
+
+// Pure function of the request's facts, the counterpart of the reference's
+// selectContractionAlgorithm (include/TianChenRV/Plugin/RVV/RVVContractionPathSelection.h:31-70).
+ContractionSelection selectContractionAlgorithm(QuantType quant, MRegime regime);
+
+// Lowers every `tcrv_rvv.quant_contraction` under a CUDA-provider boundary of `kernel` to
+// the concrete block-dot op it stands for and stamps the audit attributes
+// (lib/Plugin/RVV/RVVLowerQuantContraction.cpp:80-99, :301).  `lowered` counts rewrites.
+Error lowerQuantContractions(Op &kernel, int &lowered);
+
+}  // namespace cuda
+}  // namespace tcrv

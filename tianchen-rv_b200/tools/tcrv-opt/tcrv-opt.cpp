@@ -4,6 +4,7 @@
 //   --tcrv-check-capability-requires
 //   --tcrv-materialize-selected-lowering-boundaries
 //   --tcrv-materialize-emission-plans
+//   --tcrv-cuda-lower-quant-contraction   (counterpart of --tcrv-rvv-lower-quant-contraction)
 //   --tcrv-disable-builtin-plugins
 // Passes run in command-line order over every variant whose origin names a registered
 // provider; variants of other origins (e.g. a scalar fallback) are left untouched.
@@ -13,6 +14,7 @@
 #include <string>
 #include <vector>
 
+#include "tcrv/CUDAPlugin.h"
 #include "tcrv/ExtensionPlugin.h"
 
 using namespace tcrv;
@@ -41,12 +43,12 @@ int main(int argc, char **argv) {
     if (a == "--tcrv-disable-builtin-plugins")
       builtin = false;
     else if (a == "--tcrv-check-capability-requires" || a == "--tcrv-materialize-selected-lowering-boundaries" ||
-             a == "--tcrv-materialize-emission-plans")
+             a == "--tcrv-materialize-emission-plans" || a == "--tcrv-cuda-lower-quant-contraction")
       passes.push_back(a);
     else if (a == "--help" || a == "-h") {
       std::cout << "usage: tcrv-opt [file|-] [--tcrv-check-capability-requires] "
                    "[--tcrv-materialize-selected-lowering-boundaries] [--tcrv-materialize-emission-plans] "
-                   "[--tcrv-disable-builtin-plugins]\n";
+                   "[--tcrv-cuda-lower-quant-contraction] [--tcrv-disable-builtin-plugins]\n";
       return 0;
     } else if (a.rfind("--", 0) == 0)
       return fail("unknown option '" + a + "'");
@@ -74,6 +76,12 @@ int main(int argc, char **argv) {
       if (kop->name != "tcrv.exec.kernel")
         continue;
       Op &kernel = *kop;
+      if (pass == "--tcrv-cuda-lower-quant-contraction") {
+        int lowered = 0;
+        if (Error e = cuda::lowerQuantContractions(kernel, lowered))
+          return fail(e.message);
+        continue;
+      }
       std::vector<std::unique_ptr<Op>> plans;
       for (auto &vop : kernel.body) {
         if (vop->name != "tcrv.exec.variant")
