@@ -108,10 +108,21 @@ int tcrv_cuda_vec_dot_q8_0_q8_0(size_t n, float *s, const uint8_t *vx, const uin
  *
  * `tcrv_cuda_gemv_*` is the decode path (nc <= 8, HBM-bound weight streaming);
  * `tcrv_cuda_gemm_*` is the prefill path (int8 tensor-core contraction, needs a workspace).
- * The GEMV folds each row in 32 lane partials (lane l owns block pairs l, l+32, ... in
- * ascending order) that are combined by a butterfly; TCRV_CUDA_FLAG_STRICT_ORDER selects
- * the sequential fold.  The GEMM folds every output element in strict ascending block
- * order.  Both use the fused form fma((float)sumi * d_x, d_y, sumf). */
+ * fp32 order of the GEMV (all within rel 1e-5 of the sequential fold; tcrv_cuda_gemv_fold_order
+ * tells which one a call uses):
+ *   1..5 columns: 32 lane partials (lane l owns block pairs l, l+32, ... ascending), combined
+ *     by a butterfly (TCRV_CUDA_ORDER_LANE_PAIRS);
+ *   6..8 columns (tensor-core kernel): the blocks are cut into chunks of 8, partial w of 16 folds chunks w, w+16,
+ *     ... ascending, and the row is ((p_0 + p_1) + ...) + p_15 (TCRV_CUDA_ORDER_KSPLIT16);
+ *   TCRV_CUDA_FLAG_STRICT_ORDER, and operands that rule out 16-byte bulk copies: sequential
+ *     or lane-pair order on the generic kernel.
+ * The GEMM folds every output element in strict ascending block order.  All use the fused
+ * form fma((float)sumi * d_x, d_y, sumf). */
+#define TCRV_CUDA_ORDER_STRICT 0
+#define TCRV_CUDA_ORDER_LANE_PAIRS 1
+#define TCRV_CUDA_ORDER_KSPLIT16 2
+int tcrv_cuda_gemv_fold_order(int q8_weights, size_t n, size_t nc, const void *vx, size_t bx, const void *vy,
+                              size_t by, unsigned flags);
 int tcrv_cuda_gemv_q4_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by,
                              size_t nr, size_t nc, size_t bx, size_t bs, unsigned flags,
                              tcrv_cuda_stream stream);

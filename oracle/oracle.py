@@ -75,6 +75,7 @@ def _declare(L: ctypes.CDLL) -> None:
     L.tcrv_oracle_gemm_q4_0_q8_0.argtypes = gemm
     L.tcrv_oracle_gemm_q8_0_q8_0.argtypes = gemm
     L.tcrv_oracle_gemv_lane_order.argtypes = [_sz, _p, _p, _p, _sz, _sz, _sz, _sz, _sz, ctypes.c_int]
+    L.tcrv_oracle_gemv_ksplit_order.argtypes = [_sz, _p, _p, _p, _sz, _sz, _sz, _sz, _sz, ctypes.c_int, _sz, _sz]
     L.tcrv_oracle_gemm_abs_terms.argtypes = [_sz, _p, _p, _p, _sz, _sz, _sz, _sz, _sz, ctypes.c_int]
 
 
@@ -237,6 +238,12 @@ def gemm(w: np.ndarray, x: np.ndarray, q8_weights: bool = False, fold: int = FOL
 def gemv_lane_order(w: np.ndarray, x: np.ndarray, q8_weights: bool = False) -> np.ndarray:
     """The CUDA GEMV's fp32 order restated on the CPU (lane partials + butterfly)."""
     return _gemm_like(lib().tcrv_oracle_gemv_lane_order, w, x, (1 if q8_weights else 0,))
+
+
+def gemv_ksplit_order(w: np.ndarray, x: np.ndarray, q8_weights: bool = False, chunk_blocks: int = 8,
+                      split: int = 16) -> np.ndarray:
+    """The tensor-core decode GEMV's fp32 order restated on the CPU (K split over 16 warps)."""
+    return _gemm_like(lib().tcrv_oracle_gemv_ksplit_order, w, x, (1 if q8_weights else 0, chunk_blocks, split))
 
 
 def abs_terms(w: np.ndarray, x: np.ndarray, q8_weights: bool = False) -> np.ndarray:

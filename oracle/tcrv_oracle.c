@@ -422,6 +422,36 @@ void tcrv_oracle_gemv_lane_order(size_t n, float *s, const uint8_t *vx, const ui
   }
 }
 
+void tcrv_oracle_gemv_ksplit_order(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by,
+                                   size_t nr, size_t nc, size_t bx, size_t bs, int q8_weights,
+                                   size_t chunk_blocks, size_t split) {
+  size_t nb = n / TCRV_QK;
+  size_t wstride = q8_weights ? TCRV_Q8_0_BLOCK_BYTES : TCRV_Q4_0_BLOCK_BYTES;
+  size_t nchunks = (nb + chunk_blocks - 1) / chunk_blocks;
+  for (size_t ir = 0; ir < nr; ++ir) {
+    const uint8_t *xr = vx + ir * bx;
+    for (size_t col = 0; col < nc; ++col) {
+      const uint8_t *yc = vy + col * by;
+      float total = 0.0f;
+      for (size_t w = 0; w < split; ++w) {
+        float part = 0.0f; /* warp w: chunks w, w+split, ... ascending, blocks ascending */
+        for (size_t c = w; c < nchunks; c += split) {
+          for (size_t ib = c * chunk_blocks; ib < (c + 1) * chunk_blocks && ib < nb; ++ib) {
+            const uint8_t *xb = xr + ib * wstride;
+            const uint8_t *yb = yc + ib * TCRV_Q8_0_BLOCK_BYTES;
+            if (q8_weights)
+              part = fold_q8(part, block_sum_q8_0_q8_0(xb, yb), block_scale(xb), block_scale(yb), TCRV_FOLD_FMA);
+            else
+              part = fold_q4(part, block_sum_q4_0_q8_0(xb, yb), block_scale(xb), block_scale(yb), TCRV_FOLD_FMA);
+          }
+        }
+        total = w == 0 ? part : total + part;
+      }
+      s[ir * bs + col] = total;
+    }
+  }
+}
+
 void tcrv_oracle_gemm_abs_terms(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by,
                                 size_t nr, size_t nc, size_t bx, size_t bs, int q8_weights) {
   size_t nb = n / TCRV_QK;

@@ -105,6 +105,14 @@ void tcrv_oracle_gemm_q8_0_q8_0(size_t n, float *s, const uint8_t *vx, const uin
 void tcrv_oracle_gemv_lane_order(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by,
                                  size_t nr, size_t nc, size_t bx, size_t bs, int q8_weights);
 
+/* Restatement of the tensor-core decode GEMV's fp32 order (2..8 activation columns): the
+ * blocks of a row are cut into chunks of `chunk_blocks`; partial w (0 <= w < split) folds the
+ * chunks w, w+split, ... in ascending order with the fused fold starting from 0.0f, and the
+ * row value is ((p_0 + p_1) + p_2) + ... + p_{split-1}. */
+void tcrv_oracle_gemv_ksplit_order(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by,
+                                   size_t nr, size_t nc, size_t bx, size_t bs, int q8_weights,
+                                   size_t chunk_blocks, size_t split);
+
 /* Sum over blocks of |term| for one (row, column): the cancellation scale tests use to
  * judge a relative error on a row whose terms nearly cancel. */
 void tcrv_oracle_gemm_abs_terms(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by,

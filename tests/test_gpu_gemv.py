@@ -21,8 +21,19 @@ def make(O, nr, k, nc, q8w, seed):
     return w, x
 
 
-def check_rows(O, got, w, x, q8w):
-    assert np.array_equal(got.view(np.uint32), O.gemv_lane_order(w, x, q8w).view(np.uint32))
+def restated(O, w, x, q8w, order):
+    """The oracle's restatement of the order the library reports for a call."""
+    if order == 2:
+        return O.gemv_ksplit_order(w, x, q8w)
+    if order == 1:
+        return O.gemv_lane_order(w, x, q8w)
+    return O.gemm(w, x, q8_weights=q8w, fold=O.FOLD_FMA)
+
+
+def check_rows(O, got, w, x, q8w, order=None):
+    if order is None:  # packed, aligned operands: up to 5 columns -> lane pairs, 6..8 -> K split
+        order = 1 if (x.shape[0] < 6 or (x.shape[1] // 34) % 8 != 0) else 2
+    assert np.array_equal(got.view(np.uint32), restated(O, w, x, q8w, order).view(np.uint32))
     ref = O.gemm(w, x, q8_weights=q8w)
     err = np.abs(got - ref)
     ok = (err <= REL * np.abs(ref)) | (err <= CANCEL * O.abs_terms(w, x, q8w))
@@ -78,8 +89,9 @@ def test_block_sums_extreme_bytes(cuda, pkg, O):
     got = pkg.block_sums(dev(cuda, w), dev(cuda, x)).cpu().numpy()
     want = O.block_sums(w, x)
     assert np.array_equal(got, want) and want.min() == -8 * 127 * 32 and want.max() == 8 * 128 * 32
-    y = pkg.gemv(dev(cuda, w), dev(cuda, x)).cpu().numpy()
-    assert np.array_equal(y, O.gemv_lane_order(w, x))
+    wd, xd = dev(cuda, w), dev(cuda, x)
+    y = pkg.gemv(wd, xd).cpu().numpy()
+    assert np.array_equal(y, restated(O, w, x, False, pkg.gemv_fold_order(wd, xd)))
 
 
 def test_vec_dot_entry_points(cuda, pkg, O):
@@ -103,6 +115,7 @@ def test_padded_strides(cuda, pkg, O):
     assert st == 0
     pkg.check_device_errors()
     res = out.cpu().numpy()
+    assert L.tcrv_cuda_gemv_fold_order(0, 2048, 4, wt.data_ptr(), wt.stride(0), xt.data_ptr(), xt.stride(0), 0) == 1
     assert np.array_equal(res[:, :4], O.gemv_lane_order(w, x)) and np.all(res[:, 4:] == -1.0)
 
 
@@ -156,3 +169,22 @@ def test_rows_per_slot_choices_give_identical_rows(cuda, pkg, O, forced, q8w):
         got = pkg.gemv(dev(cuda, w), dev(cuda, x), q8_weights=q8w, flags=forced << 8).cpu().numpy()
         pkg.check_device_errors()
         assert np.array_equal(got.view(np.uint32), O.gemv_lane_order(w, x, q8w).view(np.uint32))
+
+
+@pytest.mark.parametrize("q8w", [False, True])
+@pytest.mark.parametrize("nr,k,nc", [(16, 256, 6), (33, 256, 8), (1000, 4096, 8), (257, 11008, 7), (4096, 4096, 8)])
+def test_tensor_core_gemv_reports_and_follows_its_order(cuda, pkg, O, q8w, nr, k, nc):
+    w, x = make(O, nr, k, nc, q8w, 1300 + nr)
+    wd, xd = dev(cuda, w), dev(cuda, x)
+    order = pkg.gemv_fold_order(wd, xd, q8_weights=q8w)
+    # Q8_0 rows of K = 11008 leave no room for the slot rings: that case stays on the dp4a kernel
+    assert order == (1 if (q8w and k == 11008) else 2)
+    assert pkg.gemv_fold_order(wd, xd, q8_weights=q8w, flags=pkg.FLAG_STRICT_ORDER) == 0
+    assert pkg.gemv_fold_order(wd, xd[:1], q8_weights=q8w) == 1 and pkg.gemv_fold_order(wd, xd[:5], q8_weights=q8w) == 1
+    got = pkg.gemv(wd, xd, q8_weights=q8w).cpu().numpy()
+    pkg.check_device_errors()
+    rows = np.unique(np.concatenate([np.arange(0, nr, 37), np.arange(max(0, nr - 20), nr)]))
+    check_rows(O, got[rows], w[rows], x, q8w, order=order)
+    # the dp4a kernel (flags bit 12) still serves several columns, in lane-pair order
+    alt = pkg.gemv(wd, xd, q8_weights=q8w, flags=0x1000).cpu().numpy()
+    assert np.array_equal(alt[rows].view(np.uint32), O.gemv_lane_order(w[rows], x, q8w).view(np.uint32))

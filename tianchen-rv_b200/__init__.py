@@ -52,6 +52,7 @@ ABI = {
     "tcrv_cuda_gemm_q4_0_q8_0": [_sz, _p, _p, _p, _sz, _sz, _sz, _sz, _sz, _p, _sz, ctypes.c_uint, _p],
     "tcrv_cuda_gemm_q4_0_q8_0_prepared": [_sz, _p, _p, _p, _sz, _sz, _sz, _sz, _p, _sz, ctypes.c_uint, _p],
     "tcrv_cuda_gemm_q4_0_q8_0_static_scratch": [_sz, _p, _p, _p, _sz, _sz, _sz, _sz, _sz, ctypes.c_uint, _p],
+    "tcrv_cuda_gemv_fold_order": [_i, _sz, _sz, _p, _sz, _p, _sz, ctypes.c_uint],
     "tcrv_cuda_block_sums_q4_0_q8_0": [_sz, _p, _p, _p, _sz, _sz, _sz, _sz, _p],
     "tcrv_cuda_block_sums_q8_0_q8_0": [_sz, _p, _p, _p, _sz, _sz, _sz, _sz, _p],
 }
@@ -266,6 +267,14 @@ def gemv(w, x, q8_weights: bool = False, flags: int = FLAG_NONE, out=None):
     _check(fn(n, _dev(out, torch.float32), w.data_ptr(), x.data_ptr(), by, nr, nc, bx, out.stride(0), flags, _stream()),
            name)
     return out
+
+
+def gemv_fold_order(w, x, q8_weights: bool = False, flags: int = FLAG_NONE) -> int:
+    """0 = strict ascending, 1 = lane pairs + butterfly, 2 = 16-way K split: the fp32 order
+    `gemv(w, x, ...)` uses for these operands."""
+    wblock = Q8_0_BLOCK if q8_weights else Q4_0_BLOCK
+    n, nr, nc, bx, by, _ = _matrix_args(w, x, wblock)
+    return lib().tcrv_cuda_gemv_fold_order(1 if q8_weights else 0, n, nc, w.data_ptr(), bx, x.data_ptr(), by, flags)
 
 
 def block_sums(w, x, q8_weights: bool = False):

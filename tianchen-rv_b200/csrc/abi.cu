@@ -177,6 +177,12 @@ int tcrv_cuda_gemv_q8_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_
   return launch_gemv<true>(n, s, vx, vy, by, nr, nc, bx, bs, flags, as_stream(stream));
 }
 
+int tcrv_cuda_gemv_fold_order(int q8_weights, size_t n, size_t nc, const void *vx, size_t bx, const void *vy,
+                              size_t by, unsigned flags) {
+  return q8_weights ? gemv_fold_order<true>(n, nc, vx, bx, vy, by, flags)
+                    : gemv_fold_order<false>(n, nc, vx, bx, vy, by, flags);
+}
+
 int tcrv_cuda_block_sums_q4_0_q8_0(size_t n, int32_t *sumi, const uint8_t *vx, const uint8_t *vy, size_t by,
                                    size_t nr, size_t nc, size_t bx, tcrv_cuda_stream stream) {
   const int st = check_matrix_args(n, sumi, vx, vy, by, nr, nc, bx, nc, TCRV_Q4_0_BLOCK_BYTES);

@@ -197,6 +197,12 @@ int run_gemm(size_t n, float *s, const uint8_t *weights_planar, const uint8_t *a
 
 }  // namespace
 
+int encode_tensor_map_2d_u16(CUtensorMap *map, const void *base, uint64_t inner_elems, uint64_t outer,
+                             uint64_t row_stride_bytes, uint32_t box_inner_elems, uint32_t box_outer) {
+  return make_map_2d(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, base, inner_elems, outer, row_stride_bytes,
+                     box_inner_elems, box_outer, CU_TENSOR_MAP_SWIZZLE_NONE);
+}
+
 size_t gemm_weights_bytes(size_t n, size_t nr) {
   const PlanarSizes p = planar_sizes(n, nr, 0);
   return p.w8 + p.dw;

@@ -2,7 +2,9 @@
 // bulk copies, otherwise a generic warp-per-row kernel that accepts any alignment and any
 // block count and also implements the strict (sequential) fold order.  Plus the debug kernel
 // that exposes the integer stage (per-block int32 sums).
+#include "gemv_mma.cuh"
 #include "gemv_stream.cuh"
+#include "launchers.h"
 
 namespace tcrv {
 
@@ -174,7 +176,83 @@ int launch_stream(const GemvArgs &args, uint32_t nc, int grid, size_t smem, cuda
 
 inline bool multiple_of(const void *p, uintptr_t m) { return reinterpret_cast<uintptr_t>(p) % m == 0; }
 
+constexpr size_t kMmaMinCols = 6;
+
+// Ring depth of the tensor-core GEMV for a row of nb blocks, 0 if it does not fit.
+template <bool kQ8W>
+size_t mma_slots(uint32_t nb) {
+  const size_t fixed = kMmaBarrierBytes + kMmaPartialBytes + static_cast<size_t>(nb) * kMmaXBytesPerBlock;
+  const size_t slot = static_cast<size_t>(kMmaRows) * kMmaChunkBlocks * WeightFormat<kQ8W>::kBlockBytes;
+  if (fixed + 2 * kMmaWarps * slot > kMaxDynamicSmem)
+    return 0;
+  size_t spw = (kMaxDynamicSmem - fixed) / (kMmaWarps * slot);
+  return spw > kMmaMaxSlots ? kMmaMaxSlots : spw;
+}
+
+template <bool kQ8W>
+int launch_mma(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by, size_t nr, size_t nc, size_t bx,
+               size_t bs, unsigned flags, size_t spw, cudaStream_t stream) {
+  constexpr int WB = WeightFormat<kQ8W>::kBlockBytes;
+  const uint32_t nb = static_cast<uint32_t>(n / kQK);
+  CUtensorMap map;
+  const int st = encode_tensor_map_2d_u16(&map, vx, static_cast<uint64_t>(nb) * WB / 2, nr, bx,
+                                          kMmaChunkBlocks * WB / 2, kMmaRows);
+  if (st != TCRV_CUDA_OK)
+    return st;
+  GemvMmaArgs args;
+  args.vy = vy;
+  args.s = s;
+  args.by = by;
+  args.bs = bs;
+  args.nr = static_cast<uint32_t>(nr);
+  args.nc = static_cast<uint32_t>(nc);
+  args.nb = nb;
+  args.slots = static_cast<uint32_t>(spw);
+  args.static_weights = (flags & TCRV_CUDA_FLAG_STATIC_WEIGHTS) ? 1u : 0u;
+  const size_t smem = kMmaBarrierBytes + kMmaPartialBytes + static_cast<size_t>(nb) * kMmaXBytesPerBlock +
+                      spw * kMmaWarps * kMmaRows * kMmaChunkBlocks * WB;
+  auto kernel = gemv_mma_kernel<kQ8W>;
+  static bool configured[64] = {};
+  int dev = 0;
+  TCRV_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 64 && !configured[dev]) {
+    TCRV_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(kMaxDynamicSmem)));
+    configured[dev] = true;
+  }
+  const size_t groups = (nr + kMmaRows - 1) / kMmaRows;
+  const int sms = sm_count();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(groups < static_cast<size_t>(sms) ? groups : sms));
+  cfg.blockDim = dim3(kMmaThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  TCRV_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, map, args));
+  return TCRV_CUDA_OK;
+}
+
 }  // namespace
+
+// 0 = strict ascending, 1 = lane pairs + butterfly, 2 = 16-way K split (see tcrv_cuda.h).
+template <bool kQ8W>
+int gemv_fold_order(size_t n, size_t nc, const void *vx, size_t bx, const void *vy, size_t by, unsigned flags) {
+  const uint32_t nb = static_cast<uint32_t>(n / kQK);
+  if (flags & TCRV_CUDA_FLAG_STRICT_ORDER)
+    return TCRV_CUDA_ORDER_STRICT;
+  const bool bulk = nb > 0 && nb % 8 == 0 && nc <= kGemvMaxCols && multiple_of(vx, 16) && bx % 16 == 0 &&
+                    multiple_of(vy, 2) && by % 2 == 0;
+  if (bulk && nc >= kMmaMinCols && (flags & 0x1000u) == 0 && mma_slots<kQ8W>(nb) >= 2)
+    return TCRV_CUDA_ORDER_KSPLIT16;
+  return TCRV_CUDA_ORDER_LANE_PAIRS;
+}
+
+template int gemv_fold_order<false>(size_t, size_t, const void *, size_t, const void *, size_t, unsigned);
+template int gemv_fold_order<true>(size_t, size_t, const void *, size_t, const void *, size_t, unsigned);
 
 template <bool kQ8W>
 int launch_gemv(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by, size_t nr, size_t nc,
@@ -188,6 +266,13 @@ int launch_gemv(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t
 
   if (!strict && nb > 0 && nb % 8 == 0 && nc <= kGemvMaxCols && multiple_of(vx, 16) && bx % 16 == 0 &&
       multiple_of(vy, 2) && by % 2 == 0) {
+    // Many activation columns: the tensor-core kernel (measured faster from about 6 columns
+    // on; flags bit 12 keeps the dp4a kernel).
+    if (nc >= kMmaMinCols && (flags & 0x1000u) == 0) {
+      const size_t spw = mma_slots<kQ8W>(nb);
+      if (spw >= 2)
+        return launch_mma<kQ8W>(n, s, vx, vy, by, nr, nc, bx, bs, flags, spw, stream);
+    }
     const size_t fixed = kGemvBarrierBytes + nc * static_cast<size_t>(gemv_xcol_bytes(nb));
     // Rows per slot: a warp folds all rows of a slot together, and more independent rows per
     // warp hide more latency (the kernel is issue/latency-bound); measured best is 4 rows for

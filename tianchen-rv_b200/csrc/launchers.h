@@ -1,6 +1,7 @@
 // Internal launch functions behind the C ABI (device pointers, already validated).
 #pragma once
 
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <stddef.h>
 #include <stdint.h>
@@ -19,6 +20,8 @@ template <bool kQ8W>
 int launch_gemv(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by, size_t nr, size_t nc,
                 size_t bx, size_t bs, unsigned flags, cudaStream_t stream);
 template <bool kQ8W>
+int gemv_fold_order(size_t n, size_t nc, const void *vx, size_t bx, const void *vy, size_t by, unsigned flags);
+template <bool kQ8W>
 int launch_block_sums(size_t n, int32_t *sumi, const uint8_t *vx, const uint8_t *vy, size_t by, size_t nr,
                       size_t nc, size_t bx, cudaStream_t stream);
 
@@ -36,4 +39,10 @@ int launch_gemm_static_scratch(size_t n, float *s, const uint8_t *vx, size_t bx,
                                size_t nr, size_t nc, size_t bs, cudaStream_t stream);
 int launch_gemm_prepared(size_t n, float *s, const uint8_t *weights_planar, const uint8_t *acts_planar, size_t nr,
                          size_t nc, size_t bs, cudaStream_t stream);
+}  // namespace tcrv
+
+namespace tcrv {
+// Tiled TMA descriptor over a matrix of 16-bit elements (rows `row_stride_bytes` apart), no swizzle.
+int encode_tensor_map_2d_u16(CUtensorMap *map, const void *base, uint64_t inner_elems, uint64_t outer,
+                             uint64_t row_stride_bytes, uint32_t box_inner_elems, uint32_t box_outer);
 }  // namespace tcrv
