@@ -74,6 +74,27 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity
   }
 }
 
+// The same bounded wait for warps that share a scheduler with a latency-critical issuing
+// thread: between polls the warp sleeps a few tens of nanoseconds instead of spinning, so
+// that its polling does not take issue slots away from that thread.
+__device__ __forceinline__ bool mbar_wait_bounded_relaxed(uint64_t *bar, uint32_t parity,
+                                                          volatile uint32_t *abort_flag = nullptr) {
+  if (mbar_try_wait(bar, parity))
+    return true;
+  const uint64_t start = global_timer_ns();
+  for (uint32_t i = 1;; ++i) {
+    __nanosleep(32);
+    if (mbar_try_wait(bar, parity))
+      return true;
+    if ((i & 255u) == 0) {
+      if (abort_flag != nullptr && *abort_flag != 0)
+        return false;
+      if (global_timer_ns() - start > kMbarTimeoutNs)
+        return false;
+    }
+  }
+}
+
 // global -> shared bulk copy; dst, src and bytes must be multiples of 16.
 __device__ __forceinline__ void bulk_copy_g2s(void *dst_smem, const void *src_gmem, uint32_t bytes,
                                               uint64_t *bar) {

@@ -10,16 +10,23 @@
 // before the next block's tile arrives.  The fold runs in strict ascending block order per
 // output element, in the fused form fma((float)S * d_w, d_x, acc).
 //
+// The epilogue, not the tensor pipe, bounds this kernel; see scaled_pair() for how the
+// int->float step is done on the integer and FMA pipes.
+//
 // Operands come from a planar ("prepared") layout written by the unpack kernels: int8
 // matrices [rows][K] and fp32 scale matrices, all fetched with tiled TMA loads (128-byte
-// swizzle for the int8 tiles).  Warp roles in a CTA of 10 warps:
-//   warps 0..7  epilogue: warp w reads TMEM lanes 32*(w%4).. (its weight rows) and columns
-//               64*(w/4).. of every accumulator tile
-//   warp 8      TMA producer (one lane)
-//   warp 9      TMEM allocation + MMA issue (one lane)
+// swizzle for the int8 tiles).  Warp roles in a CTA of 18 warps:
+//   warps 0..15 epilogue: warp w reads TMEM lanes 32*(w%4).. (its weight rows) and columns
+//               32*(w/4).. of every accumulator tile
+//   warp 16     TMA producer (one lane)
+//   warp 17     TMEM allocation + MMA issue (one lane)
 // Pipelines: kSmemStages shared-memory stages of 4 blocks each (full/empty mbarriers) and
-// kTmemStages TMEM accumulator tiles of 128 columns (full/empty mbarriers).  Every wait is
-// bounded; a failed wait raises the device error word and the CTA winds down.
+// kTmemStages TMEM stages (full/empty mbarriers).  A TMEM stage holds the accumulator tiles of
+// kGemmHandBlocks consecutive blocks (2 x 128 columns): the issuing thread fills both tiles,
+// commits once, and every epilogue warp waits and releases once per pair, which halves the
+// barrier traffic per block; the epilogue still folds the two tiles one after the other, in
+// block order.  Every wait is bounded; a failed wait raises the device error word and the CTA
+// winds down.
 #pragma once
 
 #include "tcgen05.cuh"
@@ -31,9 +38,12 @@ constexpr int kGemmTileRows = 128;   // weight rows per tile  (MMA M, TMEM lanes
 constexpr int kGemmTileCols = 128;   // activation columns per tile (MMA N, TMEM columns)
 constexpr int kGemmStageBlocks = 4;  // ggml blocks per shared-memory stage (128 bytes of K)
 constexpr int kGemmSmemStages = 5;
-constexpr int kGemmTmemStages = 4;
-constexpr int kGemmTmemCols = kGemmTmemStages * kGemmTileCols;  // 512
-constexpr int kGemmEpilogueWarps = 8;
+constexpr int kGemmHandBlocks = 2;  // ggml blocks (accumulator tiles) handed to the epilogue per barrier phase
+constexpr int kGemmTmemStages = 2;  // each stage holds kGemmHandBlocks accumulator tiles
+constexpr int kGemmTmemStageCols = kGemmHandBlocks * kGemmTileCols;  // 256
+constexpr int kGemmTmemCols = kGemmTmemStages * kGemmTmemStageCols;  // 512
+constexpr int kGemmEpilogueWarps = 16;                                  // 4 lane quarters x 4 column groups
+constexpr int kGemmColsPerWarp = kGemmTileCols / (kGemmEpilogueWarps / 4);  // 32
 constexpr int kGemmThreads = (kGemmEpilogueWarps + 2) * 32;
 
 constexpr int kGemmABytes = kGemmTileRows * kGemmStageBlocks * kQK;           // 16384
@@ -70,6 +80,19 @@ __device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c
   uint64_t r;
   asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
   return r;
+}
+
+// (float)S * d_w for two int32 block sums without an int->float conversion instruction (the
+// conversion unit, at 16 results per clock per SM, was what bounded this kernel): adding
+// 0x4B400000 to S as an INTEGER gives the bit pattern of the float 12582912 + S exactly
+// (|S| <= 32512 stays inside the binade whose ulp is 1), and
+// fma(12582912 + S, d_w, -12582912 * d_w) is the exact product S * d_w rounded once, i.e.
+// bit-identical to (float)S * d_w.  `c2` holds -12582912 * d_w (exact) in both halves.
+constexpr uint32_t kMagicBits = 0x4B400000u;
+constexpr float kMagic = 12582912.0f;
+
+__device__ __forceinline__ uint64_t scaled_pair(uint32_t s_lo, uint32_t s_hi, uint64_t dw2, uint64_t c2) {
+  return fma_f32x2(pack_f32x2(__uint_as_float(s_lo + kMagicBits), __uint_as_float(s_hi + kMagicBits)), dw2, c2);
 }
 
 struct PipeState {
@@ -179,13 +202,18 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           const uint32_t a_addr = stage_base_addr + ps.stage * kGemmStageBytes;
           const uint32_t b_addr = a_addr + kGemmABytes;
           const uint32_t steps = min(static_cast<uint32_t>(kGemmStageBlocks), a.nb - kb * kGemmStageBlocks);
-          for (uint32_t kk = 0; kk < steps; ++kk) {
+          for (uint32_t kk = 0; kk < steps; kk += kGemmHandBlocks) {
             ok = mbar_wait_bounded(&tmem_empty[ts.stage], ts.phase ^ 1, abort_flag);
             if (!ok)
               break;
             tcgen05_fence_after_thread_sync();
-            umma_s8_ss(tmem_base + ts.stage * kGemmTileCols, umma_desc_k_major_sw128(a_addr + kk * kQK),
-                       umma_desc_k_major_sw128(b_addr + kk * kQK), idesc, 0u);
+#pragma unroll
+            for (uint32_t h = 0; h < kGemmHandBlocks; ++h) {
+              if (kk + h < steps)
+                umma_s8_ss(tmem_base + ts.stage * kGemmTmemStageCols + h * kGemmTileCols,
+                           umma_desc_k_major_sw128(a_addr + (kk + h) * kQK),
+                           umma_desc_k_major_sw128(b_addr + (kk + h) * kQK), idesc, 0u);
+            }
             umma_commit(&tmem_full[ts.stage]);
             ts.advance(kGemmTmemStages);
           }
@@ -204,69 +232,69 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     }
   } else {
     // ------------------------------ epilogue warps ------------------------------
-    const int quarter = warp & 3, half = warp >> 2;
+    const int quarter = warp & 3, colgroup = warp >> 2;
+    constexpr int CPW = kGemmColsPerWarp;  // accumulator columns of this thread
     const int row_local = quarter * 32 + lane;
     const uint32_t lane_field = static_cast<uint32_t>(quarter * 32) << 16;
     PipeState ps, ts;
     bool ok = true;
     for (uint32_t t = blockIdx.x; t < a.tiles && ok; t += gridDim.x) {
       const uint32_t n0 = (t / a.tiles_m) * kGemmTileRows;
-      const uint32_t m0 = (t % a.tiles_m) * kGemmTileCols + half * 64;
-      uint64_t acc[32];
+      const uint32_t m0 = (t % a.tiles_m) * kGemmTileCols + colgroup * CPW;
+      uint64_t acc[CPW / 2];
 #pragma unroll
-      for (int j = 0; j < 32; ++j)
+      for (int j = 0; j < CPW / 2; ++j)
         acc[j] = 0ull;
       for (uint32_t kb = 0; kb < nkb && ok; ++kb) {
-        ok = mbar_wait_bounded(&smem_full[ps.stage], ps.phase, abort_flag);
+        ok = mbar_wait_bounded_relaxed(&smem_full[ps.stage], ps.phase, abort_flag);
         if (!ok)
           break;
         const uint8_t *st = stages + static_cast<size_t>(ps.stage) * kGemmStageBytes;
         const float4 dw4 = reinterpret_cast<const float4 *>(st + kGemmABytes + kGemmBBytes)[row_local];
         const float dws[4] = {dw4.x, dw4.y, dw4.z, dw4.w};
-        const uint8_t *dx_base = st + kGemmABytes + kGemmBBytes + kGemmDwBytes + half * 64 * 4;
+        const uint8_t *dx_base = st + kGemmABytes + kGemmBBytes + kGemmDwBytes + colgroup * CPW * 4;
         const uint32_t steps = min(static_cast<uint32_t>(kGemmStageBlocks), a.nb - kb * kGemmStageBlocks);
 #pragma unroll
-        for (uint32_t kk = 0; kk < kGemmStageBlocks; ++kk) {
+        for (uint32_t kk = 0; kk < kGemmStageBlocks; kk += kGemmHandBlocks) {
           if (kk < steps && ok) {
-            ok = mbar_wait_bounded(&tmem_full[ts.stage], ts.phase, abort_flag);
+            ok = mbar_wait_bounded_relaxed(&tmem_full[ts.stage], ts.phase, abort_flag);
             if (ok) {
               tcgen05_fence_after_thread_sync();
-              uint32_t v0[32], v1[32];
-              const uint32_t taddr = tmem_base + lane_field + ts.stage * kGemmTileCols + half * 64;
-              tmem_ld_32x32b_x32(taddr, v0);
-              tmem_ld_32x32b_x32(taddr + 32, v1);
-              tmem_ld_wait();
-              tcgen05_fence_before_thread_sync();
-              __syncwarp();
-              if (lane == 0)
-                mbar_arrive(&tmem_empty[ts.stage]);
+#pragma unroll
+              for (uint32_t h = 0; h < kGemmHandBlocks; ++h) {
+                if (kk + h < steps) {
+                  uint32_t v[CPW / 32][32];
+#pragma unroll
+                  for (int c = 0; c < CPW / 32; ++c)
+                    tmem_ld_32x32b_x32(tmem_base + lane_field + ts.stage * kGemmTmemStageCols + h * kGemmTileCols +
+                                           colgroup * CPW + 32 * c,
+                                       v[c]);
+                  tmem_ld_wait();
+                  if (h + 1 == kGemmHandBlocks || kk + h + 1 == steps) {
+                    // the last accumulator tile of this hand-over is in registers: release the stage
+                    tcgen05_fence_before_thread_sync();
+                    __syncwarp();
+                    if (lane == 0)
+                      mbar_arrive(&tmem_empty[ts.stage]);
+                  }
+                  const uint64_t dw2 = pack_f32x2(dws[kk + h], dws[kk + h]);
+                  const float cneg = __fmul_rn(-kMagic, dws[kk + h]);  // exact: 2-bit x 11-bit significands
+                  const uint64_t c2 = pack_f32x2(cneg, cneg);
+                  const ulonglong2 *dx2 = reinterpret_cast<const ulonglong2 *>(dx_base + (kk + h) * kGemmTileCols * 4);
+#pragma unroll
+                  for (int c = 0; c < CPW / 32; ++c) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                      const ulonglong2 d = dx2[8 * c + j];
+                      const uint64_t t0 = scaled_pair(v[c][4 * j], v[c][4 * j + 1], dw2, c2);
+                      const uint64_t t1 = scaled_pair(v[c][4 * j + 2], v[c][4 * j + 3], dw2, c2);
+                      acc[16 * c + 2 * j] = fma_f32x2(t0, d.x, acc[16 * c + 2 * j]);
+                      acc[16 * c + 2 * j + 1] = fma_f32x2(t1, d.y, acc[16 * c + 2 * j + 1]);
+                    }
+                  }
+                }
+              }
               ts.advance(kGemmTmemStages);
-              const uint64_t dw2 = pack_f32x2(dws[kk], dws[kk]);
-              const ulonglong2 *dx2 = reinterpret_cast<const ulonglong2 *>(dx_base + kk * kGemmTileCols * 4);
-#pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                const ulonglong2 d = dx2[j];
-                const uint64_t t0 = mul_f32x2(
-                    pack_f32x2(__int2float_rn(static_cast<int>(v0[4 * j])), __int2float_rn(static_cast<int>(v0[4 * j + 1]))),
-                    dw2);
-                const uint64_t t1 = mul_f32x2(pack_f32x2(__int2float_rn(static_cast<int>(v0[4 * j + 2])),
-                                                         __int2float_rn(static_cast<int>(v0[4 * j + 3]))),
-                                              dw2);
-                acc[2 * j] = fma_f32x2(t0, d.x, acc[2 * j]);
-                acc[2 * j + 1] = fma_f32x2(t1, d.y, acc[2 * j + 1]);
-              }
-#pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                const ulonglong2 d = dx2[8 + j];
-                const uint64_t t0 = mul_f32x2(
-                    pack_f32x2(__int2float_rn(static_cast<int>(v1[4 * j])), __int2float_rn(static_cast<int>(v1[4 * j + 1]))),
-                    dw2);
-                const uint64_t t1 = mul_f32x2(pack_f32x2(__int2float_rn(static_cast<int>(v1[4 * j + 2])),
-                                                         __int2float_rn(static_cast<int>(v1[4 * j + 3]))),
-                                              dw2);
-                acc[16 + 2 * j] = fma_f32x2(t0, d.x, acc[16 + 2 * j]);
-                acc[16 + 2 * j + 1] = fma_f32x2(t1, d.y, acc[16 + 2 * j + 1]);
-              }
             }
           }
         }
@@ -278,14 +306,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       }
       if (!ok)
         break;
-      // ---- store: this thread owns 64 consecutive outputs of one weight row
+      // ---- store: this thread owns CPW consecutive outputs of one weight row
       const uint32_t row = n0 + row_local;
       if (row < a.nr) {
         float *dst = a.s + static_cast<size_t>(row) * a.bs + m0;
-        const bool vec = (a.bs % 4 == 0) && ((reinterpret_cast<uintptr_t>(a.s) & 15u) == 0) && (m0 + 64 <= a.nc);
+        const bool vec = (a.bs % 4 == 0) && ((reinterpret_cast<uintptr_t>(a.s) & 15u) == 0) && (m0 + CPW <= a.nc);
         if (vec) {
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
+          for (int j = 0; j < CPW / 4; ++j) {
             float4 o;
             unpack_f32x2(acc[2 * j], o.x, o.y);
             unpack_f32x2(acc[2 * j + 1], o.z, o.w);
@@ -293,7 +321,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           }
         } else {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
+          for (int j = 0; j < CPW / 2; ++j) {
             float lo, hi;
             unpack_f32x2(acc[j], lo, hi);
             if (m0 + 2 * j < a.nc)

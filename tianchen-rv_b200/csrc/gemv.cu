@@ -283,14 +283,16 @@ int launch_gemv(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t
     const unsigned forced = (flags >> 8) & 0xfu;
     if (forced == 1 || forced == 2 || (forced == 4 && nc == 1))
       rps = forced;
-    while (rps > 1 && fixed + 2 * rps * row_bytes > kMaxDynamicSmem)
+    const size_t smem_cap = kMaxDynamicSmem;
+    const size_t warp_cap = kGemvMaxConsumerWarps;
+    while (rps > 1 && fixed + 2 * rps * row_bytes > smem_cap)
       rps /= 2;
     const size_t slot = rps * row_bytes;
-    if (fixed + 2 * slot <= kMaxDynamicSmem) {
-      const size_t total_slots = (kMaxDynamicSmem - fixed) / slot;
+    if (fixed + 2 * slot <= smem_cap) {
+      const size_t total_slots = (smem_cap - fixed) / slot;
       size_t nwarps, spw;
-      if (total_slots >= 2 * kGemvMaxConsumerWarps) {
-        nwarps = kGemvMaxConsumerWarps;
+      if (total_slots >= 2 * warp_cap) {
+        nwarps = warp_cap;
         spw = total_slots / nwarps;
         if (spw > kGemvMaxSlotsPerWarp)
           spw = kGemvMaxSlotsPerWarp;

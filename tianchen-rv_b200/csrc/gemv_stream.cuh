@@ -1,12 +1,13 @@
 // Decode GEMV, streaming form: s[row*bs + col] = block dot(weight row, activation column),
 // for up to 8 activation columns.  HBM-bound: the weight matrix is read exactly once.
 //
-// One persistent CTA per SM owns a contiguous range of weight rows, taken two rows at a
-// time.  Up to 16 warps each own a private ring of shared-memory slots (one slot = 1, 2 or 4
-// adjacent rows, chosen by the launcher from the rows each CTA gets) and keep it full themselves: lane 0 issues a 1-D bulk copy
+// One persistent CTA per SM owns a contiguous range of weight rows, divided evenly (to within
+// one row) among its warps.  Up to 16 warps each own a private ring of shared-memory slots
+// (one slot = up to 1, 2 or 4 adjacent rows, the maximum chosen by the launcher) and keep it
+// full themselves: lane 0 issues a 1-D bulk copy
 // (cp.async.bulk, completion counted on the slot's mbarrier) for the slot it has just
 // finished, so copy issue is spread over all warps and no warp waits for another.  Each warp
-// works on both rows of a slot at once; about 32 rows are in flight per SM, below that the
+// works on all rows of a slot at once; about 32 rows are in flight per SM, below that the
 // kernel is latency-bound.  Rows stay in the plain 18-byte (Q4_0) or 34-byte (Q8_0) block
 // format.  A lane owns PAIRS of adjacent blocks: a pair is 36 or 68 bytes, i.e. 9 or 17
 // aligned 32-bit words, and both strides are odd, so the 32 lanes of a warp read shared
@@ -189,18 +190,24 @@ __global__ void __launch_bounds__(kGemvMaxThreads, 1) gemv_stream_kernel(const G
 
   const uint32_t warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  // contiguous, balanced row range of this CTA, walked two rows (one slot) at a time;
-  // warp w takes slots w, w + nwarps, ...
+  // Contiguous, balanced row range of this CTA, split again into contiguous, balanced ranges
+  // per warp (they differ by at most one row, so no warp does a whole slot more than the
+  // others).  A warp walks its n rows in k = ceil(n / rps) slots of n/k or n/k + 1 rows.
   const uint32_t r0 = static_cast<uint32_t>(static_cast<uint64_t>(a.nr) * blockIdx.x / gridDim.x);
   const uint32_t r1 = static_cast<uint32_t>(static_cast<uint64_t>(a.nr) * (blockIdx.x + 1) / gridDim.x);
-  const uint32_t nslots = (r1 - r0 + rps - 1) / rps;
-  const uint32_t mine = warp < nslots ? (nslots - warp + nwarps - 1) / nwarps : 0;  // slots of this warp
+  const uint32_t w0 = r0 + (r1 - r0) * warp / nwarps;
+  const uint32_t wrows = r0 + (r1 - r0) * (warp + 1) / nwarps - w0;
+  const uint32_t mine = (wrows + rps - 1) / rps;  // slots of this warp
+  const uint32_t slot_rows = mine > 0 ? wrows / mine : 0, slot_extra = mine > 0 ? wrows % mine : 0;
+  // first row and row count of this warp's t-th slot
+  auto slot_row = [&](uint32_t t) { return w0 + t * slot_rows + min(t, slot_extra); };
+  auto slot_count = [&](uint32_t t) { return slot_rows + (t < slot_extra ? 1u : 0u); };
 
   // Issues the copy of this warp's t-th slot into ring position t % spw (one lane calls it).
   auto issue = [&](uint32_t t) {
     const uint32_t bar = warp * spw + t % spw;
-    const uint32_t row = r0 + (warp + t * nwarps) * rps;
-    const uint32_t rows = min(rps, r1 - row);
+    const uint32_t row = slot_row(t);
+    const uint32_t rows = slot_count(t);
     mbar_arrive_expect_tx(&full[bar], rows * a.row_bytes);
     uint8_t *dst = slots + static_cast<size_t>(bar) * slot_bytes;
     const uint8_t *src = a.vx + static_cast<size_t>(row) * a.bx;
@@ -269,9 +276,9 @@ __global__ void __launch_bounds__(kGemvMaxThreads, 1) gemv_stream_kernel(const G
       }
       return;
     }
-    const uint32_t row = r0 + (warp + t * nwarps) * rps;
+    const uint32_t row = slot_row(t);
     const uint32_t *wrow = reinterpret_cast<const uint32_t *>(slots + static_cast<size_t>(bar) * slot_bytes);
-    const uint32_t rows = min(rps, r1 - row);
+    const uint32_t rows = slot_count(t);
     // all rows of the slot are folded together (independent accumulators hide latency)
     if (rows == 4) {
       if constexpr (kCols == 1)

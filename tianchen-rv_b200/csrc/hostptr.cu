@@ -33,6 +33,7 @@ struct HostContext {
   cudaStream_t stream = nullptr;
   uint8_t *arena = nullptr;
   size_t arena_cap = 0, arena_used = 0;
+  int *error_word = nullptr;  // pinned host copy of the device error word
   std::map<const void *, ResidentWeights> weights;
 };
 
@@ -208,12 +209,14 @@ int host_matmul(bool q8_weights, size_t n, float *s, const uint8_t *vx, const ui
   else
     TCRV_CUDA_TRY(cudaMemcpy2DAsync(s, bs * sizeof(float), ds, nc * sizeof(float), nc * sizeof(float), nr,
                                     cudaMemcpyDeviceToHost, c.stream));
+  // the device error word rides back on the same stream: one synchronisation per call
+  if (c.error_word == nullptr)
+    TCRV_CUDA_TRY(cudaHostAlloc(reinterpret_cast<void **>(&c.error_word), sizeof(int), cudaHostAllocDefault));
+  TCRV_CUDA_TRY(cudaMemcpyFromSymbolAsync(c.error_word, g_device_error, sizeof(int), 0, cudaMemcpyDeviceToHost, c.stream));
   st = finish(c);
   if (st != TCRV_CUDA_OK)
     return st;
-  int word = 0;
-  TCRV_CUDA_TRY(cudaMemcpyFromSymbol(&word, g_device_error, sizeof word));
-  return word != 0 ? TCRV_CUDA_ERR_DEVICE_TIMEOUT : TCRV_CUDA_OK;
+  return *c.error_word != 0 ? TCRV_CUDA_ERR_DEVICE_TIMEOUT : TCRV_CUDA_OK;
 }
 
 // The generated kernels return void and cannot fail; a provider error ends the process
@@ -286,6 +289,9 @@ int tcrv_cuda_host_release(void) {
     (void)cudaFree(c.arena);
   c.arena = nullptr;
   c.arena_cap = c.arena_used = 0;
+  if (c.error_word)
+    (void)cudaFreeHost(c.error_word);
+  c.error_word = nullptr;
   return TCRV_CUDA_OK;
 }
 
