@@ -178,25 +178,36 @@ inline bool multiple_of(const void *p, uintptr_t m) { return reinterpret_cast<ui
 
 constexpr size_t kMmaMinCols = 6;
 
-// Ring depth of the tensor-core GEMV for a row of nb blocks, 0 if it does not fit.
+// Ring depth of the tensor-core GEMV for a row of nb blocks with `groups` 16-row groups per
+// slot, 0 if it does not fit.
 template <bool kQ8W>
-size_t mma_slots(uint32_t nb) {
+size_t mma_slots(uint32_t nb, int groups) {
   const size_t fixed = kMmaBarrierBytes + kMmaPartialBytes + static_cast<size_t>(nb) * kMmaXBytesPerBlock;
-  const size_t slot = static_cast<size_t>(kMmaRows) * kMmaChunkBlocks * WeightFormat<kQ8W>::kBlockBytes;
+  const size_t slot = static_cast<size_t>(kMmaRows * groups) * kMmaChunkBlocks * WeightFormat<kQ8W>::kBlockBytes;
   if (fixed + 2 * kMmaWarps * slot > kMaxDynamicSmem)
     return 0;
   size_t spw = (kMaxDynamicSmem - fixed) / (kMmaWarps * slot);
   return spw > kMmaMaxSlots ? kMmaMaxSlots : spw;
 }
 
+// Groups per slot: two when at least two such slots per warp fit, else one; 0 = no fit at all.
+template <bool kQ8W>
+int mma_groups(uint32_t nb) {
+  if (mma_slots<kQ8W>(nb, 2) >= 2)
+    return 2;
+  return mma_slots<kQ8W>(nb, 1) >= 2 ? 1 : 0;
+}
+
 template <bool kQ8W>
 int launch_mma(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by, size_t nr, size_t nc, size_t bx,
-               size_t bs, unsigned flags, size_t spw, cudaStream_t stream) {
+               size_t bs, unsigned flags, int slot_groups, cudaStream_t stream) {
   constexpr int WB = WeightFormat<kQ8W>::kBlockBytes;
+  const int kMmaSlotRows = kMmaRows * slot_groups;
   const uint32_t nb = static_cast<uint32_t>(n / kQK);
+  const size_t spw = mma_slots<kQ8W>(nb, slot_groups);
   CUtensorMap map;
   const int st = encode_tensor_map_2d_u16(&map, vx, static_cast<uint64_t>(nb) * WB / 2, nr, bx,
-                                          kMmaChunkBlocks * WB / 2, kMmaRows);
+                                          kMmaChunkBlocks * WB / 2, kMmaSlotRows);
   if (st != TCRV_CUDA_OK)
     return st;
   GemvMmaArgs args;
@@ -210,17 +221,21 @@ int launch_mma(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t 
   args.slots = static_cast<uint32_t>(spw);
   args.static_weights = (flags & TCRV_CUDA_FLAG_STATIC_WEIGHTS) ? 1u : 0u;
   const size_t smem = kMmaBarrierBytes + kMmaPartialBytes + static_cast<size_t>(nb) * kMmaXBytesPerBlock +
-                      spw * kMmaWarps * kMmaRows * kMmaChunkBlocks * WB;
-  auto kernel = gemv_mma_kernel<kQ8W>;
-  static bool configured[64] = {};
+                      spw * kMmaWarps * kMmaSlotRows * kMmaChunkBlocks * WB;
+  // rows of at most 16 chunks: one chunk per warp, activation fragments live in registers
+  const bool xregs = nb <= static_cast<uint32_t>(kMmaWarps * kMmaChunkBlocks);
+  auto kernel = slot_groups == 2 ? (xregs ? gemv_mma_kernel<kQ8W, true, 2> : gemv_mma_kernel<kQ8W, false, 2>)
+                                 : (xregs ? gemv_mma_kernel<kQ8W, true, 1> : gemv_mma_kernel<kQ8W, false, 1>);
+  static bool configured[64][4] = {};
   int dev = 0;
   TCRV_CUDA_TRY(cudaGetDevice(&dev));
-  if (dev < 64 && !configured[dev]) {
+  const int variant = (xregs ? 1 : 0) + (slot_groups == 2 ? 2 : 0);
+  if (dev < 64 && !configured[dev][variant]) {
     TCRV_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(kMaxDynamicSmem)));
-    configured[dev] = true;
+    configured[dev][variant] = true;
   }
-  const size_t groups = (nr + kMmaRows - 1) / kMmaRows;
+  const size_t groups = (nr + kMmaSlotRows - 1) / kMmaSlotRows;
   const int sms = sm_count();
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(groups < static_cast<size_t>(sms) ? groups : sms));
@@ -246,7 +261,7 @@ int gemv_fold_order(size_t n, size_t nc, const void *vx, size_t bx, const void *
     return TCRV_CUDA_ORDER_STRICT;
   const bool bulk = nb > 0 && nb % 8 == 0 && nc <= kGemvMaxCols && multiple_of(vx, 16) && bx % 16 == 0 &&
                     multiple_of(vy, 2) && by % 2 == 0;
-  if (bulk && nc >= kMmaMinCols && (flags & 0x1000u) == 0 && mma_slots<kQ8W>(nb) >= 2)
+  if (bulk && nc >= kMmaMinCols && (flags & 0x1000u) == 0 && mma_groups<kQ8W>(nb) > 0)
     return TCRV_CUDA_ORDER_KSPLIT16;
   return TCRV_CUDA_ORDER_LANE_PAIRS;
 }
@@ -269,9 +284,9 @@ int launch_gemv(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t
     // Many activation columns: the tensor-core kernel (measured faster from about 6 columns
     // on; flags bit 12 keeps the dp4a kernel).
     if (nc >= kMmaMinCols && (flags & 0x1000u) == 0) {
-      const size_t spw = mma_slots<kQ8W>(nb);
-      if (spw >= 2)
-        return launch_mma<kQ8W>(n, s, vx, vy, by, nr, nc, bx, bs, flags, spw, stream);
+      const int slot_groups = mma_groups<kQ8W>(nb);
+      if (slot_groups > 0)
+        return launch_mma<kQ8W>(n, s, vx, vy, by, nr, nc, bx, bs, flags, slot_groups, stream);
     }
     const size_t fixed = kGemvBarrierBytes + nc * static_cast<size_t>(gemv_xcol_bytes(nb));
     // Rows per slot: a warp folds all rows of a slot together, and more independent rows per
