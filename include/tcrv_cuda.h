@@ -110,9 +110,9 @@ int tcrv_cuda_vec_dot_q8_0_q8_0(size_t n, float *s, const uint8_t *vx, const uin
  * `tcrv_cuda_gemm_*` is the prefill path (int8 tensor-core contraction, needs a workspace).
  * fp32 order of the GEMV (all within rel 1e-5 of the sequential fold; tcrv_cuda_gemv_fold_order
  * tells which one a call uses):
- *   1..5 columns: 32 lane partials (lane l owns block pairs l, l+32, ... ascending), combined
+ *   1..3 columns: 32 lane partials (lane l owns block pairs l, l+32, ... ascending), combined
  *     by a butterfly (TCRV_CUDA_ORDER_LANE_PAIRS);
- *   6..8 columns (tensor-core kernel): the blocks are cut into chunks of 8, partial w of 16 folds chunks w, w+16,
+ *   4..8 columns (tensor-core kernel): the blocks are cut into chunks of 8, partial w of 16 folds chunks w, w+16,
  *     ... ascending, and the row is ((p_0 + p_1) + ...) + p_15 (TCRV_CUDA_ORDER_KSPLIT16);
  *   TCRV_CUDA_FLAG_STRICT_ORDER, and operands that rule out 16-byte bulk copies: sequential
  *     or lane-pair order on the generic kernel.

@@ -30,9 +30,8 @@ def restated(O, w, x, q8w, order):
     return O.gemm(w, x, q8_weights=q8w, fold=O.FOLD_FMA)
 
 
-def check_rows(O, got, w, x, q8w, order=None):
-    if order is None:  # packed, aligned operands: up to 5 columns -> lane pairs, 6..8 -> K split
-        order = 1 if (x.shape[0] < 6 or (x.shape[1] // 34) % 8 != 0) else 2
+def check_rows(O, got, w, x, q8w, order):
+    """`order` is what tcrv_cuda_gemv_fold_order reported for the call that produced `got`."""
     assert np.array_equal(got.view(np.uint32), restated(O, w, x, q8w, order).view(np.uint32))
     ref = O.gemm(w, x, q8_weights=q8w)
     err = np.abs(got - ref)
@@ -46,9 +45,14 @@ def check_rows(O, got, w, x, q8w, order=None):
                                       (131, 11008, 1), (131, 11008, 5), (64, 2048, 3)])
 def test_stream_kernel_matches_oracle(cuda, pkg, O, q8w, nr, k, nc):
     w, x = make(O, nr, k, nc, q8w, 100 + nr)
-    got = pkg.gemv(dev(cuda, w), dev(cuda, x), q8_weights=q8w).cpu().numpy()
+    wd, xd = dev(cuda, w), dev(cuda, x)
+    got = pkg.gemv(wd, xd, q8_weights=q8w).cpu().numpy()
     pkg.check_device_errors()
-    check_rows(O, got, w, x, q8w)
+    order = pkg.gemv_fold_order(wd, xd, q8_weights=q8w)
+    # up to 3 columns: lane pairs; 4..8: the tensor-core kernel's K split, except Q8_0 rows of
+    # K = 11008, whose slot rings do not fit in shared memory
+    assert order == (1 if (nc < 4 or (q8w and k == 11008)) else 2)
+    check_rows(O, got, w, x, q8w, order)
 
 
 @pytest.mark.parametrize("q8w", [False, True])
@@ -56,8 +60,11 @@ def test_stream_kernel_matches_oracle(cuda, pkg, O, q8w, nr, k, nc):
 def test_generic_kernel_ragged_shapes(cuda, pkg, O, q8w, nr, k, nc):
     # block counts that are not a multiple of 8 cannot use 16-byte bulk copies
     w, x = make(O, nr, k, nc, q8w, 200 + nr)
-    got = pkg.gemv(dev(cuda, w), dev(cuda, x), q8_weights=q8w).cpu().numpy()
-    check_rows(O, got, w, x, q8w)
+    wd, xd = dev(cuda, w), dev(cuda, x)
+    got = pkg.gemv(wd, xd, q8_weights=q8w).cpu().numpy()
+    order = pkg.gemv_fold_order(wd, xd, q8_weights=q8w)
+    assert order == 1
+    check_rows(O, got, w, x, q8w, order)
 
 
 @pytest.mark.parametrize("q8w", [False, True])
@@ -115,8 +122,9 @@ def test_padded_strides(cuda, pkg, O):
     assert st == 0
     pkg.check_device_errors()
     res = out.cpu().numpy()
-    assert L.tcrv_cuda_gemv_fold_order(0, 2048, 4, wt.data_ptr(), wt.stride(0), xt.data_ptr(), xt.stride(0), 0) == 1
-    assert np.array_equal(res[:, :4], O.gemv_lane_order(w, x)) and np.all(res[:, 4:] == -1.0)
+    order = L.tcrv_cuda_gemv_fold_order(0, 2048, 4, wt.data_ptr(), wt.stride(0), xt.data_ptr(), xt.stride(0), 0)
+    assert order == 2  # four columns, 16-byte aligned padded rows: the tensor-core kernel
+    assert np.array_equal(res[:, :4], restated(O, w, x, False, order)) and np.all(res[:, 4:] == -1.0)
 
 
 @pytest.mark.parametrize("nr,k", [(4096, 4096), (11008, 4096), (4096, 11008), (32000, 4096)])
@@ -129,11 +137,14 @@ def test_llama7b_shapes_q4_0(cuda, pkg, O, nr, k, nc):
     wf = cuda.randn((nr, k), generator=gen, device="cuda") * 0.02
     wd = pkg.quantize_q4_0(wf)
     x = O.quantize_q8_0(O.fill_normal(nc * k, 700 + nc).reshape(nc, k))
-    got = pkg.gemv(wd, dev(cuda, x)).cpu().numpy()
+    xd = dev(cuda, x)
+    got = pkg.gemv(wd, xd).cpu().numpy()
     pkg.check_device_errors()
+    order = pkg.gemv_fold_order(wd, xd)
+    assert order == (1 if nc == 1 else 2)
     rows = np.unique(np.concatenate([np.arange(0, nr, 97), np.arange(nr - 40, nr), np.arange(40)]))
     w = wd.cpu().numpy()[rows]
-    frac = check_rows(O, got[rows], w, x, False)
+    frac = check_rows(O, got[rows], w, x, False, order)
     assert frac > 0.95  # nearly all rows meet the plain relative bound
     # linearity of the integer stage in the activations' scale: doubling every activation
     # scale doubles every row exactly (fp32 scaling by 2 is exact)
@@ -153,7 +164,7 @@ def test_q8_0_gemv_config(cuda, pkg, O):
     got = pkg.gemv(wd, xd, q8_weights=True).cpu().numpy()
     pkg.check_device_errors()
     rows = np.arange(0, 11008, 43)
-    check_rows(O, got[rows], w[rows], x, True)
+    check_rows(O, got[rows], w[rows], x, True, pkg.gemv_fold_order(wd, xd, q8_weights=True))
     sums = pkg.block_sums(wd[:64], xd, q8_weights=True).cpu().numpy()
     assert np.array_equal(sums, O.block_sums(w[:64], x, True))
 
@@ -180,7 +191,7 @@ def test_tensor_core_gemv_reports_and_follows_its_order(cuda, pkg, O, q8w, nr, k
     # Q8_0 rows of K = 11008 leave no room for the slot rings: that case stays on the dp4a kernel
     assert order == (1 if (q8w and k == 11008) else 2)
     assert pkg.gemv_fold_order(wd, xd, q8_weights=q8w, flags=pkg.FLAG_STRICT_ORDER) == 0
-    assert pkg.gemv_fold_order(wd, xd[:1], q8_weights=q8w) == 1 and pkg.gemv_fold_order(wd, xd[:5], q8_weights=q8w) == 1
+    assert pkg.gemv_fold_order(wd, xd[:1], q8_weights=q8w) == 1 and pkg.gemv_fold_order(wd, xd[:3], q8_weights=q8w) == 1
     got = pkg.gemv(wd, xd, q8_weights=q8w).cpu().numpy()
     pkg.check_device_errors()
     rows = np.unique(np.concatenate([np.arange(0, nr, 37), np.arange(max(0, nr - 20), nr)]))

@@ -176,7 +176,7 @@ int launch_stream(const GemvArgs &args, uint32_t nc, int grid, size_t smem, cuda
 
 inline bool multiple_of(const void *p, uintptr_t m) { return reinterpret_cast<uintptr_t>(p) % m == 0; }
 
-constexpr size_t kMmaMinCols = 6;
+constexpr size_t kMmaMinCols = 4;
 
 // Ring depth of the tensor-core GEMV for a row of nb blocks with `groups` 16-row groups per
 // slot, 0 if it does not fit.
@@ -261,7 +261,7 @@ int gemv_fold_order(size_t n, size_t nc, const void *vx, size_t bx, const void *
     return TCRV_CUDA_ORDER_STRICT;
   const bool bulk = nb > 0 && nb % 8 == 0 && nc <= kGemvMaxCols && multiple_of(vx, 16) && bx % 16 == 0 &&
                     multiple_of(vy, 2) && by % 2 == 0;
-  if (bulk && nc >= kMmaMinCols && (flags & 0x1000u) == 0 && mma_groups<kQ8W>(nb) > 0)
+  if (bulk && (nc >= kMmaMinCols || (flags & 0x4000u) != 0) && (flags & 0x1000u) == 0 && mma_groups<kQ8W>(nb) > 0)
     return TCRV_CUDA_ORDER_KSPLIT16;
   return TCRV_CUDA_ORDER_LANE_PAIRS;
 }
@@ -281,9 +281,9 @@ int launch_gemv(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t
 
   if (!strict && nb > 0 && nb % 8 == 0 && nc <= kGemvMaxCols && multiple_of(vx, 16) && bx % 16 == 0 &&
       multiple_of(vy, 2) && by % 2 == 0) {
-    // Many activation columns: the tensor-core kernel (measured faster from about 6 columns
-    // on; flags bit 12 keeps the dp4a kernel).
-    if (nc >= kMmaMinCols && (flags & 0x1000u) == 0) {
+    // Many activation columns: the tensor-core kernel (measured faster from about 4 columns
+    // on; flags bit 12 keeps the dp4a kernel, bit 14 takes this one for any column count: tuning).
+    if ((nc >= kMmaMinCols || (flags & 0x4000u) != 0) && (flags & 0x1000u) == 0) {
       const int slot_groups = mma_groups<kQ8W>(nb);
       if (slot_groups > 0)
         return launch_mma<kQ8W>(n, s, vx, vy, by, nr, nc, bx, bs, flags, slot_groups, stream);

@@ -1,4 +1,4 @@
-// Decode GEMV for several (6..8) activation columns on the tensor cores (legacy warp-level MMA,
+// Decode GEMV for several (4..8) activation columns on the tensor cores (legacy warp-level MMA,
 // mma.sync.m16n8k32.s8: 16 weight rows x 32 K x 8 columns is exactly one ggml block of a
 // 16-row group against all columns).  With several columns the dp4a kernel is issue-bound
 // long before HBM is; here one MMA replaces 16 x 8 x 8 dp4a.
@@ -54,7 +54,7 @@ struct GemvMmaArgs {
 // c = a * b + (bias_even, bias_odd) per column pair: rows g and g+8 share the column biases.
 __device__ __forceinline__ void mma_m16n8k32_s8(int (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1,
                                                 int bias_even, int bias_odd) {
-  asm volatile(
+  asm(
       "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
       "{%10, %11, %10, %11};"
       : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
