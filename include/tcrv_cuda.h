@@ -161,6 +161,33 @@ int tcrv_cuda_gemm_q4_0_q8_0_prepared(size_t n, float *s, const void *prepared_w
                                       size_t by, size_t nr, size_t nc, size_t bs, void *workspace,
                                       size_t workspace_bytes, unsigned flags, tcrv_cuda_stream stream);
 
+/* The prepared-weights GEMM delivering its result to `ndst` (1..8) output bases of identical
+ * layout: `dst` is a HOST array of device pointers, dst[0] normally this GPU's buffer, the
+ * others peers' buffers mapped into this process (tcrv_cuda_peer_open).  This is the N-sharded
+ * prefill GEMM with the all-gather fused into the epilogue: every rank passes its weight-row
+ * slab and, for each rank's copy of the full N x M output, the address of that slab's first
+ * row; finished tiles are stored to all copies (plain stores over NVLink) while later tiles
+ * still compute.  The outputs are complete on every rank once all ranks' kernels have
+ * finished (a stream synchronisation plus a barrier between the ranks).  The reference has no
+ * multi-device form of this op (its generated kernels are single-hart); the sharding follows
+ * the row independence of lib/Conversion/RVV/RVVToEmitCBlockQuantLinear.cpp:1797-1819. */
+int tcrv_cuda_gemm_q4_0_q8_0_prepared_multi(size_t n, float *const *dst, size_t ndst, const void *prepared_weights,
+                                            const uint8_t *vy, size_t by, size_t nr, size_t nc, size_t bs,
+                                            void *workspace, size_t workspace_bytes, unsigned flags,
+                                            tcrv_cuda_stream stream);
+
+/* Device buffers that other processes on the same node can map (CUDA IPC; one process per
+ * GPU).  peer_alloc/peer_free own the memory (cudaMalloc, 256-byte aligned); peer_export fills
+ * a 64-byte handle to send to the other ranks by any host channel; peer_open maps such a
+ * handle from ANOTHER process and enables peer access lazily; peer_close unmaps it.  No
+ * counterpart in the reference. */
+#define TCRV_CUDA_PEER_HANDLE_BYTES 64
+int tcrv_cuda_peer_alloc(size_t bytes, void **ptr);
+int tcrv_cuda_peer_free(void *ptr);
+int tcrv_cuda_peer_export(const void *ptr, unsigned char *handle);
+int tcrv_cuda_peer_open(const unsigned char *handle, void **ptr);
+int tcrv_cuda_peer_close(void *ptr);
+
 /* The plain-format GEMM for callers that cannot allocate device memory.  No counterpart in
  * the reference (its kernels take every buffer from the caller and need no scratch).
  *

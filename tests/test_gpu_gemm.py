@@ -62,6 +62,41 @@ def test_gemm_prepared_weights_and_strided_output(cuda, pkg, O):
     assert np.array_equal(pkg.gemm(pw, xd).cpu().numpy(), want)
 
 
+def test_gemm_multi_destination_writes_every_copy(cuda, pkg, O):
+    # the fused all-gather epilogue, exercised on one GPU: three output bases (two aligned
+    # copies and one at an odd float offset, which forces the scalar store path for all)
+    import ctypes
+
+    w, x = make(O, 260, 1024, 150, 1200)
+    pw = pkg.PreparedWeights(dev(cuda, w))
+    xd = dev(cuda, x)
+    L = pkg.lib()
+    ws = cuda.empty(L.tcrv_cuda_gemm_acts_workspace_bytes(1024, 150), dtype=cuda.uint8, device="cuda")
+    want = O.gemm(w, x, fold=O.FOLD_FMA, threads=8)
+    for odd in (0, 1):
+        outs = [cuda.full((260 * 152 + 8,), -1.0, dtype=cuda.float32, device="cuda") for _ in range(3)]
+        bases = [outs[0].data_ptr(), outs[1].data_ptr(), outs[2].data_ptr() + 4 * odd]
+        dst = (ctypes.c_void_p * 3)(*bases)
+        st = L.tcrv_cuda_gemm_q4_0_q8_0_prepared_multi(1024, dst, 3, pw.buffer.data_ptr(), xd.data_ptr(), xd.stride(0),
+                                                       260, 150, 152, ws.data_ptr(), ws.numel(), 0,
+                                                       cuda.cuda.current_stream().cuda_stream)
+        assert st == 0
+        pkg.check_device_errors()
+        for i, o in enumerate(outs):
+            shift = odd if i == 2 else 0
+            res = o.cpu().numpy()[shift:shift + 260 * 152].reshape(260, 152)
+            assert np.array_equal(res[:, :150].view(np.uint32), want.view(np.uint32))
+            assert np.all(res[:, 150:] == -1.0)
+    # argument checks: no destinations, too many, a null base
+    assert L.tcrv_cuda_gemm_q4_0_q8_0_prepared_multi(1024, dst, 0, pw.buffer.data_ptr(), xd.data_ptr(), xd.stride(0),
+                                                     260, 150, 152, ws.data_ptr(), ws.numel(), 0, None) == -1
+    assert L.tcrv_cuda_gemm_q4_0_q8_0_prepared_multi(1024, dst, 9, pw.buffer.data_ptr(), xd.data_ptr(), xd.stride(0),
+                                                     260, 150, 152, ws.data_ptr(), ws.numel(), 0, None) == -1
+    bad = (ctypes.c_void_p * 2)(outs[0].data_ptr(), None)
+    assert L.tcrv_cuda_gemm_q4_0_q8_0_prepared_multi(1024, bad, 2, pw.buffer.data_ptr(), xd.data_ptr(), xd.stride(0),
+                                                     260, 150, 152, ws.data_ptr(), ws.numel(), 0, None) == -1
+
+
 def test_gemm_workspace_errors(cuda, pkg):
     L = pkg.lib()
     w = cuda.zeros((128, 18 * 4), dtype=cuda.uint8, device="cuda")

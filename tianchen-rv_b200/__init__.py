@@ -52,6 +52,12 @@ ABI = {
     "tcrv_cuda_gemm_q4_0_q8_0": [_sz, _p, _p, _p, _sz, _sz, _sz, _sz, _sz, _p, _sz, ctypes.c_uint, _p],
     "tcrv_cuda_gemm_q4_0_q8_0_prepared": [_sz, _p, _p, _p, _sz, _sz, _sz, _sz, _p, _sz, ctypes.c_uint, _p],
     "tcrv_cuda_gemm_q4_0_q8_0_static_scratch": [_sz, _p, _p, _p, _sz, _sz, _sz, _sz, _sz, ctypes.c_uint, _p],
+    "tcrv_cuda_gemm_q4_0_q8_0_prepared_multi": [_sz, _p, _sz, _p, _p, _sz, _sz, _sz, _sz, _p, _sz, ctypes.c_uint, _p],
+    "tcrv_cuda_peer_alloc": [_sz, _p],
+    "tcrv_cuda_peer_free": [_p],
+    "tcrv_cuda_peer_export": [_p, _p],
+    "tcrv_cuda_peer_open": [_p, _p],
+    "tcrv_cuda_peer_close": [_p],
     "tcrv_cuda_gemv_fold_order": [_i, _sz, _sz, _p, _sz, _p, _sz, ctypes.c_uint],
     "tcrv_cuda_block_sums_q4_0_q8_0": [_sz, _p, _p, _p, _sz, _sz, _sz, _sz, _p],
     "tcrv_cuda_block_sums_q8_0_q8_0": [_sz, _p, _p, _p, _sz, _sz, _sz, _sz, _p],
@@ -357,6 +363,87 @@ def row_shard(nr: int, world: int, rank: int):
         raise ValueError(f"{nr} weight rows do not split evenly over {world} ranks")
     rows = nr // world
     return rank * rows, rows
+
+
+class SharedOutput:
+    """One rank's copy of an N-sharded GEMM output that the other ranks' kernels can write.
+
+    Every rank allocates its (nr, nc) fp32 buffer with the library (CUDA IPC needs the
+    allocation's own base pointer), exchanges the 64-byte handle over torch.distributed and maps
+    the peers' buffers.  `gemm_into` then runs this rank's row shard and stores each finished
+    tile into every rank's copy; after `wait()` (stream synchronisation + barrier) all copies
+    hold all rows."""
+
+    def __init__(self, nr: int, nc: int, dist, rank: int, world: int, device):
+        import torch
+
+        self.nr, self.nc, self.rank, self.world, self.dist = nr, nc, rank, world, dist
+        own = ctypes.c_void_p()
+        _check(lib().tcrv_cuda_peer_alloc(nr * nc * 4, ctypes.byref(own)), "tcrv_cuda_peer_alloc")
+        self.own = own.value
+        handle = (ctypes.c_ubyte * 64)()
+        _check(lib().tcrv_cuda_peer_export(self.own, handle), "tcrv_cuda_peer_export")
+        handles = [None] * world
+        dist.all_gather_object(handles, bytes(handle))
+        self.bases, self._opened = [], []
+        for r in range(world):
+            if r == rank:
+                self.bases.append(self.own)
+                continue
+            ptr = ctypes.c_void_p()
+            buf = (ctypes.c_ubyte * 64).from_buffer_copy(handles[r])
+            _check(lib().tcrv_cuda_peer_open(buf, ctypes.byref(ptr)), "tcrv_cuda_peer_open")
+            self.bases.append(ptr.value)
+            self._opened.append(ptr.value)
+        self.device = device
+
+    def local(self):
+        """This rank's copy as a torch tensor (no ownership: keep the SharedOutput alive)."""
+        import torch
+
+        class _Holder:
+            pass
+
+        h = _Holder()
+        h.__cuda_array_interface__ = {"shape": (self.nr, self.nc), "typestr": "<f4", "data": (self.own, False),
+                                      "version": 2}
+        return torch.as_tensor(h, device=self.device)
+
+    def gemm_into(self, prepared, x, workspace=None):
+        """Runs rows row_shard(nr, world, rank) (the rows of `prepared`) and stores them into
+        every rank's copy."""
+        first, rows = row_shard(self.nr, self.world, self.rank)
+        if prepared.nr != rows:
+            raise ValueError("prepared weights must hold this rank's row shard")
+        n, nc, by = prepared.n, x.shape[0], x.stride(0)
+        if nc != self.nc or _rows(x, Q8_0_BLOCK) * QK != n:
+            raise ValueError("activation shape does not match the shared output")
+        if workspace is None:
+            workspace = _workspace(lib().tcrv_cuda_gemm_acts_workspace_bytes(n, nc), x.device)
+        # own copy first, then the peers in ring order so that the ranks do not all write to
+        # the same peer at once
+        order = [(self.rank + k) % self.world for k in range(self.world)]
+        dst = (ctypes.c_void_p * self.world)(*[self.bases[r] + first * self.nc * 4 for r in order])
+        _check(lib().tcrv_cuda_gemm_q4_0_q8_0_prepared_multi(n, dst, self.world, prepared.buffer.data_ptr(), x.data_ptr(),
+                                                             by, rows, nc, self.nc, workspace.data_ptr(),
+                                                             workspace.numel(), 0, _stream()),
+               "tcrv_cuda_gemm_q4_0_q8_0_prepared_multi")
+
+    def wait(self):
+        """All ranks' kernels have finished: every copy is complete."""
+        import torch
+
+        torch.cuda.current_stream().synchronize()
+        self.dist.barrier()
+
+    def close(self):
+        for ptr in self._opened:
+            lib().tcrv_cuda_peer_close(ptr)
+        self._opened = []
+        self.dist.barrier()  # nobody frees while a peer still has the buffer mapped
+        if self.own:
+            lib().tcrv_cuda_peer_free(self.own)
+            self.own = None
 
 
 def gather_row_slabs(full, dist, rank: int, world: int):

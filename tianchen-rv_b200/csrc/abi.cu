@@ -1,6 +1,7 @@
 // extern "C" surface of the provider: argument validation, status codes, error text and the
 // device-side error word.  Every function here takes device pointers and launches on the
 // caller's stream; none allocates, and none has a CPU fallback.
+#include <cstring>
 #include <stdio.h>
 #include <string.h>
 
@@ -240,6 +241,74 @@ int tcrv_cuda_gemm_q4_0_q8_0_prepared(size_t n, float *s, const void *prepared_w
     return rc;
   return launch_gemm_prepared(n, s, static_cast<const uint8_t *>(prepared_weights), acts, nr, nc, bs,
                               as_stream(stream));
+}
+
+int tcrv_cuda_gemm_q4_0_q8_0_prepared_multi(size_t n, float *const *dst, size_t ndst, const void *prepared_weights,
+                                            const uint8_t *vy, size_t by, size_t nr, size_t nc, size_t bs,
+                                            void *workspace, size_t workspace_bytes, unsigned flags,
+                                            tcrv_cuda_stream stream) {
+  (void)flags;  // the GEMM always folds in strict ascending block order
+  if (!dst || ndst == 0 || ndst > 8)
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  for (size_t d = 0; d < ndst; ++d) {
+    const int st = check_matrix_args(n, dst[d], prepared_weights, vy, by, nr, nc, static_cast<size_t>(-1), bs, 0);
+    if (st != TCRV_CUDA_OK)
+      return st;
+  }
+  if (nr == 0 || nc == 0 || n == 0) {
+    if (n == 0)
+      for (size_t d = 0; d < ndst; ++d)
+        for (size_t r = 0; r < nr; ++r)
+          TCRV_CUDA_TRY(cudaMemsetAsync(dst[d] + r * bs, 0, nc * sizeof(float), as_stream(stream)));
+    return TCRV_CUDA_OK;
+  }
+  if (!workspace || workspace_bytes < gemm_acts_bytes(n, nc) || reinterpret_cast<uintptr_t>(workspace) % 256 != 0 ||
+      reinterpret_cast<uintptr_t>(prepared_weights) % 256 != 0)
+    return TCRV_CUDA_ERR_WORKSPACE;
+  uint8_t *acts = static_cast<uint8_t *>(workspace);
+  int rc = launch_gemm_prepare_acts_q8_0(n, vy, by, nc, acts, as_stream(stream));
+  if (rc != TCRV_CUDA_OK)
+    return rc;
+  return launch_gemm_prepared_multi(n, dst, ndst, static_cast<const uint8_t *>(prepared_weights), acts, nr, nc, bs,
+                                    as_stream(stream));
+}
+
+int tcrv_cuda_peer_alloc(size_t bytes, void **ptr) {
+  if (!ptr || bytes == 0)
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  TCRV_CUDA_TRY(cudaMalloc(ptr, bytes));
+  return TCRV_CUDA_OK;
+}
+
+int tcrv_cuda_peer_free(void *ptr) {
+  if (ptr)
+    TCRV_CUDA_TRY(cudaFree(ptr));
+  return TCRV_CUDA_OK;
+}
+
+int tcrv_cuda_peer_export(const void *ptr, unsigned char *handle) {
+  static_assert(sizeof(cudaIpcMemHandle_t) == TCRV_CUDA_PEER_HANDLE_BYTES, "handle size");
+  if (!ptr || !handle)
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  cudaIpcMemHandle_t h;
+  TCRV_CUDA_TRY(cudaIpcGetMemHandle(&h, const_cast<void *>(ptr)));
+  memcpy(handle, &h, sizeof h);
+  return TCRV_CUDA_OK;
+}
+
+int tcrv_cuda_peer_open(const unsigned char *handle, void **ptr) {
+  if (!ptr || !handle)
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, sizeof h);
+  TCRV_CUDA_TRY(cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess));
+  return TCRV_CUDA_OK;
+}
+
+int tcrv_cuda_peer_close(void *ptr) {
+  if (ptr)
+    TCRV_CUDA_TRY(cudaIpcCloseMemHandle(ptr));
+  return TCRV_CUDA_OK;
 }
 
 int tcrv_cuda_gemm_q4_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by, size_t nr,

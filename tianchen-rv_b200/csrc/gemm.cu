@@ -148,8 +148,8 @@ inline int blocks_for(size_t items) {
   return static_cast<int>(b < cap ? (b ? b : 1) : cap);
 }
 
-int run_gemm(size_t n, float *s, const uint8_t *weights_planar, const uint8_t *acts_planar, size_t nr, size_t nc,
-             size_t bs, cudaStream_t stream) {
+int run_gemm(size_t n, float *const *dst, size_t ndst, const uint8_t *weights_planar, const uint8_t *acts_planar,
+             size_t nr, size_t nc, size_t bs, cudaStream_t stream) {
   const PlanarSizes p = planar_sizes(n, nr, nc);
   const int8_t *w8 = reinterpret_cast<const int8_t *>(weights_planar);
   const float *dw = reinterpret_cast<const float *>(weights_planar + p.w8);
@@ -171,8 +171,10 @@ int run_gemm(size_t n, float *s, const uint8_t *weights_planar, const uint8_t *a
   if (st != TCRV_CUDA_OK)
     return st;
 
-  GemmArgs args;
-  args.s = s;
+  GemmArgs args = {};
+  for (size_t d = 0; d < ndst; ++d)
+    args.dst[d] = dst[d];
+  args.ndst = static_cast<uint32_t>(ndst);
   args.bs = bs;
   args.nr = static_cast<uint32_t>(nr);
   args.nc = static_cast<uint32_t>(nc);
@@ -180,17 +182,26 @@ int run_gemm(size_t n, float *s, const uint8_t *weights_planar, const uint8_t *a
   args.tiles_m = static_cast<uint32_t>((nc + kGemmTileCols - 1) / kGemmTileCols);
   args.tiles = static_cast<uint32_t>((nr + kGemmTileRows - 1) / kGemmTileRows) * args.tiles_m;
 
-  static bool configured[64] = {};
+  const bool multi = ndst > 1;
+  static bool configured[64][2] = {};
   int dev = 0;
   TCRV_CUDA_TRY(cudaGetDevice(&dev));
-  if (dev < 64 && !configured[dev]) {
-    TCRV_CUDA_TRY(cudaFuncSetAttribute(gemm_q4_0_q8_0_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       static_cast<int>(kGemmSmemBytes)));
-    configured[dev] = true;
+  if (dev < 64 && !configured[dev][multi ? 1 : 0]) {
+    if (multi)
+      TCRV_CUDA_TRY(cudaFuncSetAttribute(gemm_q4_0_q8_0_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(kGemmSmemBytesMulti)));
+    else
+      TCRV_CUDA_TRY(cudaFuncSetAttribute(gemm_q4_0_q8_0_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(kGemmSmemBytesSingle)));
+    configured[dev][multi ? 1 : 0] = true;
   }
   const int sms = sm_count();
   const int grid = static_cast<int>(args.tiles < static_cast<uint32_t>(sms) ? args.tiles : sms);
-  gemm_q4_0_q8_0_tc_kernel<<<grid, kGemmThreads, kGemmSmemBytes, stream>>>(map_w, map_x, map_dw, map_dx, args);
+  if (multi)
+    gemm_q4_0_q8_0_tc_kernel<true><<<grid, kGemmThreads, kGemmSmemBytesMulti, stream>>>(map_w, map_x, map_dw, map_dx, args);
+  else
+    gemm_q4_0_q8_0_tc_kernel<false><<<grid, kGemmThreads, kGemmSmemBytesSingle, stream>>>(map_w, map_x, map_dw, map_dx,
+                                                                                         args);
   TCRV_CUDA_TRY(cudaGetLastError());
   return TCRV_CUDA_OK;
 }
@@ -252,7 +263,16 @@ int launch_gemm_prepared(size_t n, float *s, const uint8_t *weights_planar, cons
                          size_t nc, size_t bs, cudaStream_t stream) {
   if (nr == 0 || nc == 0)
     return TCRV_CUDA_OK;
-  return run_gemm(n, s, weights_planar, acts_planar, nr, nc, bs, stream);
+  return run_gemm(n, &s, 1, weights_planar, acts_planar, nr, nc, bs, stream);
+}
+
+int launch_gemm_prepared_multi(size_t n, float *const *dst, size_t ndst, const uint8_t *weights_planar,
+                               const uint8_t *acts_planar, size_t nr, size_t nc, size_t bs, cudaStream_t stream) {
+  if (ndst == 0 || ndst > static_cast<size_t>(kGemmMaxDst))
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  if (nr == 0 || nc == 0)
+    return TCRV_CUDA_OK;
+  return run_gemm(n, dst, ndst, weights_planar, acts_planar, nr, nc, bs, stream);
 }
 
 // ------------------------------------------------------------ allocation-free variant
@@ -287,7 +307,7 @@ int launch_gemm_static_scratch(size_t n, float *s, const uint8_t *vx, size_t bx,
   if (st == TCRV_CUDA_OK)
     st = launch_gemm_prepare_acts_q8_0(n, vy, by, nc, acts, stream);
   if (st == TCRV_CUDA_OK)
-    st = run_gemm(n, s, weights, acts, nr, nc, bs, stream);
+    st = run_gemm(n, &s, 1, weights, acts, nr, nc, bs, stream);
   return st;
 }
 

@@ -37,7 +37,8 @@ namespace tcrv {
 constexpr int kGemmTileRows = 128;   // weight rows per tile  (MMA M, TMEM lanes)
 constexpr int kGemmTileCols = 128;   // activation columns per tile (MMA N, TMEM columns)
 constexpr int kGemmStageBlocks = 4;  // ggml blocks per shared-memory stage (128 bytes of K)
-constexpr int kGemmSmemStages = 5;
+constexpr int kGemmSmemStagesSingle = 5;  // one output copy
+constexpr int kGemmSmemStagesMulti = 4;   // several copies: one stage's worth of room goes to the store tiles
 constexpr int kGemmHandBlocks = 2;  // ggml blocks (accumulator tiles) handed to the epilogue per barrier phase
 constexpr int kGemmTmemStages = 2;  // each stage holds kGemmHandBlocks accumulator tiles
 constexpr int kGemmTmemStageCols = kGemmHandBlocks * kGemmTileCols;  // 256
@@ -52,10 +53,23 @@ constexpr int kGemmDwBytes = kGemmTileRows * kGemmStageBlocks * 4;            //
 constexpr int kGemmDxBytes = kGemmStageBlocks * kGemmTileCols * 4;            // [4][128] fp32
 constexpr int kGemmStageBytes = kGemmABytes + kGemmBBytes + kGemmDwBytes + kGemmDxBytes;
 constexpr int kGemmCtrlBytes = 1024;  // barriers, TMEM base, abort flag
-constexpr size_t kGemmSmemBytes = kGemmCtrlBytes + static_cast<size_t>(kGemmSmemStages) * kGemmStageBytes + 1024;
+// per epilogue warp a 32 x 32 fp32 tile for the transposing output store
+constexpr int kGemmOutTileBytes = 32 * kGemmColsPerWarp * 4;
+constexpr size_t kGemmOutBytes = static_cast<size_t>(kGemmEpilogueWarps) * kGemmOutTileBytes;
+constexpr size_t kGemmSmemBytesSingle =
+    kGemmCtrlBytes + static_cast<size_t>(kGemmSmemStagesSingle) * kGemmStageBytes + 1024;
+constexpr size_t kGemmSmemBytesMulti =
+    kGemmCtrlBytes + static_cast<size_t>(kGemmSmemStagesMulti) * kGemmStageBytes + 1024 + kGemmOutBytes;
+
+constexpr int kGemmMaxDst = 8;  // copies of the output written by the epilogue (this GPU's and its peers')
 
 struct GemmArgs {
-  float *s;
+  // Output bases, all with row stride bs.  dst[0] is normally this GPU's buffer; further
+  // entries may be peers' buffers (plain st.global over NVLink): the N-sharded GEMM delivers
+  // each finished tile to every rank's copy of the full matrix, so the all-gather overlaps the
+  // remaining tiles instead of following the kernel.
+  float *dst[kGemmMaxDst];
+  uint32_t ndst;
   size_t bs;
   uint32_t nr, nc, nb;
   uint32_t tiles_m;  // column tiles
@@ -105,10 +119,14 @@ struct PipeState {
   }
 };
 
+// kMulti: the result goes to several output copies (peers); stores are transposed through
+// shared memory into full 128-byte lines.  Otherwise each lane stores its own row directly.
+template <bool kMulti>
 __global__ void __launch_bounds__(kGemmThreads, 1)
     gemm_q4_0_q8_0_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                              const __grid_constant__ CUtensorMap map_dw, const __grid_constant__ CUtensorMap map_dx,
-                             const GemmArgs a) {
+                             const __grid_constant__ GemmArgs a) {
+  constexpr int kGemmSmemStages = kMulti ? kGemmSmemStagesMulti : kGemmSmemStagesSingle;
   extern __shared__ uint8_t smem_raw[];
   // control block first, then stages on a 1024-byte boundary (required by the 128B swizzle)
   uint8_t *ctrl = smem_raw;
@@ -121,6 +139,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   volatile uint32_t *abort_flag = tmem_base_slot + 1;
   const uint32_t stage_base_addr = (smem_addr(smem_raw) + kGemmCtrlBytes + 1023u) & ~1023u;
   uint8_t *stages = smem_raw + (stage_base_addr - smem_addr(smem_raw));
+  uint8_t *out_tiles = stages + static_cast<size_t>(kGemmSmemStages) * kGemmStageBytes;  // 1024-byte aligned
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t nkb = (a.nb + kGemmStageBlocks - 1) / kGemmStageBlocks;
@@ -306,20 +325,56 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       }
       if (!ok)
         break;
-      // ---- store: this thread owns CPW consecutive outputs of one weight row
+      // ---- store: this thread owns CPW consecutive outputs of one weight row, written to
+      // every destination
       const uint32_t row = n0 + row_local;
-      if (row < a.nr) {
-        float *dst = a.s + static_cast<size_t>(row) * a.bs + m0;
-        const bool vec = (a.bs % 4 == 0) && ((reinterpret_cast<uintptr_t>(a.s) & 15u) == 0) && (m0 + CPW <= a.nc);
-        if (vec) {
+      bool vec = (a.bs % 4 == 0) && (m0 + CPW <= a.nc);  // warp-uniform
+      for (uint32_t d = 0; d < a.ndst; ++d)
+        vec = vec && ((reinterpret_cast<uintptr_t>(a.dst[d]) & 15u) == 0);
+      if (kMulti && vec) {
+        // Transposing store: a lane holds one row's 32 columns (one 128-byte line), but a store
+        // instruction in which every lane writes 16 bytes of a different line reaches a peer as
+        // 32 small writes.  The warp's 32 x 32 tile goes through shared memory (16-byte units
+        // swizzled by the row, conflict-free both ways) so that each instruction writes 4 rows
+        // x 128 contiguous bytes.
+        float4 *tile = reinterpret_cast<float4 *>(out_tiles + static_cast<size_t>(warp) * kGemmOutTileBytes);
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < CPW / 4; ++j) {
+          float4 o;
+          unpack_f32x2(acc[2 * j], o.x, o.y);
+          unpack_f32x2(acc[2 * j + 1], o.z, o.w);
+          tile[lane * (CPW / 4) + (j ^ (lane & 7))] = o;
+        }
+        __syncwarp();
+        const int sub = lane >> 3, unit = lane & 7;  // row within a group of 4, 16-byte unit of the line
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int r = 4 * i + sub;
+          const float4 o = tile[r * (CPW / 4) + (unit ^ (r & 7))];
+          const uint32_t grow = n0 + quarter * 32 + r;
+          if (grow < a.nr) {
+            const size_t off4 = (static_cast<size_t>(grow) * a.bs + m0) / 4 + unit;
+            for (uint32_t d = 0; d < a.ndst; ++d)
+              reinterpret_cast<float4 *>(a.dst[d])[off4] = o;
+          }
+        }
+      } else if (vec) {
+        if (row < a.nr) {
+          float4 *dst = reinterpret_cast<float4 *>(a.dst[0] + static_cast<size_t>(row) * a.bs + m0);
 #pragma unroll
           for (int j = 0; j < CPW / 4; ++j) {
             float4 o;
             unpack_f32x2(acc[2 * j], o.x, o.y);
             unpack_f32x2(acc[2 * j + 1], o.z, o.w);
-            reinterpret_cast<float4 *>(dst)[j] = o;
+            dst[j] = o;
           }
-        } else {
+        }
+      } else if (row < a.nr) {
+        // ragged columns or unaligned bases: this lane writes its row element by element
+        const size_t off = static_cast<size_t>(row) * a.bs + m0;
+        for (uint32_t d = 0; d < a.ndst; ++d) {
+          float *dst = a.dst[d] + off;
 #pragma unroll
           for (int j = 0; j < CPW / 2; ++j) {
             float lo, hi;

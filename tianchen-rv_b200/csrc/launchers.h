@@ -39,6 +39,10 @@ int launch_gemm_static_scratch(size_t n, float *s, const uint8_t *vx, size_t bx,
                                size_t nr, size_t nc, size_t bs, cudaStream_t stream);
 int launch_gemm_prepared(size_t n, float *s, const uint8_t *weights_planar, const uint8_t *acts_planar, size_t nr,
                          size_t nc, size_t bs, cudaStream_t stream);
+// The same GEMM writing its result to `ndst` (1..8) output bases of equal layout, e.g. every
+// rank's copy of an N-sharded output (peer pointers).
+int launch_gemm_prepared_multi(size_t n, float *const *dst, size_t ndst, const uint8_t *weights_planar,
+                               const uint8_t *acts_planar, size_t nr, size_t nc, size_t bs, cudaStream_t stream);
 }  // namespace tcrv
 
 namespace tcrv {
