@@ -161,6 +161,35 @@ int tcrv_cuda_gemm_q4_0_q8_0_prepared(size_t n, float *s, const void *prepared_w
                                       size_t by, size_t nr, size_t nc, size_t bs, void *workspace,
                                       size_t workspace_bytes, unsigned flags, tcrv_cuda_stream stream);
 
+/* ---- f32 forward-pass ops the reference compiles next to the quantized matmul ----------
+ * Bit-exact with the reference's arithmetic (every operation IEEE round-to-nearest, nothing
+ * fused that the reference does not fuse); see each entry for the one exception. */
+
+/* y[i] *= v in place.  Replaces tcrv_rvv.ggml_vec_scale_f32
+ * (lib/Conversion/RVV/RVVToEmitCForwardElementwise.cpp:29-135); ABI order n, y, v. */
+int tcrv_cuda_vec_scale_f32(size_t n, float *y, float v, tcrv_cuda_stream stream);
+
+/* y[i] = x[i] / (1 + exp(-x[i])) with the reference's exp polynomial, node for node
+ * (RVVToEmitCForwardElementwise.cpp:363-498 and :501-609); ABI order n, x, y. */
+int tcrv_cuda_vec_silu_f32(size_t n, const float *x, float *y, tcrv_cuda_stream stream);
+
+/* RMS norm of `nrows` rows of ne00 floats (row strides in floats; the reference's kernel is
+ * the nrows = 1 case, ABI order ne00, x, y, eps): sum of the f32-rounded squares in double,
+ * mean = (float)(sum / ne00), scale = 1.0f / sqrtf(mean + eps), y = x * scale
+ * (RVVToEmitCForwardElementwise.cpp:136-361).  The double sum is a fixed tree instead of the
+ * reference's ascending chain; the two agree bit for bit whenever the sum is exact in double
+ * (exponent spread of the squares + log2(ne00) <= 29 bits) and otherwise differ by less than
+ * one part in 2^50 before the result is rounded to f32. */
+int tcrv_cuda_rms_norm_f32(size_t ne00, const float *x, float *y, float eps, size_t nrows, size_t x_stride,
+                           size_t y_stride, tcrv_cuda_stream stream);
+
+/* y[i] = exp(x[i] - max) (same polynomial) and, when `sum` is not null, *sum = f64 sum of
+ * the y (device pointer).  Replaces tcrv_rvv.ggml_vec_soft_max_f32, whose function returns
+ * that sum (RVVToEmitCForwardElementwise.cpp:611-750); ABI order n, y, x, max.  The reference
+ * folds the sum with an unordered vector reduction, so only its value up to f64 rounding is
+ * defined; the y are bit-exact. */
+int tcrv_cuda_vec_soft_max_f32(size_t n, float *y, const float *x, float max, double *sum, tcrv_cuda_stream stream);
+
 /* The prepared-weights GEMM delivering its result to `ndst` (1..8) output bases of identical
  * layout: `dst` is a HOST array of device pointers, dst[0] normally this GPU's buffer, the
  * others peers' buffers mapped into this process (tcrv_cuda_peer_open).  This is the N-sharded

@@ -57,6 +57,13 @@ def _declare(L: ctypes.CDLL) -> None:
     L.tcrv_oracle_fp16_to_fp32.restype = ctypes.c_float
     L.tcrv_oracle_fp32_to_fp16.argtypes = [ctypes.c_float]
     L.tcrv_oracle_fp32_to_fp16.restype = ctypes.c_uint16
+    L.tcrv_oracle_vec_scale_f32.argtypes = [_sz, _p, ctypes.c_float]
+    L.tcrv_oracle_rms_norm_f32.argtypes = [_sz, _p, _p, ctypes.c_float]
+    L.tcrv_oracle_expf.argtypes = [ctypes.c_float]
+    L.tcrv_oracle_expf.restype = ctypes.c_float
+    L.tcrv_oracle_vec_silu_f32.argtypes = [_sz, _p, _p]
+    L.tcrv_oracle_vec_soft_max_f32.argtypes = [_sz, _p, _p, ctypes.c_float]
+    L.tcrv_oracle_vec_soft_max_f32.restype = ctypes.c_double
     L.tcrv_oracle_fill_uniform.argtypes = [_p, _sz, ctypes.c_uint64, ctypes.c_float, ctypes.c_float]
     L.tcrv_oracle_fill_normal.argtypes = [_p, _sz, ctypes.c_uint64, ctypes.c_float, ctypes.c_float]
     L.tcrv_oracle_add_f32.argtypes = [_p, _p, _p, _sz]
@@ -167,6 +174,39 @@ def dequantize_q4_0(q: np.ndarray) -> np.ndarray:
     out = np.empty(q.shape[:-1] + (q.shape[-1] // Q4_0_BLOCK * QK,), dtype=np.float32)
     lib().tcrv_oracle_dequantize_row_q4_0(_ptr(q), _ptr(out), out.size)
     return out
+
+
+def vec_scale_f32(y: np.ndarray, v: float) -> np.ndarray:
+    out = np.ascontiguousarray(y, dtype=np.float32).copy()
+    lib().tcrv_oracle_vec_scale_f32(out.size, _ptr(out), ctypes.c_float(v))
+    return out
+
+
+def rms_norm_f32(x: np.ndarray, eps: float) -> np.ndarray:
+    """Row-wise (last dimension) RMS norm of a 1-D or 2-D array."""
+    x2 = np.ascontiguousarray(x, dtype=np.float32).reshape(-1, x.shape[-1])
+    out = np.empty_like(x2)
+    for r in range(x2.shape[0]):
+        lib().tcrv_oracle_rms_norm_f32(x2.shape[1], _ptr(x2[r]), _ptr(out[r]), ctypes.c_float(eps))
+    return out.reshape(x.shape)
+
+
+def expf(x: float) -> np.float32:
+    return np.float32(lib().tcrv_oracle_expf(ctypes.c_float(x)))
+
+
+def vec_silu_f32(x: np.ndarray) -> np.ndarray:
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    out = np.empty_like(x)
+    lib().tcrv_oracle_vec_silu_f32(x.size, _ptr(x), _ptr(out))
+    return out
+
+
+def vec_soft_max_f32(x: np.ndarray, max_value: float):
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    out = np.empty_like(x)
+    total = lib().tcrv_oracle_vec_soft_max_f32(x.size, _ptr(out), _ptr(x), ctypes.c_float(max_value))
+    return out, float(total)
 
 
 def decode_nibbles(byte: int) -> tuple[int, int]:

@@ -471,3 +471,72 @@ void tcrv_oracle_gemm_abs_terms(size_t n, float *s, const uint8_t *vx, const uin
     }
   }
 }
+
+/* ---- forward-pass f32 ops --------------------------------------------------------------- */
+
+void tcrv_oracle_vec_scale_f32(size_t n, float *y, float v) {
+  for (size_t i = 0; i < n; ++i)
+    y[i] = y[i] * v;
+}
+
+void tcrv_oracle_rms_norm_f32(size_t n, const float *x, float *y, float eps) {
+  double sum = 0.0;
+  for (size_t i = 0; i < n; ++i) {
+    const float p = x[i] * x[i]; /* the f32 product rounds before it is widened */
+    sum = sum + (double)p;
+  }
+  const float mean = (float)(sum / (double)n);
+  const float scale = 1.0f / sqrtf(mean + eps);
+  for (size_t i = 0; i < n; ++i)
+    y[i] = x[i] * scale;
+}
+
+static float bits_to_float(uint32_t u) {
+  float f;
+  memcpy(&f, &u, sizeof f);
+  return f;
+}
+
+static uint32_t float_to_bits(float f) {
+  uint32_t u;
+  memcpy(&u, &f, sizeof u);
+  return u;
+}
+
+float tcrv_oracle_expf(float x) {
+  const float r = 0x1.8p23f;
+  const float z = fmaf(0x1.715476p+0f, x, r);
+  const float n = z - r;
+  const float b = fmaf(-0x1.7f7d1cp-20f, n, fmaf(-0x1.62e4p-1f, n, x));
+  const uint32_t e = float_to_bits(z) << 23;
+  const float k = bits_to_float(e + 0x3f800000u);
+  const int c = fabsf(n) > 126.0f;
+  const float u = b * b;
+  const float j_outer = b * 0x1.ffffecp-1f;
+  const float j_a = fmaf(0x1.555e66p-3f, b, 0x1.fffdb6p-2f);
+  const float j_b = fmaf(0x1.0e4020p-7f, b, 0x1.573e2ep-5f);
+  const float j_mid = fmaf(j_b, u, j_a);
+  const float j = fmaf(j_mid, u, j_outer);
+  const uint32_t d = (n <= 0.0f) ? 0x82000000u : 0u;
+  const float s1 = bits_to_float(d + 0x7f000000u);
+  const float s2 = bits_to_float(e - d);
+  const float r_fast = fmaf(k, j, k);
+  const float r_slow = fmaf(s2, j, s2) * s1;
+  const float r1 = c ? r_slow : r_fast;
+  return (fabsf(n) > 192.0f) ? s1 * s1 : r1;
+}
+
+void tcrv_oracle_vec_silu_f32(size_t n, const float *x, float *y) {
+  for (size_t i = 0; i < n; ++i)
+    y[i] = x[i] / (tcrv_oracle_expf(-x[i]) + 1.0f);
+}
+
+double tcrv_oracle_vec_soft_max_f32(size_t n, float *y, const float *x, float max) {
+  double sum = 0.0;
+  for (size_t i = 0; i < n; ++i) {
+    const float v = tcrv_oracle_expf(x[i] - max);
+    y[i] = v;
+    sum += (double)v;
+  }
+  return sum;
+}

@@ -63,6 +63,34 @@ void tcrv_oracle_quantize_row_q8_0(const float *x, uint8_t *vy, size_t n);
  * to 15, element j in the low nibble of byte j and element j+16 in the high nibble. */
 void tcrv_oracle_quantize_row_q4_0(const float *x, uint8_t *vx, size_t n);
 
+/* ---- forward-pass f32 ops next to the quantized matmul -------------------------------- */
+
+/* tcrv_rvv.ggml_vec_scale_f32, y[i] *= v in place (one f32 multiply per element):
+ * lib/Conversion/RVV/RVVToEmitCForwardElementwise.cpp:29-135. */
+void tcrv_oracle_vec_scale_f32(size_t n, float *y, float v);
+
+/* tcrv_rvv.ggml_rms_norm_f32 for one row: sum += (double)(x[i]*x[i]) ascending (the f32
+ * product rounds first), mean = (float)(sum / (double)n), scale = 1.0f / sqrtf(mean + eps),
+ * y[i] = x[i] * scale: RVVToEmitCForwardElementwise.cpp:136-361 (fold :222-243, mean :251-258,
+ * scale :260-276). */
+void tcrv_oracle_rms_norm_f32(size_t n, const float *x, float *y, float eps);
+
+/* The exp polynomial both silu and soft_max use, node for node as the reference emits it
+ * (RVVToEmitCForwardElementwise.cpp:363-498): range reduction with the 0x1.8p23f shifter,
+ * degree-5 polynomial in fused multiply-adds, exponent rebuilt with integer adds, the
+ * |n| > 126 and |n| > 192 merges evaluated unconditionally. */
+float tcrv_oracle_expf(float x);
+
+/* tcrv_rvv.ggml_vec_silu_f32, y[i] = x[i] / (1.0f + expf(-x[i])):
+ * RVVToEmitCForwardElementwise.cpp:501-609 (neg, exp, +1, divide at :585-598). */
+void tcrv_oracle_vec_silu_f32(size_t n, const float *x, float *y);
+
+/* tcrv_rvv.ggml_vec_soft_max_f32: y[i] = expf(x[i] - max), returns the f64 sum of the y
+ * (RVVToEmitCForwardElementwise.cpp:611-750).  The reference folds each strip with an
+ * UNORDERED widening reduction, so the sum's association is not fixed by the reference; this
+ * restatement adds in ascending order. */
+double tcrv_oracle_vec_soft_max_f32(size_t n, float *y, const float *x, float max);
+
 /* Block dequantisation y = d * q.  Per element this is the i32->f32 dequantize math
  * (RVVToEmitC.cpp:3347-3394) with d read from the block header. */
 void tcrv_oracle_dequantize_row_q8_0(const uint8_t *vx, float *y, size_t n);

@@ -161,3 +161,90 @@ def test_dequant_round_trip_bounds(O):
     # idempotence: re-quantising dequantised Q8_0 data reproduces the quants
     again = O.quantize_q8_0(O.dequantize_q8_0(q8))
     assert np.array_equal(again.reshape(-1, 34)[:, 2:], q8.reshape(-1, 34)[:, 2:])
+
+
+# ---------------------------------------------------------------- forward-pass f32 ops
+
+
+def _round_fraction_to_f32(q):
+    """Correctly rounded float32 of an exact rational (ties to even)."""
+    from fractions import Fraction
+
+    if q == 0:
+        return np.float32(0.0)
+    d = float(q)  # correctly rounded to float64
+    f = np.float32(d)
+    # repair a double rounding: compare the exact value with f's neighbours
+    lo, hi = np.nextafter(f, np.float32(-np.inf)), np.nextafter(f, np.float32(np.inf))
+    best = min((lo, f, hi), key=lambda c: (abs(Fraction(float(c)) - q), int(np.float32(c).view(np.uint32)) & 1))
+    return np.float32(best)
+
+
+def _fma32(a, b, c):
+    from fractions import Fraction
+
+    return _round_fraction_to_f32(Fraction(float(a)) * Fraction(float(b)) + Fraction(float(c)))
+
+
+def _expf_restated(x):
+    """The reference's exp chain (RVVToEmitCForwardElementwise.cpp:363-498) in exact rational
+    arithmetic with explicit float32 roundings: an independent check of the C restatement."""
+    f = np.float32
+    r = f(float.fromhex("0x1.8p23"))
+    z = _fma32(f(float.fromhex("0x1.715476p+0")), x, r)
+    n = f(z - r)
+    b = _fma32(f(-float.fromhex("0x1.7f7d1cp-20")), n, _fma32(f(-float.fromhex("0x1.62e4p-1")), n, x))
+    e = (int(z.view(np.uint32)) << 23) & 0xFFFFFFFF
+    k = np.uint32((e + 0x3F800000) & 0xFFFFFFFF).view(np.float32)
+    u = f(b * b)
+    j_outer = f(b * f(float.fromhex("0x1.ffffecp-1")))
+    j_a = _fma32(f(float.fromhex("0x1.555e66p-3")), b, f(float.fromhex("0x1.fffdb6p-2")))
+    j_b = _fma32(f(float.fromhex("0x1.0e4020p-7")), b, f(float.fromhex("0x1.573e2ep-5")))
+    j = _fma32(_fma32(j_b, u, j_a), u, j_outer)
+    d = 0x82000000 if n <= 0 else 0
+    s1 = np.uint32((d + 0x7F000000) & 0xFFFFFFFF).view(np.float32)
+    s2 = np.uint32((e - d) & 0xFFFFFFFF).view(np.float32)
+    if abs(n) > 192:
+        with np.errstate(over="ignore", under="ignore"):
+            return f(s1 * s1)
+    if abs(n) > 126:
+        with np.errstate(over="ignore", under="ignore"):
+            return f(_fma32(s2, j, s2) * s1)
+    return _fma32(k, j, k)
+
+
+def test_expf_chain_matches_exact_restatement_and_libm(O):
+    xs = np.concatenate([np.linspace(-104, 89, 97), [0.0, -0.0, 1e-30, -1e-30, 87.5, -87.5, -103.9, 88.7]])
+    for x in xs.astype(np.float32):
+        got = O.expf(float(x))
+        assert got.view(np.uint32) == _expf_restated(np.float32(x)).view(np.uint32), float(x)
+    # accuracy: within 2 ulp of the correctly rounded exponential over the normal range
+    for x in np.linspace(-87, 88, 701).astype(np.float32):
+        want = np.float32(np.exp(np.float64(x)))
+        assert abs(int(O.expf(float(x)).view(np.int32)) - int(want.view(np.int32))) <= 2
+    assert O.expf(0.0) == 1.0 and O.expf(float("-inf")) == 0.0 and O.expf(-200.0) == 0.0
+    assert np.isinf(O.expf(200.0)) and np.isinf(O.expf(float("inf")))
+
+
+def test_forward_ops_hand_cases(O):
+    # scale: one multiply per element
+    y = O.vec_scale_f32(np.array([1.5, -2.0, 3.0e38, 0.1], np.float32), 2.0)
+    assert np.array_equal(y[:2], np.array([3.0, -4.0], np.float32)) and np.isinf(y[2]) and y[3] == np.float32(0.1) * 2
+    # rms_norm of (3, 4): sum = 25, mean = 12.5, scale = 1/sqrt(12.5 + eps)
+    x = np.array([3.0, 4.0], np.float32)
+    eps = np.float32(1e-6)
+    scale = np.float32(1.0) / np.sqrt(np.float32(12.5) + eps, dtype=np.float32)
+    assert np.array_equal(O.rms_norm_f32(x, float(eps)), x * scale)
+    # the squares are rounded to f32 BEFORE they are widened: x = 1 + 2^-12 squares to
+    # 1 + 2^-11 + 2^-24, which f32 rounds (ties to even) to 1 + 2^-11
+    t = np.float32(1.0 + 2.0 ** -12)
+    got = O.rms_norm_f32(np.array([t], np.float32), 0.0)
+    mean = np.float32(np.float64(np.float32(t * t)))
+    assert got[0] == t * (np.float32(1.0) / np.sqrt(mean, dtype=np.float32))
+    # silu and soft_max on a few points
+    assert O.vec_silu_f32(np.array([0.0], np.float32))[0] == 0.0
+    s = O.vec_silu_f32(np.array([1.0, -1.0, 30.0, -30.0], np.float32))
+    assert np.allclose(s, [0.7310586, -0.26894143, 30.0, -2.8e-12], rtol=1e-6, atol=1e-13)
+    y, total = O.vec_soft_max_f32(np.array([1.0, 2.0, 3.0, -np.inf], np.float32), 3.0)
+    assert y[2] == 1.0 and y[3] == 0.0 and abs(total - (np.exp(-2.0) + np.exp(-1.0) + 1.0)) < 1e-6
+    assert total == float(np.float64(y[0]) + np.float64(y[1]) + np.float64(y[2]) + np.float64(y[3]))

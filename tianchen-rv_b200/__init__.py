@@ -53,6 +53,10 @@ ABI = {
     "tcrv_cuda_gemm_q4_0_q8_0_prepared": [_sz, _p, _p, _p, _sz, _sz, _sz, _sz, _p, _sz, ctypes.c_uint, _p],
     "tcrv_cuda_gemm_q4_0_q8_0_static_scratch": [_sz, _p, _p, _p, _sz, _sz, _sz, _sz, _sz, ctypes.c_uint, _p],
     "tcrv_cuda_gemm_q4_0_q8_0_prepared_multi": [_sz, _p, _sz, _p, _p, _sz, _sz, _sz, _sz, _p, _sz, ctypes.c_uint, _p],
+    "tcrv_cuda_vec_scale_f32": [_sz, _p, ctypes.c_float, _p],
+    "tcrv_cuda_vec_silu_f32": [_sz, _p, _p, _p],
+    "tcrv_cuda_rms_norm_f32": [_sz, _p, _p, ctypes.c_float, _sz, _sz, _sz, _p],
+    "tcrv_cuda_vec_soft_max_f32": [_sz, _p, _p, ctypes.c_float, _p, _p],
     "tcrv_cuda_peer_alloc": [_sz, _p],
     "tcrv_cuda_peer_free": [_p],
     "tcrv_cuda_peer_export": [_p, _p],
@@ -346,6 +350,53 @@ def gemm(w, x, out=None, workspace=None):
                                           out.stride(0), workspace.data_ptr(), workspace.numel(), 0, _stream()),
            "tcrv_cuda_gemm_q4_0_q8_0")
     return out
+
+
+# ------------------------------------------------------------------ f32 forward-pass ops
+
+
+def vec_scale_(y, v: float):
+    """y *= v in place."""
+    import torch
+
+    _check(lib().tcrv_cuda_vec_scale_f32(y.numel(), _dev(y, torch.float32), v, _stream()),
+           "tcrv_cuda_vec_scale_f32")
+    return y
+
+
+def vec_silu(x, out=None):
+    import torch
+
+    if out is None:
+        out = torch.empty_like(x)
+    _check(lib().tcrv_cuda_vec_silu_f32(x.numel(), _dev(x, torch.float32), _dev(out, torch.float32), _stream()), "tcrv_cuda_vec_silu_f32")
+    return out
+
+
+def rms_norm(x, eps: float, out=None):
+    """RMS norm over the last dimension of a 2-D (rows, ne00) tensor (row strides honoured)."""
+    import torch
+
+    if x.dim() != 2 or x.stride(1) != 1 or x.dtype != torch.float32 or not x.is_cuda:
+        raise ValueError("x must be a 2-D float32 CUDA tensor with unit inner stride")
+    if out is None:
+        out = torch.empty((x.shape[0], x.shape[1]), dtype=torch.float32, device=x.device)
+    _check(lib().tcrv_cuda_rms_norm_f32(x.shape[1], x.data_ptr(), out.data_ptr(), eps, x.shape[0], x.stride(0),
+                                        out.stride(0), _stream()), "tcrv_cuda_rms_norm_f32")
+    return out
+
+
+def vec_soft_max(x, max_value: float, out=None):
+    """(y, sum): y = exp(x - max_value), sum = float64 sum of y as a 1-element CUDA tensor."""
+    import torch
+
+    if out is None:
+        out = torch.empty_like(x)
+    total = torch.empty(1, dtype=torch.float64, device=x.device)
+    _check(lib().tcrv_cuda_vec_soft_max_f32(x.numel(), _dev(out, torch.float32), _dev(x, torch.float32), max_value,
+                                            total.data_ptr(), _stream()),
+           "tcrv_cuda_vec_soft_max_f32")
+    return out, total
 
 
 # ------------------------------------------------------------------ N-sharding (multi-GPU GEMM)

@@ -273,6 +273,33 @@ int tcrv_cuda_gemm_q4_0_q8_0_prepared_multi(size_t n, float *const *dst, size_t 
                                     as_stream(stream));
 }
 
+int tcrv_cuda_vec_scale_f32(size_t n, float *y, float v, tcrv_cuda_stream stream) {
+  if (n != 0 && !y)
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  return launch_vec_scale_f32(n, y, v, as_stream(stream));
+}
+
+int tcrv_cuda_vec_silu_f32(size_t n, const float *x, float *y, tcrv_cuda_stream stream) {
+  if (n != 0 && (!x || !y))
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  return launch_vec_silu_f32(n, x, y, as_stream(stream));
+}
+
+int tcrv_cuda_rms_norm_f32(size_t ne00, const float *x, float *y, float eps, size_t nrows, size_t x_stride,
+                           size_t y_stride, tcrv_cuda_stream stream) {
+  if (ne00 == 0 || nrows == 0)
+    return TCRV_CUDA_OK;
+  if (!x || !y || (nrows > 1 && (x_stride < ne00 || y_stride < ne00)))
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  return launch_rms_norm_f32(ne00, x, y, eps, nrows, x_stride, y_stride, as_stream(stream));
+}
+
+int tcrv_cuda_vec_soft_max_f32(size_t n, float *y, const float *x, float max, double *sum, tcrv_cuda_stream stream) {
+  if (n != 0 && (!x || !y))
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  return launch_vec_soft_max_f32(n, y, x, max, sum, as_stream(stream));
+}
+
 int tcrv_cuda_peer_alloc(size_t bytes, void **ptr) {
   if (!ptr || bytes == 0)
     return TCRV_CUDA_ERR_INVALID_ARGUMENT;

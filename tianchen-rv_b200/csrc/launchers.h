@@ -10,6 +10,12 @@ namespace tcrv {
 
 int launch_add_f32(const float *lhs, const float *rhs, float *out, size_t n, cudaStream_t stream);
 int launch_add_i32(const int32_t *lhs, const int32_t *rhs, int32_t *out, size_t n, cudaStream_t stream);
+// forward-pass f32 ops (forward.cu)
+int launch_vec_scale_f32(size_t n, float *y, float v, cudaStream_t stream);
+int launch_vec_silu_f32(size_t n, const float *x, float *y, cudaStream_t stream);
+int launch_rms_norm_f32(size_t n, const float *x, float *y, float eps, size_t nrows, size_t x_stride, size_t y_stride,
+                        cudaStream_t stream);
+int launch_vec_soft_max_f32(size_t n, float *y, const float *x, float max, double *sum, cudaStream_t stream);
 int launch_dequantize_i32_f32(const int32_t *lhs, float scale, float *out, size_t n, cudaStream_t stream);
 int launch_dequantize_row_q8_0(const uint8_t *vx, float *y, size_t n, cudaStream_t stream);
 int launch_dequantize_row_q4_0(const uint8_t *vx, float *y, size_t n, cudaStream_t stream);
