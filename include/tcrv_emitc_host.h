@@ -31,6 +31,11 @@ int tcrv_cuda_host_add_f32(const float *lhs, const float *rhs, float *out, size_
 int tcrv_cuda_host_add_i32(const int32_t *lhs, const int32_t *rhs, int32_t *out, size_t n);
 int tcrv_cuda_host_dequantize_i32_f32(const int32_t *lhs, float scale, float *out, size_t n);
 int tcrv_cuda_host_quantize_row_q8_0(size_t n, const float *x, uint8_t *vy);
+/* f32 forward-pass ops (one vector per call, as the reference's kernels) */
+int tcrv_cuda_host_vec_scale_f32(size_t n, float *y, float v);
+int tcrv_cuda_host_rms_norm_f32(size_t ne00, const float *x, float *y, float eps);
+int tcrv_cuda_host_vec_silu_f32(size_t n, const float *x, float *y);
+int tcrv_cuda_host_vec_soft_max_f32(size_t n, float *y, const float *x, float max, double *sum);
 /* nc <= 8 runs the decode GEMV, larger nc the tensor-core GEMM. */
 int tcrv_cuda_host_gemm_q4_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by, size_t nr,
                                   size_t nc, size_t bx, size_t bs);
@@ -53,6 +58,14 @@ void tcrv_emitc_explicit_selected_body_dequantize_i32_to_f32_kernel_explicit_sel
     const int32_t *lhs, float scale, float *out, size_t n);
 /* test/Conversion/RVV/rvv-to-emitc-ggml-quantize-row-q8-0.mlir:40 */
 void tcrv_emitc_quantize_row_q8_0_kernel_quantize_row_q8_0(size_t n, const float *x, uint8_t *vy);
+/* test/Conversion/RVV/rvv-to-emitc-ggml-vec-scale-f32.mlir:37 */
+void tcrv_emitc_ggml_vec_scale_f32_kernel_ggml_vec_scale_f32(size_t n, float *y, float v);
+/* test/Conversion/RVV/rvv-to-emitc-ggml-rms-norm-f32.mlir:48 */
+void tcrv_emitc_ggml_rms_norm_f32_kernel_ggml_rms_norm_f32(size_t ne00, const float *x, float *y, float eps);
+/* test/Conversion/RVV/rvv-to-emitc-ggml-vec-silu-f32.mlir:39 */
+void tcrv_emitc_ggml_vec_silu_f32_kernel_ggml_vec_silu_f32(size_t n, const float *x, float *y);
+/* test/Conversion/RVV/rvv-to-emitc-ggml-vec-soft-max-f32.mlir:47-48: returns the f64 sum */
+double tcrv_emitc_ggml_vec_soft_max_f32_kernel_ggml_vec_soft_max_f32(size_t n, float *y, const float *x, float max);
 /* test/Conversion/RVV/rvv-to-emitc-q4-0-q8-0-block-dot.mlir:44 */
 void tcrv_emitc_ggml_vec_dot_q4_0_q8_0_kernel_ggml_vec_dot_q4_0_q8_0(size_t n, float *s, size_t bs, const uint8_t *vx,
                                                                      size_t bx, const uint8_t *vy, size_t by,

@@ -51,6 +51,14 @@ PROTOTYPES = {
         "const int32_t *lhs, float scale, float *out, size_t n);",
     "cuda-quantize-row-q8-0.mlir": "void tcrv_emitc_quantize_row_q8_0_kernel_quantize_row_q8_0("
                                    "size_t n, const float *x, uint8_t *vy);",
+    "cuda-ggml-vec-scale-f32.mlir": "void tcrv_emitc_ggml_vec_scale_f32_kernel_ggml_vec_scale_f32("
+                                    "size_t n, float *y, float v);",
+    "cuda-ggml-rms-norm-f32.mlir": "void tcrv_emitc_ggml_rms_norm_f32_kernel_ggml_rms_norm_f32("
+                                   "size_t ne00, const float *x, float *y, float eps);",
+    "cuda-ggml-vec-silu-f32.mlir": "void tcrv_emitc_ggml_vec_silu_f32_kernel_ggml_vec_silu_f32("
+                                   "size_t n, const float *x, float *y);",
+    "cuda-ggml-vec-soft-max-f32.mlir": "double tcrv_emitc_ggml_vec_soft_max_f32_kernel_ggml_vec_soft_max_f32("
+                                       "size_t n, float *y, const float *x, float max);",
     "cuda-q4-0-q8-0-block-dot.mlir": "void tcrv_emitc_ggml_vec_dot_q4_0_q8_0_kernel_ggml_vec_dot_q4_0_q8_0("
                                      "size_t n, float *s, size_t bs, const uint8_t *vx, size_t bx, const uint8_t *vy, "
                                      "size_t by, int32_t nrc);",

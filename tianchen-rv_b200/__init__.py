@@ -75,6 +75,10 @@ ABI.update({
     "tcrv_cuda_host_add_i32": [_p, _p, _p, _sz],
     "tcrv_cuda_host_dequantize_i32_f32": [_p, ctypes.c_float, _p, _sz],
     "tcrv_cuda_host_quantize_row_q8_0": [_sz, _p, _p],
+    "tcrv_cuda_host_vec_scale_f32": [_sz, _p, ctypes.c_float],
+    "tcrv_cuda_host_rms_norm_f32": [_sz, _p, _p, ctypes.c_float],
+    "tcrv_cuda_host_vec_silu_f32": [_sz, _p, _p],
+    "tcrv_cuda_host_vec_soft_max_f32": [_sz, _p, _p, ctypes.c_float, _p],
     "tcrv_cuda_host_gemm_q4_0_q8_0": [_sz, _p, _p, _p, _sz, _sz, _sz, _sz, _sz],
     "tcrv_cuda_host_gemm_q8_0_q8_0": [_sz, _p, _p, _p, _sz, _sz, _sz, _sz, _sz],
 })

@@ -219,6 +219,52 @@ int host_matmul(bool q8_weights, size_t n, float *s, const uint8_t *vx, const ui
   return *c.error_word != 0 ? TCRV_CUDA_ERR_DEVICE_TIMEOUT : TCRV_CUDA_OK;
 }
 
+// One f32 vector in, one out (in == out for the in-place scale); `sum` receives the soft-max
+// row sum when the op produces one.
+enum class ForwardOp { Scale, Silu, RmsNorm, SoftMax };
+
+int host_forward(ForwardOp op, size_t n, const float *x, float *y, float param, double *sum) {
+  if (n == 0) {
+    if (sum)
+      *sum = 0.0;
+    return TCRV_CUDA_OK;
+  }
+  if (!x || !y)
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  HostContext &c = ctx();
+  std::lock_guard<std::mutex> lock(c.mu);
+  int st = ensure_stream(c);
+  if (st == TCRV_CUDA_OK)
+    st = arena_reserve(c, 2 * up256(n * 4) + 256);
+  if (st != TCRV_CUDA_OK)
+    return st;
+  float *dx = reinterpret_cast<float *>(arena_take(c, n * 4));
+  float *dy = reinterpret_cast<float *>(arena_take(c, n * 4));
+  double *dsum = reinterpret_cast<double *>(arena_take(c, sizeof(double)));
+  TCRV_CUDA_TRY(cudaMemcpyAsync(dx, x, n * 4, cudaMemcpyHostToDevice, c.stream));
+  switch (op) {
+    case ForwardOp::Scale:
+      st = launch_vec_scale_f32(n, dx, param, c.stream);
+      dy = dx;
+      break;
+    case ForwardOp::Silu:
+      st = launch_vec_silu_f32(n, dx, dy, c.stream);
+      break;
+    case ForwardOp::RmsNorm:
+      st = launch_rms_norm_f32(n, dx, dy, param, 1, n, n, c.stream);
+      break;
+    case ForwardOp::SoftMax:
+      st = launch_vec_soft_max_f32(n, dy, dx, param, dsum, c.stream);
+      break;
+  }
+  if (st != TCRV_CUDA_OK)
+    return st;
+  TCRV_CUDA_TRY(cudaMemcpyAsync(y, dy, n * 4, cudaMemcpyDeviceToHost, c.stream));
+  if (op == ForwardOp::SoftMax && sum)
+    TCRV_CUDA_TRY(cudaMemcpyAsync(sum, dsum, sizeof(double), cudaMemcpyDeviceToHost, c.stream));
+  return finish(c);
+}
+
 // The generated kernels return void and cannot fail; a provider error ends the process
 // with a message instead of returning garbage.
 void must(int status, const char *entry) {
@@ -377,6 +423,40 @@ void tcrv_emitc_explicit_selected_body_add_f32_kernel_explicit_selected_body_cud
 void tcrv_emitc_explicit_selected_body_dequantize_i32_to_f32_kernel_explicit_selected_body_rvv_dequantize_i32_to_f32(
     const int32_t *lhs, float scale, float *out, size_t n) {
   must(tcrv_cuda_host_dequantize_i32_f32(lhs, scale, out, n), __func__);
+}
+
+int tcrv_cuda_host_vec_scale_f32(size_t n, float *y, float v) {
+  return host_forward(ForwardOp::Scale, n, y, y, v, nullptr);
+}
+
+int tcrv_cuda_host_rms_norm_f32(size_t ne00, const float *x, float *y, float eps) {
+  return host_forward(ForwardOp::RmsNorm, ne00, x, y, eps, nullptr);
+}
+
+int tcrv_cuda_host_vec_silu_f32(size_t n, const float *x, float *y) {
+  return host_forward(ForwardOp::Silu, n, x, y, 0.0f, nullptr);
+}
+
+int tcrv_cuda_host_vec_soft_max_f32(size_t n, float *y, const float *x, float max, double *sum) {
+  return host_forward(ForwardOp::SoftMax, n, x, y, max, sum);
+}
+
+void tcrv_emitc_ggml_vec_scale_f32_kernel_ggml_vec_scale_f32(size_t n, float *y, float v) {
+  must(tcrv_cuda_host_vec_scale_f32(n, y, v), __func__);
+}
+
+void tcrv_emitc_ggml_rms_norm_f32_kernel_ggml_rms_norm_f32(size_t ne00, const float *x, float *y, float eps) {
+  must(tcrv_cuda_host_rms_norm_f32(ne00, x, y, eps), __func__);
+}
+
+void tcrv_emitc_ggml_vec_silu_f32_kernel_ggml_vec_silu_f32(size_t n, const float *x, float *y) {
+  must(tcrv_cuda_host_vec_silu_f32(n, x, y), __func__);
+}
+
+double tcrv_emitc_ggml_vec_soft_max_f32_kernel_ggml_vec_soft_max_f32(size_t n, float *y, const float *x, float max) {
+  double sum = 0.0;
+  must(tcrv_cuda_host_vec_soft_max_f32(n, y, x, max, &sum), __func__);
+  return sum;
 }
 
 void tcrv_emitc_quantize_row_q8_0_kernel_quantize_row_q8_0(size_t n, const float *x, uint8_t *vy) {

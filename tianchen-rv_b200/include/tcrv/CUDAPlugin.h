@@ -45,6 +45,7 @@ struct RouteEntry {
   std::string kernelFamily;
   std::string rooflineBound;             // "hbm", "tensor" or both
   std::string foldOrder;                 // fp32 fold convention ("" for non-dot kernels)
+  std::string returnType = "void";       // C return type of the entry (soft_max returns its f64 sum)
 };
 
 const std::vector<RouteEntry> &routeTable();

@@ -76,6 +76,34 @@ std::vector<RouteEntry> buildTable() {
                {{"runtime-element-count", "size_t"}, {"lhs-input-buffer", "const float *"}, {"output-buffer", "uint8_t *"}},
                "quantize_row_q8_0", "cuda-ggml-quantize-row-q8_0-callable-c-abi.v1", "tcrv_cuda_quantize_row_q8_0",
                "tcrv_cuda_host_quantize_row_q8_0", "streaming-quantizer", "hbm", ""});
+  // f32 forward-pass ops around the matmul (lib/Conversion/RVV/RVVToEmitCForwardElementwise.cpp)
+  t.push_back({"tcrv_rvv.ggml_vec_scale_f32", withKind("ggml_vec_scale_f32", {}), "", {"tcrv_rvv.ggml_vec_scale_f32"},
+               {"output-buffer", "dequant-scale-value", "runtime-element-count"},
+               {{"runtime-element-count", "size_t"}, {"output-buffer", "float *"}, {"dequant-scale-value", "float"}},
+               "ggml_vec_scale_f32", "cuda-ggml-vec-scale-f32-callable-c-abi.v1", "tcrv_cuda_vec_scale_f32",
+               "tcrv_cuda_host_vec_scale_f32", "streaming-elementwise", "hbm", ""});
+  t.push_back({"tcrv_rvv.ggml_rms_norm_f32", withKind("ggml_rms_norm_f32", {}), "", {"tcrv_rvv.ggml_rms_norm_f32"},
+               {"lhs-input-buffer", "output-buffer", "dequant-scale-value", "runtime-element-count"},
+               {{"runtime-element-count", "size_t"}, {"lhs-input-buffer", "const float *"}, {"output-buffer", "float *"},
+                {"dequant-scale-value", "float"}},
+               "ggml_rms_norm_f32", "cuda-ggml-rms-norm-f32-callable-c-abi.v1", "tcrv_cuda_rms_norm_f32",
+               "tcrv_cuda_host_rms_norm_f32", "row-reduction-f64-then-scale", "hbm", ""});
+  t.push_back({"tcrv_rvv.ggml_vec_silu_f32", withKind("ggml_vec_silu_f32", {}), "", {"tcrv_rvv.ggml_vec_silu_f32"},
+               {"lhs-input-buffer", "output-buffer", "runtime-element-count"},
+               {{"runtime-element-count", "size_t"}, {"lhs-input-buffer", "const float *"}, {"output-buffer", "float *"}},
+               "ggml_vec_silu_f32", "cuda-ggml-vec-silu-f32-callable-c-abi.v1", "tcrv_cuda_vec_silu_f32",
+               "tcrv_cuda_host_vec_silu_f32", "streaming-elementwise-exp-polynomial", "hbm", ""});
+  {
+    RouteEntry e{"tcrv_rvv.ggml_vec_soft_max_f32", withKind("ggml_vec_soft_max_f32", {}), "",
+                 {"tcrv_rvv.ggml_vec_soft_max_f32"},
+                 {"output-buffer", "lhs-input-buffer", "dequant-scale-value", "runtime-element-count"},
+                 {{"runtime-element-count", "size_t"}, {"output-buffer", "float *"}, {"lhs-input-buffer", "const float *"},
+                  {"dequant-scale-value", "float"}},
+                 "ggml_vec_soft_max_f32", "cuda-ggml-vec-soft-max-f32-callable-c-abi.v1", "tcrv_cuda_vec_soft_max_f32",
+                 "tcrv_cuda_host_vec_soft_max_f32", "streaming-elementwise-exp-polynomial+f64-sum", "hbm", ""};
+    e.returnType = "double";
+    t.push_back(e);
+  }
   t.push_back({"tcrv_rvv.q4_0_q8_0_block_dot", withKind("ggml_q4_0_q8_0_block_dot", kQ4Q8Facts), "",
                {"tcrv_rvv.q4_0_q8_0_block_dot"},
                {"lhs-input-buffer", "rhs-input-buffer", "output-buffer", "runtime-element-count"},

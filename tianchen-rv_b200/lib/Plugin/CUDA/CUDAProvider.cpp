@@ -172,6 +172,8 @@ public:
     meta("tcrv_cuda.roofline_bound", route->rooflineBound);
     if (!route->foldOrder.empty())
       meta("tcrv_cuda.fp32_fold_order", route->foldOrder);
+    if (route->returnType != "void")
+      meta("tcrv_cuda.return_type", route->returnType);
     meta("tcrv_cuda.target_arch", "sm_100a");
     meta("tcrv_cuda.required_capabilities", joinSymbols(r.variant->attr("requires")));
     meta("tcrv_cuda.required_header_declarations", "stddef.h,stdint.h");

@@ -83,7 +83,11 @@ Error collectCoherentPlans(const Op &module, const ExtensionPluginRegistry &regi
 
 std::string cPrototype(const VariantEmissionPlan &plan) {
   std::ostringstream os;
-  os << "void " << plan.entrySymbol << "(";
+  std::string ret = "void";
+  for (const auto &kv : plan.metadata)
+    if (kv.first == "tcrv_cuda.return_type")
+      ret = kv.second;
+  os << ret << " " << plan.entrySymbol << "(";
   for (size_t i = 0; i < plan.abiParameters.size(); ++i) {
     const auto &p = plan.abiParameters[i];
     const bool pointer = !p.cType.empty() && p.cType.back() == '*';
