@@ -455,6 +455,15 @@ def measure_other_kernels(pkg, torch):
     y8 = torch.empty((32000, 8), device="cuda")
     timed("gemv_q4_0_q8_0_batch8", lambda c: pkg.gemv(w4[c], x8, out=y8, flags=pkg.FLAG_STATIC_WEIGHTS), 5,
           gemv_bytes(32000, 4096, 8), "32000 x 4096, batch 8")
+    del w4
+    # f32 forward-pass ops on a prefill-sized activation (512 tokens x 11008 = 22.5 MB; 8 sets)
+    acts = [torch.randn((512, 11008), generator=gen, device="cuda") for _ in range(8)]
+    outs = [torch.empty((512, 11008), device="cuda") for _ in range(8)]
+    nbytes = 512 * 11008 * 4
+    timed("vec_silu_f32", lambda c: pkg.vec_silu(acts[c], out=outs[c]), 8, 2 * nbytes, "512 x 11008")
+    timed("rms_norm_f32", lambda c: pkg.rms_norm(acts[c], 1e-6, out=outs[c]), 8, 2 * nbytes,
+          "512 rows x 11008 (each row read once, kept in registers)")
+    timed("vec_scale_f32", lambda c: pkg.vec_scale_(outs[c], 0.5), 8, 2 * nbytes, "512 x 11008, in place")
     pkg.check_device_errors()
     return out
 

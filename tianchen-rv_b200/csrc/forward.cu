@@ -117,12 +117,17 @@ __device__ __forceinline__ double block_sum(double v, double *scratch) {
   return total;
 }
 
+constexpr int kRmsRegVec = 12;  // float4 per thread kept in registers: rows up to 12288 floats
+
 // One CTA per row (grid-stride over rows).  The squares are rounded to f32 before they are
 // widened, as in the reference; they are then added in double by a fixed tree (thread-strided
 // partials, warp butterfly, warps in order) instead of one ascending chain.  A double holds
 // the sum of f32 values exactly unless their exponents span more than 29 bits plus log2(n),
 // so the two associations agree except in the last bits of such sums, long before the result
 // is rounded back to f32.
+// kCached: the row (ne00 % 4 == 0, 16-byte aligned, at most kThreads * 4 * kRmsRegVec floats)
+// is read from global memory once and stays in registers between the reduction and the scaling.
+template <bool kCached>
 __global__ void __launch_bounds__(kThreads)
     rms_norm_kernel(size_t n, const float *x, float *y, float eps, size_t nrows, size_t x_stride, size_t y_stride) {
   __shared__ double scratch[kThreads / 32];
@@ -130,15 +135,43 @@ __global__ void __launch_bounds__(kThreads)
     const float *xr = x + row * x_stride;
     float *yr = y + row * y_stride;
     double part = 0.0;
-    for (size_t i = threadIdx.x; i < n; i += kThreads) {
-      const float v = xr[i];
-      part += static_cast<double>(__fmul_rn(v, v));
+    if constexpr (kCached) {
+      const float4 *x4 = reinterpret_cast<const float4 *>(xr);
+      float4 *y4 = reinterpret_cast<float4 *>(yr);
+      const uint32_t nvec = static_cast<uint32_t>(n / 4);
+      float4 v[kRmsRegVec];
+#pragma unroll
+      for (int j = 0; j < kRmsRegVec; ++j) {
+        const uint32_t i = threadIdx.x + j * kThreads;
+        if (i < nvec) {
+          v[j] = x4[i];
+          part += static_cast<double>(__fmul_rn(v[j].x, v[j].x));
+          part += static_cast<double>(__fmul_rn(v[j].y, v[j].y));
+          part += static_cast<double>(__fmul_rn(v[j].z, v[j].z));
+          part += static_cast<double>(__fmul_rn(v[j].w, v[j].w));
+        }
+      }
+      const double sum = block_sum(part, scratch);
+      const float mean = __double2float_rn(__ddiv_rn(sum, static_cast<double>(n)));
+      const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, eps)));
+#pragma unroll
+      for (int j = 0; j < kRmsRegVec; ++j) {
+        const uint32_t i = threadIdx.x + j * kThreads;
+        if (i < nvec)
+          y4[i] = make_float4(__fmul_rn(v[j].x, scale), __fmul_rn(v[j].y, scale), __fmul_rn(v[j].z, scale),
+                              __fmul_rn(v[j].w, scale));
+      }
+    } else {
+      for (size_t i = threadIdx.x; i < n; i += kThreads) {
+        const float v = xr[i];
+        part += static_cast<double>(__fmul_rn(v, v));
+      }
+      const double sum = block_sum(part, scratch);
+      const float mean = __double2float_rn(__ddiv_rn(sum, static_cast<double>(n)));
+      const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, eps)));
+      for (size_t i = threadIdx.x; i < n; i += kThreads)
+        yr[i] = __fmul_rn(xr[i], scale);
     }
-    const double sum = block_sum(part, scratch);
-    const float mean = __double2float_rn(__ddiv_rn(sum, static_cast<double>(n)));
-    const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, eps)));
-    for (size_t i = threadIdx.x; i < n; i += kThreads)
-      yr[i] = __fmul_rn(xr[i], scale);
   }
 }
 
@@ -169,7 +202,12 @@ int launch_rms_norm_f32(size_t n, const float *x, float *y, float eps, size_t nr
     return TCRV_CUDA_OK;
   const size_t cap = static_cast<size_t>(sm_count()) * 8;
   const int grid = static_cast<int>(nrows < cap ? nrows : cap);
-  rms_norm_kernel<<<grid, kThreads, 0, stream>>>(n, x, y, eps, nrows, x_stride, y_stride);
+  const bool cached = n % 4 == 0 && n <= static_cast<size_t>(kThreads) * 4 * kRmsRegVec && aligned16(x) && aligned16(y) &&
+                      (nrows == 1 || (x_stride % 4 == 0 && y_stride % 4 == 0));
+  if (cached)
+    rms_norm_kernel<true><<<grid, kThreads, 0, stream>>>(n, x, y, eps, nrows, x_stride, y_stride);
+  else
+    rms_norm_kernel<false><<<grid, kThreads, 0, stream>>>(n, x, y, eps, nrows, x_stride, y_stride);
   TCRV_CUDA_TRY(cudaGetLastError());
   return TCRV_CUDA_OK;
 }
