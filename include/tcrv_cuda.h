@@ -161,6 +161,16 @@ int tcrv_cuda_gemm_q4_0_q8_0_prepared(size_t n, float *s, const void *prepared_w
                                       size_t by, size_t nr, size_t nc, size_t bs, void *workspace,
                                       size_t workspace_bytes, unsigned flags, tcrv_cuda_stream stream);
 
+/* The reference's 16-row interleaved weight layout (block_q4_0x16, 288 bytes: 16 fp16 scales,
+ * then quant byte `off` of the 16 source blocks side by side, xor 0x88), as a device repack:
+ * `pack` replaces tcrv_rvv.pack_q4_0_to_q4_0x16 (lib/Conversion/RVV/RVVToEmitCBlockQuantLinear.cpp:
+ * 2674-2852; ABI order nblocks, src, dst; nblocks counts OUTPUT blocks, src holds 16 * nblocks
+ * consecutive block_q4_0, one from each interleaved row); `unpack` is its inverse, so weights
+ * repacked for the RVV kernels can be fed to this provider's kernels, which read plain rows
+ * (the GEMM's own layout contract is the prepared form above).  Byte-exact; src != dst. */
+int tcrv_cuda_pack_q4_0_to_q4_0x16(size_t nblocks, const uint8_t *src, uint8_t *dst, tcrv_cuda_stream stream);
+int tcrv_cuda_unpack_q4_0x16_to_q4_0(size_t nblocks, const uint8_t *src, uint8_t *dst, tcrv_cuda_stream stream);
+
 /* ---- f32 forward-pass ops the reference compiles next to the quantized matmul ----------
  * Bit-exact with the reference's arithmetic (every operation IEEE round-to-nearest, nothing
  * fused that the reference does not fuse); see each entry for the one exception. */
@@ -189,6 +199,20 @@ int tcrv_cuda_rms_norm_f32(size_t ne00, const float *x, float *y, float eps, siz
  * folds the sum with an unordered vector reduction, so only its value up to f64 rounding is
  * defined; the y are bit-exact. */
 int tcrv_cuda_vec_soft_max_f32(size_t n, float *y, const float *x, float max, double *sum, tcrv_cuda_stream stream);
+
+/* Rotary position embedding, consecutive-pair ("norm") form, in the two steps ggml itself
+ * takes (angle cache, then rotation).  Replaces tcrv_rvv.ggml_rope_norm_f32
+ * (RVVToEmitCForwardElementwise.cpp:959-1162; ABI order n_dims, x, y, theta_base, theta_scale).
+ *   rope_cache: cache[2p] = cosf(theta_p), cache[2p+1] = sinf(theta_p) with the reference's f32
+ *     recurrence theta_0 = theta_base, theta_{p+1} = theta_p * theta_scale (bit-exact; `thetas`,
+ *     when not null, receives the n_dims/2 angles).  cosf/sinf are libm calls in the reference;
+ *     CUDA's differ from a host libm's by a few ulp -- the one inexact step.
+ *   rope_apply: y[2p] = fma(x0, c, -(x1*s)), y[2p+1] = fma(x0, s, x1*c) for `nrows` rows sharing
+ *     the cache (the heads of one token); bit-exact given the cache.  x == y is allowed. */
+int tcrv_cuda_rope_cache_f32(size_t n_dims, float theta_base, float theta_scale, float *cache, float *thetas,
+                             tcrv_cuda_stream stream);
+int tcrv_cuda_rope_apply_f32(size_t n_dims, const float *x, float *y, const float *cache, size_t nrows, size_t x_stride,
+                             size_t y_stride, tcrv_cuda_stream stream);
 
 /* The prepared-weights GEMM delivering its result to `ndst` (1..8) output bases of identical
  * layout: `dst` is a HOST array of device pointers, dst[0] normally this GPU's buffer, the

@@ -36,6 +36,8 @@ int tcrv_cuda_host_vec_scale_f32(size_t n, float *y, float v);
 int tcrv_cuda_host_rms_norm_f32(size_t ne00, const float *x, float *y, float eps);
 int tcrv_cuda_host_vec_silu_f32(size_t n, const float *x, float *y);
 int tcrv_cuda_host_vec_soft_max_f32(size_t n, float *y, const float *x, float max, double *sum);
+int tcrv_cuda_host_rope_norm_f32(size_t n_dims, const float *x, float *y, float theta_base, float theta_scale);
+int tcrv_cuda_host_pack_q4_0_to_q4_0x16(size_t nblocks, const uint8_t *src, uint8_t *dst);
 /* nc <= 8 runs the decode GEMV, larger nc the tensor-core GEMM. */
 int tcrv_cuda_host_gemm_q4_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by, size_t nr,
                                   size_t nc, size_t bx, size_t bs);
@@ -66,6 +68,12 @@ void tcrv_emitc_ggml_rms_norm_f32_kernel_ggml_rms_norm_f32(size_t ne00, const fl
 void tcrv_emitc_ggml_vec_silu_f32_kernel_ggml_vec_silu_f32(size_t n, const float *x, float *y);
 /* test/Conversion/RVV/rvv-to-emitc-ggml-vec-soft-max-f32.mlir:47-48: returns the f64 sum */
 double tcrv_emitc_ggml_vec_soft_max_f32_kernel_ggml_vec_soft_max_f32(size_t n, float *y, const float *x, float max);
+/* test/Conversion/RVV/rvv-to-emitc-ggml-rope-norm-f32.mlir:58 */
+void tcrv_emitc_ggml_rope_norm_f32_kernel_ggml_rope_norm_f32(size_t n_dims, const float *x, float *y, float theta_base,
+                                                             float theta_scale);
+/* test/Conversion/RVV/rvv-to-emitc-pack-q4-0-to-q4-0x16.mlir:35 */
+void tcrv_emitc_ggml_pack_q4_0_to_q4_0x16_kernel_ggml_pack_q4_0_to_q4_0x16(size_t nblocks, const uint8_t *src,
+                                                                           uint8_t *dst);
 /* test/Conversion/RVV/rvv-to-emitc-q4-0-q8-0-block-dot.mlir:44 */
 void tcrv_emitc_ggml_vec_dot_q4_0_q8_0_kernel_ggml_vec_dot_q4_0_q8_0(size_t n, float *s, size_t bs, const uint8_t *vx,
                                                                      size_t bx, const uint8_t *vy, size_t by,

@@ -64,6 +64,11 @@ def _declare(L: ctypes.CDLL) -> None:
     L.tcrv_oracle_vec_silu_f32.argtypes = [_sz, _p, _p]
     L.tcrv_oracle_vec_soft_max_f32.argtypes = [_sz, _p, _p, ctypes.c_float]
     L.tcrv_oracle_vec_soft_max_f32.restype = ctypes.c_double
+    L.tcrv_oracle_rope_norm_f32.argtypes = [_sz, _p, _p, ctypes.c_float, ctypes.c_float, ctypes.c_int, _p]
+    L.tcrv_oracle_rope_apply_f32.argtypes = [_sz, _p, _p, _p, ctypes.c_int]
+    L.tcrv_oracle_rope_thetas.argtypes = [_sz, ctypes.c_float, ctypes.c_float, _p]
+    L.tcrv_oracle_pack_q4_0_to_q4_0x16.argtypes = [_sz, _p, _p]
+    L.tcrv_oracle_unpack_q4_0x16_to_q4_0.argtypes = [_sz, _p, _p]
     L.tcrv_oracle_fill_uniform.argtypes = [_p, _sz, ctypes.c_uint64, ctypes.c_float, ctypes.c_float]
     L.tcrv_oracle_fill_normal.argtypes = [_p, _sz, ctypes.c_uint64, ctypes.c_float, ctypes.c_float]
     L.tcrv_oracle_add_f32.argtypes = [_p, _p, _p, _sz]
@@ -207,6 +212,48 @@ def vec_soft_max_f32(x: np.ndarray, max_value: float):
     out = np.empty_like(x)
     total = lib().tcrv_oracle_vec_soft_max_f32(x.size, _ptr(out), _ptr(x), ctypes.c_float(max_value))
     return out, float(total)
+
+
+def rope_norm_f32(x: np.ndarray, theta_base: float, theta_scale: float, fold: int = FOLD_FMA):
+    """(y, cache): one head row rotated, and the (cos, sin) pairs the host libm produced."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    y, cache = np.empty_like(x), np.empty(x.size // 2 * 2, dtype=np.float32)
+    lib().tcrv_oracle_rope_norm_f32(x.size, _ptr(x), _ptr(y), ctypes.c_float(theta_base), ctypes.c_float(theta_scale),
+                                    fold, _ptr(cache))
+    return y, cache
+
+
+def rope_apply_f32(x: np.ndarray, cache: np.ndarray, fold: int = FOLD_FMA) -> np.ndarray:
+    """Rows of x (last dimension n_dims) rotated with the given (cos, sin) pairs."""
+    x2 = np.ascontiguousarray(x, dtype=np.float32).reshape(-1, x.shape[-1])
+    cache = np.ascontiguousarray(cache, dtype=np.float32)
+    out = np.empty_like(x2)
+    for r in range(x2.shape[0]):
+        lib().tcrv_oracle_rope_apply_f32(x2.shape[1], _ptr(x2[r]), _ptr(out[r]), _ptr(cache), fold)
+    return out.reshape(x.shape)
+
+
+def rope_thetas(n_pairs: int, theta_base: float, theta_scale: float) -> np.ndarray:
+    out = np.empty(n_pairs, dtype=np.float32)
+    lib().tcrv_oracle_rope_thetas(n_pairs, ctypes.c_float(theta_base), ctypes.c_float(theta_scale), _ptr(out))
+    return out
+
+
+def pack_q4_0_to_q4_0x16(src: np.ndarray) -> np.ndarray:
+    """16*nblocks consecutive block_q4_0 (flat uint8, 288*nblocks bytes) -> nblocks block_q4_0x16."""
+    src = np.ascontiguousarray(src, dtype=np.uint8).reshape(-1)
+    assert src.size % 288 == 0
+    dst = np.empty_like(src)
+    lib().tcrv_oracle_pack_q4_0_to_q4_0x16(src.size // 288, _ptr(src), _ptr(dst))
+    return dst
+
+
+def unpack_q4_0x16_to_q4_0(src: np.ndarray) -> np.ndarray:
+    src = np.ascontiguousarray(src, dtype=np.uint8).reshape(-1)
+    assert src.size % 288 == 0
+    dst = np.empty_like(src)
+    lib().tcrv_oracle_unpack_q4_0x16_to_q4_0(src.size // 288, _ptr(src), _ptr(dst))
+    return dst
 
 
 def decode_nibbles(byte: int) -> tuple[int, int]:

@@ -540,3 +540,67 @@ double tcrv_oracle_vec_soft_max_f32(size_t n, float *y, const float *x, float ma
   }
   return sum;
 }
+
+void tcrv_oracle_rope_thetas(size_t n_pairs, float theta_base, float theta_scale, float *theta) {
+  float t = theta_base;
+  for (size_t p = 0; p < n_pairs; ++p) {
+    theta[p] = t;
+    t = t * theta_scale;
+  }
+}
+
+void tcrv_oracle_rope_apply_f32(size_t n_dims, const float *x, float *y, const float *cache, int fold) {
+  for (size_t p = 0; p < n_dims / 2; ++p) {
+    const float c = cache[2 * p], s = cache[2 * p + 1];
+    const float x0 = x[2 * p], x1 = x[2 * p + 1];
+    if (fold == TCRV_FOLD_FMA) {
+      y[2 * p] = fmaf(x0, c, -(x1 * s));
+      y[2 * p + 1] = fmaf(x0, s, x1 * c);
+    } else {
+      y[2 * p] = x0 * c - x1 * s;
+      y[2 * p + 1] = x0 * s + x1 * c;
+    }
+  }
+}
+
+void tcrv_oracle_rope_norm_f32(size_t n_dims, const float *x, float *y, float theta_base, float theta_scale,
+                               int fold, float *cache) {
+  float theta = theta_base;
+  for (size_t p = 0; p < n_dims / 2; ++p) {
+    const float pair[2] = {cosf(theta), sinf(theta)};
+    if (cache) {
+      cache[2 * p] = pair[0];
+      cache[2 * p + 1] = pair[1];
+    }
+    float out[2];
+    const float in[2] = {x[2 * p], x[2 * p + 1]};
+    tcrv_oracle_rope_apply_f32(2, in, out, pair, fold);
+    y[2 * p] = out[0];
+    y[2 * p + 1] = out[1];
+    theta = theta * theta_scale;
+  }
+}
+
+void tcrv_oracle_pack_q4_0_to_q4_0x16(size_t nblocks, const uint8_t *src, uint8_t *dst) {
+  for (size_t b = 0; b < nblocks; ++b) {
+    const size_t sbase = b * 16 * 18, dbase = b * 288;
+    for (size_t j = 0; j < 16; ++j)
+      for (size_t k = 0; k < 2; ++k)
+        dst[dbase + j * 2 + k] = src[sbase + j * 18 + k];
+    for (size_t off = 0; off < 16; ++off)
+      for (size_t blk = 0; blk < 16; ++blk)
+        dst[dbase + 32 + off * 16 + blk] = (uint8_t)(src[sbase + blk * 18 + 2 + off] ^ 0x88);
+  }
+}
+
+void tcrv_oracle_unpack_q4_0x16_to_q4_0(size_t nblocks, const uint8_t *src, uint8_t *dst) {
+  for (size_t b = 0; b < nblocks; ++b) {
+    const size_t sbase = b * 288, dbase = b * 16 * 18;
+    for (size_t j = 0; j < 16; ++j)
+      for (size_t k = 0; k < 2; ++k)
+        dst[dbase + j * 18 + k] = src[sbase + j * 2 + k];
+    for (size_t off = 0; off < 16; ++off)
+      for (size_t blk = 0; blk < 16; ++blk)
+        dst[dbase + blk * 18 + 2 + off] = (uint8_t)(src[sbase + 32 + off * 16 + blk] ^ 0x88);
+  }
+}

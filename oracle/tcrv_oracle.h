@@ -91,6 +91,29 @@ void tcrv_oracle_vec_silu_f32(size_t n, const float *x, float *y);
  * restatement adds in ascending order. */
 double tcrv_oracle_vec_soft_max_f32(size_t n, float *y, const float *x, float max);
 
+/* tcrv_rvv.ggml_rope_norm_f32 for one head row (RVVToEmitCForwardElementwise.cpp:959-1162):
+ * theta = theta_base; for each consecutive pair p: c = cosf(theta), s = sinf(theta),
+ * y[2p] = x0*c - x1*s, y[2p+1] = x0*s + x1*c, theta = theta * theta_scale (f32 recurrence).
+ * Each rotation output is ONE C expression in the reference, so the deployed build contracts
+ * it (left product fused): fma(x0, c, -(x1*s)) and fma(x0, s, x1*c); `fold` = TCRV_FOLD_FMA
+ * gives that, TCRV_FOLD_NOFMA rounds every operator.  cosf/sinf are the host libm's here, as
+ * they are libm calls in the reference.  `cache`, when not null, receives the (cos, sin) pair
+ * used for every p (n_dims floats). */
+void tcrv_oracle_rope_norm_f32(size_t n_dims, const float *x, float *y, float theta_base, float theta_scale,
+                               int fold, float *cache);
+/* The rotation alone with given (cos, sin) pairs: the bit-exact part of the op. */
+void tcrv_oracle_rope_apply_f32(size_t n_dims, const float *x, float *y, const float *cache, int fold);
+/* theta_p for p = 0 .. n_pairs-1 (the f32 recurrence alone). */
+void tcrv_oracle_rope_thetas(size_t n_pairs, float theta_base, float theta_scale, float *theta);
+
+/* tcrv_rvv.pack_q4_0_to_q4_0x16 (lib/Conversion/RVV/RVVToEmitCBlockQuantLinear.cpp:2674-2852,
+ * loop nest stated at :2755-2771): output block b gathers the 16 consecutive source blocks
+ * 16b..16b+15 (one from each interleaved row): dst[288b + 2j + k] = src[(16b+j)*18 + k] for the
+ * 16 fp16 scales (verbatim), dst[288b + 32 + off*16 + blk] = src[(16b+blk)*18 + 2 + off] ^ 0x88
+ * for the nibble bytes.  `unpack` is the inverse permutation. */
+void tcrv_oracle_pack_q4_0_to_q4_0x16(size_t nblocks, const uint8_t *src, uint8_t *dst);
+void tcrv_oracle_unpack_q4_0x16_to_q4_0(size_t nblocks, const uint8_t *src, uint8_t *dst);
+
 /* Block dequantisation y = d * q.  Per element this is the i32->f32 dequantize math
  * (RVVToEmitC.cpp:3347-3394) with d read from the block header. */
 void tcrv_oracle_dequantize_row_q8_0(const uint8_t *vx, float *y, size_t n);

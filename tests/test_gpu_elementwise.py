@@ -91,3 +91,18 @@ def test_full_size_dequant_q8_0_config(cuda, pkg, O):
     assert np.array_equal(bits(got), bits(O.dequantize_q8_0(q)))
     # and the GPU quantizer reproduces the same bytes from the same fp32 input
     assert np.array_equal(pkg.quantize_q8_0(dev(cuda, x)).cpu().numpy(), q)
+
+
+@pytest.mark.parametrize("nblocks", [1, 7, 1000, 4096 * 8])
+def test_q4_0x16_repack_byte_exact(cuda, pkg, O, nblocks):
+    rng = np.random.default_rng(nblocks)
+    src = rng.integers(0, 256, size=nblocks * 288, dtype=np.uint8)
+    sd = cuda.from_numpy(src).cuda()
+    packed = pkg.pack_q4_0_to_q4_0x16(sd)
+    assert np.array_equal(packed.cpu().numpy(), O.pack_q4_0_to_q4_0x16(src))
+    assert np.array_equal(pkg.unpack_q4_0x16_to_q4_0(packed).cpu().numpy(), src)
+    # bases that are not 4-byte aligned take the byte path
+    buf = cuda.zeros(nblocks * 288 + 1, dtype=cuda.uint8, device="cuda")
+    buf[1:] = sd
+    assert np.array_equal(pkg.pack_q4_0_to_q4_0x16(buf[1:]).cpu().numpy(), O.pack_q4_0_to_q4_0x16(src))
+    pkg.check_device_errors()

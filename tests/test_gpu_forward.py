@@ -101,3 +101,38 @@ def test_forward_ops_argument_checks(cuda, pkg):
     assert L.tcrv_cuda_rms_norm_f32(8, t.data_ptr(), t.data_ptr(), 1e-6, 2, 4, 8, None) == -1  # x_stride < ne00
     assert L.tcrv_cuda_vec_soft_max_f32(8, None, t.data_ptr(), 0.0, None, None) == -1
     assert L.tcrv_cuda_vec_scale_f32(0, None, 1.0, None) == 0 and L.tcrv_cuda_rms_norm_f32(0, None, None, 0.0, 4, 0, 0, None) == 0
+
+
+@pytest.mark.parametrize("n_dims,rows", [(2, 1), (64, 3), (128, 32), (256, 5)])
+def test_rope_recurrence_and_rotation_bit_exact_angles_within_libm_ulps(cuda, pkg, O, n_dims, rows):
+    theta_base, theta_scale = 1234.0, float(np.float32(10000.0) ** np.float32(-2.0 / n_dims))
+    x = O.fill_normal(rows * n_dims, 90 + n_dims, 0.0, 1.0).reshape(rows, n_dims)
+    cache, thetas = pkg.rope_cache(n_dims, theta_base, theta_scale, with_thetas=True)
+    # 1. the f32 angle recurrence is the reference's, bit for bit
+    assert np.array_equal(bits(thetas.cpu().numpy()), bits(O.rope_thetas(n_dims // 2, theta_base, theta_scale)))
+    # 2. cosf/sinf: CUDA's against the host libm's, a few ulp of a value in [-1, 1]
+    _, host_cache = O.rope_norm_f32(x[0], theta_base, theta_scale)
+    got_cache = cache.cpu().numpy()
+    assert np.max(np.abs(got_cache - host_cache)) <= 4 * 2.0 ** -24
+    # 3. the rotation is bit-exact given the (cos, sin) pairs it used
+    got = pkg.rope_apply(dev(cuda, x), cache).cpu().numpy()
+    assert np.array_equal(bits(got), bits(O.rope_apply_f32(x, got_cache)))
+    # 4. end to end against the oracle with the host libm: within the angle error times |x|
+    want = np.stack([O.rope_norm_f32(x[r], theta_base, theta_scale)[0] for r in range(rows)])
+    bound = 8 * 2.0 ** -24 * (np.abs(x[:, 0::2]) + np.abs(x[:, 1::2])) + 1e-30
+    assert np.all(np.abs(got[:, 0::2] - want[:, 0::2]) <= bound) and np.all(np.abs(got[:, 1::2] - want[:, 1::2]) <= bound)
+    # in place, and padded strides
+    buf = cuda.zeros((rows, n_dims + 6), dtype=cuda.float32, device="cuda")
+    buf[:, :n_dims] = dev(cuda, x)
+    pkg.rope_apply(buf[:, :n_dims], cache, out=buf[:, :n_dims])
+    assert np.array_equal(bits(buf[:, :n_dims].cpu().numpy()), bits(got)) and float(buf[:, n_dims:].abs().sum()) == 0.0
+    pkg.check_device_errors()
+
+
+def test_rope_argument_checks(cuda, pkg):
+    L = pkg.lib()
+    t = cuda.zeros(8, dtype=cuda.float32, device="cuda")
+    assert L.tcrv_cuda_rope_cache_f32(7, 1.0, 0.5, t.data_ptr(), None, None) == -1  # odd n_dims
+    assert L.tcrv_cuda_rope_cache_f32(8, 1.0, 0.5, None, None, None) == -1
+    assert L.tcrv_cuda_rope_apply_f32(8, t.data_ptr(), t.data_ptr(), t.data_ptr(), 2, 4, 8, None) == -1  # stride < n_dims
+    assert L.tcrv_cuda_rope_apply_f32(0, None, None, None, 0, 0, 0, None) == 0

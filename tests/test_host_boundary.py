@@ -59,6 +59,10 @@ PROTOTYPES = {
                                    "size_t n, const float *x, float *y);",
     "cuda-ggml-vec-soft-max-f32.mlir": "double tcrv_emitc_ggml_vec_soft_max_f32_kernel_ggml_vec_soft_max_f32("
                                        "size_t n, float *y, const float *x, float max);",
+    "cuda-ggml-rope-norm-f32.mlir": "void tcrv_emitc_ggml_rope_norm_f32_kernel_ggml_rope_norm_f32("
+                                    "size_t n_dims, const float *x, float *y, float theta_base, float theta_scale);",
+    "cuda-pack-q4-0-to-q4-0x16.mlir": "void tcrv_emitc_ggml_pack_q4_0_to_q4_0x16_kernel_ggml_pack_q4_0_to_q4_0x16("
+                                      "size_t nblocks, const uint8_t *src, uint8_t *dst);",
     "cuda-q4-0-q8-0-block-dot.mlir": "void tcrv_emitc_ggml_vec_dot_q4_0_q8_0_kernel_ggml_vec_dot_q4_0_q8_0("
                                      "size_t n, float *s, size_t bs, const uint8_t *vx, size_t bx, const uint8_t *vy, "
                                      "size_t by, int32_t nrc);",

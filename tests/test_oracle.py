@@ -248,3 +248,31 @@ def test_forward_ops_hand_cases(O):
     y, total = O.vec_soft_max_f32(np.array([1.0, 2.0, 3.0, -np.inf], np.float32), 3.0)
     assert y[2] == 1.0 and y[3] == 0.0 and abs(total - (np.exp(-2.0) + np.exp(-1.0) + 1.0)) < 1e-6
     assert total == float(np.float64(y[0]) + np.float64(y[1]) + np.float64(y[2]) + np.float64(y[3]))
+
+
+def test_rope_hand_case(O):
+    # theta = pi/2 for the first pair, then scaled by 0: (1, 0) -> (cos, sin), second pair unrotated
+    x = np.array([1.0, 0.0, 3.0, 4.0], np.float32)
+    y, cache = O.rope_norm_f32(x, float(np.float32(np.pi / 2)), 0.0)
+    assert np.array_equal(O.rope_thetas(2, float(np.float32(np.pi / 2)), 0.0), np.array([np.float32(np.pi / 2), 0.0], np.float32))
+    assert abs(cache[0]) < 1e-7 and cache[1] == 1.0 and cache[2] == 1.0 and cache[3] == 0.0
+    assert y[1] == 1.0 and abs(y[0]) < 1e-7 and y[2] == 3.0 and y[3] == 4.0
+    # fused and unfused rotations agree to an ulp and are both reachable
+    x = O.fill_normal(64, 5)
+    a, c = O.rope_norm_f32(x, 17.0, 0.75, fold=O.FOLD_FMA)
+    b, _ = O.rope_norm_f32(x, 17.0, 0.75, fold=O.FOLD_NOFMA)
+    assert np.allclose(a, b, rtol=0, atol=4e-7) and np.array_equal(a, O.rope_apply_f32(x, c, fold=O.FOLD_FMA))
+
+
+def test_q4_0x16_pack_layout_and_inverse(O):
+    rng = np.random.default_rng(3)
+    src = rng.integers(0, 256, size=3 * 288, dtype=np.uint8)
+    dst = O.pack_q4_0_to_q4_0x16(src)
+    # spelled out from the loop nest at RVVToEmitCBlockQuantLinear.cpp:2755-2771
+    for b in range(3):
+        for j in range(16):
+            assert dst[288 * b + 2 * j] == src[(16 * b + j) * 18] and dst[288 * b + 2 * j + 1] == src[(16 * b + j) * 18 + 1]
+        for off in range(16):
+            for blk in range(16):
+                assert dst[288 * b + 32 + off * 16 + blk] == src[(16 * b + blk) * 18 + 2 + off] ^ 0x88
+    assert np.array_equal(O.unpack_q4_0x16_to_q4_0(dst), src)

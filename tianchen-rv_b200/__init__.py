@@ -57,6 +57,10 @@ ABI = {
     "tcrv_cuda_vec_silu_f32": [_sz, _p, _p, _p],
     "tcrv_cuda_rms_norm_f32": [_sz, _p, _p, ctypes.c_float, _sz, _sz, _sz, _p],
     "tcrv_cuda_vec_soft_max_f32": [_sz, _p, _p, ctypes.c_float, _p, _p],
+    "tcrv_cuda_rope_cache_f32": [_sz, ctypes.c_float, ctypes.c_float, _p, _p, _p],
+    "tcrv_cuda_rope_apply_f32": [_sz, _p, _p, _p, _sz, _sz, _sz, _p],
+    "tcrv_cuda_pack_q4_0_to_q4_0x16": [_sz, _p, _p, _p],
+    "tcrv_cuda_unpack_q4_0x16_to_q4_0": [_sz, _p, _p, _p],
     "tcrv_cuda_peer_alloc": [_sz, _p],
     "tcrv_cuda_peer_free": [_p],
     "tcrv_cuda_peer_export": [_p, _p],
@@ -79,6 +83,8 @@ ABI.update({
     "tcrv_cuda_host_rms_norm_f32": [_sz, _p, _p, ctypes.c_float],
     "tcrv_cuda_host_vec_silu_f32": [_sz, _p, _p],
     "tcrv_cuda_host_vec_soft_max_f32": [_sz, _p, _p, ctypes.c_float, _p],
+    "tcrv_cuda_host_rope_norm_f32": [_sz, _p, _p, ctypes.c_float, ctypes.c_float],
+    "tcrv_cuda_host_pack_q4_0_to_q4_0x16": [_sz, _p, _p],
     "tcrv_cuda_host_gemm_q4_0_q8_0": [_sz, _p, _p, _p, _sz, _sz, _sz, _sz, _sz],
     "tcrv_cuda_host_gemm_q8_0_q8_0": [_sz, _p, _p, _p, _sz, _sz, _sz, _sz, _sz],
 })
@@ -356,6 +362,31 @@ def gemm(w, x, out=None, workspace=None):
     return out
 
 
+def pack_q4_0_to_q4_0x16(src, out=None):
+    """16 * nblocks consecutive block_q4_0 (flat uint8 tensor) -> nblocks block_q4_0x16."""
+    import torch
+
+    if src.numel() % 288 != 0:
+        raise ValueError("the source must hold a multiple of 16 blocks (288 bytes)")
+    if out is None:
+        out = torch.empty_like(src)
+    _check(lib().tcrv_cuda_pack_q4_0_to_q4_0x16(src.numel() // 288, _dev(src, torch.uint8), _dev(out, torch.uint8),
+                                                _stream()), "tcrv_cuda_pack_q4_0_to_q4_0x16")
+    return out
+
+
+def unpack_q4_0x16_to_q4_0(src, out=None):
+    import torch
+
+    if src.numel() % 288 != 0:
+        raise ValueError("the source must hold whole 288-byte blocks")
+    if out is None:
+        out = torch.empty_like(src)
+    _check(lib().tcrv_cuda_unpack_q4_0x16_to_q4_0(src.numel() // 288, _dev(src, torch.uint8), _dev(out, torch.uint8),
+                                                  _stream()), "tcrv_cuda_unpack_q4_0x16_to_q4_0")
+    return out
+
+
 # ------------------------------------------------------------------ f32 forward-pass ops
 
 
@@ -401,6 +432,31 @@ def vec_soft_max(x, max_value: float, out=None):
                                             total.data_ptr(), _stream()),
            "tcrv_cuda_vec_soft_max_f32")
     return out, total
+
+
+def rope_cache(n_dims: int, theta_base: float, theta_scale: float, device="cuda", with_thetas: bool = False):
+    """(cos, sin) pairs of the rope angles as a (n_dims,) float32 tensor [, the angles]."""
+    import torch
+
+    cache = torch.empty(n_dims, dtype=torch.float32, device=device)
+    thetas = torch.empty(n_dims // 2, dtype=torch.float32, device=device) if with_thetas else None
+    _check(lib().tcrv_cuda_rope_cache_f32(n_dims, theta_base, theta_scale, cache.data_ptr(),
+                                          thetas.data_ptr() if with_thetas else None, _stream()),
+           "tcrv_cuda_rope_cache_f32")
+    return (cache, thetas) if with_thetas else cache
+
+
+def rope_apply(x, cache, out=None):
+    """Rotates the rows of a 2-D (rows, n_dims) tensor with one shared angle cache."""
+    import torch
+
+    if x.dim() != 2 or x.stride(1) != 1 or x.dtype != torch.float32 or not x.is_cuda:
+        raise ValueError("x must be a 2-D float32 CUDA tensor with unit inner stride")
+    if out is None:
+        out = torch.empty((x.shape[0], x.shape[1]), dtype=torch.float32, device=x.device)
+    _check(lib().tcrv_cuda_rope_apply_f32(x.shape[1], x.data_ptr(), out.data_ptr(), _dev(cache, torch.float32), x.shape[0],
+                                          x.stride(0), out.stride(0), _stream()), "tcrv_cuda_rope_apply_f32")
+    return out
 
 
 # ------------------------------------------------------------------ N-sharding (multi-GPU GEMM)

@@ -300,6 +300,39 @@ int tcrv_cuda_vec_soft_max_f32(size_t n, float *y, const float *x, float max, do
   return launch_vec_soft_max_f32(n, y, x, max, sum, as_stream(stream));
 }
 
+int tcrv_cuda_rope_cache_f32(size_t n_dims, float theta_base, float theta_scale, float *cache, float *thetas,
+                             tcrv_cuda_stream stream) {
+  if (n_dims % 2 != 0 || n_dims > 0xffffffffull)
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  if (n_dims != 0 && (!cache || reinterpret_cast<uintptr_t>(cache) % 8 != 0))
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  return launch_rope_cache_f32(n_dims, theta_base, theta_scale, cache, thetas, as_stream(stream));
+}
+
+int tcrv_cuda_rope_apply_f32(size_t n_dims, const float *x, float *y, const float *cache, size_t nrows, size_t x_stride,
+                             size_t y_stride, tcrv_cuda_stream stream) {
+  if (n_dims % 2 != 0 || n_dims > 0xffffffffull)
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  if (n_dims == 0 || nrows == 0)
+    return TCRV_CUDA_OK;
+  if (!x || !y || !cache || reinterpret_cast<uintptr_t>(cache) % 8 != 0 ||
+      (nrows > 1 && (x_stride < n_dims || y_stride < n_dims)))
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  return launch_rope_apply_f32(n_dims, x, y, cache, nrows, x_stride, y_stride, as_stream(stream));
+}
+
+int tcrv_cuda_pack_q4_0_to_q4_0x16(size_t nblocks, const uint8_t *src, uint8_t *dst, tcrv_cuda_stream stream) {
+  if (nblocks != 0 && (!src || !dst || src == dst))
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  return launch_pack_q4_0_to_q4_0x16(nblocks, src, dst, as_stream(stream));
+}
+
+int tcrv_cuda_unpack_q4_0x16_to_q4_0(size_t nblocks, const uint8_t *src, uint8_t *dst, tcrv_cuda_stream stream) {
+  if (nblocks != 0 && (!src || !dst || src == dst))
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  return launch_unpack_q4_0x16_to_q4_0(nblocks, src, dst, as_stream(stream));
+}
+
 int tcrv_cuda_peer_alloc(size_t bytes, void **ptr) {
   if (!ptr || bytes == 0)
     return TCRV_CUDA_ERR_INVALID_ARGUMENT;

@@ -315,7 +315,105 @@ __global__ void __launch_bounds__(kThreads) quantize_q4_0_kernel(const float *__
 
 }  // namespace
 
+namespace {
+
+// ---------------------------------------------------------------- q4_0 <-> q4_0x16 repack
+//
+// One warp per 288-byte group (16 plain blocks <-> one interleaved block): the group is staged
+// in shared memory with word loads, every output word is assembled from four staged bytes and
+// written with a word store.  Byte i of the interleaved block is
+//   i < 32 : scale byte (i % 2) of plain block i / 2
+//   else   : quant byte off = (i - 32) / 16 of plain block blk = (i - 32) % 16, xor 0x88.
+constexpr int kRepackWarps = 8;
+
+template <bool kPack>
+__device__ __forceinline__ uint32_t repack_source_index(uint32_t i) {
+  if constexpr (kPack) {  // i indexes the interleaved block, result indexes the 16 plain blocks
+    if (i < 32)
+      return (i >> 1) * 18 + (i & 1);
+    const uint32_t q = i - 32;
+    return (q & 15) * 18 + 2 + (q >> 4);
+  } else {  // i indexes the 16 plain blocks, result indexes the interleaved block
+    const uint32_t blk = i / 18, k = i - blk * 18;
+    if (k < 2)
+      return blk * 2 + k;
+    return 32 + (k - 2) * 16 + blk;
+  }
+}
+
+template <bool kPack>
+__device__ __forceinline__ bool repack_is_quant(uint32_t out_index) {
+  if constexpr (kPack)
+    return out_index >= 32;
+  else
+    return out_index % 18 >= 2;
+}
+
+template <bool kPack, bool kWords>
+__global__ void __launch_bounds__(kRepackWarps * 32)
+    repack_q4_0x16_kernel(size_t ngroups, const uint8_t *__restrict__ src, uint8_t *__restrict__ dst) {
+  __shared__ __align__(16) uint8_t stage[kRepackWarps][288];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  uint8_t *mine = stage[warp];
+  for (size_t g = static_cast<size_t>(blockIdx.x) * kRepackWarps + warp; g < ngroups;
+       g += static_cast<size_t>(gridDim.x) * kRepackWarps) {
+    const uint8_t *s = src + g * 288;
+    uint8_t *d = dst + g * 288;
+    if constexpr (kWords) {
+      for (int w = lane; w < 72; w += 32)
+        reinterpret_cast<uint32_t *>(mine)[w] = reinterpret_cast<const uint32_t *>(s)[w];
+    } else {
+      for (int i = lane; i < 288; i += 32)
+        mine[i] = s[i];
+    }
+    __syncwarp();
+    for (int w = lane; w < 72; w += 32) {
+      uint32_t word = 0;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const uint32_t i = 4 * w + k;
+        uint32_t byte = mine[repack_source_index<kPack>(i)];
+        if (repack_is_quant<kPack>(i))
+          byte ^= 0x88u;
+        word |= byte << (8 * k);
+      }
+      if constexpr (kWords) {
+        reinterpret_cast<uint32_t *>(d)[w] = word;
+      } else {
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          d[4 * w + k] = static_cast<uint8_t>(word >> (8 * k));
+      }
+    }
+    __syncwarp();
+  }
+}
+
+template <bool kPack>
+int launch_repack(size_t ngroups, const uint8_t *src, uint8_t *dst, cudaStream_t stream) {
+  if (ngroups == 0)
+    return TCRV_CUDA_OK;
+  const int grid = grid_for(ngroups, kRepackWarps, 8);
+  const bool words = (reinterpret_cast<uintptr_t>(src) & 3u) == 0 && (reinterpret_cast<uintptr_t>(dst) & 3u) == 0;
+  if (words)
+    repack_q4_0x16_kernel<kPack, true><<<grid, kRepackWarps * 32, 0, stream>>>(ngroups, src, dst);
+  else
+    repack_q4_0x16_kernel<kPack, false><<<grid, kRepackWarps * 32, 0, stream>>>(ngroups, src, dst);
+  TCRV_CUDA_TRY(cudaGetLastError());
+  return TCRV_CUDA_OK;
+}
+
+}  // namespace
+
 // -------------------------------------------------------------------------- launchers
+
+int launch_pack_q4_0_to_q4_0x16(size_t nblocks, const uint8_t *src, uint8_t *dst, cudaStream_t stream) {
+  return launch_repack<true>(nblocks, src, dst, stream);
+}
+
+int launch_unpack_q4_0x16_to_q4_0(size_t nblocks, const uint8_t *src, uint8_t *dst, cudaStream_t stream) {
+  return launch_repack<false>(nblocks, src, dst, stream);
+}
 
 int launch_add_f32(const float *lhs, const float *rhs, float *out, size_t n, cudaStream_t stream) {
   if (n == 0)

@@ -186,6 +186,44 @@ __global__ void __launch_bounds__(kThreads) sum_f64_kernel(size_t n, const float
     *sum = total;
 }
 
+// (cos, sin) of the rope angles: thread p replays the reference's f32 recurrence
+// theta_p = (...(theta_base * theta_scale) * ...) * theta_scale, p multiplications, so the
+// angle is the reference's bit for bit; cosf/sinf are CUDA's (libm calls in the reference:
+// the two libraries differ by a few ulp, which is the only inexact step of the op).
+__global__ void rope_cache_kernel(uint32_t n_pairs, float theta_base, float theta_scale, float *cache, float *thetas) {
+  const uint32_t p = blockIdx.x * blockDim.x + threadIdx.x;
+  if (p >= n_pairs)
+    return;
+  float theta = theta_base;
+  for (uint32_t i = 0; i < p; ++i)
+    theta = __fmul_rn(theta, theta_scale);
+  cache[2 * p] = cosf(theta);
+  cache[2 * p + 1] = sinf(theta);
+  if (thetas)
+    thetas[p] = theta;
+}
+
+// y = rotation of consecutive pairs, rows sharing one cache.  The left product of each output
+// is fused, as the reference's single C expression compiles: fma(x0, c, -(x1*s)), fma(x0, s, x1*c).
+__global__ void __launch_bounds__(kThreads)
+    rope_apply_kernel(uint32_t n_pairs, const float *x, float *y, const float *cache, size_t nrows, size_t x_stride,
+                      size_t y_stride) {
+  const size_t total = nrows * n_pairs;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const size_t row = i / n_pairs;
+    const uint32_t p = static_cast<uint32_t>(i - row * n_pairs);
+    const float2 cs = reinterpret_cast<const float2 *>(cache)[p];
+    const float *xr = x + row * x_stride + 2 * p;
+    float *yr = y + row * y_stride + 2 * p;
+    const float x0 = xr[0], x1 = xr[1];
+    const float lo = __fmaf_rn(x0, cs.x, -__fmul_rn(x1, cs.y));
+    const float hi = __fmaf_rn(x0, cs.y, __fmul_rn(x1, cs.x));
+    yr[0] = lo;
+    yr[1] = hi;
+  }
+}
+
 }  // namespace
 
 int launch_vec_scale_f32(size_t n, float *y, float v, cudaStream_t stream) {
@@ -222,6 +260,27 @@ int launch_vec_soft_max_f32(size_t n, float *y, const float *x, float max, doubl
   if (st != TCRV_CUDA_OK || !sum)
     return st;
   sum_f64_kernel<<<1, kThreads, 0, stream>>>(n, y, sum);
+  TCRV_CUDA_TRY(cudaGetLastError());
+  return TCRV_CUDA_OK;
+}
+
+int launch_rope_cache_f32(size_t n_dims, float theta_base, float theta_scale, float *cache, float *thetas,
+                          cudaStream_t stream) {
+  const uint32_t n_pairs = static_cast<uint32_t>(n_dims / 2);
+  if (n_pairs == 0)
+    return TCRV_CUDA_OK;
+  rope_cache_kernel<<<(n_pairs + 127) / 128, 128, 0, stream>>>(n_pairs, theta_base, theta_scale, cache, thetas);
+  TCRV_CUDA_TRY(cudaGetLastError());
+  return TCRV_CUDA_OK;
+}
+
+int launch_rope_apply_f32(size_t n_dims, const float *x, float *y, const float *cache, size_t nrows, size_t x_stride,
+                          size_t y_stride, cudaStream_t stream) {
+  const uint32_t n_pairs = static_cast<uint32_t>(n_dims / 2);
+  if (n_pairs == 0 || nrows == 0)
+    return TCRV_CUDA_OK;
+  const int grid = grid_for(nrows * n_pairs, kThreads * 4, 8);
+  rope_apply_kernel<<<grid, kThreads, 0, stream>>>(n_pairs, x, y, cache, nrows, x_stride, y_stride);
   TCRV_CUDA_TRY(cudaGetLastError());
   return TCRV_CUDA_OK;
 }

@@ -425,6 +425,66 @@ void tcrv_emitc_explicit_selected_body_dequantize_i32_to_f32_kernel_explicit_sel
   must(tcrv_cuda_host_dequantize_i32_f32(lhs, scale, out, n), __func__);
 }
 
+int tcrv_cuda_host_pack_q4_0_to_q4_0x16(size_t nblocks, const uint8_t *src, uint8_t *dst) {
+  if (nblocks == 0)
+    return TCRV_CUDA_OK;
+  if (!src || !dst)
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  HostContext &c = ctx();
+  std::lock_guard<std::mutex> lock(c.mu);
+  const size_t bytes = nblocks * 288;
+  int st = ensure_stream(c);
+  if (st == TCRV_CUDA_OK)
+    st = arena_reserve(c, 2 * up256(bytes));
+  if (st != TCRV_CUDA_OK)
+    return st;
+  uint8_t *ds = arena_take(c, bytes);
+  uint8_t *dd = arena_take(c, bytes);
+  TCRV_CUDA_TRY(cudaMemcpyAsync(ds, src, bytes, cudaMemcpyHostToDevice, c.stream));
+  st = launch_pack_q4_0_to_q4_0x16(nblocks, ds, dd, c.stream);
+  if (st != TCRV_CUDA_OK)
+    return st;
+  TCRV_CUDA_TRY(cudaMemcpyAsync(dst, dd, bytes, cudaMemcpyDeviceToHost, c.stream));
+  return finish(c);
+}
+
+void tcrv_emitc_ggml_pack_q4_0_to_q4_0x16_kernel_ggml_pack_q4_0_to_q4_0x16(size_t nblocks, const uint8_t *src,
+                                                                           uint8_t *dst) {
+  must(tcrv_cuda_host_pack_q4_0_to_q4_0x16(nblocks, src, dst), __func__);
+}
+
+int tcrv_cuda_host_rope_norm_f32(size_t n_dims, const float *x, float *y, float theta_base, float theta_scale) {
+  if (n_dims % 2 != 0)
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  if (n_dims == 0)
+    return TCRV_CUDA_OK;
+  if (!x || !y)
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  HostContext &c = ctx();
+  std::lock_guard<std::mutex> lock(c.mu);
+  int st = ensure_stream(c);
+  if (st == TCRV_CUDA_OK)
+    st = arena_reserve(c, 3 * up256(n_dims * 4));
+  if (st != TCRV_CUDA_OK)
+    return st;
+  float *dx = reinterpret_cast<float *>(arena_take(c, n_dims * 4));
+  float *dy = reinterpret_cast<float *>(arena_take(c, n_dims * 4));
+  float *dcache = reinterpret_cast<float *>(arena_take(c, n_dims * 4));
+  TCRV_CUDA_TRY(cudaMemcpyAsync(dx, x, n_dims * 4, cudaMemcpyHostToDevice, c.stream));
+  st = launch_rope_cache_f32(n_dims, theta_base, theta_scale, dcache, nullptr, c.stream);
+  if (st == TCRV_CUDA_OK)
+    st = launch_rope_apply_f32(n_dims, dx, dy, dcache, 1, n_dims, n_dims, c.stream);
+  if (st != TCRV_CUDA_OK)
+    return st;
+  TCRV_CUDA_TRY(cudaMemcpyAsync(y, dy, n_dims * 4, cudaMemcpyDeviceToHost, c.stream));
+  return finish(c);
+}
+
+void tcrv_emitc_ggml_rope_norm_f32_kernel_ggml_rope_norm_f32(size_t n_dims, const float *x, float *y, float theta_base,
+                                                             float theta_scale) {
+  must(tcrv_cuda_host_rope_norm_f32(n_dims, x, y, theta_base, theta_scale), __func__);
+}
+
 int tcrv_cuda_host_vec_scale_f32(size_t n, float *y, float v) {
   return host_forward(ForwardOp::Scale, n, y, y, v, nullptr);
 }

@@ -16,6 +16,12 @@ int launch_vec_silu_f32(size_t n, const float *x, float *y, cudaStream_t stream)
 int launch_rms_norm_f32(size_t n, const float *x, float *y, float eps, size_t nrows, size_t x_stride, size_t y_stride,
                         cudaStream_t stream);
 int launch_vec_soft_max_f32(size_t n, float *y, const float *x, float max, double *sum, cudaStream_t stream);
+int launch_rope_cache_f32(size_t n_dims, float theta_base, float theta_scale, float *cache, float *thetas,
+                          cudaStream_t stream);
+int launch_rope_apply_f32(size_t n_dims, const float *x, float *y, const float *cache, size_t nrows, size_t x_stride,
+                          size_t y_stride, cudaStream_t stream);
+int launch_pack_q4_0_to_q4_0x16(size_t nblocks, const uint8_t *src, uint8_t *dst, cudaStream_t stream);
+int launch_unpack_q4_0x16_to_q4_0(size_t nblocks, const uint8_t *src, uint8_t *dst, cudaStream_t stream);
 int launch_dequantize_i32_f32(const int32_t *lhs, float scale, float *out, size_t n, cudaStream_t stream);
 int launch_dequantize_row_q8_0(const uint8_t *vx, float *y, size_t n, cudaStream_t stream);
 int launch_dequantize_row_q4_0(const uint8_t *vx, float *y, size_t n, cudaStream_t stream);

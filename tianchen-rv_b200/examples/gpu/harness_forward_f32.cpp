@@ -1,5 +1,6 @@
 // GPU harness for the f32 forward-pass ops (fixtures test/fixtures/cuda-ggml-vec-scale-f32.mlir,
-// cuda-ggml-rms-norm-f32.mlir, cuda-ggml-vec-silu-f32.mlir, cuda-ggml-vec-soft-max-f32.mlir).
+// cuda-ggml-rms-norm-f32.mlir, cuda-ggml-vec-silu-f32.mlir, cuda-ggml-vec-soft-max-f32.mlir,
+// cuda-ggml-rope-norm-f32.mlir).
 // The scalar checks below spell the same arithmetic with <cmath>'s correctly rounded fmaf /
 // sqrtf; build with contraction off (the Makefile does) so that nothing else fuses.
 #include "harness_common.h"
@@ -9,6 +10,8 @@ void tcrv_emitc_ggml_vec_scale_f32_kernel_ggml_vec_scale_f32(size_t n, float *y,
 void tcrv_emitc_ggml_rms_norm_f32_kernel_ggml_rms_norm_f32(size_t ne00, const float *x, float *y, float eps);
 void tcrv_emitc_ggml_vec_silu_f32_kernel_ggml_vec_silu_f32(size_t n, const float *x, float *y);
 double tcrv_emitc_ggml_vec_soft_max_f32_kernel_ggml_vec_soft_max_f32(size_t n, float *y, const float *x, float max);
+void tcrv_emitc_ggml_rope_norm_f32_kernel_ggml_rope_norm_f32(size_t n_dims, const float *x, float *y, float theta_base,
+                                                             float theta_scale);
 }
 
 namespace {
@@ -103,6 +106,22 @@ int main() {
     std::printf("soft_max: sum %.17g, expected %.17g\n", got, want);
     return 1;
   }
-  std::printf("forward_f32 proof ok: scale, silu, rms_norm, soft_max over %zu elements\n", n);
+  // rope: the angle recurrence and the rotation are exact; cosf/sinf come from two different
+  // math libraries (a libm call in the reference), so the outputs agree to a few ulp of |x|
+  const size_t n_dims = 128;
+  const float theta_scale = std::pow(10000.0f, -2.0f / n_dims);
+  tcrv_emitc_ggml_rope_norm_f32_kernel_ggml_rope_norm_f32(n_dims, x.data(), y.data(), 77.0f, theta_scale);
+  float theta = 77.0f;
+  for (size_t p = 0; p < n_dims / 2; ++p) {
+    const float c = std::cos(theta), s = std::sin(theta), x0 = x[2 * p], x1 = x[2 * p + 1];
+    const float lo = std::fmaf(x0, c, -(x1 * s)), hi = std::fmaf(x0, s, x1 * c);
+    const float bound = 8.0f * 5.9604645e-8f * (std::fabs(x0) + std::fabs(x1)) + 1e-30f;
+    if (std::fabs(y[2 * p] - lo) > bound || std::fabs(y[2 * p + 1] - hi) > bound) {
+      std::printf("rope: pair %zu differs beyond the angle tolerance\n", p);
+      return 1;
+    }
+    theta = theta * theta_scale;
+  }
+  std::printf("forward_f32 proof ok: scale, silu, rms_norm, soft_max over %zu elements, rope over %zu\n", n, n_dims);
   return 0;
 }

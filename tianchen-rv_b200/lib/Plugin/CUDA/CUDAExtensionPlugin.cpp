@@ -76,6 +76,19 @@ std::vector<RouteEntry> buildTable() {
                {{"runtime-element-count", "size_t"}, {"lhs-input-buffer", "const float *"}, {"output-buffer", "uint8_t *"}},
                "quantize_row_q8_0", "cuda-ggml-quantize-row-q8_0-callable-c-abi.v1", "tcrv_cuda_quantize_row_q8_0",
                "tcrv_cuda_host_quantize_row_q8_0", "streaming-quantizer", "hbm", ""});
+  // weight repack into the reference's 16-row interleaved layout
+  t.push_back({"tcrv_rvv.pack_q4_0_to_q4_0x16",
+               withKind("ggml_pack_q4_0_to_q4_0x16",
+                        {{"qk", true, "", 32}, {"src_block_stride", true, "", 18}, {"dst_block_stride", true, "", 288},
+                         {"src_quant_byte_offset", true, "", 2}, {"dst_quant_byte_offset", true, "", 32},
+                         {"weight_interleave", true, "", 16}, {"xor_mask", true, "", 136}}),
+               "", {"tcrv_rvv.pack_q4_0_to_q4_0x16"},
+               {"lhs-input-buffer", "output-buffer", "runtime-element-count"},
+               {{"runtime-element-count", "size_t"}, {"lhs-input-buffer", "const uint8_t *"},
+                {"output-buffer", "uint8_t *"}},
+               "pack_q4_0_to_q4_0x16", "cuda-ggml-pack-q4_0-to-q4_0x16-callable-c-abi.v1",
+               "tcrv_cuda_pack_q4_0_to_q4_0x16", "tcrv_cuda_host_pack_q4_0_to_q4_0x16", "streaming-byte-permutation",
+               "hbm", ""});
   // f32 forward-pass ops around the matmul (lib/Conversion/RVV/RVVToEmitCForwardElementwise.cpp)
   t.push_back({"tcrv_rvv.ggml_vec_scale_f32", withKind("ggml_vec_scale_f32", {}), "", {"tcrv_rvv.ggml_vec_scale_f32"},
                {"output-buffer", "dequant-scale-value", "runtime-element-count"},
@@ -104,6 +117,14 @@ std::vector<RouteEntry> buildTable() {
     e.returnType = "double";
     t.push_back(e);
   }
+  t.push_back({"tcrv_rvv.ggml_rope_norm_f32", withKind("ggml_rope_norm_f32", {}), "", {"tcrv_rvv.ggml_rope_norm_f32"},
+               {"lhs-input-buffer", "output-buffer", "dequant-scale-value", "dequant-scale-value",
+                "runtime-element-count"},
+               {{"runtime-element-count", "size_t"}, {"lhs-input-buffer", "const float *"}, {"output-buffer", "float *"},
+                {"dequant-scale-value", "float"}, {"dequant-scale-value", "float"}},
+               "ggml_rope_norm_f32", "cuda-ggml-rope-norm-f32-callable-c-abi.v1",
+               "tcrv_cuda_rope_cache_f32|tcrv_cuda_rope_apply_f32", "tcrv_cuda_host_rope_norm_f32",
+               "angle-cache+pair-rotation", "hbm", ""});
   t.push_back({"tcrv_rvv.q4_0_q8_0_block_dot", withKind("ggml_q4_0_q8_0_block_dot", kQ4Q8Facts), "",
                {"tcrv_rvv.q4_0_q8_0_block_dot"},
                {"lhs-input-buffer", "rhs-input-buffer", "output-buffer", "runtime-element-count"},
