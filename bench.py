@@ -399,7 +399,7 @@ def measure_e2e(pkg, torch, layers, steps, dist):
 
 
 def measure_other_kernels(pkg, torch):
-    """The remaining kernels of the path at their BASELINE sizes, device-resident, timed with
+    """The remaining kernels of the path at their benchmark sizes, device-resident, timed with
     events over CUDA-graph replays on rotating buffers (> L2 in total): algorithmic GB/s."""
     side = torch.cuda.Stream()
     gen = torch.Generator(device="cuda").manual_seed(5)

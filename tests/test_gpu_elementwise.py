@@ -84,7 +84,7 @@ def test_quantize_q4_0_tie_in_magnitude_takes_first(cuda, pkg, O):
 
 
 def test_full_size_dequant_q8_0_config(cuda, pkg, O):
-    # BASELINE config: 4096x4096 ~ N(0, 0.02), Q8_0, dequantised to fp32, bit-exact
+    # benchmark configuration: 4096x4096 ~ N(0, 0.02), Q8_0, dequantised to fp32, bit-exact
     x = O.fill_normal(4096 * 4096, 41, 0, 0.02).reshape(4096, 4096)
     q = O.quantize_q8_0(x)
     got = pkg.dequantize_q8_0(dev(cuda, q)).cpu().numpy()

@@ -113,7 +113,7 @@ def test_gemm_workspace_errors(cuda, pkg):
 
 @pytest.mark.parametrize("nr", [11008, 32000])
 def test_gemm_prefill_config(cuda, pkg, O, nr):
-    # BASELINE config: M = 512 tokens, K = 4096, N = 11008 / 32000.  Weights are quantised on
+    # benchmark configuration: M = 512 tokens, K = 4096, N = 11008 / 32000.  Weights are quantised on
     # the GPU; the oracle consumes the same bytes on a strided row sample plus both ends.
     k, nc = 4096, 512
     gen = cuda.Generator(device="cuda").manual_seed(nr)

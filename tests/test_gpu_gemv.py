@@ -130,7 +130,7 @@ def test_padded_strides(cuda, pkg, O):
 @pytest.mark.parametrize("nr,k", [(4096, 4096), (11008, 4096), (4096, 11008), (32000, 4096)])
 @pytest.mark.parametrize("nc", [1, 8])
 def test_llama7b_shapes_q4_0(cuda, pkg, O, nr, k, nc):
-    # BASELINE config: Q4_0 x Q8_0 decode GEMV, batch 1 and 8, W ~ N(0, 0.02), x ~ N(0, 1).
+    # benchmark configuration: Q4_0 x Q8_0 decode GEMV, batch 1 and 8, W ~ N(0, 0.02), x ~ N(0, 1).
     # Weights are quantised on the GPU (that kernel is checked bit-exact elsewhere) and the
     # oracle consumes the same bytes; a row subset keeps the CPU side to seconds.
     gen = cuda.Generator(device="cuda").manual_seed(nr + k)
@@ -156,7 +156,7 @@ def test_llama7b_shapes_q4_0(cuda, pkg, O, nr, k, nc):
 
 
 def test_q8_0_gemv_config(cuda, pkg, O):
-    # BASELINE config: W 11008x4096 Q8_0, x 1x4096 ~ N(0,1): per-block int32 bit-exact, rows 1e-5
+    # benchmark configuration: W 11008x4096 Q8_0, x 1x4096 ~ N(0,1): per-block int32 bit-exact, rows 1e-5
     wf = O.fill_normal(11008 * 4096, 801, 0, 0.02).reshape(11008, 4096)
     w = O.quantize_q8_0(wf)
     x = O.quantize_q8_0(O.fill_normal(4096, 802).reshape(1, 4096))

@@ -11,6 +11,7 @@
 namespace tcrv {
 
 __device__ int g_device_error = 0;
+__device__ int *g_host_error_mirror = nullptr;
 
 namespace {
 thread_local char t_error_text[256] = "";

@@ -197,7 +197,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       }
       if (!ok) {
         *abort_flag = 1;
-        atomicOr(&g_device_error, kDevErrBarrierTimeout);
+        raise_device_error(kDevErrBarrierTimeout);
       }
       if (*abort_flag != 0) {
         // winding down after a failed wait: let this CTA's own copies land before it exits
@@ -243,7 +243,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       }
       if (!ok) {
         *abort_flag = 1;
-        atomicOr(&g_device_error, kDevErrBarrierTimeout);
+        raise_device_error(kDevErrBarrierTimeout);
       }
       // every MMA issued above must have finished before TMEM is released
       umma_commit(drain_bar);
@@ -389,7 +389,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     }
     if (!ok && lane == 0) {
       *abort_flag = 1;
-      atomicOr(&g_device_error, kDevErrBarrierTimeout);
+      raise_device_error(kDevErrBarrierTimeout);
     }
   }
 

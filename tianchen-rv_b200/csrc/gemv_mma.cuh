@@ -222,7 +222,7 @@ __global__ void __launch_bounds__(kMmaThreads, 1)
       const uint32_t bar = warp * spw + i % spw;
       if (!mbar_wait_bounded(&full[bar], (i / spw) & 1, abort_flag)) {
         if (lane == 0 && *abort_flag == 0)
-          atomicOr(&g_device_error, kDevErrBarrierTimeout);
+          raise_device_error(kDevErrBarrierTimeout);
         *abort_flag = 1;
         dead = true;
         continue;
@@ -295,7 +295,7 @@ __global__ void __launch_bounds__(kMmaThreads, 1)
     float4 *buf = partial + r * (kMmaWarps * kMmaSlotGroups * 32);
     if (!mbar_wait_bounded(&pempty[r], rphase ^ 1, abort_flag)) {
       if (lane == 0 && *abort_flag == 0)
-        atomicOr(&g_device_error, kDevErrBarrierTimeout);
+        raise_device_error(kDevErrBarrierTimeout);
       *abort_flag = 1;
       dead = true;
       continue;
@@ -313,7 +313,7 @@ __global__ void __launch_bounds__(kMmaThreads, 1)
     if (warp == (j & (kMmaWarps - 1))) {
       if (!mbar_wait_bounded(&pfull[r], rphase, abort_flag)) {
         if (lane == 0 && *abort_flag == 0)
-          atomicOr(&g_device_error, kDevErrBarrierTimeout);
+          raise_device_error(kDevErrBarrierTimeout);
         *abort_flag = 1;
         dead = true;
         continue;

@@ -269,7 +269,7 @@ __global__ void __launch_bounds__(kGemvMaxThreads, 1) gemv_stream_kernel(const G
     const uint32_t bar = warp * spw + t % spw;
     if (!mbar_wait_bounded(&full[bar], (t / spw) & 1)) {
       if (lane == 0) {
-        atomicOr(&g_device_error, kDevErrBarrierTimeout);
+        raise_device_error(kDevErrBarrierTimeout);
         // copies already issued for later slots must land before the CTA's memory goes away
         for (uint32_t u = t + 1; u < min(mine, t + spw); ++u)
           (void)mbar_wait_bounded(&full[warp * spw + u % spw], (u / spw) & 1);

@@ -11,6 +11,7 @@
 #include <stdio.h>
 #include <stdlib.h>
 
+#include <chrono>
 #include <map>
 #include <mutex>
 
@@ -33,7 +34,7 @@ struct HostContext {
   cudaStream_t stream = nullptr;
   uint8_t *arena = nullptr;
   size_t arena_cap = 0, arena_used = 0;
-  int *error_word = nullptr;  // pinned host copy of the device error word
+  int *error_word = nullptr;  // mapped host mirror of the device error word
   std::map<const void *, ResidentWeights> weights;
 };
 
@@ -44,10 +45,12 @@ HostContext &ctx() {
 
 inline size_t up256(size_t v) { return (v + 255) / 256 * 256; }
 
+int ensure_error_mirror(HostContext &c);
+
 int ensure_stream(HostContext &c) {
   if (c.stream == nullptr)
     TCRV_CUDA_TRY(cudaStreamCreateWithFlags(&c.stream, cudaStreamNonBlocking));
-  return TCRV_CUDA_OK;
+  return ensure_error_mirror(c);
 }
 
 // Makes room for `total` bytes and resets the bump pointer.  Growing frees the old arena,
@@ -84,8 +87,36 @@ int upload_rows(HostContext &c, uint8_t *dst, const void *src, size_t rows, size
   return TCRV_CUDA_OK;
 }
 
+// Waits for the context's stream.  Decode-sized calls finish within tens of microseconds, less
+// than a blocking synchronisation takes to wake the thread up, so the stream is polled for a
+// short while first.
 int finish(HostContext &c) {
-  TCRV_CUDA_TRY(cudaStreamSynchronize(c.stream));
+  const auto start = std::chrono::steady_clock::now();
+  for (;;) {
+    const cudaError_t e = cudaStreamQuery(c.stream);
+    if (e == cudaSuccess)
+      break;
+    if (e != cudaErrorNotReady)
+      TCRV_CUDA_TRY(e);
+    if (std::chrono::steady_clock::now() - start > std::chrono::microseconds(300)) {
+      TCRV_CUDA_TRY(cudaStreamSynchronize(c.stream));
+      break;
+    }
+  }
+  if (c.error_word != nullptr && *reinterpret_cast<volatile int *>(c.error_word) != 0)
+    return TCRV_CUDA_ERR_DEVICE_TIMEOUT;
+  return TCRV_CUDA_OK;
+}
+
+// Allocates the mapped host mirror of the device error word (once) and points the device at it.
+int ensure_error_mirror(HostContext &c) {
+  if (c.error_word != nullptr)
+    return TCRV_CUDA_OK;
+  TCRV_CUDA_TRY(cudaHostAlloc(reinterpret_cast<void **>(&c.error_word), sizeof(int), cudaHostAllocMapped));
+  *c.error_word = 0;
+  int *dev = nullptr;
+  TCRV_CUDA_TRY(cudaHostGetDevicePointer(reinterpret_cast<void **>(&dev), c.error_word, 0));
+  TCRV_CUDA_TRY(cudaMemcpyToSymbol(g_host_error_mirror, &dev, sizeof dev));
   return TCRV_CUDA_OK;
 }
 
@@ -209,14 +240,7 @@ int host_matmul(bool q8_weights, size_t n, float *s, const uint8_t *vx, const ui
   else
     TCRV_CUDA_TRY(cudaMemcpy2DAsync(s, bs * sizeof(float), ds, nc * sizeof(float), nc * sizeof(float), nr,
                                     cudaMemcpyDeviceToHost, c.stream));
-  // the device error word rides back on the same stream: one synchronisation per call
-  if (c.error_word == nullptr)
-    TCRV_CUDA_TRY(cudaHostAlloc(reinterpret_cast<void **>(&c.error_word), sizeof(int), cudaHostAllocDefault));
-  TCRV_CUDA_TRY(cudaMemcpyFromSymbolAsync(c.error_word, g_device_error, sizeof(int), 0, cudaMemcpyDeviceToHost, c.stream));
-  st = finish(c);
-  if (st != TCRV_CUDA_OK)
-    return st;
-  return *c.error_word != 0 ? TCRV_CUDA_ERR_DEVICE_TIMEOUT : TCRV_CUDA_OK;
+  return finish(c);  // also reports a device-side wait that expired (host mirror of the error word)
 }
 
 // One f32 vector in, one out (in == out for the in-place scale); `sum` receives the soft-max
@@ -335,8 +359,11 @@ int tcrv_cuda_host_release(void) {
     (void)cudaFree(c.arena);
   c.arena = nullptr;
   c.arena_cap = c.arena_used = 0;
-  if (c.error_word)
+  if (c.error_word) {
+    int *none = nullptr;
+    (void)cudaMemcpyToSymbol(g_host_error_mirror, &none, sizeof none);
     (void)cudaFreeHost(c.error_word);
+  }
   c.error_word = nullptr;
   return TCRV_CUDA_OK;
 }

@@ -18,7 +18,21 @@ constexpr int kNumSMsB200 = 148;
 // Device-side error word: kernels with bounded waits OR a code into it when a wait
 // expires.  Read and cleared by tcrv_cuda_check_device_errors().
 extern __device__ int g_device_error;
+// Optional mirror of the error word in mapped host memory (set by the host-pointer layer, null
+// otherwise): a failed wait also stores its code there, so a synchronous caller learns of it
+// from the stream synchronisation it does anyway instead of a device-to-host copy per call.
+extern __device__ int *g_host_error_mirror;
 constexpr int kDevErrBarrierTimeout = 1;
+
+// What a kernel calls when one of its bounded waits expires.
+__device__ __forceinline__ void raise_device_error(int code) {
+  atomicOr(&g_device_error, code);
+  int *mirror = g_host_error_mirror;
+  if (mirror != nullptr) {
+    *reinterpret_cast<volatile int *>(mirror) = code;
+    __threadfence_system();
+  }
+}
 
 // Records a failing CUDA runtime call for tcrv_cuda_last_error_text().
 int record_cuda_error(cudaError_t err, const char *what);

@@ -5,7 +5,7 @@ extern "C" void tcrv_emitc_explicit_selected_body_add_f32_kernel_explicit_select
     const float *lhs, const float *rhs, float *out, size_t n);
 
 int main() {
-  const size_t n = 1048576 + 7;  // BASELINE size plus a ragged tail
+  const size_t n = 1048576 + 7;  // the benchmark size plus a ragged tail
   std::vector<float> lhs(n), rhs(n), out(n, 0.f);
   harness::Rng rng(1);
   for (size_t i = 0; i < n; ++i)
