@@ -213,36 +213,65 @@ __device__ __forceinline__ uint32_t narrow_q8(float v) {
   return static_cast<uint32_t>(r) & 0xffu;
 }
 
+// A warp quantises 16 consecutive blocks per iteration: lane l holds elements 4*(l%8).. of
+// block l/8 of each of 4 groups (four 16-byte loads in flight per lane).  The 16 x 34 output
+// bytes are contiguous in memory; they are assembled in shared memory and leave as 32-bit
+// words (2-byte stores only when the destination is not 4-byte aligned).
+constexpr int kQ8GroupsPerIter = 4;
+constexpr int kQ8IterBlocks = 4 * kQ8GroupsPerIter;         // 16
+constexpr int kQ8IterBytes = kQ8IterBlocks * kQ8Block;      // 544
+
 template <bool kAlignedIn>
 __global__ void __launch_bounds__(kThreads) quantize_q8_0_kernel(const float *__restrict__ x,
                                                                  uint8_t *__restrict__ vy, size_t nblocks,
                                                                  bool out_aligned2) {
+  __shared__ __align__(16) uint8_t stage_all[kThreads / 32][kQ8IterBytes];
   const int lane = threadIdx.x & 31;
-  const int sub = lane & 7;
+  const int sub = lane & 7, blk_in_group = lane >> 3;
+  uint8_t *stage = stage_all[threadIdx.x >> 5];
   const size_t warp = (static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x) >> 5;
   const size_t nwarps = (static_cast<size_t>(gridDim.x) * kThreads) >> 5;
-  const size_t ngroups = (nblocks + 3) / 4;
-  for (size_t g = warp; g < ngroups; g += nwarps) {
-    const size_t ib = g * 4 + (lane >> 3);
-    const bool live = ib < nblocks;
-    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (live)
-      v = load_x4<kAlignedIn>(x + ib * kQK + 4 * sub);
-    float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
-    const float d = __fdiv_rn(amax, 127.0f);
-    const float id = d != 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
-    if (live) {
-      uint8_t *yb = vy + ib * kQ8Block;
-      if (sub == 0)
-        store_u16(yb, __half_as_ushort(__float2half_rn(d)), out_aligned2);
-      const uint32_t q01 = narrow_q8(__fmul_rn(v.x, id)) | (narrow_q8(__fmul_rn(v.y, id)) << 8);
-      const uint32_t q23 = narrow_q8(__fmul_rn(v.z, id)) | (narrow_q8(__fmul_rn(v.w, id)) << 8);
-      store_u16(yb + 2 + 4 * sub, q01, out_aligned2);
-      store_u16(yb + 4 + 4 * sub, q23, out_aligned2);
+  const bool out_aligned4 = (reinterpret_cast<uintptr_t>(vy) & 3u) == 0;
+  for (size_t b0 = warp * kQ8IterBlocks; b0 < nblocks; b0 += nwarps * kQ8IterBlocks) {
+    float4 v[kQ8GroupsPerIter];
+#pragma unroll
+    for (int u = 0; u < kQ8GroupsPerIter; ++u) {
+      const size_t ib = b0 + u * 4 + blk_in_group;
+      v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (ib < nblocks)
+        v[u] = load_x4<kAlignedIn>(x + ib * kQK + 4 * sub);
     }
+#pragma unroll
+    for (int u = 0; u < kQ8GroupsPerIter; ++u) {
+      float amax = fmaxf(fmaxf(fabsf(v[u].x), fabsf(v[u].y)), fmaxf(fabsf(v[u].z), fabsf(v[u].w)));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+      const float d = __fdiv_rn(amax, 127.0f);
+      const float id = d != 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
+      uint8_t *yb = stage + (u * 4 + blk_in_group) * kQ8Block;  // 2-byte aligned
+      if (sub == 0)
+        *reinterpret_cast<unsigned short *>(yb) = __half_as_ushort(__float2half_rn(d));
+      const uint32_t q01 = narrow_q8(__fmul_rn(v[u].x, id)) | (narrow_q8(__fmul_rn(v[u].y, id)) << 8);
+      const uint32_t q23 = narrow_q8(__fmul_rn(v[u].z, id)) | (narrow_q8(__fmul_rn(v[u].w, id)) << 8);
+      *reinterpret_cast<unsigned short *>(yb + 2 + 4 * sub) = static_cast<unsigned short>(q01);
+      *reinterpret_cast<unsigned short *>(yb + 4 + 4 * sub) = static_cast<unsigned short>(q23);
+    }
+    __syncwarp();
+    const size_t left = nblocks - b0;
+    const uint32_t bytes = static_cast<uint32_t>(left < static_cast<size_t>(kQ8IterBlocks) ? left : kQ8IterBlocks) * kQ8Block;
+    uint8_t *dst = vy + b0 * kQ8Block;  // b0 is a multiple of 16: dst - vy is a multiple of 544
+    if (out_aligned4) {
+      const uint32_t words = bytes / 4;
+      for (uint32_t w = lane; w < words; w += 32)
+        reinterpret_cast<uint32_t *>(dst)[w] = reinterpret_cast<const uint32_t *>(stage)[w];
+      if ((bytes & 2u) != 0 && lane == 0)
+        *reinterpret_cast<unsigned short *>(dst + words * 4) = *reinterpret_cast<const unsigned short *>(stage + words * 4);
+    } else {
+      for (uint32_t h = lane; h < bytes / 2; h += 32)
+        store_u16(dst + 2 * h, *reinterpret_cast<const unsigned short *>(stage + 2 * h), out_aligned2);
+    }
+    __syncwarp();
   }
 }
 
@@ -463,7 +492,7 @@ int launch_quantize_row_q8_0(size_t n, const float *x, uint8_t *vy, cudaStream_t
   if (n == 0)
     return TCRV_CUDA_OK;
   const size_t nblocks = n / kQK;
-  const int grid = grid_for(nblocks, (kThreads / 32) * 4 * 4, 8);
+  const int grid = grid_for(nblocks, (kThreads / 32) * kQ8IterBlocks * 2, 8);
   if (aligned16(x))
     quantize_q8_0_kernel<true><<<grid, kThreads, 0, stream>>>(x, vy, nblocks, aligned2(vy));
   else
