@@ -161,6 +161,31 @@ int tcrv_cuda_gemm_q4_0_q8_0_prepared(size_t n, float *s, const void *prepared_w
                                       size_t by, size_t nr, size_t nc, size_t bs, void *workspace,
                                       size_t workspace_bytes, unsigned flags, tcrv_cuda_stream stream);
 
+/* ---- sibling block formats: Q4_1 x Q8_1, Q5_0 x Q8_0, Q5_1 x Q8_1 -------------------------
+ * block_q4_1 20 B (fp16 d, fp16 m, 16 nibble bytes, unsigned nibbles), block_q5_0 22 B (fp16 d,
+ * 32-bit qh, 16 nibble bytes; value = (nibble | bit << 4) - 16), block_q5_1 24 B (d, m, qh,
+ * nibbles; value 0..31), block_q8_1 36 B (fp16 d, fp16 s = d * sum(q), 32 int8).  Replaces
+ * tcrv_rvv.q4_1_q8_1_block_dot, q5_0_q8_0_block_dot, q5_1_q8_1_block_dot
+ * (include/TianChenRV/Dialect/RVV/IR/RVVOps.td:5247-5358, 5359-5480, 5957-6080; emitters
+ * lib/Conversion/RVV/RVVToEmitCBlockQuantLinear.cpp:6817-7263, 472-915, 916-1391): per-block
+ * int32 sums bit-exact, fp32 rows folded in strict ascending block order,
+ *   Q5_0:        sumf = fma(d_x*d_y, (float)sumi, sumf)
+ *   Q4_1, Q5_1:  sumf = sumf + fma(d_x*d_y, (float)sumi, m_x*s_y),
+ * i.e. bit-identical to the sequential fold.  `dot_rows` is the matrix form
+ * (s[row*bs + col], strides as in tcrv_cuda_gemv_*); the vec_dot entries are the reference's
+ * one-row kernels (ABI order n, s, vx, vy).  These run on a general warp-per-output kernel,
+ * not on the streaming kernels of the Q4_0/Q8_0 path. */
+#define TCRV_CUDA_FORMAT_Q4_1_Q8_1 1
+#define TCRV_CUDA_FORMAT_Q5_0_Q8_0 2
+#define TCRV_CUDA_FORMAT_Q5_1_Q8_1 3
+int tcrv_cuda_sibling_dot_rows(int format, size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by,
+                               size_t nr, size_t nc, size_t bx, size_t bs, tcrv_cuda_stream stream);
+int tcrv_cuda_sibling_block_sums(int format, size_t n, int32_t *sumi, const uint8_t *vx, const uint8_t *vy, size_t by,
+                                 size_t nr, size_t nc, size_t bx, tcrv_cuda_stream stream);
+int tcrv_cuda_vec_dot_q4_1_q8_1(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, tcrv_cuda_stream stream);
+int tcrv_cuda_vec_dot_q5_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, tcrv_cuda_stream stream);
+int tcrv_cuda_vec_dot_q5_1_q8_1(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, tcrv_cuda_stream stream);
+
 /* The reference's 16-row interleaved weight layout (block_q4_0x16, 288 bytes: 16 fp16 scales,
  * then quant byte `off` of the 16 source blocks side by side, xor 0x88), as a device repack:
  * `pack` replaces tcrv_rvv.pack_q4_0_to_q4_0x16 (lib/Conversion/RVV/RVVToEmitCBlockQuantLinear.cpp:

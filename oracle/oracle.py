@@ -69,6 +69,8 @@ def _declare(L: ctypes.CDLL) -> None:
     L.tcrv_oracle_rope_thetas.argtypes = [_sz, ctypes.c_float, ctypes.c_float, _p]
     L.tcrv_oracle_pack_q4_0_to_q4_0x16.argtypes = [_sz, _p, _p]
     L.tcrv_oracle_unpack_q4_0x16_to_q4_0.argtypes = [_sz, _p, _p]
+    L.tcrv_oracle_sibling_block_sums.argtypes = [ctypes.c_int, _sz, _p, _p, _p]
+    L.tcrv_oracle_sibling_vec_dot.argtypes = [ctypes.c_int, _sz, _p, _p, _p, ctypes.c_int]
     L.tcrv_oracle_fill_uniform.argtypes = [_p, _sz, ctypes.c_uint64, ctypes.c_float, ctypes.c_float]
     L.tcrv_oracle_fill_normal.argtypes = [_p, _sz, ctypes.c_uint64, ctypes.c_float, ctypes.c_float]
     L.tcrv_oracle_add_f32.argtypes = [_p, _p, _p, _sz]
@@ -254,6 +256,31 @@ def unpack_q4_0x16_to_q4_0(src: np.ndarray) -> np.ndarray:
     dst = np.empty_like(src)
     lib().tcrv_oracle_unpack_q4_0x16_to_q4_0(src.size // 288, _ptr(src), _ptr(dst))
     return dst
+
+
+FORMAT_Q4_1_Q8_1, FORMAT_Q5_0_Q8_0, FORMAT_Q5_1_Q8_1 = 1, 2, 3
+SIBLING_STRIDES = {1: (20, 36), 2: (22, 34), 3: (24, 36)}  # (weight, activation) block bytes
+
+
+def sibling_block_sums(fmt: int, w_row: np.ndarray, x_row: np.ndarray) -> np.ndarray:
+    w_row, x_row = np.ascontiguousarray(w_row, dtype=np.uint8), np.ascontiguousarray(x_row, dtype=np.uint8)
+    nb = w_row.size // SIBLING_STRIDES[fmt][0]
+    out = np.empty(nb, dtype=np.int32)
+    lib().tcrv_oracle_sibling_block_sums(fmt, nb * QK, _ptr(out), _ptr(w_row), _ptr(x_row))
+    return out
+
+
+def sibling_dot_rows(fmt: int, w: np.ndarray, x: np.ndarray, fold: int = FOLD_FMA) -> np.ndarray:
+    """out[row, col] = block dot of weight row `row` and activation column `col`."""
+    w, x = np.ascontiguousarray(w, dtype=np.uint8), np.ascontiguousarray(x, dtype=np.uint8)
+    nb = w.shape[1] // SIBLING_STRIDES[fmt][0]
+    out = np.empty((w.shape[0], x.shape[0]), dtype=np.float32)
+    one = np.empty(1, dtype=np.float32)
+    for r in range(w.shape[0]):
+        for c in range(x.shape[0]):
+            lib().tcrv_oracle_sibling_vec_dot(fmt, nb * QK, _ptr(one), _ptr(w[r]), _ptr(x[c]), fold)
+            out[r, c] = one[0]
+    return out
 
 
 def decode_nibbles(byte: int) -> tuple[int, int]:

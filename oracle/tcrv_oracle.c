@@ -604,3 +604,70 @@ void tcrv_oracle_unpack_q4_0x16_to_q4_0(size_t nblocks, const uint8_t *src, uint
         dst[dbase + blk * 18 + 2 + off] = (uint8_t)(src[sbase + 32 + off * 16 + blk] ^ 0x88);
   }
 }
+
+/* ---- sibling block formats ------------------------------------------------------------- */
+
+typedef struct {
+  size_t wstride, astride, wq, aq, qh, has_min;
+} sibling_layout;
+
+static int sibling_get(int format, sibling_layout *l) {
+  switch (format) {
+    case TCRV_ORACLE_FORMAT_Q4_1_Q8_1: *l = (sibling_layout){20, 36, 4, 4, 0, 1}; return 1;
+    case TCRV_ORACLE_FORMAT_Q5_0_Q8_0: *l = (sibling_layout){22, 34, 6, 2, 2, 0}; return 1;
+    case TCRV_ORACLE_FORMAT_Q5_1_Q8_1: *l = (sibling_layout){24, 36, 8, 4, 4, 1}; return 1;
+    default: return 0;
+  }
+}
+
+static uint16_t read_u16(const uint8_t *p) { return (uint16_t)(p[0] | (p[1] << 8)); }
+
+static int32_t sibling_sumi(int format, const sibling_layout *l, const uint8_t *xb, const uint8_t *yb) {
+  uint32_t qh = 0;
+  if (l->qh)
+    qh = (uint32_t)read_u16(xb + l->qh) | ((uint32_t)read_u16(xb + l->qh + 2) << 16);
+  int32_t sumi = 0;
+  for (int j = 0; j < 16; ++j) {
+    int lo = xb[l->wq + j] & 0x0f, hi = xb[l->wq + j] >> 4;
+    if (l->qh) {
+      lo |= (int)((qh >> j) & 1u) << 4;
+      hi |= (int)((qh >> (j + 16)) & 1u) << 4;
+    }
+    if (format == TCRV_ORACLE_FORMAT_Q5_0_Q8_0) {
+      lo -= 16;
+      hi -= 16;
+    }
+    sumi += lo * (int8_t)yb[l->aq + j] + hi * (int8_t)yb[l->aq + 16 + j];
+  }
+  return sumi;
+}
+
+void tcrv_oracle_sibling_block_sums(int format, size_t n, int32_t *sumi, const uint8_t *vx, const uint8_t *vy) {
+  sibling_layout l;
+  if (!sibling_get(format, &l))
+    return;
+  for (size_t ib = 0; ib < n / 32; ++ib)
+    sumi[ib] = sibling_sumi(format, &l, vx + ib * l.wstride, vy + ib * l.astride);
+}
+
+void tcrv_oracle_sibling_vec_dot(int format, size_t n, float *s, const uint8_t *vx, const uint8_t *vy, int fold) {
+  sibling_layout l;
+  if (!sibling_get(format, &l))
+    return;
+  float sumf = 0.0f;
+  for (size_t ib = 0; ib < n / 32; ++ib) {
+    const uint8_t *xb = vx + ib * l.wstride, *yb = vy + ib * l.astride;
+    const float dx = tcrv_oracle_fp16_to_fp32(read_u16(xb)), dy = tcrv_oracle_fp16_to_fp32(read_u16(yb));
+    const float fs = (float)sibling_sumi(format, &l, xb, yb);
+    const float p = dx * dy;
+    if (l.has_min) {
+      const float mx = tcrv_oracle_fp16_to_fp32(read_u16(xb + 2)), sy = tcrv_oracle_fp16_to_fp32(read_u16(yb + 2));
+      const float ms = mx * sy;
+      const float t = fold == TCRV_FOLD_FMA ? fmaf(p, fs, ms) : p * fs + ms;
+      sumf = sumf + t;
+    } else {
+      sumf = fold == TCRV_FOLD_FMA ? fmaf(p, fs, sumf) : sumf + p * fs;
+    }
+  }
+  *s = sumf;
+}

@@ -63,6 +63,25 @@ void tcrv_oracle_quantize_row_q8_0(const float *x, uint8_t *vy, size_t n);
  * to 15, element j in the low nibble of byte j and element j+16 in the high nibble. */
 void tcrv_oracle_quantize_row_q4_0(const float *x, uint8_t *vx, size_t n);
 
+/* ---- sibling block formats ------------------------------------------------------------
+ * format: 1 = Q4_1 x Q8_1, 2 = Q5_0 x Q8_0, 3 = Q5_1 x Q8_1 (TCRV_ORACLE_FORMAT_*).
+ *   block_q4_1 20 B: fp16 d @0, fp16 m @2, 16 nibble bytes @4 (unsigned nibbles 0..15)
+ *   block_q5_0 22 B: fp16 d @0, 32-bit qh @2, 16 nibble bytes @6; value = (nibble | bit<<4) - 16,
+ *                    bit of element j = bit j of qh (elements 16..31: bits 16..31)
+ *   block_q5_1 24 B: fp16 d @0, fp16 m @2, qh @4, nibbles @8; value = nibble | bit<<4 (0..31)
+ *   block_q8_1 36 B: fp16 d @0, fp16 s @2 (the precomputed d * sum(q)), 32 int8 @4
+ * (include/TianChenRV/Dialect/RVV/IR/RVVOps.td:5247-5358, :5359-5480, :5957-6080; emitters
+ * lib/Conversion/RVV/RVVToEmitCBlockQuantLinear.cpp:6817-7263, :472-915, :916-1391).
+ * Folds, ascending blocks:  Q5_0: sumf = sumf + (d_x*d_y)*(float)sumi;
+ *   Q4_1, Q5_1: sumf = sumf + ((d_x*d_y)*(float)sumi + m_x*s_y)  (the two products are added
+ *   first).  TCRV_FOLD_FMA is what one C expression contracts to: fma(d_x*d_y, sumi, sumf),
+ *   resp. sumf + fma(d_x*d_y, sumi, m_x*s_y); TCRV_FOLD_NOFMA rounds every operator. */
+#define TCRV_ORACLE_FORMAT_Q4_1_Q8_1 1
+#define TCRV_ORACLE_FORMAT_Q5_0_Q8_0 2
+#define TCRV_ORACLE_FORMAT_Q5_1_Q8_1 3
+void tcrv_oracle_sibling_block_sums(int format, size_t n, int32_t *sumi, const uint8_t *vx, const uint8_t *vy);
+void tcrv_oracle_sibling_vec_dot(int format, size_t n, float *s, const uint8_t *vx, const uint8_t *vy, int fold);
+
 /* ---- forward-pass f32 ops next to the quantized matmul -------------------------------- */
 
 /* tcrv_rvv.ggml_vec_scale_f32, y[i] *= v in place (one f32 multiply per element):

@@ -1,6 +1,7 @@
 """CPU tests of the oracle itself: hand-computed cases, format identities and the one numeric
 fixture the reference ships (the i32 add harness)."""
 import numpy as np
+import pytest
 
 
 def f16(v):
@@ -276,3 +277,50 @@ def test_q4_0x16_pack_layout_and_inverse(O):
             for blk in range(16):
                 assert dst[288 * b + 32 + off * 16 + blk] == src[(16 * b + blk) * 18 + 2 + off] ^ 0x88
     assert np.array_equal(O.unpack_q4_0x16_to_q4_0(dst), src)
+
+
+@pytest.mark.parametrize("fmt", [1, 2, 3])
+def test_sibling_formats_integer_stage_and_folds(O, fmt):
+    import sibling_data as sd
+
+    w, x = sd.make(fmt, 3, 2, 40, 500 + fmt)
+    for r in range(3):
+        for c in range(2):
+            assert np.array_equal(O.sibling_block_sums(fmt, w[r], x[c]), sd.block_sums_numpy(fmt, w[r], x[c]))
+    # the fold, restated in numpy float32 for the every-operator-rounds reading
+    wb, ab = sd.STRIDES[fmt]
+    sums = sd.block_sums_numpy(fmt, w[1], x[0])
+    wv, xv = w[1].reshape(-1, wb), x[0].reshape(-1, ab)
+    dx = wv[:, 0:2].copy().view(np.float16).astype(np.float32)[:, 0]
+    dy = xv[:, 0:2].copy().view(np.float16).astype(np.float32)[:, 0]
+    acc = np.float32(0)
+    for b in range(40):
+        p = np.float32(dx[b] * dy[b])
+        if fmt == 2:
+            acc = np.float32(acc + np.float32(p * np.float32(sums[b])))
+        else:
+            mx = wv[b, 2:4].copy().view(np.float16).astype(np.float32)[0]
+            sy = xv[b, 2:4].copy().view(np.float16).astype(np.float32)[0]
+            acc = np.float32(acc + np.float32(np.float32(p * np.float32(sums[b])) + np.float32(mx * sy)))
+    assert O.sibling_dot_rows(fmt, w[1:2], x[0:1], fold=O.FOLD_NOFMA)[0, 0] == acc
+    fused = O.sibling_dot_rows(fmt, w, x, fold=O.FOLD_FMA)
+    plain = O.sibling_dot_rows(fmt, w, x, fold=O.FOLD_NOFMA)
+    assert np.allclose(fused, plain, rtol=1e-5, atol=1e-4) and fused.shape == (3, 2)
+
+
+def test_sibling_formats_extreme_values(O):
+    import sibling_data as sd
+
+    # Q5_0: all nibbles 0 and all high bits 0 -> every weight -16; activations -128 -> +65536 per block
+    w = np.zeros((1, 22), np.uint8)
+    w[0, 0:2] = np.array([1.0], np.float16).view(np.uint8)
+    x = np.full((1, 34), 0x80, np.uint8)
+    x[0, 0:2] = np.array([1.0], np.float16).view(np.uint8)
+    assert O.sibling_block_sums(2, w[0], x[0])[0] == 16 * 128 * 32
+    # Q5_1: all bits set -> every weight 31; activations 127
+    w = np.full((1, 24), 0xFF, np.uint8)
+    w[0, 0:4] = np.array([1.0, 0.0], np.float16).view(np.uint8)
+    x = np.full((1, 36), 0x7F, np.uint8)
+    x[0, 0:4] = np.array([1.0, 0.0], np.float16).view(np.uint8)
+    assert O.sibling_block_sums(3, w[0], x[0])[0] == 31 * 127 * 32
+    assert O.sibling_dot_rows(3, w, x)[0, 0] == np.float32(31 * 127 * 32)

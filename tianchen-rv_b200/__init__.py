@@ -61,6 +61,11 @@ ABI = {
     "tcrv_cuda_rope_apply_f32": [_sz, _p, _p, _p, _sz, _sz, _sz, _p],
     "tcrv_cuda_pack_q4_0_to_q4_0x16": [_sz, _p, _p, _p],
     "tcrv_cuda_unpack_q4_0x16_to_q4_0": [_sz, _p, _p, _p],
+    "tcrv_cuda_sibling_dot_rows": [ctypes.c_int, _sz, _p, _p, _p, _sz, _sz, _sz, _sz, _sz, _p],
+    "tcrv_cuda_sibling_block_sums": [ctypes.c_int, _sz, _p, _p, _p, _sz, _sz, _sz, _sz, _p],
+    "tcrv_cuda_vec_dot_q4_1_q8_1": [_sz, _p, _p, _p, _p],
+    "tcrv_cuda_vec_dot_q5_0_q8_0": [_sz, _p, _p, _p, _p],
+    "tcrv_cuda_vec_dot_q5_1_q8_1": [_sz, _p, _p, _p, _p],
     "tcrv_cuda_peer_alloc": [_sz, _p],
     "tcrv_cuda_peer_free": [_p],
     "tcrv_cuda_peer_export": [_p, _p],
@@ -384,6 +389,41 @@ def unpack_q4_0x16_to_q4_0(src, out=None):
         out = torch.empty_like(src)
     _check(lib().tcrv_cuda_unpack_q4_0x16_to_q4_0(src.numel() // 288, _dev(src, torch.uint8), _dev(out, torch.uint8),
                                                   _stream()), "tcrv_cuda_unpack_q4_0x16_to_q4_0")
+    return out
+
+
+# ------------------------------------------------------------------ sibling block formats
+
+FORMAT_Q4_1_Q8_1, FORMAT_Q5_0_Q8_0, FORMAT_Q5_1_Q8_1 = 1, 2, 3
+SIBLING_STRIDES = {1: (20, 36), 2: (22, 34), 3: (24, 36)}  # (weight, activation) block bytes
+
+
+def sibling_dot_rows(fmt: int, w, x, out=None):
+    """out[row, col] = block dot of weight row `row` (format's weight blocks) and activation
+    column `col` (Q8_0 or Q8_1 blocks), folded in strict ascending block order."""
+    import torch
+
+    wb, ab = SIBLING_STRIDES[fmt]
+    if w.shape[1] % wb or x.shape[1] % ab or w.shape[1] // wb != x.shape[1] // ab:
+        raise ValueError("row bytes do not match the format's block sizes")
+    n, nr, nc = w.shape[1] // wb * QK, w.shape[0], x.shape[0]
+    if out is None:
+        out = torch.empty((nr, nc), dtype=torch.float32, device=w.device)
+    _check(lib().tcrv_cuda_sibling_dot_rows(fmt, n, _dev(out, torch.float32), _dev(w, torch.uint8), _dev(x, torch.uint8),
+                                            x.stride(0), nr, nc, w.stride(0), out.stride(0), _stream()),
+           "tcrv_cuda_sibling_dot_rows")
+    return out
+
+
+def sibling_block_sums(fmt: int, w, x):
+    import torch
+
+    wb, ab = SIBLING_STRIDES[fmt]
+    nb, nr, nc = w.shape[1] // wb, w.shape[0], x.shape[0]
+    out = torch.empty((nr, nc, nb), dtype=torch.int32, device=w.device)
+    _check(lib().tcrv_cuda_sibling_block_sums(fmt, nb * QK, out.data_ptr(), _dev(w, torch.uint8), _dev(x, torch.uint8),
+                                              x.stride(0), nr, nc, w.stride(0), _stream()),
+           "tcrv_cuda_sibling_block_sums")
     return out
 
 

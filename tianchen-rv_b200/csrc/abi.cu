@@ -334,6 +334,53 @@ int tcrv_cuda_unpack_q4_0x16_to_q4_0(size_t nblocks, const uint8_t *src, uint8_t
   return launch_unpack_q4_0x16_to_q4_0(nblocks, src, dst, as_stream(stream));
 }
 
+namespace {
+int check_sibling_args(int format, size_t n, const void *out, const void *vx, const void *vy, size_t by, size_t nr,
+                       size_t nc, size_t bx, size_t out_stride) {
+  size_t wb = 0, ab = 0;
+  if (sibling_block_bytes(format, &wb, &ab) != TCRV_CUDA_OK || n % TCRV_QK != 0)
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  if (nr == 0 || nc == 0)
+    return TCRV_CUDA_OK;
+  if (!out || !vx || !vy)
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  const size_t nb = n / TCRV_QK;
+  if (nb > 0xffffffffull / 64 || nr > 0xffffffffull || nc > 0xffffffffull)
+    return TCRV_CUDA_ERR_UNSUPPORTED;
+  if ((nr > 1 && bx < nb * wb) || (nc > 1 && by < nb * ab) || (nr > 1 && out_stride < nc))
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  return TCRV_CUDA_OK;
+}
+}  // namespace
+
+int tcrv_cuda_sibling_dot_rows(int format, size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by,
+                               size_t nr, size_t nc, size_t bx, size_t bs, tcrv_cuda_stream stream) {
+  const int st = check_sibling_args(format, n, s, vx, vy, by, nr, nc, bx, bs);
+  if (st != TCRV_CUDA_OK)
+    return st;
+  return launch_sibling_dot(format, n, s, nullptr, vx, vy, by, nr, nc, bx, bs, as_stream(stream));
+}
+
+int tcrv_cuda_sibling_block_sums(int format, size_t n, int32_t *sumi, const uint8_t *vx, const uint8_t *vy, size_t by,
+                                 size_t nr, size_t nc, size_t bx, tcrv_cuda_stream stream) {
+  const int st = check_sibling_args(format, n, sumi, vx, vy, by, nr, nc, bx, nc);
+  if (st != TCRV_CUDA_OK)
+    return st;
+  return launch_sibling_dot(format, n, nullptr, sumi, vx, vy, by, nr, nc, bx, nc, as_stream(stream));
+}
+
+int tcrv_cuda_vec_dot_q4_1_q8_1(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, tcrv_cuda_stream stream) {
+  return tcrv_cuda_sibling_dot_rows(TCRV_CUDA_FORMAT_Q4_1_Q8_1, n, s, vx, vy, 0, 1, 1, 0, 1, stream);
+}
+
+int tcrv_cuda_vec_dot_q5_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, tcrv_cuda_stream stream) {
+  return tcrv_cuda_sibling_dot_rows(TCRV_CUDA_FORMAT_Q5_0_Q8_0, n, s, vx, vy, 0, 1, 1, 0, 1, stream);
+}
+
+int tcrv_cuda_vec_dot_q5_1_q8_1(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, tcrv_cuda_stream stream) {
+  return tcrv_cuda_sibling_dot_rows(TCRV_CUDA_FORMAT_Q5_1_Q8_1, n, s, vx, vy, 0, 1, 1, 0, 1, stream);
+}
+
 int tcrv_cuda_peer_alloc(size_t bytes, void **ptr) {
   if (!ptr || bytes == 0)
     return TCRV_CUDA_ERR_INVALID_ARGUMENT;

@@ -22,6 +22,11 @@ int launch_rope_apply_f32(size_t n_dims, const float *x, float *y, const float *
                           size_t y_stride, cudaStream_t stream);
 int launch_pack_q4_0_to_q4_0x16(size_t nblocks, const uint8_t *src, uint8_t *dst, cudaStream_t stream);
 int launch_unpack_q4_0x16_to_q4_0(size_t nblocks, const uint8_t *src, uint8_t *dst, cudaStream_t stream);
+// sibling block formats (siblings.cu): format 1 = Q4_1 x Q8_1, 2 = Q5_0 x Q8_0, 3 = Q5_1 x Q8_1;
+// `sums` != null selects the integer stage (sumi[row][col][block]) instead of the fp32 rows.
+int sibling_block_bytes(int format, size_t *weight, size_t *activation);
+int launch_sibling_dot(int format, size_t n, float *s, int32_t *sums, const uint8_t *vx, const uint8_t *vy, size_t by,
+                       size_t nr, size_t nc, size_t bx, size_t bs, cudaStream_t stream);
 int launch_dequantize_i32_f32(const int32_t *lhs, float scale, float *out, size_t n, cudaStream_t stream);
 int launch_dequantize_row_q8_0(const uint8_t *vx, float *y, size_t n, cudaStream_t stream);
 int launch_dequantize_row_q4_0(const uint8_t *vx, float *y, size_t n, cudaStream_t stream);

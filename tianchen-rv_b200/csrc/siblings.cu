@@ -1,0 +1,166 @@
+// Block dots of the sibling ggml formats the reference also compiles: Q4_1 x Q8_1, Q5_0 x Q8_0
+// and Q5_1 x Q8_1.  One warp per (weight row, activation column); every lane computes one block
+// of a group of 32 (byte-granular loads: no alignment assumptions), then the 32 terms are folded
+// one after another in ascending block order, so the result is the sequential fold bit for bit.
+//   Q5_0:        sumf = fma(d_x*d_y, (float)sumi, sumf)
+//   Q4_1, Q5_1:  sumf = sumf + fma(d_x*d_y, (float)sumi, m_x*s_y)
+// (the contraction one C expression gets; lib/Conversion/RVV/RVVToEmitCBlockQuantLinear.cpp:
+// 6817-7263, 472-915, 916-1391).
+#include "launchers.h"
+#include "tcrv_common.cuh"
+
+namespace tcrv {
+
+namespace {
+
+template <int kFormat>
+struct Sibling;
+template <>
+struct Sibling<1> {  // Q4_1 x Q8_1
+  static constexpr int kW = 20, kA = 36, kWq = 4, kAq = 4, kQh = 0;
+  static constexpr bool kMin = true, kBias16 = false;
+};
+template <>
+struct Sibling<2> {  // Q5_0 x Q8_0
+  static constexpr int kW = 22, kA = 34, kWq = 6, kAq = 2, kQh = 2;
+  static constexpr bool kMin = false, kBias16 = true;
+};
+template <>
+struct Sibling<3> {  // Q5_1 x Q8_1
+  static constexpr int kW = 24, kA = 36, kWq = 8, kAq = 4, kQh = 4;
+  static constexpr bool kMin = true, kBias16 = false;
+};
+
+// int32 dot of one block: 5-bit (or 4-bit) weights against int8 activations.
+template <int kFormat>
+__device__ __forceinline__ int sibling_sumi(const uint8_t *xb, const uint8_t *yb) {
+  using F = Sibling<kFormat>;
+  uint32_t qh = 0;
+  if constexpr (F::kQh != 0)
+    qh = load_u16(xb + F::kQh) | (load_u16(xb + F::kQh + 2) << 16);
+  int sumi = 0, ysum = 0;
+#pragma unroll
+  for (int w = 0; w < 4; ++w) {
+    const uint32_t q = load_u32_bytes(xb + F::kWq + 4 * w);   // nibble bytes 4w..4w+3
+    uint32_t lo = q & 0x0f0f0f0fu, hi = (q >> 4) & 0x0f0f0f0fu;
+    if constexpr (F::kQh != 0) {
+      // bit j of qh -> bit 4 of byte j (low half), bit 16 + j -> bit 4 of byte j (high half)
+      const uint32_t bl = (qh >> (4 * w)) & 0xfu, bh = (qh >> (16 + 4 * w)) & 0xfu;
+      lo |= ((bl & 1u) << 4) | ((bl & 2u) << 11) | ((bl & 4u) << 18) | ((bl & 8u) << 25);
+      hi |= ((bh & 1u) << 4) | ((bh & 2u) << 11) | ((bh & 4u) << 18) | ((bh & 8u) << 25);
+    }
+    const uint32_t ylo = load_u32_bytes(yb + F::kAq + 4 * w), yhi = load_u32_bytes(yb + F::kAq + 16 + 4 * w);
+    sumi = __dp4a(static_cast<int>(lo), static_cast<int>(ylo), sumi);  // weights 0..31 as signed bytes
+    sumi = __dp4a(static_cast<int>(hi), static_cast<int>(yhi), sumi);
+    if constexpr (F::kBias16) {
+      ysum = __dp4a(0x01010101, static_cast<int>(ylo), ysum);
+      ysum = __dp4a(0x01010101, static_cast<int>(yhi), ysum);
+    }
+  }
+  if constexpr (F::kBias16)
+    sumi -= 16 * ysum;  // sum((v - 16) * y) = sum(v * y) - 16 * sum(y)
+  return sumi;
+}
+
+template <int kFormat>
+__global__ void __launch_bounds__(256) sibling_sums_kernel(const uint8_t *__restrict__ vx, const uint8_t *__restrict__ vy,
+                                                           int32_t *__restrict__ sumi, size_t bx, size_t by,
+                                                           uint32_t nr, uint32_t nc, uint32_t nb) {
+  using F = Sibling<kFormat>;
+  const size_t total = static_cast<size_t>(nr) * nc * nb;
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const size_t ib = i % nb, rc = i / nb, col = rc % nc, row = rc / nc;
+    sumi[i] = sibling_sumi<kFormat>(vx + row * bx + ib * F::kW, vy + col * by + ib * F::kA);
+  }
+}
+
+template <int kFormat>
+__global__ void __launch_bounds__(256) sibling_dot_kernel(const uint8_t *__restrict__ vx, const uint8_t *__restrict__ vy,
+                                                          float *__restrict__ s, size_t bx, size_t by, size_t bs,
+                                                          uint32_t nr, uint32_t nc, uint32_t nb) {
+  using F = Sibling<kFormat>;
+  const int lane = threadIdx.x & 31;
+  const size_t warp = (static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const size_t nwarps = (static_cast<size_t>(gridDim.x) * blockDim.x) >> 5;
+  const size_t total = static_cast<size_t>(nr) * nc;
+  for (size_t item = warp; item < total; item += nwarps) {
+    const size_t row = item / nc, col = item - row * nc;
+    const uint8_t *wr = vx + row * bx;
+    const uint8_t *xc = vy + col * by;
+    float acc = 0.0f;
+    for (uint32_t base = 0; base < nb; base += 32) {
+      const uint32_t ib = base + lane;
+      float term_a = 0.0f, term_b = 0.0f;  // min formats: a = the block's whole term; Q5_0: a = sumi, b = d_x*d_y
+      if (ib < nb) {
+        const uint8_t *xb = wr + static_cast<size_t>(ib) * F::kW;
+        const uint8_t *yb = xc + static_cast<size_t>(ib) * F::kA;
+        const float p = __fmul_rn(half_bits_to_float(load_u16(xb)), half_bits_to_float(load_u16(yb)));
+        const float fs = __int2float_rn(sibling_sumi<kFormat>(xb, yb));
+        if constexpr (F::kMin) {
+          const float ms = __fmul_rn(half_bits_to_float(load_u16(xb + 2)), half_bits_to_float(load_u16(yb + 2)));
+          term_a = __fmaf_rn(p, fs, ms);
+        } else {
+          term_a = fs;
+          term_b = p;
+        }
+      }
+      const uint32_t live = min(32u, nb - base);
+      for (uint32_t j = 0; j < live; ++j) {
+        const float a = __shfl_sync(0xffffffffu, term_a, j);
+        if constexpr (F::kMin) {
+          acc = __fadd_rn(acc, a);
+        } else {
+          acc = __fmaf_rn(__shfl_sync(0xffffffffu, term_b, j), a, acc);
+        }
+      }
+    }
+    if (lane == 0)
+      s[row * bs + col] = acc;
+  }
+}
+
+template <int kFormat>
+int launch_one(size_t n, float *s, int32_t *sums, const uint8_t *vx, const uint8_t *vy, size_t by, size_t nr, size_t nc,
+               size_t bx, size_t bs, cudaStream_t stream) {
+  const uint32_t nb = static_cast<uint32_t>(n / kQK);
+  if (nr == 0 || nc == 0)
+    return TCRV_CUDA_OK;
+  const size_t cap = static_cast<size_t>(sm_count()) * 8;
+  if (sums != nullptr) {
+    if (nb == 0)
+      return TCRV_CUDA_OK;
+    const size_t want = (nr * nc * nb + 255) / 256;
+    sibling_sums_kernel<kFormat><<<static_cast<int>(want < cap ? want : cap), 256, 0, stream>>>(
+        vx, vy, sums, bx, by, static_cast<uint32_t>(nr), static_cast<uint32_t>(nc), nb);
+  } else {
+    const size_t want = (nr * nc + 7) / 8;
+    sibling_dot_kernel<kFormat><<<static_cast<int>(want < cap ? want : cap), 256, 0, stream>>>(
+        vx, vy, s, bx, by, bs, static_cast<uint32_t>(nr), static_cast<uint32_t>(nc), nb);
+  }
+  TCRV_CUDA_TRY(cudaGetLastError());
+  return TCRV_CUDA_OK;
+}
+
+}  // namespace
+
+int sibling_block_bytes(int format, size_t *weight, size_t *activation) {
+  switch (format) {
+    case 1: *weight = 20, *activation = 36; return TCRV_CUDA_OK;
+    case 2: *weight = 22, *activation = 34; return TCRV_CUDA_OK;
+    case 3: *weight = 24, *activation = 36; return TCRV_CUDA_OK;
+    default: return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  }
+}
+
+int launch_sibling_dot(int format, size_t n, float *s, int32_t *sums, const uint8_t *vx, const uint8_t *vy, size_t by,
+                       size_t nr, size_t nc, size_t bx, size_t bs, cudaStream_t stream) {
+  switch (format) {
+    case 1: return launch_one<1>(n, s, sums, vx, vy, by, nr, nc, bx, bs, stream);
+    case 2: return launch_one<2>(n, s, sums, vx, vy, by, nr, nc, bx, bs, stream);
+    case 3: return launch_one<3>(n, s, sums, vx, vy, by, nr, nc, bx, bs, stream);
+    default: return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  }
+}
+
+}  // namespace tcrv
