@@ -38,6 +38,10 @@ int tcrv_cuda_host_vec_silu_f32(size_t n, const float *x, float *y);
 int tcrv_cuda_host_vec_soft_max_f32(size_t n, float *y, const float *x, float max, double *sum);
 int tcrv_cuda_host_rope_norm_f32(size_t n_dims, const float *x, float *y, float theta_base, float theta_scale);
 int tcrv_cuda_host_pack_q4_0_to_q4_0x16(size_t nblocks, const uint8_t *src, uint8_t *dst);
+/* sibling formats, one row per call */
+int tcrv_cuda_host_vec_dot_q4_1_q8_1(size_t n, float *s, const uint8_t *vx, const uint8_t *vy);
+int tcrv_cuda_host_vec_dot_q5_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy);
+int tcrv_cuda_host_vec_dot_q5_1_q8_1(size_t n, float *s, const uint8_t *vx, const uint8_t *vy);
 /* nc <= 8 runs the decode GEMV, larger nc the tensor-core GEMM. */
 int tcrv_cuda_host_gemm_q4_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by, size_t nr,
                                   size_t nc, size_t bx, size_t bs);
@@ -74,6 +78,15 @@ void tcrv_emitc_ggml_rope_norm_f32_kernel_ggml_rope_norm_f32(size_t n_dims, cons
 /* test/Conversion/RVV/rvv-to-emitc-pack-q4-0-to-q4-0x16.mlir:35 */
 void tcrv_emitc_ggml_pack_q4_0_to_q4_0x16_kernel_ggml_pack_q4_0_to_q4_0x16(size_t nblocks, const uint8_t *src,
                                                                            uint8_t *dst);
+/* tcrv_rvv.q4_1_q8_1_block_dot / q5_0_q8_0_block_dot / q5_1_q8_1_block_dot
+ * (include/TianChenRV/Dialect/RVV/IR/RVVOps.td:5247, 5359, 5957), named as the Q8_0 sibling's
+ * fixture names its kernel (ggml_vec_dot_<formats>) */
+void tcrv_emitc_ggml_vec_dot_q4_1_q8_1_kernel_ggml_vec_dot_q4_1_q8_1(size_t n, float *s, const uint8_t *vx,
+                                                                     const uint8_t *vy);
+void tcrv_emitc_ggml_vec_dot_q5_0_q8_0_kernel_ggml_vec_dot_q5_0_q8_0(size_t n, float *s, const uint8_t *vx,
+                                                                     const uint8_t *vy);
+void tcrv_emitc_ggml_vec_dot_q5_1_q8_1_kernel_ggml_vec_dot_q5_1_q8_1(size_t n, float *s, const uint8_t *vx,
+                                                                     const uint8_t *vy);
 /* test/Conversion/RVV/rvv-to-emitc-q4-0-q8-0-block-dot.mlir:44 */
 void tcrv_emitc_ggml_vec_dot_q4_0_q8_0_kernel_ggml_vec_dot_q4_0_q8_0(size_t n, float *s, size_t bs, const uint8_t *vx,
                                                                      size_t bx, const uint8_t *vy, size_t by,

@@ -63,6 +63,12 @@ PROTOTYPES = {
                                     "size_t n_dims, const float *x, float *y, float theta_base, float theta_scale);",
     "cuda-pack-q4-0-to-q4-0x16.mlir": "void tcrv_emitc_ggml_pack_q4_0_to_q4_0x16_kernel_ggml_pack_q4_0_to_q4_0x16("
                                       "size_t nblocks, const uint8_t *src, uint8_t *dst);",
+    "cuda-q4-1-q8-1-block-dot.mlir": "void tcrv_emitc_ggml_vec_dot_q4_1_q8_1_kernel_ggml_vec_dot_q4_1_q8_1("
+        "size_t n, float *s, const uint8_t *vx, const uint8_t *vy);",
+    "cuda-q5-0-q8-0-block-dot.mlir": "void tcrv_emitc_ggml_vec_dot_q5_0_q8_0_kernel_ggml_vec_dot_q5_0_q8_0("
+        "size_t n, float *s, const uint8_t *vx, const uint8_t *vy);",
+    "cuda-q5-1-q8-1-block-dot.mlir": "void tcrv_emitc_ggml_vec_dot_q5_1_q8_1_kernel_ggml_vec_dot_q5_1_q8_1("
+        "size_t n, float *s, const uint8_t *vx, const uint8_t *vy);",
     "cuda-q4-0-q8-0-block-dot.mlir": "void tcrv_emitc_ggml_vec_dot_q4_0_q8_0_kernel_ggml_vec_dot_q4_0_q8_0("
                                      "size_t n, float *s, size_t bs, const uint8_t *vx, size_t bx, const uint8_t *vy, "
                                      "size_t by, int32_t nrc);",
@@ -183,7 +189,7 @@ NEGATIVES = [
     ("cuda-q4-0-q8-0-gemm.mlir", "tcrv_rvv.q4_0_q8_0_gemm %vx, %vy", "tcrv_rvv.q4_0_q8_0_gemm %vy, %vx", "operand #0 must be the lhs-input-buffer"),
     ("cuda-q8-0-q8-0-block-dot.mlir", "weight_block_stride = 34", "weight_block_stride = 18", "'weight_block_stride' must be 34"),
     ("cuda-quantize-row-q8-0.mlir", "block_stride = 34", "block_stride = 36", "'block_stride' must be 34"),
-    ("cuda-q4-0-q8-0-block-dot.mlir", "tcrv_rvv.q4_0_q8_0_block_dot", "tcrv_rvv.q5_0_q8_0_block_dot", "no kernel for op"),
+    ("cuda-q4-0-q8-0-block-dot.mlir", "tcrv_rvv.q4_0_q8_0_block_dot", "tcrv_rvv.iq4_nl_q8_0_block_dot", "no kernel for op"),
 ]
 
 

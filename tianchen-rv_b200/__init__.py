@@ -90,6 +90,9 @@ ABI.update({
     "tcrv_cuda_host_vec_soft_max_f32": [_sz, _p, _p, ctypes.c_float, _p],
     "tcrv_cuda_host_rope_norm_f32": [_sz, _p, _p, ctypes.c_float, ctypes.c_float],
     "tcrv_cuda_host_pack_q4_0_to_q4_0x16": [_sz, _p, _p],
+    "tcrv_cuda_host_vec_dot_q4_1_q8_1": [_sz, _p, _p, _p],
+    "tcrv_cuda_host_vec_dot_q5_0_q8_0": [_sz, _p, _p, _p],
+    "tcrv_cuda_host_vec_dot_q5_1_q8_1": [_sz, _p, _p, _p],
     "tcrv_cuda_host_gemm_q4_0_q8_0": [_sz, _p, _p, _p, _sz, _sz, _sz, _sz, _sz],
     "tcrv_cuda_host_gemm_q8_0_q8_0": [_sz, _p, _p, _p, _sz, _sz, _sz, _sz, _sz],
 })

@@ -452,6 +452,35 @@ void tcrv_emitc_explicit_selected_body_dequantize_i32_to_f32_kernel_explicit_sel
   must(tcrv_cuda_host_dequantize_i32_f32(lhs, scale, out, n), __func__);
 }
 
+// One-row block dot of a sibling format over host buffers.
+int host_sibling_dot(int format, size_t n, float *s, const uint8_t *vx, const uint8_t *vy) {
+  size_t wb = 0, ab = 0;
+  if (sibling_block_bytes(format, &wb, &ab) != TCRV_CUDA_OK || n % kQK != 0 || !s)
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  const size_t nb = n / kQK;
+  if (nb != 0 && (!vx || !vy))
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  HostContext &c = ctx();
+  std::lock_guard<std::mutex> lock(c.mu);
+  int st = ensure_stream(c);
+  if (st == TCRV_CUDA_OK)
+    st = arena_reserve(c, up256(nb * wb) + up256(nb * ab) + 256);
+  if (st != TCRV_CUDA_OK)
+    return st;
+  uint8_t *dw = arena_take(c, nb * wb);
+  uint8_t *dx = arena_take(c, nb * ab);
+  float *ds = reinterpret_cast<float *>(arena_take(c, sizeof(float)));
+  if (nb != 0) {
+    TCRV_CUDA_TRY(cudaMemcpyAsync(dw, vx, nb * wb, cudaMemcpyHostToDevice, c.stream));
+    TCRV_CUDA_TRY(cudaMemcpyAsync(dx, vy, nb * ab, cudaMemcpyHostToDevice, c.stream));
+  }
+  st = launch_sibling_dot(format, n, ds, nullptr, dw, dx, 0, 1, 1, 0, 1, c.stream);
+  if (st != TCRV_CUDA_OK)
+    return st;
+  TCRV_CUDA_TRY(cudaMemcpyAsync(s, ds, sizeof(float), cudaMemcpyDeviceToHost, c.stream));
+  return finish(c);
+}
+
 int tcrv_cuda_host_pack_q4_0_to_q4_0x16(size_t nblocks, const uint8_t *src, uint8_t *dst) {
   if (nblocks == 0)
     return TCRV_CUDA_OK;
@@ -473,6 +502,28 @@ int tcrv_cuda_host_pack_q4_0_to_q4_0x16(size_t nblocks, const uint8_t *src, uint
     return st;
   TCRV_CUDA_TRY(cudaMemcpyAsync(dst, dd, bytes, cudaMemcpyDeviceToHost, c.stream));
   return finish(c);
+}
+
+int tcrv_cuda_host_vec_dot_q4_1_q8_1(size_t n, float *s, const uint8_t *vx, const uint8_t *vy) {
+  return host_sibling_dot(1, n, s, vx, vy);
+}
+int tcrv_cuda_host_vec_dot_q5_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy) {
+  return host_sibling_dot(2, n, s, vx, vy);
+}
+int tcrv_cuda_host_vec_dot_q5_1_q8_1(size_t n, float *s, const uint8_t *vx, const uint8_t *vy) {
+  return host_sibling_dot(3, n, s, vx, vy);
+}
+void tcrv_emitc_ggml_vec_dot_q4_1_q8_1_kernel_ggml_vec_dot_q4_1_q8_1(size_t n, float *s, const uint8_t *vx,
+                                                                     const uint8_t *vy) {
+  must(host_sibling_dot(1, n, s, vx, vy), __func__);
+}
+void tcrv_emitc_ggml_vec_dot_q5_0_q8_0_kernel_ggml_vec_dot_q5_0_q8_0(size_t n, float *s, const uint8_t *vx,
+                                                                     const uint8_t *vy) {
+  must(host_sibling_dot(2, n, s, vx, vy), __func__);
+}
+void tcrv_emitc_ggml_vec_dot_q5_1_q8_1_kernel_ggml_vec_dot_q5_1_q8_1(size_t n, float *s, const uint8_t *vx,
+                                                                     const uint8_t *vy) {
+  must(host_sibling_dot(3, n, s, vx, vy), __func__);
 }
 
 void tcrv_emitc_ggml_pack_q4_0_to_q4_0x16_kernel_ggml_pack_q4_0_to_q4_0x16(size_t nblocks, const uint8_t *src,

@@ -76,6 +76,44 @@ std::vector<RouteEntry> buildTable() {
                {{"runtime-element-count", "size_t"}, {"lhs-input-buffer", "const float *"}, {"output-buffer", "uint8_t *"}},
                "quantize_row_q8_0", "cuda-ggml-quantize-row-q8_0-callable-c-abi.v1", "tcrv_cuda_quantize_row_q8_0",
                "tcrv_cuda_host_quantize_row_q8_0", "streaming-quantizer", "hbm", ""});
+  // sibling block formats (general strict-order kernel)
+  {
+    const Sig dotSig = {{"runtime-element-count", "size_t"}, {"output-buffer", "float *"},
+                        {"lhs-input-buffer", "const uint8_t *"}, {"rhs-input-buffer", "const uint8_t *"}};
+    const std::vector<std::string> dotRoles = {"lhs-input-buffer", "rhs-input-buffer", "output-buffer",
+                                               "runtime-element-count"};
+    t.push_back({"tcrv_rvv.q4_1_q8_1_block_dot",
+                 withKind("ggml_q4_1_q8_1_block_dot",
+                          {{"scale_model", false, "dual-fp16-per-block-d_x.d_y-plus-min", 0}, {"qk", true, "", 32},
+                           {"weight_block_stride", true, "", 20}, {"activation_block_stride", true, "", 36},
+                           {"quant_byte_offset", true, "", 4}, {"activation_high_byte_offset", true, "", 16},
+                           {"weight_min_byte_offset", true, "", 2}, {"activation_sum_byte_offset", true, "", 2}}),
+                 "", {"tcrv_rvv.q4_1_q8_1_block_dot"}, dotRoles, dotSig, "q4_1_q8_1_block_dot",
+                 "cuda-ggml-q4_1-q8_1-block-dot-callable-c-abi.v1", "tcrv_cuda_vec_dot_q4_1_q8_1",
+                 "tcrv_cuda_host_vec_dot_q4_1_q8_1", "block-dot-strict-order", "hbm",
+                 "sumf = sumf + fma(d_x*d_y, (float)sumi, m_x*s_y), ascending blocks"});
+    t.push_back({"tcrv_rvv.q5_0_q8_0_block_dot",
+                 withKind("ggml_q5_0_q8_0_block_dot",
+                          {{"scale_model", false, "dual-fp16-per-block-d_x.d_y", 0}, {"qk", true, "", 32},
+                           {"weight_block_stride", true, "", 22}, {"activation_block_stride", true, "", 34},
+                           {"quant_byte_offset", true, "", 6}, {"activation_quant_byte_offset", true, "", 2},
+                           {"activation_high_byte_offset", true, "", 16}, {"weight_qh_byte_offset", true, "", 2}}),
+                 "", {"tcrv_rvv.q5_0_q8_0_block_dot"}, dotRoles, dotSig, "q5_0_q8_0_block_dot",
+                 "cuda-ggml-q5_0-q8_0-block-dot-callable-c-abi.v1", "tcrv_cuda_vec_dot_q5_0_q8_0",
+                 "tcrv_cuda_host_vec_dot_q5_0_q8_0", "block-dot-strict-order", "hbm",
+                 "sumf = fma(d_x*d_y, (float)sumi, sumf), ascending blocks"});
+    t.push_back({"tcrv_rvv.q5_1_q8_1_block_dot",
+                 withKind("ggml_q5_1_q8_1_block_dot",
+                          {{"scale_model", false, "dual-fp16-per-block-d_x.d_y-plus-min", 0}, {"qk", true, "", 32},
+                           {"weight_block_stride", true, "", 24}, {"activation_block_stride", true, "", 36},
+                           {"quant_byte_offset", true, "", 8}, {"activation_quant_byte_offset", true, "", 4},
+                           {"activation_high_byte_offset", true, "", 16}, {"weight_qh_byte_offset", true, "", 4},
+                           {"weight_min_byte_offset", true, "", 2}, {"activation_sum_byte_offset", true, "", 2}}),
+                 "", {"tcrv_rvv.q5_1_q8_1_block_dot"}, dotRoles, dotSig, "q5_1_q8_1_block_dot",
+                 "cuda-ggml-q5_1-q8_1-block-dot-callable-c-abi.v1", "tcrv_cuda_vec_dot_q5_1_q8_1",
+                 "tcrv_cuda_host_vec_dot_q5_1_q8_1", "block-dot-strict-order", "hbm",
+                 "sumf = sumf + fma(d_x*d_y, (float)sumi, m_x*s_y), ascending blocks"});
+  }
   // weight repack into the reference's 16-row interleaved layout
   t.push_back({"tcrv_rvv.pack_q4_0_to_q4_0x16",
                withKind("ggml_pack_q4_0_to_q4_0x16",
