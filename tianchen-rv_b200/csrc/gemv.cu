@@ -330,6 +330,14 @@ int launch_gemv(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t
       args.contiguous = (bx == row_bytes) ? 1u : 0u;
       args.rps = static_cast<uint32_t>(rps);
       args.static_weights = (flags & TCRV_CUDA_FLAG_STATIC_WEIGHTS) ? 1u : 0u;
+      // One copy in flight per warp (see the kernel's header); flags bits 16..19 set another
+      // window, up to the ring depth (tuning).
+      args.window = 1;
+      {
+        const unsigned wf = (flags >> 16) & 0xfu;
+        if (wf >= 1)
+          args.window = wf < spw ? wf : static_cast<uint32_t>(spw);
+      }
       const size_t nslots = (nr + rps - 1) / rps;
       const int grid = static_cast<int>(nslots < static_cast<size_t>(sms) ? nslots : sms);
       return launch_stream<kQ8W>(args, static_cast<uint32_t>(nc), grid, fixed + nwarps * spw * slot, stream);

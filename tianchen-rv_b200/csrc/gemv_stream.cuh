@@ -3,17 +3,24 @@
 //
 // One persistent CTA per SM owns a contiguous range of weight rows, divided evenly (to within
 // one row) among its warps.  Up to 16 warps each own a private ring of shared-memory slots
-// (one slot = up to 1, 2 or 4 adjacent rows, the maximum chosen by the launcher) and keep it
-// full themselves: lane 0 issues a 1-D bulk copy
-// (cp.async.bulk, completion counted on the slot's mbarrier) for the slot it has just
-// finished, so copy issue is spread over all warps and no warp waits for another.  Each warp
-// works on all rows of a slot at once; about 32 rows are in flight per SM, below that the
-// kernel is latency-bound.  Rows stay in the plain 18-byte (Q4_0) or 34-byte (Q8_0) block
-// format.  A lane owns PAIRS of adjacent blocks: a pair is 36 or 68 bytes, i.e. 9 or 17
-// aligned 32-bit words, and both strides are odd, so the 32 lanes of a warp read shared
-// memory without bank conflicts.  The fp16 scale of the even block sits in the low half of
-// word 0 and its quants straddle words (re-aligned with funnel shifts); the odd block's
-// scale is the high half of the middle word and its quants are word aligned.
+// (one slot = up to 1, 2 or 4 adjacent rows, the maximum chosen by the launcher) and feed it
+// themselves: lane 0 issues a 1-D bulk copy (cp.async.bulk, completion counted on the slot's
+// mbarrier), so copy issue is spread over all warps and no warp waits for another.
+//
+// A warp keeps ONE copy in flight (`window`): the next slot's copy goes out when the current
+// one has landed, before its rows are folded.  When every slot was requested at once, all
+// copies of all CTAs shared the memory system fairly and completed together at the end of the
+// stream (measured: first slot after 3.3 us of a 3.9 us stream), so nothing could be folded
+// before then; one slot per warp (110..200 KB per SM) already covers the bandwidth-latency
+// product and lets the fold overlap the stream (-15 % on the 25 MB matrices).
+//
+// A warp folds all rows of a slot at once (independent accumulators).  Rows stay in the plain
+// 18-byte (Q4_0) or 34-byte (Q8_0) block format.  A lane owns PAIRS of adjacent blocks: a pair
+// is 36 or 68 bytes, i.e. 9 or 17 aligned 32-bit words, and both strides are odd, so the 32
+// lanes of a warp read shared memory without bank conflicts.  The fp16 scale of the even
+// block sits in the low half of word 0 and its quants straddle words (re-aligned with funnel
+// shifts); the odd block's scale is the high half of the middle word and its quants are word
+// aligned.
 //
 // The activation columns are converted once per CTA into a lane-friendly layout: for every
 // block pair four 16-byte pieces (stored as four planes so that consecutive lanes read
@@ -50,6 +57,7 @@ struct GemvArgs {
   uint32_t contiguous; // bx == row_bytes: all rows of a slot arrive in one copy
   uint32_t rps;        // rows per slot: 1, 2 or 4 (single column), 1 or 2 otherwise
   uint32_t static_weights;  // weights may be fetched before the preceding kernel has finished
+  uint32_t window;     // copies a warp keeps in flight (1..slots); below `slots` a refill is issued on arrival
 };
 
 template <bool kQ8W>
@@ -231,7 +239,7 @@ __global__ void __launch_bounds__(kGemvMaxThreads, 1) gemv_stream_kernel(const G
       mbar_init(&full[warp * spw + i], 1);
     mbar_fence_init();
     // Start streaming weights right away; they do not depend on the activation staging.
-    for (uint32_t t = 0; t < min(spw, mine); ++t)
+    for (uint32_t t = 0; t < min(a.window, mine); ++t)
       issue(t);
   }
   if (a.static_weights)
@@ -271,10 +279,16 @@ __global__ void __launch_bounds__(kGemvMaxThreads, 1) gemv_stream_kernel(const G
       if (lane == 0) {
         raise_device_error(kDevErrBarrierTimeout);
         // copies already issued for later slots must land before the CTA's memory goes away
-        for (uint32_t u = t + 1; u < min(mine, t + spw); ++u)
+        for (uint32_t u = t + 1; u < min(mine, t + a.window); ++u)
           (void)mbar_wait_bounded(&full[warp * spw + u % spw], (u / spw) & 1);
       }
       return;
+    }
+    // a window smaller than the ring: the next copy goes out as soon as this one has landed,
+    // into a ring position whose rows were folded earlier
+    if (a.window < spw && lane == 0 && t + a.window < mine) {
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      issue(t + a.window);
     }
     const uint32_t row = slot_row(t);
     const uint32_t *wrow = reinterpret_cast<const uint32_t *>(slots + static_cast<size_t>(bar) * slot_bytes);
@@ -294,7 +308,7 @@ __global__ void __launch_bounds__(kGemvMaxThreads, 1) gemv_stream_kernel(const G
     // Every lane has consumed its words of the slot (their values fed the reduction above);
     // order those reads before the copy engine overwrites the slot, then refill it.
     __syncwarp();
-    if (lane == 0 && t + spw < mine) {
+    if (a.window >= spw && lane == 0 && t + spw < mine) {
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       issue(t + spw);
     }
