@@ -133,6 +133,7 @@ __global__ void __launch_bounds__(kMmaThreads, 1)
   int *xs8 = reinterpret_cast<int *>(xsm + nb * 288u);               // [nb][8]
   uint8_t *slots = xsm + static_cast<size_t>(nb) * kMmaXBytesPerBlock;
   const uint32_t spw = a.slots;
+  const uint32_t window = spw >= 2 ? 1u : spw;  // copies in flight per warp
 
   const uint32_t warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
@@ -169,7 +170,9 @@ __global__ void __launch_bounds__(kMmaThreads, 1)
     for (uint32_t i = 0; i < spw; ++i)
       mbar_init(&full[warp * spw + i], 1);
     mbar_fence_init();
-    for (uint32_t i = 0; i < min(spw, items); ++i)
+    // one copy in flight per warp: item i + 1 is requested when item i has landed (see the
+    // streaming kernel for why requesting everything at once delays every first slot)
+    for (uint32_t i = 0; i < min(window, items); ++i)
       issue(i);
   }
   if (a.static_weights)
@@ -227,6 +230,10 @@ __global__ void __launch_bounds__(kMmaThreads, 1)
         dead = true;
         continue;
       }
+      if (window < spw && lane == 0 && i + window < items) {
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        issue(i + window);  // into a ring position whose rows were consumed earlier
+      }
       const uint8_t *slot = slots + static_cast<size_t>(bar) * kSlotBytes;
       [[maybe_unused]] const uint32_t ib0 = (warp + kMmaWarps * u) * kMmaChunkBlocks;
 #pragma unroll
@@ -281,7 +288,7 @@ __global__ void __launch_bounds__(kMmaThreads, 1)
       }
       // every lane has consumed the slot: refill it with this warp's item i + spw
       __syncwarp();
-      if (lane == 0 && i + spw < items) {
+      if (window >= spw && lane == 0 && i + spw < items) {
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         issue(i + spw);
       }
