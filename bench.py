@@ -531,21 +531,27 @@ def measure_gemm(pkg, torch, dist, rank, world):
                            "allgather_bytes": nr * GEMM_TOKENS * 4})
             # the all-gather fused into the epilogue: finished tiles are stored into every rank's
             # copy of the output (peer memory over NVLink) while later tiles compute
-            shared = pkg.SharedOutput(nr, GEMM_TOKENS, dist, rank, world, torch.device("cuda", torch.cuda.current_device()))
+            # (SharedOutput agrees on success or failure across the ranks, so every rank takes
+            # the same branch below)
+            shared = pkg.SharedOutput(nr, GEMM_TOKENS, dist, rank, world,
+                                      torch.device("cuda", torch.cuda.current_device()))
+            if shared.error is not None:
+                entry_["fused_allgather_error"] = f"{type(shared.error).__name__}: {shared.error}"
+                shared.close()
+            else:
+                def fused():
+                    shared.gemm_into(pw, x, workspace=ws)
 
-            def fused():
-                shared.gemm_into(pw, x, workspace=ws)
-
-            with_gather()
-            fused()
-            shared.wait()
-            same = bool(torch.equal(shared.local(), full))
-            ms_f = timed(fused)
-            shared.wait()
-            entry_.update({"fused_allgather_ms": round(ms_f, 4), "fused_allgather_tops": round(ops / ms_f / 1e9, 1),
-                           "fused_equals_nccl": same,
-                           "fused_link_gbs_per_gpu": round(rows * GEMM_TOKENS * 4 * (world - 1) / ms_f / 1e6, 1)})
-            shared.close()
+                with_gather()
+                fused()
+                shared.wait()
+                same = bool(torch.equal(shared.local(), full))
+                ms_f = timed(fused)
+                shared.wait()
+                entry_.update({"fused_allgather_ms": round(ms_f, 4), "fused_allgather_tops": round(ops / ms_f / 1e9, 1),
+                               "fused_equals_nccl": same,
+                               "fused_link_gbs_per_gpu": round(rows * GEMM_TOKENS * 4 * (world - 1) / ms_f / 1e6, 1)})
+                shared.close()
         entry_["roofline"] = {"bound": "tensor", "achieved": entry_["compute_tops"], "peak": int8_peak,
                               "unit": "TOP/s", "frac": round(entry_["compute_tops"] / world / int8_peak, 4),
                               "peak_kind": f"2 x bf16 burst peak ({peak_kind}); no int8 figure is measured on this pool"}

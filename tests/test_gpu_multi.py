@@ -34,6 +34,7 @@ def _worker(rank, world, port, nr, k, nc, out_path):
     pw = pkg.PreparedWeights(torch.from_numpy(w[first:first + rows]).cuda())
     xd = torch.from_numpy(x).cuda()
     shared = pkg.SharedOutput(nr, nc, dist, rank, world, torch.device("cuda", rank))
+    assert shared.error is None, shared.error
     shared.local().fill_(float("nan"))
     shared.wait()
     for _ in range(2):  # twice in a row: the second call overwrites the same bytes

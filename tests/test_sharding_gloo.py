@@ -59,3 +59,32 @@ def test_row_shard_arithmetic():
         pkg.row_shard(10, 4, 0)
     with pytest.raises(ValueError):
         pkg.row_shard(8, 4, 4)
+
+
+def _failing_worker(rank, world, port, out_path):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    pkg = entry.load_package()
+    # no GPU here: the allocation fails on every rank; the set-up must still be collective-safe
+    shared = pkg.SharedOutput(64, 8, dist, rank, world, "cpu")
+    verdict = "failed" if shared.error is not None else "ok"
+    try:
+        shared.gemm_into(None, None)
+    except RuntimeError:
+        verdict += "+refused"
+    shared.close()
+    with open(f"{out_path}.{rank}.txt", "w") as f:
+        f.write(verdict)
+    dist.destroy_process_group()
+
+
+def test_shared_output_setup_failure_is_agreed_on_and_does_not_hang(tmp_path):
+    import torch
+
+    if torch.cuda.is_available():
+        pytest.skip("exercises the no-GPU failure path")
+    port, out = _free_port(), str(tmp_path / "verdict")
+    mp.spawn(_failing_worker, args=(2, port, out), nprocs=2, join=True)
+    for rank in range(2):
+        assert open(f"{out}.{rank}.txt").read() == "failed+refused"

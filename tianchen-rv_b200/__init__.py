@@ -529,27 +529,42 @@ class SharedOutput:
     hold all rows."""
 
     def __init__(self, nr: int, nc: int, dist, rank: int, world: int, device):
-        import torch
-
-        self.nr, self.nc, self.rank, self.world, self.dist = nr, nc, rank, world, dist
-        own = ctypes.c_void_p()
-        _check(lib().tcrv_cuda_peer_alloc(nr * nc * 4, ctypes.byref(own)), "tcrv_cuda_peer_alloc")
-        self.own = own.value
-        handle = (ctypes.c_ubyte * 64)()
-        _check(lib().tcrv_cuda_peer_export(self.own, handle), "tcrv_cuda_peer_export")
+        """Collective: every rank calls it, and every rank reaches every collective inside even
+        when its own allocation or mapping fails.  The outcome is in `self.error` (None on
+        success, the same verdict on all ranks); a failed object only supports close()."""
+        self.nr, self.nc, self.rank, self.world, self.dist, self.device = nr, nc, rank, world, dist, device
+        self.own, self.bases, self._opened, self.error = None, [], [], None
+        payload = None
+        try:
+            own = ctypes.c_void_p()
+            _check(lib().tcrv_cuda_peer_alloc(nr * nc * 4, ctypes.byref(own)), "tcrv_cuda_peer_alloc")
+            self.own = own.value
+            handle = (ctypes.c_ubyte * 64)()
+            _check(lib().tcrv_cuda_peer_export(self.own, handle), "tcrv_cuda_peer_export")
+            payload = bytes(handle)
+        except Exception as exc:  # noqa: BLE001 - agreed on below
+            self.error = exc
         handles = [None] * world
-        dist.all_gather_object(handles, bytes(handle))
-        self.bases, self._opened = [], []
-        for r in range(world):
-            if r == rank:
-                self.bases.append(self.own)
-                continue
-            ptr = ctypes.c_void_p()
-            buf = (ctypes.c_ubyte * 64).from_buffer_copy(handles[r])
-            _check(lib().tcrv_cuda_peer_open(buf, ctypes.byref(ptr)), "tcrv_cuda_peer_open")
-            self.bases.append(ptr.value)
-            self._opened.append(ptr.value)
-        self.device = device
+        dist.all_gather_object(handles, payload)
+        if self.error is None and any(h is None for h in handles):
+            self.error = RuntimeError("a peer could not allocate or export its buffer")
+        if self.error is None:
+            try:
+                for r in range(world):
+                    if r == rank:
+                        self.bases.append(self.own)
+                        continue
+                    ptr = ctypes.c_void_p()
+                    buf = (ctypes.c_ubyte * 64).from_buffer_copy(handles[r])
+                    _check(lib().tcrv_cuda_peer_open(buf, ctypes.byref(ptr)), "tcrv_cuda_peer_open")
+                    self.bases.append(ptr.value)
+                    self._opened.append(ptr.value)
+            except Exception as exc:  # noqa: BLE001
+                self.error = exc
+        verdicts = [None] * world
+        dist.all_gather_object(verdicts, None if self.error is None else f"{type(self.error).__name__}: {self.error}")
+        if self.error is None and any(v is not None for v in verdicts):
+            self.error = RuntimeError("a peer could not map the buffers: " + next(v for v in verdicts if v is not None))
 
     def local(self):
         """This rank's copy as a torch tensor (no ownership: keep the SharedOutput alive)."""
@@ -566,6 +581,8 @@ class SharedOutput:
     def gemm_into(self, prepared, x, workspace=None):
         """Runs rows row_shard(nr, world, rank) (the rows of `prepared`) and stores them into
         every rank's copy."""
+        if self.error is not None:
+            raise RuntimeError("the shared output is not usable") from self.error
         first, rows = row_shard(self.nr, self.world, self.rank)
         if prepared.nr != rows:
             raise ValueError("prepared weights must hold this rank's row shard")
