@@ -14,6 +14,7 @@
 #include <chrono>
 #include <map>
 #include <mutex>
+#include <vector>
 
 #include "launchers.h"
 #include "tcrv_common.cuh"
@@ -29,8 +30,28 @@ struct ResidentWeights {
   size_t prepared_n = 0, prepared_nr = 0, prepared_bx = 0;
 };
 
+// A decode call seen before with the same buffers: its copy-in, kernel and copy-out replayed as
+// one CUDA graph (one launch instead of three, no gaps between the operations).
+struct ReplayKey {
+  const void *vx, *vy, *s;
+  size_t n, by, nr, nc, bx, bs;
+  bool q8;
+  unsigned flags;
+  bool operator==(const ReplayKey &o) const {
+    return vx == o.vx && vy == o.vy && s == o.s && n == o.n && by == o.by && nr == o.nr && nc == o.nc && bx == o.bx &&
+           bs == o.bs && q8 == o.q8 && flags == o.flags;
+  }
+};
+struct Replay {
+  ReplayKey key;
+  cudaGraphExec_t exec = nullptr;
+  bool unusable = false;  // capture was refused once (e.g. pageable host buffers): do not try again
+};
+constexpr size_t kMaxReplays = 64;
+
 struct HostContext {
   std::mutex mu;
+  std::vector<Replay> replays;
   cudaStream_t stream = nullptr;
   uint8_t *arena = nullptr;
   size_t arena_cap = 0, arena_used = 0;
@@ -45,6 +66,24 @@ HostContext &ctx() {
 
 inline size_t up256(size_t v) { return (v + 255) / 256 * 256; }
 
+// The cached graphs hold arena addresses and resident-weight pointers: drop them whenever
+// either may change.
+void drop_replays(HostContext &c) {
+  for (Replay &r : c.replays)
+    if (r.exec)
+      (void)cudaGraphExecDestroy(r.exec);
+  c.replays.clear();
+}
+
+bool is_pinned_host(const void *p) {
+  cudaPointerAttributes attr;
+  if (cudaPointerGetAttributes(&attr, p) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return false;
+  }
+  return attr.type == cudaMemoryTypeHost;
+}
+
 int ensure_error_mirror(HostContext &c);
 
 int ensure_stream(HostContext &c) {
@@ -58,6 +97,7 @@ int ensure_stream(HostContext &c) {
 int arena_reserve(HostContext &c, size_t total) {
   if (total > c.arena_cap) {
     TCRV_CUDA_TRY(cudaStreamSynchronize(c.stream));
+    drop_replays(c);
     if (c.arena)
       TCRV_CUDA_TRY(cudaFree(c.arena));
     c.arena = nullptr;
@@ -145,6 +185,9 @@ int host_binary(const T *lhs, const T *rhs, T *out, size_t n, Launch launch) {
   return finish(c);
 }
 
+int host_matmul_locked(HostContext &c, bool q8_weights, size_t n, float *s, const uint8_t *vx, const uint8_t *vy,
+                       size_t by, size_t nr, size_t nc, size_t bx, size_t bs, unsigned flags);
+
 // s[ir*bs + col] for host operands; q8_weights selects the Q8_0 x Q8_0 block dot.
 int host_matmul(bool q8_weights, size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by, size_t nr,
                 size_t nc, size_t bx, size_t bs, unsigned flags = TCRV_CUDA_FLAG_NONE) {
@@ -154,12 +197,17 @@ int host_matmul(bool q8_weights, size_t n, float *s, const uint8_t *vx, const ui
     return TCRV_CUDA_OK;
   if (!s || !vx || !vy)
     return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  HostContext &c = ctx();
+  std::lock_guard<std::mutex> lock(c.mu);
+  return host_matmul_locked(c, q8_weights, n, s, vx, vy, by, nr, nc, bx, bs, flags);
+}
+
+int host_matmul_locked(HostContext &c, bool q8_weights, size_t n, float *s, const uint8_t *vx, const uint8_t *vy,
+                       size_t by, size_t nr, size_t nc, size_t bx, size_t bs, unsigned flags) {
   const size_t nb = n / kQK;
   const size_t wrow = nb * (q8_weights ? kQ8Block : kQ4Block), xrow = nb * kQ8Block;
   if ((nr > 1 && bx < wrow) || (nc > 1 && by < xrow) || (nr > 1 && bs < nc))
     return TCRV_CUDA_ERR_INVALID_ARGUMENT;
-  HostContext &c = ctx();
-  std::lock_guard<std::mutex> lock(c.mu);
   int st = ensure_stream(c);
   if (st != TCRV_CUDA_OK)
     return st;
@@ -172,6 +220,29 @@ int host_matmul(bool q8_weights, size_t n, float *s, const uint8_t *vx, const ui
   if (res && res->bytes < (nr - 1) * bx + wrow)
     return TCRV_CUDA_ERR_INVALID_ARGUMENT;
 
+  // Decode calls on resident weights that repeat with the same buffers replay a captured graph.
+  const bool replayable = res != nullptr && !use_gemm;
+  const ReplayKey key{vx, vy, s, n, by, nr, nc, bx, bs, q8_weights, flags};
+  Replay *replay = nullptr;
+  if (replayable) {
+    for (Replay &r : c.replays)
+      if (r.key == key)
+        replay = &r;
+    if (replay != nullptr && replay->exec != nullptr) {
+      TCRV_CUDA_TRY(cudaGraphLaunch(replay->exec, c.stream));
+      return finish(c);
+    }
+  }
+  // second sighting of a call: capture it (host buffers must be pinned for that)
+  const bool capture = replayable && replay != nullptr && !replay->unusable && is_pinned_host(vy) && is_pinned_host(s);
+  if (replayable && replay == nullptr) {
+    if (c.replays.size() >= kMaxReplays)
+      drop_replays(c);
+    c.replays.push_back(Replay{key});
+  } else if (replay != nullptr && !capture) {
+    replay->unusable = true;
+  }
+
   const size_t w_dev_bytes = res ? 0 : nr * wrow;
   const size_t prep_bytes = use_gemm && !(res && res->prepared) ? gemm_weights_bytes(n, nr) : 0;
   const size_t acts_ws = use_gemm ? gemm_acts_bytes(n, nc) : 0;
@@ -181,6 +252,29 @@ int host_matmul(bool q8_weights, size_t n, float *s, const uint8_t *vx, const ui
                             up256(nr * nc * sizeof(float)) + 1024);
   if (st != TCRV_CUDA_OK)
     return st;
+
+  // (arena_reserve may have dropped the replay entries: look the entry up again)
+  replay = nullptr;
+  if (capture)
+    for (Replay &r : c.replays)
+      if (r.key == key)
+        replay = &r;
+  const bool capturing = capture && replay != nullptr &&
+                         cudaStreamBeginCapture(c.stream, cudaStreamCaptureModeThreadLocal) == cudaSuccess;
+  // every early return below must leave capture mode
+  struct CaptureGuard {
+    cudaStream_t stream;
+    bool active;
+    ~CaptureGuard() {
+      if (active) {
+        cudaGraph_t g = nullptr;
+        (void)cudaStreamEndCapture(stream, &g);
+        if (g)
+          (void)cudaGraphDestroy(g);
+        (void)cudaGetLastError();
+      }
+    }
+  } guard{c.stream, capturing};
 
   const uint8_t *dw;
   size_t dbx;
@@ -240,6 +334,23 @@ int host_matmul(bool q8_weights, size_t n, float *s, const uint8_t *vx, const ui
   else
     TCRV_CUDA_TRY(cudaMemcpy2DAsync(s, bs * sizeof(float), ds, nc * sizeof(float), nc * sizeof(float), nr,
                                     cudaMemcpyDeviceToHost, c.stream));
+  if (capturing) {
+    guard.active = false;
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    const bool ok = cudaStreamEndCapture(c.stream, &graph) == cudaSuccess && graph != nullptr &&
+                    cudaGraphInstantiate(&exec, graph, 0) == cudaSuccess;
+    if (graph)
+      (void)cudaGraphDestroy(graph);
+    if (!ok) {
+      // the call has not run: forget the capture and issue it directly (the entry stays unusable)
+      (void)cudaGetLastError();
+      replay->unusable = true;
+      return host_matmul_locked(c, q8_weights, n, s, vx, vy, by, nr, nc, bx, bs, flags);
+    }
+    replay->exec = exec;
+    TCRV_CUDA_TRY(cudaGraphLaunch(exec, c.stream));
+  }
   return finish(c);  // also reports a device-side wait that expired (host mirror of the error word)
 }
 
@@ -316,6 +427,7 @@ int tcrv_cuda_host_register_weights(const void *host, size_t bytes) {
   ResidentWeights &r = c.weights[host];
   if (r.dev) {
     TCRV_CUDA_TRY(cudaStreamSynchronize(c.stream));
+    drop_replays(c);
     TCRV_CUDA_TRY(cudaFree(r.dev));
     if (r.prepared)
       TCRV_CUDA_TRY(cudaFree(r.prepared));
@@ -335,6 +447,7 @@ int tcrv_cuda_host_unregister_weights(const void *host) {
     return TCRV_CUDA_ERR_INVALID_ARGUMENT;
   if (c.stream)
     TCRV_CUDA_TRY(cudaStreamSynchronize(c.stream));
+  drop_replays(c);
   if (it->second.dev)
     TCRV_CUDA_TRY(cudaFree(it->second.dev));
   if (it->second.prepared)
@@ -348,6 +461,7 @@ int tcrv_cuda_host_release(void) {
   std::lock_guard<std::mutex> lock(c.mu);
   if (c.stream)
     TCRV_CUDA_TRY(cudaStreamSynchronize(c.stream));
+  drop_replays(c);
   for (auto &kv : c.weights) {
     if (kv.second.dev)
       (void)cudaFree(kv.second.dev);
