@@ -1,0 +1,91 @@
+"""The host-pointer layer (the entry points a harness written for the reference's generated
+kernels links against): resident weights, pageable and pinned buffers, and the replay of
+repeated decode calls, all against the oracle."""
+import ctypes
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def make(O, nr, k, nc, seed):
+    w = O.quantize_q4_0(O.fill_normal(nr * k, seed, 0, 0.02).reshape(nr, k))
+    x = O.quantize_q8_0(O.fill_normal(nc * k, seed + 1).reshape(nc, k))
+    return w, x
+
+
+@pytest.mark.parametrize("pinned", [False, True])
+@pytest.mark.parametrize("registered", [False, True])
+def test_repeated_host_calls_track_the_host_buffers(cuda, pkg, O, pinned, registered):
+    # The same call five times with the activations changed in between: a pinned, registered
+    # call is captured on its second sighting and replayed afterwards; every result must follow
+    # the CURRENT contents of the host buffers.
+    L = pkg.lib()
+    nr, k = 300, 2048
+    w, x = make(O, nr, k, 1, 4100)
+    wh = np.ascontiguousarray(w)
+    xt = cuda.from_numpy(x.copy())
+    yt = cuda.empty((nr, 1), dtype=cuda.float32)
+    if pinned:
+        xt, yt = xt.pin_memory(), yt.pin_memory()
+    if registered:
+        assert L.tcrv_cuda_host_register_weights(wh.ctypes.data, wh.nbytes) == 0
+    try:
+        for step in range(5):
+            xs = O.quantize_q8_0(O.fill_normal(k, 4200 + step).reshape(1, k))
+            xt.copy_(cuda.from_numpy(xs))
+            yt.fill_(-1.0)
+            st = L.tcrv_cuda_host_gemm_q4_0_q8_0(k, yt.data_ptr(), wh.ctypes.data, xt.data_ptr(), xt.stride(0), nr, 1,
+                                                 wh.strides[0], 1)
+            assert st == 0
+            assert np.array_equal(yt.numpy().view(np.uint32), O.gemv_lane_order(w, xs).view(np.uint32)), step
+    finally:
+        if registered:
+            assert L.tcrv_cuda_host_unregister_weights(wh.ctypes.data) == 0
+        L.tcrv_cuda_host_release()
+
+
+def test_replay_is_dropped_when_weights_are_registered_again(cuda, pkg, O):
+    L = pkg.lib()
+    nr, k = 64, 1024
+    w1, x = make(O, nr, k, 1, 4300)
+    w2, _ = make(O, nr, k, 1, 4400)
+    buf = np.ascontiguousarray(w1.copy())
+    xt = cuda.from_numpy(x.copy()).pin_memory()
+    yt = cuda.empty((nr, 1), dtype=cuda.float32).pin_memory()
+    call = lambda: L.tcrv_cuda_host_gemm_q4_0_q8_0(k, yt.data_ptr(), buf.ctypes.data, xt.data_ptr(), xt.stride(0), nr, 1,
+                                                   buf.strides[0], 1)
+    try:
+        assert L.tcrv_cuda_host_register_weights(buf.ctypes.data, buf.nbytes) == 0
+        for _ in range(3):
+            assert call() == 0
+        assert np.array_equal(yt.numpy(), O.gemv_lane_order(w1, x))
+        buf[...] = w2  # new weights under the same host address: registering again uploads them
+        assert L.tcrv_cuda_host_register_weights(buf.ctypes.data, buf.nbytes) == 0
+        for _ in range(3):
+            assert call() == 0
+            assert np.array_equal(yt.numpy(), O.gemv_lane_order(w2, x))
+    finally:
+        L.tcrv_cuda_host_unregister_weights(buf.ctypes.data)
+        L.tcrv_cuda_host_release()
+
+
+def test_host_prefill_and_q8_paths(cuda, pkg, O):
+    L = pkg.lib()
+    w, x = make(O, 130, 1024, 20, 4500)  # 20 columns: the tensor-core GEMM behind the same entry
+    wh, xh = np.ascontiguousarray(w), np.ascontiguousarray(x)
+    out = np.full((130, 20), -1.0, np.float32)
+    st = L.tcrv_cuda_host_gemm_q4_0_q8_0(1024, out.ctypes.data, wh.ctypes.data, xh.ctypes.data, xh.strides[0], 130, 20,
+                                         wh.strides[0], 20)
+    assert st == 0 and np.array_equal(out.view(np.uint32), O.gemm(w, x, fold=O.FOLD_FMA).view(np.uint32))
+    w8 = O.quantize_q8_0(O.fill_normal(40 * 1024, 4600, 0, 0.02).reshape(40, 1024))
+    out8 = np.empty((40, 2), np.float32)
+    st = L.tcrv_cuda_host_gemm_q8_0_q8_0(1024, out8.ctypes.data, w8.ctypes.data, xh.ctypes.data, xh.strides[0], 40, 2,
+                                         w8.strides[0], 2)
+    assert st == 0 and np.array_equal(out8.view(np.uint32), O.gemv_lane_order(w8, x[:2], True).view(np.uint32))
+    # a Q8_0-weight prefill kernel does not exist: refused, not approximated
+    big = np.empty((40, 20), np.float32)
+    assert L.tcrv_cuda_host_gemm_q8_0_q8_0(1024, big.ctypes.data, w8.ctypes.data, xh.ctypes.data, xh.strides[0], 40, 20,
+                                           w8.strides[0], 20) == -2
+    L.tcrv_cuda_host_release()
