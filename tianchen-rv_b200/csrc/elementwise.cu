@@ -49,7 +49,27 @@ __global__ void __launch_bounds__(kThreads) add_kernel(const T *__restrict__ lhs
     const V *l4 = reinterpret_cast<const V *>(lhs);
     const V *r4 = reinterpret_cast<const V *>(rhs);
     V *o4 = reinterpret_cast<V *>(out);
-    for (size_t i = tid; i < nvec; i += nthreads) {
+    // four vectors per thread and iteration, all eight loads issued before the first add
+    constexpr int kUnroll = 4;
+    size_t i = tid;
+    for (; i + (kUnroll - 1) * nthreads < nvec; i += kUnroll * nthreads) {
+      V a[kUnroll], b[kUnroll];
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        a[u] = __ldg(l4 + i + u * nthreads);
+        b[u] = __ldg(r4 + i + u * nthreads);
+      }
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        V c;
+        c.x = add_one(a[u].x, b[u].x);
+        c.y = add_one(a[u].y, b[u].y);
+        c.z = add_one(a[u].z, b[u].z);
+        c.w = add_one(a[u].w, b[u].w);
+        o4[i + u * nthreads] = c;
+      }
+    }
+    for (; i < nvec; i += nthreads) {
       V a = __ldg(l4 + i), b = __ldg(r4 + i), c;
       c.x = add_one(a.x, b.x);
       c.y = add_one(a.y, b.y);
@@ -57,8 +77,8 @@ __global__ void __launch_bounds__(kThreads) add_kernel(const T *__restrict__ lhs
       c.w = add_one(a.w, b.w);
       o4[i] = c;
     }
-    for (size_t i = nvec * 4 + tid; i < n; i += nthreads)
-      out[i] = add_one(lhs[i], rhs[i]);
+    for (size_t j = nvec * 4 + tid; j < n; j += nthreads)
+      out[j] = add_one(lhs[j], rhs[j]);
   } else {
     for (size_t i = tid; i < n; i += nthreads)
       out[i] = add_one(lhs[i], rhs[i]);
@@ -447,7 +467,7 @@ int launch_unpack_q4_0x16_to_q4_0(size_t nblocks, const uint8_t *src, uint8_t *d
 int launch_add_f32(const float *lhs, const float *rhs, float *out, size_t n, cudaStream_t stream) {
   if (n == 0)
     return TCRV_CUDA_OK;
-  const int grid = grid_for(n, kThreads * 8, 8);
+  const int grid = grid_for(n, kThreads * 16, 8);
   if (aligned16(lhs) && aligned16(rhs) && aligned16(out))
     add_kernel<float, true><<<grid, kThreads, 0, stream>>>(lhs, rhs, out, n);
   else
@@ -459,7 +479,7 @@ int launch_add_f32(const float *lhs, const float *rhs, float *out, size_t n, cud
 int launch_add_i32(const int32_t *lhs, const int32_t *rhs, int32_t *out, size_t n, cudaStream_t stream) {
   if (n == 0)
     return TCRV_CUDA_OK;
-  const int grid = grid_for(n, kThreads * 8, 8);
+  const int grid = grid_for(n, kThreads * 16, 8);
   if (aligned16(lhs) && aligned16(rhs) && aligned16(out))
     add_kernel<int32_t, true><<<grid, kThreads, 0, stream>>>(lhs, rhs, out, n);
   else
