@@ -31,6 +31,8 @@ METRIC = "q4_0_q8_0_decode_gemv_hbm_gbs"
 UNIT = "GB/s"
 WORKLOAD = "q4_0_q8_0_gemv_llama7b_layers_batch1"
 ROTATION_SETS = 8       # distinct copies of every weight matrix; 8 x 134 MB, far beyond the 126 MB L2
+GRAPH_STEPS = 16        # steps per CUDA graph of the timed region (measured: 8..32 steps 4.51-4.53 TB/s,
+                        # 64: 4.46, 128: 4.32, 256: 4.16 -- long graphs dispatch their nodes more slowly)
 MIN_WARM_SECONDS = 1.5  # warm-up runs at least this long so that the clock sampler sees load
 
 
@@ -220,16 +222,27 @@ def run_ours(args):
         with torch.cuda.graph(g, stream=side):
             launch_set(r)
         graphs.append(g)
-    rotation_graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(rotation_graph, stream=side):
-        for r in range(ROTATION_SETS):
-            launch_set(r)
+    # The timed region replays graphs that hold `--graph-steps` consecutive steps each (step i
+    # uses weight copy i mod 8), so that Python's per-call cost does not sit between kernels.
+    def steps_graph(count: int):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            for i in range(count):
+                launch_set(i % ROTATION_SETS)
+        return g
+
+    chunk = min(args.steps, args.graph_steps) // ROTATION_SETS * ROTATION_SETS  # keeps the rotation aligned
+    chunk_graph = steps_graph(chunk) if chunk > 0 else None
+    tail_steps = args.steps - (args.steps // chunk) * chunk if chunk > 0 else args.steps
+    tail_graph = steps_graph(tail_steps) if tail_steps > 0 else None
 
     def run_steps(count: int):
-        for _ in range(count // ROTATION_SETS):
-            rotation_graph.replay()
-        for i in range(count % ROTATION_SETS):
-            graphs[i].replay()
+        assert count == args.steps
+        if chunk_graph is not None:
+            for _ in range(count // chunk):
+                chunk_graph.replay()
+        if tail_graph is not None:
+            tail_graph.replay()
 
     def step(i: int):
         graphs[i % ROTATION_SETS].replay()
@@ -319,7 +332,7 @@ def run_ours(args):
         "data": "synthetic",
         "config": {"workload": WORKLOAD, "shapes": [f"{n}x{k}" for n, k in SHAPES], "batch": 1,
                    "l2": f"weights rotate over {ROTATION_SETS} distinct copies per shape ({ROTATION_SETS} x 134 MB in all, L2 is 126 MB)",
-                   "launch": f"CUDA graphs: {ROTATION_SETS} consecutive steps (4 GEMV kernels each) per graph, single-step graphs for the remainder",
+                   "launch": f"CUDA graphs of up to {args.graph_steps} consecutive steps (4 GEMV kernels each)",
                    "parallelism": "replicas only" if world > 1 else "single GPU"},
         "roofline": {"bound": "hbm", "achieved": round(per_gpu, 2), "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": round(per_gpu / peaks["hbm_gbs"], 4), "traffic": round(step_traffic / launches_per_step),
@@ -573,6 +586,7 @@ def main():
     ap.add_argument("--min-warm-seconds", type=float, default=MIN_WARM_SECONDS,
                     help="warm-up lasts at least this long (0 for a profiler's launch-list pass)")
     ap.add_argument("--skip-gemm", action="store_true", help="leave out the prefill-GEMM section")
+    ap.add_argument("--graph-steps", type=int, default=GRAPH_STEPS, help="steps captured per CUDA graph of the timed region")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
