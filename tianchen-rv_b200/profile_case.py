@@ -2,7 +2,8 @@
 
     python tianchen-rv_b200/profile_case.py gemv [--rows 32000] [--k 4096] [--cols 1] [--launches 6]
     python tianchen-rv_b200/profile_case.py gemm [--rows 11008] [--k 4096] [--tokens 512] [--launches 4]
-    python tianchen-rv_b200/profile_case.py dequant [--rows 4096] [--k 4096]
+    python tianchen-rv_b200/profile_case.py dequant | quantize [--rows 4096] [--k 4096]
+    python tianchen-rv_b200/profile_case.py silu | rms_norm [--rows 512] [--k 11008]
 
 Each case holds well under a few GB on the device and launches the kernel a handful of
 times over rotating weight copies larger than the L2, so DRAM counters mean something.
@@ -20,7 +21,7 @@ import __graft_entry__ as entry  # noqa: E402
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["gemv", "gemv_q8", "gemm", "dequant"])
+    ap.add_argument("case", choices=["gemv", "gemv_q8", "gemm", "dequant", "quantize", "silu", "rms_norm"])
     ap.add_argument("--rows", type=int, default=None)
     ap.add_argument("--k", type=int, default=4096)
     ap.add_argument("--cols", type=int, default=1)
@@ -51,6 +52,19 @@ def main():
         out = torch.empty((rows, args.tokens), dtype=torch.float32, device="cuda")
         for _ in range(args.launches):
             pkg.gemm(pw, x, out=out)
+    elif args.case in ("quantize", "silu", "rms_norm"):
+        rows = args.rows or (4096 if args.case == "quantize" else 512)
+        k = args.k if (args.case == "quantize" or args.k != 4096) else 11008
+        xs = [torch.randn((rows, k), generator=gen, device="cuda") for _ in range(6)]
+        out = torch.empty((rows, k), dtype=torch.float32, device="cuda")
+        qout = torch.empty((rows, k // 32 * 34), dtype=torch.uint8, device="cuda")
+        for i in range(args.launches):
+            if args.case == "quantize":
+                pkg.quantize_q8_0(xs[i % len(xs)], out=qout)
+            elif args.case == "silu":
+                pkg.vec_silu(xs[i % len(xs)], out=out)
+            else:
+                pkg.rms_norm(xs[i % len(xs)], 1e-6, out=out)
     else:
         rows = args.rows or 4096
         q = pkg.quantize_q8_0(torch.randn((rows, args.k), generator=gen, device="cuda") * 0.02)
