@@ -196,6 +196,51 @@ int tcrv_cuda_vec_dot_q5_1_q8_1(size_t n, float *s, const uint8_t *vx, const uin
 int tcrv_cuda_pack_q4_0_to_q4_0x16(size_t nblocks, const uint8_t *src, uint8_t *dst, tcrv_cuda_stream stream);
 int tcrv_cuda_unpack_q4_0x16_to_q4_0(size_t nblocks, const uint8_t *src, uint8_t *dst, tcrv_cuda_stream stream);
 
+/* ---- consumers of the 16-row interleaved weight layouts ------------------------------------
+ * Decode GEMV reading block_q4_0x16 (288 B) or block_q8_0x16 (544 B: 16 fp16 scales, then
+ * byte 32 + 16*i + r = element i of row r) weights directly: group g of 16 weight rows is nb
+ * consecutive blocks at vx + g*nb*block_bytes, vy is ONE plain block_q8_0 column, and
+ *   s[16*g + r] = sum over blocks of fma((float)sumi, d_w * d_a, .)
+ * with d_w * d_a the exact product of the two fp16 scales.  Replace
+ * tcrv_rvv.repack_gemv_q4_0_q8_0 (lib/Conversion/RVV/RVVToEmitCBlockQuantLinear.cpp:2853-3344)
+ * and tcrv_rvv.repack_gemv_q8_0_q8_0 (:3930-4378); ABI order n, s, vx, vy, nc (nc = weight
+ * rows, a multiple of 16; test/Conversion/RVV/rvv-to-emitc-repack-gemv-q4-0-q8-0.mlir:27-31).
+ * Integer block sums are exact.  The fp32 summation order is the kernel's, not the
+ * reference's strict block order: the ceil(nb/8) steps of 8 blocks are cut into
+ * tcrv_cuda_repack_gemv_parts(n) contiguous ranges; inside a range chain c (0..7) folds
+ * blocks 8*step + c in ascending order from 0.0f, the chains are added as
+ * ((c0+c4) + (c2+c6)) + ((c1+c5) + (c3+c7)), and the ranges in ascending order.  The order
+ * depends on n alone (not on nc or the GPU).  vx must be 16-byte aligned (bulk copies).
+ * `flags`: 0, or tuning overrides (bits 8..11 ring depth, bits 16..19 copies in flight). */
+size_t tcrv_cuda_repack_gemv_parts(size_t n);
+int tcrv_cuda_repack_gemv_q4_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t nc,
+                                    unsigned flags, tcrv_cuda_stream stream);
+int tcrv_cuda_repack_gemv_q8_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t nc,
+                                    unsigned flags, tcrv_cuda_stream stream);
+
+/* Prefill GEMM over the interleaved layouts: weights in block_q4_0x16 groups (nc weight rows,
+ * a multiple of 16), activations in block_q8_0x4 groups (136 B: 4 fp16 scales, then byte
+ * 8 + 4*i + c = element i of column c; group y of 4 activation rows is nb consecutive blocks
+ * at vy + y*nb*136; nr activation rows, a multiple of 4), output token-major:
+ *   s[(4y + c)*bs + 16x + r] = sum over blocks, in strict ascending order, of
+ *                              fma((float)sumi, d_w * d_a, .)
+ * Replaces tcrv_rvv.repack_gemm_q4_0_q8_0 (lib/Conversion/RVV/RVVToEmitCBlockQuantLinear.cpp:
+ * 2122-2600; ABI order n, s, vx, vy, nr, nc, bs:
+ * test/Conversion/RVV/rvv-to-emitc-repack-gemm-q4-0-q8-0.mlir:22-28) bit for bit.  Runs on the
+ * tensor-core kernel of the plain GEMM: both operands are first unpacked into its planar
+ * form inside `workspace` (256-byte aligned, tcrv_cuda_repack_gemm_workspace_bytes(n, nr, nc)
+ * bytes).  Resident weights: unpack them once with `_prepare_weights_q4_0x16` into
+ * tcrv_cuda_gemm_weights_bytes(n, nc) bytes and call `_prepared` with a workspace of
+ * tcrv_cuda_gemm_acts_workspace_bytes(n, nr) bytes for the per-call activation copy. */
+size_t tcrv_cuda_repack_gemm_workspace_bytes(size_t n, size_t nr, size_t nc);
+int tcrv_cuda_repack_gemm_q4_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t nr, size_t nc,
+                                    size_t bs, void *workspace, size_t workspace_bytes, tcrv_cuda_stream stream);
+int tcrv_cuda_repack_gemm_prepare_weights_q4_0x16(size_t n, const uint8_t *vx, size_t nc, void *prepared,
+                                                  size_t prepared_bytes, tcrv_cuda_stream stream);
+int tcrv_cuda_repack_gemm_q4_0_q8_0_prepared(size_t n, float *s, const void *prepared_weights, const uint8_t *vy,
+                                             size_t nr, size_t nc, size_t bs, void *workspace, size_t workspace_bytes,
+                                             tcrv_cuda_stream stream);
+
 /* ---- f32 forward-pass ops the reference compiles next to the quantized matmul ----------
  * Bit-exact with the reference's arithmetic (every operation IEEE round-to-nearest, nothing
  * fused that the reference does not fuse); see each entry for the one exception. */

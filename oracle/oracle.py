@@ -69,6 +69,13 @@ def _declare(L: ctypes.CDLL) -> None:
     L.tcrv_oracle_rope_thetas.argtypes = [_sz, ctypes.c_float, ctypes.c_float, _p]
     L.tcrv_oracle_pack_q4_0_to_q4_0x16.argtypes = [_sz, _p, _p]
     L.tcrv_oracle_unpack_q4_0x16_to_q4_0.argtypes = [_sz, _p, _p]
+    L.tcrv_oracle_rows_to_q4_0x16.argtypes = [_sz, _sz, _p, _p]
+    L.tcrv_oracle_rows_to_q8_0x16.argtypes = [_sz, _sz, _p, _p]
+    L.tcrv_oracle_rows_to_q8_0x4.argtypes = [_sz, _sz, _p, _p]
+    L.tcrv_oracle_repack_gemv_q4_0_q8_0.argtypes = [_sz, _p, _p, _p, _sz]
+    L.tcrv_oracle_repack_gemv_q8_0_q8_0.argtypes = [_sz, _p, _p, _p, _sz]
+    L.tcrv_oracle_repack_gemv_split_order.argtypes = [ctypes.c_int, _sz, _p, _p, _p, _sz, _sz]
+    L.tcrv_oracle_repack_gemm_q4_0_q8_0.argtypes = [_sz, _p, _p, _p, _sz, _sz, _sz]
     L.tcrv_oracle_sibling_block_sums.argtypes = [ctypes.c_int, _sz, _p, _p, _p]
     L.tcrv_oracle_sibling_vec_dot.argtypes = [ctypes.c_int, _sz, _p, _p, _p, ctypes.c_int]
     L.tcrv_oracle_fill_uniform.argtypes = [_p, _sz, ctypes.c_uint64, ctypes.c_float, ctypes.c_float]
@@ -256,6 +263,63 @@ def unpack_q4_0x16_to_q4_0(src: np.ndarray) -> np.ndarray:
     dst = np.empty_like(src)
     lib().tcrv_oracle_unpack_q4_0x16_to_q4_0(src.size // 288, _ptr(src), _ptr(dst))
     return dst
+
+
+def rows_to_q4_0x16(w: np.ndarray) -> np.ndarray:
+    """Plain Q4_0 rows [nc][nb*18] (nc a multiple of 16) -> block_q4_0x16 groups, flat uint8."""
+    w = np.ascontiguousarray(w, dtype=np.uint8)
+    nc, nb = w.shape[0], w.shape[1] // 18
+    assert nc % 16 == 0
+    dst = np.empty(nc // 16 * nb * 288, dtype=np.uint8)
+    lib().tcrv_oracle_rows_to_q4_0x16(nb * 32, nc, _ptr(w), _ptr(dst))
+    return dst
+
+
+def rows_to_q8_0x16(w: np.ndarray) -> np.ndarray:
+    """Plain Q8_0 rows [nc][nb*34] -> block_q8_0x16 groups, flat uint8."""
+    w = np.ascontiguousarray(w, dtype=np.uint8)
+    nc, nb = w.shape[0], w.shape[1] // 34
+    assert nc % 16 == 0
+    dst = np.empty(nc // 16 * nb * 544, dtype=np.uint8)
+    lib().tcrv_oracle_rows_to_q8_0x16(nb * 32, nc, _ptr(w), _ptr(dst))
+    return dst
+
+
+def rows_to_q8_0x4(x: np.ndarray) -> np.ndarray:
+    """Plain Q8_0 activation rows [nr][nb*34] (nr a multiple of 4) -> block_q8_0x4 groups."""
+    x = np.ascontiguousarray(x, dtype=np.uint8)
+    nr, nb = x.shape[0], x.shape[1] // 34
+    assert nr % 4 == 0
+    dst = np.empty(nr // 4 * nb * 136, dtype=np.uint8)
+    lib().tcrv_oracle_rows_to_q8_0x4(nb * 32, nr, _ptr(x), _ptr(dst))
+    return dst
+
+
+def repack_gemv(wx16: np.ndarray, x_row: np.ndarray, nc: int, q8_weights: bool = False, parts: int = 0) -> np.ndarray:
+    """Repacked GEMV: s[nc].  parts = 0: the reference's strict block order; parts >= 1: the
+    CUDA kernel's summation order with that many ranges."""
+    wx16 = np.ascontiguousarray(wx16, dtype=np.uint8).reshape(-1)
+    x_row = np.ascontiguousarray(x_row, dtype=np.uint8).reshape(-1)
+    n = x_row.size // 34 * 32
+    assert wx16.size == nc // 16 * (n // 32) * (544 if q8_weights else 288)
+    s = np.empty(nc, dtype=np.float32)
+    if parts == 0:
+        fn = lib().tcrv_oracle_repack_gemv_q8_0_q8_0 if q8_weights else lib().tcrv_oracle_repack_gemv_q4_0_q8_0
+        fn(n, _ptr(s), _ptr(wx16), _ptr(x_row), nc)
+    else:
+        lib().tcrv_oracle_repack_gemv_split_order(int(q8_weights), n, _ptr(s), _ptr(wx16), _ptr(x_row), nc, parts)
+    return s
+
+
+def repack_gemm(wx16: np.ndarray, xx4: np.ndarray, n: int, nr: int, nc: int, bs: int = 0) -> np.ndarray:
+    """Repacked GEMM: s[nr][bs] (bs defaults to nc), token-major."""
+    wx16 = np.ascontiguousarray(wx16, dtype=np.uint8).reshape(-1)
+    xx4 = np.ascontiguousarray(xx4, dtype=np.uint8).reshape(-1)
+    bs = bs or nc
+    assert wx16.size == nc // 16 * (n // 32) * 288 and xx4.size == nr // 4 * (n // 32) * 136
+    s = np.zeros((nr, bs), dtype=np.float32)
+    lib().tcrv_oracle_repack_gemm_q4_0_q8_0(n, _ptr(s), _ptr(wx16), _ptr(xx4), nr, nc, bs)
+    return s
 
 
 FORMAT_Q4_1_Q8_1, FORMAT_Q5_0_Q8_0, FORMAT_Q5_1_Q8_1 = 1, 2, 3

@@ -671,3 +671,156 @@ void tcrv_oracle_sibling_vec_dot(int format, size_t n, float *s, const uint8_t *
   }
   *s = sumf;
 }
+
+/* ---- consumers of the 16-row interleaved weight layouts --------------------------------- */
+
+enum { X16_Q4_BYTES = 288, X16_Q8_BYTES = 544, X4_Q8_BYTES = 136 };
+
+void tcrv_oracle_rows_to_q4_0x16(size_t n, size_t nc, const uint8_t *plain, uint8_t *dst) {
+  const size_t nb = n / 32;
+  uint8_t run[16 * 18];
+  for (size_t g = 0; g < nc / 16; ++g)
+    for (size_t l = 0; l < nb; ++l) {
+      for (size_t r = 0; r < 16; ++r)
+        memcpy(run + r * 18, plain + ((g * 16 + r) * nb + l) * 18, 18);
+      tcrv_oracle_pack_q4_0_to_q4_0x16(1, run, dst + (g * nb + l) * X16_Q4_BYTES);
+    }
+}
+
+void tcrv_oracle_rows_to_q8_0x16(size_t n, size_t nc, const uint8_t *plain, uint8_t *dst) {
+  const size_t nb = n / 32;
+  for (size_t g = 0; g < nc / 16; ++g)
+    for (size_t l = 0; l < nb; ++l) {
+      uint8_t *out = dst + (g * nb + l) * X16_Q8_BYTES;
+      for (size_t r = 0; r < 16; ++r) {
+        const uint8_t *in = plain + ((g * 16 + r) * nb + l) * 34;
+        out[2 * r] = in[0];
+        out[2 * r + 1] = in[1];
+        for (size_t i = 0; i < 32; ++i)
+          out[32 + i * 16 + r] = in[2 + i];
+      }
+    }
+}
+
+void tcrv_oracle_rows_to_q8_0x4(size_t n, size_t nr, const uint8_t *plain, uint8_t *dst) {
+  const size_t nb = n / 32;
+  for (size_t y = 0; y < nr / 4; ++y)
+    for (size_t l = 0; l < nb; ++l) {
+      uint8_t *out = dst + (y * nb + l) * X4_Q8_BYTES;
+      for (size_t c = 0; c < 4; ++c) {
+        const uint8_t *in = plain + ((y * 4 + c) * nb + l) * 34;
+        out[2 * c] = in[0];
+        out[2 * c + 1] = in[1];
+        for (size_t i = 0; i < 32; ++i)
+          out[8 + i * 4 + c] = in[2 + i];
+      }
+    }
+}
+
+/* Integer stage of one x16 block against one activation column, all 16 lanes.  q4: two int16
+ * lane accumulators (low / high nibbles, sign-extended by shifts: the xor 0x88 is in the
+ * layout), then the widening add; q8: int32 lane accumulators.  `aq` points at the 32
+ * activation quants, `astep` is their stride (1 plain, 4 inside block_q8_0x4). */
+static void x16_block_sums(int q8w, const uint8_t *bl, const int8_t *aq, size_t astep, int32_t sumi[16]) {
+  if (q8w) {
+    for (size_t r = 0; r < 16; ++r)
+      sumi[r] = 0;
+    for (size_t i = 0; i < 32; ++i)
+      for (size_t r = 0; r < 16; ++r) {
+        const int16_t prod = (int16_t)((int16_t)(int8_t)bl[32 + i * 16 + r] * (int16_t)aq[i * astep]);
+        sumi[r] += prod;
+      }
+  } else {
+    int16_t lo[16] = {0}, hi[16] = {0};
+    for (size_t i = 0; i < 16; ++i)
+      for (size_t r = 0; r < 16; ++r) {
+        const uint8_t u = bl[32 + i * 16 + r];
+        const int8_t blo = (int8_t)((int8_t)(uint8_t)(u << 4) >> 4), bhi = (int8_t)((int8_t)u >> 4);
+        lo[r] = (int16_t)(lo[r] + aq[i * astep] * blo);
+        hi[r] = (int16_t)(hi[r] + aq[(16 + i) * astep] * bhi);
+      }
+    for (size_t r = 0; r < 16; ++r)
+      sumi[r] = (int32_t)lo[r] + (int32_t)hi[r];
+  }
+}
+
+/* vfwmul of two fp16 scales: the exact product, representable in f32. */
+static float x16_scale(const uint8_t *bl, size_t r, uint16_t da) {
+  return tcrv_oracle_fp16_to_fp32(read_u16(bl + 2 * r)) * tcrv_oracle_fp16_to_fp32(da);
+}
+
+static void repack_gemv_strict(int q8w, size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t nc) {
+  const size_t nb = n / 32, wb = q8w ? X16_Q8_BYTES : X16_Q4_BYTES;
+  for (size_t x = 0; x < nc / 16; ++x) {
+    float sumf[16] = {0};
+    for (size_t l = 0; l < nb; ++l) {
+      const uint8_t *bl = vx + (x * nb + l) * wb, *al = vy + l * 34;
+      int32_t sumi[16];
+      x16_block_sums(q8w, bl, (const int8_t *)(al + 2), 1, sumi);
+      for (size_t r = 0; r < 16; ++r)
+        sumf[r] = fmaf((float)sumi[r], x16_scale(bl, r, read_u16(al)), sumf[r]);
+    }
+    for (size_t r = 0; r < 16; ++r)
+      s[x * 16 + r] = sumf[r];
+  }
+}
+
+void tcrv_oracle_repack_gemv_q4_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t nc) {
+  repack_gemv_strict(0, n, s, vx, vy, nc);
+}
+
+void tcrv_oracle_repack_gemv_q8_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t nc) {
+  repack_gemv_strict(1, n, s, vx, vy, nc);
+}
+
+void tcrv_oracle_repack_gemv_split_order(int q8w, size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t nc,
+                                         size_t parts) {
+  const size_t nb = n / 32, wb = q8w ? X16_Q8_BYTES : X16_Q4_BYTES;
+  const size_t steps = (nb + 7) / 8;
+  for (size_t x = 0; x < nc / 16; ++x) {
+    float total[16] = {0};
+    for (size_t j = 0; j < parts; ++j) {
+      const size_t s0 = j * steps / parts, s1 = (j + 1) * steps / parts;
+      float chain[8][16];
+      memset(chain, 0, sizeof chain);
+      for (size_t st = s0; st < s1; ++st)
+        for (size_t c = 0; c < 8; ++c) {
+          const size_t l = st * 8 + c;
+          if (l >= nb)
+            continue;
+          const uint8_t *bl = vx + (x * nb + l) * wb, *al = vy + l * 34;
+          int32_t sumi[16];
+          x16_block_sums(q8w, bl, (const int8_t *)(al + 2), 1, sumi);
+          for (size_t r = 0; r < 16; ++r)
+            chain[c][r] = fmaf((float)sumi[r], x16_scale(bl, r, read_u16(al)), chain[c][r]);
+        }
+      for (size_t r = 0; r < 16; ++r) {
+        const float t0 = chain[0][r] + chain[4][r], t1 = chain[1][r] + chain[5][r];
+        const float t2 = chain[2][r] + chain[6][r], t3 = chain[3][r] + chain[7][r];
+        const float p = (t0 + t2) + (t1 + t3);
+        total[r] = j == 0 ? p : total[r] + p;
+      }
+    }
+    for (size_t r = 0; r < 16; ++r)
+      s[x * 16 + r] = total[r];
+  }
+}
+
+void tcrv_oracle_repack_gemm_q4_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t nr, size_t nc,
+                                       size_t bs) {
+  const size_t nb = n / 32;
+  for (size_t y = 0; y < nr / 4; ++y)
+    for (size_t x = 0; x < nc / 16; ++x)
+      for (size_t c = 0; c < 4; ++c) {
+        float sumf[16] = {0};
+        for (size_t l = 0; l < nb; ++l) {
+          const uint8_t *bl = vx + (x * nb + l) * X16_Q4_BYTES, *al = vy + (y * nb + l) * X4_Q8_BYTES;
+          int32_t sumi[16];
+          x16_block_sums(0, bl, (const int8_t *)(al + 8 + c), 4, sumi);
+          for (size_t r = 0; r < 16; ++r)
+            sumf[r] = fmaf((float)sumi[r], x16_scale(bl, r, read_u16(al + 2 * c)), sumf[r]);
+        }
+        for (size_t r = 0; r < 16; ++r)
+          s[(y * 4 + c) * bs + x * 16 + r] = sumf[r];
+      }
+}

@@ -133,6 +133,37 @@ void tcrv_oracle_rope_thetas(size_t n_pairs, float theta_base, float theta_scale
 void tcrv_oracle_pack_q4_0_to_q4_0x16(size_t nblocks, const uint8_t *src, uint8_t *dst);
 void tcrv_oracle_unpack_q4_0x16_to_q4_0(size_t nblocks, const uint8_t *src, uint8_t *dst);
 
+/* Layout builders for the consumers below, from plain row-major block rows (row r, block l at
+ * (r*nb + l) * block bytes).  block_q4_0x16 of group g, block l = pack of the 16 blocks
+ * (row 16g+j, block l); block_q8_0x16 (544 B): 16 fp16 scales, then qs[i*16 + r] = element i
+ * of row r; block_q8_0x4 (136 B): 4 fp16 scales, then qs[i*4 + c] = element i of column c
+ * (the offsets the emitters read: RVVToEmitCBlockQuantLinear.cpp:2912-2936, 3990-4016,
+ * 2186-2236). */
+void tcrv_oracle_rows_to_q4_0x16(size_t n, size_t nc, const uint8_t *plain, uint8_t *dst);
+void tcrv_oracle_rows_to_q8_0x16(size_t n, size_t nc, const uint8_t *plain, uint8_t *dst);
+void tcrv_oracle_rows_to_q8_0x4(size_t n, size_t nr, const uint8_t *plain, uint8_t *dst);
+
+/* tcrv_rvv.repack_gemv_q4_0_q8_0 (RVVToEmitCBlockQuantLinear.cpp:2853-3344) and
+ * tcrv_rvv.repack_gemv_q8_0_q8_0 (:3930-4378): for every group x of 16 weight rows and every
+ * block l in ascending order, lane-wise integer sums (q4: int16 vwmacc of the sign-extended
+ * low and high nibbles, then vwadd; q8: int16 products added into int32), then
+ * sumf = fma((float)sumi, d_w * d_a, sumf) with d_w * d_a the exact product of the two fp16
+ * scales (vfwmul, vfcvt, vfmacc); s[x*16 + r] = sumf.  ABI order n, s, vx, vy, nc. */
+void tcrv_oracle_repack_gemv_q4_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t nc);
+void tcrv_oracle_repack_gemv_q8_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t nc);
+/* The same sums and folds in the summation order of the CUDA kernel: the ceil(nb/8) steps of
+ * 8 blocks are cut into `parts` contiguous ranges (range j = steps [j*steps/parts,
+ * (j+1)*steps/parts)); inside a range chain c (0..7) folds blocks 8*step + c in ascending
+ * order from 0.0f; the chains are added as ((c0+c4) + (c2+c6)) + ((c1+c5) + (c3+c7)) and the
+ * ranges in ascending order. */
+void tcrv_oracle_repack_gemv_split_order(int q8_weights, size_t n, float *s, const uint8_t *vx, const uint8_t *vy,
+                                         size_t nc, size_t parts);
+/* tcrv_rvv.repack_gemm_q4_0_q8_0 (RVVToEmitCBlockQuantLinear.cpp:2122-2600): activations in
+ * block_q8_0x4 groups of 4 columns; per (row group y, column c, weight group x) the GEMV's
+ * block loop; s[(y*4 + c)*bs + x*16 + r].  ABI order n, s, vx, vy, nr, nc, bs. */
+void tcrv_oracle_repack_gemm_q4_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t nr, size_t nc,
+                                       size_t bs);
+
 /* Block dequantisation y = d * q.  Per element this is the i32->f32 dequantize math
  * (RVVToEmitC.cpp:3347-3394) with d read from the block header. */
 void tcrv_oracle_dequantize_row_q8_0(const uint8_t *vx, float *y, size_t n);

@@ -279,6 +279,53 @@ def test_q4_0x16_pack_layout_and_inverse(O):
     assert np.array_equal(O.unpack_q4_0x16_to_q4_0(dst), src)
 
 
+def test_x16_layout_builders_and_repacked_consumers(O):
+    nc, k, nb = 32, 320, 10
+    w4 = O.quantize_q4_0(O.fill_normal(nc * k, 11, 0.0, 0.02).reshape(nc, k))
+    w8 = O.quantize_q8_0(O.fill_normal(nc * k, 12, 0.0, 0.02).reshape(nc, k))
+    xs = O.quantize_q8_0(O.fill_normal(4 * k, 13).reshape(4, k))
+    # block_q4_0x16 of group g, block l = the pack op applied to the blocks (row 16g+j, block l)
+    gathered = w4.reshape(nc // 16, 16, nb, 18).transpose(0, 2, 1, 3).reshape(-1)
+    wx4 = O.rows_to_q4_0x16(w4)
+    assert np.array_equal(wx4, O.pack_q4_0_to_q4_0x16(gathered))
+    # block_q8_0x16 / block_q8_0x4 byte positions, spelled out from the offsets the emitters read
+    wx8, xx4 = O.rows_to_q8_0x16(w8), O.rows_to_q8_0x4(xs)
+    g, l, r, i = 1, 7, 5, 29
+    blk = wx8[(g * nb + l) * 544:][:544]
+    src = w8[16 * g + r, l * 34:][:34]
+    assert blk[2 * r] == src[0] and blk[2 * r + 1] == src[1] and blk[32 + i * 16 + r] == src[2 + i]
+    c = 3
+    ablk = xx4[l * 136:][:136]
+    asrc = xs[c, l * 34:][:34]
+    assert ablk[2 * c] == asrc[0] and ablk[2 * c + 1] == asrc[1]
+    assert ablk[8 + 5 * 4 + c] == asrc[2 + 5] and ablk[8 + 64 + 9 * 4 + c] == asrc[2 + 16 + 9]
+    # Q8_0 weights: the repacked op folds exactly like the plain Q8_0 block dot (fused form)
+    s8 = O.repack_gemv(wx8, xs[0], nc, q8_weights=True)
+    assert np.array_equal(s8.view(np.uint32), O.gemm(w8, xs[:1], q8_weights=True, fold=O.FOLD_FMA)[:, 0].view(np.uint32))
+    # Q4_0 weights: integer sums are the plain op's; the fold multiplies the scales first,
+    # restated here in float64 (products exact, one rounding per block)
+    sums = O.block_sums(w4, xs[:1])[:, 0, :]
+    dw = w4.reshape(nc, nb, 18)[:, :, :2].copy().view(np.float16).astype(np.float64)[:, :, 0]
+    da = xs[0].reshape(nb, 34)[:, :2].copy().view(np.float16).astype(np.float64)[:, 0]
+    acc = np.zeros(nc, dtype=np.float32)
+    for b in range(nb):
+        acc = (sums[:, b].astype(np.float64) * (dw[:, b] * da[b]) + acc.astype(np.float64)).astype(np.float32)
+    s4 = O.repack_gemv(wx4, xs[0], nc)
+    assert np.allclose(s4, acc, rtol=0, atol=1e-7) and np.mean(s4 == acc) > 0.9
+    # the GEMM is the GEMV per activation column, token-major, and honours the row stride
+    sg = O.repack_gemm(wx4, xx4, k, 4, nc, bs=nc + 3)
+    for t in range(4):
+        assert np.array_equal(sg[t, :nc].view(np.uint32), O.repack_gemv(wx4, xs[t], nc).view(np.uint32))
+    assert np.all(sg[:, nc:] == 0)
+    # kernel order: with one range and at most 8 blocks every chain holds one block
+    w1 = O.rows_to_q4_0x16(w4[:16, :18 * 8].copy())
+    x1 = xs[0, :34 * 8].copy()
+    one = O.repack_gemv(w1, x1, 16, parts=1)
+    assert np.allclose(one, O.repack_gemv(w1, x1, 16), rtol=0, atol=1e-6)
+    for parts in (1, 2):
+        assert np.allclose(O.repack_gemv(wx4, xs[0], nc, parts=parts), s4, rtol=0, atol=1e-6)
+
+
 @pytest.mark.parametrize("fmt", [1, 2, 3])
 def test_sibling_formats_integer_stage_and_folds(O, fmt):
     import sibling_data as sd

@@ -61,6 +61,13 @@ ABI = {
     "tcrv_cuda_rope_apply_f32": [_sz, _p, _p, _p, _sz, _sz, _sz, _p],
     "tcrv_cuda_pack_q4_0_to_q4_0x16": [_sz, _p, _p, _p],
     "tcrv_cuda_unpack_q4_0x16_to_q4_0": [_sz, _p, _p, _p],
+    "tcrv_cuda_repack_gemv_parts": [_sz],
+    "tcrv_cuda_repack_gemv_q4_0_q8_0": [_sz, _p, _p, _p, _sz, ctypes.c_uint, _p],
+    "tcrv_cuda_repack_gemv_q8_0_q8_0": [_sz, _p, _p, _p, _sz, ctypes.c_uint, _p],
+    "tcrv_cuda_repack_gemm_workspace_bytes": [_sz, _sz, _sz],
+    "tcrv_cuda_repack_gemm_q4_0_q8_0": [_sz, _p, _p, _p, _sz, _sz, _sz, _p, _sz, _p],
+    "tcrv_cuda_repack_gemm_prepare_weights_q4_0x16": [_sz, _p, _sz, _p, _sz, _p],
+    "tcrv_cuda_repack_gemm_q4_0_q8_0_prepared": [_sz, _p, _p, _p, _sz, _sz, _sz, _p, _sz, _p],
     "tcrv_cuda_sibling_dot_rows": [ctypes.c_int, _sz, _p, _p, _p, _sz, _sz, _sz, _sz, _sz, _p],
     "tcrv_cuda_sibling_block_sums": [ctypes.c_int, _sz, _p, _p, _p, _sz, _sz, _sz, _sz, _p],
     "tcrv_cuda_vec_dot_q4_1_q8_1": [_sz, _p, _p, _p, _p],
@@ -103,6 +110,8 @@ _RESTYPES = {
     "tcrv_cuda_gemm_weights_bytes": _sz,
     "tcrv_cuda_gemm_acts_workspace_bytes": _sz,
     "tcrv_cuda_gemm_workspace_bytes": _sz,
+    "tcrv_cuda_repack_gemv_parts": _sz,
+    "tcrv_cuda_repack_gemm_workspace_bytes": _sz,
 }
 
 _lib = None
@@ -393,6 +402,85 @@ def unpack_q4_0x16_to_q4_0(src, out=None):
     _check(lib().tcrv_cuda_unpack_q4_0x16_to_q4_0(src.numel() // 288, _dev(src, torch.uint8), _dev(out, torch.uint8),
                                                   _stream()), "tcrv_cuda_unpack_q4_0x16_to_q4_0")
     return out
+
+
+def repack_gemv_parts(n: int) -> int:
+    """Number of contiguous block ranges the repacked GEMV sums separately for rows of n elements."""
+    return int(lib().tcrv_cuda_repack_gemv_parts(n))
+
+
+def repack_gemv(wx16, x, nc: int, q8_weights: bool = False, out=None, flags: int = 0):
+    """Decode GEMV over 16-row interleaved weights: `wx16` is the flat block_q4_0x16 (or
+    block_q8_0x16) stream of nc / 16 row groups, `x` one plain Q8_0 activation row; returns
+    the nc fp32 results (tcrv_rvv.repack_gemv_q4_0_q8_0 / repack_gemv_q8_0_q8_0)."""
+    import torch
+
+    block = 544 if q8_weights else 288
+    nb = x.numel() // Q8_0_BLOCK
+    if x.numel() % Q8_0_BLOCK or nc % 16 or wx16.numel() != nc // 16 * nb * block:
+        raise ValueError("weights, activation and nc do not describe the same shape")
+    if out is None:
+        out = torch.empty(nc, dtype=torch.float32, device=wx16.device)
+    fn = lib().tcrv_cuda_repack_gemv_q8_0_q8_0 if q8_weights else lib().tcrv_cuda_repack_gemv_q4_0_q8_0
+    _check(fn(nb * QK, _dev(out, torch.float32), _dev(wx16, torch.uint8), _dev(x, torch.uint8), nc, flags, _stream()),
+           "tcrv_cuda_repack_gemv")
+    return out
+
+
+def repack_gemm(wx16, xx4, n: int, nr: int, nc: int, out=None, workspace=None):
+    """Prefill GEMM over the interleaved layouts: `wx16` the block_q4_0x16 stream of nc / 16
+    weight-row groups, `xx4` the block_q8_0x4 stream of nr / 4 activation-row groups; returns
+    the token-major result out[nr, nc] (tcrv_rvv.repack_gemm_q4_0_q8_0)."""
+    import torch
+
+    nb = n // QK
+    if n % QK or nr % 4 or nc % 16 or wx16.numel() != nc // 16 * nb * 288 or xx4.numel() != nr // 4 * nb * 136:
+        raise ValueError("weights, activations, n, nr and nc do not describe the same shape")
+    if out is None:
+        out = torch.empty((nr, nc), dtype=torch.float32, device=wx16.device)
+    need = int(lib().tcrv_cuda_repack_gemm_workspace_bytes(n, nr, nc))
+    if workspace is None:
+        workspace = torch.empty(max(need, 256), dtype=torch.uint8, device=wx16.device)
+    if out.dtype != torch.float32 or out.stride(1) != 1:
+        raise ValueError("out must be fp32 with unit column stride")
+    _check(lib().tcrv_cuda_repack_gemm_q4_0_q8_0(n, out.data_ptr(), _dev(wx16, torch.uint8),
+                                                 _dev(xx4, torch.uint8), nr, nc, out.stride(0), workspace.data_ptr(),
+                                                 workspace.numel(), _stream()), "tcrv_cuda_repack_gemm_q4_0_q8_0")
+    return out
+
+
+class PreparedX16Weights:
+    """block_q4_0x16 weights unpacked once into the tensor-core GEMM's planar form."""
+
+    def __init__(self, wx16, n: int, nc: int):
+        import torch
+
+        if n % QK or nc % 16 or wx16.numel() != nc // 16 * (n // QK) * 288:
+            raise ValueError("weights, n and nc do not describe the same shape")
+        self.n, self.nc = n, nc
+        nbytes = int(lib().tcrv_cuda_gemm_weights_bytes(n, nc))
+        self.buffer = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=wx16.device)
+        _check(lib().tcrv_cuda_repack_gemm_prepare_weights_q4_0x16(n, _dev(wx16, torch.uint8), nc, self.buffer.data_ptr(),
+                                                                   self.buffer.numel(), _stream()),
+               "tcrv_cuda_repack_gemm_prepare_weights_q4_0x16")
+
+    def gemm(self, xx4, nr: int, out=None, workspace=None):
+        import torch
+
+        if nr % 4 or xx4.numel() != nr // 4 * (self.n // QK) * 136:
+            raise ValueError("activations and nr do not describe the same shape")
+        if out is None:
+            out = torch.empty((nr, self.nc), dtype=torch.float32, device=self.buffer.device)
+        need = int(lib().tcrv_cuda_gemm_acts_workspace_bytes(self.n, nr))
+        if workspace is None:
+            workspace = torch.empty(max(need, 256), dtype=torch.uint8, device=self.buffer.device)
+        if out.dtype != torch.float32 or out.stride(1) != 1:
+            raise ValueError("out must be fp32 with unit column stride")
+        _check(lib().tcrv_cuda_repack_gemm_q4_0_q8_0_prepared(self.n, out.data_ptr(), self.buffer.data_ptr(),
+                                                              _dev(xx4, torch.uint8), nr, self.nc, out.stride(0),
+                                                              workspace.data_ptr(), workspace.numel(), _stream()),
+               "tcrv_cuda_repack_gemm_q4_0_q8_0_prepared")
+        return out
 
 
 # ------------------------------------------------------------------ sibling block formats

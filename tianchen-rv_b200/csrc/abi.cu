@@ -381,6 +381,96 @@ int tcrv_cuda_vec_dot_q5_1_q8_1(size_t n, float *s, const uint8_t *vx, const uin
   return tcrv_cuda_sibling_dot_rows(TCRV_CUDA_FORMAT_Q5_1_Q8_1, n, s, vx, vy, 0, 1, 1, 0, 1, stream);
 }
 
+size_t tcrv_cuda_repack_gemv_parts(size_t n) { return repack_gemv_parts(n); }
+
+namespace {
+int check_repack_gemv_args(size_t n, const float *s, const uint8_t *vx, const uint8_t *vy, size_t nc) {
+  if (n % TCRV_QK != 0 || nc % 16 != 0)
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  if (nc != 0 && (!s || (reinterpret_cast<uintptr_t>(s) & 3u) != 0))
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  if (nc != 0 && n != 0 && (!vx || !vy || (reinterpret_cast<uintptr_t>(vx) & 15u) != 0))
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  return TCRV_CUDA_OK;
+}
+}  // namespace
+
+int tcrv_cuda_repack_gemv_q4_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t nc,
+                                    unsigned flags, tcrv_cuda_stream stream) {
+  const int st = check_repack_gemv_args(n, s, vx, vy, nc);
+  if (st != TCRV_CUDA_OK)
+    return st;
+  if (n == 0 && nc != 0)
+    TCRV_CUDA_TRY(cudaMemsetAsync(s, 0, nc * sizeof(float), as_stream(stream)));  // empty sums
+  return launch_repack_gemv_q4_0_q8_0(n, s, vx, vy, nc, flags, as_stream(stream));
+}
+
+int tcrv_cuda_repack_gemv_q8_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t nc,
+                                    unsigned flags, tcrv_cuda_stream stream) {
+  const int st = check_repack_gemv_args(n, s, vx, vy, nc);
+  if (st != TCRV_CUDA_OK)
+    return st;
+  if (n == 0 && nc != 0)
+    TCRV_CUDA_TRY(cudaMemsetAsync(s, 0, nc * sizeof(float), as_stream(stream)));
+  return launch_repack_gemv_q8_0_q8_0(n, s, vx, vy, nc, flags, as_stream(stream));
+}
+
+size_t tcrv_cuda_repack_gemm_workspace_bytes(size_t n, size_t nr, size_t nc) {
+  return gemm_weights_bytes(n, nc) + gemm_acts_bytes(n, nr);
+}
+
+int tcrv_cuda_repack_gemm_prepare_weights_q4_0x16(size_t n, const uint8_t *vx, size_t nc, void *prepared,
+                                                  size_t prepared_bytes, tcrv_cuda_stream stream) {
+  if (n % TCRV_QK != 0 || nc % 16 != 0 || (nc != 0 && n != 0 && (!vx || !prepared)))
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  if (prepared_bytes < gemm_weights_bytes(n, nc) || reinterpret_cast<uintptr_t>(prepared) % 256 != 0)
+    return TCRV_CUDA_ERR_WORKSPACE;
+  return launch_repack_gemm_prepare_weights_q4_0x16(n, vx, nc, static_cast<uint8_t *>(prepared), as_stream(stream));
+}
+
+int tcrv_cuda_repack_gemm_q4_0_q8_0_prepared(size_t n, float *s, const void *prepared_weights, const uint8_t *vy,
+                                             size_t nr, size_t nc, size_t bs, void *workspace, size_t workspace_bytes,
+                                             tcrv_cuda_stream stream) {
+  if (n % TCRV_QK != 0 || nr % 4 != 0 || nc % 16 != 0 || (nr > 1 && bs < nc))
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  if (nr != 0 && nc != 0 && (!s || (reinterpret_cast<uintptr_t>(s) & 3u) != 0))
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  if (nr == 0 || nc == 0)
+    return TCRV_CUDA_OK;
+  if (n == 0) {
+    for (size_t r = 0; r < nr; ++r)
+      TCRV_CUDA_TRY(cudaMemsetAsync(s + r * bs, 0, nc * sizeof(float), as_stream(stream)));
+    return TCRV_CUDA_OK;
+  }
+  if (!prepared_weights || !vy)
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  if (!workspace || workspace_bytes < gemm_acts_bytes(n, nr) || reinterpret_cast<uintptr_t>(workspace) % 256 != 0 ||
+      reinterpret_cast<uintptr_t>(prepared_weights) % 256 != 0)
+    return TCRV_CUDA_ERR_WORKSPACE;
+  return launch_repack_gemm_prepared(n, s, static_cast<const uint8_t *>(prepared_weights), vy, nr, nc, bs,
+                                     static_cast<uint8_t *>(workspace), as_stream(stream));
+}
+
+int tcrv_cuda_repack_gemm_q4_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t nr, size_t nc,
+                                    size_t bs, void *workspace, size_t workspace_bytes, tcrv_cuda_stream stream) {
+  if (n % TCRV_QK != 0 || nr % 4 != 0 || nc % 16 != 0)
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  if (nr == 0 || nc == 0 || n == 0)
+    return tcrv_cuda_repack_gemm_q4_0_q8_0_prepared(n, s, nullptr, vy, nr, nc, bs, nullptr, 0, stream);
+  if (!vx)
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  const size_t wbytes = gemm_weights_bytes(n, nc);
+  if (!workspace || workspace_bytes < wbytes + gemm_acts_bytes(n, nr) ||
+      reinterpret_cast<uintptr_t>(workspace) % 256 != 0)
+    return TCRV_CUDA_ERR_WORKSPACE;
+  uint8_t *ws = static_cast<uint8_t *>(workspace);
+  const int st = launch_repack_gemm_prepare_weights_q4_0x16(n, vx, nc, ws, as_stream(stream));
+  if (st != TCRV_CUDA_OK)
+    return st;
+  return tcrv_cuda_repack_gemm_q4_0_q8_0_prepared(n, s, ws, vy, nr, nc, bs, ws + wbytes, workspace_bytes - wbytes,
+                                                  stream);
+}
+
 int tcrv_cuda_peer_alloc(size_t bytes, void **ptr) {
   if (!ptr || bytes == 0)
     return TCRV_CUDA_ERR_INVALID_ARGUMENT;

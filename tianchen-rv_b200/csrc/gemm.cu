@@ -84,6 +84,64 @@ __global__ void __launch_bounds__(256) unpack_q8_0_kernel(const uint8_t *__restr
   }
 }
 
+// One thread per (row group, block, row): block_q4_0x16 (16 fp16 scales, then byte 32 + 16*i + r
+// = elements i and i+16 of row r as nibbles xor 0x88, i.e. 4-bit two's complement) to the
+// same planar form.
+__global__ void __launch_bounds__(256) unpack_q4_0x16_kernel(const uint8_t *__restrict__ vx, uint32_t rows, uint32_t nb,
+                                                             uint32_t nbp, int8_t *__restrict__ w8,
+                                                             float *__restrict__ dw) {
+  const size_t total = static_cast<size_t>(rows) * nb;
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const uint32_t r = static_cast<uint32_t>(i % 16);
+    const size_t gl = i / 16, ib = gl % nb, g = gl / nb;
+    const uint8_t *blk = vx + gl * 288;
+    uint32_t lo[4], hi[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      uint32_t q = 0;
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        q |= static_cast<uint32_t>(blk[32 + (4 * j + k) * 16 + r]) << (8 * k);
+      q ^= 0x88888888u;  // back to offset-binary nibbles
+      lo[j] = __vsub4(q & 0x0f0f0f0fu, 0x08080808u);
+      hi[j] = __vsub4((q >> 4) & 0x0f0f0f0fu, 0x08080808u);
+    }
+    const size_t row = g * 16 + r;
+    uint4 *dst = reinterpret_cast<uint4 *>(w8 + (row * nb + ib) * kQK);
+    dst[0] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+    dst[1] = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+    dw[row * nbp + ib] = half_bits_to_float(load_u16(blk + 2 * r));
+  }
+}
+
+// One thread per (column group, block, column): block_q8_0x4 (4 fp16 scales, then byte
+// 8 + 4*i + c = element i of column c) to the planar activations.
+__global__ void __launch_bounds__(256) unpack_q8_0x4_kernel(const uint8_t *__restrict__ vy, uint32_t cols, uint32_t nb,
+                                                            uint32_t ncp, int8_t *__restrict__ x8,
+                                                            float *__restrict__ dxt) {
+  const size_t total = static_cast<size_t>(cols) * nb;
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const uint32_t c = static_cast<uint32_t>(i % 4);
+    const size_t yl = i / 4, ib = yl % nb, y = yl / nb;
+    const uint8_t *blk = vy + yl * 136;
+    uint32_t q[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      q[j] = 0;
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        q[j] |= static_cast<uint32_t>(blk[8 + (4 * j + k) * 4 + c]) << (8 * k);
+    }
+    const size_t col = y * 4 + c;
+    uint4 *dst = reinterpret_cast<uint4 *>(x8 + (col * nb + ib) * kQK);
+    dst[0] = make_uint4(q[0], q[1], q[2], q[3]);
+    dst[1] = make_uint4(q[4], q[5], q[6], q[7]);
+    dxt[ib * ncp + col] = half_bits_to_float(load_u16(blk + 2 * c));
+  }
+}
+
 // ------------------------------------------------------------------- tensor maps
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
@@ -148,8 +206,9 @@ inline int blocks_for(size_t items) {
   return static_cast<int>(b < cap ? (b ? b : 1) : cap);
 }
 
+// `repack`: fold with the scales multiplied first and store token-major (dst[0][col*bs + row]).
 int run_gemm(size_t n, float *const *dst, size_t ndst, const uint8_t *weights_planar, const uint8_t *acts_planar,
-             size_t nr, size_t nc, size_t bs, cudaStream_t stream) {
+             size_t nr, size_t nc, size_t bs, cudaStream_t stream, bool repack = false) {
   const PlanarSizes p = planar_sizes(n, nr, nc);
   const int8_t *w8 = reinterpret_cast<const int8_t *>(weights_planar);
   const float *dw = reinterpret_cast<const float *>(weights_planar + p.w8);
@@ -183,21 +242,31 @@ int run_gemm(size_t n, float *const *dst, size_t ndst, const uint8_t *weights_pl
   args.tiles = static_cast<uint32_t>((nr + kGemmTileRows - 1) / kGemmTileRows) * args.tiles_m;
 
   const bool multi = ndst > 1;
-  static bool configured[64][2] = {};
+  if (repack && multi)
+    return TCRV_CUDA_ERR_UNSUPPORTED;
+  const int variant = repack ? 2 : (multi ? 1 : 0);
+  static bool configured[64][3] = {};
   int dev = 0;
   TCRV_CUDA_TRY(cudaGetDevice(&dev));
-  if (dev < 64 && !configured[dev][multi ? 1 : 0]) {
-    if (multi)
+  if (dev < 64 && !configured[dev][variant]) {
+    if (repack)
+      TCRV_CUDA_TRY(cudaFuncSetAttribute(gemm_q4_0_q8_0_tc_kernel<false, true>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(kGemmSmemBytesSingle)));
+    else if (multi)
       TCRV_CUDA_TRY(cudaFuncSetAttribute(gemm_q4_0_q8_0_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(kGemmSmemBytesMulti)));
     else
       TCRV_CUDA_TRY(cudaFuncSetAttribute(gemm_q4_0_q8_0_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(kGemmSmemBytesSingle)));
-    configured[dev][multi ? 1 : 0] = true;
+    configured[dev][variant] = true;
   }
   const int sms = sm_count();
   const int grid = static_cast<int>(args.tiles < static_cast<uint32_t>(sms) ? args.tiles : sms);
-  if (multi)
+  if (repack)
+    gemm_q4_0_q8_0_tc_kernel<false, true><<<grid, kGemmThreads, kGemmSmemBytesSingle, stream>>>(map_w, map_x, map_dw,
+                                                                                               map_dx, args);
+  else if (multi)
     gemm_q4_0_q8_0_tc_kernel<true><<<grid, kGemmThreads, kGemmSmemBytesMulti, stream>>>(map_w, map_x, map_dw, map_dx, args);
   else
     gemm_q4_0_q8_0_tc_kernel<false><<<grid, kGemmThreads, kGemmSmemBytesSingle, stream>>>(map_w, map_x, map_dw, map_dx,
@@ -273,6 +342,40 @@ int launch_gemm_prepared_multi(size_t n, float *const *dst, size_t ndst, const u
   if (nr == 0 || nc == 0)
     return TCRV_CUDA_OK;
   return run_gemm(n, dst, ndst, weights_planar, acts_planar, nr, nc, bs, stream);
+}
+
+// ------------------------------------------------------------ interleaved-layout consumer
+//
+// tcrv_rvv.repack_gemm_q4_0_q8_0: weights in block_q4_0x16 groups (`wrows` weight rows),
+// activations in block_q8_0x4 groups (`tokens` columns); both are unpacked into the planar
+// form and contracted by the same tensor-core kernel (kRepack instantiation).
+
+int launch_repack_gemm_prepare_weights_q4_0x16(size_t n, const uint8_t *vx, size_t wrows, uint8_t *prepared,
+                                               cudaStream_t stream) {
+  const PlanarSizes p = planar_sizes(n, wrows, 0);
+  if (wrows == 0 || p.nb == 0)
+    return TCRV_CUDA_OK;
+  if (p.nbp != p.nb)
+    TCRV_CUDA_TRY(cudaMemsetAsync(prepared + p.w8, 0, wrows * p.nbp * 4, stream));
+  unpack_q4_0x16_kernel<<<blocks_for(wrows * p.nb), 256, 0, stream>>>(
+      vx, static_cast<uint32_t>(wrows), static_cast<uint32_t>(p.nb), static_cast<uint32_t>(p.nbp),
+      reinterpret_cast<int8_t *>(prepared), reinterpret_cast<float *>(prepared + p.w8));
+  TCRV_CUDA_TRY(cudaGetLastError());
+  return TCRV_CUDA_OK;
+}
+
+int launch_repack_gemm_prepared(size_t n, float *s, const uint8_t *weights_planar, const uint8_t *vy, size_t tokens,
+                                size_t wrows, size_t bs, uint8_t *acts_planar, cudaStream_t stream) {
+  const PlanarSizes p = planar_sizes(n, 0, tokens);
+  if (tokens == 0 || wrows == 0 || p.nb == 0)
+    return TCRV_CUDA_OK;
+  if (p.ncp != tokens)
+    TCRV_CUDA_TRY(cudaMemsetAsync(acts_planar + p.x8, 0, p.nb * p.ncp * 4, stream));
+  unpack_q8_0x4_kernel<<<blocks_for(tokens * p.nb), 256, 0, stream>>>(
+      vy, static_cast<uint32_t>(tokens), static_cast<uint32_t>(p.nb), static_cast<uint32_t>(p.ncp),
+      reinterpret_cast<int8_t *>(acts_planar), reinterpret_cast<float *>(acts_planar + p.x8));
+  TCRV_CUDA_TRY(cudaGetLastError());
+  return run_gemm(n, &s, 1, weights_planar, acts_planar, wrows, tokens, bs, stream, /*repack=*/true);
 }
 
 // ------------------------------------------------------------ allocation-free variant

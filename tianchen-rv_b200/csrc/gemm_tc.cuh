@@ -13,6 +13,10 @@
 // The epilogue, not the tensor pipe, bounds this kernel; see scaled_pair() for how the
 // int->float step is done on the integer and FMA pipes.
 //
+// A second instantiation (kRepack) serves the consumer of the 16-row interleaved layouts: the
+// same contraction with the fold fma((float)S, d_w * d_x, acc) (the scales multiplied first,
+// an exact product of two fp16 values) and the result stored token-major, s[col*bs + row].
+//
 // Operands come from a planar ("prepared") layout written by the unpack kernels: int8
 // matrices [rows][K] and fp32 scale matrices, all fetched with tiled TMA loads (128-byte
 // swizzle for the int8 tiles).  Warp roles in a CTA of 18 warps:
@@ -90,6 +94,11 @@ __device__ __forceinline__ uint64_t mul_f32x2(uint64_t a, uint64_t b) {
   asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
   return r;
 }
+__device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
 __device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
   uint64_t r;
   asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
@@ -109,6 +118,12 @@ __device__ __forceinline__ uint64_t scaled_pair(uint32_t s_lo, uint32_t s_hi, ui
   return fma_f32x2(pack_f32x2(__uint_as_float(s_lo + kMagicBits), __uint_as_float(s_hi + kMagicBits)), dw2, c2);
 }
 
+// (float)S for two block sums, exactly: the biased bit patterns minus the bias (no rounding,
+// both operands and the result are integers below 2^24).
+__device__ __forceinline__ uint64_t float_pair(uint32_t s_lo, uint32_t s_hi, uint64_t neg_magic2) {
+  return add_f32x2(pack_f32x2(__uint_as_float(s_lo + kMagicBits), __uint_as_float(s_hi + kMagicBits)), neg_magic2);
+}
+
 struct PipeState {
   uint32_t stage = 0, phase = 0;
   __device__ __forceinline__ void advance(uint32_t nstages) {
@@ -121,7 +136,8 @@ struct PipeState {
 
 // kMulti: the result goes to several output copies (peers); stores are transposed through
 // shared memory into full 128-byte lines.  Otherwise each lane stores its own row directly.
-template <bool kMulti>
+// kRepack (single destination only): scales multiplied first, token-major output.
+template <bool kMulti, bool kRepack = false>
 __global__ void __launch_bounds__(kGemmThreads, 1)
     gemm_q4_0_q8_0_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                              const __grid_constant__ CUtensorMap map_dw, const __grid_constant__ CUtensorMap map_dx,
@@ -298,17 +314,25 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                   }
                   const uint64_t dw2 = pack_f32x2(dws[kk + h], dws[kk + h]);
                   const float cneg = __fmul_rn(-kMagic, dws[kk + h]);  // exact: 2-bit x 11-bit significands
-                  const uint64_t c2 = pack_f32x2(cneg, cneg);
+                  const uint64_t c2 = kRepack ? pack_f32x2(-kMagic, -kMagic) : pack_f32x2(cneg, cneg);
                   const ulonglong2 *dx2 = reinterpret_cast<const ulonglong2 *>(dx_base + (kk + h) * kGemmTileCols * 4);
 #pragma unroll
                   for (int c = 0; c < CPW / 32; ++c) {
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
                       const ulonglong2 d = dx2[8 * c + j];
-                      const uint64_t t0 = scaled_pair(v[c][4 * j], v[c][4 * j + 1], dw2, c2);
-                      const uint64_t t1 = scaled_pair(v[c][4 * j + 2], v[c][4 * j + 3], dw2, c2);
-                      acc[16 * c + 2 * j] = fma_f32x2(t0, d.x, acc[16 * c + 2 * j]);
-                      acc[16 * c + 2 * j + 1] = fma_f32x2(t1, d.y, acc[16 * c + 2 * j + 1]);
+                      if constexpr (kRepack) {
+                        // fma((float)S, d_w * d_x, acc): the scale product is exact in fp32
+                        const uint64_t f0 = float_pair(v[c][4 * j], v[c][4 * j + 1], c2);
+                        const uint64_t f1 = float_pair(v[c][4 * j + 2], v[c][4 * j + 3], c2);
+                        acc[16 * c + 2 * j] = fma_f32x2(f0, mul_f32x2(dw2, d.x), acc[16 * c + 2 * j]);
+                        acc[16 * c + 2 * j + 1] = fma_f32x2(f1, mul_f32x2(dw2, d.y), acc[16 * c + 2 * j + 1]);
+                      } else {
+                        const uint64_t t0 = scaled_pair(v[c][4 * j], v[c][4 * j + 1], dw2, c2);
+                        const uint64_t t1 = scaled_pair(v[c][4 * j + 2], v[c][4 * j + 3], dw2, c2);
+                        acc[16 * c + 2 * j] = fma_f32x2(t0, d.x, acc[16 * c + 2 * j]);
+                        acc[16 * c + 2 * j + 1] = fma_f32x2(t1, d.y, acc[16 * c + 2 * j + 1]);
+                      }
                     }
                   }
                 }
@@ -328,6 +352,22 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       // ---- store: this thread owns CPW consecutive outputs of one weight row, written to
       // every destination
       const uint32_t row = n0 + row_local;
+      if constexpr (kRepack) {
+        // token-major: for one column the 32 lanes of the warp write 32 consecutive floats
+        if (row < a.nr) {
+          float *dst = a.dst[0] + row;
+#pragma unroll
+          for (int j = 0; j < CPW / 2; ++j) {
+            float lo, hi;
+            unpack_f32x2(acc[j], lo, hi);
+            if (m0 + 2 * j < a.nc)
+              dst[static_cast<size_t>(m0 + 2 * j) * a.bs] = lo;
+            if (m0 + 2 * j + 1 < a.nc)
+              dst[static_cast<size_t>(m0 + 2 * j + 1) * a.bs] = hi;
+          }
+        }
+        continue;
+      }
       bool vec = (a.bs % 4 == 0) && (m0 + CPW <= a.nc);  // warp-uniform
       for (uint32_t d = 0; d < a.ndst; ++d)
         vec = vec && ((reinterpret_cast<uintptr_t>(a.dst[d]) & 15u) == 0);

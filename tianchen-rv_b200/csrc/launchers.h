@@ -22,6 +22,12 @@ int launch_rope_apply_f32(size_t n_dims, const float *x, float *y, const float *
                           size_t y_stride, cudaStream_t stream);
 int launch_pack_q4_0_to_q4_0x16(size_t nblocks, const uint8_t *src, uint8_t *dst, cudaStream_t stream);
 int launch_unpack_q4_0x16_to_q4_0(size_t nblocks, const uint8_t *src, uint8_t *dst, cudaStream_t stream);
+// consumers of the 16-row interleaved weight layouts (repack.cu)
+size_t repack_gemv_parts(size_t n);
+int launch_repack_gemv_q4_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t nc, unsigned flags,
+                                 cudaStream_t stream);
+int launch_repack_gemv_q8_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t nc, unsigned flags,
+                                 cudaStream_t stream);
 // sibling block formats (siblings.cu): format 1 = Q4_1 x Q8_1, 2 = Q5_0 x Q8_0, 3 = Q5_1 x Q8_1;
 // `sums` != null selects the integer stage (sumi[row][col][block]) instead of the fp32 rows.
 int sibling_block_bytes(int format, size_t *weight, size_t *activation);
@@ -56,6 +62,13 @@ int launch_gemm_static_scratch(size_t n, float *s, const uint8_t *vx, size_t bx,
                                size_t nr, size_t nc, size_t bs, cudaStream_t stream);
 int launch_gemm_prepared(size_t n, float *s, const uint8_t *weights_planar, const uint8_t *acts_planar, size_t nr,
                          size_t nc, size_t bs, cudaStream_t stream);
+// Consumer of the interleaved layouts (block_q4_0x16 weights, block_q8_0x4 activations):
+// planar weights from the x16 groups, then unpack of the activations + the tensor-core kernel
+// with the scales-first fold and token-major output s[token*bs + weight row].
+int launch_repack_gemm_prepare_weights_q4_0x16(size_t n, const uint8_t *vx, size_t wrows, uint8_t *prepared,
+                                               cudaStream_t stream);
+int launch_repack_gemm_prepared(size_t n, float *s, const uint8_t *weights_planar, const uint8_t *vy, size_t tokens,
+                                size_t wrows, size_t bs, uint8_t *acts_planar, cudaStream_t stream);
 // The same GEMM writing its result to `ndst` (1..8) output bases of equal layout, e.g. every
 // rank's copy of an N-sharded output (peer pointers).
 int launch_gemm_prepared_multi(size_t n, float *const *dst, size_t ndst, const uint8_t *weights_planar,
