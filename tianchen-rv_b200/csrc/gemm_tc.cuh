@@ -105,6 +105,11 @@ __device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c
   return r;
 }
 
+// 256-bit store of four packed fp32 pairs (address 32-byte aligned).
+__device__ __forceinline__ void st_global_v4_b64(float *p, uint64_t a, uint64_t b, uint64_t c, uint64_t d) {
+  asm volatile("st.global.v4.b64 [%0], {%1, %2, %3, %4};" ::"l"(p), "l"(a), "l"(b), "l"(c), "l"(d) : "memory");
+}
+
 // (float)S * d_w for two int32 block sums without an int->float conversion instruction (the
 // conversion unit, at 16 results per clock per SM, was what bounded this kernel): adding
 // 0x4B400000 to S as an INTEGER gives the bit pattern of the float 12582912 + S exactly
@@ -401,13 +406,20 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         }
       } else if (vec) {
         if (row < a.nr) {
-          float4 *dst = reinterpret_cast<float4 *>(a.dst[0] + static_cast<size_t>(row) * a.bs + m0);
+          float *dst = a.dst[0] + static_cast<size_t>(row) * a.bs + m0;
+          if ((a.bs % 8 == 0) && ((reinterpret_cast<uintptr_t>(a.dst[0]) & 31u) == 0)) {
+            // 32-byte stores: every lane writes whole sectors of its row
 #pragma unroll
-          for (int j = 0; j < CPW / 4; ++j) {
-            float4 o;
-            unpack_f32x2(acc[2 * j], o.x, o.y);
-            unpack_f32x2(acc[2 * j + 1], o.z, o.w);
-            dst[j] = o;
+            for (int j = 0; j < CPW / 8; ++j)
+              st_global_v4_b64(dst + 8 * j, acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < CPW / 4; ++j) {
+              float4 o;
+              unpack_f32x2(acc[2 * j], o.x, o.y);
+              unpack_f32x2(acc[2 * j + 1], o.z, o.w);
+              reinterpret_cast<float4 *>(dst)[j] = o;
+            }
           }
         }
       } else if (row < a.nr) {
