@@ -41,6 +41,21 @@ def test_repack_gemv_bit_exact_in_the_kernel_order(cuda, pkg, O, nc, k, q8w):
     pkg.check_device_errors()
 
 
+@pytest.mark.parametrize("q8w", [False, True], ids=["q4_0x16", "q8_0x16"])
+def test_repack_gemv_work_split_does_not_change_the_result(cuda, pkg, O, q8w):
+    # warps per row group, ring depth and copies in flight are scheduling choices only
+    nc, k = 256, 4096
+    wx, x = make_case(O, nc, k, q8w, 900)
+    want = O.repack_gemv(wx, x[0], nc, q8_weights=q8w, parts=pkg.repack_gemv_parts(k))
+    wd, xd = dev(cuda, wx), dev(cuda, x[0])
+    for coop in (1, 2, 4, 8):
+        for depth, window in ((2, 1), (4, 3), (6, 5)):
+            flags = (depth << 8) | (coop << 12) | (window << 16)
+            got = pkg.repack_gemv(wd, xd, nc, q8_weights=q8w, flags=flags).cpu().numpy()
+            assert np.array_equal(bits(got), bits(want)), (coop, depth, window)
+    pkg.check_device_errors()
+
+
 def test_repack_gemv_parts_rule(pkg):
     # a function of K alone: every range keeps at least two 8-block steps
     assert [pkg.repack_gemv_parts(k) for k in (32, 256, 512, 1024, 2048, 4096, 11008)] == [1, 1, 1, 2, 4, 8, 8]

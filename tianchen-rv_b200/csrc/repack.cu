@@ -1,28 +1,33 @@
 // Decode GEMV over the 16-row interleaved weight layouts, block_q4_0x16 (288 bytes) and
 // block_q8_0x16 (544 bytes): 16 fp16 scales, then the quant bytes of 16 weight rows side by
 // side (byte 32 + 16*i + r = position i of row r; for q4 a byte holds elements i and i+16 of
-// the row as nibbles already xor-ed with 0x88).  Group g of 16 rows occupies nb consecutive
-// blocks at vx + g*nb*block_bytes.  The activation is one plain block_q8_0 column.
+// the row as nibbles already xor-ed with 0x88, i.e. in 4-bit two's complement).  Group g of
+// 16 rows occupies nb consecutive blocks at vx + g*nb*block_bytes.  The activation is one
+// plain block_q8_0 column.
 //
 //   s[16*g + r] = sum over blocks l of fma((float)sumi[l][r], d_w[l][r] * d_a[l], .)
 //
 // with d_w * d_a the exact product of the two fp16 scales.  HBM-bound: every weight byte is
-// read once, by 1-D bulk copies into per-warp rings of shared-memory slots (one slot = one
-// step = 8 consecutive blocks of a group).
+// read once, by 1-D bulk copies into per-warp rings of shared-memory slots (one slot = one or
+// two steps; a step = 8 consecutive blocks of a group).
 //
 // In a step, lane = 4*b + rq works on block b (0..7) of the step and on the row quad
 // rq (rows 4rq..4rq+3): it reads the 16 (q4) or 32 (q8) words that hold its four rows'
 // bytes, turns every 4 words x 4 rows into 4 rows x 4 consecutive positions with byte
-// permutes, and takes the integer sums with dp4a -- no integer reduction across lanes.  Each
-// lane therefore carries four fp32 chains (its rows) over the blocks b, b+8, b+16, ... of
-// its range.
+// permutes, and takes the integer sums with dp4a -- no integer reduction across lanes.  The
+// q4 nibbles are used where they sit: (byte & 0xf0) and (byte << 4) read as int8 are 16 times
+// the element, so the dp4a total is 16 * sumi and one arithmetic shift ends the block.  Each
+// lane carries four fp32 chains (its rows) over the blocks b, b+8, b+16, ... of a range.
 //
-// Work split: the ceil(nb/8) steps of a row are cut into `parts` contiguous ranges (a
-// function of K alone), one warp per (group, range); a CTA of 16 warps handles 16/parts
-// groups per round and walks a contiguous span of rounds.  Summation order of one output:
-// inside a range the 8 chains (one per b) fold their blocks in ascending order from 0.0f and
-// are added by a butterfly, ((c0+c4) + (c2+c6)) + ((c1+c5) + (c3+c7)); the ranges are then
-// added in ascending order by the warp of range 0.
+// Summation order of one output (a function of K alone): the ceil(nb/8) steps of a row are
+// cut into `parts` contiguous ranges; inside a range the 8 chains (one per b) fold their
+// blocks in ascending order from 0.0f and are added by a butterfly,
+// ((c0+c4) + (c2+c6)) + ((c1+c5) + (c3+c7)); the range sums are then added in ascending order.
+//
+// Work split (does not affect the order): a CTA owns a contiguous span of groups; `coop`
+// warps (a divisor of `parts`) share a group, each folding parts/coop consecutive ranges, and
+// a CTA of 16 warps handles 16/coop groups per round.  Range sums meet in shared memory and
+// the first warp of the group adds them.
 #include "async_copy.cuh"
 #include "launchers.h"
 #include "tcrv_common.cuh"
@@ -35,9 +40,10 @@ constexpr int kRpWarps = 16;
 constexpr int kRpThreads = kRpWarps * 32;
 constexpr int kRpStepBlocks = 8;
 constexpr int kRpMaxDepth = 6;
-constexpr int kRpBarrierBytes = kRpWarps * kRpMaxDepth * 8;       // 768
-constexpr int kRpPartialBytes = 2 * kRpWarps * 16 * 4;            // 2048
-constexpr int kRpFixedBytes = kRpBarrierBytes + kRpPartialBytes;  // 2816
+constexpr int kRpMaxParts = 8;
+constexpr int kRpBarrierBytes = kRpWarps * kRpMaxDepth * 8;                 // 768
+constexpr int kRpPartialBytes = 2 * kRpWarps * kRpMaxParts * 16 * 4;        // [2][group of the round][range][16 rows]
+constexpr int kRpFixedBytes = kRpBarrierBytes + kRpPartialBytes;            // 17152
 constexpr size_t kRpSmemLimit = 227 * 1024;
 
 template <bool kQ8W>
@@ -45,7 +51,10 @@ struct X16 {
   static constexpr int kBlockBytes = kQ8W ? 544 : 288;
   static constexpr int kBlockWords = kBlockBytes / 4;
   static constexpr int kQuads = kQ8W ? 8 : 4;  // groups of four 16-byte position rows
-  static constexpr int kSlotBytes = kRpStepBlocks * kBlockBytes;
+  // steps per slot: one bulk copy brings about 4.5 KB (the copy engine's rate is per copy,
+  // so 2.3 KB copies left it, not HBM, as the bound)
+  static constexpr int kSlotSteps = kQ8W ? 1 : 2;
+  static constexpr int kSlotBytes = kSlotSteps * kRpStepBlocks * kBlockBytes;
 };
 
 struct RepackGemvArgs {
@@ -54,13 +63,13 @@ struct RepackGemvArgs {
   float *s;
   uint32_t nb;      // blocks per row
   uint32_t groups;  // nc / 16
-  uint32_t parts;   // 1, 2, 4 or 8
-  uint32_t rounds;  // ceil(groups / (16 / parts))
+  uint32_t parts;   // 1, 2, 4 or 8: ranges of the summation order
+  uint32_t coop;    // warps sharing a group, divides parts
   uint32_t depth;   // ring slots per warp
   uint32_t window;  // copies a warp keeps in flight, < depth
 };
 
-__host__ __device__ inline uint32_t rp_x_bytes(uint32_t nb) { return (nb * 40u + 15u) & ~15u; }
+__host__ __device__ inline uint32_t rp_x_bytes(uint32_t nb) { return (nb * 36u + 15u) & ~15u; }
 
 // in: w[k] = bytes of rows 0..3 at position k; out: r[j] = positions 0..3 of row j.
 __device__ __forceinline__ void transpose4x4(uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3, uint32_t (&r)[4]) {
@@ -72,6 +81,12 @@ __device__ __forceinline__ void transpose4x4(uint32_t w0, uint32_t w1, uint32_t 
   r[3] = __byte_perm(t2, t3, 0x7632);
 }
 
+// (float)v for |v| < 2^22 on the integer and FP32 pipes: 0x4B400000 + v is the bit pattern of
+// 12582912 + v, and subtracting 12582912 is exact.
+__device__ __forceinline__ float small_int_to_float(int v) {
+  return __fadd_rn(__int_as_float(v + 0x4B400000), -12582912.0f);
+}
+
 template <bool kQ8W>
 __global__ void __launch_bounds__(kRpThreads, 1) repack_gemv_kernel(const RepackGemvArgs a) {
   using F = X16<kQ8W>;
@@ -79,46 +94,58 @@ __global__ void __launch_bounds__(kRpThreads, 1) repack_gemv_kernel(const Repack
   uint64_t *full = reinterpret_cast<uint64_t *>(smem);
   float *partial = reinterpret_cast<float *>(smem + kRpBarrierBytes);
   const uint32_t nb = a.nb;
-  uint4 *xq = reinterpret_cast<uint4 *>(smem + kRpFixedBytes);       // [nb][2] activation quants
+  uint4 *xq = reinterpret_cast<uint4 *>(smem + kRpFixedBytes);             // [nb][2] activation quants
   float *xd = reinterpret_cast<float *>(smem + kRpFixedBytes + nb * 32u);  // [nb] activation scales
-  int *xs = reinterpret_cast<int *>(xd + nb);                               // [nb] 8 * sum(q)  (q4 only)
   uint8_t *slots = smem + kRpFixedBytes + rp_x_bytes(nb);
 
   const uint32_t warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t b = lane >> 2, rq = lane & 3;
-  const uint32_t parts = a.parts, depth = a.depth;
-  const uint32_t gpr = kRpWarps / parts;  // groups per round
-  const uint32_t wgroup = warp / parts, part = warp % parts;
+  const uint32_t parts = a.parts, coop = a.coop, depth = a.depth;
+  const uint32_t gpr = kRpWarps / coop;     // groups per round
+  const uint32_t rpw = parts / coop;        // ranges per warp
+  const uint32_t wgroup = warp / coop, wpart = warp % coop;
   const uint32_t steps = (nb + kRpStepBlocks - 1) / kRpStepBlocks;
-  const uint32_t s0 = part * steps / parts, ns = (part + 1) * steps / parts - s0;
-  // this CTA's rounds, and how many of them have a group for this warp
-  const uint32_t r0 = static_cast<uint32_t>(static_cast<uint64_t>(a.rounds) * blockIdx.x / gridDim.x);
-  const uint32_t r1 = static_cast<uint32_t>(static_cast<uint64_t>(a.rounds) * (blockIdx.x + 1) / gridDim.x);
-  const uint32_t vend = wgroup < a.groups ? (a.groups - wgroup + gpr - 1) / gpr : 0;
-  const uint32_t rend = r1 < vend ? r1 : vend;
-  const uint32_t total = rend > r0 ? (rend - r0) * ns : 0;  // slots this warp walks
+  // this warp's steps of a group: the ranges wpart*rpw .. wpart*rpw + rpw - 1, contiguous
+  const uint32_t s_begin = wpart * rpw * steps / parts, s_end = (wpart + 1) * rpw * steps / parts;
+  const uint32_t ns = s_end - s_begin;
+  // this CTA's groups, and the rounds in which this warp has one
+  const uint32_t g0 = static_cast<uint32_t>(static_cast<uint64_t>(a.groups) * blockIdx.x / gridDim.x);
+  const uint32_t g1 = static_cast<uint32_t>(static_cast<uint64_t>(a.groups) * (blockIdx.x + 1) / gridDim.x);
+  const uint32_t ng = g1 - g0;
+  const uint32_t nrounds = ng > wgroup ? (ng - wgroup + gpr - 1) / gpr : 0;
+  const uint32_t slots_per_round = (ns + F::kSlotSteps - 1) / F::kSlotSteps;
+  const uint32_t total = nrounds * slots_per_round;  // slots this warp walks
 
-  // Copy of this warp's t-th slot into ring position t % depth (one lane calls it).
-  auto issue = [&](uint32_t t) {
-    const uint32_t round = r0 + t / ns, step = s0 + t % ns;
-    const uint32_t g = round * gpr + wgroup;
-    const uint32_t first = step * kRpStepBlocks;
-    const uint32_t blocks = nb - first < kRpStepBlocks ? nb - first : kRpStepBlocks;
-    const uint32_t bar = warp * depth + t % depth;
+  // Producer side (lane 0): the next slot to request.
+  uint32_t iss_round = 0, iss_step = s_begin, iss_pos = 0, iss_left = total;
+  auto issue_next = [&]() {
+    const uint32_t g = g0 + iss_round * gpr + wgroup;
+    const uint32_t first = iss_step * kRpStepBlocks;
+    const uint32_t cnt = s_end - iss_step < F::kSlotSteps ? s_end - iss_step : F::kSlotSteps;  // steps in this slot
+    const uint32_t blocks = nb - first < cnt * kRpStepBlocks ? nb - first : cnt * kRpStepBlocks;
+    const uint32_t bar = warp * depth + iss_pos;
     mbar_arrive_expect_tx(&full[bar], blocks * F::kBlockBytes);
     bulk_copy_g2s(slots + static_cast<size_t>(bar) * F::kSlotBytes,
                   a.vx + (static_cast<size_t>(g) * nb + first) * F::kBlockBytes, blocks * F::kBlockBytes, &full[bar]);
+    iss_step += cnt;
+    if (iss_step == s_end) {
+      iss_step = s_begin;
+      ++iss_round;
+    }
+    if (++iss_pos == depth)
+      iss_pos = 0;
+    --iss_left;
   };
 
   if (lane == 0) {
     for (uint32_t i = 0; i < depth; ++i)
       mbar_init(&full[warp * depth + i], 1);
     mbar_fence_init();
-    for (uint32_t t = 0; t < min(a.window, total); ++t)
-      issue(t);
+    for (uint32_t t = 0; t < a.window && iss_left > 0; ++t)
+      issue_next();
   }
-  // the activation column in an aligned layout: 8 words of quants, the scale, 8 * sum(q)
+  // the activation column in an aligned layout: 8 words of quants and the scale per block
   const bool aligned2 = (reinterpret_cast<uintptr_t>(a.vy) & 1u) == 0;
   for (uint32_t ib = threadIdx.x; ib < nb; ib += kRpThreads) {
     const uint8_t *src = a.vy + static_cast<size_t>(ib) * kQ8Block;
@@ -138,108 +165,121 @@ __global__ void __launch_bounds__(kRpThreads, 1) repack_gemv_kernel(const Repack
     xq[2 * ib] = make_uint4(q[0], q[1], q[2], q[3]);
     xq[2 * ib + 1] = make_uint4(q[4], q[5], q[6], q[7]);
     xd[ib] = half_bits_to_float(d);
-    if constexpr (!kQ8W)
-      xs[ib] = 8 * sum_s8x32(q);
   }
   __syncthreads();
 
   float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-  uint32_t step_in_task = 0, round = r0;
+  uint32_t step = s_begin, round = 0, pos = 0, phase = 0;
+  uint32_t range = wpart * rpw, range_end = (range + 1) * steps / parts;
   bool dead = false;  // a wait of this warp expired: walk on without data (warp-uniform)
-  uint32_t dead_at = 0;
+  uint32_t dead_left = 0, dead_pos = 0, dead_phase = 0;
   for (uint32_t t = 0; t < total; ++t) {
-    const uint32_t bar = warp * depth + t % depth;
+    const uint32_t bar = warp * depth + pos;
     if (!dead) {
-      const bool ok = mbar_wait_bounded(&full[bar], (t / depth) & 1);
+      const bool ok = mbar_wait_bounded(&full[bar], phase);
       if (!__all_sync(0xffffffffu, ok)) {
         dead = true;  // keep walking so that the other warps of the group are not left at a barrier
-        dead_at = t;
+        dead_left = min(total - t, a.window);  // copies requested and not yet seen to land
+        dead_pos = pos;
+        dead_phase = phase;
         if (lane == 0)
           raise_device_error(kDevErrBarrierTimeout);
       }
     }
     __syncwarp();
-    if (!dead && lane == 0 && t + a.window < total) {
-      // ring position (t + window) % depth was folded at least one iteration ago
+    if (!dead && lane == 0 && iss_left > 0) {
+      // the ring position this request overwrites was folded at least one iteration ago
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      issue(t + a.window);
+      issue_next();
     }
-    const uint32_t blk = (s0 + step_in_task) * kRpStepBlocks + b;
-    if (!dead && blk < nb) {
-      const uint32_t *wb =
-          reinterpret_cast<const uint32_t *>(slots + static_cast<size_t>(bar) * F::kSlotBytes) + b * F::kBlockWords;
-      const uint32_t sc0 = wb[2 * rq], sc1 = wb[2 * rq + 1];
-      const float dw[4] = {half_bits_to_float(sc0 & 0xffffu), half_bits_to_float(sc0 >> 16),
-                           half_bits_to_float(sc1 & 0xffffu), half_bits_to_float(sc1 >> 16)};
-      const uint4 xa = xq[2 * blk], xb = xq[2 * blk + 1];
-      const uint32_t xw[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
-      const float da = xd[blk];
-      uint32_t e[4][F::kQuads];  // [row][4 consecutive positions]
+    const uint32_t cnt = s_end - step < F::kSlotSteps ? s_end - step : F::kSlotSteps;  // steps in this slot
+    for (uint32_t sub = 0; sub < cnt; ++sub) {
+      const uint32_t blk = step * kRpStepBlocks + b;
+      if (!dead && blk < nb) {
+        const uint32_t *wb = reinterpret_cast<const uint32_t *>(slots + static_cast<size_t>(bar) * F::kSlotBytes) +
+                             (sub * kRpStepBlocks + b) * F::kBlockWords;
+        const uint32_t sc0 = wb[2 * rq], sc1 = wb[2 * rq + 1];
+        const uint4 xa = xq[2 * blk], xb = xq[2 * blk + 1];
+        const uint32_t xw[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+        const float da = xd[blk];
+        int sumi[4] = {0, 0, 0, 0};
 #pragma unroll
-      for (int qd = 0; qd < F::kQuads; ++qd) {
-        uint32_t r[4];
-        transpose4x4(wb[8 + 16 * qd + rq], wb[8 + 16 * qd + 4 + rq], wb[8 + 16 * qd + 8 + rq],
-                     wb[8 + 16 * qd + 12 + rq], r);
+        for (int qd = 0; qd < F::kQuads; ++qd) {
+          uint32_t r[4];
+          transpose4x4(wb[8 + 16 * qd + rq], wb[8 + 16 * qd + 4 + rq], wb[8 + 16 * qd + 8 + rq],
+                       wb[8 + 16 * qd + 12 + rq], r);
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
-          e[j][qd] = kQ8W ? r[j] : (r[j] ^ 0x88888888u);  // back to offset-binary nibbles
+          for (int j = 0; j < 4; ++j) {
+            if constexpr (kQ8W) {
+              sumi[j] = dp4a_s8(r[j], xw[qd], sumi[j]);
+            } else {
+              // int8 views of the nibbles: 16 * (elements 4qd..) and 16 * (elements 16+4qd..)
+              sumi[j] = dp4a_s8((r[j] << 4) & 0xf0f0f0f0u, xw[qd], sumi[j]);
+              sumi[j] = dp4a_s8(r[j] & 0xf0f0f0f0u, xw[4 + qd], sumi[j]);
+            }
+          }
+        }
+        const float dw[4] = {half_bits_to_float(sc0 & 0xffffu), half_bits_to_float(sc0 >> 16),
+                             half_bits_to_float(sc1 & 0xffffu), half_bits_to_float(sc1 >> 16)};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int si = kQ8W ? sumi[j] : (sumi[j] >> 4);  // exact: the total is a multiple of 16
+          acc[j] = __fmaf_rn(small_int_to_float(si), __fmul_rn(dw[j], da), acc[j]);
+        }
       }
-      int x8 = 0;
-      if constexpr (!kQ8W)
-        x8 = xs[blk];
+      ++step;
+      if (step == range_end) {
+        // a range is folded: add its 8 chains and hand the 16 sums over
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        int sumi;
-        if constexpr (kQ8W)
-          sumi = q8_0_q8_0_sumi(e[j], xw);
-        else
-          sumi = q4_0_q8_0_sumi(e[j], xw, x8);
-        acc[j] = fold_q8(acc[j], sumi, dw[j], da);
-      }
-    }
-    if (++step_in_task == ns) {
-      // the range of this (group, part) is folded: add the 8 chains, then the parts
-#pragma unroll
-      for (int off = 16; off >= 4; off >>= 1) {
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-          acc[j] = __fadd_rn(acc[j], __shfl_xor_sync(0xffffffffu, acc[j], off));
-      }
-      const uint32_t g = round * gpr + wgroup;
-      if (parts == 1) {
-        if (b == 0 && !dead) {
+        for (int off = 16; off >= 4; off >>= 1) {
 #pragma unroll
           for (int j = 0; j < 4; ++j)
-            a.s[static_cast<size_t>(g) * 16 + 4 * rq + j] = acc[j];
+            acc[j] = __fadd_rn(acc[j], __shfl_xor_sync(0xffffffffu, acc[j], off));
         }
-      } else {
-        float *mine = partial + ((round & 1u) * kRpWarps + warp) * 16;
+        float *slot = partial + (((round & 1u) * kRpWarps + wgroup) * kRpMaxParts + range) * 16;
         if (b == 0) {
 #pragma unroll
           for (int j = 0; j < 4; ++j)
-            mine[4 * rq + j] = acc[j];
+            slot[4 * rq + j] = acc[j];
         }
-        // the `parts` warps of this group meet (all of them walk the same rounds)
-        asm volatile("bar.sync %0, %1;" ::"r"(1u + wgroup), "r"(parts * 32u) : "memory");
-        if (part == 0 && lane < 16 && !dead) {
-          float tot = mine[lane];
-          for (uint32_t j = 1; j < parts; ++j)
-            tot = __fadd_rn(tot, mine[j * 16 + lane]);
-          a.s[static_cast<size_t>(g) * 16 + lane] = tot;
-        }
-      }
 #pragma unroll
-      for (int j = 0; j < 4; ++j)
-        acc[j] = 0.0f;
-      step_in_task = 0;
-      ++round;
+        for (int j = 0; j < 4; ++j)
+          acc[j] = 0.0f;
+        ++range;
+        range_end = (range + 1) * steps / parts;
+      }
+      if (step == s_end) {
+        // this warp's share of the group is done: the group's warps meet, the first one adds
+        // the range sums in ascending order
+        if (coop > 1)
+          asm volatile("bar.sync %0, %1;" ::"r"(1u + wgroup), "r"(coop * 32u) : "memory");
+        else
+          __syncwarp();
+        if (wpart == 0 && lane < 16 && !dead) {
+          const float *sums = partial + ((round & 1u) * kRpWarps + wgroup) * kRpMaxParts * 16;
+          float tot = sums[lane];
+          for (uint32_t j = 1; j < parts; ++j)
+            tot = __fadd_rn(tot, sums[j * 16 + lane]);
+          a.s[static_cast<size_t>(g0 + round * gpr + wgroup) * 16 + lane] = tot;
+        }
+        step = s_begin;
+        range = wpart * rpw;
+        range_end = (range + 1) * steps / parts;
+        ++round;
+      }
+    }  // steps of the slot
+    if (++pos == depth) {
+      pos = 0;
+      phase ^= 1;
     }
   }
   if (dead && lane == 0) {
     // copies of this warp that may still be in flight must land before the CTA's memory goes away
-    const uint32_t issued = min(total, dead_at + a.window);
-    for (uint32_t u = dead_at; u < issued; ++u)
-      (void)mbar_wait_bounded(&full[warp * depth + u % depth], (u / depth) & 1);
+    for (uint32_t u = 0; u < dead_left; ++u) {
+      const uint32_t p = dead_pos + u;
+      (void)mbar_wait_bounded(&full[warp * depth + (p >= depth ? p - depth : p)],
+                              p >= depth ? dead_phase ^ 1u : dead_phase);
+    }
   }
 }
 
@@ -257,8 +297,18 @@ int launch_repack_gemv_impl(size_t n, float *s, const uint8_t *vx, const uint8_t
   args.nb = static_cast<uint32_t>(nb);
   args.groups = static_cast<uint32_t>(groups);
   args.parts = static_cast<uint32_t>(repack_gemv_parts(n));
-  const uint32_t gpr = kRpWarps / args.parts;
-  args.rounds = static_cast<uint32_t>((groups + gpr - 1) / gpr);
+  const uint32_t sms = static_cast<uint32_t>(sm_count());
+  const uint32_t grid = args.groups < sms ? args.groups : sms;
+  // warps per group: as many as keep a CTA's groups within one or few rounds of 16 warps
+  const uint32_t groups_per_cta = (args.groups + grid - 1) / grid;
+  uint32_t coop = args.parts;
+  while (coop > 1 && groups_per_cta * coop > kRpWarps)
+    coop /= 2;
+  if (const unsigned forced = (flags >> 12) & 0xfu)
+    coop = forced > args.parts ? args.parts : forced;
+  if (coop == 0 || args.parts % coop != 0)
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  args.coop = coop;
   const size_t fixed = kRpFixedBytes + rp_x_bytes(args.nb);
   if (fixed + 2 * static_cast<size_t>(kRpWarps) * F::kSlotBytes > kRpSmemLimit)
     return TCRV_CUDA_ERR_UNSUPPORTED;  // K beyond ~100k elements: the activation column no longer fits
@@ -267,7 +317,7 @@ int launch_repack_gemv_impl(size_t n, float *s, const uint8_t *vx, const uint8_t
   if (const unsigned forced = (flags >> 8) & 0xfu)
     depth = forced < 2 ? 2 : (forced > depth ? depth : forced);
   args.depth = static_cast<uint32_t>(depth);
-  uint32_t window = (4608u + F::kSlotBytes - 1) / F::kSlotBytes;  // about 4.6 KB in flight per warp
+  uint32_t window = 1;  // one copy (about 4.5 KB) in flight per warp
   if (const unsigned forced = (flags >> 16) & 0xfu)
     window = forced;
   args.window = window < args.depth ? window : args.depth - 1;
@@ -281,8 +331,6 @@ int launch_repack_gemv_impl(size_t n, float *s, const uint8_t *vx, const uint8_t
                                        static_cast<int>(kRpSmemLimit)));
     configured[dev][kQ8W ? 1 : 0] = true;
   }
-  const uint32_t sms = static_cast<uint32_t>(sm_count());
-  const uint32_t grid = args.rounds < sms ? args.rounds : sms;
   repack_gemv_kernel<kQ8W><<<grid, kRpThreads, smem, stream>>>(args);
   TCRV_CUDA_TRY(cudaGetLastError());
   return TCRV_CUDA_OK;
