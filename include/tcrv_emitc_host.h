@@ -42,6 +42,12 @@ int tcrv_cuda_host_pack_q4_0_to_q4_0x16(size_t nblocks, const uint8_t *src, uint
 int tcrv_cuda_host_vec_dot_q4_1_q8_1(size_t n, float *s, const uint8_t *vx, const uint8_t *vy);
 int tcrv_cuda_host_vec_dot_q5_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy);
 int tcrv_cuda_host_vec_dot_q5_1_q8_1(size_t n, float *s, const uint8_t *vx, const uint8_t *vy);
+/* consumers of the 16-row interleaved layouts (block_q4_0x16 / block_q8_0x16 weights; the GEMM
+ * takes block_q8_0x4 activations and writes s[token*bs + weight row]) */
+int tcrv_cuda_host_repack_gemv_q4_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t nc);
+int tcrv_cuda_host_repack_gemv_q8_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t nc);
+int tcrv_cuda_host_repack_gemm_q4_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t nr, size_t nc,
+                                         size_t bs);
 /* nc <= 8 runs the decode GEMV, larger nc the tensor-core GEMM. */
 int tcrv_cuda_host_gemm_q4_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by, size_t nr,
                                   size_t nc, size_t bx, size_t bs);
@@ -75,6 +81,16 @@ double tcrv_emitc_ggml_vec_soft_max_f32_kernel_ggml_vec_soft_max_f32(size_t n, f
 /* test/Conversion/RVV/rvv-to-emitc-ggml-rope-norm-f32.mlir:58 */
 void tcrv_emitc_ggml_rope_norm_f32_kernel_ggml_rope_norm_f32(size_t n_dims, const float *x, float *y, float theta_base,
                                                              float theta_scale);
+/* test/Conversion/RVV/rvv-to-emitc-repack-gemv-q4-0-q8-0.mlir:49 */
+void tcrv_emitc_ggml_repack_gemv_q4_0_q8_0_kernel_ggml_repack_gemv_q4_0_q8_0(size_t n, float *s, const uint8_t *vx,
+                                                                             const uint8_t *vy, size_t nc);
+/* test/Conversion/RVV/rvv-to-emitc-repack-gemv-q8-0-q8-0.mlir:28-33 (kernel and variant symbols) */
+void tcrv_emitc_ggml_repack_gemv_q8_0_q8_0_kernel_ggml_repack_gemv_q8_0_q8_0(size_t n, float *s, const uint8_t *vx,
+                                                                             const uint8_t *vy, size_t nc);
+/* test/Conversion/RVV/rvv-to-emitc-repack-gemm-q4-0-q8-0.mlir:21-28 */
+void tcrv_emitc_ggml_repack_gemm_q4_0_q8_0_kernel_ggml_repack_gemm_q4_0_q8_0(size_t n, float *s, const uint8_t *vx,
+                                                                             const uint8_t *vy, size_t nr, size_t nc,
+                                                                             size_t bs);
 /* test/Conversion/RVV/rvv-to-emitc-pack-q4-0-to-q4-0x16.mlir:35 */
 void tcrv_emitc_ggml_pack_q4_0_to_q4_0x16_kernel_ggml_pack_q4_0_to_q4_0x16(size_t nblocks, const uint8_t *src,
                                                                            uint8_t *dst);

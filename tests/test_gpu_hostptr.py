@@ -89,3 +89,45 @@ def test_host_prefill_and_q8_paths(cuda, pkg, O):
     assert L.tcrv_cuda_host_gemm_q8_0_q8_0(1024, big.ctypes.data, w8.ctypes.data, xh.ctypes.data, xh.strides[0], 40, 20,
                                            w8.strides[0], 20) == -2
     L.tcrv_cuda_host_release()
+
+
+@pytest.mark.parametrize("registered", [False, True])
+def test_host_repacked_consumers(cuda, pkg, O, registered):
+    # the reference-named entry points over host buffers: x16 GEMV (q4 and q8 weights) and the
+    # x16 / x4 GEMM, with weights uploaded per call or kept resident
+    L = pkg.lib()
+    nc, k, nr = 160, 1024, 8
+    w4 = O.quantize_q4_0(O.fill_normal(nc * k, 4500, 0, 0.02).reshape(nc, k))
+    w8 = O.quantize_q8_0(O.fill_normal(nc * k, 4501, 0, 0.02).reshape(nc, k))
+    xs = O.quantize_q8_0(O.fill_normal(nr * k, 4502).reshape(nr, k))
+    wx4, wx8, xx4 = O.rows_to_q4_0x16(w4), O.rows_to_q8_0x16(w8), O.rows_to_q8_0x4(xs)
+    parts = pkg.repack_gemv_parts(k)
+    held = [wx4, wx8] if registered else []
+    for h in held:
+        assert L.tcrv_cuda_host_register_weights(h.ctypes.data, h.nbytes) == 0
+    try:
+        for rep in range(2):  # the second GEMM call reuses the planar copy of resident weights
+            x = np.ascontiguousarray(xs[rep])
+            s = np.full(nc, -1.0, dtype=np.float32)
+            assert L.tcrv_cuda_host_repack_gemv_q4_0_q8_0(k, s.ctypes.data, wx4.ctypes.data, x.ctypes.data, nc) == 0
+            assert np.array_equal(s.view(np.uint32), O.repack_gemv(wx4, x, nc, parts=parts).view(np.uint32))
+            s8 = np.full(nc, -1.0, dtype=np.float32)
+            L.tcrv_emitc_ggml_repack_gemv_q8_0_q8_0_kernel_ggml_repack_gemv_q8_0_q8_0.restype = None
+            L.tcrv_emitc_ggml_repack_gemv_q8_0_q8_0_kernel_ggml_repack_gemv_q8_0_q8_0.argtypes = [
+                ctypes.c_size_t, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t]
+            L.tcrv_emitc_ggml_repack_gemv_q8_0_q8_0_kernel_ggml_repack_gemv_q8_0_q8_0(
+                k, s8.ctypes.data, wx8.ctypes.data, x.ctypes.data, nc)
+            assert np.array_equal(s8.view(np.uint32),
+                                  O.repack_gemv(wx8, x, nc, q8_weights=True, parts=parts).view(np.uint32))
+            out = np.full((nr, nc + 4), -1.0, dtype=np.float32)
+            assert L.tcrv_cuda_host_repack_gemm_q4_0_q8_0(k, out.ctypes.data, wx4.ctypes.data, xx4.ctypes.data, nr, nc,
+                                                          nc + 4) == 0
+            assert np.array_equal(out[:, :nc].view(np.uint32), O.repack_gemm(wx4, xx4, k, nr, nc).view(np.uint32))
+            assert np.all(out[:, nc:] == -1.0)
+        assert L.tcrv_cuda_host_repack_gemv_q4_0_q8_0(k, s.ctypes.data, wx4.ctypes.data, x.ctypes.data, 15) == -1
+        assert L.tcrv_cuda_host_repack_gemm_q4_0_q8_0(k, out.ctypes.data, wx4.ctypes.data, xx4.ctypes.data, 6, nc,
+                                                      nc) == -1
+    finally:
+        for h in held:
+            assert L.tcrv_cuda_host_unregister_weights(h.ctypes.data) == 0
+    pkg.check_device_errors()

@@ -63,6 +63,15 @@ PROTOTYPES = {
                                     "size_t n_dims, const float *x, float *y, float theta_base, float theta_scale);",
     "cuda-pack-q4-0-to-q4-0x16.mlir": "void tcrv_emitc_ggml_pack_q4_0_to_q4_0x16_kernel_ggml_pack_q4_0_to_q4_0x16("
                                       "size_t nblocks, const uint8_t *src, uint8_t *dst);",
+    "cuda-repack-gemv-q4-0-q8-0.mlir":
+        "void tcrv_emitc_ggml_repack_gemv_q4_0_q8_0_kernel_ggml_repack_gemv_q4_0_q8_0("
+        "size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t nc);",
+    "cuda-repack-gemv-q8-0-q8-0.mlir":
+        "void tcrv_emitc_ggml_repack_gemv_q8_0_q8_0_kernel_ggml_repack_gemv_q8_0_q8_0("
+        "size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t nc);",
+    "cuda-repack-gemm-q4-0-q8-0.mlir":
+        "void tcrv_emitc_ggml_repack_gemm_q4_0_q8_0_kernel_ggml_repack_gemm_q4_0_q8_0("
+        "size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t nr, size_t nc, size_t bs);",
     "cuda-q4-1-q8-1-block-dot.mlir": "void tcrv_emitc_ggml_vec_dot_q4_1_q8_1_kernel_ggml_vec_dot_q4_1_q8_1("
         "size_t n, float *s, const uint8_t *vx, const uint8_t *vy);",
     "cuda-q5-0-q8-0-block-dot.mlir": "void tcrv_emitc_ggml_vec_dot_q5_0_q8_0_kernel_ggml_vec_dot_q5_0_q8_0("

@@ -10,6 +10,7 @@
 // prepared planar form).  Unregistered weights are uploaded on every call.
 #include <stdio.h>
 #include <stdlib.h>
+#include <string.h>
 
 #include <chrono>
 #include <map>
@@ -643,6 +644,142 @@ void tcrv_emitc_ggml_vec_dot_q5_1_q8_1_kernel_ggml_vec_dot_q5_1_q8_1(size_t n, f
 void tcrv_emitc_ggml_pack_q4_0_to_q4_0x16_kernel_ggml_pack_q4_0_to_q4_0x16(size_t nblocks, const uint8_t *src,
                                                                            uint8_t *dst) {
   must(tcrv_cuda_host_pack_q4_0_to_q4_0x16(nblocks, src, dst), __func__);
+}
+
+// Consumers of the interleaved layouts over host buffers.  Weights registered with
+// tcrv_cuda_host_register_weights stay on the device; otherwise they are uploaded per call.
+namespace {
+constexpr size_t kInterleavedSource = static_cast<size_t>(-1);  // in place of a row stride: x16 groups
+
+int host_repack_gemv(bool q8w, size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t nc) {
+  if (n % kQK != 0 || nc % 16 != 0)
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  if (nc == 0)
+    return TCRV_CUDA_OK;
+  const size_t nb = n / kQK, wbytes = nc / 16 * nb * (q8w ? 544 : 288), xbytes = nb * kQ8Block;
+  if (!s || (nb != 0 && (!vx || !vy)))
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  HostContext &c = ctx();
+  std::lock_guard<std::mutex> lock(c.mu);
+  int st = ensure_stream(c);
+  if (st != TCRV_CUDA_OK)
+    return st;
+  auto it = c.weights.find(vx);
+  ResidentWeights *res = it == c.weights.end() ? nullptr : &it->second;
+  if (res && res->bytes < wbytes)
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  st = arena_reserve(c, (res ? 0 : up256(wbytes)) + up256(xbytes) + up256(nc * sizeof(float)) + 256);
+  if (st != TCRV_CUDA_OK)
+    return st;
+  const uint8_t *dw = res ? res->dev : nullptr;
+  if (!res) {
+    uint8_t *up = arena_take(c, wbytes);
+    if (wbytes != 0)
+      TCRV_CUDA_TRY(cudaMemcpyAsync(up, vx, wbytes, cudaMemcpyHostToDevice, c.stream));
+    dw = up;
+  }
+  uint8_t *dx = arena_take(c, xbytes);
+  float *ds = reinterpret_cast<float *>(arena_take(c, nc * sizeof(float)));
+  if (xbytes != 0)
+    TCRV_CUDA_TRY(cudaMemcpyAsync(dx, vy, xbytes, cudaMemcpyHostToDevice, c.stream));
+  if (nb == 0)
+    TCRV_CUDA_TRY(cudaMemsetAsync(ds, 0, nc * sizeof(float), c.stream));
+  else
+    st = q8w ? launch_repack_gemv_q8_0_q8_0(n, ds, dw, dx, nc, 0, c.stream)
+             : launch_repack_gemv_q4_0_q8_0(n, ds, dw, dx, nc, 0, c.stream);
+  if (st != TCRV_CUDA_OK)
+    return st;
+  TCRV_CUDA_TRY(cudaMemcpyAsync(s, ds, nc * sizeof(float), cudaMemcpyDeviceToHost, c.stream));
+  return finish(c);
+}
+}  // namespace
+
+int tcrv_cuda_host_repack_gemv_q4_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t nc) {
+  return host_repack_gemv(false, n, s, vx, vy, nc);
+}
+int tcrv_cuda_host_repack_gemv_q8_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t nc) {
+  return host_repack_gemv(true, n, s, vx, vy, nc);
+}
+
+int tcrv_cuda_host_repack_gemm_q4_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t nr, size_t nc,
+                                         size_t bs) {
+  if (n % kQK != 0 || nr % 4 != 0 || nc % 16 != 0 || (nr > 1 && bs < nc))
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  if (nr == 0 || nc == 0)
+    return TCRV_CUDA_OK;
+  const size_t nb = n / kQK, wbytes = nc / 16 * nb * 288, xbytes = nr / 4 * nb * 136;
+  if (!s || (nb != 0 && (!vx || !vy)))
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  if (nb == 0) {
+    for (size_t r = 0; r < nr; ++r)
+      memset(s + r * bs, 0, nc * sizeof(float));
+    return TCRV_CUDA_OK;
+  }
+  HostContext &c = ctx();
+  std::lock_guard<std::mutex> lock(c.mu);
+  int st = ensure_stream(c);
+  if (st != TCRV_CUDA_OK)
+    return st;
+  auto it = c.weights.find(vx);
+  ResidentWeights *res = it == c.weights.end() ? nullptr : &it->second;
+  if (res && res->bytes < wbytes)
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  const size_t pbytes = gemm_weights_bytes(n, nc), abytes = gemm_acts_bytes(n, nr), obytes = nr * nc * sizeof(float);
+  // resident weights keep their planar form between calls (built on first use)
+  const bool cached = res && res->prepared && res->prepared_n == n && res->prepared_nr == nc && res->prepared_bx == kInterleavedSource;
+  st = arena_reserve(c, (res ? 0 : up256(wbytes) + up256(pbytes)) + up256(xbytes) + up256(abytes) + up256(obytes) + 256);
+  if (st != TCRV_CUDA_OK)
+    return st;
+  const uint8_t *planar = nullptr;
+  if (cached) {
+    planar = res->prepared;
+  } else if (res) {
+    if (res->prepared) {
+      TCRV_CUDA_TRY(cudaStreamSynchronize(c.stream));
+      TCRV_CUDA_TRY(cudaFree(res->prepared));
+      res->prepared = nullptr;
+    }
+    TCRV_CUDA_TRY(cudaMalloc(reinterpret_cast<void **>(&res->prepared), pbytes));
+    st = launch_repack_gemm_prepare_weights_q4_0x16(n, res->dev, nc, res->prepared, c.stream);
+    if (st != TCRV_CUDA_OK)
+      return st;
+    res->prepared_n = n;
+    res->prepared_nr = nc;
+    res->prepared_bx = kInterleavedSource;
+    planar = res->prepared;
+  } else {
+    uint8_t *up = arena_take(c, wbytes);
+    uint8_t *pl = arena_take(c, pbytes);
+    TCRV_CUDA_TRY(cudaMemcpyAsync(up, vx, wbytes, cudaMemcpyHostToDevice, c.stream));
+    st = launch_repack_gemm_prepare_weights_q4_0x16(n, up, nc, pl, c.stream);
+    if (st != TCRV_CUDA_OK)
+      return st;
+    planar = pl;
+  }
+  uint8_t *dx = arena_take(c, xbytes);
+  uint8_t *acts = arena_take(c, abytes);
+  float *ds = reinterpret_cast<float *>(arena_take(c, obytes));
+  TCRV_CUDA_TRY(cudaMemcpyAsync(dx, vy, xbytes, cudaMemcpyHostToDevice, c.stream));
+  st = launch_repack_gemm_prepared(n, ds, planar, dx, nr, nc, nc, acts, c.stream);
+  if (st != TCRV_CUDA_OK)
+    return st;
+  TCRV_CUDA_TRY(cudaMemcpy2DAsync(s, bs * sizeof(float), ds, nc * sizeof(float), nc * sizeof(float), nr,
+                                  cudaMemcpyDeviceToHost, c.stream));
+  return finish(c);
+}
+
+void tcrv_emitc_ggml_repack_gemv_q4_0_q8_0_kernel_ggml_repack_gemv_q4_0_q8_0(size_t n, float *s, const uint8_t *vx,
+                                                                             const uint8_t *vy, size_t nc) {
+  must(host_repack_gemv(false, n, s, vx, vy, nc), __func__);
+}
+void tcrv_emitc_ggml_repack_gemv_q8_0_q8_0_kernel_ggml_repack_gemv_q8_0_q8_0(size_t n, float *s, const uint8_t *vx,
+                                                                             const uint8_t *vy, size_t nc) {
+  must(host_repack_gemv(true, n, s, vx, vy, nc), __func__);
+}
+void tcrv_emitc_ggml_repack_gemm_q4_0_q8_0_kernel_ggml_repack_gemm_q4_0_q8_0(size_t n, float *s, const uint8_t *vx,
+                                                                             const uint8_t *vy, size_t nr, size_t nc,
+                                                                             size_t bs) {
+  must(tcrv_cuda_host_repack_gemm_q4_0_q8_0(n, s, vx, vy, nr, nc, bs), __func__);
 }
 
 int tcrv_cuda_host_rope_norm_f32(size_t n_dims, const float *x, float *y, float theta_base, float theta_scale) {

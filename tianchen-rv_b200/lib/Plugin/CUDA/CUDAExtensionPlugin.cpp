@@ -127,6 +127,50 @@ std::vector<RouteEntry> buildTable() {
                "pack_q4_0_to_q4_0x16", "cuda-ggml-pack-q4_0-to-q4_0x16-callable-c-abi.v1",
                "tcrv_cuda_pack_q4_0_to_q4_0x16", "tcrv_cuda_host_pack_q4_0_to_q4_0x16", "streaming-byte-permutation",
                "hbm", ""});
+  // consumers of the interleaved layouts (lib/Conversion/RVV/RVVToEmitCBlockQuantLinear.cpp:2122, 2853, 3930)
+  {
+    const std::vector<std::string> gemvRoles = {"lhs-input-buffer", "rhs-input-buffer", "output-buffer",
+                                                "runtime-element-count", "destination-byte-stride"};
+    const std::vector<std::pair<std::string, std::string>> gemvSig = {
+        {"runtime-element-count", "size_t"}, {"output-buffer", "float *"}, {"lhs-input-buffer", "const uint8_t *"},
+        {"rhs-input-buffer", "const uint8_t *"}, {"destination-byte-stride", "size_t"}};
+    t.push_back({"tcrv_rvv.repack_gemv_q4_0_q8_0",
+                 withKind("ggml_repack_gemv_q4_0_q8_0",
+                          {{"scale_model", false, "dual-fp16-per-block-d_x.d_y", 0}, {"qk", true, "", 32},
+                           {"weight_block_stride", true, "", 288}, {"activation_block_stride", true, "", 34},
+                           {"weight_quant_byte_offset", true, "", 32}, {"activation_quant_byte_offset", true, "", 2},
+                           {"weight_interleave", true, "", 16}}),
+                 "", {"tcrv_rvv.repack_gemv_q4_0_q8_0"}, gemvRoles, gemvSig, "repack_gemv_q4_0_q8_0",
+                 "cuda-ggml-repack-gemv-q4_0-q8_0-callable-c-abi.v1", "tcrv_cuda_repack_gemv_q4_0_q8_0",
+                 "tcrv_cuda_host_repack_gemv_q4_0_q8_0", "decode-gemv-x16-bulk-copy", "hbm",
+                 "fma((float)sumi, d_w*d_a, .); 8 interleaved chains per range, ranges ascending"});
+    t.push_back({"tcrv_rvv.repack_gemv_q8_0_q8_0",
+                 withKind("ggml_repack_gemv_q8_0_q8_0",
+                          {{"scale_model", false, "dual-fp16-per-block-d_x.d_y", 0}, {"qk", true, "", 32},
+                           {"weight_block_stride", true, "", 544}, {"activation_block_stride", true, "", 34},
+                           {"weight_quant_byte_offset", true, "", 32}, {"activation_quant_byte_offset", true, "", 2},
+                           {"weight_interleave", true, "", 16}}),
+                 "", {"tcrv_rvv.repack_gemv_q8_0_q8_0"}, gemvRoles, gemvSig, "repack_gemv_q8_0_q8_0",
+                 "cuda-ggml-repack-gemv-q8_0-q8_0-callable-c-abi.v1", "tcrv_cuda_repack_gemv_q8_0_q8_0",
+                 "tcrv_cuda_host_repack_gemv_q8_0_q8_0", "decode-gemv-x16-bulk-copy", "hbm",
+                 "fma((float)sumi, d_w*d_a, .); 8 interleaved chains per range, ranges ascending"});
+    t.push_back({"tcrv_rvv.repack_gemm_q4_0_q8_0",
+                 withKind("ggml_repack_gemm_q4_0_q8_0",
+                          {{"scale_model", false, "dual-fp16-per-block-d_x.d_y", 0}, {"qk", true, "", 32},
+                           {"weight_block_stride", true, "", 288}, {"activation_block_stride", true, "", 136},
+                           {"weight_quant_byte_offset", true, "", 32}, {"activation_quant_byte_offset", true, "", 8},
+                           {"weight_interleave", true, "", 16}, {"activation_interleave", true, "", 4}}),
+                 "", {"tcrv_rvv.repack_gemm_q4_0_q8_0"},
+                 {"lhs-input-buffer", "rhs-input-buffer", "output-buffer", "runtime-element-count",
+                  "source-byte-stride", "destination-byte-stride", "output-stride"},
+                 {{"runtime-element-count", "size_t"}, {"output-buffer", "float *"},
+                  {"lhs-input-buffer", "const uint8_t *"}, {"rhs-input-buffer", "const uint8_t *"},
+                  {"source-byte-stride", "size_t"}, {"destination-byte-stride", "size_t"}, {"output-stride", "size_t"}},
+                 "repack_gemm_q4_0_q8_0", "cuda-ggml-repack-gemm-q4_0-q8_0-callable-c-abi.v1",
+                 "tcrv_cuda_repack_gemm_q4_0_q8_0", "tcrv_cuda_host_repack_gemm_q4_0_q8_0",
+                 "prefill-gemm-tcgen05-i8-token-major", "tensor",
+                 "fma((float)sumi, d_w*d_a, .), ascending blocks per element"});
+  }
   // f32 forward-pass ops around the matmul (lib/Conversion/RVV/RVVToEmitCForwardElementwise.cpp)
   t.push_back({"tcrv_rvv.ggml_vec_scale_f32", withKind("ggml_vec_scale_f32", {}), "", {"tcrv_rvv.ggml_vec_scale_f32"},
                {"output-buffer", "dequant-scale-value", "runtime-element-count"},
