@@ -472,6 +472,29 @@ def measure_other_kernels(pkg, torch):
     timed("gemv_q4_0_q8_0_batch8", lambda c: pkg.gemv(w4[c], x8, out=y8, flags=pkg.FLAG_STATIC_WEIGHTS), 5,
           gemv_bytes(32000, 4096, 8), "32000 x 4096, batch 8")
     del w4
+    # consumers of the 16-row interleaved layouts: decode GEMV over block_q4_0x16 / block_q8_0x16
+    # (random bytes stand in for the weights: the timing does not depend on the values), and the
+    # prefill GEMM over block_q4_0x16 x block_q8_0x4 with resident weights
+    x1r = x1.reshape(-1)
+    for q8w, rows, block, copies in ((False, 32000, 288, 5), (True, 11008, 544, 6)):
+        wx = [torch.randint(0, 256, (rows // 16 * 128 * block,), dtype=torch.uint8, device="cuda", generator=gen)
+              for _ in range(copies)]
+        yr = torch.empty(rows, device="cuda")
+        timed("repack_gemv_q8_0x16" if q8w else "repack_gemv_q4_0x16",
+              lambda c, wx=wx, yr=yr, rows=rows, q8w=q8w: pkg.repack_gemv(wx[c], x1r, rows, q8_weights=q8w, out=yr),
+              copies, rows * 128 * (34 if q8w else 18) + 128 * 34 + 4 * rows, f"{rows} x 4096, batch 1")
+        del wx
+    wx = torch.randint(0, 256, (11008 // 16 * 128 * 288,), dtype=torch.uint8, device="cuda", generator=gen)
+    xx = torch.randint(0, 256, (GEMM_TOKENS // 4 * 128 * 136,), dtype=torch.uint8, device="cuda", generator=gen)
+    pw = pkg.PreparedX16Weights(wx, 4096, 11008)
+    og = torch.empty((GEMM_TOKENS, 11008), device="cuda")
+    wsg = torch.empty(int(pkg.lib().tcrv_cuda_gemm_acts_workspace_bytes(4096, GEMM_TOKENS)), dtype=torch.uint8,
+                      device="cuda")
+    timed("repack_gemm_q4_0x16_q8_0x4", lambda c: pw.gemm(xx, GEMM_TOKENS, out=og, workspace=wsg), 4,
+          11008 * 128 * 18 + GEMM_TOKENS * 128 * 34 + 4 * GEMM_TOKENS * 11008,
+          "M512 x N11008 x K4096, resident weights; tensor-bound: see tops")
+    out[-1]["tops"] = round(2 * GEMM_TOKENS * 11008 * 4096 / out[-1]["us"] / 1e6, 1)
+    del wx, xx, pw, og, wsg
     # f32 forward-pass ops on a prefill-sized activation (512 tokens x 11008 = 22.5 MB; 8 sets)
     acts = [torch.randn((512, 11008), generator=gen, device="cuda") for _ in range(8)]
     outs = [torch.empty((512, 11008), device="cuda") for _ in range(8)]
