@@ -21,6 +21,10 @@ import sibling_data  # noqa: E402
 CASES = {"nr": 16, "k": 512, "nc": 5, "seed": 9100}
 
 
+def c_nr():
+    return CASES["nr"]
+
+
 def inputs(O):
     c = CASES
     wf = O.fill_normal(c["nr"] * c["k"], c["seed"], 0.0, 0.02).reshape(c["nr"], c["k"])
@@ -44,6 +48,13 @@ def build(O):
         "rope_thetas": O.rope_thetas(64, 1234.0, 0.8660254),
         "pack_x16": O.pack_q4_0_to_q4_0x16(w4[:16].reshape(-1)),
     }
+    # consumers of the interleaved layouts: strict order (the reference's), the kernel's order
+    # for K = 512 (one range), and the token-major GEMM over the first four activation rows
+    wx4, wx8, xx4 = O.rows_to_q4_0x16(w4), O.rows_to_q8_0x16(w8), O.rows_to_q8_0x4(x8[:4])
+    out["repack_gemv_q4_strict"] = O.repack_gemv(wx4, x8[0], c_nr())
+    out["repack_gemv_q4_kernel"] = O.repack_gemv(wx4, x8[0], c_nr(), parts=1)
+    out["repack_gemv_q8_kernel"] = O.repack_gemv(wx8, x8[0], c_nr(), q8_weights=True, parts=1)
+    out["repack_gemm_q4"] = O.repack_gemm(wx4, xx4, CASES["k"], 4, c_nr())
     for fmt in (1, 2, 3):
         w, x = sibling_data.make(fmt, 6, 2, 16, 9200 + fmt)
         out[f"sibling{fmt}"] = O.sibling_dot_rows(fmt, w, x)

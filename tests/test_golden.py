@@ -56,8 +56,19 @@ def test_kernels_reproduce_the_fixture(cuda, pkg, O, golden):
     for fmt in (1, 2, 3):
         w, x = sibling_data.make(fmt, 6, 2, 16, 9200 + fmt)
         got[f"sibling{fmt}"] = pkg.sibling_dot_rows(fmt, dev(w), dev(x))
+    wx4 = dev(O.rows_to_q4_0x16(w4.cpu().numpy()))
+    wx8 = dev(O.rows_to_q8_0x16(w8.cpu().numpy()))
+    xx4 = dev(O.rows_to_q8_0x4(x8[:4].cpu().numpy()))
+    nr, k = make_golden.CASES["nr"], make_golden.CASES["k"]
+    assert pkg.repack_gemv_parts(k) == 1
+    got["repack_gemv_q4_kernel"] = pkg.repack_gemv(wx4, x8[0], nr)
+    got["repack_gemv_q8_kernel"] = pkg.repack_gemv(wx8, x8[0], nr, q8_weights=True)
+    got["repack_gemm_q4"] = pkg.repack_gemm(wx4, xx4, k, 4, nr)
     # five columns, K = 512: the tensor-core GEMV serves the unflagged call (order 2)
     assert pkg.gemv_fold_order(w4, x8) == 2 and pkg.gemv_fold_order(w4, x8, flags=0x1000) == 1
     pkg.check_device_errors()
     for name, value in got.items():
         assert same(value.cpu().numpy(), golden[name]), name
+    # the strict-order entry of the fixture has no kernel of its own: the kernel order stays
+    # within rounding of it
+    assert np.allclose(got["repack_gemv_q4_kernel"].cpu().numpy(), golden["repack_gemv_q4_strict"], rtol=0, atol=1e-6)

@@ -65,3 +65,58 @@ def test_checksum_of_block_sums_matches_integer_matmul(cuda, pkg):
     xq = x.view(4, 128, 34)[:, :, 2:].contiguous().view(cuda.int8).to(cuda.int64).view(4, 4096)
     ref = wdec.to(cuda.float64) @ xq.to(cuda.float64).t()  # exact: every partial sum is far below 2^53
     assert cuda.equal(sums.to(cuda.float64), ref)
+
+
+def _rows_to_x16(cuda, pkg, w):
+    """Plain Q4_0 rows (device) -> block_q4_0x16 groups with the device pack kernel: the 16
+    blocks (row 16g+j, block l) are gathered side by side first, as the pack op expects."""
+    nr, nb = w.shape[0], w.shape[1] // 18
+    gathered = w.view(nr // 16, 16, nb, 18).permute(0, 2, 1, 3).contiguous().view(-1)
+    return pkg.pack_q4_0_to_q4_0x16(gathered)
+
+
+def test_repacked_gemv_full_size_agrees_with_plain_rows_and_ignores_group_placement(cuda, pkg, O):
+    gen = cuda.Generator(device="cuda").manual_seed(77)
+    nr, k = 32000, 4096
+    w = pkg.quantize_q4_0(cuda.randn((nr, k), generator=gen, device="cuda") * 0.02)
+    x = pkg.quantize_q8_0(cuda.randn((1, k), generator=gen, device="cuda"))
+    wx = _rows_to_x16(cuda, pkg, w)
+    got = pkg.repack_gemv(wx, x[0], nr)
+    # same integers, two fold conventions and two summation orders: equal to rounding
+    plain = pkg.gemv(w, x)[:, 0]
+    scale = float(plain.abs().max())
+    assert float((got - plain).abs().max()) <= 2e-5 * scale
+    # a row group's result does not depend on which CTA or warp folds it: reverse the groups
+    nb = k // 32
+    rev = wx.view(nr // 16, nb * 288).flip(0).contiguous().view(-1)
+    got_rev = pkg.repack_gemv(rev, x[0], nr)
+    assert cuda.equal(got_rev.view(nr // 16, 16).flip(0).reshape(-1), got)
+    # and a slice of groups, restated by the oracle, bit for bit
+    groups = slice(1000, 1003)
+    sub = wx.view(nr // 16, nb * 288)[groups].contiguous().view(-1).cpu().numpy()
+    want = O.repack_gemv(sub, x[0].cpu().numpy(), 48, parts=pkg.repack_gemv_parts(k))
+    assert np.array_equal(got[16000:16048].cpu().numpy().view(np.uint32), want.view(np.uint32))
+    pkg.check_device_errors()
+
+
+def test_repacked_gemm_full_size_agrees_with_plain_gemm_and_oracle_slices(cuda, pkg, O):
+    gen = cuda.Generator(device="cuda").manual_seed(78)
+    nc, k, nr = 11008, 4096, 512
+    w = pkg.quantize_q4_0(cuda.randn((nc, k), generator=gen, device="cuda") * 0.02)
+    x = pkg.quantize_q8_0(cuda.randn((nr, k), generator=gen, device="cuda"))
+    wx = _rows_to_x16(cuda, pkg, w)
+    xx = cuda.from_numpy(O.rows_to_q8_0x4(x.cpu().numpy())).cuda()
+    got = pkg.repack_gemm(wx, xx, k, nr, nc)                # [token][weight row]
+    plain = pkg.gemm(w, x)                                   # [weight row][token], the other fold convention
+    assert float((got - plain.t()).abs().max()) <= 2e-6 * float(plain.abs().max())
+    # oracle on two weight-row groups x two token groups taken from the corners of the problem
+    nb = k // 32
+    wgroups = wx.view(nc // 16, nb * 288)
+    xgroups = xx.view(nr // 4, nb * 136)
+    for g0, y0 in ((0, 0), (nc // 16 - 2, nr // 4 - 2), (343, 77)):
+        subw = wgroups[g0:g0 + 2].contiguous().view(-1).cpu().numpy()
+        subx = xgroups[y0:y0 + 2].contiguous().view(-1).cpu().numpy()
+        want = O.repack_gemm(subw, subx, k, 8, 32)
+        have = got[4 * y0:4 * y0 + 8, 16 * g0:16 * g0 + 32].cpu().numpy()
+        assert np.array_equal(np.ascontiguousarray(have).view(np.uint32), want.view(np.uint32))
+    pkg.check_device_errors()
