@@ -63,6 +63,8 @@ __device__ __forceinline__ float apply_one(float x, float v) {
     return ggml_expf(__fsub_rn(x, v));
 }
 
+constexpr int kMapUnroll = 4;
+
 template <int kOp, bool kVector>
 __global__ void __launch_bounds__(kThreads) map_kernel(const float *x, float *y, float v, size_t n) {
   const size_t tid = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -71,7 +73,25 @@ __global__ void __launch_bounds__(kThreads) map_kernel(const float *x, float *y,
     const size_t nvec = n / 4;
     const float4 *x4 = reinterpret_cast<const float4 *>(x);
     float4 *y4 = reinterpret_cast<float4 *>(y);
-    for (size_t i = tid; i < nvec; i += nthreads) {
+    // four independent 16-byte loads in flight per thread before the first result is stored
+    size_t i = tid;
+    for (; i + (kMapUnroll - 1) * nthreads < nvec; i += kMapUnroll * nthreads) {
+      float4 a[kMapUnroll];
+#pragma unroll
+      for (int u = 0; u < kMapUnroll; ++u)
+        a[u] = x4[i + u * nthreads];
+#pragma unroll
+      for (int u = 0; u < kMapUnroll; ++u) {
+        a[u].x = apply_one<kOp>(a[u].x, v);
+        a[u].y = apply_one<kOp>(a[u].y, v);
+        a[u].z = apply_one<kOp>(a[u].z, v);
+        a[u].w = apply_one<kOp>(a[u].w, v);
+      }
+#pragma unroll
+      for (int u = 0; u < kMapUnroll; ++u)
+        y4[i + u * nthreads] = a[u];
+    }
+    for (; i < nvec; i += nthreads) {
       float4 a = x4[i];
       a.x = apply_one<kOp>(a.x, v);
       a.y = apply_one<kOp>(a.y, v);
@@ -91,7 +111,7 @@ template <int kOp>
 int launch_map(const float *x, float *y, float v, size_t n, cudaStream_t stream) {
   if (n == 0)
     return TCRV_CUDA_OK;
-  const int grid = grid_for(n, kThreads * 8, 8);
+  const int grid = grid_for(n, kThreads * 4 * kMapUnroll, 8);
   if (aligned16(x) && aligned16(y))
     map_kernel<kOp, true><<<grid, kThreads, 0, stream>>>(x, y, v, n);
   else
