@@ -1,6 +1,7 @@
 // extern "C" surface of the provider: argument validation, status codes, error text and the
 // device-side error word.  Every function here takes device pointers and launches on the
 // caller's stream; none allocates, and none has a CPU fallback.
+#include <atomic>
 #include <cstring>
 #include <stdio.h>
 #include <string.h>
@@ -24,7 +25,7 @@ int record_cuda_error(cudaError_t err, const char *what) {
 }
 
 int sm_count() {
-  static int cached[64] = {};
+  static std::atomic<int> cached[64];
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64)
     return kNumSMsB200;

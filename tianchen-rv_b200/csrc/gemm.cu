@@ -7,6 +7,7 @@
 //   weight scale fp32 [nr][nbp]          nbp = blocks per row rounded up to 4
 //   activations  int8 [nc][K]
 //   act. scale   fp32 [nb][ncp]          transposed; ncp = columns rounded up to 4
+#include <atomic>
 #include <cuda.h>
 
 #include "gemm_tc.cuh"
@@ -149,8 +150,8 @@ using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_
                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 int get_encode_fn(EncodeTiledFn *out) {
-  static EncodeTiledFn cached = nullptr;
-  if (cached == nullptr) {
+  static std::atomic<EncodeTiledFn> cached{nullptr};  // host threads may race to fill it with the same value
+  if (cached.load() == nullptr) {
     void *fn = nullptr;
     cudaDriverEntryPointQueryResult qres;
     TCRV_CUDA_TRY(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
@@ -245,7 +246,7 @@ int run_gemm(size_t n, float *const *dst, size_t ndst, const uint8_t *weights_pl
   if (repack && multi)
     return TCRV_CUDA_ERR_UNSUPPORTED;
   const int variant = repack ? 2 : (multi ? 1 : 0);
-  static bool configured[64][3] = {};
+  static std::atomic<bool> configured[64][3];
   int dev = 0;
   TCRV_CUDA_TRY(cudaGetDevice(&dev));
   if (dev < 64 && !configured[dev][variant]) {
@@ -395,7 +396,7 @@ int launch_gemm_static_scratch(size_t n, float *s, const uint8_t *vx, size_t bx,
   const size_t wbytes = gemm_weights_bytes(n, nr), abytes = gemm_acts_bytes(n, nc);
   if (wbytes + abytes > kStaticScratchBytes)
     return TCRV_CUDA_ERR_WORKSPACE;
-  static uint8_t *base[64] = {};
+  static std::atomic<uint8_t *> base[64];
   int dev = 0;
   TCRV_CUDA_TRY(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 64)

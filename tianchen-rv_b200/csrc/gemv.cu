@@ -2,6 +2,7 @@
 // bulk copies, otherwise a generic warp-per-row kernel that accepts any alignment and any
 // block count and also implements the strict (sequential) fold order.  Plus the debug kernel
 // that exposes the integer stage (per-block int32 sums).
+#include <atomic>
 #include "gemv_mma.cuh"
 #include "gemv_stream.cuh"
 #include "launchers.h"
@@ -122,7 +123,7 @@ constexpr size_t kMaxDynamicSmem = 227 * 1024;
 template <bool kQ8W, int kCols, int kXRegPairs>
 int launch_stream_instance(const GemvArgs &args, int grid, size_t smem, cudaStream_t stream) {
   auto kernel = gemv_stream_kernel<kQ8W, kCols, kXRegPairs>;
-  static bool configured[64] = {};
+  static std::atomic<bool> configured[64];
   int dev = 0;
   TCRV_CUDA_TRY(cudaGetDevice(&dev));
   if (dev < 64 && !configured[dev]) {
@@ -226,7 +227,7 @@ int launch_mma(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t 
   const bool xregs = nb <= static_cast<uint32_t>(kMmaWarps * kMmaChunkBlocks);
   auto kernel = slot_groups == 2 ? (xregs ? gemv_mma_kernel<kQ8W, true, 2> : gemv_mma_kernel<kQ8W, false, 2>)
                                  : (xregs ? gemv_mma_kernel<kQ8W, true, 1> : gemv_mma_kernel<kQ8W, false, 1>);
-  static bool configured[64][4] = {};
+  static std::atomic<bool> configured[64][4];
   int dev = 0;
   TCRV_CUDA_TRY(cudaGetDevice(&dev));
   const int variant = (xregs ? 1 : 0) + (slot_groups == 2 ? 2 : 0);

@@ -28,6 +28,7 @@
 // warps (a divisor of `parts`) share a group, each folding parts/coop consecutive ranges, and
 // a CTA of 16 warps handles 16/coop groups per round.  Range sums meet in shared memory and
 // the first warp of the group adds them.
+#include <atomic>
 #include "async_copy.cuh"
 #include "launchers.h"
 #include "tcrv_common.cuh"
@@ -323,7 +324,7 @@ int launch_repack_gemv_impl(size_t n, float *s, const uint8_t *vx, const uint8_t
   args.window = window < args.depth ? window : args.depth - 1;
   const size_t smem = fixed + static_cast<size_t>(kRpWarps) * args.depth * F::kSlotBytes;
 
-  static bool configured[64][2] = {};
+  static std::atomic<bool> configured[64][2];
   int dev = 0;
   TCRV_CUDA_TRY(cudaGetDevice(&dev));
   if (dev < 64 && !configured[dev][kQ8W ? 1 : 0]) {
