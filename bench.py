@@ -411,7 +411,9 @@ def measure_e2e(pkg, torch, layers, steps, dist):
             "h2d_bytes_per_step": sum(int(x.numel()) for _, _, x, _ in host),
             "d2h_bytes_per_step": sum(int(y.numel()) * 4 for _, _, _, y in host),
             "ms_per_step": round(dt / steps * 1e3, 4), "steps": steps,
-            "weights": "registered once (resident); activations and outputs cross PCIe every step"}
+            "weights": "registered once (resident); activations and outputs cross PCIe every step "
+                       "(inputs by a copy from the pinned buffer, results stored by the kernel into the pinned "
+                       "output through its device mapping)"}
 
 
 def measure_other_kernels(pkg, torch):

@@ -113,11 +113,14 @@ __device__ __forceinline__ float fold_pair(float acc, const uint32_t *w, const X
   return acc;
 }
 
-// Folds all block pairs of `kRows` weight rows (kRows = 1 or 2, the rows of one slot) against
-// every activation column, then reduces over the warp and stores.
+// Folds all block pairs of `kRows` weight rows (the rows of one slot) against every
+// activation column and reduces over the warp.  Several columns: stores the results.  One
+// column: hands the kRows sums back in `res` (every lane holds them) so that the caller can
+// collect a warp's consecutive rows and store them together.
 template <bool kQ8W, int kCols, int kXRegPairs, int kRows>
 __device__ __forceinline__ void gemv_rows(const GemvArgs &a, const uint32_t *wrow0, const uint8_t *xsm,
-                                          uint32_t xcol_bytes, const XBlockPair *xr, uint32_t row, int lane) {
+                                          uint32_t xcol_bytes, const XBlockPair *xr, uint32_t row, int lane,
+                                          float (&res)[kGemvMaxRowsPerSlot]) {
   using F = WeightFormat<kQ8W>;
   constexpr int PW = F::kPairWords;
   const uint32_t nb = a.nb, npairs = nb / 2;
@@ -170,14 +173,20 @@ __device__ __forceinline__ void gemv_rows(const GemvArgs &a, const uint32_t *wro
       for (int b = 0; b < kCols; ++b)
         acc[r][b] = __fadd_rn(acc[r][b], __shfl_xor_sync(0xffffffffu, acc[r][b], off));
   }
+  if constexpr (kCols == 1) {
 #pragma unroll
-  for (int r = 0; r < kRows; ++r) {
-    float mine = acc[r][0];
+    for (int r = 0; r < kRows; ++r)
+      res[r] = acc[r][0];
+  } else {
 #pragma unroll
-    for (int b = 1; b < kCols; ++b)
-      mine = lane == b ? acc[r][b] : mine;
-    if (lane < kCols)
-      a.s[static_cast<size_t>(row + r) * a.bs + lane] = mine;
+    for (int r = 0; r < kRows; ++r) {
+      float mine = acc[r][0];
+#pragma unroll
+      for (int b = 1; b < kCols; ++b)
+        mine = lane == b ? acc[r][b] : mine;
+      if (lane < kCols)
+        a.s[static_cast<size_t>(row + r) * a.bs + lane] = mine;
+    }
   }
 }
 
@@ -273,6 +282,8 @@ __global__ void __launch_bounds__(kGemvMaxThreads, 1) gemv_stream_kernel(const G
     }
   }
 
+  float keep = 0.0f;                  // single column: a row result waiting to be stored
+  uint32_t kept = 0, kept_row = w0;   // rows waiting, first of them
   for (uint32_t t = 0; t < mine; ++t) {
     const uint32_t bar = warp * spw + t % spw;
     if (!mbar_wait_bounded(&full[bar], (t / spw) & 1)) {
@@ -294,16 +305,33 @@ __global__ void __launch_bounds__(kGemvMaxThreads, 1) gemv_stream_kernel(const G
     const uint32_t *wrow = reinterpret_cast<const uint32_t *>(slots + static_cast<size_t>(bar) * slot_bytes);
     const uint32_t rows = slot_count(t);
     // all rows of the slot are folded together (independent accumulators hide latency)
+    float res[kGemvMaxRowsPerSlot];
     if (rows == 4) {
       if constexpr (kCols == 1)
-        gemv_rows<kQ8W, kCols, kXRegPairs, 4>(a, wrow, xsm, xcol_bytes, xr, row, lane);
+        gemv_rows<kQ8W, kCols, kXRegPairs, 4>(a, wrow, xsm, xcol_bytes, xr, row, lane, res);
     } else if (rows == 3) {
       if constexpr (kCols == 1)
-        gemv_rows<kQ8W, kCols, kXRegPairs, 3>(a, wrow, xsm, xcol_bytes, xr, row, lane);
+        gemv_rows<kQ8W, kCols, kXRegPairs, 3>(a, wrow, xsm, xcol_bytes, xr, row, lane, res);
     } else if (rows == 2) {
-      gemv_rows<kQ8W, kCols, kXRegPairs, 2>(a, wrow, xsm, xcol_bytes, xr, row, lane);
+      gemv_rows<kQ8W, kCols, kXRegPairs, 2>(a, wrow, xsm, xcol_bytes, xr, row, lane, res);
     } else {
-      gemv_rows<kQ8W, kCols, kXRegPairs, 1>(a, wrow, xsm, xcol_bytes, xr, row, lane);
+      gemv_rows<kQ8W, kCols, kXRegPairs, 1>(a, wrow, xsm, xcol_bytes, xr, row, lane, res);
+    }
+    if constexpr (kCols == 1) {
+      // One column: lane j keeps the j-th unsaved row of this warp, and the rows leave together
+      // (one store of up to 32 consecutive floats when bs == 1) instead of one 4-byte store
+      // per row; this matters when the output lies in mapped host memory.
+      if (kept + rows > 32) {
+        if (static_cast<uint32_t>(lane) < kept)
+          a.s[static_cast<size_t>(kept_row + lane) * a.bs] = keep;
+        kept_row += kept;
+        kept = 0;
+      }
+#pragma unroll
+      for (uint32_t r = 0; r < kGemvMaxRowsPerSlot; ++r)
+        if (r < rows && static_cast<uint32_t>(lane) == kept + r)
+          keep = res[r];
+      kept += rows;
     }
     // Every lane has consumed its words of the slot (their values fed the reduction above);
     // order those reads before the copy engine overwrites the slot, then refill it.
@@ -312,6 +340,10 @@ __global__ void __launch_bounds__(kGemvMaxThreads, 1) gemv_stream_kernel(const G
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       issue(t + spw);
     }
+  }
+  if constexpr (kCols == 1) {
+    if (static_cast<uint32_t>(lane) < kept)
+      a.s[static_cast<size_t>(kept_row + lane) * a.bs] = keep;
   }
 }
 

@@ -260,6 +260,17 @@ int host_matmul_locked(HostContext &c, bool q8_weights, size_t n, float *s, cons
     for (Replay &r : c.replays)
       if (r.key == key)
         replay = &r;
+  // A replayed single-column decode call writes its result straight into the caller's pinned
+  // buffer through its device mapping (the kernel stores a warp's consecutive rows together):
+  // one graph node and one DMA latency less than a copy back.
+  float *mapped_out = nullptr;
+  if (capture && replay != nullptr && !use_gemm && nc == 1) {
+    void *m = nullptr;
+    if (cudaHostGetDevicePointer(&m, s, 0) == cudaSuccess)
+      mapped_out = static_cast<float *>(m);
+    else
+      (void)cudaGetLastError();
+  }
   const bool capturing = capture && replay != nullptr &&
                          cudaStreamBeginCapture(c.stream, cudaStreamCaptureModeThreadLocal) == cudaSuccess;
   // every early return below must leave capture mode
@@ -323,18 +334,23 @@ int host_matmul_locked(HostContext &c, bool q8_weights, size_t n, float *s, cons
     st = launch_gemm_prepare_acts_q8_0(n, dx, xrow, nc, acts, c.stream);
     if (st == TCRV_CUDA_OK)
       st = launch_gemm_prepared(n, ds, prepared, acts, nr, nc, nc, c.stream);
-  } else if (q8_weights) {
-    st = launch_gemv<true>(n, ds, dw, dx, xrow, nr, nc, dbx, nc, flags, c.stream);
   } else {
-    st = launch_gemv<false>(n, ds, dw, dx, xrow, nr, nc, dbx, nc, flags, c.stream);
+    float *out = capturing && mapped_out != nullptr ? mapped_out : ds;
+    const size_t out_bs = out == ds ? nc : bs;
+    st = q8_weights ? launch_gemv<true>(n, out, dw, dx, xrow, nr, nc, dbx, out_bs, flags, c.stream)
+                    : launch_gemv<false>(n, out, dw, dx, xrow, nr, nc, dbx, out_bs, flags, c.stream);
+    if (out != ds)
+      ds = nullptr;  // nothing to copy back
   }
   if (st != TCRV_CUDA_OK)
     return st;
-  if (nr == 1 || bs == nc)
-    TCRV_CUDA_TRY(cudaMemcpyAsync(s, ds, nr * nc * sizeof(float), cudaMemcpyDeviceToHost, c.stream));
-  else
-    TCRV_CUDA_TRY(cudaMemcpy2DAsync(s, bs * sizeof(float), ds, nc * sizeof(float), nc * sizeof(float), nr,
-                                    cudaMemcpyDeviceToHost, c.stream));
+  if (ds != nullptr) {
+    if (nr == 1 || bs == nc)
+      TCRV_CUDA_TRY(cudaMemcpyAsync(s, ds, nr * nc * sizeof(float), cudaMemcpyDeviceToHost, c.stream));
+    else
+      TCRV_CUDA_TRY(cudaMemcpy2DAsync(s, bs * sizeof(float), ds, nc * sizeof(float), nc * sizeof(float), nr,
+                                      cudaMemcpyDeviceToHost, c.stream));
+  }
   if (capturing) {
     guard.active = false;
     cudaGraph_t graph = nullptr;
