@@ -118,6 +118,31 @@ uint8_t *arena_take(HostContext &c, size_t bytes) {
 }
 
 // rows x row_bytes, host stride -> packed device rows
+// Copies `rows` rows of `row_bytes` from mapped pinned host memory into a packed device buffer
+// with SM loads, and lets the next kernel of the stream start at once (programmatic dependent
+// launch): a decode GEMV launched behind it streams its first weight slots while the few KB of
+// activations cross PCIe, instead of waiting behind a copy node.
+__global__ void __launch_bounds__(512) fetch_rows_kernel(const uint8_t *__restrict__ src, uint8_t *__restrict__ dst,
+                                                         uint32_t rows, uint32_t row_bytes, size_t stride) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  const bool vec = row_bytes % 16 == 0 && stride % 16 == 0 && (reinterpret_cast<uintptr_t>(src) & 15u) == 0 &&
+                   (reinterpret_cast<uintptr_t>(dst) & 15u) == 0;
+  if (vec) {
+    const uint32_t per_row = row_bytes / 16, total = rows * per_row;
+    for (uint32_t i = threadIdx.x; i < total; i += blockDim.x) {
+      const uint32_t r = i / per_row, j = i - r * per_row;
+      reinterpret_cast<uint4 *>(dst + static_cast<size_t>(r) * row_bytes)[j] =
+          reinterpret_cast<const uint4 *>(src + r * stride)[j];
+    }
+  } else {
+    const uint32_t total = rows * row_bytes;
+    for (uint32_t i = threadIdx.x; i < total; i += blockDim.x) {
+      const uint32_t r = i / row_bytes, j = i - r * row_bytes;
+      dst[static_cast<size_t>(r) * row_bytes + j] = src[r * stride + j];
+    }
+  }
+}
+
 int upload_rows(HostContext &c, uint8_t *dst, const void *src, size_t rows, size_t row_bytes, size_t stride) {
   if (rows == 0 || row_bytes == 0)
     return TCRV_CUDA_OK;
@@ -271,6 +296,15 @@ int host_matmul_locked(HostContext &c, bool q8_weights, size_t n, float *s, cons
     else
       (void)cudaGetLastError();
   }
+  // ... and fetches its activations with a kernel the GEMV can start behind (see fetch_rows_kernel)
+  const uint8_t *mapped_in = nullptr;
+  if (capture && replay != nullptr && !use_gemm && nc * xrow <= (256u << 10)) {
+    void *m = nullptr;
+    if (cudaHostGetDevicePointer(&m, const_cast<uint8_t *>(vy), 0) == cudaSuccess)
+      mapped_in = static_cast<const uint8_t *>(m);
+    else
+      (void)cudaGetLastError();
+  }
   const bool capturing = capture && replay != nullptr &&
                          cudaStreamBeginCapture(c.stream, cudaStreamCaptureModeThreadLocal) == cudaSuccess;
   // every early return below must leave capture mode
@@ -302,9 +336,15 @@ int host_matmul_locked(HostContext &c, bool q8_weights, size_t n, float *s, cons
     dbx = wrow;
   }
   uint8_t *dx = arena_take(c, nc * xrow);
-  st = upload_rows(c, dx, vy, nc, xrow, by);
-  if (st != TCRV_CUDA_OK)
-    return st;
+  const bool fetched = capturing && mapped_in != nullptr;
+  if (fetched) {
+    fetch_rows_kernel<<<1, 512, 0, c.stream>>>(mapped_in, dx, static_cast<uint32_t>(nc), static_cast<uint32_t>(xrow), by);
+    TCRV_CUDA_TRY(cudaGetLastError());
+  } else {
+    st = upload_rows(c, dx, vy, nc, xrow, by);
+    if (st != TCRV_CUDA_OK)
+      return st;
+  }
   float *ds = reinterpret_cast<float *>(arena_take(c, nr * nc * sizeof(float)));
 
   if (use_gemm) {
@@ -337,8 +377,10 @@ int host_matmul_locked(HostContext &c, bool q8_weights, size_t n, float *s, cons
   } else {
     float *out = capturing && mapped_out != nullptr ? mapped_out : ds;
     const size_t out_bs = out == ds ? nc : bs;
-    st = q8_weights ? launch_gemv<true>(n, out, dw, dx, xrow, nr, nc, dbx, out_bs, flags, c.stream)
-                    : launch_gemv<false>(n, out, dw, dx, xrow, nr, nc, dbx, out_bs, flags, c.stream);
+    // resident weights are static: behind the fetch kernel the GEMV may stream them at once
+    const unsigned lf = flags | (fetched && res ? TCRV_CUDA_FLAG_STATIC_WEIGHTS : 0u);
+    st = q8_weights ? launch_gemv<true>(n, out, dw, dx, xrow, nr, nc, dbx, out_bs, lf, c.stream)
+                    : launch_gemv<false>(n, out, dw, dx, xrow, nr, nc, dbx, out_bs, lf, c.stream);
     if (out != ds)
       ds = nullptr;  // nothing to copy back
   }
