@@ -12,7 +12,7 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 PKG = os.path.join(ROOT, "tianchen-rv_b200")
 HARNESSES = ["add_f32", "add_i32", "q4_0_q8_0_block_dot", "q8_0_q8_0_block_dot", "q4_0_q8_0_gemm", "quantize_row_q8_0",
-             "forward_f32"]
+             "forward_f32", "repack_q4_0_q8_0"]
 
 
 @pytest.fixture(scope="module")

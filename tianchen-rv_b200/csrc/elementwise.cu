@@ -261,17 +261,32 @@ __global__ void __launch_bounds__(kThreads) quantize_q8_0_kernel(const float *__
       if (ib < nblocks)
         v[u] = load_x4<kAlignedIn>(x + ib * kQK + 4 * sub);
     }
+    // block maxima: lane (blk_in_group, sub) ends up with the maximum of block 4u + blk_in_group
+    float amax[kQ8GroupsPerIter];
 #pragma unroll
     for (int u = 0; u < kQ8GroupsPerIter; ++u) {
-      float amax = fmaxf(fmaxf(fabsf(v[u].x), fabsf(v[u].y)), fmaxf(fabsf(v[u].z), fabsf(v[u].w)));
-      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
-      const float d = __fdiv_rn(amax, 127.0f);
-      const float id = d != 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
+      float m = fmaxf(fmaxf(fabsf(v[u].x), fabsf(v[u].y)), fmaxf(fabsf(v[u].z), fabsf(v[u].w)));
+      m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+      m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+      amax[u] = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 4));
+    }
+    // The two IEEE divisions of a block run once per block, not once per lane: lane j (0..15)
+    // takes block j's maximum (held by the lanes of block group j % 4 in register j / 4),
+    // computes d and 1/d, writes the fp16 scale, and every lane fetches its blocks' 1/d back.
+    float mine = 0.0f;
+#pragma unroll
+    for (int u = 0; u < kQ8GroupsPerIter; ++u) {
+      const float t = __shfl_sync(0xffffffffu, amax[u], (lane & 3) * 8);
+      mine = ((lane >> 2) & 3) == u ? t : mine;
+    }
+    const float d = __fdiv_rn(mine, 127.0f);
+    const float id_mine = d != 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
+    if (lane < kQ8IterBlocks)
+      *reinterpret_cast<unsigned short *>(stage + lane * kQ8Block) = __half_as_ushort(__float2half_rn(d));
+#pragma unroll
+    for (int u = 0; u < kQ8GroupsPerIter; ++u) {
+      const float id = __shfl_sync(0xffffffffu, id_mine, u * 4 + blk_in_group);
       uint8_t *yb = stage + (u * 4 + blk_in_group) * kQ8Block;  // 2-byte aligned
-      if (sub == 0)
-        *reinterpret_cast<unsigned short *>(yb) = __half_as_ushort(__float2half_rn(d));
       const uint32_t q01 = narrow_q8(__fmul_rn(v[u].x, id)) | (narrow_q8(__fmul_rn(v[u].y, id)) << 8);
       const uint32_t q23 = narrow_q8(__fmul_rn(v[u].z, id)) | (narrow_q8(__fmul_rn(v[u].w, id)) << 8);
       *reinterpret_cast<unsigned short *>(yb + 2 + 4 * sub) = static_cast<unsigned short>(q01);
