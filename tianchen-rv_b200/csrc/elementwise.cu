@@ -41,6 +41,7 @@ __device__ __forceinline__ int32_t add_one(int32_t a, int32_t b) {
 template <typename T, bool kVector>
 __global__ void __launch_bounds__(kThreads) add_kernel(const T *__restrict__ lhs, const T *__restrict__ rhs,
                                                        T *__restrict__ out, size_t n) {
+  pdl_enter();
   const size_t tid = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   const size_t nthreads = static_cast<size_t>(gridDim.x) * blockDim.x;
   if constexpr (kVector) {
@@ -123,6 +124,7 @@ template <int kBlockBytes, bool kAlignedIn, bool kAlignedOut>
 __global__ void __launch_bounds__(kThreads) dequantize_rows_kernel(const uint8_t *__restrict__ vx,
                                                                    float *__restrict__ y, size_t nblocks) {
   __shared__ __align__(16) uint8_t tile[kTileBlocks * kBlockBytes];
+  pdl_enter();
   const size_t ntiles = (nblocks + kTileBlocks - 1) / kTileBlocks;
   for (size_t t = blockIdx.x; t < ntiles; t += gridDim.x) {
     const size_t first = t * kTileBlocks;
@@ -190,13 +192,13 @@ int launch_dequantize_rows(const uint8_t *vx, float *y, size_t n, cudaStream_t s
   const int grid = grid_for(nblocks, kTileBlocks, 8);
   const bool ain = aligned16(vx), aout = aligned16(y);
   if (ain && aout)
-    dequantize_rows_kernel<kBlockBytes, true, true><<<grid, kThreads, 0, stream>>>(vx, y, nblocks);
+    TCRV_CUDA_TRY(launch_pdl(dequantize_rows_kernel<kBlockBytes, true, true>, grid, kThreads, 0, stream, vx, y, nblocks));
   else if (ain)
-    dequantize_rows_kernel<kBlockBytes, true, false><<<grid, kThreads, 0, stream>>>(vx, y, nblocks);
+    TCRV_CUDA_TRY(launch_pdl(dequantize_rows_kernel<kBlockBytes, true, false>, grid, kThreads, 0, stream, vx, y, nblocks));
   else if (aout)
-    dequantize_rows_kernel<kBlockBytes, false, true><<<grid, kThreads, 0, stream>>>(vx, y, nblocks);
+    TCRV_CUDA_TRY(launch_pdl(dequantize_rows_kernel<kBlockBytes, false, true>, grid, kThreads, 0, stream, vx, y, nblocks));
   else
-    dequantize_rows_kernel<kBlockBytes, false, false><<<grid, kThreads, 0, stream>>>(vx, y, nblocks);
+    TCRV_CUDA_TRY(launch_pdl(dequantize_rows_kernel<kBlockBytes, false, false>, grid, kThreads, 0, stream, vx, y, nblocks));
   TCRV_CUDA_TRY(cudaGetLastError());
   return TCRV_CUDA_OK;
 }
@@ -246,6 +248,7 @@ __global__ void __launch_bounds__(kThreads) quantize_q8_0_kernel(const float *__
                                                                  uint8_t *__restrict__ vy, size_t nblocks,
                                                                  bool out_aligned2) {
   __shared__ __align__(16) uint8_t stage_all[kThreads / 32][kQ8IterBytes];
+  pdl_enter();
   const int lane = threadIdx.x & 31;
   const int sub = lane & 7, blk_in_group = lane >> 3;
   uint8_t *stage = stage_all[threadIdx.x >> 5];
@@ -484,9 +487,9 @@ int launch_add_f32(const float *lhs, const float *rhs, float *out, size_t n, cud
     return TCRV_CUDA_OK;
   const int grid = grid_for(n, kThreads * 16, 8);
   if (aligned16(lhs) && aligned16(rhs) && aligned16(out))
-    add_kernel<float, true><<<grid, kThreads, 0, stream>>>(lhs, rhs, out, n);
+    TCRV_CUDA_TRY(launch_pdl(add_kernel<float, true>, grid, kThreads, 0, stream, lhs, rhs, out, n));
   else
-    add_kernel<float, false><<<grid, kThreads, 0, stream>>>(lhs, rhs, out, n);
+    TCRV_CUDA_TRY(launch_pdl(add_kernel<float, false>, grid, kThreads, 0, stream, lhs, rhs, out, n));
   TCRV_CUDA_TRY(cudaGetLastError());
   return TCRV_CUDA_OK;
 }
@@ -496,9 +499,9 @@ int launch_add_i32(const int32_t *lhs, const int32_t *rhs, int32_t *out, size_t 
     return TCRV_CUDA_OK;
   const int grid = grid_for(n, kThreads * 16, 8);
   if (aligned16(lhs) && aligned16(rhs) && aligned16(out))
-    add_kernel<int32_t, true><<<grid, kThreads, 0, stream>>>(lhs, rhs, out, n);
+    TCRV_CUDA_TRY(launch_pdl(add_kernel<int32_t, true>, grid, kThreads, 0, stream, lhs, rhs, out, n));
   else
-    add_kernel<int32_t, false><<<grid, kThreads, 0, stream>>>(lhs, rhs, out, n);
+    TCRV_CUDA_TRY(launch_pdl(add_kernel<int32_t, false>, grid, kThreads, 0, stream, lhs, rhs, out, n));
   TCRV_CUDA_TRY(cudaGetLastError());
   return TCRV_CUDA_OK;
 }
@@ -529,9 +532,9 @@ int launch_quantize_row_q8_0(size_t n, const float *x, uint8_t *vy, cudaStream_t
   const size_t nblocks = n / kQK;
   const int grid = grid_for(nblocks, (kThreads / 32) * kQ8IterBlocks * 2, 8);
   if (aligned16(x))
-    quantize_q8_0_kernel<true><<<grid, kThreads, 0, stream>>>(x, vy, nblocks, aligned2(vy));
+    TCRV_CUDA_TRY(launch_pdl(quantize_q8_0_kernel<true>, grid, kThreads, 0, stream, x, vy, nblocks, aligned2(vy)));
   else
-    quantize_q8_0_kernel<false><<<grid, kThreads, 0, stream>>>(x, vy, nblocks, aligned2(vy));
+    TCRV_CUDA_TRY(launch_pdl(quantize_q8_0_kernel<false>, grid, kThreads, 0, stream, x, vy, nblocks, aligned2(vy)));
   TCRV_CUDA_TRY(cudaGetLastError());
   return TCRV_CUDA_OK;
 }

@@ -67,6 +67,7 @@ constexpr int kMapUnroll = 4;
 
 template <int kOp, bool kVector>
 __global__ void __launch_bounds__(kThreads) map_kernel(const float *x, float *y, float v, size_t n) {
+  pdl_enter();
   const size_t tid = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   const size_t nthreads = static_cast<size_t>(gridDim.x) * blockDim.x;
   if constexpr (kVector) {
@@ -113,9 +114,9 @@ int launch_map(const float *x, float *y, float v, size_t n, cudaStream_t stream)
     return TCRV_CUDA_OK;
   const int grid = grid_for(n, kThreads * 4 * kMapUnroll, 8);
   if (aligned16(x) && aligned16(y))
-    map_kernel<kOp, true><<<grid, kThreads, 0, stream>>>(x, y, v, n);
+    TCRV_CUDA_TRY(launch_pdl(map_kernel<kOp, true>, grid, kThreads, 0, stream, x, y, v, n));
   else
-    map_kernel<kOp, false><<<grid, kThreads, 0, stream>>>(x, y, v, n);
+    TCRV_CUDA_TRY(launch_pdl(map_kernel<kOp, false>, grid, kThreads, 0, stream, x, y, v, n));
   TCRV_CUDA_TRY(cudaGetLastError());
   return TCRV_CUDA_OK;
 }
@@ -151,6 +152,7 @@ template <bool kCached>
 __global__ void __launch_bounds__(kThreads)
     rms_norm_kernel(size_t n, const float *x, float *y, float eps, size_t nrows, size_t x_stride, size_t y_stride) {
   __shared__ double scratch[kThreads / 32];
+  pdl_enter();
   for (size_t row = blockIdx.x; row < nrows; row += gridDim.x) {
     const float *xr = x + row * x_stride;
     float *yr = y + row * y_stride;
@@ -263,9 +265,9 @@ int launch_rms_norm_f32(size_t n, const float *x, float *y, float eps, size_t nr
   const bool cached = n % 4 == 0 && n <= static_cast<size_t>(kThreads) * 4 * kRmsRegVec && aligned16(x) && aligned16(y) &&
                       (nrows == 1 || (x_stride % 4 == 0 && y_stride % 4 == 0));
   if (cached)
-    rms_norm_kernel<true><<<grid, kThreads, 0, stream>>>(n, x, y, eps, nrows, x_stride, y_stride);
+    TCRV_CUDA_TRY(launch_pdl(rms_norm_kernel<true>, grid, kThreads, 0, stream, n, x, y, eps, nrows, x_stride, y_stride));
   else
-    rms_norm_kernel<false><<<grid, kThreads, 0, stream>>>(n, x, y, eps, nrows, x_stride, y_stride);
+    TCRV_CUDA_TRY(launch_pdl(rms_norm_kernel<false>, grid, kThreads, 0, stream, n, x, y, eps, nrows, x_stride, y_stride));
   TCRV_CUDA_TRY(cudaGetLastError());
   return TCRV_CUDA_OK;
 }

@@ -44,6 +44,33 @@ int record_cuda_error(cudaError_t err, const char *what);
       return ::tcrv::record_cuda_error(tcrv_err_, #expr);        \
   } while (0)
 
+// Programmatic dependent launch for the short streaming kernels.  A kernel launched through
+// launch_pdl may be scheduled while its predecessor on the stream still drains, so launch
+// latency and block scheduling overlap that tail; it runs pdl_enter() before it touches any
+// memory: its own dependents are released at once (they wait in turn), and it waits until
+// the predecessor has completed and its writes are visible.  Launched any other way,
+// pdl_enter() returns immediately.
+__device__ __forceinline__ void pdl_enter() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), int grid, int block, size_t smem, cudaStream_t stream,
+                              Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(grid));
+  cfg.blockDim = dim3(static_cast<unsigned>(block));
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // Number of SMs of the current device (cached per device).
 int sm_count();
 
