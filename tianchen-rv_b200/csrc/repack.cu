@@ -92,6 +92,7 @@ template <bool kQ8W>
 __global__ void __launch_bounds__(kRpThreads, 1) repack_gemv_kernel(const RepackGemvArgs a) {
   using F = X16<kQ8W>;
   extern __shared__ __align__(128) uint8_t smem[];
+  pdl_enter();
   uint64_t *full = reinterpret_cast<uint64_t *>(smem);
   float *partial = reinterpret_cast<float *>(smem + kRpBarrierBytes);
   const uint32_t nb = a.nb;
@@ -332,7 +333,7 @@ int launch_repack_gemv_impl(size_t n, float *s, const uint8_t *vx, const uint8_t
                                        static_cast<int>(kRpSmemLimit)));
     configured[dev][kQ8W ? 1 : 0] = true;
   }
-  repack_gemv_kernel<kQ8W><<<grid, kRpThreads, smem, stream>>>(args);
+  TCRV_CUDA_TRY(launch_pdl(repack_gemv_kernel<kQ8W>, static_cast<int>(grid), kRpThreads, smem, stream, args));
   TCRV_CUDA_TRY(cudaGetLastError());
   return TCRV_CUDA_OK;
 }
