@@ -265,13 +265,14 @@ int run_gemm(size_t n, float *const *dst, size_t ndst, const uint8_t *weights_pl
   const int sms = sm_count();
   const int grid = static_cast<int>(args.tiles < static_cast<uint32_t>(sms) ? args.tiles : sms);
   if (repack)
-    gemm_q4_0_q8_0_tc_kernel<false, true><<<grid, kGemmThreads, kGemmSmemBytesSingle, stream>>>(map_w, map_x, map_dw,
-                                                                                               map_dx, args);
+    TCRV_CUDA_TRY(launch_pdl(gemm_q4_0_q8_0_tc_kernel<false, true>, grid, kGemmThreads, kGemmSmemBytesSingle, stream,
+                             map_w, map_x, map_dw, map_dx, args));
   else if (multi)
-    gemm_q4_0_q8_0_tc_kernel<true><<<grid, kGemmThreads, kGemmSmemBytesMulti, stream>>>(map_w, map_x, map_dw, map_dx, args);
+    TCRV_CUDA_TRY(launch_pdl(gemm_q4_0_q8_0_tc_kernel<true>, grid, kGemmThreads, kGemmSmemBytesMulti, stream, map_w,
+                             map_x, map_dw, map_dx, args));
   else
-    gemm_q4_0_q8_0_tc_kernel<false><<<grid, kGemmThreads, kGemmSmemBytesSingle, stream>>>(map_w, map_x, map_dw, map_dx,
-                                                                                         args);
+    TCRV_CUDA_TRY(launch_pdl(gemm_q4_0_q8_0_tc_kernel<false>, grid, kGemmThreads, kGemmSmemBytesSingle, stream, map_w,
+                             map_x, map_dw, map_dx, args));
   TCRV_CUDA_TRY(cudaGetLastError());
   return TCRV_CUDA_OK;
 }

@@ -164,6 +164,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t nkb = (a.nb + kGemmStageBlocks - 1) / kGemmStageBlocks;
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < kGemmSmemStages; ++i) {
@@ -186,6 +187,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   __syncthreads();
   tcgen05_fence_after_thread_sync();
   const uint32_t tmem_base = *tmem_base_slot;
+  // Programmatic dependent launch: everything above touched only this CTA's shared memory and
+  // TMEM, so it may overlap the tail of the preceding kernel (the activation unpack); operands
+  // are read and outputs written only after that kernel has completed.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
 
   if (warp == kGemmEpilogueWarps) {
     // ------------------------------ TMA producer ------------------------------
