@@ -131,3 +131,37 @@ def test_host_repacked_consumers(cuda, pkg, O, registered):
         for h in held:
             assert L.tcrv_cuda_host_unregister_weights(h.ctypes.data) == 0
     pkg.check_device_errors()
+
+
+def test_replayed_calls_with_offset_buffers_and_row_strides(cuda, pkg, O):
+    # the replayed path reads the activations with a fetch kernel and stores single-column
+    # results through the pinned buffer's device mapping: activations at a 2-byte offset (the
+    # fetch kernel's byte path), an output with a row stride (bs = 3), several columns (copy-out
+    # path), each seen often enough to be captured and replayed
+    L = pkg.lib()
+    nr, k = 333, 1024
+    w, _ = make(O, nr, k, 1, 4600)
+    wh = np.ascontiguousarray(w)
+    xrow = k // 32 * 34
+    pin = cuda.empty(8 * xrow + 64, dtype=cuda.uint8).pin_memory()
+    y1 = cuda.empty((nr, 3), dtype=cuda.float32).pin_memory()
+    y3 = cuda.empty((nr, 3), dtype=cuda.float32).pin_memory()
+    assert L.tcrv_cuda_host_register_weights(wh.ctypes.data, wh.nbytes) == 0
+    try:
+        for step in range(4):
+            xs = O.quantize_q8_0(O.fill_normal(3 * k, 4700 + step).reshape(3, k))
+            pin[2:2 + 3 * xrow].copy_(cuda.from_numpy(xs.reshape(-1)))
+            y1.fill_(-1.0)
+            y3.fill_(-1.0)
+            xptr = pin.data_ptr() + 2
+            assert L.tcrv_cuda_host_gemm_q4_0_q8_0(k, y1.data_ptr(), wh.ctypes.data, xptr, xrow, nr, 1, wh.strides[0], 3) == 0
+            assert L.tcrv_cuda_host_gemm_q4_0_q8_0(k, y3.data_ptr(), wh.ctypes.data, xptr, xrow, nr, 3, wh.strides[0], 3) == 0
+            want = O.gemv_lane_order(w, xs)
+            got1, got3 = y1.numpy(), y3.numpy()
+            assert np.array_equal(got1[:, 0].view(np.uint32), want[:, 0].view(np.uint32)), step
+            assert np.all(got1[:, 1:] == -1.0)  # the stride's padding is untouched
+            assert np.array_equal(got3.view(np.uint32), want.view(np.uint32)), step
+    finally:
+        assert L.tcrv_cuda_host_unregister_weights(wh.ctypes.data) == 0
+        L.tcrv_cuda_host_release()
+    pkg.check_device_errors()
