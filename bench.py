@@ -563,6 +563,17 @@ def measure_gemm(pkg, torch, dist, rank, world):
 
         ms_c = timed(compute)
         ms_p = timed(compute_plain)
+        # calibration of the int8 tensor pipe on this GPU and this shape: the plain library
+        # int8 GEMM (cuBLASLt through torch._int_mm, int32 out, no scales), this rank's rows
+        cal_tops = None
+        try:
+            a8 = torch.randint(-127, 128, (GEMM_TOKENS, k), dtype=torch.int8, device="cuda", generator=gen)
+            b8 = torch.randint(-8, 8, (rows, k), dtype=torch.int8, device="cuda", generator=gen).t()
+            ms_cal = timed(lambda: torch._int_mm(a8, b8))
+            cal_tops = 2.0 * GEMM_TOKENS * rows * k / ms_cal / 1e9
+            del a8, b8
+        except Exception as exc:  # noqa: BLE001 - the calibration is optional
+            cal_note = f"{type(exc).__name__}: {exc}"[:120]
         entry_ = {"shape": f"M{GEMM_TOKENS}xN{nr}xK{k}", "rows_per_gpu": rows,
                   "compute_ms": round(ms_c, 4), "compute_tops": round(ops / ms_c / 1e9, 1),
                   "plain_format_ms": round(ms_p, 4), "plain_format_tops": round(ops / ms_p / 1e9, 1)}
@@ -596,6 +607,15 @@ def measure_gemm(pkg, torch, dist, rank, world):
         entry_["roofline"] = {"bound": "tensor", "achieved": entry_["compute_tops"], "peak": int8_peak,
                               "unit": "TOP/s", "frac": round(entry_["compute_tops"] / world / int8_peak, 4),
                               "peak_kind": f"2 x bf16 burst peak ({peak_kind}); no int8 figure is measured on this pool"}
+        if cal_tops is not None:
+            # per-GPU figures on both sides: this rank's share of the work over the calibration
+            entry_["roofline"]["library_int8_gemm_tops"] = round(cal_tops, 1)
+            entry_["roofline"]["frac_of_library_int8_gemm"] = round(ops / world / ms_c / 1e9 / cal_tops, 4)
+            entry_["roofline"]["library_int8_gemm"] = ("torch._int_mm (cuBLASLt), same M, K and rows per GPU, int32 "
+                                                       "output, no block scales: what the tensor pipe sustains "
+                                                       "without the per-block fp32 fold")
+        else:
+            entry_["roofline"]["library_int8_gemm"] = "unavailable: " + cal_note
         pkg.check_device_errors()
         results.append(entry_)
         del wq, pw, full, ws, ws_plain
