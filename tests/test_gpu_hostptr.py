@@ -165,3 +165,37 @@ def test_replayed_calls_with_offset_buffers_and_row_strides(cuda, pkg, O):
         assert L.tcrv_cuda_host_unregister_weights(wh.ctypes.data) == 0
         L.tcrv_cuda_host_release()
     pkg.check_device_errors()
+
+
+def test_replay_is_abandoned_when_the_buffers_are_no_longer_page_locked(cuda, pkg, O):
+    # a captured call addresses the host buffers through their device mappings; once the caller
+    # unpins them the same call must go back to ordinary copies instead of replaying the graph
+    L = pkg.lib()
+    rt = cuda.cuda.cudart()
+    nr, k = 128, 1024
+    w, x = make(O, nr, k, 1, 4800)
+    wh = np.ascontiguousarray(w)
+    xh = np.zeros(1 << 16, dtype=np.uint8)     # buffers of whole pages, registered by hand
+    yh = np.zeros(1 << 14, dtype=np.float32)
+    xh[:x.size] = x.reshape(-1)
+    call = lambda: L.tcrv_cuda_host_gemm_q4_0_q8_0(k, yh.ctypes.data, wh.ctypes.data, xh.ctypes.data, x.shape[1], nr, 1,
+                                                   wh.strides[0], 1)
+    want = O.gemv_lane_order(w, x)[:, 0]
+    assert L.tcrv_cuda_host_register_weights(wh.ctypes.data, wh.nbytes) == 0
+    try:
+        assert int(rt.cudaHostRegister(xh.ctypes.data, xh.nbytes, 0)) == 0
+        assert int(rt.cudaHostRegister(yh.ctypes.data, yh.nbytes, 0)) == 0
+        for _ in range(3):
+            yh[:nr] = -1.0
+            assert call() == 0
+            assert np.array_equal(yh[:nr].view(np.uint32), want.view(np.uint32))
+        assert int(rt.cudaHostUnregister(xh.ctypes.data)) == 0
+        assert int(rt.cudaHostUnregister(yh.ctypes.data)) == 0
+        for _ in range(3):
+            yh[:nr] = -1.0
+            assert call() == 0
+            assert np.array_equal(yh[:nr].view(np.uint32), want.view(np.uint32))
+    finally:
+        assert L.tcrv_cuda_host_unregister_weights(wh.ctypes.data) == 0
+        L.tcrv_cuda_host_release()
+    pkg.check_device_errors()

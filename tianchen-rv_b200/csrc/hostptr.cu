@@ -85,6 +85,11 @@ bool is_pinned_host(const void *p) {
   return attr.type == cudaMemoryTypeHost;
 }
 
+// First and last byte of a host range are page-locked (a range inside one pinned allocation).
+bool is_pinned_range(const void *p, size_t bytes) {
+  return is_pinned_host(p) && (bytes <= 1 || is_pinned_host(static_cast<const uint8_t *>(p) + bytes - 1));
+}
+
 int ensure_error_mirror(HostContext &c);
 
 int ensure_stream(HostContext &c) {
@@ -250,17 +255,29 @@ int host_matmul_locked(HostContext &c, bool q8_weights, size_t n, float *s, cons
   const bool replayable = res != nullptr && !use_gemm;
   const ReplayKey key{vx, vy, s, n, by, nr, nc, bx, bs, q8_weights, flags};
   Replay *replay = nullptr;
+  // page-locked start of both host buffers (checked on every call, replayed ones included:
+  // about half a microsecond each); the whole ranges are checked before a capture
+  const bool host_pinned = replayable && is_pinned_host(vy) && is_pinned_host(s);
   if (replayable) {
     for (Replay &r : c.replays)
       if (r.key == key)
         replay = &r;
     if (replay != nullptr && replay->exec != nullptr) {
-      TCRV_CUDA_TRY(cudaGraphLaunch(replay->exec, c.stream));
-      return finish(c);
+      // The graph reads and writes the host buffers through their device mappings: they must
+      // still be page-locked (the caller may have freed and reallocated at the same address).
+      if (host_pinned) {
+        TCRV_CUDA_TRY(cudaGraphLaunch(replay->exec, c.stream));
+        return finish(c);
+      }
+      (void)cudaGraphExecDestroy(replay->exec);
+      replay->exec = nullptr;
+      replay->unusable = true;
     }
   }
   // second sighting of a call: capture it (host buffers must be pinned for that)
-  const bool capture = replayable && replay != nullptr && !replay->unusable && is_pinned_host(vy) && is_pinned_host(s);
+  const bool capture = replayable && replay != nullptr && !replay->unusable && host_pinned &&
+                       is_pinned_range(vy, (nc - 1) * by + xrow) &&
+                       is_pinned_range(s, ((nr - 1) * bs + nc) * sizeof(float));
   if (replayable && replay == nullptr) {
     if (c.replays.size() >= kMaxReplays)
       drop_replays(c);
