@@ -51,6 +51,9 @@ int tcrv_cuda_host_repack_gemm_q4_0_q8_0(size_t n, float *s, const uint8_t *vx, 
 /* nc <= 8 runs the decode GEMV, larger nc the tensor-core GEMM. */
 int tcrv_cuda_host_gemm_q4_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by, size_t nr,
                                   size_t nc, size_t bx, size_t bs);
+/* One weight row against `cols` (1..16) activation columns, strict block order per column. */
+int tcrv_cuda_host_gemm_tile_q4_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by,
+                                       size_t cols);
 /* Q8_0 weights: decode GEMV only (nc <= 8). */
 int tcrv_cuda_host_gemm_q8_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by, size_t nr,
                                   size_t nc, size_t bx, size_t bs);
@@ -81,6 +84,10 @@ double tcrv_emitc_ggml_vec_soft_max_f32_kernel_ggml_vec_soft_max_f32(size_t n, f
 /* test/Conversion/RVV/rvv-to-emitc-ggml-rope-norm-f32.mlir:58 */
 void tcrv_emitc_ggml_rope_norm_f32_kernel_ggml_rope_norm_f32(size_t n_dims, const float *x, float *y, float theta_base,
                                                              float theta_scale);
+/* test/Conversion/RVV/rvv-to-emitc-q4-0-q8-0-gemm-tile.mlir:40 (the fixture's variant has
+ * activation_cols = 4; other column counts get their entry from `--tcrv-cuda-launch-to-cpp`) */
+void tcrv_emitc_ggml_q4_0_q8_0_gemm_tile_kernel_ggml_q4_0_q8_0_gemm_tile(size_t n, float *s, const uint8_t *vx,
+                                                                         const uint8_t *vy, size_t by);
 /* test/Conversion/RVV/rvv-to-emitc-repack-gemv-q4-0-q8-0.mlir:49 */
 void tcrv_emitc_ggml_repack_gemv_q4_0_q8_0_kernel_ggml_repack_gemv_q4_0_q8_0(size_t n, float *s, const uint8_t *vx,
                                                                              const uint8_t *vy, size_t nc);

@@ -199,3 +199,28 @@ def test_replay_is_abandoned_when_the_buffers_are_no_longer_page_locked(cuda, pk
         assert L.tcrv_cuda_host_unregister_weights(wh.ctypes.data) == 0
         L.tcrv_cuda_host_release()
     pkg.check_device_errors()
+
+
+def test_host_gemm_tile_every_column_count(cuda, pkg, O):
+    # tcrv_rvv.q4_0_q8_0_gemm_tile: one weight row against 1..16 activation columns, every column
+    # the strict-order block dot (up to 8 columns the strict GEMV, beyond that the tensor-core GEMM)
+    L = pkg.lib()
+    k = 1024
+    w, x = make(O, 1, k, 16, 4900)
+    want = O.gemm(w, x, fold=O.FOLD_FMA)[0]
+    wh, xh = np.ascontiguousarray(w), np.ascontiguousarray(x)
+    for cols in range(1, 17):
+        s = np.full(16, -1.0, dtype=np.float32)
+        assert L.tcrv_cuda_host_gemm_tile_q4_0_q8_0(k, s.ctypes.data, wh.ctypes.data, xh.ctypes.data, xh.strides[0], cols) == 0
+        assert np.array_equal(s[:cols].view(np.uint32), want[:cols].view(np.uint32)), cols
+        assert np.all(s[cols:] == -1.0)
+    assert L.tcrv_cuda_host_gemm_tile_q4_0_q8_0(k, s.ctypes.data, wh.ctypes.data, xh.ctypes.data, xh.strides[0], 17) == -1
+    # the reference fixture's entry (activation_cols = 4)
+    fn = L.tcrv_emitc_ggml_q4_0_q8_0_gemm_tile_kernel_ggml_q4_0_q8_0_gemm_tile
+    fn.restype = None
+    fn.argtypes = [ctypes.c_size_t, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t]
+    s = np.full(16, -1.0, dtype=np.float32)
+    fn(k, s.ctypes.data, wh.ctypes.data, xh.ctypes.data, xh.strides[0])
+    assert np.array_equal(s[:4].view(np.uint32), want[:4].view(np.uint32)) and np.all(s[4:] == -1.0)
+    L.tcrv_cuda_host_release()
+    pkg.check_device_errors()

@@ -63,6 +63,8 @@ PROTOTYPES = {
                                     "size_t n_dims, const float *x, float *y, float theta_base, float theta_scale);",
     "cuda-pack-q4-0-to-q4-0x16.mlir": "void tcrv_emitc_ggml_pack_q4_0_to_q4_0x16_kernel_ggml_pack_q4_0_to_q4_0x16("
                                       "size_t nblocks, const uint8_t *src, uint8_t *dst);",
+    "cuda-q4-0-q8-0-gemm-tile.mlir": "void tcrv_emitc_ggml_q4_0_q8_0_gemm_tile_kernel_ggml_q4_0_q8_0_gemm_tile("
+                                     "size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by);",
     "cuda-repack-gemv-q4-0-q8-0.mlir":
         "void tcrv_emitc_ggml_repack_gemv_q4_0_q8_0_kernel_ggml_repack_gemv_q4_0_q8_0("
         "size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t nc);",
@@ -134,6 +136,22 @@ def test_add_plan_records_role_facts_and_abi_order():
             '"n|size_t|runtime-element-count|target-export-abi-owned"]') in p
     m = run([TRANSLATE, "-", "--tcrv-export-emission-manifest"], p)
     assert m.returncode == 0 and "launcher=tcrv_cuda_add_f32" in m.stdout and 'role="dispatch case"' in m.stdout
+
+
+def test_gemm_tile_column_count_is_a_checked_compile_time_argument():
+    src = fixture("cuda-q4-0-q8-0-gemm-tile.mlir")
+    p = plan(src)
+    assert '"tcrv_cuda.constant_arguments=activation_cols=4"' in p
+    # another column count: the generated entry passes it to the host-pointer call as a literal
+    p7 = plan(src.replace("activation_cols = 4", "activation_cols = 7"))
+    stub = run([TRANSLATE, "-", "--tcrv-cuda-launch-to-cpp"], p7)
+    assert stub.returncode == 0, stub.stderr
+    assert "tcrv_cuda_host_gemm_tile_q4_0_q8_0(n, s, vx, vy, by, /*activation_cols=*/7);" in stub.stdout
+    for bad in ("activation_cols = 0", "activation_cols = 17"):
+        r = run([OPT, "-", *PLAN_PASSES], src.replace("activation_cols = 4", bad))
+        assert r.returncode != 0 and "'activation_cols' must lie in 1..16" in r.stderr, r.stderr
+    r = run([OPT, "-", *PLAN_PASSES], src.replace(", activation_cols = 4 : i64", ""))
+    assert r.returncode != 0 and "missing integer attribute 'activation_cols'" in r.stderr, r.stderr
 
 
 def test_gemm_plan_pins_block_format_facts():

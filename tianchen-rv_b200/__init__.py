@@ -100,6 +100,7 @@ ABI.update({
     "tcrv_cuda_host_vec_dot_q4_1_q8_1": [_sz, _p, _p, _p],
     "tcrv_cuda_host_vec_dot_q5_0_q8_0": [_sz, _p, _p, _p],
     "tcrv_cuda_host_vec_dot_q5_1_q8_1": [_sz, _p, _p, _p],
+    "tcrv_cuda_host_gemm_tile_q4_0_q8_0": [_sz, _p, _p, _p, _sz, _sz],
     "tcrv_cuda_host_repack_gemv_q4_0_q8_0": [_sz, _p, _p, _p, _sz],
     "tcrv_cuda_host_repack_gemv_q8_0_q8_0": [_sz, _p, _p, _p, _sz],
     "tcrv_cuda_host_repack_gemm_q4_0_q8_0": [_sz, _p, _p, _p, _sz, _sz, _sz],

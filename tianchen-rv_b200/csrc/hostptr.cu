@@ -618,6 +618,21 @@ int tcrv_cuda_host_gemm_q4_0_q8_0(size_t n, float *s, const uint8_t *vx, const u
   return host_matmul(false, n, s, vx, vy, by, nr, nc, bx, bs);
 }
 
+// tcrv_rvv.q4_0_q8_0_gemm_tile: one weight row against `cols` activation columns (a compile-time
+// 1..16 in the reference), every column folded like the block dot, in strict block order.
+int tcrv_cuda_host_gemm_tile_q4_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by,
+                                       size_t cols) {
+  if (cols < 1 || cols > 16)
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  return host_matmul(false, n, s, vx, vy, by, 1, cols, 0, cols, TCRV_CUDA_FLAG_STRICT_ORDER);
+}
+
+void tcrv_emitc_ggml_q4_0_q8_0_gemm_tile_kernel_ggml_q4_0_q8_0_gemm_tile(size_t n, float *s, const uint8_t *vx,
+                                                                         const uint8_t *vy, size_t by) {
+  // the reference fixture's variant: activation_cols = 4
+  must(tcrv_cuda_host_gemm_tile_q4_0_q8_0(n, s, vx, vy, by, 4), __func__);
+}
+
 int tcrv_cuda_host_gemm_q8_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by, size_t nr,
                                   size_t nc, size_t bx, size_t bs) {
   return host_matmul(true, n, s, vx, vy, by, nr, nc, bx, bs);

@@ -46,6 +46,14 @@ struct RouteEntry {
   std::string rooflineBound;             // "hbm", "tensor" or both
   std::string foldOrder;                 // fp32 fold convention ("" for non-dot kernels)
   std::string returnType = "void";       // C return type of the entry (soft_max returns its f64 sum)
+  // Integer attributes of the compute op that are compile-time parameters of the reference's
+  // kernel (e.g. the column count of a GEMM tile): each must lie in [lo, hi] and is passed to
+  // the host-pointer entry as a trailing literal argument.
+  struct ConstantArg {
+    std::string attr;
+    long long lo, hi;
+  };
+  std::vector<ConstantArg> constantArgs = {};
 };
 
 const std::vector<RouteEntry> &routeTable();

@@ -237,6 +237,21 @@ std::vector<RouteEntry> buildTable() {
                "tcrv_cuda_gemv_q4_0_q8_0|tcrv_cuda_gemm_q4_0_q8_0", "tcrv_cuda_host_gemm_q4_0_q8_0",
                "decode-gemv-bulk-copy(nc<=8)|prefill-gemm-tcgen05-i8(nc>8)", "hbm|tensor",
                "gemv: 32 lane partials + butterfly; gemm: ascending blocks per element; fused fold"});
+  {
+    // one weight row against M activation columns, M a compile-time attribute (1..16)
+    RouteEntry e{"tcrv_rvv.q4_0_q8_0_gemm_tile", withKind("ggml_q4_0_q8_0_gemm_tile", kQ4Q8Facts), "",
+                 {"tcrv_rvv.q4_0_q8_0_gemm_tile"},
+                 {"lhs-input-buffer", "rhs-input-buffer", "rhs-input-stride", "output-buffer", "runtime-element-count"},
+                 {{"runtime-element-count", "size_t"}, {"output-buffer", "float *"},
+                  {"lhs-input-buffer", "const uint8_t *"}, {"rhs-input-buffer", "const uint8_t *"},
+                  {"rhs-input-stride", "size_t"}},
+                 "q4_0_q8_0_gemm_tile", "cuda-ggml-q4_0-q8_0-gemm-tile-callable-c-abi.v1",
+                 "tcrv_cuda_gemv_q4_0_q8_0|tcrv_cuda_gemm_q4_0_q8_0", "tcrv_cuda_host_gemm_tile_q4_0_q8_0",
+                 "block-dot-strict-order(cols<=8)|prefill-gemm-tcgen05-i8(cols>8)", "hbm|tensor",
+                 "sumf = fma((float)sumi * d_x, d_y, sumf), ascending blocks, per column"};
+    e.constantArgs = {{"activation_cols", 1, 16}};
+    t.push_back(e);
+  }
   return t;
 }
 
@@ -265,6 +280,14 @@ std::string factMismatch(const Op &op, const RouteEntry &e) {
       if (a->str != f.str)
         return "'" + f.key + "' must be \"" + f.str + "\", got \"" + a->str + "\"";
     }
+  }
+  for (const RouteEntry::ConstantArg &c : e.constantArgs) {
+    long long v = 0;
+    if (!op.intAttr(c.attr, v))
+      return "missing integer attribute '" + c.attr + "'";
+    if (v < c.lo || v > c.hi)
+      return "'" + c.attr + "' must lie in " + std::to_string(c.lo) + ".." + std::to_string(c.hi) + ", got " +
+             std::to_string(v);
   }
   return {};
 }

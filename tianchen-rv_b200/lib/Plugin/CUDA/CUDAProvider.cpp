@@ -174,6 +174,15 @@ public:
       meta("tcrv_cuda.fp32_fold_order", route->foldOrder);
     if (route->returnType != "void")
       meta("tcrv_cuda.return_type", route->returnType);
+    if (!route->constantArgs.empty()) {
+      std::string consts;
+      for (const RouteEntry::ConstantArg &c : route->constantArgs) {
+        long long v = 0;
+        (void)compute->intAttr(c.attr, v);  // presence and range were checked when the route was selected
+        consts += (consts.empty() ? "" : ";") + c.attr + "=" + std::to_string(v);
+      }
+      meta("tcrv_cuda.constant_arguments", consts);
+    }
     meta("tcrv_cuda.target_arch", "sm_100a");
     meta("tcrv_cuda.required_capabilities", joinSymbols(r.variant->attr("requires")));
     meta("tcrv_cuda.required_header_declarations", "stddef.h,stdint.h");

@@ -156,10 +156,13 @@ std::string exportLaunchDescriptor(const VariantEmissionPlan &plan) {
 // host-pointer C ABI; what `tcrv-opt --tcrv-rvv-lower-to-emitc | mlir-translate --mlir-to-cpp`
 // yields in the reference (generated RVV C), here a call into the prebuilt library.
 std::string exportLaunchStubCpp(const VariantEmissionPlan &plan) {
-  std::string host;
-  for (const auto &kv : plan.metadata)
+  std::string host, constants;
+  for (const auto &kv : plan.metadata) {
     if (kv.first == "tcrv_cuda.host_pointer_symbol")
       host = kv.second;
+    if (kv.first == "tcrv_cuda.constant_arguments")
+      constants = kv.second;
+  }
   std::ostringstream os;
   os << "#include <stddef.h>\n#include <stdint.h>\n#include <stdio.h>\n#include <stdlib.h>\n";
   os << "#include \"tcrv_emitc_host.h\"\n";
@@ -173,6 +176,16 @@ std::string exportLaunchStubCpp(const VariantEmissionPlan &plan) {
   os << "  " << (returnsStatus ? "const int status = " : "") << host << "(";
   for (size_t i = 0; i < plan.abiParameters.size(); ++i)
     os << (i ? ", " : "") << plan.abiParameters[i].cName;
+  // compile-time parameters of the reference kernel ("name=value;..."): trailing literals
+  for (size_t b = 0; b < constants.size();) {
+    size_t e = constants.find(';', b);
+    if (e == std::string::npos)
+      e = constants.size();
+    const std::string item = constants.substr(b, e - b);
+    const size_t eq = item.find('=');
+    os << ", /*" << item.substr(0, eq) << "=*/" << item.substr(eq == std::string::npos ? item.size() : eq + 1);
+    b = e + 1;
+  }
   os << ");\n";
   if (returnsStatus) {
     os << "  if (status != 0) {\n    fprintf(stderr, \"" << plan.entrySymbol
