@@ -186,6 +186,16 @@ int tcrv_cuda_vec_dot_q4_1_q8_1(size_t n, float *s, const uint8_t *vx, const uin
 int tcrv_cuda_vec_dot_q5_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, tcrv_cuda_stream stream);
 int tcrv_cuda_vec_dot_q5_1_q8_1(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, tcrv_cuda_stream stream);
 
+/* The integer core of the Q4_0 x Q8_0 block dot as a kernel of its own (the reference's
+ * rvv_q4_0_q8_0_integer_core: test/Conversion/RVV/rvv-to-emitc-packed-i4-offset-binary-x-i8-product-reduce.mlir:24-37,
+ * op include/TianChenRV/Dialect/RVV/IR/RVVOps.td:3814-3871, decode lib/Conversion/RVV/RVVToEmitC.cpp:2524-2589):
+ *   out[0] = acc[0] + sum over j < n of v0(w[j]) * qlo[j] + v1(w[j]) * qhi[j]
+ * with t = w[j] ^ 0x88, v0 = (int8)(t << 4) >> 4, v1 = (int8)t >> 4; int32 arithmetic, exact.
+ * ABI order w, qlo, qhi, acc, out, n.  For a block_q4_0 (w = its 16 quant bytes, qlo / qhi the
+ * two halves of a block_q8_0, acc[0] = 0) this is the block's sumi. */
+int tcrv_cuda_q4_0_q8_0_integer_core(const int8_t *w, const int8_t *qlo, const int8_t *qhi, const int32_t *acc,
+                                     int32_t *out, size_t n, tcrv_cuda_stream stream);
+
 /* The reference's 16-row interleaved weight layout (block_q4_0x16, 288 bytes: 16 fp16 scales,
  * then quant byte `off` of the 16 source blocks side by side, xor 0x88), as a device repack:
  * `pack` replaces tcrv_rvv.pack_q4_0_to_q4_0x16 (lib/Conversion/RVV/RVVToEmitCBlockQuantLinear.cpp:

@@ -38,6 +38,8 @@ int tcrv_cuda_host_vec_silu_f32(size_t n, const float *x, float *y);
 int tcrv_cuda_host_vec_soft_max_f32(size_t n, float *y, const float *x, float max, double *sum);
 int tcrv_cuda_host_rope_norm_f32(size_t n_dims, const float *x, float *y, float theta_base, float theta_scale);
 int tcrv_cuda_host_pack_q4_0_to_q4_0x16(size_t nblocks, const uint8_t *src, uint8_t *dst);
+int tcrv_cuda_host_q4_0_q8_0_integer_core(const int8_t *w, const int8_t *qlo, const int8_t *qhi, const int32_t *acc,
+                                          int32_t *out, size_t n);
 /* sibling formats, one row per call */
 int tcrv_cuda_host_vec_dot_q4_1_q8_1(size_t n, float *s, const uint8_t *vx, const uint8_t *vy);
 int tcrv_cuda_host_vec_dot_q5_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy);
@@ -84,6 +86,10 @@ double tcrv_emitc_ggml_vec_soft_max_f32_kernel_ggml_vec_soft_max_f32(size_t n, f
 /* test/Conversion/RVV/rvv-to-emitc-ggml-rope-norm-f32.mlir:58 */
 void tcrv_emitc_ggml_rope_norm_f32_kernel_ggml_rope_norm_f32(size_t n_dims, const float *x, float *y, float theta_base,
                                                              float theta_scale);
+/* test/Conversion/RVV/rvv-to-emitc-packed-i4-offset-binary-x-i8-product-reduce.mlir:45 */
+void tcrv_emitc_rvv_q4_0_q8_0_integer_core_kernel_rvv_q4_0_q8_0_integer_core(const int8_t *w, const int8_t *qlo,
+                                                                             const int8_t *qhi, const int32_t *acc,
+                                                                             int32_t *out, size_t n);
 /* test/Conversion/RVV/rvv-to-emitc-q4-0-q8-0-gemm-tile.mlir:40 (the fixture's variant has
  * activation_cols = 4; other column counts get their entry from `--tcrv-cuda-launch-to-cpp`) */
 void tcrv_emitc_ggml_q4_0_q8_0_gemm_tile_kernel_ggml_q4_0_q8_0_gemm_tile(size_t n, float *s, const uint8_t *vx,

@@ -69,6 +69,7 @@ def _declare(L: ctypes.CDLL) -> None:
     L.tcrv_oracle_rope_thetas.argtypes = [_sz, ctypes.c_float, ctypes.c_float, _p]
     L.tcrv_oracle_pack_q4_0_to_q4_0x16.argtypes = [_sz, _p, _p]
     L.tcrv_oracle_unpack_q4_0x16_to_q4_0.argtypes = [_sz, _p, _p]
+    L.tcrv_oracle_q4_0_q8_0_integer_core.argtypes = [_p, _p, _p, _p, _p, _sz]
     L.tcrv_oracle_rows_to_q4_0x16.argtypes = [_sz, _sz, _p, _p]
     L.tcrv_oracle_rows_to_q8_0x16.argtypes = [_sz, _sz, _p, _p]
     L.tcrv_oracle_rows_to_q8_0x4.argtypes = [_sz, _sz, _p, _p]
@@ -263,6 +264,15 @@ def unpack_q4_0x16_to_q4_0(src: np.ndarray) -> np.ndarray:
     dst = np.empty_like(src)
     lib().tcrv_oracle_unpack_q4_0x16_to_q4_0(src.size // 288, _ptr(src), _ptr(dst))
     return dst
+
+
+def integer_core(w: np.ndarray, qlo: np.ndarray, qhi: np.ndarray, acc: int = 0) -> int:
+    """acc + sum of (low nibble - 8) * qlo + (high nibble - 8) * qhi over the weight bytes, int32."""
+    w, qlo, qhi = (np.ascontiguousarray(a).view(np.int8).reshape(-1) for a in (w, qlo, qhi))
+    assert w.size == qlo.size == qhi.size
+    seed, out = np.array([acc], dtype=np.int32), np.zeros(1, dtype=np.int32)
+    lib().tcrv_oracle_q4_0_q8_0_integer_core(_ptr(w), _ptr(qlo), _ptr(qhi), _ptr(seed), _ptr(out), w.size)
+    return int(out[0])
 
 
 def rows_to_q4_0x16(w: np.ndarray) -> np.ndarray:

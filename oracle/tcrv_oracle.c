@@ -824,3 +824,15 @@ void tcrv_oracle_repack_gemm_q4_0_q8_0(size_t n, float *s, const uint8_t *vx, co
           s[(y * 4 + c) * bs + x * 16 + r] = sumf[r];
       }
 }
+
+void tcrv_oracle_q4_0_q8_0_integer_core(const int8_t *w, const int8_t *qlo, const int8_t *qhi, const int32_t *acc,
+                                        int32_t *out, size_t n) {
+  uint32_t total = (uint32_t)acc[0];
+  for (size_t j = 0; j < n; ++j) {
+    int8_t v0, v1;
+    tcrv_oracle_decode_nibbles((uint8_t)w[j], &v0, &v1);
+    const int16_t pair = (int16_t)((int16_t)(v0 * qlo[j]) + (int16_t)(v1 * qhi[j]));
+    total += (uint32_t)(int32_t)pair;
+  }
+  out[0] = (int32_t)total;
+}

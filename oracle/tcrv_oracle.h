@@ -133,6 +133,13 @@ void tcrv_oracle_rope_thetas(size_t n_pairs, float theta_base, float theta_scale
 void tcrv_oracle_pack_q4_0_to_q4_0x16(size_t nblocks, const uint8_t *src, uint8_t *dst);
 void tcrv_oracle_unpack_q4_0x16_to_q4_0(size_t nblocks, const uint8_t *src, uint8_t *dst);
 
+/* The integer core as a kernel of its own (tcrv_rvv.packed_i4_offset_binary_x_i8_product +
+ * standalone_reduce; test/Conversion/RVV/rvv-to-emitc-packed-i4-offset-binary-x-i8-product-reduce.mlir:24-37):
+ * out[0] = acc[0] + sum over j < n of v0 * qlo[j] + v1 * qhi[j], the pair product formed in int16
+ * (vwmul + vwmacc), the sum in wrapping int32 (vwredsum). */
+void tcrv_oracle_q4_0_q8_0_integer_core(const int8_t *w, const int8_t *qlo, const int8_t *qhi, const int32_t *acc,
+                                        int32_t *out, size_t n);
+
 /* Layout builders for the consumers below, from plain row-major block rows (row r, block l at
  * (r*nb + l) * block bytes).  block_q4_0x16 of group g, block l = pack of the 16 blocks
  * (row 16g+j, block l); block_q8_0x16 (544 B): 16 fp16 scales, then qs[i*16 + r] = element i

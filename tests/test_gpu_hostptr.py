@@ -224,3 +224,27 @@ def test_host_gemm_tile_every_column_count(cuda, pkg, O):
     assert np.array_equal(s[:4].view(np.uint32), want[:4].view(np.uint32)) and np.all(s[4:] == -1.0)
     L.tcrv_cuda_host_release()
     pkg.check_device_errors()
+
+
+def test_integer_core_device_and_host_entries(cuda, pkg, O):
+    L = pkg.lib()
+    rng = np.random.default_rng(12)
+    for n in (0, 1, 16, 1000, 70001):
+        w = rng.integers(0, 256, n, dtype=np.uint8)
+        lo = rng.integers(-128, 128, n, dtype=np.int64).astype(np.int8)
+        hi = rng.integers(-128, 128, n, dtype=np.int64).astype(np.int8)
+        for seed in (0, -12345, 2**31 - 1):
+            want = O.integer_core(w, lo, hi, acc=seed)
+            acc, out = np.array([seed], dtype=np.int32), np.zeros(1, dtype=np.int32)
+            assert L.tcrv_cuda_host_q4_0_q8_0_integer_core(w.ctypes.data, lo.ctypes.data, hi.ctypes.data, acc.ctypes.data,
+                                                           out.ctypes.data, n) == 0
+            assert int(out[0]) == want, (n, seed)
+            wd, lod, hid = (cuda.from_numpy(a.view(np.int8).copy()).cuda() for a in (w, lo, hi))
+            accd, outd = cuda.from_numpy(acc).cuda(), cuda.zeros(1, dtype=cuda.int32, device="cuda")
+            assert L.tcrv_cuda_q4_0_q8_0_integer_core(wd.data_ptr() if n else None, lod.data_ptr() if n else None,
+                                                      hid.data_ptr() if n else None, accd.data_ptr(), outd.data_ptr(), n,
+                                                      None) == 0
+            assert int(outd.cpu()[0]) == want
+    assert L.tcrv_cuda_q4_0_q8_0_integer_core(None, None, None, None, None, 4, None) == -1
+    L.tcrv_cuda_host_release()
+    pkg.check_device_errors()

@@ -63,6 +63,9 @@ PROTOTYPES = {
                                     "size_t n_dims, const float *x, float *y, float theta_base, float theta_scale);",
     "cuda-pack-q4-0-to-q4-0x16.mlir": "void tcrv_emitc_ggml_pack_q4_0_to_q4_0x16_kernel_ggml_pack_q4_0_to_q4_0x16("
                                       "size_t nblocks, const uint8_t *src, uint8_t *dst);",
+    "cuda-q4-0-q8-0-integer-core.mlir":
+        "void tcrv_emitc_rvv_q4_0_q8_0_integer_core_kernel_rvv_q4_0_q8_0_integer_core("
+        "const int8_t *w, const int8_t *qlo, const int8_t *qhi, const int32_t *acc, int32_t *out, size_t n);",
     "cuda-q4-0-q8-0-gemm-tile.mlir": "void tcrv_emitc_ggml_q4_0_q8_0_gemm_tile_kernel_ggml_q4_0_q8_0_gemm_tile("
                                      "size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by);",
     "cuda-repack-gemv-q4-0-q8-0.mlir":

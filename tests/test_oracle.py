@@ -279,6 +279,22 @@ def test_q4_0x16_pack_layout_and_inverse(O):
     assert np.array_equal(O.unpack_q4_0x16_to_q4_0(dst), src)
 
 
+def test_integer_core_is_the_block_sum_on_a_seed(O):
+    # the integer-core kernel on a block_q4_0 / block_q8_0 pair gives that block's sumi; the
+    # seed is added; int32 wraps
+    w = O.quantize_q4_0(O.fill_normal(96, 21, 0.0, 0.02).reshape(1, 96))
+    x = O.quantize_q8_0(O.fill_normal(96, 22).reshape(1, 96))
+    sums = O.block_sums(w, x)[0, 0]
+    for b in range(3):
+        wq, lo, hi = w[0, 18 * b + 2:18 * b + 18], x[0, 34 * b + 2:34 * b + 18], x[0, 34 * b + 18:34 * b + 34]
+        assert O.integer_core(wq, lo, hi) == sums[b] and O.integer_core(wq, lo, hi, acc=-1000) == sums[b] - 1000
+    # hand case: bytes 0x00 (both nibbles -8) and 0xFF (both +7) against -128 / 127
+    assert O.integer_core(np.array([0x00, 0xFF], np.uint8), np.array([-128, 127], np.int8), np.array([127, -128], np.int8)) \
+        == (-8 * -128 + -8 * 127) + (7 * 127 + 7 * -128)
+    assert O.integer_core(np.array([0xFF], np.uint8), np.array([127], np.int8), np.array([127], np.int8), acc=2**31 - 1) \
+        == (2**31 - 1 + 2 * 7 * 127) - 2**32
+
+
 def test_x16_layout_builders_and_repacked_consumers(O):
     nc, k, nb = 32, 320, 10
     w4 = O.quantize_q4_0(O.fill_normal(nc * k, 11, 0.0, 0.02).reshape(nc, k))

@@ -61,6 +61,7 @@ ABI = {
     "tcrv_cuda_rope_apply_f32": [_sz, _p, _p, _p, _sz, _sz, _sz, _p],
     "tcrv_cuda_pack_q4_0_to_q4_0x16": [_sz, _p, _p, _p],
     "tcrv_cuda_unpack_q4_0x16_to_q4_0": [_sz, _p, _p, _p],
+    "tcrv_cuda_q4_0_q8_0_integer_core": [_p, _p, _p, _p, _p, _sz, _p],
     "tcrv_cuda_repack_gemv_parts": [_sz],
     "tcrv_cuda_repack_gemv_q4_0_q8_0": [_sz, _p, _p, _p, _sz, ctypes.c_uint, _p],
     "tcrv_cuda_repack_gemv_q8_0_q8_0": [_sz, _p, _p, _p, _sz, ctypes.c_uint, _p],
@@ -101,6 +102,7 @@ ABI.update({
     "tcrv_cuda_host_vec_dot_q5_0_q8_0": [_sz, _p, _p, _p],
     "tcrv_cuda_host_vec_dot_q5_1_q8_1": [_sz, _p, _p, _p],
     "tcrv_cuda_host_gemm_tile_q4_0_q8_0": [_sz, _p, _p, _p, _sz, _sz],
+    "tcrv_cuda_host_q4_0_q8_0_integer_core": [_p, _p, _p, _p, _p, _sz],
     "tcrv_cuda_host_repack_gemv_q4_0_q8_0": [_sz, _p, _p, _p, _sz],
     "tcrv_cuda_host_repack_gemv_q8_0_q8_0": [_sz, _p, _p, _p, _sz],
     "tcrv_cuda_host_repack_gemm_q4_0_q8_0": [_sz, _p, _p, _p, _sz, _sz, _sz],

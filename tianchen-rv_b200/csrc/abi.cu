@@ -472,6 +472,13 @@ int tcrv_cuda_repack_gemm_q4_0_q8_0(size_t n, float *s, const uint8_t *vx, const
                                                   stream);
 }
 
+int tcrv_cuda_q4_0_q8_0_integer_core(const int8_t *w, const int8_t *qlo, const int8_t *qhi, const int32_t *acc,
+                                     int32_t *out, size_t n, tcrv_cuda_stream stream) {
+  if (!acc || !out || (n != 0 && (!w || !qlo || !qhi)))
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  return launch_q4_0_q8_0_integer_core(w, qlo, qhi, acc, out, n, as_stream(stream));
+}
+
 int tcrv_cuda_peer_alloc(size_t bytes, void **ptr) {
   if (!ptr || bytes == 0)
     return TCRV_CUDA_ERR_INVALID_ARGUMENT;

@@ -618,6 +618,41 @@ int tcrv_cuda_host_gemm_q4_0_q8_0(size_t n, float *s, const uint8_t *vx, const u
   return host_matmul(false, n, s, vx, vy, by, nr, nc, bx, bs);
 }
 
+int tcrv_cuda_host_q4_0_q8_0_integer_core(const int8_t *w, const int8_t *qlo, const int8_t *qhi, const int32_t *acc,
+                                          int32_t *out, size_t n) {
+  if (!acc || !out || (n != 0 && (!w || !qlo || !qhi)))
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  HostContext &c = ctx();
+  std::lock_guard<std::mutex> lock(c.mu);
+  int st = ensure_stream(c);
+  if (st == TCRV_CUDA_OK)
+    st = arena_reserve(c, 3 * up256(n) + 2 * 256);
+  if (st != TCRV_CUDA_OK)
+    return st;
+  int8_t *dw = reinterpret_cast<int8_t *>(arena_take(c, n));
+  int8_t *dlo = reinterpret_cast<int8_t *>(arena_take(c, n));
+  int8_t *dhi = reinterpret_cast<int8_t *>(arena_take(c, n));
+  int32_t *dacc = reinterpret_cast<int32_t *>(arena_take(c, sizeof(int32_t)));
+  int32_t *dout = reinterpret_cast<int32_t *>(arena_take(c, sizeof(int32_t)));
+  if (n != 0) {
+    TCRV_CUDA_TRY(cudaMemcpyAsync(dw, w, n, cudaMemcpyHostToDevice, c.stream));
+    TCRV_CUDA_TRY(cudaMemcpyAsync(dlo, qlo, n, cudaMemcpyHostToDevice, c.stream));
+    TCRV_CUDA_TRY(cudaMemcpyAsync(dhi, qhi, n, cudaMemcpyHostToDevice, c.stream));
+  }
+  TCRV_CUDA_TRY(cudaMemcpyAsync(dacc, acc, sizeof(int32_t), cudaMemcpyHostToDevice, c.stream));
+  st = launch_q4_0_q8_0_integer_core(dw, dlo, dhi, dacc, dout, n, c.stream);
+  if (st != TCRV_CUDA_OK)
+    return st;
+  TCRV_CUDA_TRY(cudaMemcpyAsync(out, dout, sizeof(int32_t), cudaMemcpyDeviceToHost, c.stream));
+  return finish(c);
+}
+
+void tcrv_emitc_rvv_q4_0_q8_0_integer_core_kernel_rvv_q4_0_q8_0_integer_core(const int8_t *w, const int8_t *qlo,
+                                                                             const int8_t *qhi, const int32_t *acc,
+                                                                             int32_t *out, size_t n) {
+  must(tcrv_cuda_host_q4_0_q8_0_integer_core(w, qlo, qhi, acc, out, n), __func__);
+}
+
 // tcrv_rvv.q4_0_q8_0_gemm_tile: one weight row against `cols` activation columns (a compile-time
 // 1..16 in the reference), every column folded like the block dot, in strict block order.
 int tcrv_cuda_host_gemm_tile_q4_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by,

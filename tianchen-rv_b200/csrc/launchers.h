@@ -30,6 +30,8 @@ int launch_repack_gemv_q8_0_q8_0(size_t n, float *s, const uint8_t *vx, const ui
                                  cudaStream_t stream);
 // sibling block formats (siblings.cu): format 1 = Q4_1 x Q8_1, 2 = Q5_0 x Q8_0, 3 = Q5_1 x Q8_1;
 // `sums` != null selects the integer stage (sumi[row][col][block]) instead of the fp32 rows.
+int launch_q4_0_q8_0_integer_core(const int8_t *w, const int8_t *qlo, const int8_t *qhi, const int32_t *acc,
+                                  int32_t *out, size_t n, cudaStream_t stream);
 int sibling_block_bytes(int format, size_t *weight, size_t *activation);
 int launch_sibling_dot(int format, size_t n, float *s, int32_t *sums, const uint8_t *vx, const uint8_t *vy, size_t by,
                        size_t nr, size_t nc, size_t bx, size_t bs, cudaStream_t stream);

@@ -142,7 +142,42 @@ int launch_one(size_t n, float *s, int32_t *sums, const uint8_t *vx, const uint8
   return TCRV_CUDA_OK;
 }
 
+// out[0] = acc[0] + sum over the n weight bytes of v0 * qlo + v1 * qhi, v0 / v1 the low / high
+// nibble of (byte ^ 0x88) sign-extended: the reference's integer-core kernel.  int32 wraps, so
+// the order of the additions does not matter; one CTA.
+__global__ void __launch_bounds__(256) integer_core_kernel(const int8_t *__restrict__ w, const int8_t *__restrict__ qlo,
+                                                           const int8_t *__restrict__ qhi,
+                                                           const int32_t *__restrict__ acc, int32_t *__restrict__ out,
+                                                           size_t n) {
+  __shared__ uint32_t partial[8];
+  uint32_t sum = 0;
+  for (size_t j = threadIdx.x; j < n; j += blockDim.x) {
+    const uint8_t t = static_cast<uint8_t>(w[j]) ^ 0x88u;
+    const int v0 = static_cast<int8_t>(static_cast<uint8_t>(t << 4)) >> 4, v1 = static_cast<int8_t>(t) >> 4;
+    sum += static_cast<uint32_t>(v0 * qlo[j] + v1 * qhi[j]);
+  }
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1)
+    sum += __shfl_xor_sync(0xffffffffu, sum, off);
+  if ((threadIdx.x & 31) == 0)
+    partial[threadIdx.x >> 5] = sum;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    uint32_t total = static_cast<uint32_t>(acc[0]);
+    for (int i = 0; i < 8; ++i)
+      total += partial[i];
+    out[0] = static_cast<int32_t>(total);
+  }
+}
+
 }  // namespace
+
+int launch_q4_0_q8_0_integer_core(const int8_t *w, const int8_t *qlo, const int8_t *qhi, const int32_t *acc,
+                                  int32_t *out, size_t n, cudaStream_t stream) {
+  integer_core_kernel<<<1, 256, 0, stream>>>(w, qlo, qhi, acc, out, n);
+  TCRV_CUDA_TRY(cudaGetLastError());
+  return TCRV_CUDA_OK;
+}
 
 int sibling_block_bytes(int format, size_t *weight, size_t *activation) {
   switch (format) {

@@ -237,6 +237,22 @@ std::vector<RouteEntry> buildTable() {
                "tcrv_cuda_gemv_q4_0_q8_0|tcrv_cuda_gemm_q4_0_q8_0", "tcrv_cuda_host_gemm_q4_0_q8_0",
                "decode-gemv-bulk-copy(nc<=8)|prefill-gemm-tcgen05-i8(nc>8)", "hbm|tensor",
                "gemv: 32 lane partials + butterfly; gemm: ascending blocks per element; fused fold"});
+  // the integer core of the Q4_0 x Q8_0 block dot as a kernel of its own: offset-binary nibble
+  // decode, products against the two activation halves, widening reduction onto a seed
+  // (test/Conversion/RVV/rvv-to-emitc-packed-i4-offset-binary-x-i8-product-reduce.mlir)
+  t.push_back({"tcrv_rvv.packed_i4_offset_binary_x_i8_product",
+               withKind("signed_packed_i4_offset_binary_x_i8_product",
+                        {{"product_relation", false, "offset-binary-i4mf4-x-i8mf4x2-to-i16mf2", 0}}),
+               "",
+               {"tcrv_rvv.load", "tcrv_rvv.load", "tcrv_rvv.load", "tcrv_rvv.packed_i4_offset_binary_x_i8_product",
+                "tcrv_rvv.standalone_reduce", "tcrv_rvv.store"},
+               {},
+               {{"lhs-input-buffer", "const int8_t *"}, {"rhs-input-buffer", "const int8_t *"},
+                {"rhs-input-buffer", "const int8_t *"}, {"accumulator-input-buffer", "const int32_t *"},
+                {"output-buffer", "int32_t *"}, {"runtime-element-count", "size_t"}},
+               "q4_0_q8_0_integer_core", "cuda-q4_0-q8_0-integer-core-callable-c-abi.v1",
+               "tcrv_cuda_q4_0_q8_0_integer_core", "tcrv_cuda_host_q4_0_q8_0_integer_core", "single-cta-reduction",
+               "latency", ""});
   {
     // one weight row against M activation columns, M a compile-time attribute (1..16)
     RouteEntry e{"tcrv_rvv.q4_0_q8_0_gemm_tile", withKind("ggml_q4_0_q8_0_gemm_tile", kQ4Q8Facts), "",

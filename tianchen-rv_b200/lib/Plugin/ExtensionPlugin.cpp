@@ -108,7 +108,7 @@ static bool cTypeAllowed(const std::string &role, const std::string &cType) {
                                                      "const double *"};
   static const std::set<std::string> outputBuffers = {"int8_t *",  "uint8_t *", "int16_t *", "int32_t *",
                                                       "int64_t *", "float *",   "double *"};
-  if (role == "lhs-input-buffer" || role == "rhs-input-buffer")
+  if (role == "lhs-input-buffer" || role == "rhs-input-buffer" || role == "accumulator-input-buffer")
     return inputBuffers.count(cType) != 0;
   if (role == "output-buffer")
     return outputBuffers.count(cType) != 0;
