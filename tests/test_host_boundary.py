@@ -141,6 +141,21 @@ def test_add_plan_records_role_facts_and_abi_order():
     assert m.returncode == 0 and "launcher=tcrv_cuda_add_f32" in m.stdout and 'role="dispatch case"' in m.stdout
 
 
+@pytest.mark.parametrize("extra", [
+    'integer_core_lmul = "m1"',
+    'integer_core_lmul = "m1", multi_block_factor = 2 : i64, strip_elision = "robust"',
+    'integer_core_lmul = "m1", multi_block_factor = 4 : i64, strip_elision = "elided"',
+])
+def test_block_dot_schedule_attributes_of_the_rvv_variants_are_accepted(extra):
+    # the reference's -m1 / -mb2-robust / -mb4-elided fixtures differ from the base block dot only in
+    # attributes that choose HOW the RVV kernel is scheduled; they do not select another kernel here
+    src = fixture("cuda-q4-0-q8-0-block-dot.mlir")
+    anchor = "activation_high_byte_offset = 16 : i64"
+    assert anchor in src
+    p = plan(src.replace(anchor, anchor + ", " + extra))
+    assert 'status = "supported"' in p and 'runtime_abi_name = "cuda-ggml-q4_0-q8_0-block-dot-callable-c-abi.v1"' in p
+
+
 def test_gemm_tile_column_count_is_a_checked_compile_time_argument():
     src = fixture("cuda-q4-0-q8-0-gemm-tile.mlir")
     p = plan(src)
