@@ -220,7 +220,8 @@ int tcrv_cuda_unpack_q4_0x16_to_q4_0(size_t nblocks, const uint8_t *src, uint8_t
  * tcrv_cuda_repack_gemv_parts(n) contiguous ranges; inside a range chain c (0..7) folds
  * blocks 8*step + c in ascending order from 0.0f, the chains are added as
  * ((c0+c4) + (c2+c6)) + ((c1+c5) + (c3+c7)), and the ranges in ascending order.  The order
- * depends on n alone (not on nc or the GPU).  vx must be 16-byte aligned (bulk copies).
+ * depends on n alone (not on nc or the GPU).  A weight pointer that is not 16-byte aligned takes
+ * a slow byte-wise kernel with the same order (the fast path streams with 16-byte bulk copies).
  * `flags`: 0, or tuning overrides that leave the result unchanged (bits 8..11 ring depth,
  * bits 12..15 warps per row group, bits 16..19 copies in flight). */
 size_t tcrv_cuda_repack_gemv_parts(size_t n);

@@ -56,6 +56,19 @@ def test_repack_gemv_work_split_does_not_change_the_result(cuda, pkg, O, q8w):
     pkg.check_device_errors()
 
 
+@pytest.mark.parametrize("q8w", [False, True], ids=["q4_0x16", "q8_0x16"])
+def test_repack_gemv_unaligned_weights_take_the_byte_path_with_the_same_bits(cuda, pkg, O, q8w):
+    for nc, k in ((48, 4096), (160, 1312), (16, 32)):
+        wx, x = make_case(O, nc, k, q8w, 950 + nc)
+        want = O.repack_gemv(wx, x[0], nc, q8_weights=q8w, parts=pkg.repack_gemv_parts(k))
+        buf = cuda.zeros(wx.size + 16, dtype=cuda.uint8, device="cuda")
+        for shift in (4, 1):
+            buf[shift:shift + wx.size] = dev(cuda, wx)
+            got = pkg.repack_gemv(buf[shift:shift + wx.size], dev(cuda, x[0]), nc, q8_weights=q8w).cpu().numpy()
+            assert np.array_equal(bits(got), bits(want)), (nc, k, shift)
+    pkg.check_device_errors()
+
+
 def test_repack_gemv_parts_rule(pkg):
     # a function of K alone: every range keeps at least two 8-block steps
     assert [pkg.repack_gemv_parts(k) for k in (32, 256, 512, 1024, 2048, 4096, 11008)] == [1, 1, 1, 2, 4, 8, 8]
@@ -95,7 +108,7 @@ def test_repack_gemv_argument_checks(cuda, pkg):
     assert L.tcrv_cuda_repack_gemv_q4_0_q8_0(*ok) == 0
     assert L.tcrv_cuda_repack_gemv_q4_0_q8_0(250, *ok[1:]) == -1          # n not a multiple of 32
     assert L.tcrv_cuda_repack_gemv_q4_0_q8_0(256, ok[1], ok[2], ok[3], 15, 0, None) == -1  # nc % 16
-    assert L.tcrv_cuda_repack_gemv_q4_0_q8_0(256, ok[1], ok[2] + 4, ok[3], 16, 0, None) == -1  # vx alignment
+    assert L.tcrv_cuda_repack_gemv_q4_0_q8_0(256, ok[1], ok[2] + 4, ok[3], 16, 0, None) == 0   # byte-wise path
     assert L.tcrv_cuda_repack_gemv_q4_0_q8_0(256, None, ok[2], ok[3], 16, 0, None) == -1
     assert L.tcrv_cuda_repack_gemv_q8_0_q8_0(256, ok[1], None, ok[3], 16, 0, None) == -1
     assert L.tcrv_cuda_repack_gemv_q4_0_q8_0(256, None, None, None, 0, 0, None) == 0        # no rows

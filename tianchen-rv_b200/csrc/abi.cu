@@ -390,7 +390,7 @@ int check_repack_gemv_args(size_t n, const float *s, const uint8_t *vx, const ui
     return TCRV_CUDA_ERR_INVALID_ARGUMENT;
   if (nc != 0 && (!s || (reinterpret_cast<uintptr_t>(s) & 3u) != 0))
     return TCRV_CUDA_ERR_INVALID_ARGUMENT;
-  if (nc != 0 && n != 0 && (!vx || !vy || (reinterpret_cast<uintptr_t>(vx) & 15u) != 0))
+  if (nc != 0 && n != 0 && (!vx || !vy))
     return TCRV_CUDA_ERR_INVALID_ARGUMENT;
   return TCRV_CUDA_OK;
 }

@@ -285,6 +285,67 @@ __global__ void __launch_bounds__(kRpThreads, 1) repack_gemv_kernel(const Repack
   }
 }
 
+// The same sums in the same order without bulk copies or shared memory, for weight pointers
+// that are not 16-byte aligned and for rows too long for the staged activation column: one
+// warp per row group, every byte read straight from global memory.  Slow, and only there so
+// that no argument the reference's kernel accepts is refused.
+template <bool kQ8W>
+__global__ void __launch_bounds__(256) repack_gemv_generic_kernel(const uint8_t *__restrict__ vx,
+                                                                  const uint8_t *__restrict__ vy,
+                                                                  float *__restrict__ s, uint32_t nb, uint32_t groups,
+                                                                  uint32_t parts) {
+  using F = X16<kQ8W>;
+  const int lane = threadIdx.x & 31;
+  const uint32_t b = lane >> 2, rq = lane & 3;
+  const uint32_t steps = (nb + kRpStepBlocks - 1) / kRpStepBlocks;
+  const uint32_t warps = (gridDim.x * blockDim.x) >> 5;
+  for (uint32_t g = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; g < groups; g += warps) {
+    float tot[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    for (uint32_t j = 0; j < parts; ++j) {
+      float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+      for (uint32_t st = j * steps / parts; st < (j + 1) * steps / parts; ++st) {
+        const uint32_t blk = st * kRpStepBlocks + b;
+        if (blk >= nb)
+          continue;
+        const uint8_t *bl = vx + (static_cast<size_t>(g) * nb + blk) * F::kBlockBytes;
+        const uint8_t *al = vy + static_cast<size_t>(blk) * kQ8Block;
+        const float da = half_bits_to_float(load_u16(al));
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          const uint32_t row = 4 * rq + r;
+          int sumi = 0;
+          if constexpr (kQ8W) {
+            for (int i = 0; i < 32; ++i)
+              sumi += static_cast<int8_t>(bl[32 + 16 * i + row]) * static_cast<int8_t>(al[2 + i]);
+          } else {
+            for (int i = 0; i < 16; ++i) {
+              const uint8_t t = bl[32 + 16 * i + row];  // two's-complement nibbles (the xor is in the layout)
+              const int v0 = static_cast<int8_t>(static_cast<uint8_t>(t << 4)) >> 4, v1 = static_cast<int8_t>(t) >> 4;
+              sumi += v0 * static_cast<int8_t>(al[2 + i]) + v1 * static_cast<int8_t>(al[18 + i]);
+            }
+          }
+          const float dw = half_bits_to_float(load_u16(bl + 2 * row));
+          acc[r] = __fmaf_rn(__int2float_rn(sumi), __fmul_rn(dw, da), acc[r]);
+        }
+      }
+#pragma unroll
+      for (int off = 16; off >= 4; off >>= 1) {
+#pragma unroll
+        for (int r = 0; r < 4; ++r)
+          acc[r] = __fadd_rn(acc[r], __shfl_xor_sync(0xffffffffu, acc[r], off));
+      }
+#pragma unroll
+      for (int r = 0; r < 4; ++r)
+        tot[r] = j == 0 ? acc[r] : __fadd_rn(tot[r], acc[r]);
+    }
+    if (b == 0) {
+#pragma unroll
+      for (int r = 0; r < 4; ++r)
+        s[static_cast<size_t>(g) * 16 + 4 * rq + r] = tot[r];
+    }
+  }
+}
+
 template <bool kQ8W>
 int launch_repack_gemv_impl(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t nc, unsigned flags,
                             cudaStream_t stream) {
@@ -312,8 +373,15 @@ int launch_repack_gemv_impl(size_t n, float *s, const uint8_t *vx, const uint8_t
     return TCRV_CUDA_ERR_INVALID_ARGUMENT;
   args.coop = coop;
   const size_t fixed = kRpFixedBytes + rp_x_bytes(args.nb);
-  if (fixed + 2 * static_cast<size_t>(kRpWarps) * F::kSlotBytes > kRpSmemLimit)
-    return TCRV_CUDA_ERR_UNSUPPORTED;  // K beyond ~100k elements: the activation column no longer fits
+  if ((reinterpret_cast<uintptr_t>(vx) & 15u) != 0 ||
+      fixed + 2 * static_cast<size_t>(kRpWarps) * F::kSlotBytes > kRpSmemLimit) {
+    // unaligned weights, or K beyond ~100k elements (the activation column no longer fits)
+    const size_t want = (groups + 7) / 8, cap = static_cast<size_t>(sm_count()) * 8;
+    repack_gemv_generic_kernel<kQ8W><<<static_cast<int>(want < cap ? want : cap), 256, 0, stream>>>(
+        vx, vy, s, args.nb, args.groups, args.parts);
+    TCRV_CUDA_TRY(cudaGetLastError());
+    return TCRV_CUDA_OK;
+  }
   size_t depth = (kRpSmemLimit - fixed) / (static_cast<size_t>(kRpWarps) * F::kSlotBytes);
   depth = depth > kRpMaxDepth ? kRpMaxDepth : depth;
   if (const unsigned forced = (flags >> 8) & 0xfu)
