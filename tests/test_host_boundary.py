@@ -234,6 +234,18 @@ NEGATIVES = [
     ("cuda-q4-0-q8-0-gemm.mlir", "tcrv_rvv.q4_0_q8_0_gemm %vx, %vy", "tcrv_rvv.q4_0_q8_0_gemm %vy, %vx", "operand #0 must be the lhs-input-buffer"),
     ("cuda-q8-0-q8-0-block-dot.mlir", "weight_block_stride = 34", "weight_block_stride = 18", "'weight_block_stride' must be 34"),
     ("cuda-quantize-row-q8-0.mlir", "block_stride = 34", "block_stride = 36", "'block_stride' must be 34"),
+    # the interleaved layouts are pinned fact by fact, as the reference's verifiers pin them
+    ("cuda-repack-gemv-q4-0-q8-0.mlir", "weight_block_stride = 288", "weight_block_stride = 144", "'weight_block_stride' must be 288"),
+    ("cuda-repack-gemv-q4-0-q8-0.mlir", "weight_quant_byte_offset = 32", "weight_quant_byte_offset = 2", "'weight_quant_byte_offset' must be 32"),
+    ("cuda-repack-gemv-q8-0-q8-0.mlir", "weight_block_stride = 544", "weight_block_stride = 288", "'weight_block_stride' must be 544"),
+    ("cuda-repack-gemv-q8-0-q8-0.mlir", "weight_interleave = 16", "weight_interleave = 8", "'weight_interleave' must be 16"),
+    ("cuda-repack-gemm-q4-0-q8-0.mlir", "activation_block_stride = 136", "activation_block_stride = 34", "'activation_block_stride' must be 136"),
+    ("cuda-repack-gemm-q4-0-q8-0.mlir", "activation_interleave = 4", "activation_interleave = 8", "'activation_interleave' must be 4"),
+    ("cuda-repack-gemm-q4-0-q8-0.mlir", 'role = "output-stride"', 'role = "lhs-input-stride"', "must be {output-stride, size_t}"),
+    ("cuda-q4-0-q8-0-integer-core.mlir", 'product_relation = "offset-binary-i4mf4-x-i8mf4x2-to-i16mf2"',
+     'product_relation = "twos-complement"', "'product_relation' must be"),
+    ("cuda-q4-0-q8-0-integer-core.mlir", 'c_type = "const int32_t *"', 'c_type = "const float *"',
+     "must be {accumulator-input-buffer, const int32_t *}"),
     ("cuda-q4-0-q8-0-block-dot.mlir", "tcrv_rvv.q4_0_q8_0_block_dot", "tcrv_rvv.iq4_nl_q8_0_block_dot", "no kernel for op"),
 ]
 
