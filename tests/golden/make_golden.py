@@ -55,6 +55,8 @@ def build(O):
     out["repack_gemv_q4_kernel"] = O.repack_gemv(wx4, x8[0], c_nr(), parts=1)
     out["repack_gemv_q8_kernel"] = O.repack_gemv(wx8, x8[0], c_nr(), q8_weights=True, parts=1)
     out["repack_gemm_q4"] = O.repack_gemm(wx4, xx4, CASES["k"], 4, c_nr())
+    # the integer core on the first block of row 0 / column 0, seeded
+    out["integer_core"] = np.array([O.integer_core(w4[0, 2:18], x8[0, 2:18], x8[0, 18:34], acc=-77)], dtype=np.int32)
     for fmt in (1, 2, 3):
         w, x = sibling_data.make(fmt, 6, 2, 16, 9200 + fmt)
         out[f"sibling{fmt}"] = O.sibling_dot_rows(fmt, w, x)

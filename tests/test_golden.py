@@ -64,6 +64,11 @@ def test_kernels_reproduce_the_fixture(cuda, pkg, O, golden):
     got["repack_gemv_q4_kernel"] = pkg.repack_gemv(wx4, x8[0], nr)
     got["repack_gemv_q8_kernel"] = pkg.repack_gemv(wx8, x8[0], nr, q8_weights=True)
     got["repack_gemm_q4"] = pkg.repack_gemm(wx4, xx4, k, 4, nr)
+    seed, core = dev(np.array([-77], dtype=np.int32)), cuda.zeros(1, dtype=cuda.int32, device="cuda")
+    w0, x0 = w4[0].contiguous(), x8[0].contiguous()
+    assert pkg.lib().tcrv_cuda_q4_0_q8_0_integer_core(w0.data_ptr() + 2, x0.data_ptr() + 2, x0.data_ptr() + 18,
+                                                      seed.data_ptr(), core.data_ptr(), 16, None) == 0
+    got["integer_core"] = core
     # five columns, K = 512: the tensor-core GEMV serves the unflagged call (order 2)
     assert pkg.gemv_fold_order(w4, x8) == 2 and pkg.gemv_fold_order(w4, x8, flags=0x1000) == 1
     pkg.check_device_errors()
