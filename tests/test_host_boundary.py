@@ -312,6 +312,57 @@ def test_launch_stub_defines_the_reference_named_entry():
     assert c.returncode == 0, c.stderr
 
 
+def test_target_artifact_bundle_export_writes_files_and_index(tmp_path):
+    # tcrv-export-target-artifact-bundle (reference driver, tools/tcrv-translate/tcrv-translate.cpp:40-48,
+    # 469-474): one file per artifact plus the index, two lines on stdout
+    p = plan(fixture("cuda-q4-0-q8-0-gemm.mlir"))
+    out = tmp_path / "bundle"
+    out.mkdir()
+    r = run([TRANSLATE, "-", "--tcrv-export-target-artifact-bundle", f"--tcrv-target-artifact-bundle-output-dir={out}"], p)
+    assert r.returncode == 0, r.stderr
+    assert r.stdout == ('tianchenrv.target_artifact_bundle_export: complete\n'
+                        'index_file: "tianchenrv-target-artifact-bundle.index"\n')
+    names = sorted(os.listdir(out))
+    obj = "artifact-0-cuda-sm100a-launch-descriptor-cuda-sm100a-typed-body-launch-route-family.json"
+    hdr = "artifact-1-c-header-cuda-sm100a-typed-body-launch-route-family.h"
+    assert names == [obj, hdr, "tianchenrv-target-artifact-bundle.index"]
+    # the files are what the single-artifact exports print
+    assert (out / hdr).read_text() == header(p).stdout
+    assert (out / obj).read_text() == run([TRANSLATE, "-", "--tcrv-export-target-artifact"], p).stdout
+    desc = json.loads((out / obj).read_text())
+    assert "tcrv_cuda_gemm_q4_0_q8_0" in desc["launcher_symbol"].split("|")
+    index = (out / "tianchenrv-target-artifact-bundle.index").read_text()
+    for line in ["tianchenrv.target_artifact_bundle.version: 1", 'bundle_status: "complete"', "artifact_count: 2",
+                 "artifact[0]:", f'  file_name: "{obj}"', '  component_role: "object"', "artifact[1]:",
+                 f'  file_name: "{hdr}"', '  component_role: "header"',
+                 "  selected_variant: @ggml_q4_0_q8_0_gemm", '  route: "cuda-sm100a-typed-body-launch-route-family"',
+                 '  owner: "cuda-plugin"', "  runtime_abi_parameter_count: 9", '    c_name: "vx"',
+                 '    ownership: "target-export-abi-owned"']:
+        assert line in index.splitlines(), line
+
+
+def test_target_artifact_bundle_export_fails_closed(tmp_path):
+    p = plan(fixture("cuda-add-f32.mlir"))
+    flag = "--tcrv-export-target-artifact-bundle"
+    r = run([TRANSLATE, "-", flag], p)
+    assert r.returncode != 0 and "--tcrv-target-artifact-bundle-output-dir is required" in r.stderr
+    r = run([TRANSLATE, "-", flag, f"--tcrv-target-artifact-bundle-output-dir={tmp_path / 'missing'}"], p)
+    assert r.returncode != 0 and "does not exist" in r.stderr
+    # a tampered plan reaches no file
+    out = tmp_path / "b"
+    out.mkdir()
+    bad = p.replace("tcrv_cuda.element_type=f32", "tcrv_cuda.element_type=f16", 1)
+    r = run([TRANSLATE, "-", flag, f"--tcrv-target-artifact-bundle-output-dir={out}"], bad)
+    assert r.returncode != 0 and "stale emission plan" in r.stderr and os.listdir(out) == []
+    # without providers there is no bundle, no exporter and no translate route
+    r = run([TRANSLATE, "-", "--tcrv-disable-builtin-plugins", flag, f"--tcrv-target-artifact-bundle-output-dir={out}"], p)
+    assert r.returncode != 0 and 'no provider named "cuda-plugin"' in r.stderr and os.listdir(out) == []
+    r = run([TRANSLATE, "-", "--tcrv-disable-builtin-plugins", "--tcrv-cuda-launch-to-cpp"], p)
+    assert r.returncode != 0 and "unknown option '--tcrv-cuda-launch-to-cpp'" in r.stderr
+    r = run([TRANSLATE, "-", "--tcrv-export-target-artifact", "--tcrv-export-emission-manifest"], p)
+    assert r.returncode != 0 and "more than one translation" in r.stderr
+
+
 # ---- abstract contraction request (tcrv_rvv.quant_contraction) -> provider picks the kernel
 
 LOWER = "--tcrv-cuda-lower-quant-contraction"

@@ -8,6 +8,8 @@
 // types, capability records -- never by kernel or variant names.
 #pragma once
 
+#include <functional>
+#include <iosfwd>
 #include <memory>
 #include <string>
 #include <utility>
@@ -74,6 +76,77 @@ struct VariantEmissionPlan {
   std::string diagnostic;          // set when !supported
 };
 
+class ExtensionPluginRegistry;
+
+// ---- target side of a provider -----------------------------------------------------------
+//
+// One exporter of a provider's target support: turns an emission plan of route `routeID` into
+// one artifact of `artifactKind` (the reference's exporter registry by route id,
+// lib/Target/RVV/RVVTargetSupportBundle.cpp:1738-1806).
+struct TargetArtifactExporter {
+  std::string routeID;
+  std::string artifactKind;
+  std::string componentRole;  // "header", "object" or "artifact": how a bundle index lists the file
+  std::string fileExtension;  // including the dot
+  std::function<std::string(const VariantEmissionPlan &)> exportFn;
+};
+
+// What a provider contributes to the target side, filled by
+// ExtensionPlugin::configureTargetSupportExtensionBundle (the reference's ExtensionBundle,
+// include/TianChenRV/Plugin/ExtensionBundle.h:26-61).
+class ExtensionBundle {
+public:
+  ExtensionBundle() = default;
+  ExtensionBundle(std::string bundleID, std::string pluginName)
+      : bundleID(std::move(bundleID)), pluginName(std::move(pluginName)) {}
+  const std::string &getBundleID() const { return bundleID; }
+  const std::string &getPluginName() const { return pluginName; }
+  const std::vector<std::string> &getRequiredDialectNames() const { return requiredDialectNames; }
+  const std::vector<std::string> &getLoweringBoundaryOps() const { return loweringBoundaryOps; }
+  const std::vector<TargetArtifactExporter> &getTargetArtifactExporters() const { return exporters; }
+  void addRequiredDialectName(const std::string &name) { requiredDialectNames.push_back(name); }
+  void addLoweringBoundaryOp(const std::string &name) { loweringBoundaryOps.push_back(name); }
+  // Fails on a second exporter for the same (route, component role).
+  Error addTargetArtifactExporter(TargetArtifactExporter exporter);
+  const TargetArtifactExporter *lookupExporter(const std::string &routeID, const std::string &componentRole) const;
+
+private:
+  std::string bundleID, pluginName;
+  std::vector<std::string> requiredDialectNames, loweringBoundaryOps;
+  std::vector<TargetArtifactExporter> exporters;
+};
+
+class ExtensionBundleRegistry {
+public:
+  Error registerBundle(ExtensionBundle bundle);
+  const ExtensionBundle *lookupPluginBundle(const std::string &pluginName) const;
+  const std::vector<ExtensionBundle> &getBundles() const { return bundles; }
+
+private:
+  std::vector<ExtensionBundle> bundles;
+};
+
+// A named translation of the tcrv-translate driver that a provider registers
+// (include/TianChenRV/Target/TargetTranslateRegistration.h:20-58): `--<routeID>` on the command
+// line runs exportFn over the module.
+struct TargetTranslateRoute {
+  std::string routeID;
+  std::string description;
+  std::function<Error(const Op &module, const ExtensionPluginRegistry &plugins, std::ostream &os)> exportFn;
+  std::string targetArtifactRouteID;  // the plan route this translation serves ("" = any)
+};
+
+class TargetTranslateRouteRegistry {
+public:
+  Error registerRoute(TargetTranslateRoute route);
+  const TargetTranslateRoute *lookup(const std::string &routeID) const;
+  const std::vector<TargetTranslateRoute> &getRoutes() const { return routes; }
+  size_t size() const { return routes.size(); }
+
+private:
+  std::vector<TargetTranslateRoute> routes;
+};
+
 class ExtensionPlugin {
 public:
   virtual ~ExtensionPlugin() = default;
@@ -91,6 +164,12 @@ public:
   // Expands a pre-realized typed body into setvl + boundary + load/compute/store in place.
   virtual Error materializeSelectedLoweringBoundary(Op &kernel, Op &variant) const = 0;
   virtual Error validateSelectedLoweringBoundary(const VariantRequest &request) const = 0;
+  // Target support (include/TianChenRV/Plugin/ExtensionPlugin.h:689-692): the provider names the
+  // dialects and boundary ops its bundle needs and hands over its artifact exporters, and
+  // registers the translations the driver exposes for it.  A provider without target support
+  // keeps the defaults, which add nothing.
+  virtual Error configureTargetSupportExtensionBundle(ExtensionBundle &bundle) const;
+  virtual Error registerTargetSupportTranslateRoutes(TargetTranslateRouteRegistry &registry) const;
 };
 
 class ExtensionPluginRegistry {
@@ -98,6 +177,7 @@ public:
   Error registerPlugin(std::shared_ptr<const ExtensionPlugin> plugin);
   const ExtensionPlugin *lookup(const std::string &origin) const;
   std::vector<std::string> names() const;
+  const std::vector<std::shared_ptr<const ExtensionPlugin>> &getPlugins() const { return plugins; }
   bool empty() const { return plugins.empty(); }
 
 private:
@@ -107,6 +187,10 @@ private:
 // The built-in provider table: one line per provider, as in the reference's
 // lib/Plugin/Builtin/BuiltinExtensionPlugins.cpp:34-42.
 void registerBuiltinPlugins(ExtensionPluginRegistry &registry);
+// One bundle per registered provider, configured by the provider itself, and the translate
+// routes the providers register (lib/Target/BuiltinTargetTranslateRoutes.cpp in the reference).
+Error registerExtensionBundles(const ExtensionPluginRegistry &plugins, ExtensionBundleRegistry &bundles);
+Error registerTargetTranslateRoutes(const ExtensionPluginRegistry &plugins, TargetTranslateRouteRegistry &routes);
 
 // ---- checks shared by every provider (the envelope is dialect-level in the reference) ----
 

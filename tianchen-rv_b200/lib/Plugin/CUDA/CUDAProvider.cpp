@@ -6,6 +6,7 @@
 #include <sstream>
 
 #include "tcrv/CUDAPlugin.h"
+#include "tcrv/CUDATarget.h"
 
 namespace tcrv {
 namespace cuda {
@@ -195,6 +196,13 @@ public:
   // elementwise body, test/Target/RVV/pre-realized-selected-body-artifact-add.mlir:25) into
   // setvl + boundary + load/load/binary/store.  A variant that already has a boundary is
   // left alone.
+  Error configureTargetSupportExtensionBundle(ExtensionBundle &bundle) const override {
+    return configureCUDATargetSupportExtensionBundle(bundle);
+  }
+  Error registerTargetSupportTranslateRoutes(TargetTranslateRouteRegistry &registry) const override {
+    return registerCUDATargetSupportTranslateRoutes(registry);
+  }
+
   Error materializeSelectedLoweringBoundary(Op &kernel, Op &variant) const override {
     VariantRequest r{&kernel, &variant};
     if (Error e = verifyVariantLegality(r))

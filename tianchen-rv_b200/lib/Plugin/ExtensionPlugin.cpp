@@ -42,6 +42,87 @@ std::vector<std::string> ExtensionPluginRegistry::names() const {
   return out;
 }
 
+// ------------------------------------------------------------------ target support
+
+Error ExtensionPlugin::configureTargetSupportExtensionBundle(ExtensionBundle &) const { return Error::success(); }
+Error ExtensionPlugin::registerTargetSupportTranslateRoutes(TargetTranslateRouteRegistry &) const {
+  return Error::success();
+}
+
+Error ExtensionBundle::addTargetArtifactExporter(TargetArtifactExporter exporter) {
+  if (exporter.routeID.empty() || exporter.artifactKind.empty() || exporter.componentRole.empty() || !exporter.exportFn)
+    return Error("bundle '" + bundleID + "': an artifact exporter needs a route id, an artifact kind, a component role "
+                 "and an export function");
+  if (lookupExporter(exporter.routeID, exporter.componentRole))
+    return Error("bundle '" + bundleID + "': route '" + exporter.routeID + "' already has a '" + exporter.componentRole +
+                 "' exporter");
+  exporters.push_back(std::move(exporter));
+  return Error::success();
+}
+
+const TargetArtifactExporter *ExtensionBundle::lookupExporter(const std::string &routeID,
+                                                              const std::string &componentRole) const {
+  for (const auto &e : exporters)
+    if (e.routeID == routeID && e.componentRole == componentRole)
+      return &e;
+  return nullptr;
+}
+
+Error ExtensionBundleRegistry::registerBundle(ExtensionBundle bundle) {
+  if (bundle.getBundleID().empty() || bundle.getPluginName().empty())
+    return Error("an extension bundle needs an id and a provider name");
+  for (const auto &b : bundles)
+    if (b.getBundleID() == bundle.getBundleID() || b.getPluginName() == bundle.getPluginName())
+      return Error("extension bundle '" + bundle.getBundleID() + "' (provider '" + bundle.getPluginName() +
+                   "') is already registered");
+  bundles.push_back(std::move(bundle));
+  return Error::success();
+}
+
+const ExtensionBundle *ExtensionBundleRegistry::lookupPluginBundle(const std::string &pluginName) const {
+  for (const auto &b : bundles)
+    if (b.getPluginName() == pluginName)
+      return &b;
+  return nullptr;
+}
+
+Error TargetTranslateRouteRegistry::registerRoute(TargetTranslateRoute route) {
+  if (route.routeID.empty() || !route.exportFn)
+    return Error("a translate route needs an id and an export function");
+  if (lookup(route.routeID))
+    return Error("translate route '" + route.routeID + "' is already registered");
+  routes.push_back(std::move(route));
+  return Error::success();
+}
+
+const TargetTranslateRoute *TargetTranslateRouteRegistry::lookup(const std::string &routeID) const {
+  for (const auto &r : routes)
+    if (r.routeID == routeID)
+      return &r;
+  return nullptr;
+}
+
+Error registerExtensionBundles(const ExtensionPluginRegistry &plugins, ExtensionBundleRegistry &bundles) {
+  for (const auto &p : plugins.getPlugins()) {
+    if (!p->isEnabled())
+      continue;
+    ExtensionBundle bundle(p->getName() + "-bundle", p->getName());
+    if (Error e = p->configureTargetSupportExtensionBundle(bundle))
+      return e;
+    if (Error e = bundles.registerBundle(std::move(bundle)))
+      return e;
+  }
+  return Error::success();
+}
+
+Error registerTargetTranslateRoutes(const ExtensionPluginRegistry &plugins, TargetTranslateRouteRegistry &routes) {
+  for (const auto &p : plugins.getPlugins())
+    if (p->isEnabled())
+      if (Error e = p->registerTargetSupportTranslateRoutes(routes))
+        return e;
+  return Error::success();
+}
+
 // ------------------------------------------------------------------ envelope checks
 
 static std::string where(const VariantRequest &r) {

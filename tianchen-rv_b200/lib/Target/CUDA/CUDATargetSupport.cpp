@@ -205,5 +205,113 @@ std::string exportManifestLine(const VariantEmissionPlan &plan) {
   return os.str();
 }
 
+// ------------------------------------------------------------------ provider hooks
+
+const char *const kBundleIndexFileName = "tianchenrv-target-artifact-bundle.index";
+
+Error configureCUDATargetSupportExtensionBundle(ExtensionBundle &bundle) {
+  bundle.addRequiredDialectName("tcrv.exec");
+  bundle.addRequiredDialectName("tcrv_rvv");
+  bundle.addLoweringBoundaryOp(kBoundaryOp);
+  if (Error e = bundle.addTargetArtifactExporter({kRouteId, kArtifactKind, "object", ".json", exportLaunchDescriptor}))
+    return e;
+  return bundle.addTargetArtifactExporter({kRouteId, "c-header", "header", ".h", exportHeaderArtifact});
+}
+
+Error registerCUDATargetSupportTranslateRoutes(TargetTranslateRouteRegistry &registry) {
+  TargetTranslateRoute route;
+  route.routeID = "tcrv-cuda-launch-to-cpp";
+  route.description = "C++ translation unit that defines the reference-named entry point over the prebuilt library";
+  route.targetArtifactRouteID = kRouteId;
+  route.exportFn = [](const Op &module, const ExtensionPluginRegistry &plugins, std::ostream &os) -> Error {
+    std::vector<PlannedVariant> planned;
+    if (Error e = collectCoherentPlans(module, plugins, planned))
+      return e;
+    for (const auto &pv : planned) {
+      if (pv.plan.routeID != kRouteId)
+        return Error("translate route 'tcrv-cuda-launch-to-cpp' serves route '" + std::string(kRouteId) +
+                     "', the plan of @" + pv.plan.variantSymbol + " names '" + pv.plan.routeID + "'");
+      os << exportLaunchStubCpp(pv.plan);
+    }
+    return Error::success();
+  };
+  return registry.registerRoute(std::move(route));
+}
+
+Error collectBundleArtifacts(const Op &module, const ExtensionPluginRegistry &plugins,
+                             const ExtensionBundleRegistry &bundles, std::vector<BundleArtifact> &out) {
+  std::vector<PlannedVariant> planned;
+  if (Error e = collectCoherentPlans(module, plugins, planned))
+    return e;
+  for (const auto &pv : planned) {
+    const ExtensionBundle *bundle = bundles.lookupPluginBundle(pv.plan.originPlugin);
+    if (!bundle)
+      return Error("provider '" + pv.plan.originPlugin + "' registered no target-support bundle");
+    bool any = false;
+    for (const char *role : {"object", "artifact", "header"}) {
+      const TargetArtifactExporter *ex = bundle->lookupExporter(pv.plan.routeID, role);
+      if (!ex)
+        continue;
+      if (std::string(role) != "header" && ex->artifactKind != pv.plan.artifactKind)
+        return Error("route id '" + pv.plan.routeID + "' does not support artifact_kind '" + pv.plan.artifactKind +
+                     "'; registered artifact_kind is '" + ex->artifactKind + "'");
+      BundleArtifact a;
+      a.componentRole = role;
+      a.exporter = ex;
+      a.plan = pv.plan;
+      a.contents = ex->exportFn(pv.plan);
+      a.fileName = "artifact-" + std::to_string(out.size()) + "-" + ex->artifactKind + "-" + ex->routeID + ex->fileExtension;
+      out.push_back(std::move(a));
+      any = true;
+    }
+    if (!any)
+      return Error("bundle '" + bundle->getBundleID() + "' has no exporter for route '" + pv.plan.routeID + "'");
+  }
+  return Error::success();
+}
+
+static std::string quoted(const std::string &s) { return "\"" + jsonEscape(s) + "\""; }
+
+std::string renderBundleIndex(const std::vector<BundleArtifact> &artifacts) {
+  std::ostringstream os;
+  os << "tianchenrv.target_artifact_bundle.version: 1\n";
+  os << "bundle_status: \"complete\"\n";
+  os << "artifact_count: " << artifacts.size() << "\n";
+  for (size_t i = 0; i < artifacts.size(); ++i) {
+    const BundleArtifact &a = artifacts[i];
+    const VariantEmissionPlan &p = a.plan;
+    os << "artifact[" << i << "]:\n";
+    os << "  file_name: " << quoted(a.fileName) << "\n";
+    os << "  component_group: " << quoted(p.kernelSymbol + "." + p.variantSymbol) << "\n";
+    os << "  component_role: " << quoted(a.componentRole) << "\n";
+    os << "  external_abi_name: " << quoted(p.runtimeABIName) << "\n";
+    os << "  selected_variant: @" << p.variantSymbol << "\n";
+    os << "  role: " << quoted(toString(p.role)) << "\n";
+    os << "  artifact_kind: " << quoted(a.exporter->artifactKind) << "\n";
+    os << "  route: " << quoted(p.routeID) << "\n";
+    os << "  owner: " << quoted(p.originPlugin) << "\n";
+    os << "  runtime_abi: " << quoted(p.entrySymbol) << "\n";
+    os << "  runtime_abi_kind: " << quoted(p.runtimeABIKind) << "\n";
+    os << "  runtime_abi_name: " << quoted(p.runtimeABIName) << "\n";
+    os << "  runtime_abi_parameter_count: " << p.abiParameters.size() << "\n";
+    for (size_t j = 0; j < p.abiParameters.size(); ++j) {
+      const RuntimeABIParameter &q = p.abiParameters[j];
+      os << "  runtime_abi_parameter[" << j << "]:\n";
+      os << "    c_name: " << quoted(q.cName) << "\n";
+      os << "    c_type: " << quoted(q.cType) << "\n";
+      os << "    role: " << quoted(q.role) << "\n";
+      os << "    ownership: " << quoted(q.ownership) << "\n";
+    }
+    for (size_t j = 0; j < p.metadata.size(); ++j) {
+      os << "  artifact_metadata[" << j << "]:\n";
+      os << "    key: " << quoted(p.metadata[j].first) << "\n";
+      os << "    value: " << quoted(p.metadata[j].second) << "\n";
+    }
+    os << "  handoff_kind: " << quoted(p.emissionKind) << "\n";
+    os << "  evidence_role: " << quoted(a.componentRole == "header" ? "c-abi-declaration" : "launch-descriptor") << "\n";
+  }
+  return os.str();
+}
+
 }  // namespace cuda
 }  // namespace tcrv
