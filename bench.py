@@ -31,14 +31,16 @@ METRIC = "q4_0_q8_0_decode_gemv_hbm_gbs"
 UNIT = "GB/s"
 WORKLOAD = "q4_0_q8_0_gemv_llama7b_layers_batch1"
 ROTATION_SETS = 8       # distinct copies of every weight matrix; 8 x 134 MB, far beyond the 126 MB L2
-GRAPH_STEPS = 16        # steps per CUDA graph of the timed region (measured: 8..32 steps 4.51-4.53 TB/s,
+GRAPH_STEPS = 32        # most steps per CUDA graph of the timed region (measured: 8..32 steps 4.51-4.53 TB/s,
                         # 64: 4.46, 128: 4.32, 256: 4.16 -- long graphs dispatch their nodes more slowly)
+MIN_REGIONS = 30        # the K-step region is timed this many times at least; the median is reported
+MIN_TIMED_MS = 20.0     # ... and often enough that the timed regions add up to this much device time
 MIN_WARM_SECONDS = 1.5  # warm-up runs at least this long so that the clock sampler sees load
 
 
-# DRAM traffic per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures
-# summarised under profiles/: measured for two shapes, the other two scaled from the larger
-# one by their weight bytes (traffic grows in proportion to the rows streamed).
+# DRAM traffic per launch (dram__bytes_read.sum + dram__bytes_write.sum) from ncu captures of the
+# 32000x4096 and 4096x4096 launches; the other two shapes are scaled from the larger one by
+# their weight bytes (traffic grows in proportion to the rows streamed).
 NCU_TRAFFIC = {"32000x4096": 74_489_856, "4096x4096": 9_463_040}
 NCU_TRAFFIC_RATIO = 74_489_856 / 73_860_352  # traffic / algorithmic bytes of the measured launch
 
@@ -155,7 +157,7 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": None, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "int8 products, int32 block sums, fp32 fold",
-        "data": "synthetic", "config": {"workload": WORKLOAD},
+        "data": "synthetic", "config": bench_config(args, args.gpus),
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": desc},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "note": "CPU oracle (restatement of the reference's scalar kernel); the reference's generated RVV C "
@@ -204,45 +206,42 @@ def run_ours(args):
         for l in layers:
             pkg.gemv(l["w"][r], l["x"], out=l["y"], flags=pkg.FLAG_STATIC_WEIGHTS)
 
-    # One CUDA graph per rotation set: a step is one graph launch (4 GEMV kernels), so the
-    # host's per-call cost does not sit between the kernels.
+    # First launches outside capture (function attributes, lazy loading).
     side = torch.cuda.Stream()
     with torch.cuda.stream(side):
         for r in range(ROTATION_SETS):
-            launch_set(r)  # first launches outside capture (function attributes, lazy loading)
+            launch_set(r)
     torch.cuda.synchronize()
     pkg.check_device_errors()
-    # A CUDA graph of one decode pass per rotation set, plus one graph holding a whole rotation
-    # (ROTATION_SETS consecutive passes = 32 kernels), the way a decoder captures all the
-    # layers of a token in one graph: K steps replay the long graph K // ROTATION_SETS times
-    # and single-pass graphs cover the remainder, so exactly K passes are timed.
+    # Warm-up replays one graph per rotation set (one decode pass, 4 GEMV kernels).
     graphs = []
     for r in range(ROTATION_SETS):
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g, stream=side):
             launch_set(r)
         graphs.append(g)
-    # The timed region replays graphs that hold `--graph-steps` consecutive steps each (step i
-    # uses weight copy i mod 8), so that Python's per-call cost does not sit between kernels.
-    def steps_graph(count: int):
+
+    # The timed region is K consecutive steps (step i uses weight copy i mod 8) captured in CUDA
+    # graphs, the way a decoder captures all the layers of a token, so that Python's per-call cost
+    # does not sit between kernels: ONE graph when K <= --graph-steps, otherwise graphs of
+    # --graph-steps steps plus one for the remainder, each starting at the rotation offset where
+    # its predecessor stopped.
+    def steps_graph(first: int, count: int):
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g, stream=side):
-            for i in range(count):
+            for i in range(first, first + count):
                 launch_set(i % ROTATION_SETS)
         return g
 
-    chunk = min(args.steps, args.graph_steps) // ROTATION_SETS * ROTATION_SETS  # keeps the rotation aligned
-    chunk_graph = steps_graph(chunk) if chunk > 0 else None
-    tail_steps = args.steps - (args.steps // chunk) * chunk if chunk > 0 else args.steps
-    tail_graph = steps_graph(tail_steps) if tail_steps > 0 else None
+    region, done = [], 0
+    while done < args.steps:
+        count = min(args.graph_steps, args.steps - done)
+        region.append(steps_graph(done, count))
+        done += count
 
-    def run_steps(count: int):
-        assert count == args.steps
-        if chunk_graph is not None:
-            for _ in range(count // chunk):
-                chunk_graph.replay()
-        if tail_graph is not None:
-            tail_graph.replay()
+    def run_steps():
+        for g in region:
+            g.replay()
 
     def step(i: int):
         graphs[i % ROTATION_SETS].replay()
@@ -262,21 +261,43 @@ def run_ours(args):
         if i % 64 == 0:
             torch.cuda.synchronize()
     pkg.check_device_errors()
+    run_steps()  # the region's graphs once, untimed (first replay uploads them)
     sync_all()
 
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    start.record()
-    run_steps(args.steps)
-    stop.record()
-    sync_all()
-    elapsed_ms = start.elapsed_time(stop)
+    # The K-step region is timed `regions` times (events on the replay stream, a barrier and a
+    # synchronize on both sides of each) and the median is reported: K steps alone last well under
+    # a millisecond.  One untimed pass is queued directly before the start event so that the
+    # region's first kernel follows a predecessor, as every other one does.
+    def time_region():
+        sync_all()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        step(ROTATION_SETS - 1)
+        start.record()
+        run_steps()
+        stop.record()
+        sync_all()
+        return start.elapsed_time(stop)
+
+    times = [time_region() for _ in range(max(1, args.regions))]
+    # more regions until they add up to --min-timed-ms; every rank must run the same number
+    more = 0
+    if sum(times) < args.min_timed_ms:
+        more = min(2000, int((args.min_timed_ms - sum(times)) / (sum(times) / len(times))) + 1)
+    if dist is not None:
+        t = torch.tensor([more], dtype=torch.int64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        more = int(t.item())
+    times += [time_region() for _ in range(more)]
+    times.sort()
+    elapsed_ms = times[len(times) // 2]
+    elapsed_best = times[0]
     launches = launches_per_step * args.steps
     clocks = sampler.stop(warm_mark) if rank == 0 else None
     pkg.check_device_errors()
     if dist is not None:
-        t = torch.tensor([elapsed_ms], dtype=torch.float64, device="cuda")
+        t = torch.tensor([elapsed_ms, elapsed_best], dtype=torch.float64, device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        elapsed_ms = float(t.item())
+        elapsed_ms, elapsed_best = float(t[0].item()), float(t[1].item())
 
     # ---- per-shape timing (explains the aggregate): one graph per shape holding one launch
     # per rotation copy, timed with events on the replay stream
@@ -299,6 +320,7 @@ def run_ours(args):
         us = a.elapsed_time(b) * 1e3 / (reps * ROTATION_SETS)
         per_shape.append({"shape": f"{l['nr']}x{l['k']}", "us": round(us, 3), "gbs": round(l["bytes"] / us / 1e3, 1)})
 
+    batch8 = measure_batch8(pkg, torch, layers, side, gen)
     e2e = measure_e2e(pkg, torch, layers, max(10, min(args.steps, 50)), dist)
     try:
         others = measure_other_kernels(pkg, torch) if (rank == 0 and not args.skip_gemm) else None
@@ -325,33 +347,112 @@ def run_ours(args):
     value = step_bytes * args.steps * world / (elapsed_ms * 1e-3) / 1e9
     per_gpu = value / world
     big = per_shape[-1]
+    b8_bytes = sum(gemv_bytes(l["nr"], l["k"], 8) for l in layers)
+    roofline = {
+        "bound": "hbm", "achieved": round(per_gpu, 2), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+        "frac": round(per_gpu / peaks["hbm_gbs"], 4), "traffic": round(step_traffic / launches_per_step),
+        "algorithmic_bytes_per_launch": round(step_bytes / launches_per_step),
+        "traffic_source": "from profile: ncu dram bytes per launch (32000x4096 and 4096x4096 captured, the other "
+                          "two shapes scaled by weight bytes), averaged over the step's 4 launches",
+        "peak_kind": f"of {peak_kind}", "kernel": "gemv_stream_kernel<q4_0, 1 column>", "largest_shape": big,
+        "per_shape_sum_us": round(sum(p["us"] for p in per_shape), 3),
+        # batch 8 (tensor-core decode kernel): the same four-shape pass and its largest launch
+        "batch8": {"kernel": "gemv_mma_kernel<q4_0, 8 columns>", "pass_us": batch8["pass_us"],
+                   "pass_gbs": round(b8_bytes / batch8["pass_us"] / 1e3, 1),
+                   "frac": round(b8_bytes / batch8["pass_us"] / 1e3 / peaks["hbm_gbs"], 4),
+                   "per_shape": batch8["per_shape"],
+                   "largest_shape_frac": round(batch8["per_shape"][-1]["gbs"] / peaks["hbm_gbs"], 4)},
+        # prefill GEMM (the metric's second half): int8 TOP/s of the N-sharded GEMM on this many GPUs
+        "gemm": gemm_summary(gemm),
+    }
     line = {
         "metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": round(elapsed_ms / args.steps, 6), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "int8 products, int32 block sums, fp32 fold",
         "data": "synthetic",
-        "config": {"workload": WORKLOAD, "shapes": [f"{n}x{k}" for n, k in SHAPES], "batch": 1,
-                   "l2": f"weights rotate over {ROTATION_SETS} distinct copies per shape ({ROTATION_SETS} x 134 MB in all, L2 is 126 MB)",
-                   "launch": f"CUDA graphs of up to {args.graph_steps} consecutive steps (4 GEMV kernels each)",
-                   "parallelism": "replicas only" if world > 1 else "single GPU"},
-        "roofline": {"bound": "hbm", "achieved": round(per_gpu, 2), "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                     "frac": round(per_gpu / peaks["hbm_gbs"], 4), "traffic": round(step_traffic / launches_per_step),
-                     "algorithmic_bytes_per_launch": round(step_bytes / launches_per_step),
-                     "traffic_source": "ncu dram bytes per launch, averaged over the step's 4 launches "
-                                       "(profiles/gemv_stream_q4_0_b1_32000x4096.md)",
-                     "peak_kind": f"of {peak_kind}",
-                     "kernel": "gemv_stream_kernel<q4_0, 1 column>", "largest_shape": big},
+        "config": bench_config(args, world),
+        "roofline": roofline,
         "e2e": e2e,
         "cpu_baseline": cpu,
-        "per_shape": per_shape,
-        "gemm": gemm,
-        "other_kernels": others,
         "gpu_launches": launches,
         "clocks": clocks,
+        "timing": {"regions": len(times), "region_ms_median": round(elapsed_ms, 5), "region_ms_best": round(elapsed_best, 5),
+                   "note": "the K-step region is replayed `regions` times; value and ms_per_step use the median"},
+        "per_shape": per_shape,
+        "other_kernels": others,
+        "gemm": gemm,
     }
     print(json.dumps(line))
     if dist is not None:
         dist.destroy_process_group()
+
+
+def bench_config(args, world):
+    """The `config` object; both arms print the same workload, shapes and batch."""
+    return {"workload": WORKLOAD, "shapes": [f"{n}x{k}" for n, k in SHAPES], "batch": 1,
+            "l2": f"weights rotate over {ROTATION_SETS} distinct copies per shape ({ROTATION_SETS} x 134 MB in all, L2 is 126 MB)",
+            "launch": f"CUDA graphs of up to {args.graph_steps} consecutive steps (4 GEMV kernels each)",
+            "parallelism": "replicas only" if world > 1 else "single GPU"}
+
+
+def gemm_summary(gemm):
+    """The figures of measure_gemm() a reader needs first, one short object per shape."""
+    if not isinstance(gemm, list):
+        return gemm
+    keys = ("shape", "rows_per_gpu", "compute_ms", "compute_tops", "with_allgather_ms", "with_allgather_tops",
+            "fused_allgather_ms", "fused_allgather_tops", "fused_equals_nccl", "fused_link_gbs_per_gpu")
+    out = []
+    for g in gemm:
+        e = {k: g[k] for k in keys if k in g}
+        r = g.get("roofline", {})
+        e.update({"bound": "tensor", "frac": r.get("frac"), "peak_tops": r.get("peak"),
+                  "library_int8_gemm_tops": r.get("library_int8_gemm_tops"),
+                  "frac_of_library_int8": r.get("frac_of_library_int8_gemm")})
+        out.append(e)
+    return out
+
+
+def measure_batch8(pkg, torch, layers, side, gen):
+    """The four-shape decode pass with 8 activation columns (tensor-core decode kernel) over the
+    same rotating weight copies: one graph of 8 passes, events on the replay stream."""
+    xs = [pkg.quantize_q8_0(torch.randn((8, l["k"]), generator=gen, device="cuda")) for l in layers]
+    ys = [torch.empty((l["nr"], 8), dtype=torch.float32, device="cuda") for l in layers]
+
+    def timed(fn, launches):
+        with torch.cuda.stream(side):
+            fn()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            fn()
+        for _ in range(3):
+            g.replay()
+        torch.cuda.synchronize()
+        reps = 10
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            g.replay()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) * 1e3 / (reps * launches)
+
+    def whole():
+        for r in range(ROTATION_SETS):
+            for l, x, y in zip(layers, xs, ys):
+                pkg.gemv(l["w"][r], x, out=y, flags=pkg.FLAG_STATIC_WEIGHTS)
+
+    pass_us = timed(whole, ROTATION_SETS)
+    per_shape = []
+    for l, x, y in zip(layers, xs, ys):
+        def one(l=l, x=x, y=y):
+            for r in range(ROTATION_SETS):
+                pkg.gemv(l["w"][r], x, out=y, flags=pkg.FLAG_STATIC_WEIGHTS)
+        us = timed(one, ROTATION_SETS)
+        per_shape.append({"shape": f"{l['nr']}x{l['k']}", "us": round(us, 3),
+                          "gbs": round(gemv_bytes(l["nr"], l["k"], 8) / us / 1e3, 1)})
+    pkg.check_device_errors()
+    return {"pass_us": round(pass_us, 3), "per_shape": per_shape}
 
 
 def measure_e2e(pkg, torch, layers, steps, dist):
@@ -363,6 +464,9 @@ def measure_e2e(pkg, torch, layers, steps, dist):
     import ctypes
 
     L = pkg.lib()
+    # the entry's default is the reference's strict block order (a verification-grade path); a
+    # decoder opts in to the streaming kernels' own summation orders, as the device-timed arm does
+    previous_order = L.tcrv_cuda_host_set_fold_order(1)
     host = []
     for l in layers:
         w_host = l["w"][0].cpu().numpy()  # pageable host copy of the block_q4_0 rows
@@ -406,11 +510,13 @@ def measure_e2e(pkg, torch, layers, steps, dist):
     for l, w_host, x_host, y_host in host:
         L.tcrv_cuda_host_unregister_weights(w_host.ctypes.data)
     L.tcrv_cuda_host_release()
+    L.tcrv_cuda_host_set_fold_order(previous_order)
     step_bytes = sum(l["bytes"] for l in layers)
     return {"value": round(step_bytes * steps * world / dt / 1e9, 2), "unit": UNIT,
             "h2d_bytes_per_step": sum(int(x.numel()) for _, _, x, _ in host),
             "d2h_bytes_per_step": sum(int(y.numel()) * 4 for _, _, _, y in host),
             "ms_per_step": round(dt / steps * 1e3, 4), "steps": steps,
+            "fold_order": "TCRV_CUDA_HOST_FOLD_FAST (lane pairs), selected with tcrv_cuda_host_set_fold_order",
             "weights": "registered once (resident); activations and outputs cross PCIe every step "
                        "(inputs by a copy from the pinned buffer, results stored by the kernel into the pinned "
                        "output through its device mapping)"}
@@ -622,6 +728,90 @@ def measure_gemm(pkg, torch, dist, rank, world):
     return results
 
 
+PROFILE_CASES = ["gemv", "gemv_q8", "gemm", "dequant", "quantize", "silu", "rms_norm", "repack_gemv", "repack_gemv_q8",
+                 "repack_gemm"]
+
+
+def run_profile_case(args):
+    """`--profile-case NAME`: a small, self-ending workload that launches ONE kernel family a
+    handful of times (a few GB on the device at most, rotating weight copies larger than the L2
+    so that DRAM counters mean something), for a profiler to capture.  Prints no metric."""
+    args.case = args.profile_case
+    args.rows = args.case_rows
+    args.k = args.case_k
+    args.cols = args.case_cols
+    args.tokens = args.case_tokens
+    args.launches = args.case_launches
+    import torch
+
+    pkg = entry.load_package()
+    torch.cuda.set_device(0)
+    gen = torch.Generator(device="cuda").manual_seed(7)
+    if args.case in ("gemv", "gemv_q8"):
+        rows = args.rows or 32000
+        q8w = args.case == "gemv_q8"
+        wf = torch.randn((rows, args.k), generator=gen, device="cuda") * 0.02
+        w = pkg.quantize_q8_0(wf) if q8w else pkg.quantize_q4_0(wf)
+        copies = [w] + [w.clone() for _ in range(max(2, (300 << 20) // w.numel()))]
+        x = pkg.quantize_q8_0(torch.randn((args.cols, args.k), generator=gen, device="cuda"))
+        y = torch.empty((rows, args.cols), dtype=torch.float32, device="cuda")
+        for i in range(args.launches):
+            pkg.gemv(copies[i % len(copies)], x, q8_weights=q8w, out=y)
+    elif args.case in ("repack_gemv", "repack_gemv_q8"):
+        # random bytes stand in for the interleaved weights (timing and traffic do not depend on them)
+        rows = args.rows or 32000
+        q8w = args.case == "repack_gemv_q8"
+        nbytes = rows // 16 * (args.k // 32) * (544 if q8w else 288)
+        copies = [torch.randint(0, 256, (nbytes,), dtype=torch.uint8, device="cuda", generator=gen)
+                  for _ in range(max(3, (300 << 20) // nbytes + 1))]
+        x = pkg.quantize_q8_0(torch.randn((1, args.k), generator=gen, device="cuda")).reshape(-1)
+        y = torch.empty(rows, dtype=torch.float32, device="cuda")
+        for i in range(args.launches):
+            pkg.repack_gemv(copies[i % len(copies)], x, rows, q8_weights=q8w, out=y)
+    elif args.case == "repack_gemm":
+        rows = args.rows or 11008
+        nb = args.k // 32
+        wx = torch.randint(0, 256, (rows // 16 * nb * 288,), dtype=torch.uint8, device="cuda", generator=gen)
+        xx = torch.randint(0, 256, (args.tokens // 4 * nb * 136,), dtype=torch.uint8, device="cuda", generator=gen)
+        pw = pkg.PreparedX16Weights(wx, args.k, rows)
+        out = torch.empty((args.tokens, rows), dtype=torch.float32, device="cuda")
+        for _ in range(args.launches):
+            pw.gemm(xx, args.tokens, out=out)
+    elif args.case == "gemm":
+        rows = args.rows or 11008
+        w = pkg.quantize_q4_0(torch.randn((rows, args.k), generator=gen, device="cuda") * 0.02)
+        x = pkg.quantize_q8_0(torch.randn((args.tokens, args.k), generator=gen, device="cuda"))
+        pw = pkg.PreparedWeights(w)
+        out = torch.empty((rows, args.tokens), dtype=torch.float32, device="cuda")
+        for _ in range(args.launches):
+            pkg.gemm(pw, x, out=out)
+    elif args.case in ("quantize", "silu", "rms_norm"):
+        rows = args.rows or (4096 if args.case == "quantize" else 512)
+        k = args.k if (args.case == "quantize" or args.k != 4096) else 11008
+        xs = [torch.randn((rows, k), generator=gen, device="cuda") for _ in range(6)]
+        out = torch.empty((rows, k), dtype=torch.float32, device="cuda")
+        qout = torch.empty((rows, k // 32 * 34), dtype=torch.uint8, device="cuda")
+        for i in range(args.launches):
+            if args.case == "quantize":
+                pkg.quantize_q8_0(xs[i % len(xs)], out=qout)
+            elif args.case == "silu":
+                pkg.vec_silu(xs[i % len(xs)], out=out)
+            else:
+                pkg.rms_norm(xs[i % len(xs)], 1e-6, out=out)
+    else:
+        rows = args.rows or 4096
+        q = pkg.quantize_q8_0(torch.randn((rows, args.k), generator=gen, device="cuda") * 0.02)
+        copies = [q] + [q.clone() for _ in range(8)]
+        out = torch.empty((rows, args.k), dtype=torch.float32, device="cuda")
+        for i in range(args.launches):
+            pkg.dequantize_q8_0(copies[i % len(copies)], out=out)
+    torch.cuda.synchronize()
+    pkg.check_device_errors()
+    print("profile case done")
+
+
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -631,9 +821,21 @@ def main():
     ap.add_argument("--min-warm-seconds", type=float, default=MIN_WARM_SECONDS,
                     help="warm-up lasts at least this long (0 for a profiler's launch-list pass)")
     ap.add_argument("--skip-gemm", action="store_true", help="leave out the prefill-GEMM section")
-    ap.add_argument("--graph-steps", type=int, default=GRAPH_STEPS, help="steps captured per CUDA graph of the timed region")
+    ap.add_argument("--graph-steps", type=int, default=GRAPH_STEPS, help="most steps captured per CUDA graph of the timed region")
+    ap.add_argument("--regions", type=int, default=MIN_REGIONS, help="how often the K-step region is timed (median reported)")
+    ap.add_argument("--min-timed-ms", type=float, default=MIN_TIMED_MS,
+                    help="more regions are timed until they add up to this much device time (0 for a profiler pass)")
+    ap.add_argument("--profile-case", choices=PROFILE_CASES, default=None,
+                    help="run a small self-ending workload of one kernel family for a profiler instead of the benchmark")
+    ap.add_argument("--case-rows", type=int, default=None)
+    ap.add_argument("--case-k", type=int, default=4096)
+    ap.add_argument("--case-cols", type=int, default=1)
+    ap.add_argument("--case-tokens", type=int, default=512)
+    ap.add_argument("--case-launches", type=int, default=6)
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.profile_case:
+        run_profile_case(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

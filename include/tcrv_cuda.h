@@ -215,15 +215,17 @@ int tcrv_cuda_unpack_q4_0x16_to_q4_0(size_t nblocks, const uint8_t *src, uint8_t
  * tcrv_rvv.repack_gemv_q4_0_q8_0 (lib/Conversion/RVV/RVVToEmitCBlockQuantLinear.cpp:2853-3344)
  * and tcrv_rvv.repack_gemv_q8_0_q8_0 (:3930-4378); ABI order n, s, vx, vy, nc (nc = weight
  * rows, a multiple of 16; test/Conversion/RVV/rvv-to-emitc-repack-gemv-q4-0-q8-0.mlir:27-31).
- * Integer block sums are exact.  The fp32 summation order is the kernel's, not the
- * reference's strict block order: the ceil(nb/8) steps of 8 blocks are cut into
+ * Integer block sums are exact.  With TCRV_CUDA_FLAG_STRICT_ORDER every row folds its blocks
+ * one after the other from 0.0f, the reference's own lane-wise chain (:3262-3298), bit for bit
+ * (a chain of nb dependent operations per row: a verification path, not a fast one).  Without
+ * the flag the fp32 summation order is the kernel's: the ceil(nb/8) steps of 8 blocks are cut into
  * tcrv_cuda_repack_gemv_parts(n) contiguous ranges; inside a range chain c (0..7) folds
  * blocks 8*step + c in ascending order from 0.0f, the chains are added as
  * ((c0+c4) + (c2+c6)) + ((c1+c5) + (c3+c7)), and the ranges in ascending order.  The order
  * depends on n alone (not on nc or the GPU).  A weight pointer that is not 16-byte aligned takes
  * a slow byte-wise kernel with the same order (the fast path streams with 16-byte bulk copies).
- * `flags`: 0, or tuning overrides that leave the result unchanged (bits 8..11 ring depth,
- * bits 12..15 warps per row group, bits 16..19 copies in flight). */
+ * `flags`: 0, TCRV_CUDA_FLAG_STRICT_ORDER, or tuning overrides that leave the result unchanged
+ * (bits 8..11 ring depth, bits 12..15 warps per row group, bits 16..19 copies in flight). */
 size_t tcrv_cuda_repack_gemv_parts(size_t n);
 int tcrv_cuda_repack_gemv_q4_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t nc,
                                     unsigned flags, tcrv_cuda_stream stream);
@@ -274,6 +276,12 @@ int tcrv_cuda_vec_silu_f32(size_t n, const float *x, float *y, tcrv_cuda_stream 
  * one part in 2^50 before the result is rounded to f32. */
 int tcrv_cuda_rms_norm_f32(size_t ne00, const float *x, float *y, float eps, size_t nrows, size_t x_stride,
                            size_t y_stride, tcrv_cuda_stream stream);
+/* The same with `flags`: TCRV_CUDA_FLAG_STRICT_ORDER adds the squares as the reference does,
+ * sum = sum + (double)(x_i * x_i) for i = 0, 1, 2, ... (RVVToEmitCForwardElementwise.cpp:169-234),
+ * and so returns the reference's bits for every input; one warp per row walks the chain, which
+ * takes tens of microseconds for a row of 11008 floats.  0 selects the tree described above. */
+int tcrv_cuda_rms_norm_f32_flags(size_t ne00, const float *x, float *y, float eps, size_t nrows, size_t x_stride,
+                                 size_t y_stride, unsigned flags, tcrv_cuda_stream stream);
 
 /* y[i] = exp(x[i] - max) (same polynomial) and, when `sum` is not null, *sum = f64 sum of
  * the y (device pointer).  Replaces tcrv_rvv.ggml_vec_soft_max_f32, whose function returns

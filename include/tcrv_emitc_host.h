@@ -9,6 +9,9 @@
  * All pointers are HOST pointers; a call returns when its output is in host memory.  Like
  * the generated kernels they return void; a provider failure prints a message and aborts.
  * The `tcrv_cuda_host_*` functions are the same operations returning a tcrv_cuda_status.
+ * Every call works on the CUDA device that is current on the calling thread; stream, scratch
+ * arena and registered weights are kept per device (weights registered with one device current
+ * are resident on that device only), and calls on one device serialise on that device's lock.
  */
 #ifndef TCRV_EMITC_HOST_H
 #define TCRV_EMITC_HOST_H
@@ -26,6 +29,21 @@ int tcrv_cuda_host_register_weights(const void *host, size_t bytes);
 int tcrv_cuda_host_unregister_weights(const void *host);
 /* Frees every device allocation this front end made (arena and resident weights). */
 int tcrv_cuda_host_release(void);
+
+/* fp32 summation order of the matrix entries below whose signatures carry no flags
+ * (tcrv_cuda_host_gemm_q4_0_q8_0 / _q8_0_q8_0 with up to 8 columns, the repacked GEMVs,
+ * tcrv_cuda_host_rms_norm_f32's double sum of squares, and the reference-named stubs over them).  The reference's kernels fold every output in strict
+ * ascending block order and pin byte-exactness on it, so that is the default:
+ *   TCRV_CUDA_HOST_FOLD_STRICT  every output = blocks 0, 1, 2, ... folded one after the other;
+ *                               byte-identical to the generated RVV kernel's result
+ *   TCRV_CUDA_HOST_FOLD_FAST    the streaming decode kernels' own orders (lane pairs, 16-way K
+ *                               split, range/chain order; see tcrv_cuda_gemv_fold_order): same
+ *                               integer block sums, rows within rel 1e-5, several times faster
+ * The GEMM with more than 8 columns and the block-dot / GEMM-tile entries are strict either
+ * way.  Process-wide; returns the previous setting, or TCRV_CUDA_ERR_INVALID_ARGUMENT. */
+#define TCRV_CUDA_HOST_FOLD_STRICT 0
+#define TCRV_CUDA_HOST_FOLD_FAST 1
+int tcrv_cuda_host_set_fold_order(int order);
 
 int tcrv_cuda_host_add_f32(const float *lhs, const float *rhs, float *out, size_t n);
 int tcrv_cuda_host_add_i32(const int32_t *lhs, const int32_t *rhs, int32_t *out, size_t n);
@@ -50,7 +68,7 @@ int tcrv_cuda_host_repack_gemv_q4_0_q8_0(size_t n, float *s, const uint8_t *vx, 
 int tcrv_cuda_host_repack_gemv_q8_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t nc);
 int tcrv_cuda_host_repack_gemm_q4_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t nr, size_t nc,
                                          size_t bs);
-/* nc <= 8 runs the decode GEMV, larger nc the tensor-core GEMM. */
+/* nc <= 8 runs the decode GEMV (order: tcrv_cuda_host_set_fold_order), larger nc the tensor-core GEMM. */
 int tcrv_cuda_host_gemm_q4_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by, size_t nr,
                                   size_t nc, size_t bx, size_t bs);
 /* One weight row against `cols` (1..16) activation columns, strict block order per column. */

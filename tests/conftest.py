@@ -12,6 +12,7 @@ import __graft_entry__ as entry  # noqa: E402
 
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run on a B200)")
+    config.addinivalue_line("markers", "strict_default: host-pointer test that keeps the library's default fold order")
 
 
 @pytest.fixture(scope="session")

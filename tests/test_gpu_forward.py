@@ -77,6 +77,28 @@ def test_rms_norm_wide_dynamic_range_stays_within_one_ulp(cuda, pkg, O):
     assert diff.max() <= 1 and np.mean(diff == 0) > 0.999
 
 
+@pytest.mark.parametrize("rows,ne00", [(1, 1), (3, 31), (5, 33), (64, 4096), (9, 11008), (2, 100003)])
+def test_rms_norm_strict_order_has_the_reference_bits(cuda, pkg, O, rows, ne00):
+    # TCRV_CUDA_FLAG_STRICT_ORDER replays the reference's ascending f64 chain, so the result is
+    # bit-equal also where the double sum is inexact (squares spanning ~80 binades, shuffled so
+    # that large and small terms alternate)
+    x = O.fill_normal(rows * ne00, 75 + ne00, 0.0, 1.0).reshape(rows, ne00)
+    spread = np.exp2(np.linspace(-40, 0, ne00)).astype(np.float32)
+    np.random.default_rng(ne00).shuffle(spread)
+    for xs in (x, x * spread):
+        got = pkg.rms_norm(dev(cuda, xs), 1e-6, flags=pkg.FLAG_STRICT_ORDER).cpu().numpy()
+        assert np.array_equal(bits(got), bits(O.rms_norm_f32(xs, 1e-6)))
+    # padded strides
+    xp = cuda.zeros((rows, ne00 + 3), dtype=cuda.float32, device="cuda")
+    xp[:, :ne00] = dev(cuda, x * spread)
+    outp = cuda.full((rows, ne00 + 5), -1.0, dtype=cuda.float32, device="cuda")
+    pkg.rms_norm(xp[:, :ne00], 1e-5, out=outp[:, :ne00], flags=pkg.FLAG_STRICT_ORDER)
+    res = outp.cpu().numpy()
+    assert np.array_equal(bits(res[:, :ne00]), bits(O.rms_norm_f32(x * spread, 1e-5))) and np.all(res[:, ne00:] == -1.0)
+    assert pkg.lib().tcrv_cuda_rms_norm_f32_flags(8, xp.data_ptr(), outp.data_ptr(), 1e-6, 1, 8, 8, 4, None) == -1
+    pkg.check_device_errors()
+
+
 @pytest.mark.parametrize("n", [1, 33, 4096, 32000, 1 << 18])
 def test_vec_soft_max_exponentials_bit_exact(cuda, pkg, O, n):
     x = O.fill_normal(n, 80 + n, 0.0, 3.0)

@@ -8,6 +8,9 @@ pytestmark = pytest.mark.gpu
 
 REL = 1e-5        # tolerance the path is specified to
 CANCEL = 1e-6     # |err| allowed per unit of sum(|terms|) on rows that nearly cancel
+# A row may use the CANCEL bound only if it really cancels: sum(|terms|) / |ref| of the worst row
+# that needed it must exceed this (a row that misses REL without cancelling is a failure).
+MIN_CANCEL_RATIO = 10.0
 
 
 def dev(torch, a):
@@ -34,10 +37,25 @@ def check_rows(O, got, w, x, q8w, order):
     """`order` is what tcrv_cuda_gemv_fold_order reported for the call that produced `got`."""
     assert np.array_equal(got.view(np.uint32), restated(O, w, x, q8w, order).view(np.uint32))
     ref = O.gemm(w, x, q8_weights=q8w)
+    return check_against_sequential(got, ref, O.abs_terms(w, x, q8w))
+
+
+def check_against_sequential(got, ref, terms, label=""):
+    """rel 1e-5 per row against the sequential oracle; a row that misses it must be a row whose
+    terms cancel (sum|term| >> |ref|) and is then held to 1e-6 * sum|term|.  Prints how many
+    rows needed the second bound and the weakest cancellation among them, so that the
+    relaxation can be audited from the test log (pytest -s / -rA)."""
     err = np.abs(got - ref)
-    ok = (err <= REL * np.abs(ref)) | (err <= CANCEL * O.abs_terms(w, x, q8w))
-    assert np.all(ok)
-    return float(np.mean(err <= REL * np.abs(ref)))
+    plain = err <= REL * np.abs(ref)
+    assert np.all(plain | (err <= CANCEL * terms))
+    relaxed = ~plain
+    if relaxed.any():
+        ratio = terms[relaxed] / np.maximum(np.abs(ref[relaxed]), 1e-300)
+        worst = float(ratio.min())
+        print(f"{label} rows on the cancellation bound: {int(relaxed.sum())} of {relaxed.size}; "
+              f"smallest sum|term|/|ref| among them {worst:.1f}; largest err/|ref| {float((err[relaxed] / np.maximum(np.abs(ref[relaxed]), 1e-300)).max()):.2e}")
+        assert worst >= MIN_CANCEL_RATIO, f"a row missed rel {REL} with sum|term|/|ref| = {worst:.2f}: not a cancellation"
+    return float(np.mean(plain))
 
 
 @pytest.mark.parametrize("q8w", [False, True])

@@ -8,6 +8,22 @@ import pytest
 
 pytestmark = pytest.mark.gpu
 
+FOLD_STRICT, FOLD_FAST = 0, 1
+
+
+@pytest.fixture(autouse=True)
+def fast_fold(request, cuda, pkg):
+    """Most tests here exercise the streaming kernels behind the host entries (replay, resident
+    weights, pinned buffers), so they opt in to the kernels' own summation orders; tests marked
+    `strict_default` run with the library default (the reference's strict block order)."""
+    if "strict_default" in request.keywords:
+        yield
+        return
+    L = pkg.lib()
+    prev = L.tcrv_cuda_host_set_fold_order(FOLD_FAST)
+    yield
+    L.tcrv_cuda_host_set_fold_order(prev)
+
 
 def make(O, nr, k, nc, seed):
     w = O.quantize_q4_0(O.fill_normal(nr * k, seed, 0, 0.02).reshape(nr, k))
@@ -248,3 +264,47 @@ def test_integer_core_device_and_host_entries(cuda, pkg, O):
     assert L.tcrv_cuda_q4_0_q8_0_integer_core(None, None, None, None, None, 4, None) == -1
     L.tcrv_cuda_host_release()
     pkg.check_device_errors()
+
+
+@pytest.mark.strict_default
+def test_reference_named_gemm_stub_is_byte_exact_with_the_reference_order(cuda, pkg, O):
+    # The generated RVV kernel folds every output in strict ascending block order and its
+    # tests pin byte-exactness on that: the same symbol here must return the same bytes for
+    # decode shapes too (1, 4 and 8 columns take three different kernels when the fast orders
+    # are enabled), and for a prefill-sized call.
+    L = pkg.lib()
+    fn = L.tcrv_emitc_ggml_q4_0_q8_0_gemm_kernel_ggml_q4_0_q8_0_gemm
+    fn.restype = None
+    fn.argtypes = [ctypes.c_size_t, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p] + [ctypes.c_size_t] * 5
+    assert L.tcrv_cuda_host_set_fold_order(FOLD_STRICT) == FOLD_STRICT  # the default
+    nr, k = 200, 4096
+    for nc in (1, 4, 8, 20):
+        w, x = make(O, nr, k, nc, 5100 + nc)
+        wh, xh = np.ascontiguousarray(w), np.ascontiguousarray(x)
+        out = np.full((nr, nc), np.nan, dtype=np.float32)
+        fn(k, out.ctypes.data, wh.ctypes.data, xh.ctypes.data, xh.strides[0], nr, nc, wh.strides[0], nc)
+        want = O.gemm(w, x, fold=O.FOLD_FMA, threads=8)
+        assert np.array_equal(out.view(np.uint32), want.view(np.uint32)), nc
+        out2 = np.full((nr, nc), np.nan, dtype=np.float32)
+        assert L.tcrv_cuda_host_gemm_q4_0_q8_0(k, out2.ctypes.data, wh.ctypes.data, xh.ctypes.data, xh.strides[0], nr, nc,
+                                               wh.strides[0], nc) == 0
+        assert np.array_equal(out2.view(np.uint32), want.view(np.uint32)), nc
+    # Q8_0 weights, and the repacked GEMV: strict by default as well
+    w8 = O.quantize_q8_0(O.fill_normal(48 * k, 5200, 0, 0.02).reshape(48, k))
+    x = O.quantize_q8_0(O.fill_normal(2 * k, 5201).reshape(2, k))
+    out8 = np.empty((48, 2), dtype=np.float32)
+    assert L.tcrv_cuda_host_gemm_q8_0_q8_0(k, out8.ctypes.data, w8.ctypes.data, x.ctypes.data, x.strides[0], 48, 2,
+                                           w8.strides[0], 2) == 0
+    assert np.array_equal(out8.view(np.uint32), O.gemm(w8, x, q8_weights=True, fold=O.FOLD_FMA).view(np.uint32))
+    wx = O.rows_to_q4_0x16(O.quantize_q4_0(O.fill_normal(48 * k, 5300, 0, 0.02).reshape(48, k)))
+    s = np.empty(48, dtype=np.float32)
+    assert L.tcrv_cuda_host_repack_gemv_q4_0_q8_0(k, s.ctypes.data, wx.ctypes.data, x[0].ctypes.data, 48) == 0
+    assert np.array_equal(s.view(np.uint32), O.repack_gemv(wx, x[0], 48).view(np.uint32))
+    # the opt-in: the kernels' own orders, and the setter reports what it replaced
+    assert L.tcrv_cuda_host_set_fold_order(FOLD_FAST) == FOLD_STRICT
+    assert L.tcrv_cuda_host_repack_gemv_q4_0_q8_0(k, s.ctypes.data, wx.ctypes.data, x[0].ctypes.data, 48) == 0
+    assert np.array_equal(s.view(np.uint32),
+                          O.repack_gemv(wx, x[0], 48, parts=pkg.repack_gemv_parts(k)).view(np.uint32))
+    assert L.tcrv_cuda_host_set_fold_order(7) == -1
+    assert L.tcrv_cuda_host_set_fold_order(FOLD_STRICT) == FOLD_FAST
+    L.tcrv_cuda_host_release()

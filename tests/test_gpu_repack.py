@@ -14,12 +14,12 @@ def bits(a):
     return np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)
 
 
-def make_case(O, nc, k, q8w, seed):
+def make_case(O, nc, k, q8w, seed, with_rows=False):
     w = O.fill_normal(nc * k, seed, 0.0, 0.02).reshape(nc, k)
     x = O.quantize_q8_0(O.fill_normal(k, seed + 1).reshape(1, k))
-    if q8w:
-        return O.rows_to_q8_0x16(O.quantize_q8_0(w)), x
-    return O.rows_to_q4_0x16(O.quantize_q4_0(w)), x
+    rows = O.quantize_q8_0(w) if q8w else O.quantize_q4_0(w)
+    wx = O.rows_to_q8_0x16(rows) if q8w else O.rows_to_q4_0x16(rows)
+    return (wx, x, rows) if with_rows else (wx, x)
 
 
 # (weight rows, K): one step, several parts, a ragged last step (K/32 not a multiple of 8),
@@ -30,14 +30,34 @@ SHAPES = [(16, 32), (16, 256), (48, 512), (256, 1024), (160, 4096), (4096, 4096)
 @pytest.mark.parametrize("q8w", [False, True], ids=["q4_0x16", "q8_0x16"])
 @pytest.mark.parametrize("nc,k", SHAPES)
 def test_repack_gemv_bit_exact_in_the_kernel_order(cuda, pkg, O, nc, k, q8w):
-    wx, x = make_case(O, nc, k, q8w, 300 + nc + k)
+    from test_gpu_gemv import check_against_sequential
+
+    wx, x, rows = make_case(O, nc, k, q8w, 300 + nc + k, with_rows=True)
     parts = pkg.repack_gemv_parts(k)
     got = pkg.repack_gemv(dev(cuda, wx), dev(cuda, x[0]), nc, q8_weights=q8w).cpu().numpy()
     want = O.repack_gemv(wx, x[0], nc, q8_weights=q8w, parts=parts)
     assert np.array_equal(bits(got), bits(want))
-    # against the reference's strict block order: same integers, fp32 sums regrouped
+    # against the reference's strict block order: same integers, fp32 sums regrouped -- every
+    # row within rel 1e-5, rows whose terms cancel within 1e-6 * sum|term|
     strict = O.repack_gemv(wx, x[0], nc, q8_weights=q8w)
-    assert np.allclose(got, strict, rtol=0, atol=2e-5 * np.abs(strict).max() + 1e-30)
+    check_against_sequential(got, strict, O.abs_terms(rows, x, q8w)[:, 0], label=f"repack {nc}x{k}")
+    pkg.check_device_errors()
+
+
+@pytest.mark.parametrize("q8w", [False, True], ids=["q4_0x16", "q8_0x16"])
+@pytest.mark.parametrize("nc,k", SHAPES + [(32, 96), (16, 64)])
+def test_repack_gemv_strict_order_flag_is_the_reference_order(cuda, pkg, O, nc, k, q8w):
+    # TCRV_CUDA_FLAG_STRICT_ORDER: lane-wise fma chain over the blocks in ascending order, as the
+    # reference folds (lib/Conversion/RVV/RVVToEmitCBlockQuantLinear.cpp:3262-3298): bit-exact
+    wx, x = make_case(O, nc, k, q8w, 700 + nc + k)
+    got = pkg.repack_gemv(dev(cuda, wx), dev(cuda, x[0]), nc, q8_weights=q8w, flags=pkg.FLAG_STRICT_ORDER)
+    want = O.repack_gemv(wx, x[0], nc, q8_weights=q8w)
+    assert np.array_equal(bits(got.cpu().numpy()), bits(want))
+    # an unaligned weight pointer changes nothing
+    buf = cuda.zeros(wx.size + 16, dtype=cuda.uint8, device="cuda")
+    buf[1:1 + wx.size] = dev(cuda, wx).reshape(-1)
+    got = pkg.repack_gemv(buf[1:1 + wx.size], dev(cuda, x[0]), nc, q8_weights=q8w, flags=pkg.FLAG_STRICT_ORDER)
+    assert np.array_equal(bits(got.cpu().numpy()), bits(want))
     pkg.check_device_errors()
 
 

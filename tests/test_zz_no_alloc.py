@@ -40,6 +40,39 @@ def test_static_scratch_matches_workspace_entry_point_twice(cuda, pkg, O):
     run_both(cuda, pkg, O, 4096, 4096, 512, 4300)
 
 
+def test_static_scratch_call_allocates_no_device_memory(cuda, pkg, O):
+    # The reason the entry exists: once the library and its kernels are loaded (one warm-up
+    # call), a call must not take a single byte from the device allocator.  The driver's own
+    # count of free device memory is read around a call; torch is only asked for the inputs and
+    # the output beforehand.  The activations sit at a row stride larger than the row.
+    L = pkg.lib()
+    nr, k, nc = 640, 2048, 96
+    w = O.quantize_q4_0(O.fill_normal(nr * k, 4400, 0, 0.02).reshape(nr, k))
+    x = O.quantize_q8_0(O.fill_normal(nc * k, 4401).reshape(nc, k))
+    wd = cuda.from_numpy(w).cuda()
+    row = x.shape[1]
+    xpad = cuda.zeros((nc, row + 46), dtype=cuda.uint8, device="cuda")
+    xpad[:, :row] = cuda.from_numpy(x).cuda()
+    got = cuda.empty((nr, nc), dtype=cuda.float32, device="cuda")
+    stream = cuda.cuda.current_stream().cuda_stream
+
+    def call():
+        return L.tcrv_cuda_gemm_q4_0_q8_0_static_scratch(k, got.data_ptr(), wd.data_ptr(), xpad.data_ptr(), xpad.stride(0),
+                                                         nr, nc, wd.stride(0), nc, 0, stream)
+
+    assert call() == 0  # warm-up: module load, function attributes, the scratch address
+    cuda.cuda.synchronize()
+    free_before, _ = cuda.cuda.mem_get_info()
+    for _ in range(3):
+        assert call() == 0
+    cuda.cuda.synchronize()
+    free_after, _ = cuda.cuda.mem_get_info()
+    assert free_after == free_before
+    pkg.check_device_errors()
+    want = O.gemm(w, x, fold=O.FOLD_FMA, threads=8)
+    assert np.array_equal(got.cpu().numpy().view(np.uint32), want.view(np.uint32))
+
+
 def test_static_scratch_rejects_oversize(cuda, pkg):
     L = pkg.lib()
     nr, k, nc = 11008, 4096, 512

@@ -56,6 +56,7 @@ ABI = {
     "tcrv_cuda_vec_scale_f32": [_sz, _p, ctypes.c_float, _p],
     "tcrv_cuda_vec_silu_f32": [_sz, _p, _p, _p],
     "tcrv_cuda_rms_norm_f32": [_sz, _p, _p, ctypes.c_float, _sz, _sz, _sz, _p],
+    "tcrv_cuda_rms_norm_f32_flags": [_sz, _p, _p, ctypes.c_float, _sz, _sz, _sz, ctypes.c_uint, _p],
     "tcrv_cuda_vec_soft_max_f32": [_sz, _p, _p, ctypes.c_float, _p, _p],
     "tcrv_cuda_rope_cache_f32": [_sz, ctypes.c_float, ctypes.c_float, _p, _p, _p],
     "tcrv_cuda_rope_apply_f32": [_sz, _p, _p, _p, _sz, _sz, _sz, _p],
@@ -88,6 +89,7 @@ ABI.update({
     "tcrv_cuda_host_register_weights": [_p, _sz],
     "tcrv_cuda_host_unregister_weights": [_p],
     "tcrv_cuda_host_release": [],
+    "tcrv_cuda_host_set_fold_order": [_i],
     "tcrv_cuda_host_add_f32": [_p, _p, _p, _sz],
     "tcrv_cuda_host_add_i32": [_p, _p, _p, _sz],
     "tcrv_cuda_host_dequantize_i32_f32": [_p, ctypes.c_float, _p, _sz],
@@ -545,16 +547,17 @@ def vec_silu(x, out=None):
     return out
 
 
-def rms_norm(x, eps: float, out=None):
-    """RMS norm over the last dimension of a 2-D (rows, ne00) tensor (row strides honoured)."""
+def rms_norm(x, eps: float, out=None, flags: int = FLAG_NONE):
+    """RMS norm over the last dimension of a 2-D (rows, ne00) tensor (row strides honoured).
+    FLAG_STRICT_ORDER adds the squares in the reference's ascending chain."""
     import torch
 
     if x.dim() != 2 or x.stride(1) != 1 or x.dtype != torch.float32 or not x.is_cuda:
         raise ValueError("x must be a 2-D float32 CUDA tensor with unit inner stride")
     if out is None:
         out = torch.empty((x.shape[0], x.shape[1]), dtype=torch.float32, device=x.device)
-    _check(lib().tcrv_cuda_rms_norm_f32(x.shape[1], x.data_ptr(), out.data_ptr(), eps, x.shape[0], x.stride(0),
-                                        out.stride(0), _stream()), "tcrv_cuda_rms_norm_f32")
+    _check(lib().tcrv_cuda_rms_norm_f32_flags(x.shape[1], x.data_ptr(), out.data_ptr(), eps, x.shape[0], x.stride(0),
+                                              out.stride(0), flags, _stream()), "tcrv_cuda_rms_norm_f32_flags")
     return out
 
 

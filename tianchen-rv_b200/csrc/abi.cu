@@ -100,6 +100,7 @@ int tcrv_cuda_check_device_errors(tcrv_cuda_stream stream) {
   if (word != 0) {
     const int zero = 0;
     TCRV_CUDA_TRY(cudaMemcpyToSymbol(g_device_error, &zero, sizeof zero));
+    host_error_mirror_reset();
     return TCRV_CUDA_ERR_DEVICE_TIMEOUT;
   }
   return TCRV_CUDA_OK;
@@ -293,7 +294,16 @@ int tcrv_cuda_rms_norm_f32(size_t ne00, const float *x, float *y, float eps, siz
     return TCRV_CUDA_OK;
   if (!x || !y || (nrows > 1 && (x_stride < ne00 || y_stride < ne00)))
     return TCRV_CUDA_ERR_INVALID_ARGUMENT;
-  return launch_rms_norm_f32(ne00, x, y, eps, nrows, x_stride, y_stride, as_stream(stream));
+  return launch_rms_norm_f32(ne00, x, y, eps, nrows, x_stride, y_stride, TCRV_CUDA_FLAG_NONE, as_stream(stream));
+}
+
+int tcrv_cuda_rms_norm_f32_flags(size_t ne00, const float *x, float *y, float eps, size_t nrows, size_t x_stride,
+                                 size_t y_stride, unsigned flags, tcrv_cuda_stream stream) {
+  if (ne00 == 0 || nrows == 0)
+    return TCRV_CUDA_OK;
+  if (!x || !y || (nrows > 1 && (x_stride < ne00 || y_stride < ne00)) || (flags & ~TCRV_CUDA_FLAG_STRICT_ORDER) != 0)
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  return launch_rms_norm_f32(ne00, x, y, eps, nrows, x_stride, y_stride, flags, as_stream(stream));
 }
 
 int tcrv_cuda_vec_soft_max_f32(size_t n, float *y, const float *x, float max, double *sum, tcrv_cuda_stream stream) {

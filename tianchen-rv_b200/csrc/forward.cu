@@ -197,6 +197,43 @@ __global__ void __launch_bounds__(kThreads)
   }
 }
 
+// The reference's own summation (TCRV_CUDA_FLAG_STRICT_ORDER): sum = sum + (double)(x_i * x_i)
+// for i = 0, 1, 2, ... as one chain (lib/Conversion/RVV/RVVToEmitCForwardElementwise.cpp:169-234),
+// so the result has the reference's bits for every input, also where the double sum is inexact.
+// One warp per row: the lanes square 32 consecutive elements, and every lane then replays the
+// same 32 dependent additions on values handed round by shuffles.  n dependent double additions
+// per row: tens of microseconds for a row of 11008, however many rows run beside it.
+__global__ void __launch_bounds__(kThreads)
+    rms_norm_strict_kernel(size_t n, const float *x, float *y, float eps, size_t nrows, size_t x_stride,
+                           size_t y_stride) {
+  pdl_enter();
+  const int lane = threadIdx.x & 31;
+  const size_t warps = static_cast<size_t>(gridDim.x) * (kThreads / 32);
+  for (size_t row = static_cast<size_t>(blockIdx.x) * (kThreads / 32) + (threadIdx.x >> 5); row < nrows; row += warps) {
+    const float *xr = x + row * x_stride;
+    float *yr = y + row * y_stride;
+    double sum = 0.0;
+    for (size_t base = 0; base < n; base += 32) {
+      const size_t i = base + lane;
+      const float v = i < n ? xr[i] : 0.0f;
+      const float sq = __fmul_rn(v, v);
+      const int cnt = n - base < 32 ? static_cast<int>(n - base) : 32;  // warp-uniform
+      if (cnt == 32) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          sum = __dadd_rn(sum, static_cast<double>(__shfl_sync(0xffffffffu, sq, j)));
+      } else {
+        for (int j = 0; j < cnt; ++j)
+          sum = __dadd_rn(sum, static_cast<double>(__shfl_sync(0xffffffffu, sq, j)));
+      }
+    }
+    const float mean = __double2float_rn(__ddiv_rn(sum, static_cast<double>(n)));
+    const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, eps)));
+    for (size_t i = lane; i < n; i += 32)
+      yr[i] = __fmul_rn(xr[i], scale);
+  }
+}
+
 // f64 sum of a f32 vector into *sum (one CTA; the vector is one soft-max row).
 __global__ void __launch_bounds__(kThreads) sum_f64_kernel(size_t n, const float *y, double *sum) {
   __shared__ double scratch[kThreads / 32];
@@ -257,9 +294,16 @@ int launch_vec_silu_f32(size_t n, const float *x, float *y, cudaStream_t stream)
 }
 
 int launch_rms_norm_f32(size_t n, const float *x, float *y, float eps, size_t nrows, size_t x_stride, size_t y_stride,
-                        cudaStream_t stream) {
+                        unsigned flags, cudaStream_t stream) {
   if (n == 0 || nrows == 0)
     return TCRV_CUDA_OK;
+  if (flags & TCRV_CUDA_FLAG_STRICT_ORDER) {
+    const size_t want = (nrows + kThreads / 32 - 1) / (kThreads / 32), limit = static_cast<size_t>(sm_count()) * 8;
+    TCRV_CUDA_TRY(launch_pdl(rms_norm_strict_kernel, static_cast<int>(want < limit ? want : limit), kThreads, 0, stream, n,
+                             x, y, eps, nrows, x_stride, y_stride));
+    TCRV_CUDA_TRY(cudaGetLastError());
+    return TCRV_CUDA_OK;
+  }
   const size_t cap = static_cast<size_t>(sm_count()) * 8;
   const int grid = static_cast<int>(nrows < cap ? nrows : cap);
   const bool cached = n % 4 == 0 && n <= static_cast<size_t>(kThreads) * 4 * kRmsRegVec && aligned16(x) && aligned16(y) &&

@@ -3,12 +3,14 @@
 // maps, and the launchers.
 //
 // Planar layout (all regions 256-byte aligned inside the caller's workspace):
-//   weights      int8 [nr][K]            value = nibble - 8
+//   weights      8-bit [nr][K]           value = nibble - 8, as e4m3 (every integer in [-8, 7] is exact)
 //   weight scale fp32 [nr][nbp]          nbp = blocks per row rounded up to 4
-//   activations  int8 [nc][K]
+//   activations  8-bit [nc][K] twice     an int8 q as two e4m3 planes: q & 15 and q - (q & 15), q = sum of both
 //   act. scale   fp32 [nb][ncp]          transposed; ncp = columns rounded up to 4
+// (built with TCRV_GEMM_KIND_I8 the 8-bit matrices are plain int8 and there is one activation plane)
 #include <atomic>
 #include <cuda.h>
+#include <cuda_fp8.h>
 
 #include "gemm_tc.cuh"
 #include "launchers.h"
@@ -17,8 +19,63 @@ namespace tcrv {
 
 namespace {
 
+#ifdef TCRV_GEMM_KIND_I8
+constexpr bool kGemmF8 = false;
+#else
+constexpr bool kGemmF8 = true;
+#endif
+
 constexpr size_t kAlign = 256;
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// Four signed bytes, each an integer that e4m3 represents exactly (|v| <= 16, or a multiple of
+// 16 up to 128), to four e4m3 bytes.
+__device__ __forceinline__ uint32_t e4m3x4_from_s8x4(uint32_t v) {
+  uint32_t r = 0;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const float f = static_cast<float>(static_cast<int>(static_cast<int8_t>(v >> (8 * k))));
+    r |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(f, __NV_SATFINITE, __NV_E4M3)) << (8 * k);
+  }
+  return r;
+}
+
+// Stores 32 weight values (nibble - 8, packed as int8 in lo[4] = elements 0..15 and hi[4] =
+// elements 16..31) in the operand encoding of the tensor-core kernel.
+__device__ __forceinline__ void store_weight_block(int8_t *dst32, const uint32_t (&lo)[4], const uint32_t (&hi)[4]) {
+  uint4 *dst = reinterpret_cast<uint4 *>(dst32);
+  if constexpr (kGemmF8) {
+    dst[0] = make_uint4(e4m3x4_from_s8x4(lo[0]), e4m3x4_from_s8x4(lo[1]), e4m3x4_from_s8x4(lo[2]),
+                        e4m3x4_from_s8x4(lo[3]));
+    dst[1] = make_uint4(e4m3x4_from_s8x4(hi[0]), e4m3x4_from_s8x4(hi[1]), e4m3x4_from_s8x4(hi[2]),
+                        e4m3x4_from_s8x4(hi[3]));
+  } else {
+    dst[0] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+    dst[1] = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+  }
+}
+
+// Stores 32 int8 activation values q[8]: one int8 plane, or the two e4m3 planes q & 15 (0..15)
+// and q & 0xf0 read as a signed byte (16 * (q >> 4): -128, -112, ..., 112), `plane` bytes apart.
+__device__ __forceinline__ void store_act_block(int8_t *dst32, size_t plane, const uint32_t (&q)[8]) {
+  uint4 *dst = reinterpret_cast<uint4 *>(dst32);
+  if constexpr (kGemmF8) {
+    uint32_t l[8], h[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      l[j] = e4m3x4_from_s8x4(q[j] & 0x0f0f0f0fu);
+      h[j] = e4m3x4_from_s8x4(q[j] & 0xf0f0f0f0u);
+    }
+    uint4 *dsth = reinterpret_cast<uint4 *>(dst32 + plane);
+    dst[0] = make_uint4(l[0], l[1], l[2], l[3]);
+    dst[1] = make_uint4(l[4], l[5], l[6], l[7]);
+    dsth[0] = make_uint4(h[0], h[1], h[2], h[3]);
+    dsth[1] = make_uint4(h[4], h[5], h[6], h[7]);
+  } else {
+    dst[0] = make_uint4(q[0], q[1], q[2], q[3]);
+    dst[1] = make_uint4(q[4], q[5], q[6], q[7]);
+  }
+}
 
 // ---------------------------------------------------------------- unpack kernels
 
@@ -50,16 +107,14 @@ __global__ void __launch_bounds__(256) unpack_q4_0_kernel(const uint8_t *__restr
       lo[j] = __vsub4(q[j] & 0x0f0f0f0fu, 0x08080808u);         // elements 4j..4j+3
       hi[j] = __vsub4((q[j] >> 4) & 0x0f0f0f0fu, 0x08080808u);  // elements 16+4j..
     }
-    uint4 *dst = reinterpret_cast<uint4 *>(w8 + (row * nb + ib) * kQK);
-    dst[0] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-    dst[1] = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+    store_weight_block(w8 + (row * nb + ib) * kQK, lo, hi);
     dw[row * nbp + ib] = half_bits_to_float(d);
   }
 }
 
 __global__ void __launch_bounds__(256) unpack_q8_0_kernel(const uint8_t *__restrict__ vy, size_t by, uint32_t nc,
                                                           uint32_t nb, uint32_t ncp, int8_t *__restrict__ x8,
-                                                          float *__restrict__ dxt, bool aligned2) {
+                                                          size_t plane, float *__restrict__ dxt, bool aligned2) {
   const size_t total = static_cast<size_t>(nc) * nb;
   const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
   for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
@@ -78,9 +133,7 @@ __global__ void __launch_bounds__(256) unpack_q8_0_kernel(const uint8_t *__restr
       for (int j = 0; j < 8; ++j)
         q[j] = load_u32_bytes(blk + 2 + 4 * j);
     }
-    uint4 *dst = reinterpret_cast<uint4 *>(x8 + (col * nb + ib) * kQK);
-    dst[0] = make_uint4(q[0], q[1], q[2], q[3]);
-    dst[1] = make_uint4(q[4], q[5], q[6], q[7]);
+    store_act_block(x8 + (col * nb + ib) * kQK, plane, q);
     dxt[ib * ncp + col] = half_bits_to_float(d);
   }
 }
@@ -109,9 +162,7 @@ __global__ void __launch_bounds__(256) unpack_q4_0x16_kernel(const uint8_t *__re
       hi[j] = __vsub4((q >> 4) & 0x0f0f0f0fu, 0x08080808u);
     }
     const size_t row = g * 16 + r;
-    uint4 *dst = reinterpret_cast<uint4 *>(w8 + (row * nb + ib) * kQK);
-    dst[0] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-    dst[1] = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+    store_weight_block(w8 + (row * nb + ib) * kQK, lo, hi);
     dw[row * nbp + ib] = half_bits_to_float(load_u16(blk + 2 * r));
   }
 }
@@ -119,7 +170,7 @@ __global__ void __launch_bounds__(256) unpack_q4_0x16_kernel(const uint8_t *__re
 // One thread per (column group, block, column): block_q8_0x4 (4 fp16 scales, then byte
 // 8 + 4*i + c = element i of column c) to the planar activations.
 __global__ void __launch_bounds__(256) unpack_q8_0x4_kernel(const uint8_t *__restrict__ vy, uint32_t cols, uint32_t nb,
-                                                            uint32_t ncp, int8_t *__restrict__ x8,
+                                                            uint32_t ncp, int8_t *__restrict__ x8, size_t plane,
                                                             float *__restrict__ dxt) {
   const size_t total = static_cast<size_t>(cols) * nb;
   const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
@@ -136,9 +187,7 @@ __global__ void __launch_bounds__(256) unpack_q8_0x4_kernel(const uint8_t *__res
         q[j] |= static_cast<uint32_t>(blk[8 + (4 * j + k) * 4 + c]) << (8 * k);
     }
     const size_t col = y * 4 + c;
-    uint4 *dst = reinterpret_cast<uint4 *>(x8 + (col * nb + ib) * kQK);
-    dst[0] = make_uint4(q[0], q[1], q[2], q[3]);
-    dst[1] = make_uint4(q[4], q[5], q[6], q[7]);
+    store_act_block(x8 + (col * nb + ib) * kQK, plane, q);
     dxt[ib * ncp + col] = half_bits_to_float(load_u16(blk + 2 * c));
   }
 }
@@ -186,6 +235,7 @@ int make_map_2d(CUtensorMap *map, CUtensorMapDataType type, size_t elem_bytes, c
 struct PlanarSizes {
   size_t nb, nbp, ncp, k;
   size_t w8, dw, x8, dxt;  // region sizes (aligned)
+  size_t x_plane;          // one activation plane; x8 holds one (int8) or two (e4m3 low, high)
 };
 
 PlanarSizes planar_sizes(size_t n, size_t nr, size_t nc) {
@@ -196,7 +246,8 @@ PlanarSizes planar_sizes(size_t n, size_t nr, size_t nc) {
   p.k = n;
   p.w8 = align_up(nr * n, kAlign);
   p.dw = align_up(nr * p.nbp * 4, kAlign);
-  p.x8 = align_up(nc * n, kAlign);
+  p.x_plane = align_up(nc * n, kAlign);
+  p.x8 = (kGemmF8 ? 2 : 1) * p.x_plane;
   p.dxt = align_up(p.nb * p.ncp * 4, kAlign);
   return p;
 }
@@ -216,21 +267,29 @@ int run_gemm(size_t n, float *const *dst, size_t ndst, const uint8_t *weights_pl
   const int8_t *x8 = reinterpret_cast<const int8_t *>(acts_planar);
   const float *dxt = reinterpret_cast<const float *>(acts_planar + p.x8);
 
-  CUtensorMap map_w, map_x, map_dw, map_dx;
+  CUtensorMap map_w, map_x, map_xhi, map_dw, map_dx;
   int st = make_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w8, n, nr, n, kGemmStageBlocks * kQK, kGemmTileRows,
                        CU_TENSOR_MAP_SWIZZLE_128B);
+  // activations and their scales are fetched in boxes of 64 columns (two per full tile)
   if (st == TCRV_CUDA_OK)
-    st = make_map_2d(&map_x, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, x8, n, nc, n, kGemmStageBlocks * kQK, kGemmTileCols,
+    st = make_map_2d(&map_x, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, x8, n, nc, n, kGemmStageBlocks * kQK, kGemmHalfCols,
                      CU_TENSOR_MAP_SWIZZLE_128B);
+  if (st == TCRV_CUDA_OK)
+    st = make_map_2d(&map_xhi, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, x8 + (kGemmF8 ? p.x_plane : 0), n, nc, n,
+                     kGemmStageBlocks * kQK, kGemmHalfCols, CU_TENSOR_MAP_SWIZZLE_128B);
   if (st == TCRV_CUDA_OK)
     st = make_map_2d(&map_dw, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, dw, p.nbp, nr, p.nbp * 4, kGemmStageBlocks,
                      kGemmTileRows, CU_TENSOR_MAP_SWIZZLE_NONE);
   if (st == TCRV_CUDA_OK)
-    st = make_map_2d(&map_dx, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, dxt, p.ncp, p.nb, p.ncp * 4, kGemmTileCols,
+    st = make_map_2d(&map_dx, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, dxt, p.ncp, p.nb, p.ncp * 4, kGemmHalfCols,
                      kGemmStageBlocks, CU_TENSOR_MAP_SWIZZLE_NONE);
   if (st != TCRV_CUDA_OK)
     return st;
 
+  const bool multi = ndst > 1;
+  if (repack && multi)
+    return TCRV_CUDA_ERR_UNSUPPORTED;
+  const int sms = sm_count();
   GemmArgs args = {};
   for (size_t d = 0; d < ndst; ++d)
     args.dst[d] = dst[d];
@@ -240,39 +299,48 @@ int run_gemm(size_t n, float *const *dst, size_t ndst, const uint8_t *weights_pl
   args.nc = static_cast<uint32_t>(nc);
   args.nb = static_cast<uint32_t>(p.nb);
   args.tiles_m = static_cast<uint32_t>((nc + kGemmTileCols - 1) / kGemmTileCols);
-  args.tiles = static_cast<uint32_t>((nr + kGemmTileRows - 1) / kGemmTileRows) * args.tiles_m;
+  // Work items: whole tiles round-robin over the CTAs; a last round that would occupy at most
+  // half of them is cut into half-width items instead (see gemm_tc.cuh).
+  const uint32_t tiles = static_cast<uint32_t>((nr + kGemmTileRows - 1) / kGemmTileRows) * args.tiles_m;
+  const uint32_t ctas = static_cast<uint32_t>(sms);
+  const uint32_t rem = tiles % ctas;
+  if (rem != 0 && 2 * rem <= ctas) {
+    args.full_items = tiles - rem;
+    args.items = args.full_items + 2 * rem;
+  } else {
+    args.full_items = tiles;
+    args.items = tiles;
+  }
+  const int grid = static_cast<int>(args.items < ctas ? args.items : ctas);
 
-  const bool multi = ndst > 1;
-  if (repack && multi)
-    return TCRV_CUDA_ERR_UNSUPPORTED;
   const int variant = repack ? 2 : (multi ? 1 : 0);
   static std::atomic<bool> configured[64][3];
   int dev = 0;
   TCRV_CUDA_TRY(cudaGetDevice(&dev));
-  if (dev < 64 && !configured[dev][variant]) {
+  constexpr size_t smem_single = GemmSmem<false, kGemmF8>::kBytes, smem_multi = GemmSmem<true, kGemmF8>::kBytes;
+  if (dev < 0 || dev >= 64)
+    return TCRV_CUDA_ERR_UNSUPPORTED;
+  if (!configured[dev][variant]) {
     if (repack)
-      TCRV_CUDA_TRY(cudaFuncSetAttribute(gemm_q4_0_q8_0_tc_kernel<false, true>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         static_cast<int>(kGemmSmemBytesSingle)));
+      TCRV_CUDA_TRY(cudaFuncSetAttribute(gemm_q4_0_q8_0_tc_kernel<false, true, kGemmF8>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_single)));
     else if (multi)
-      TCRV_CUDA_TRY(cudaFuncSetAttribute(gemm_q4_0_q8_0_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         static_cast<int>(kGemmSmemBytesMulti)));
+      TCRV_CUDA_TRY(cudaFuncSetAttribute(gemm_q4_0_q8_0_tc_kernel<true, false, kGemmF8>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_multi)));
     else
-      TCRV_CUDA_TRY(cudaFuncSetAttribute(gemm_q4_0_q8_0_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         static_cast<int>(kGemmSmemBytesSingle)));
+      TCRV_CUDA_TRY(cudaFuncSetAttribute(gemm_q4_0_q8_0_tc_kernel<false, false, kGemmF8>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_single)));
     configured[dev][variant] = true;
   }
-  const int sms = sm_count();
-  const int grid = static_cast<int>(args.tiles < static_cast<uint32_t>(sms) ? args.tiles : sms);
   if (repack)
-    TCRV_CUDA_TRY(launch_pdl(gemm_q4_0_q8_0_tc_kernel<false, true>, grid, kGemmThreads, kGemmSmemBytesSingle, stream,
-                             map_w, map_x, map_dw, map_dx, args));
+    TCRV_CUDA_TRY(launch_pdl(gemm_q4_0_q8_0_tc_kernel<false, true, kGemmF8>, grid, kGemmThreads, smem_single, stream,
+                             map_w, map_x, map_xhi, map_dw, map_dx, args));
   else if (multi)
-    TCRV_CUDA_TRY(launch_pdl(gemm_q4_0_q8_0_tc_kernel<true>, grid, kGemmThreads, kGemmSmemBytesMulti, stream, map_w,
-                             map_x, map_dw, map_dx, args));
+    TCRV_CUDA_TRY(launch_pdl(gemm_q4_0_q8_0_tc_kernel<true, false, kGemmF8>, grid, kGemmThreads, smem_multi, stream,
+                             map_w, map_x, map_xhi, map_dw, map_dx, args));
   else
-    TCRV_CUDA_TRY(launch_pdl(gemm_q4_0_q8_0_tc_kernel<false>, grid, kGemmThreads, kGemmSmemBytesSingle, stream, map_w,
-                             map_x, map_dw, map_dx, args));
+    TCRV_CUDA_TRY(launch_pdl(gemm_q4_0_q8_0_tc_kernel<false, false, kGemmF8>, grid, kGemmThreads, smem_single, stream,
+                             map_w, map_x, map_xhi, map_dw, map_dx, args));
   TCRV_CUDA_TRY(cudaGetLastError());
   return TCRV_CUDA_OK;
 }
@@ -324,7 +392,7 @@ int launch_gemm_prepare_acts_q8_0(size_t n, const uint8_t *vy, size_t by, size_t
   unpack_q8_0_kernel<<<blocks_for(nc * p.nb), 256, 0, stream>>>(vy, by, static_cast<uint32_t>(nc),
                                                                 static_cast<uint32_t>(p.nb),
                                                                 static_cast<uint32_t>(p.ncp),
-                                                                reinterpret_cast<int8_t *>(prepared),
+                                                                reinterpret_cast<int8_t *>(prepared), p.x_plane,
                                                                 reinterpret_cast<float *>(prepared + p.x8), aligned2);
   TCRV_CUDA_TRY(cudaGetLastError());
   return TCRV_CUDA_OK;
@@ -375,7 +443,7 @@ int launch_repack_gemm_prepared(size_t n, float *s, const uint8_t *weights_plana
     TCRV_CUDA_TRY(cudaMemsetAsync(acts_planar + p.x8, 0, p.nb * p.ncp * 4, stream));
   unpack_q8_0x4_kernel<<<blocks_for(tokens * p.nb), 256, 0, stream>>>(
       vy, static_cast<uint32_t>(tokens), static_cast<uint32_t>(p.nb), static_cast<uint32_t>(p.ncp),
-      reinterpret_cast<int8_t *>(acts_planar), reinterpret_cast<float *>(acts_planar + p.x8));
+      reinterpret_cast<int8_t *>(acts_planar), p.x_plane, reinterpret_cast<float *>(acts_planar + p.x8));
   TCRV_CUDA_TRY(cudaGetLastError());
   return run_gemm(n, &s, 1, weights_planar, acts_planar, wrows, tokens, bs, stream, /*repack=*/true);
 }

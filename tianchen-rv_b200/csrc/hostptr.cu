@@ -12,6 +12,7 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <atomic>
 #include <chrono>
 #include <map>
 #include <mutex>
@@ -60,9 +61,29 @@ struct HostContext {
   std::map<const void *, ResidentWeights> weights;
 };
 
+// One context per device ordinal: stream, arena, resident weights and error mirror belong to
+// the device that is current when the call is made.  (If the current device cannot be read the
+// first slot is used and the CUDA calls that follow report the failure.)
+constexpr int kMaxDevices = 64;
+
 HostContext &ctx() {
-  static HostContext c;
-  return c;
+  static HostContext contexts[kMaxDevices];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    (void)cudaGetLastError();
+    dev = 0;
+  }
+  return contexts[dev];
+}
+
+// Summation order of the matrix entries that take no flags (the reference's signatures have
+// none): 0 = the reference's strict ascending block order (default, byte-exact with the
+// generated kernel), 1 = the streaming kernels' own orders.  See tcrv_cuda_host_set_fold_order.
+std::atomic<int> g_host_fold_order{TCRV_CUDA_HOST_FOLD_STRICT};
+
+unsigned default_fold_flags() {
+  return g_host_fold_order.load(std::memory_order_relaxed) == TCRV_CUDA_HOST_FOLD_STRICT ? TCRV_CUDA_FLAG_STRICT_ORDER
+                                                                                          : TCRV_CUDA_FLAG_NONE;
 }
 
 inline size_t up256(size_t v) { return (v + 255) / 256 * 256; }
@@ -174,8 +195,13 @@ int finish(HostContext &c) {
       break;
     }
   }
-  if (c.error_word != nullptr && *reinterpret_cast<volatile int *>(c.error_word) != 0)
+  if (c.error_word != nullptr && *reinterpret_cast<volatile int *>(c.error_word) != 0) {
+    // reported once: clear the mirror and the device word so that later calls start clean
+    *reinterpret_cast<volatile int *>(c.error_word) = 0;
+    const int zero = 0;
+    (void)cudaMemcpyToSymbol(g_device_error, &zero, sizeof zero);
     return TCRV_CUDA_ERR_DEVICE_TIMEOUT;
+  }
   return TCRV_CUDA_OK;
 }
 
@@ -190,6 +216,19 @@ int ensure_error_mirror(HostContext &c) {
   TCRV_CUDA_TRY(cudaMemcpyToSymbol(g_host_error_mirror, &dev, sizeof dev));
   return TCRV_CUDA_OK;
 }
+
+}  // namespace
+
+// Clears the current device's host mirror of the error word (tcrv_cuda_check_device_errors has
+// just reported and cleared the device word).
+void host_error_mirror_reset() {
+  HostContext &c = ctx();
+  std::lock_guard<std::mutex> lock(c.mu);
+  if (c.error_word != nullptr)
+    *reinterpret_cast<volatile int *>(c.error_word) = 0;
+}
+
+namespace {
 
 template <typename T, typename Launch>
 int host_binary(const T *lhs, const T *rhs, T *out, size_t n, Launch launch) {
@@ -221,7 +260,7 @@ int host_matmul_locked(HostContext &c, bool q8_weights, size_t n, float *s, cons
 
 // s[ir*bs + col] for host operands; q8_weights selects the Q8_0 x Q8_0 block dot.
 int host_matmul(bool q8_weights, size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by, size_t nr,
-                size_t nc, size_t bx, size_t bs, unsigned flags = TCRV_CUDA_FLAG_NONE) {
+                size_t nc, size_t bx, size_t bs, unsigned flags) {
   if (n % kQK != 0)
     return TCRV_CUDA_ERR_INVALID_ARGUMENT;
   if (nr == 0 || nc == 0)
@@ -462,7 +501,7 @@ int host_forward(ForwardOp op, size_t n, const float *x, float *y, float param, 
       st = launch_vec_silu_f32(n, dx, dy, c.stream);
       break;
     case ForwardOp::RmsNorm:
-      st = launch_rms_norm_f32(n, dx, dy, param, 1, n, n, c.stream);
+      st = launch_rms_norm_f32(n, dx, dy, param, 1, n, n, default_fold_flags(), c.stream);
       break;
     case ForwardOp::SoftMax:
       st = launch_vec_soft_max_f32(n, dy, dx, param, dsum, c.stream);
@@ -615,7 +654,13 @@ int tcrv_cuda_host_quantize_row_q8_0(size_t n, const float *x, uint8_t *vy) {
 
 int tcrv_cuda_host_gemm_q4_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by, size_t nr,
                                   size_t nc, size_t bx, size_t bs) {
-  return host_matmul(false, n, s, vx, vy, by, nr, nc, bx, bs);
+  return host_matmul(false, n, s, vx, vy, by, nr, nc, bx, bs, default_fold_flags());
+}
+
+int tcrv_cuda_host_set_fold_order(int order) {
+  if (order != TCRV_CUDA_HOST_FOLD_STRICT && order != TCRV_CUDA_HOST_FOLD_FAST)
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  return g_host_fold_order.exchange(order);
 }
 
 int tcrv_cuda_host_q4_0_q8_0_integer_core(const int8_t *w, const int8_t *qlo, const int8_t *qhi, const int32_t *acc,
@@ -670,7 +715,7 @@ void tcrv_emitc_ggml_q4_0_q8_0_gemm_tile_kernel_ggml_q4_0_q8_0_gemm_tile(size_t 
 
 int tcrv_cuda_host_gemm_q8_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by, size_t nr,
                                   size_t nc, size_t bx, size_t bs) {
-  return host_matmul(true, n, s, vx, vy, by, nr, nc, bx, bs);
+  return host_matmul(true, n, s, vx, vy, by, nr, nc, bx, bs, default_fold_flags());
 }
 
 // ---- reference-named entry points (fixture kernel symbol + variant symbol) ----
@@ -810,8 +855,8 @@ int host_repack_gemv(bool q8w, size_t n, float *s, const uint8_t *vx, const uint
   if (nb == 0)
     TCRV_CUDA_TRY(cudaMemsetAsync(ds, 0, nc * sizeof(float), c.stream));
   else
-    st = q8w ? launch_repack_gemv_q8_0_q8_0(n, ds, dw, dx, nc, 0, c.stream)
-             : launch_repack_gemv_q4_0_q8_0(n, ds, dw, dx, nc, 0, c.stream);
+    st = q8w ? launch_repack_gemv_q8_0_q8_0(n, ds, dw, dx, nc, default_fold_flags(), c.stream)
+             : launch_repack_gemv_q4_0_q8_0(n, ds, dw, dx, nc, default_fold_flags(), c.stream);
   if (st != TCRV_CUDA_OK)
     return st;
   TCRV_CUDA_TRY(cudaMemcpyAsync(s, ds, nc * sizeof(float), cudaMemcpyDeviceToHost, c.stream));
@@ -995,7 +1040,7 @@ void tcrv_emitc_ggml_vec_dot_q8_0_q8_0_kernel_ggml_vec_dot_q8_0_q8_0(size_t n, f
 void tcrv_emitc_ggml_q4_0_q8_0_gemm_kernel_ggml_q4_0_q8_0_gemm(size_t n, float *s, const uint8_t *vx,
                                                                const uint8_t *vy, size_t by, size_t nr, size_t nc,
                                                                size_t bx, size_t bs) {
-  must(host_matmul(false, n, s, vx, vy, by, nr, nc, bx, bs), __func__);
+  must(host_matmul(false, n, s, vx, vy, by, nr, nc, bx, bs, default_fold_flags()), __func__);
 }
 
 }  // extern "C"

@@ -14,7 +14,7 @@ int launch_add_i32(const int32_t *lhs, const int32_t *rhs, int32_t *out, size_t 
 int launch_vec_scale_f32(size_t n, float *y, float v, cudaStream_t stream);
 int launch_vec_silu_f32(size_t n, const float *x, float *y, cudaStream_t stream);
 int launch_rms_norm_f32(size_t n, const float *x, float *y, float eps, size_t nrows, size_t x_stride, size_t y_stride,
-                        cudaStream_t stream);
+                        unsigned flags, cudaStream_t stream);
 int launch_vec_soft_max_f32(size_t n, float *y, const float *x, float max, double *sum, cudaStream_t stream);
 int launch_rope_cache_f32(size_t n_dims, float theta_base, float theta_scale, float *cache, float *thetas,
                           cudaStream_t stream);
@@ -78,6 +78,8 @@ int launch_gemm_prepared_multi(size_t n, float *const *dst, size_t ndst, const u
 }  // namespace tcrv
 
 namespace tcrv {
+// Host-pointer layer: clears the current device's mapped mirror of the device error word.
+void host_error_mirror_reset();
 // Tiled TMA descriptor over a matrix of 16-bit elements (rows `row_stride_bytes` apart), no swizzle.
 int encode_tensor_map_2d_u16(CUtensorMap *map, const void *base, uint64_t inner_elems, uint64_t outer,
                              uint64_t row_stride_bytes, uint32_t box_inner_elems, uint32_t box_outer);

@@ -346,6 +346,55 @@ __global__ void __launch_bounds__(256) repack_gemv_generic_kernel(const uint8_t 
   }
 }
 
+// The reference's own order (TCRV_CUDA_FLAG_STRICT_ORDER): every output row folds its blocks
+// one after the other, acc = fma((float)sumi, d_w * d_a, acc) for block 0, 1, 2, ... from 0.0f,
+// which is what the lane-wise vfmacc chain of the RVV kernel computes
+// (lib/Conversion/RVV/RVVToEmitCBlockQuantLinear.cpp:3262-3298).  One warp per row group: lane
+// 16*h + r owns row r and takes the integer sums of the blocks with index parity h; the two
+// halves exchange them so that the lower half folds block 2m and then block 2m+1.  A chain of
+// nb dependent FMAs per row cannot be fast; this path exists for byte-exact comparison.
+template <bool kQ8W>
+__global__ void __launch_bounds__(256) repack_gemv_strict_kernel(const uint8_t *__restrict__ vx,
+                                                                 const uint8_t *__restrict__ vy,
+                                                                 float *__restrict__ s, uint32_t nb, uint32_t groups) {
+  using F = X16<kQ8W>;
+  const int lane = threadIdx.x & 31;
+  const uint32_t r = lane & 15, h = lane >> 4;
+  const uint32_t warps = (gridDim.x * blockDim.x) >> 5;
+  for (uint32_t g = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; g < groups; g += warps) {
+    float acc = 0.0f;
+    for (uint32_t l0 = 0; l0 < nb; l0 += 2) {
+      const uint32_t l = l0 + h;
+      float f = 0.0f, scale = 0.0f;
+      if (l < nb) {
+        const uint8_t *bl = vx + (static_cast<size_t>(g) * nb + l) * F::kBlockBytes;
+        const uint8_t *al = vy + static_cast<size_t>(l) * kQ8Block;
+        int sumi = 0;
+        if constexpr (kQ8W) {
+          for (int i = 0; i < 32; ++i)
+            sumi += static_cast<int8_t>(bl[32 + 16 * i + r]) * static_cast<int8_t>(al[2 + i]);
+        } else {
+          for (int i = 0; i < 16; ++i) {
+            const uint8_t t = bl[32 + 16 * i + r];  // two's-complement nibbles (the xor is in the layout)
+            const int v0 = static_cast<int8_t>(static_cast<uint8_t>(t << 4)) >> 4, v1 = static_cast<int8_t>(t) >> 4;
+            sumi += v0 * static_cast<int8_t>(al[2 + i]) + v1 * static_cast<int8_t>(al[18 + i]);
+          }
+        }
+        f = __int2float_rn(sumi);
+        scale = __fmul_rn(half_bits_to_float(load_u16(bl + 2 * r)), half_bits_to_float(load_u16(al)));
+      }
+      const float f1 = __shfl_sync(0xffffffffu, f, r + 16), scale1 = __shfl_sync(0xffffffffu, scale, r + 16);
+      if (h == 0) {
+        acc = __fmaf_rn(f, scale, acc);
+        if (l0 + 1 < nb)
+          acc = __fmaf_rn(f1, scale1, acc);
+      }
+    }
+    if (h == 0)
+      s[static_cast<size_t>(g) * 16 + r] = acc;
+  }
+}
+
 template <bool kQ8W>
 int launch_repack_gemv_impl(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t nc, unsigned flags,
                             cudaStream_t stream) {
@@ -353,6 +402,13 @@ int launch_repack_gemv_impl(size_t n, float *s, const uint8_t *vx, const uint8_t
   const size_t nb = n / kQK, groups = nc / 16;
   if (nb == 0 || groups == 0)
     return TCRV_CUDA_OK;
+  if (flags & TCRV_CUDA_FLAG_STRICT_ORDER) {
+    const size_t want = (groups + 7) / 8, cap = static_cast<size_t>(sm_count()) * 16;
+    repack_gemv_strict_kernel<kQ8W><<<static_cast<int>(want < cap ? want : cap), 256, 0, stream>>>(
+        vx, vy, s, static_cast<uint32_t>(nb), static_cast<uint32_t>(groups));
+    TCRV_CUDA_TRY(cudaGetLastError());
+    return TCRV_CUDA_OK;
+  }
   RepackGemvArgs args = {};
   args.vx = vx;
   args.vy = vy;

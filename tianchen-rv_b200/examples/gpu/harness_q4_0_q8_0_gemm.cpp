@@ -1,7 +1,10 @@
 // GPU harness for the Q4_0 x Q8_0 GEMM (fixture test/fixtures/cuda-q4-0-q8-0-gemm.mlir):
-// the prefill shape class (nc > 8, tensor-core kernel, bit-exact with the scalar fold) and
-// the decode shape class (nc <= 8, streaming kernel, within rel 1e-5 of the scalar fold).
+// the prefill shape class (nc > 8, tensor-core kernel) and the decode shape class (nc <= 8),
+// both bit-exact with the scalar fold in strict block order, which is the library's default
+// for this entry; then the decode class once more with the streaming kernels' own summation
+// orders switched on (tcrv_cuda_host_set_fold_order), within rel 1e-5 of the scalar fold.
 #include "harness_common.h"
+#include "tcrv_emitc_host.h"
 
 extern "C" void tcrv_emitc_ggml_q4_0_q8_0_gemm_kernel_ggml_q4_0_q8_0_gemm(size_t n, float *s, const uint8_t *vx,
                                                                           const uint8_t *vy, size_t by, size_t nr,
@@ -41,7 +44,12 @@ int main() {
   harness::Rng rng(4);
   size_t checked = 0;
   if (run(1024, 200, 70, true, rng, checked) || run(4096, 256, 128, true, rng, checked) ||
-      run(4096, 300, 1, false, rng, checked) || run(2048, 129, 8, false, rng, checked))
+      run(4096, 300, 1, true, rng, checked) || run(2048, 129, 8, true, rng, checked))
+    return 1;
+  if (tcrv_cuda_host_set_fold_order(TCRV_CUDA_HOST_FOLD_FAST) != TCRV_CUDA_HOST_FOLD_STRICT)
+    return 1;
+  if (run(4096, 300, 1, false, rng, checked) || run(2048, 129, 4, false, rng, checked) ||
+      run(2048, 129, 8, false, rng, checked))
     return 1;
   std::printf("q4_0_q8_0_gemm proof ok: %zu outputs checked\n", checked);
   return 0;
