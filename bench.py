@@ -184,6 +184,16 @@ def run_ours(args):
 
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
+    if args.gemm_only:
+        # the prefill-GEMM section alone (N-sharded over the ranks): a short run for tuning and
+        # profiling; prints its own object, not the benchmark line
+        gemm = measure_gemm(pkg, torch, dist, rank, world)
+        if rank == 0:
+            print(json.dumps({"gemm_only": True, "n_gpus": world, "gemm": gemm}))
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
@@ -477,36 +487,57 @@ def measure_e2e(pkg, torch, layers, steps, dist):
             raise RuntimeError(f"register_weights failed: {st}")
         host.append((l, w_host, x_host, y_host))
     # the argument lists are fixed: build them once so that the timed loop is the C call itself
-    fn = L.tcrv_cuda_host_gemm_q4_0_q8_0
     calls = [(l["k"], y_host.data_ptr(), w_host.ctypes.data, x_host.data_ptr(), x_host.stride(0), l["nr"], 1,
               w_host.strides[0], 1) for l, w_host, x_host, y_host in host]
 
-    def one_pass():
+    def one_pass_blocking():
+        # one synchronous call per layer: every call returns with its result in host memory
         for args in calls:
-            st = fn(*args)
+            st = L.tcrv_cuda_host_gemm_q4_0_q8_0(*args)
             if st != 0:
                 raise RuntimeError(f"host gemv failed: {st}")
 
-    for _ in range(3):
+    def one_pass_queued():
+        # the four layers of a step queued one after the other, one wait at the end of the step
+        for args in calls:
+            st = L.tcrv_cuda_host_gemm_q4_0_q8_0_async(*args)
+            if st != 0:
+                raise RuntimeError(f"host gemv failed: {st}")
+        st = L.tcrv_cuda_host_sync()
+        if st != 0:
+            raise RuntimeError(f"host sync failed: {st}")
+
+    def check():
+        # the resident path must agree with the device-pointer path
+        for l, w_host, x_host, y_host in host:
+            pkg.gemv(l["w"][0], l["x"], out=l["y"])
+            torch.cuda.synchronize()
+            if not torch.equal(l["y"].cpu(), y_host):
+                raise RuntimeError("host-pointer path disagrees with the device-pointer path")
+            y_host.fill_(float("nan"))
+
+    def timed(one_pass):
+        for _ in range(3):
+            one_pass()
+        check()
         one_pass()
-    # the resident path must agree with the device-pointer path
-    for l, w_host, x_host, y_host in host:
-        pkg.gemv(l["w"][0], l["x"], out=l["y"])
-        torch.cuda.synchronize()
-        if not torch.equal(l["y"].cpu(), y_host):
-            raise RuntimeError("host-pointer path disagrees with the device-pointer path")
-    if dist is not None:
-        dist.barrier()
-    t0 = time.perf_counter()
-    for _ in range(steps):
-        one_pass()
-    dt = time.perf_counter() - t0
-    world = 1
-    if dist is not None:
-        t = torch.tensor([dt], dtype=torch.float64, device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        dt = float(t.item())
-        world = dist.get_world_size()
+        if dist is not None:
+            dist.barrier()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            one_pass()
+        dt = time.perf_counter() - t0
+        if dist is not None:
+            t = torch.tensor([dt], dtype=torch.float64, device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            dt = float(t.item())
+        return dt
+
+    dt_blocking = timed(one_pass_blocking)
+    dt = timed(one_pass_queued)
+    one_pass_queued()
+    check()
+    world = dist.get_world_size() if dist is not None else 1
     for l, w_host, x_host, y_host in host:
         L.tcrv_cuda_host_unregister_weights(w_host.ctypes.data)
     L.tcrv_cuda_host_release()
@@ -516,6 +547,11 @@ def measure_e2e(pkg, torch, layers, steps, dist):
             "h2d_bytes_per_step": sum(int(x.numel()) for _, _, x, _ in host),
             "d2h_bytes_per_step": sum(int(y.numel()) * 4 for _, _, _, y in host),
             "ms_per_step": round(dt / steps * 1e3, 4), "steps": steps,
+            "call": "tcrv_cuda_host_gemm_q4_0_q8_0_async per layer + tcrv_cuda_host_sync per step (one host round trip "
+                    "per step)",
+            "blocking_calls": {"value": round(step_bytes * steps * world / dt_blocking / 1e9, 2),
+                               "ms_per_step": round(dt_blocking / steps * 1e3, 4),
+                               "call": "tcrv_cuda_host_gemm_q4_0_q8_0 per layer (each call waits for its result)"},
             "fold_order": "TCRV_CUDA_HOST_FOLD_FAST (lane pairs), selected with tcrv_cuda_host_set_fold_order",
             "weights": "registered once (resident); activations and outputs cross PCIe every step "
                        "(inputs by a copy from the pinned buffer, results stored by the kernel into the pinned "
@@ -821,6 +857,7 @@ def main():
     ap.add_argument("--min-warm-seconds", type=float, default=MIN_WARM_SECONDS,
                     help="warm-up lasts at least this long (0 for a profiler's launch-list pass)")
     ap.add_argument("--skip-gemm", action="store_true", help="leave out the prefill-GEMM section")
+    ap.add_argument("--gemm-only", action="store_true", help="run the prefill-GEMM section alone (not the benchmark line)")
     ap.add_argument("--graph-steps", type=int, default=GRAPH_STEPS, help="most steps captured per CUDA graph of the timed region")
     ap.add_argument("--regions", type=int, default=MIN_REGIONS, help="how often the K-step region is timed (median reported)")
     ap.add_argument("--min-timed-ms", type=float, default=MIN_TIMED_MS,

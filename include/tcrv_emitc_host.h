@@ -71,6 +71,17 @@ int tcrv_cuda_host_repack_gemm_q4_0_q8_0(size_t n, float *s, const uint8_t *vx, 
 /* nc <= 8 runs the decode GEMV (order: tcrv_cuda_host_set_fold_order), larger nc the tensor-core GEMM. */
 int tcrv_cuda_host_gemm_q4_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by, size_t nr,
                                   size_t nc, size_t bx, size_t bs);
+/* Queued twins of the two calls above, for a caller that issues several operations before it
+ * needs any result (the layers of one decode step): the call returns once its work is queued
+ * on the current device's stream; tcrv_cuda_host_sync() waits for everything queued so far
+ * and reports a failure of any of it.  Between the call and the sync the caller must neither
+ * read the output buffer nor change the inputs (page-locked inputs are read by the GPU after
+ * the call returns; pageable ones have been staged by then).  Queued calls run in call order. */
+int tcrv_cuda_host_gemm_q4_0_q8_0_async(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by, size_t nr,
+                                        size_t nc, size_t bx, size_t bs);
+int tcrv_cuda_host_gemm_q8_0_q8_0_async(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by, size_t nr,
+                                        size_t nc, size_t bx, size_t bs);
+int tcrv_cuda_host_sync(void);
 /* One weight row against `cols` (1..16) activation columns, strict block order per column. */
 int tcrv_cuda_host_gemm_tile_q4_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by,
                                        size_t cols);

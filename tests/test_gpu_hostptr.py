@@ -308,3 +308,37 @@ def test_reference_named_gemm_stub_is_byte_exact_with_the_reference_order(cuda, 
     assert L.tcrv_cuda_host_set_fold_order(7) == -1
     assert L.tcrv_cuda_host_set_fold_order(FOLD_STRICT) == FOLD_FAST
     L.tcrv_cuda_host_release()
+
+
+@pytest.mark.parametrize("pinned", [False, True])
+def test_queued_host_calls_complete_at_the_sync(cuda, pkg, O, pinned):
+    # Four layers queued with the _async twins and one tcrv_cuda_host_sync: the results must be
+    # those of the blocking calls, on the first (direct), second (captured) and later (replayed)
+    # rounds, with resident weights and with weights uploaded per call.
+    L = pkg.lib()
+    shapes = [(96, 1024), (200, 512), (64, 2048), (130, 1024)]
+    layers = []
+    for i, (nr, k) in enumerate(shapes):
+        w, x = make(O, nr, k, 1, 6100 + i)
+        wh = np.ascontiguousarray(w)
+        xt = cuda.from_numpy(x.copy())
+        yt = cuda.empty((nr, 1), dtype=cuda.float32)
+        if pinned:
+            xt, yt = xt.pin_memory(), yt.pin_memory()
+        layers.append((nr, k, w, x, wh, xt, yt))
+    for nr, k, w, x, wh, xt, yt in layers[:2]:
+        assert L.tcrv_cuda_host_register_weights(wh.ctypes.data, wh.nbytes) == 0
+    try:
+        for rnd in range(4):
+            for nr, k, w, x, wh, xt, yt in layers:
+                yt.fill_(float("nan"))
+                assert L.tcrv_cuda_host_gemm_q4_0_q8_0_async(k, yt.data_ptr(), wh.ctypes.data, xt.data_ptr(), xt.stride(0),
+                                                             nr, 1, wh.strides[0], 1) == 0
+            assert L.tcrv_cuda_host_sync() == 0
+            for nr, k, w, x, wh, xt, yt in layers:
+                assert np.array_equal(yt.numpy().view(np.uint32), O.gemv_lane_order(w, x).view(np.uint32)), rnd
+        assert L.tcrv_cuda_host_sync() == 0  # nothing queued: returns at once
+    finally:
+        for nr, k, w, x, wh, xt, yt in layers[:2]:
+            L.tcrv_cuda_host_unregister_weights(wh.ctypes.data)
+        L.tcrv_cuda_host_release()

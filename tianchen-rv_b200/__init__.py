@@ -110,6 +110,9 @@ ABI.update({
     "tcrv_cuda_host_repack_gemm_q4_0_q8_0": [_sz, _p, _p, _p, _sz, _sz, _sz],
     "tcrv_cuda_host_gemm_q4_0_q8_0": [_sz, _p, _p, _p, _sz, _sz, _sz, _sz, _sz],
     "tcrv_cuda_host_gemm_q8_0_q8_0": [_sz, _p, _p, _p, _sz, _sz, _sz, _sz, _sz],
+    "tcrv_cuda_host_gemm_q4_0_q8_0_async": [_sz, _p, _p, _p, _sz, _sz, _sz, _sz, _sz],
+    "tcrv_cuda_host_gemm_q8_0_q8_0_async": [_sz, _p, _p, _p, _sz, _sz, _sz, _sz, _sz],
+    "tcrv_cuda_host_sync": [],
 })
 
 _RESTYPES = {

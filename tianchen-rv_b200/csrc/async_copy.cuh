@@ -45,11 +45,32 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
   return done != 0;
 }
 
+// The same test with a suspend-time hint: the thread may sleep in hardware for up to `hint_ns`
+// and is woken when the phase completes, instead of returning at once.  A waiter that spins on
+// the plain form re-reads the barrier word every few cycles; with many warps waiting on one
+// barrier those reads compete with the arrivals on the same word and with the other warps'
+// issue slots.
+__device__ __forceinline__ bool mbar_try_wait_suspend(uint64_t *bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}"
+      : "=r"(done)
+      : "r"(smem_addr(bar)), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return done != 0;
+}
+
 // Bounded wait for the phase with the given parity: gives up after kMbarTimeoutNs of wall
-// time (the global nanosecond timer is sampled every 256 polls), far beyond any legitimate
-// wait of these kernels (microseconds).  `abort_flag`, when given, is a shared-memory word
-// another role sets after its own wait failed, so that the whole CTA leaves promptly.
+// time, far beyond any legitimate wait of these kernels (microseconds).  Each poll may sleep up
+// to kMbarSuspendNs in hardware (see mbar_try_wait_suspend); the global nanosecond timer is
+// read every 16 polls.  `abort_flag`, when given, is a shared-memory word another role sets
+// after its own wait failed, so that the whole CTA leaves promptly.
 constexpr uint64_t kMbarTimeoutNs = 2000000000ull;
+constexpr uint32_t kMbarSuspendNs = 20000u;
 
 __device__ __forceinline__ uint64_t global_timer_ns() {
   uint64_t t;
@@ -61,35 +82,17 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity
                                                   volatile uint32_t *abort_flag = nullptr) {
   if (mbar_try_wait(bar, parity))
     return true;
-  const uint64_t start = global_timer_ns();
+  uint64_t start = 0;
   for (uint32_t i = 1;; ++i) {
-    if (mbar_try_wait(bar, parity))
+    if (mbar_try_wait_suspend(bar, parity, kMbarSuspendNs))
       return true;
-    if ((i & 255u) == 0) {
+    if ((i & 15u) == 0) {
       if (abort_flag != nullptr && *abort_flag != 0)
         return false;
-      if (global_timer_ns() - start > kMbarTimeoutNs)
-        return false;
-    }
-  }
-}
-
-// The same bounded wait for warps that share a scheduler with a latency-critical issuing
-// thread: between polls the warp sleeps a few tens of nanoseconds instead of spinning, so
-// that its polling does not take issue slots away from that thread.
-__device__ __forceinline__ bool mbar_wait_bounded_relaxed(uint64_t *bar, uint32_t parity,
-                                                          volatile uint32_t *abort_flag = nullptr) {
-  if (mbar_try_wait(bar, parity))
-    return true;
-  const uint64_t start = global_timer_ns();
-  for (uint32_t i = 1;; ++i) {
-    __nanosleep(32);
-    if (mbar_try_wait(bar, parity))
-      return true;
-    if ((i & 255u) == 0) {
-      if (abort_flag != nullptr && *abort_flag != 0)
-        return false;
-      if (global_timer_ns() - start > kMbarTimeoutNs)
+      const uint64_t now = global_timer_ns();
+      if (start == 0)
+        start = now;
+      else if (now - start > kMbarTimeoutNs)
         return false;
     }
   }

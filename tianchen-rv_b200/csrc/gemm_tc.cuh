@@ -525,24 +525,33 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           if (!ok)
             break;
           tcgen05_fence_after_thread_sync();
+          // Operand descriptors of the stage's first block; a block further along K is 32 bytes
+          // further inside the 128-byte swizzled rows, i.e. +2 in the descriptor's 16-byte
+          // address field.  One thread feeds the tensor core, so its per-block work is kept to
+          // a wait, one addition per operand and the instructions themselves.
           const uint32_t a_addr = stage_base_addr + ps.stage * Stage::kBytes;
-          const uint32_t b_addr = a_addr + Stage::kOffB;
+          const uint64_t da0 = umma_desc_k_major_sw128(a_addr);
+          const uint64_t db0 = umma_desc_k_major_sw128(a_addr + Stage::kOffB);
+          [[maybe_unused]] const uint64_t dh0 = umma_desc_k_major_sw128(a_addr + Stage::kOffB + kGemmBPlaneBytes);
           const uint32_t steps = min(static_cast<uint32_t>(kGemmStageBlocks), a.nb - kb * kGemmStageBlocks);
-          for (uint32_t kk = 0; kk < steps; ++kk) {
-            ok = mbar_wait_bounded(&tmem_empty[ts.stage], ts.phase ^ 1, abort_flag);
-            if (!ok)
-              break;
-            tcgen05_fence_after_thread_sync();
-            const uint32_t d_tmem = tmem_base + ts.stage * kGemmTileCols;
-            const uint64_t da = umma_desc_k_major_sw128(a_addr + kk * kQK);
-            if constexpr (kF8) {
-              umma_f8_ss(d_tmem, da, umma_desc_k_major_sw128(b_addr + kk * kQK), idesc, 0u);
-              umma_f8_ss(d_tmem, da, umma_desc_k_major_sw128(b_addr + kGemmBPlaneBytes + kk * kQK), idesc, 1u);
-            } else {
-              umma_s8_ss(d_tmem, da, umma_desc_k_major_sw128(b_addr + kk * kQK), idesc, 0u);
+#pragma unroll
+          for (uint32_t kk = 0; kk < kGemmStageBlocks; ++kk) {
+            if (kk < steps && ok) {
+              ok = mbar_wait_bounded(&tmem_empty[ts.stage], ts.phase ^ 1, abort_flag);
+              if (ok) {
+                tcgen05_fence_after_thread_sync();
+                const uint32_t d_tmem = tmem_base + ts.stage * kGemmTileCols;
+                constexpr uint64_t kStep = (kQK >> 4);  // 32 bytes in 16-byte units
+                if constexpr (kF8) {
+                  umma_f8_ss<false>(d_tmem, da0 + kk * kStep, db0 + kk * kStep, idesc);
+                  umma_f8_ss<true>(d_tmem, da0 + kk * kStep, dh0 + kk * kStep, idesc);
+                } else {
+                  umma_s8_ss<false>(d_tmem, da0 + kk * kStep, db0 + kk * kStep, idesc);
+                }
+                umma_commit(&tmem_full[ts.stage]);
+                ts.advance(kGemmTmemStages);
+              }
             }
-            umma_commit(&tmem_full[ts.stage]);
-            ts.advance(kGemmTmemStages);
           }
           if (ok)
             umma_commit(&smem_empty[ps.stage]);

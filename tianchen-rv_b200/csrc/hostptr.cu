@@ -255,12 +255,14 @@ int host_binary(const T *lhs, const T *rhs, T *out, size_t n, Launch launch) {
   return finish(c);
 }
 
+// `wait`: return when the result is in host memory; otherwise the work is only queued on the
+// context's stream and tcrv_cuda_host_sync() completes it.
 int host_matmul_locked(HostContext &c, bool q8_weights, size_t n, float *s, const uint8_t *vx, const uint8_t *vy,
-                       size_t by, size_t nr, size_t nc, size_t bx, size_t bs, unsigned flags);
+                       size_t by, size_t nr, size_t nc, size_t bx, size_t bs, unsigned flags, bool wait);
 
 // s[ir*bs + col] for host operands; q8_weights selects the Q8_0 x Q8_0 block dot.
 int host_matmul(bool q8_weights, size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by, size_t nr,
-                size_t nc, size_t bx, size_t bs, unsigned flags) {
+                size_t nc, size_t bx, size_t bs, unsigned flags, bool wait = true) {
   if (n % kQK != 0)
     return TCRV_CUDA_ERR_INVALID_ARGUMENT;
   if (nr == 0 || nc == 0)
@@ -269,11 +271,11 @@ int host_matmul(bool q8_weights, size_t n, float *s, const uint8_t *vx, const ui
     return TCRV_CUDA_ERR_INVALID_ARGUMENT;
   HostContext &c = ctx();
   std::lock_guard<std::mutex> lock(c.mu);
-  return host_matmul_locked(c, q8_weights, n, s, vx, vy, by, nr, nc, bx, bs, flags);
+  return host_matmul_locked(c, q8_weights, n, s, vx, vy, by, nr, nc, bx, bs, flags, wait);
 }
 
 int host_matmul_locked(HostContext &c, bool q8_weights, size_t n, float *s, const uint8_t *vx, const uint8_t *vy,
-                       size_t by, size_t nr, size_t nc, size_t bx, size_t bs, unsigned flags) {
+                       size_t by, size_t nr, size_t nc, size_t bx, size_t bs, unsigned flags, bool wait) {
   const size_t nb = n / kQK;
   const size_t wrow = nb * (q8_weights ? kQ8Block : kQ4Block), xrow = nb * kQ8Block;
   if ((nr > 1 && bx < wrow) || (nc > 1 && by < xrow) || (nr > 1 && bs < nc))
@@ -306,7 +308,7 @@ int host_matmul_locked(HostContext &c, bool q8_weights, size_t n, float *s, cons
       // still be page-locked (the caller may have freed and reallocated at the same address).
       if (host_pinned) {
         TCRV_CUDA_TRY(cudaGraphLaunch(replay->exec, c.stream));
-        return finish(c);
+        return wait ? finish(c) : TCRV_CUDA_OK;
       }
       (void)cudaGraphExecDestroy(replay->exec);
       replay->exec = nullptr;
@@ -461,11 +463,13 @@ int host_matmul_locked(HostContext &c, bool q8_weights, size_t n, float *s, cons
       // the call has not run: forget the capture and issue it directly (the entry stays unusable)
       (void)cudaGetLastError();
       replay->unusable = true;
-      return host_matmul_locked(c, q8_weights, n, s, vx, vy, by, nr, nc, bx, bs, flags);
+      return host_matmul_locked(c, q8_weights, n, s, vx, vy, by, nr, nc, bx, bs, flags, wait);
     }
     replay->exec = exec;
     TCRV_CUDA_TRY(cudaGraphLaunch(exec, c.stream));
   }
+  if (!wait)
+    return TCRV_CUDA_OK;
   return finish(c);  // also reports a device-side wait that expired (host mirror of the error word)
 }
 
@@ -655,6 +659,27 @@ int tcrv_cuda_host_quantize_row_q8_0(size_t n, const float *x, uint8_t *vy) {
 int tcrv_cuda_host_gemm_q4_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by, size_t nr,
                                   size_t nc, size_t bx, size_t bs) {
   return host_matmul(false, n, s, vx, vy, by, nr, nc, bx, bs, default_fold_flags());
+}
+
+// Queued twins: the same calls without the wait at the end.  All work of a device's context runs
+// on one stream, so queued calls execute in call order and may share the scratch arena; a call
+// that has to grow the arena synchronises first.
+int tcrv_cuda_host_gemm_q4_0_q8_0_async(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by, size_t nr,
+                                        size_t nc, size_t bx, size_t bs) {
+  return host_matmul(false, n, s, vx, vy, by, nr, nc, bx, bs, default_fold_flags(), /*wait=*/false);
+}
+
+int tcrv_cuda_host_gemm_q8_0_q8_0_async(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by, size_t nr,
+                                        size_t nc, size_t bx, size_t bs) {
+  return host_matmul(true, n, s, vx, vy, by, nr, nc, bx, bs, default_fold_flags(), /*wait=*/false);
+}
+
+int tcrv_cuda_host_sync(void) {
+  HostContext &c = ctx();
+  std::lock_guard<std::mutex> lock(c.mu);
+  if (c.stream == nullptr)
+    return TCRV_CUDA_OK;
+  return finish(c);
 }
 
 int tcrv_cuda_host_set_fold_order(int order) {

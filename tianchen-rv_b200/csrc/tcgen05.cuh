@@ -67,16 +67,16 @@ __host__ __device__ constexpr uint32_t umma_idesc_s8(int m, int n) {
          | (static_cast<uint32_t>(m >> 4) << 24);  // M / 16
 }
 
-// D[tmem] = A[smem] * B[smem] (accumulate == 0) or D += A * B.  One thread issues.
-__device__ __forceinline__ void umma_s8_ss(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
-                                           uint32_t accumulate) {
+// D[tmem] = A[smem] * B[smem] (kAccumulate false) or D += A * B.  One thread issues.
+template <bool kAccumulate>
+__device__ __forceinline__ void umma_s8_ss(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc) {
   asm volatile(
       "{\n\t"
       ".reg .pred p;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t"
       "}\n" ::"r"(tmem_d),
-      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "n"(kAccumulate ? 1 : 0)
       : "memory");
 }
 
@@ -94,15 +94,15 @@ __host__ __device__ constexpr uint32_t umma_idesc_e4m3(int m, int n) {
          | (static_cast<uint32_t>(m >> 4) << 24);  // M / 16
 }
 
-__device__ __forceinline__ void umma_f8_ss(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
-                                           uint32_t accumulate) {
+template <bool kAccumulate>
+__device__ __forceinline__ void umma_f8_ss(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc) {
   asm volatile(
       "{\n\t"
       ".reg .pred p;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t"
       "}\n" ::"r"(tmem_d),
-      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "n"(kAccumulate ? 1 : 0)
       : "memory");
 }
 

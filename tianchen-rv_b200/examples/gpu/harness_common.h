@@ -120,6 +120,23 @@ inline float scalar_dot_q4_0_q8_0(size_t n, const uint8_t *vx, const uint8_t *vy
   return sumf;
 }
 
+// Sum of the magnitudes of the per-block terms of the same dot product: the scale against
+// which a row whose terms cancel is judged (an fp32 sum in another order can differ from the
+// sequential one by a few ulp of the largest partial sum, whatever the size of the result).
+inline float scalar_abs_terms_q4_0_q8_0(size_t n, const uint8_t *vx, const uint8_t *vy) {
+  double total = 0.0;
+  for (size_t ib = 0; ib < n / 32; ++ib) {
+    const uint8_t *x = vx + ib * 18, *y = vy + ib * 34;
+    int32_t sumi = 0;
+    for (int j = 0; j < 16; ++j) {
+      sumi += ((x[2 + j] & 15) - 8) * static_cast<int8_t>(y[2 + j]);
+      sumi += ((x[2 + j] >> 4) - 8) * static_cast<int8_t>(y[2 + j + 16]);
+    }
+    total += std::fabs(static_cast<double>(sumi) * scale_of(x) * scale_of(y));
+  }
+  return static_cast<float>(total);
+}
+
 // sumf = fma((float)sumi, d_x * d_y, sumf), ascending blocks
 inline float scalar_dot_q8_0_q8_0(size_t n, const uint8_t *vx, const uint8_t *vy) {
   float sumf = 0.f;
