@@ -705,6 +705,21 @@ def measure_gemm(pkg, torch, dist, rank, world):
 
         ms_c = timed(compute)
         ms_p = timed(compute_plain)
+        # the multi-destination kernel with two copies in THIS GPU's memory: what the staged bulk
+        # stores cost without a link behind them
+        import ctypes
+        second = torch.empty((rows, GEMM_TOKENS), dtype=torch.float32, device="cuda")
+        dst2 = (ctypes.c_void_p * 2)(slab.data_ptr(), second.data_ptr())
+
+        def compute_two_local():
+            st = pkg.lib().tcrv_cuda_gemm_q4_0_q8_0_prepared_multi(k, dst2, 2, pw.buffer.data_ptr(), x.data_ptr(), x.stride(0),
+                                                                    rows, GEMM_TOKENS, GEMM_TOKENS, ws.data_ptr(), ws.numel(), 0,
+                                                                    torch.cuda.current_stream().cuda_stream)
+            if st != 0:
+                raise RuntimeError(f"prepared_multi failed: {st}")
+
+        ms_2 = timed(compute_two_local)
+        del second
         # calibration of the int8 tensor pipe on this GPU and this shape: the plain library
         # int8 GEMM (cuBLASLt through torch._int_mm, int32 out, no scales), this rank's rows
         cal_tops = None
@@ -718,7 +733,8 @@ def measure_gemm(pkg, torch, dist, rank, world):
             cal_note = f"{type(exc).__name__}: {exc}"[:120]
         entry_ = {"shape": f"M{GEMM_TOKENS}xN{nr}xK{k}", "rows_per_gpu": rows,
                   "compute_ms": round(ms_c, 4), "compute_tops": round(ops / ms_c / 1e9, 1),
-                  "plain_format_ms": round(ms_p, 4), "plain_format_tops": round(ops / ms_p / 1e9, 1)}
+                  "plain_format_ms": round(ms_p, 4), "plain_format_tops": round(ops / ms_p / 1e9, 1),
+                  "two_local_copies_ms": round(ms_2, 4)}
         if dist is not None:
             ms_g = timed(with_gather)
             entry_.update({"with_allgather_ms": round(ms_g, 4), "with_allgather_tops": round(ops / ms_g / 1e9, 1),
