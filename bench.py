@@ -593,6 +593,13 @@ def measure_other_kernels(pkg, torch):
              torch.empty(n, device="cuda")) for _ in range(24)]
     timed("add_f32", lambda c: pkg.add(sets[c][0], sets[c][1], out=sets[c][2]), 24, 12 * n, "n = 1,048,576")
     del sets
+    # the same kernel on 64 Mi elements (805 MB per launch; 2 buffer sets): long enough that launch
+    # latency no longer hides the kernel's own bandwidth
+    nbig = 64 << 20
+    big = [(torch.rand(nbig, generator=gen, device="cuda"), torch.rand(nbig, generator=gen, device="cuda"),
+            torch.empty(nbig, device="cuda")) for _ in range(2)]
+    timed("add_f32_64Mi", lambda c: pkg.add(big[c][0], big[c][1], out=big[c][2]), 2, 12 * nbig, "n = 67,108,864")
+    del big
     # Q8_0 dequant 4096 x 4096 (84.9 MB per launch; 4 sets)
     wf = torch.randn((4096, 4096), generator=gen, device="cuda") * 0.02
     q8 = [pkg.quantize_q8_0(wf) for _ in range(4)]

@@ -312,6 +312,15 @@ def test_launch_stub_defines_the_reference_named_entry():
     assert c.returncode == 0, c.stderr
 
 
+def test_repacked_gemv_plan_says_which_layout_is_native():
+    # the interleaved layout is served as a compatibility path: the plan a scheduler reads says so
+    # and names both summation orders
+    p = plan(fixture("cuda-repack-gemv-q4-0-q8-0.mlir"))
+    assert "tcrv_cuda.layout_note=compatibility path" in p and "plain block rows are the native layout" in p
+    assert "strict ascending blocks (the reference's lane-wise chain)" in p
+    assert "tcrv_cuda.layout_note" not in plan(fixture("cuda-q4-0-q8-0-gemm.mlir"))
+
+
 def test_target_artifact_bundle_export_writes_files_and_index(tmp_path):
     # tcrv-export-target-artifact-bundle (reference driver, tools/tcrv-translate/tcrv-translate.cpp:40-48,
     # 469-474): one file per artifact plus the index, two lines on stdout

@@ -54,6 +54,9 @@ struct RouteEntry {
     long long lo, hi;
   };
   std::vector<ConstantArg> constantArgs = {};
+  // What a planner should know about the route beyond its bound, e.g. that a layout is served
+  // for compatibility and another one is the fast one ("" = nothing to say).
+  std::string layoutNote = "";
 };
 
 const std::vector<RouteEntry> &routeTable();

@@ -143,7 +143,12 @@ std::vector<RouteEntry> buildTable() {
                  "", {"tcrv_rvv.repack_gemv_q4_0_q8_0"}, gemvRoles, gemvSig, "repack_gemv_q4_0_q8_0",
                  "cuda-ggml-repack-gemv-q4_0-q8_0-callable-c-abi.v1", "tcrv_cuda_repack_gemv_q4_0_q8_0",
                  "tcrv_cuda_host_repack_gemv_q4_0_q8_0", "decode-gemv-x16-bulk-copy", "hbm",
-                 "fma((float)sumi, d_w*d_a, .); 8 interleaved chains per range, ranges ascending"});
+                 "fma((float)sumi, d_w*d_a, .); host entry: strict ascending blocks (the reference's lane-wise chain); "
+                 "device entry without TCRV_CUDA_FLAG_STRICT_ORDER: 8 interleaved chains per range, ranges ascending"});
+    t.back().layoutNote =
+        "compatibility path: the 16-row interleaved layout is made for RVV lanes; on sm_100a plain block rows are the "
+        "native layout (streaming GEMV 12.6 us against 16.5 us here for 32000x4096), so repack only when the caller "
+        "already holds x16 weights";
     t.push_back({"tcrv_rvv.repack_gemv_q8_0_q8_0",
                  withKind("ggml_repack_gemv_q8_0_q8_0",
                           {{"scale_model", false, "dual-fp16-per-block-d_x.d_y", 0}, {"qk", true, "", 32},
@@ -153,7 +158,12 @@ std::vector<RouteEntry> buildTable() {
                  "", {"tcrv_rvv.repack_gemv_q8_0_q8_0"}, gemvRoles, gemvSig, "repack_gemv_q8_0_q8_0",
                  "cuda-ggml-repack-gemv-q8_0-q8_0-callable-c-abi.v1", "tcrv_cuda_repack_gemv_q8_0_q8_0",
                  "tcrv_cuda_host_repack_gemv_q8_0_q8_0", "decode-gemv-x16-bulk-copy", "hbm",
-                 "fma((float)sumi, d_w*d_a, .); 8 interleaved chains per range, ranges ascending"});
+                 "fma((float)sumi, d_w*d_a, .); host entry: strict ascending blocks (the reference's lane-wise chain); "
+                 "device entry without TCRV_CUDA_FLAG_STRICT_ORDER: 8 interleaved chains per range, ranges ascending"});
+    t.back().layoutNote =
+        "compatibility path: the 16-row interleaved layout is made for RVV lanes; on sm_100a plain block rows are the "
+        "native layout (streaming GEMV 12.6 us against 16.5 us here for 32000x4096), so repack only when the caller "
+        "already holds x16 weights";
     t.push_back({"tcrv_rvv.repack_gemm_q4_0_q8_0",
                  withKind("ggml_repack_gemm_q4_0_q8_0",
                           {{"scale_model", false, "dual-fp16-per-block-d_x.d_y", 0}, {"qk", true, "", 32},

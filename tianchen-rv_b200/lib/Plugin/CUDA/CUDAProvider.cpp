@@ -173,6 +173,8 @@ public:
     meta("tcrv_cuda.roofline_bound", route->rooflineBound);
     if (!route->foldOrder.empty())
       meta("tcrv_cuda.fp32_fold_order", route->foldOrder);
+    if (!route->layoutNote.empty())
+      meta("tcrv_cuda.layout_note", route->layoutNote);
     if (route->returnType != "void")
       meta("tcrv_cuda.return_type", route->returnType);
     if (!route->constantArgs.empty()) {
