@@ -548,7 +548,8 @@ def measure_e2e(pkg, torch, layers, steps, dist):
             "d2h_bytes_per_step": sum(int(y.numel()) * 4 for _, _, _, y in host),
             "ms_per_step": round(dt / steps * 1e3, 4), "steps": steps,
             "call": "tcrv_cuda_host_gemm_q4_0_q8_0_async per layer + tcrv_cuda_host_sync per step (one host round trip "
-                    "per step)",
+                    "per step; the library replays a repeated step as one graph: one fetch of the four layers' "
+                    "activations, four GEMV kernels)",
             "blocking_calls": {"value": round(step_bytes * steps * world / dt_blocking / 1e9, 2),
                                "ms_per_step": round(dt_blocking / steps * 1e3, 4),
                                "call": "tcrv_cuda_host_gemm_q4_0_q8_0 per layer (each call waits for its result)"},

@@ -76,7 +76,13 @@ int tcrv_cuda_host_gemm_q4_0_q8_0(size_t n, float *s, const uint8_t *vx, const u
  * on the current device's stream; tcrv_cuda_host_sync() waits for everything queued so far
  * and reports a failure of any of it.  Between the call and the sync the caller must neither
  * read the output buffer nor change the inputs (page-locked inputs are read by the GPU after
- * the call returns; pageable ones have been staged by then).  Queued calls run in call order. */
+ * the call returns; pageable ones have been staged by then).  Queued calls run in call order.
+ * A run of queued decode calls (resident weights, nc <= 8, page-locked buffers, at most 16
+ * calls, nothing else in between) that repeats between syncs with the same arguments - a decode
+ * step - is recorded the first time, captured the second and from then on held back until the
+ * sync (or the next other call) and launched as ONE graph: a single kernel fetches every call's
+ * activations, the GEMVs follow back to back.  Results are those of the calls made one by one;
+ * a run in which a call reads a buffer an earlier call of the run writes is never merged. */
 int tcrv_cuda_host_gemm_q4_0_q8_0_async(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by, size_t nr,
                                         size_t nc, size_t bx, size_t bs);
 int tcrv_cuda_host_gemm_q8_0_q8_0_async(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by, size_t nr,

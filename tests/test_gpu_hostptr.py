@@ -342,3 +342,125 @@ def test_queued_host_calls_complete_at_the_sync(cuda, pkg, O, pinned):
         for nr, k, w, x, wh, xt, yt in layers[:2]:
             L.tcrv_cuda_host_unregister_weights(wh.ctypes.data)
         L.tcrv_cuda_host_release()
+
+
+def test_a_repeated_run_of_queued_calls_is_replayed_as_one_sequence(cuda, pkg, O):
+    # A decode step (the same queued calls on the same page-locked buffers, then one sync) is
+    # recorded on its first round, captured as one graph on the second and replayed from the third:
+    # every round must give the blocking calls' bits for the CURRENT activations.  The run then
+    # changes shape (a shorter step, a blocking call in the middle, a different third call) and
+    # must still follow call order.
+    L = pkg.lib()
+    shapes = [(96, 1024, 1), (200, 512, 1), (64, 2048, 4), (130, 1024, 1)]
+    layers = []
+    for i, (nr, k, nc) in enumerate(shapes):
+        w, _ = make(O, nr, k, nc, 6300 + i)
+        wh = np.ascontiguousarray(w)
+        xt = cuda.empty((nc, k // 32 * 34), dtype=cuda.uint8).pin_memory()
+        yt = cuda.empty((nr, nc), dtype=cuda.float32).pin_memory()
+        assert L.tcrv_cuda_host_register_weights(wh.ctypes.data, wh.nbytes) == 0
+        layers.append((nr, k, nc, w, wh, xt, yt))
+
+    def queue(layer):
+        nr, k, nc, w, wh, xt, yt = layer
+        return L.tcrv_cuda_host_gemm_q4_0_q8_0_async(k, yt.data_ptr(), wh.ctypes.data, xt.data_ptr(), xt.stride(0), nr, nc,
+                                                     wh.strides[0], nc)
+
+    def blocking(layer, out):
+        nr, k, nc, w, wh, xt, yt = layer
+        return L.tcrv_cuda_host_gemm_q4_0_q8_0(k, out.data_ptr(), wh.ctypes.data, xt.data_ptr(), xt.stride(0), nr, nc,
+                                               wh.strides[0], nc)
+
+    def refill(seed):
+        for j, (nr, k, nc, w, wh, xt, yt) in enumerate(layers):
+            xs = O.quantize_q8_0(O.fill_normal(nc * k, seed + j).reshape(nc, k))
+            xt.copy_(cuda.from_numpy(xs))
+            yt.fill_(float("nan"))
+
+    def check(which, tag):
+        # the blocking call on a separate output buffer is the statement of what the queued one owes
+        for j in which:
+            nr, k, nc, w, wh, xt, yt = layers[j]
+            ref = cuda.empty((nr, nc), dtype=cuda.float32)
+            assert blocking(layers[j], ref) == 0
+            assert np.array_equal(yt.numpy().view(np.uint32), ref.numpy().view(np.uint32)), (tag, j)
+
+    try:
+        for rnd in range(6):
+            refill(7000 + 10 * rnd)
+            for layer in layers:
+                assert queue(layer) == 0
+            assert L.tcrv_cuda_host_sync() == 0
+            check(range(4), ("full", rnd))
+        # single-column results also against the oracle's statement of the kernel's order
+        nr, k, nc, w, wh, xt, yt = layers[0]
+        assert np.array_equal(yt.numpy().view(np.uint32), O.gemv_lane_order(w, xt.numpy()).view(np.uint32))
+        # a step that stops after two calls: the held-back prefix runs at the sync
+        refill(7100)
+        assert queue(layers[0]) == 0 and queue(layers[1]) == 0
+        assert L.tcrv_cuda_host_sync() == 0
+        check([0, 1], "prefix")
+        # a blocking call in the middle of a step: it must come after the two queued before it
+        refill(7200)
+        assert queue(layers[0]) == 0 and queue(layers[1]) == 0
+        mid = cuda.empty((layers[3][0], 1), dtype=cuda.float32)
+        assert blocking(layers[3], mid) == 0
+        assert queue(layers[2]) == 0 and queue(layers[3]) == 0
+        assert L.tcrv_cuda_host_sync() == 0
+        check(range(4), "blocking in the middle")
+        assert np.array_equal(mid.numpy().view(np.uint32), layers[3][6].numpy().view(np.uint32))
+        # a step that leaves the known sequence at its third call
+        refill(7300)
+        assert queue(layers[0]) == 0 and queue(layers[1]) == 0 and queue(layers[3]) == 0
+        assert L.tcrv_cuda_host_sync() == 0
+        check([0, 1, 3], "diverging")
+        # and the full step again, twice (replayed, then replayed after the other runs)
+        for rnd in range(2):
+            refill(7400 + rnd)
+            for layer in layers:
+                assert queue(layer) == 0
+            assert L.tcrv_cuda_host_sync() == 0
+            check(range(4), ("again", rnd))
+    finally:
+        for layer in layers:
+            L.tcrv_cuda_host_unregister_weights(layer[4].ctypes.data)
+        L.tcrv_cuda_host_release()
+
+
+def test_a_sequence_whose_call_reads_an_earlier_calls_output_keeps_call_order(cuda, pkg, O):
+    # Call B's activations lie in the buffer call A writes its result to.  Fetching all inputs at
+    # the start of a captured sequence would hand B the bytes from before A ran, so such a run
+    # must not be captured that way: on every round B sees A's result, as with blocking calls.
+    L = pkg.lib()
+    nr_a, k_a = 272, 512      # A writes 272 floats = 1088 bytes
+    nr_b, k_b = 64, 1024      # B reads 32 blocks = 1088 bytes
+    wa = np.ascontiguousarray(make(O, nr_a, k_a, 1, 6500)[0])
+    wb = np.ascontiguousarray(make(O, nr_b, k_b, 1, 6502)[0])
+    xa = cuda.from_numpy(O.quantize_q8_0(O.fill_normal(k_a, 6504).reshape(1, k_a)).copy()).pin_memory()
+    shared = cuda.empty((nr_a,), dtype=cuda.float32).pin_memory()   # A's output, B's activations
+    yb = cuda.empty((nr_b, 1), dtype=cuda.float32).pin_memory()
+    for w in (wa, wb):
+        assert L.tcrv_cuda_host_register_weights(w.ctypes.data, w.nbytes) == 0
+    xrow_b = k_b // 32 * 34
+    assert xrow_b == nr_a * 4
+
+    def step(a_call, b_call, sync):
+        # the host puts valid activations for B into the shared buffer; A then overwrites them
+        xb = O.quantize_q8_0(O.fill_normal(k_b, 6506).reshape(1, k_b))
+        shared.view(cuda.uint8).copy_(cuda.from_numpy(xb.reshape(-1).copy()))
+        yb.fill_(float("nan"))
+        assert a_call(k_a, shared.data_ptr(), wa.ctypes.data, xa.data_ptr(), xa.stride(0), nr_a, 1, wa.strides[0], 1) == 0
+        assert b_call(k_b, yb.data_ptr(), wb.ctypes.data, shared.data_ptr(), xrow_b, nr_b, 1, wb.strides[0], 1) == 0
+        if sync:
+            assert L.tcrv_cuda_host_sync() == 0
+        return yb.numpy().view(np.uint32).copy()
+
+    try:
+        want = step(L.tcrv_cuda_host_gemm_q4_0_q8_0, L.tcrv_cuda_host_gemm_q4_0_q8_0, False)
+        for rnd in range(5):
+            got = step(L.tcrv_cuda_host_gemm_q4_0_q8_0_async, L.tcrv_cuda_host_gemm_q4_0_q8_0_async, True)
+            assert np.array_equal(got, want), rnd
+    finally:
+        for w in (wa, wb):
+            L.tcrv_cuda_host_unregister_weights(w.ctypes.data)
+        L.tcrv_cuda_host_release()

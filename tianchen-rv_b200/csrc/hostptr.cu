@@ -51,9 +51,26 @@ struct Replay {
 };
 constexpr size_t kMaxReplays = 64;
 
+// A run of queued decode calls between two waits that was seen before with the same buffers (a
+// decode step: the same operators on the same buffers every token).  Its calls are replayed as ONE
+// graph: a single kernel fetches every call's activations, the GEMVs follow back to back.
+constexpr size_t kMaxSequenceCalls = 16, kMaxSequences = 8;
+struct Sequence {
+  std::vector<ReplayKey> keys;
+  cudaGraphExec_t exec = nullptr;
+  bool unusable = false;  // could not be captured (overlapping buffers, capture refused)
+};
+
 struct HostContext {
   std::mutex mu;
   std::vector<Replay> replays;
+  std::vector<Sequence> sequences;
+  // queued calls held back because they are so far a prefix of a captured sequence; they are
+  // launched (as the sequence's graph, or one by one) by the next wait or the next other call
+  std::vector<ReplayKey> pending;
+  // queued decode calls launched one by one since the last wait: what a sequence is learnt from
+  std::vector<ReplayKey> trace;
+  bool trace_pure = true;  // no other work was issued between them
   cudaStream_t stream = nullptr;
   uint8_t *arena = nullptr;
   size_t arena_cap = 0, arena_used = 0;
@@ -95,6 +112,10 @@ void drop_replays(HostContext &c) {
     if (r.exec)
       (void)cudaGraphExecDestroy(r.exec);
   c.replays.clear();
+  for (Sequence &q : c.sequences)
+    if (q.exec)
+      (void)cudaGraphExecDestroy(q.exec);
+  c.sequences.clear();
 }
 
 bool is_pinned_host(const void *p) {
@@ -112,11 +133,19 @@ bool is_pinned_range(const void *p, size_t bytes) {
 }
 
 int ensure_error_mirror(HostContext &c);
+int flush_pending(HostContext &c);
 
-int ensure_stream(HostContext &c) {
+// Every entry starts here.  `sequenced`: the caller is a queued decode call (or the flush of
+// such calls); anything else first launches the calls that were held back, so that the stream
+// keeps call order, and ends the run of calls a sequence could be learnt from.
+int ensure_stream(HostContext &c, bool sequenced = false) {
   if (c.stream == nullptr)
     TCRV_CUDA_TRY(cudaStreamCreateWithFlags(&c.stream, cudaStreamNonBlocking));
-  return ensure_error_mirror(c);
+  const int st = ensure_error_mirror(c);
+  if (st != TCRV_CUDA_OK || sequenced)
+    return st;
+  c.trace_pure = false;
+  return flush_pending(c);
 }
 
 // Makes room for `total` bytes and resets the bump pointer.  Growing frees the old arena,
@@ -169,6 +198,38 @@ __global__ void __launch_bounds__(512) fetch_rows_kernel(const uint8_t *__restri
   }
 }
 
+// The same for every call of a sequence at once: CTA i fetches call i's activations.
+struct FetchList {
+  const uint8_t *src[kMaxSequenceCalls];
+  uint8_t *dst[kMaxSequenceCalls];
+  uint32_t rows[kMaxSequenceCalls], row_bytes[kMaxSequenceCalls];
+  size_t stride[kMaxSequenceCalls];
+};
+__global__ void __launch_bounds__(512) fetch_rows_multi_kernel(const __grid_constant__ FetchList list) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  const uint32_t c = blockIdx.x;
+  const uint8_t *src = list.src[c];
+  uint8_t *dst = list.dst[c];
+  const uint32_t rows = list.rows[c], row_bytes = list.row_bytes[c];
+  const size_t stride = list.stride[c];
+  const bool vec = row_bytes % 16 == 0 && stride % 16 == 0 && (reinterpret_cast<uintptr_t>(src) & 15u) == 0 &&
+                   (reinterpret_cast<uintptr_t>(dst) & 15u) == 0;
+  if (vec) {
+    const uint32_t per_row = row_bytes / 16, total = rows * per_row;
+    for (uint32_t i = threadIdx.x; i < total; i += blockDim.x) {
+      const uint32_t r = i / per_row, j = i - r * per_row;
+      reinterpret_cast<uint4 *>(dst + static_cast<size_t>(r) * row_bytes)[j] =
+          reinterpret_cast<const uint4 *>(src + r * stride)[j];
+    }
+  } else {
+    const uint32_t total = rows * row_bytes;
+    for (uint32_t i = threadIdx.x; i < total; i += blockDim.x) {
+      const uint32_t r = i / row_bytes, j = i - r * row_bytes;
+      dst[static_cast<size_t>(r) * row_bytes + j] = src[r * stride + j];
+    }
+  }
+}
+
 int upload_rows(HostContext &c, uint8_t *dst, const void *src, size_t rows, size_t row_bytes, size_t stride) {
   if (rows == 0 || row_bytes == 0)
     return TCRV_CUDA_OK;
@@ -183,6 +244,9 @@ int upload_rows(HostContext &c, uint8_t *dst, const void *src, size_t rows, size
 // than a blocking synchronisation takes to wake the thread up, so the stream is polled for a
 // short while first.
 int finish(HostContext &c) {
+  // a wait ends the run of queued calls a sequence is learnt from
+  c.trace.clear();
+  c.trace_pure = true;
   const auto start = std::chrono::steady_clock::now();
   for (;;) {
     const cudaError_t e = cudaStreamQuery(c.stream);
@@ -256,9 +320,53 @@ int host_binary(const T *lhs, const T *rhs, T *out, size_t n, Launch launch) {
 }
 
 // `wait`: return when the result is in host memory; otherwise the work is only queued on the
-// context's stream and tcrv_cuda_host_sync() completes it.
+// context's stream and tcrv_cuda_host_sync() completes it.  `sequenced`: see ensure_stream.
 int host_matmul_locked(HostContext &c, bool q8_weights, size_t n, float *s, const uint8_t *vx, const uint8_t *vy,
-                       size_t by, size_t nr, size_t nc, size_t bx, size_t bs, unsigned flags, bool wait);
+                       size_t by, size_t nr, size_t nc, size_t bx, size_t bs, unsigned flags, bool wait,
+                       bool sequenced = false);
+
+int run_key(HostContext &c, const ReplayKey &k) {
+  return host_matmul_locked(c, k.q8, k.n, static_cast<float *>(const_cast<void *>(k.s)),
+                            static_cast<const uint8_t *>(k.vx), static_cast<const uint8_t *>(k.vy), k.by, k.nr, k.nc,
+                            k.bx, k.bs, k.flags, /*wait=*/false, /*sequenced=*/true);
+}
+
+// The held-back calls followed by `next` are the beginning of a captured sequence.
+bool extends_sequence(const HostContext &c, const ReplayKey &next) {
+  const size_t have = c.pending.size();
+  for (const Sequence &q : c.sequences) {
+    if (q.exec == nullptr || q.keys.size() <= have || !(q.keys[have] == next))
+      continue;
+    bool same = true;
+    for (size_t i = 0; i < have && same; ++i)
+      same = q.keys[i] == c.pending[i];
+    if (same)
+      return true;
+  }
+  return false;
+}
+
+// Launches the held-back calls: as the sequence's graph when they are a whole captured sequence,
+// otherwise one by one (they then count towards the run a sequence is learnt from).
+int flush_pending(HostContext &c) {
+  if (c.pending.empty())
+    return TCRV_CUDA_OK;
+  std::vector<ReplayKey> calls;
+  calls.swap(c.pending);
+  for (const Sequence &q : c.sequences)
+    if (q.exec != nullptr && q.keys == calls) {
+      TCRV_CUDA_TRY(cudaGraphLaunch(q.exec, c.stream));
+      return TCRV_CUDA_OK;
+    }
+  for (const ReplayKey &k : calls) {
+    const int st = run_key(c, k);
+    if (st != TCRV_CUDA_OK)
+      return st;
+    if (c.trace.size() <= kMaxSequenceCalls)
+      c.trace.push_back(k);
+  }
+  return TCRV_CUDA_OK;
+}
 
 // s[ir*bs + col] for host operands; q8_weights selects the Q8_0 x Q8_0 block dot.
 int host_matmul(bool q8_weights, size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by, size_t nr,
@@ -271,16 +379,43 @@ int host_matmul(bool q8_weights, size_t n, float *s, const uint8_t *vx, const ui
     return TCRV_CUDA_ERR_INVALID_ARGUMENT;
   HostContext &c = ctx();
   std::lock_guard<std::mutex> lock(c.mu);
-  return host_matmul_locked(c, q8_weights, n, s, vx, vy, by, nr, nc, bx, bs, flags, wait);
+  if (wait)
+    return host_matmul_locked(c, q8_weights, n, s, vx, vy, by, nr, nc, bx, bs, flags, true);
+  // A queued decode call on resident weights with page-locked buffers can be part of a sequence.
+  const size_t nb = n / kQK;
+  const size_t wrow = nb * (q8_weights ? kQ8Block : kQ4Block), xrow = nb * kQ8Block;
+  const auto it = c.weights.find(vx);
+  const bool valid = !((nr > 1 && bx < wrow) || (nc > 1 && by < xrow) || (nr > 1 && bs < nc)) &&
+                     it != c.weights.end() && it->second.bytes >= (nr - 1) * bx + wrow;
+  if (!valid || nc > 8 || !is_pinned_host(vy) || !is_pinned_host(s))
+    return host_matmul_locked(c, q8_weights, n, s, vx, vy, by, nr, nc, bx, bs, flags, false);
+  const ReplayKey key{vx, vy, s, n, by, nr, nc, bx, bs, q8_weights, flags};
+  if (extends_sequence(c, key)) {
+    c.pending.push_back(key);
+    return TCRV_CUDA_OK;
+  }
+  int st = ensure_stream(c, /*sequenced=*/true);
+  if (st == TCRV_CUDA_OK)
+    st = flush_pending(c);
+  if (st == TCRV_CUDA_OK && extends_sequence(c, key)) {  // the first call of a sequence, right after another one
+    c.pending.push_back(key);
+    return TCRV_CUDA_OK;
+  }
+  if (st == TCRV_CUDA_OK)
+    st = run_key(c, key);
+  if (st == TCRV_CUDA_OK && c.trace.size() <= kMaxSequenceCalls)
+    c.trace.push_back(key);
+  return st;
 }
 
 int host_matmul_locked(HostContext &c, bool q8_weights, size_t n, float *s, const uint8_t *vx, const uint8_t *vy,
-                       size_t by, size_t nr, size_t nc, size_t bx, size_t bs, unsigned flags, bool wait) {
+                       size_t by, size_t nr, size_t nc, size_t bx, size_t bs, unsigned flags, bool wait,
+                       bool sequenced) {
   const size_t nb = n / kQK;
   const size_t wrow = nb * (q8_weights ? kQ8Block : kQ4Block), xrow = nb * kQ8Block;
   if ((nr > 1 && bx < wrow) || (nc > 1 && by < xrow) || (nr > 1 && bs < nc))
     return TCRV_CUDA_ERR_INVALID_ARGUMENT;
-  int st = ensure_stream(c);
+  int st = ensure_stream(c, sequenced);
   if (st != TCRV_CUDA_OK)
     return st;
 
@@ -463,7 +598,7 @@ int host_matmul_locked(HostContext &c, bool q8_weights, size_t n, float *s, cons
       // the call has not run: forget the capture and issue it directly (the entry stays unusable)
       (void)cudaGetLastError();
       replay->unusable = true;
-      return host_matmul_locked(c, q8_weights, n, s, vx, vy, by, nr, nc, bx, bs, flags, wait);
+      return host_matmul_locked(c, q8_weights, n, s, vx, vy, by, nr, nc, bx, bs, flags, wait, sequenced);
     }
     replay->exec = exec;
     TCRV_CUDA_TRY(cudaGraphLaunch(exec, c.stream));
@@ -471,6 +606,153 @@ int host_matmul_locked(HostContext &c, bool q8_weights, size_t n, float *s, cons
   if (!wait)
     return TCRV_CUDA_OK;
   return finish(c);  // also reports a device-side wait that expired (host mirror of the error word)
+}
+
+bool ranges_overlap(const void *a, size_t a_bytes, const void *b, size_t b_bytes) {
+  const uintptr_t a0 = reinterpret_cast<uintptr_t>(a), b0 = reinterpret_cast<uintptr_t>(b);
+  return a0 < b0 + b_bytes && b0 < a0 + a_bytes;
+}
+
+// Captures the calls of `keys` as one graph: one kernel fetches every call's activations from the
+// page-locked buffers' device mappings, then the GEMVs run back to back (each may stream its
+// resident weights while its predecessor drains), single-column results go straight into the
+// caller's buffers, the others are copied out at the end.  Fetching everything first is only the
+// same as running the calls in order if no call reads what an earlier one writes: such a
+// sequence is refused.  Returns nullptr when the sequence cannot be captured.
+cudaGraphExec_t capture_sequence(HostContext &c, const std::vector<ReplayKey> &keys) {
+  struct Item {
+    const ResidentWeights *res;
+    size_t xrow;
+    uint8_t *dx;
+    float *ds;
+  };
+  const size_t count = keys.size();
+  if (count < 2 || count > kMaxSequenceCalls)
+    return nullptr;
+  std::vector<Item> items(count);
+  size_t total = 1024;
+  for (size_t i = 0; i < count; ++i) {
+    const ReplayKey &k = keys[i];
+    const auto it = c.weights.find(k.vx);
+    if (it == c.weights.end())
+      return nullptr;
+    const size_t nb = k.n / kQK, xrow = nb * kQ8Block;
+    const size_t in_bytes = (k.nc - 1) * k.by + xrow, out_bytes = ((k.nr - 1) * k.bs + k.nc) * sizeof(float);
+    if (k.nc * xrow > (256u << 10) || !is_pinned_range(k.vy, in_bytes) || !is_pinned_range(k.s, out_bytes))
+      return nullptr;
+    for (size_t j = 0; j < i; ++j)
+      if (ranges_overlap(k.vy, in_bytes, keys[j].s, ((keys[j].nr - 1) * keys[j].bs + keys[j].nc) * sizeof(float)))
+        return nullptr;
+    items[i] = Item{&it->second, xrow, nullptr, nullptr};
+    total += up256(k.nc * xrow) + up256(k.nr * k.nc * sizeof(float));
+  }
+  if (total > c.arena_cap)
+    return nullptr;  // the caller grows the arena (which drops every graph) and tries again later
+  c.arena_used = 0;
+  FetchList list{};
+  for (size_t i = 0; i < count; ++i) {
+    const ReplayKey &k = keys[i];
+    void *m = nullptr;
+    if (cudaHostGetDevicePointer(&m, const_cast<void *>(k.vy), 0) != cudaSuccess) {
+      (void)cudaGetLastError();
+      return nullptr;
+    }
+    items[i].dx = arena_take(c, k.nc * items[i].xrow);
+    items[i].ds = reinterpret_cast<float *>(arena_take(c, k.nr * k.nc * sizeof(float)));
+    list.src[i] = static_cast<const uint8_t *>(m);
+    list.dst[i] = items[i].dx;
+    list.rows[i] = static_cast<uint32_t>(k.nc);
+    list.row_bytes[i] = static_cast<uint32_t>(items[i].xrow);
+    list.stride[i] = k.by;
+  }
+  if (cudaStreamBeginCapture(c.stream, cudaStreamCaptureModeThreadLocal) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return nullptr;
+  }
+  bool ok = true;
+  fetch_rows_multi_kernel<<<static_cast<unsigned>(count), 512, 0, c.stream>>>(list);
+  ok = cudaGetLastError() == cudaSuccess;
+  for (size_t i = 0; i < count && ok; ++i) {
+    const ReplayKey &k = keys[i];
+    float *out = items[i].ds;
+    size_t out_bs = k.nc;
+    if (k.nc == 1) {
+      void *m = nullptr;
+      if (cudaHostGetDevicePointer(&m, const_cast<void *>(k.s), 0) == cudaSuccess) {
+        out = static_cast<float *>(m);
+        out_bs = k.bs;
+        items[i].ds = nullptr;  // nothing to copy back
+      } else {
+        (void)cudaGetLastError();
+      }
+    }
+    const unsigned lf = k.flags | TCRV_CUDA_FLAG_STATIC_WEIGHTS;
+    const uint8_t *vy = items[i].dx;
+    const int st = k.q8 ? launch_gemv<true>(k.n, out, items[i].res->dev, vy, items[i].xrow, k.nr, k.nc, k.bx, out_bs, lf,
+                                            c.stream)
+                        : launch_gemv<false>(k.n, out, items[i].res->dev, vy, items[i].xrow, k.nr, k.nc, k.bx, out_bs,
+                                             lf, c.stream);
+    ok = st == TCRV_CUDA_OK;
+  }
+  for (size_t i = 0; i < count && ok; ++i) {
+    if (items[i].ds == nullptr)
+      continue;
+    const ReplayKey &k = keys[i];
+    float *s = static_cast<float *>(const_cast<void *>(k.s));
+    const cudaError_t e =
+        k.nr == 1 || k.bs == k.nc
+            ? cudaMemcpyAsync(s, items[i].ds, k.nr * k.nc * sizeof(float), cudaMemcpyDeviceToHost, c.stream)
+            : cudaMemcpy2DAsync(s, k.bs * sizeof(float), items[i].ds, k.nc * sizeof(float), k.nc * sizeof(float), k.nr,
+                                cudaMemcpyDeviceToHost, c.stream);
+    ok = e == cudaSuccess;
+  }
+  cudaGraph_t graph = nullptr;
+  cudaGraphExec_t exec = nullptr;
+  ok = cudaStreamEndCapture(c.stream, &graph) == cudaSuccess && graph != nullptr && ok;
+  if (ok)
+    ok = cudaGraphInstantiate(&exec, graph, 0) == cudaSuccess;
+  if (graph)
+    (void)cudaGraphDestroy(graph);
+  if (!ok) {
+    (void)cudaGetLastError();
+    return nullptr;
+  }
+  return exec;
+}
+
+// Called after a wait with the queued decode calls that ran one by one since the wait before:
+// the first sighting of a run records it, the second captures it.
+void learn_sequence(HostContext &c, const std::vector<ReplayKey> &run) {
+  auto find = [&]() -> Sequence * {
+    for (Sequence &q : c.sequences)
+      if (q.keys == run)
+        return &q;
+    return nullptr;
+  };
+  Sequence *q = find();
+  if (q == nullptr) {
+    if (c.sequences.size() >= kMaxSequences) {
+      for (Sequence &old : c.sequences)
+        if (old.exec)
+          (void)cudaGraphExecDestroy(old.exec);
+      c.sequences.clear();
+    }
+    c.sequences.push_back(Sequence{run});
+    return;
+  }
+  if (q->exec != nullptr || q->unusable)
+    return;
+  size_t total = 1024;
+  for (const ReplayKey &k : run)
+    total += up256(k.nc * (k.n / kQK) * kQ8Block) + up256(k.nr * k.nc * sizeof(float));
+  if (total > c.arena_cap) {
+    // growing drops every graph, this entry included: record the run again and capture next time
+    if (arena_reserve(c, total) == TCRV_CUDA_OK)
+      c.sequences.push_back(Sequence{run});
+    return;
+  }
+  q->exec = capture_sequence(c, run);
+  q->unusable = q->exec == nullptr;
 }
 
 // One f32 vector in, one out (in == out for the in-place scale); `sum` receives the soft-max
@@ -561,6 +843,11 @@ int tcrv_cuda_host_register_weights(const void *host, size_t bytes) {
 int tcrv_cuda_host_unregister_weights(const void *host) {
   HostContext &c = ctx();
   std::lock_guard<std::mutex> lock(c.mu);
+  if (c.stream) {  // held-back calls may read these weights
+    const int st = flush_pending(c);
+    if (st != TCRV_CUDA_OK)
+      return st;
+  }
   auto it = c.weights.find(host);
   if (it == c.weights.end())
     return TCRV_CUDA_ERR_INVALID_ARGUMENT;
@@ -578,8 +865,12 @@ int tcrv_cuda_host_unregister_weights(const void *host) {
 int tcrv_cuda_host_release(void) {
   HostContext &c = ctx();
   std::lock_guard<std::mutex> lock(c.mu);
-  if (c.stream)
+  if (c.stream) {
+    (void)flush_pending(c);
     TCRV_CUDA_TRY(cudaStreamSynchronize(c.stream));
+  }
+  c.pending.clear();
+  c.trace.clear();
   drop_replays(c);
   for (auto &kv : c.weights) {
     if (kv.second.dev)
@@ -679,7 +970,16 @@ int tcrv_cuda_host_sync(void) {
   std::lock_guard<std::mutex> lock(c.mu);
   if (c.stream == nullptr)
     return TCRV_CUDA_OK;
-  return finish(c);
+  int st = flush_pending(c);
+  const bool pure = c.trace_pure;
+  std::vector<ReplayKey> run;
+  run.swap(c.trace);
+  const int fin = finish(c);
+  if (st == TCRV_CUDA_OK)
+    st = fin;
+  if (st == TCRV_CUDA_OK && pure && run.size() >= 2 && run.size() <= kMaxSequenceCalls)
+    learn_sequence(c, run);
+  return st;
 }
 
 int tcrv_cuda_host_set_fold_order(int order) {
