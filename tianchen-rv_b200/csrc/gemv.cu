@@ -4,6 +4,7 @@
 // that exposes the integer stage (per-block int32 sums).
 #include <atomic>
 #include "gemv_mma.cuh"
+#include "gemv_mma_rows.cuh"
 #include "gemv_stream.cuh"
 #include "launchers.h"
 
@@ -252,6 +253,75 @@ int launch_mma(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t 
   return TCRV_CUDA_OK;
 }
 
+// The whole-row form of the tensor-core GEMV (rows of at most 16 chunks): ring depth in units of
+// 16 rows, and the bytes between the row pairs of a unit (a multiple of 128 plus 16, which
+// spreads a fragment load over all banks).
+template <bool kQ8W>
+size_t mma_rows_pair_pitch(uint32_t nb) {
+  const size_t two_rows = 2 * static_cast<size_t>(nb) * WeightFormat<kQ8W>::kBlockBytes;
+  return (two_rows + 127) / 128 * 128 + 16;
+}
+template <bool kQ8W>
+size_t mma_rows_ring(uint32_t nb) {
+  if (nb > static_cast<uint32_t>(kMmaWarps * kMmaChunkBlocks))
+    return 0;
+  const size_t unit = kRowsPairs * mma_rows_pair_pitch<kQ8W>(nb);
+  const size_t fixed = kRowsBarrierBytes + kRowsScratchBytes;
+  if (fixed + 2 * unit > kMaxDynamicSmem)
+    return 0;
+  const size_t ring = (kMaxDynamicSmem - fixed) / unit;
+  return ring > static_cast<size_t>(kRowsMaxRing) ? static_cast<size_t>(kRowsMaxRing) : ring;
+}
+
+template <bool kQ8W>
+int launch_mma_rows(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by, size_t nr, size_t nc,
+                    size_t bx, size_t bs, unsigned flags, cudaStream_t stream) {
+  constexpr int WB = WeightFormat<kQ8W>::kBlockBytes;
+  const uint32_t nb = static_cast<uint32_t>(n / kQK);
+  const size_t ring = mma_rows_ring<kQ8W>(nb);
+  const int groups = ring >= 4 ? 2 : 1;  // two 16-row groups per iteration when two more units fit beside them
+  GemvRowsArgs args;
+  args.vx = vx;
+  args.vy = vy;
+  args.s = s;
+  args.bx = bx;
+  args.by = by;
+  args.bs = bs;
+  args.nr = static_cast<uint32_t>(nr);
+  args.nc = static_cast<uint32_t>(nc);
+  args.nb = nb;
+  args.row_bytes = nb * WB;
+  args.pair_pitch = static_cast<uint32_t>(mma_rows_pair_pitch<kQ8W>(nb));
+  args.ring = static_cast<uint32_t>(ring);
+  args.contiguous = bx == static_cast<size_t>(nb) * WB ? 1u : 0u;
+  args.static_weights = (flags & TCRV_CUDA_FLAG_STATIC_WEIGHTS) ? 1u : 0u;
+  args.x_aligned = multiple_of(vy, 16) && by % 16 == 0 ? 1u : 0u;
+  const size_t smem = kRowsBarrierBytes + kRowsScratchBytes + ring * kRowsPairs * args.pair_pitch;
+  auto kernel = groups == 2 ? gemv_mma_rows_kernel<kQ8W, 2> : gemv_mma_rows_kernel<kQ8W, 1>;
+  static std::atomic<bool> configured[64][2];
+  int dev = 0;
+  TCRV_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 64 && !configured[dev][groups - 1]) {
+    TCRV_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(kMaxDynamicSmem)));
+    configured[dev][groups - 1] = true;
+  }
+  const size_t slots = (nr + static_cast<size_t>(kMmaRows) * groups - 1) / (static_cast<size_t>(kMmaRows) * groups);
+  const int sms = sm_count();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(slots < static_cast<size_t>(sms) ? slots : sms));
+  cfg.blockDim = dim3(kRowsThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  TCRV_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, args));
+  return TCRV_CUDA_OK;
+}
+
 }  // namespace
 
 // 0 = strict ascending, 1 = lane pairs + butterfly, 2 = 16-way K split (see tcrv_cuda.h).
@@ -285,6 +355,9 @@ int launch_gemv(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t
     // Many activation columns: the tensor-core kernel (measured faster from about 4 columns
     // on; flags bit 12 keeps the dp4a kernel, bit 14 takes this one for any column count: tuning).
     if ((nc >= kMmaMinCols || (flags & 0x4000u) != 0) && (flags & 0x1000u) == 0) {
+      // rows of up to 4096 elements come in as whole rows (flags bit 13 keeps the tiled form: tuning)
+      if ((flags & 0x2000u) == 0 && mma_rows_ring<kQ8W>(nb) >= 2)
+        return launch_mma_rows<kQ8W>(n, s, vx, vy, by, nr, nc, bx, bs, flags, stream);
       const int slot_groups = mma_groups<kQ8W>(nb);
       if (slot_groups > 0)
         return launch_mma<kQ8W>(n, s, vx, vy, by, nr, nc, bx, bs, flags, slot_groups, stream);
