@@ -46,3 +46,32 @@ def test_sibling_vec_dot_entries_padded_and_unaligned(cuda, pkg, O, fmt, entry):
     assert getattr(L, entry)(64, None, wb.data_ptr(), xd.data_ptr(), None) == -1
     assert L.tcrv_cuda_sibling_dot_rows(9, 64, out.data_ptr(), wb.data_ptr(), xd.data_ptr(), 0, 1, 1, 0, 1, None) == -1
     assert L.tcrv_cuda_sibling_dot_rows(fmt, 64, out.data_ptr(), wb.data_ptr(), xd.data_ptr(), 10, 1, 2, 100, 2, None) == -1
+
+
+@pytest.mark.parametrize("fmt", [1, 2, 3])
+@pytest.mark.parametrize("nr,nb,pad", [(2000, 128, 0), (777, 8, 0), (130, 40, 48), (4099, 64, 16)])
+def test_sibling_streaming_rows_bit_exact(cuda, pkg, O, fmt, nr, nb, pad):
+    # One column against many 16-byte aligned rows takes the streaming kernel: contiguous rows,
+    # rows with a stride, ragged last slots, and an activation column at an odd address.
+    w, x = sd.make(fmt, nr, 1, nb, 900 + fmt + nr)
+    wb = w.shape[1]
+    padded = np.zeros((nr, wb + pad), dtype=np.uint8)
+    padded[:, :wb] = w
+    wd = dev(cuda, padded)
+    xd = dev(cuda, x)
+    L = pkg.lib()
+    rows = np.unique(np.concatenate([np.arange(0, nr, max(1, nr // 60)), np.arange(max(0, nr - 40), nr)]))
+    want = O.sibling_dot_rows(fmt, w[rows], x)
+
+    def run(x_ptr):
+        out = cuda.full((nr, 1), float("nan"), dtype=cuda.float32, device="cuda")
+        assert L.tcrv_cuda_sibling_dot_rows(fmt, nb * 32, out.data_ptr(), wd.data_ptr(), x_ptr, x.shape[1], nr, 1,
+                                            wb + pad, 1, None) == 0
+        return out.cpu().numpy()
+
+    assert np.array_equal(run(xd.data_ptr())[rows].view(np.uint32), want.view(np.uint32))
+    # the same column one byte further on
+    flat = cuda.zeros(x.shape[1] + 1, dtype=cuda.uint8, device="cuda")
+    flat[1:] = xd[0]
+    assert np.array_equal(run(flat.data_ptr() + 1)[rows].view(np.uint32), want.view(np.uint32))
+    pkg.check_device_errors()
