@@ -647,6 +647,24 @@ def measure_other_kernels(pkg, torch):
           "M512 x N11008 x K4096, resident weights; tensor-bound: see tops")
     out[-1]["tops"] = round(2 * GEMM_TOKENS * 11008 * 4096 / out[-1]["us"] / 1e6, 1)
     del wx, xx, pw, og, wsg
+    # sibling block formats, one column against 32000 x 4096 (strict ascending order): random quants,
+    # fp16 scales in a sane range so that the arithmetic sees ordinary numbers
+    def sibling_blocks(rows, nb, block, scale_fields):
+        b = torch.randint(0, 256, (rows, nb, block), dtype=torch.uint8, device="cuda", generator=gen)
+        for f in range(scale_fields):
+            d = (torch.rand((rows, nb), generator=gen, device="cuda") * 0.05 + 0.01).to(torch.float16)
+            b[:, :, 2 * f:2 * f + 2] = d.view(torch.uint8).reshape(rows, nb, 2)
+        return b.reshape(rows, nb * block)
+
+    for fmt, name, (wb, ab), (wf, af) in ((1, "q4_1_q8_1", (20, 36), (2, 2)), (2, "q5_0_q8_0", (22, 34), (1, 1)),
+                                          (3, "q5_1_q8_1", (24, 36), (2, 2))):
+        rows, copies = 32000, 3
+        ws = [sibling_blocks(rows, 128, wb, wf) for _ in range(copies)]
+        xs1 = sibling_blocks(1, 128, ab, af)
+        ys = torch.empty((rows, 1), device="cuda")
+        timed(f"sibling_dot_rows_{name}", lambda c, ws=ws, xs1=xs1, ys=ys, fmt=fmt: pkg.sibling_dot_rows(fmt, ws[c], xs1, out=ys),
+              copies, rows * 128 * wb + 128 * ab + 4 * rows, f"{rows} x 4096, one column, strict block order")
+        del ws
     # f32 forward-pass ops on a prefill-sized activation (512 tokens x 11008 = 22.5 MB; 8 sets)
     acts = [torch.randn((512, 11008), generator=gen, device="cuda") for _ in range(8)]
     outs = [torch.empty((512, 11008), device="cuda") for _ in range(8)]

@@ -173,8 +173,11 @@ int tcrv_cuda_gemm_q4_0_q8_0_prepared(size_t n, float *s, const void *prepared_w
  *   Q4_1, Q5_1:  sumf = sumf + fma(d_x*d_y, (float)sumi, m_x*s_y),
  * i.e. bit-identical to the sequential fold.  `dot_rows` is the matrix form
  * (s[row*bs + col], strides as in tcrv_cuda_gemv_*); the vec_dot entries are the reference's
- * one-row kernels (ABI order n, s, vx, vy).  These run on a general warp-per-output kernel,
- * not on the streaming kernels of the Q4_0/Q8_0 path. */
+ * one-row kernels (ABI order n, s, vx, vy).  One column (nc == 1) against at least 64 rows whose
+ * base and stride are multiples of 16 bytes, with a block count that is a multiple of 8, runs on
+ * a streaming kernel (bulk copies, a table of block terms folded row by row in ascending
+ * order); everything else on a general warp-per-output kernel.  Both perform the same
+ * operations in the same order. */
 #define TCRV_CUDA_FORMAT_Q4_1_Q8_1 1
 #define TCRV_CUDA_FORMAT_Q5_0_Q8_0 2
 #define TCRV_CUDA_FORMAT_Q5_1_Q8_1 3
