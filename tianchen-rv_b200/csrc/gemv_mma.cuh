@@ -178,23 +178,71 @@ __global__ void __launch_bounds__(kMmaThreads, 1)
   if (a.static_weights)
     asm volatile("griddepcontrol.wait;" ::: "memory");
 
-  // Activation columns -> fragment layout; columns beyond nc are zero.
-  for (uint32_t idx = threadIdx.x; idx < nb * 8; idx += kMmaThreads) {
+  // Activation columns -> fragment layout; columns beyond nc are zero.  With 4-byte aligned
+  // columns a block is read as 9 aligned words (a block starts on a word boundary or in the
+  // middle of one, alternately) instead of 17 halfwords, and two blocks are read per round.
+  const bool x_words = (reinterpret_cast<uintptr_t>(a.vy) & 3u) == 0 && (a.by & 3u) == 0;
+  auto stage_block = [&](uint32_t idx, const uint32_t (&w)[9]) {
     const uint32_t ib = idx >> 3, col = idx & 7;
-    uint32_t q[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    float d = 0.0f;
-    if (col < a.nc) {
-      const unsigned short *h =
-          reinterpret_cast<const unsigned short *>(a.vy + col * a.by + static_cast<size_t>(ib) * kQ8Block);
+    uint32_t q[8];
+    unsigned short dbits;
+    if ((ib & 1u) == 0) {  // the block starts at w[0]
+      dbits = static_cast<unsigned short>(w[0] & 0xffffu);
 #pragma unroll
       for (int j = 0; j < 8; ++j)
-        q[j] = static_cast<uint32_t>(h[1 + 2 * j]) | (static_cast<uint32_t>(h[2 + 2 * j]) << 16);
-      d = half_bits_to_float(h[0]);
+        q[j] = __funnelshift_r(w[j], w[j + 1], 16);
+    } else {  // the block starts in the middle of w[0]
+      dbits = static_cast<unsigned short>(w[0] >> 16);
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        q[j] = w[j + 1];
     }
     reinterpret_cast<uint4 *>(xq)[(ib * 2 + 0) * 8 + col] = make_uint4(q[0], q[1], q[2], q[3]);
     reinterpret_cast<uint4 *>(xq)[(ib * 2 + 1) * 8 + col] = make_uint4(q[4], q[5], q[6], q[7]);
-    xd[ib * 8 + col] = d;
+    xd[ib * 8 + col] = half_bits_to_float(dbits);
     xs8[ib * 8 + col] = -8 * sum_s8x32(q);
+  };
+  auto load_block = [&](uint32_t idx, uint32_t (&w)[9]) {
+    const uint32_t ib = idx >> 3, col = idx & 7;
+#pragma unroll
+    for (int j = 0; j < 9; ++j)
+      w[j] = 0;
+    if (idx < nb * 8 && col < a.nc) {
+      // an odd block begins 2 bytes into a word: start at the word that holds its scale
+      const uint32_t *src = reinterpret_cast<const uint32_t *>(a.vy + col * a.by + static_cast<size_t>(ib) * kQ8Block -
+                                                               ((ib & 1u) ? 2 : 0));
+#pragma unroll
+      for (int j = 0; j < 9; ++j)
+        w[j] = src[j];
+    }
+  };
+  if (x_words) {
+    for (uint32_t idx = threadIdx.x; idx < nb * 8; idx += 2 * kMmaThreads) {
+      uint32_t w0[9], w1[9];
+      load_block(idx, w0);
+      load_block(idx + kMmaThreads, w1);
+      stage_block(idx, w0);
+      if (idx + kMmaThreads < nb * 8)
+        stage_block(idx + kMmaThreads, w1);
+    }
+  } else {
+    for (uint32_t idx = threadIdx.x; idx < nb * 8; idx += kMmaThreads) {
+      const uint32_t ib = idx >> 3, col = idx & 7;
+      uint32_t q[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      float d = 0.0f;
+      if (col < a.nc) {
+        const unsigned short *h =
+            reinterpret_cast<const unsigned short *>(a.vy + col * a.by + static_cast<size_t>(ib) * kQ8Block);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          q[j] = static_cast<uint32_t>(h[1 + 2 * j]) | (static_cast<uint32_t>(h[2 + 2 * j]) << 16);
+        d = half_bits_to_float(h[0]);
+      }
+      reinterpret_cast<uint4 *>(xq)[(ib * 2 + 0) * 8 + col] = make_uint4(q[0], q[1], q[2], q[3]);
+      reinterpret_cast<uint4 *>(xq)[(ib * 2 + 1) * 8 + col] = make_uint4(q[4], q[5], q[6], q[7]);
+      xd[ib * 8 + col] = d;
+      xs8[ib * 8 + col] = -8 * sum_s8x32(q);
+    }
   }
   __syncthreads();
 
