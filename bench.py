@@ -807,7 +807,7 @@ def measure_gemm(pkg, torch, dist, rank, world):
 
 
 PROFILE_CASES = ["gemv", "gemv_q8", "gemm", "dequant", "quantize", "silu", "rms_norm", "repack_gemv", "repack_gemv_q8",
-                 "repack_gemm"]
+                 "repack_gemm", "sibling_q4_1", "sibling_q5_0", "sibling_q5_1"]
 
 
 def run_profile_case(args):
@@ -846,6 +846,24 @@ def run_profile_case(args):
         y = torch.empty(rows, dtype=torch.float32, device="cuda")
         for i in range(args.launches):
             pkg.repack_gemv(copies[i % len(copies)], x, rows, q8_weights=q8w, out=y)
+    elif args.case.startswith("sibling_"):
+        # random quants, fp16 scales in a sane range; one column against `rows` rows
+        fmt, wb, ab, wf, af = {"sibling_q4_1": (1, 20, 36, 2, 2), "sibling_q5_0": (2, 22, 34, 1, 1),
+                               "sibling_q5_1": (3, 24, 36, 2, 2)}[args.case]
+        rows, nb = args.rows or 32000, args.k // 32
+
+        def blocks(r, block, fields):
+            b = torch.randint(0, 256, (r, nb, block), dtype=torch.uint8, device="cuda", generator=gen)
+            for f in range(fields):
+                d = (torch.rand((r, nb), generator=gen, device="cuda") * 0.05 + 0.01).to(torch.float16)
+                b[:, :, 2 * f:2 * f + 2] = d.view(torch.uint8).reshape(r, nb, 2)
+            return b.reshape(r, nb * block)
+
+        copies = [blocks(rows, wb, wf) for _ in range(4)]
+        x = blocks(1, ab, af)
+        y = torch.empty((rows, 1), dtype=torch.float32, device="cuda")
+        for i in range(args.launches):
+            pkg.sibling_dot_rows(fmt, copies[i % len(copies)], x, out=y)
     elif args.case == "repack_gemm":
         rows = args.rows or 11008
         nb = args.k // 32
