@@ -91,7 +91,8 @@ int tcrv_cuda_host_sync(void);
 /* One weight row against `cols` (1..16) activation columns, strict block order per column. */
 int tcrv_cuda_host_gemm_tile_q4_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by,
                                        size_t cols);
-/* Q8_0 weights: decode GEMV only (nc <= 8). */
+/* Q8_0 weights: the GEMV kernels (streaming for nc <= 8, the general warp-per-output kernel beyond;
+ * there is no Q8_0-weight tensor-core prefill kernel). */
 int tcrv_cuda_host_gemm_q8_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by, size_t nr,
                                   size_t nc, size_t bx, size_t bs);
 

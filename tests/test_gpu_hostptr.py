@@ -100,10 +100,17 @@ def test_host_prefill_and_q8_paths(cuda, pkg, O):
     st = L.tcrv_cuda_host_gemm_q8_0_q8_0(1024, out8.ctypes.data, w8.ctypes.data, xh.ctypes.data, xh.strides[0], 40, 2,
                                          w8.strides[0], 2)
     assert st == 0 and np.array_equal(out8.view(np.uint32), O.gemv_lane_order(w8, x[:2], True).view(np.uint32))
-    # a Q8_0-weight prefill kernel does not exist: refused, not approximated
+    # Q8_0 weights have no tensor-core prefill kernel: more than 8 columns run on the general GEMV
+    # kernel, in the order tcrv_cuda_gemv_fold_order reports for the call
     big = np.empty((40, 20), np.float32)
     assert L.tcrv_cuda_host_gemm_q8_0_q8_0(1024, big.ctypes.data, w8.ctypes.data, xh.ctypes.data, xh.strides[0], 40, 20,
-                                           w8.strides[0], 20) == -2
+                                           w8.strides[0], 20) == 0
+    assert np.array_equal(big.view(np.uint32), O.gemv_lane_order(w8, x, True).view(np.uint32))
+    prev = L.tcrv_cuda_host_set_fold_order(FOLD_STRICT)
+    assert L.tcrv_cuda_host_gemm_q8_0_q8_0(1024, big.ctypes.data, w8.ctypes.data, xh.ctypes.data, xh.strides[0], 40, 20,
+                                           w8.strides[0], 20) == 0
+    L.tcrv_cuda_host_set_fold_order(prev)
+    assert np.array_equal(big.view(np.uint32), O.gemm(w8, x, fold=O.FOLD_FMA, q8_weights=True).view(np.uint32))
     L.tcrv_cuda_host_release()
 
 

@@ -421,9 +421,9 @@ int host_matmul_locked(HostContext &c, bool q8_weights, size_t n, float *s, cons
 
   auto it = c.weights.find(vx);
   ResidentWeights *res = it == c.weights.end() ? nullptr : &it->second;
+  // more than 8 columns: the tensor-core GEMM for Q4_0 weights; Q8_0 weights have no prefill kernel and
+  // stay on the GEMV entry, whose general kernel takes any column count
   const bool use_gemm = !q8_weights && nc > 8;
-  if (q8_weights && nc > 8)
-    return TCRV_CUDA_ERR_UNSUPPORTED;  // no Q8_0-weight prefill kernel
   if (res && res->bytes < (nr - 1) * bx + wrow)
     return TCRV_CUDA_ERR_INVALID_ARGUMENT;
 
