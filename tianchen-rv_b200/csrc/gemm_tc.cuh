@@ -53,8 +53,18 @@ constexpr int kGemmTileRows = 128;   // weight rows per tile  (MMA M, TMEM lanes
 constexpr int kGemmTileCols = 128;   // activation columns per full tile (MMA N, TMEM columns)
 constexpr int kGemmHalfCols = 64;    // columns of a half item; also the column count of one activation TMA box
 constexpr int kGemmStageBlocks = 4;  // ggml blocks per shared-memory stage (128 bytes of K)
-constexpr int kGemmTmemStages = 4;   // accumulator tiles in flight, one block each
-constexpr int kGemmTmemCols = kGemmTmemStages * kGemmTileCols;  // 512: all of TMEM
+// Blocks per accumulator hand-over.  Every hand-over costs an epilogue warp a barrier test and a
+// release (about 180 + 110 cycles in the instrumented kernel) whatever it carries, so a TMEM
+// stage holds the tiles of two consecutive blocks: measured 355 -> 331 us on N = 32000 and
+// 147 -> 133 us on N = 11008 against one block per hand-over (TCRV_GEMM_HANDOVER_BLOCKS=1).
+#ifndef TCRV_GEMM_HANDOVER_BLOCKS
+#define TCRV_GEMM_HANDOVER_BLOCKS 2
+#endif
+constexpr int kGemmHandover = TCRV_GEMM_HANDOVER_BLOCKS;  // 1 or 2
+static_assert(kGemmHandover == 1 || kGemmHandover == 2, "a stage of 4 blocks is handed over in ones or pairs");
+constexpr int kGemmTmemStages = 4 / kGemmHandover;        // accumulator stages in flight
+constexpr int kGemmTmemStageCols = kGemmTileCols * kGemmHandover;
+constexpr int kGemmTmemCols = kGemmTmemStages * kGemmTmemStageCols;  // 512: all of TMEM
 constexpr int kGemmEpilogueWarps = 16;                          // 4 lane quarters x 4 column groups
 constexpr int kGemmThreads = (kGemmEpilogueWarps + 2) * 32;
 
@@ -280,21 +290,29 @@ __device__ __forceinline__ bool gemm_epilogue_item(const GemmArgs &a, GemmEpilog
     const uint8_t *dx_base = st + Stage::kOffDx + dx_off;
     const uint32_t steps = min(static_cast<uint32_t>(kGemmStageBlocks), a.nb - kb * kGemmStageBlocks);
 #pragma unroll
-    for (uint32_t kk = 0; kk < kGemmStageBlocks; ++kk) {
+    for (uint32_t kk = 0; kk < kGemmStageBlocks; kk += kGemmHandover) {
       if (kk < steps) {
         if (!mbar_wait_bounded(&c.tmem_full[c.ts.stage], c.ts.phase, c.abort_flag))
           return false;
         tcgen05_fence_after_thread_sync();
+        const uint32_t taddr = c.tmem_base + lane_field + c.ts.stage * kGemmTmemStageCols + tmem_col;
         uint32_t v[CPW];
-        tmem_ld_32x32b<CPW>(c.tmem_base + lane_field + c.ts.stage * kGemmTileCols + tmem_col, v);
+        tmem_ld_32x32b<CPW>(taddr, v);
         tmem_ld_wait();
-        // the accumulator tile is in registers: hand the TMEM stage back
+        if (kGemmHandover == 2 && kk + 1 < steps) {
+          // two blocks per hand-over: the stage goes back when the second tile has been read
+          fold_block<CPW, kRepack, kF8>(v, acc, dws[kk], dx_base + kk * (kGemmHalfCols * 4));
+          tmem_ld_32x32b<CPW>(taddr + kGemmTileCols, v);
+          tmem_ld_wait();
+        }
+        // the accumulator tiles are in registers: hand the TMEM stage back
         tcgen05_fence_before_thread_sync();
         __syncwarp();
         if (lane == 0)
           mbar_arrive(&c.tmem_empty[c.ts.stage]);
         c.ts.advance(kGemmTmemStages);
-        fold_block<CPW, kRepack, kF8>(v, acc, dws[kk], dx_base + kk * (kGemmHalfCols * 4));
+        const uint32_t last = (kGemmHandover == 2 && kk + 1 < steps) ? kk + 1 : kk;
+        fold_block<CPW, kRepack, kF8>(v, acc, dws[last], dx_base + last * (kGemmHalfCols * 4));
       }
     }
     // this warp no longer needs the stage's scale tiles
@@ -535,18 +553,24 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           [[maybe_unused]] const uint64_t dh0 = umma_desc_k_major_sw128(a_addr + Stage::kOffB + kGemmBPlaneBytes);
           const uint32_t steps = min(static_cast<uint32_t>(kGemmStageBlocks), a.nb - kb * kGemmStageBlocks);
 #pragma unroll
-          for (uint32_t kk = 0; kk < kGemmStageBlocks; ++kk) {
+          for (uint32_t kk = 0; kk < kGemmStageBlocks; kk += kGemmHandover) {
             if (kk < steps && ok) {
               ok = mbar_wait_bounded(&tmem_empty[ts.stage], ts.phase ^ 1, abort_flag);
               if (ok) {
                 tcgen05_fence_after_thread_sync();
-                const uint32_t d_tmem = tmem_base + ts.stage * kGemmTileCols;
                 constexpr uint64_t kStep = (kQK >> 4);  // 32 bytes in 16-byte units
-                if constexpr (kF8) {
-                  umma_f8_ss<false>(d_tmem, da0 + kk * kStep, db0 + kk * kStep, idesc);
-                  umma_f8_ss<true>(d_tmem, da0 + kk * kStep, dh0 + kk * kStep, idesc);
-                } else {
-                  umma_s8_ss<false>(d_tmem, da0 + kk * kStep, db0 + kk * kStep, idesc);
+#pragma unroll
+                for (uint32_t h = 0; h < static_cast<uint32_t>(kGemmHandover); ++h) {
+                  if (kk + h < steps) {
+                    const uint32_t d_tmem = tmem_base + ts.stage * kGemmTmemStageCols + h * kGemmTileCols;
+                    const uint64_t off = (kk + h) * kStep;
+                    if constexpr (kF8) {
+                      umma_f8_ss<false>(d_tmem, da0 + off, db0 + off, idesc);
+                      umma_f8_ss<true>(d_tmem, da0 + off, dh0 + off, idesc);
+                    } else {
+                      umma_s8_ss<false>(d_tmem, da0 + off, db0 + off, idesc);
+                    }
+                  }
                 }
                 umma_commit(&tmem_full[ts.stage]);
                 ts.advance(kGemmTmemStages);
