@@ -282,11 +282,14 @@ __device__ __forceinline__ bool gemm_epilogue_item(const GemmArgs &a, GemmEpilog
   for (int j = 0; j < CPW / 2; ++j)
     acc[j] = 0ull;
   for (uint32_t kb = 0; kb < nkb; ++kb) {
-    if (!mbar_wait_bounded(&c.smem_full[c.ps.stage], c.ps.phase, c.abort_flag))
-      return false;
+    // The stage's scale tiles arrive with its operands (same transaction barrier), and the MMA
+    // thread issues a block's MMAs only after that barrier has completed; so when an
+    // accumulator barrier of this stage has completed, the scale tiles are in shared memory.
+    // The epilogue therefore does not wait on the stage's own barrier (one barrier test per
+    // warp and stage less: 332 -> 307 us on N = 32000) and reads no scale before its first
+    // accumulator wait of the stage.
     const uint8_t *st = c.stages + static_cast<size_t>(c.ps.stage) * Stage::kBytes;
-    const float4 dw4 = reinterpret_cast<const float4 *>(st + Stage::kOffDw)[row_local];
-    const float dws[4] = {dw4.x, dw4.y, dw4.z, dw4.w};
+    float dws[4];
     const uint8_t *dx_base = st + Stage::kOffDx + dx_off;
     const uint32_t steps = min(static_cast<uint32_t>(kGemmStageBlocks), a.nb - kb * kGemmStageBlocks);
 #pragma unroll
@@ -295,6 +298,10 @@ __device__ __forceinline__ bool gemm_epilogue_item(const GemmArgs &a, GemmEpilog
         if (!mbar_wait_bounded(&c.tmem_full[c.ts.stage], c.ts.phase, c.abort_flag))
           return false;
         tcgen05_fence_after_thread_sync();
+        if (kk == 0) {
+          const float4 dw4 = reinterpret_cast<const float4 *>(st + Stage::kOffDw)[row_local];
+          dws[0] = dw4.x, dws[1] = dw4.y, dws[2] = dw4.z, dws[3] = dw4.w;
+        }
         const uint32_t taddr = c.tmem_base + lane_field + c.ts.stage * kGemmTmemStageCols + tmem_col;
         uint32_t v[CPW];
         tmem_ld_32x32b<CPW>(taddr, v);
