@@ -214,6 +214,9 @@ def test_tensor_core_gemv_reports_and_follows_its_order(cuda, pkg, O, q8w, nr, k
     pkg.check_device_errors()
     rows = np.unique(np.concatenate([np.arange(0, nr, 37), np.arange(max(0, nr - 20), nr)]))
     check_rows(O, got[rows], w[rows], x, q8w, order=order)
+    # rows of up to 4096 elements take the whole-row kernel; the tiled one (flags bit 13) gives the same bits
+    tiled = pkg.gemv(wd, xd, q8_weights=q8w, flags=0x2000).cpu().numpy()
+    assert np.array_equal(tiled.view(np.uint32), got.view(np.uint32))
     # the dp4a kernel (flags bit 12) still serves several columns, in lane-pair order
     alt = pkg.gemv(wd, xd, q8_weights=q8w, flags=0x1000).cpu().numpy()
     assert np.array_equal(alt[rows].view(np.uint32), O.gemv_lane_order(w[rows], x, q8w).view(np.uint32))
