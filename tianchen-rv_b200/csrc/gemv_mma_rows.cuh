@@ -4,10 +4,14 @@
 // rows by the 1-D bulk copy engine instead of as narrow tiled boxes.
 //
 // Why: a tiled TMA box that is only one K chunk wide (144 bytes of Q4_0 per row, two cache lines)
-// costs the copy engine about 8 cycles per row; at one box per warp that limited the kernel to
-// about 4.9 TB/s on the whole GPU and made the time per 32-row slot grow with the number of
-// boxes (measured: 16 boxes of 32 rows 2.4 us, 32 boxes of 16 rows 3.5 us per slot).  Contiguous
-// copies of 4.6 KB run at the engine's full rate.
+// costs the copy engine about 8 cycles per row, so the time per 32-row slot grows with the
+// number of boxes (measured: 16 boxes of 32 rows 2.4 us, 32 boxes of 16 rows 3.5 us per slot)
+// and the ring cannot be made deeper by making the boxes smaller.  Contiguous copies of 4.6 KB
+// run at the engine's full rate (this kernel's ring and producer alone: 6.0 TB/s), and one
+// producer warp for the whole CTA takes the copy issue out of the consumer warps, which are
+// the bottleneck (instruction issue and dependency latency, not memory).  Measured against the
+// tiled kernel with the same activation staging, 8 columns: 17.9 vs 19.0 us on 32000 x 4096,
+// 9.6 vs 10.3 us on 11008 x 4096, 5.5 vs 6.2 us on 4096 x 4096.
 //
 // Layout: a unit is one 16-row group, all of K, shared by the whole CTA: 8 row PAIRS (rows 2p,
 // 2p+1 are adjacent in memory and arrive in one copy) at a pitch of two rows plus 16 bytes.  The
@@ -17,8 +21,9 @@
 // which matrix row does not enter the arithmetic, so every output has the bits the tiled kernel
 // gives.
 //
-// Roles: 16 consumer warps (warp w owns K chunk w of every unit, its activation fragments stay
-// in registers and are read straight from global memory) and one producer warp that keeps every
+// Roles: 16 consumer warps (warp w owns K chunk w of every unit; its activation fragments stay
+// in registers, built once from a copy of its share of the columns in shared memory) and one
+// producer warp that keeps every
 // free ring position requested (lane p copies pair p).  An iteration folds kGroups units; with a
 // ring of 5 units and 2 per iteration, 3 units (about 110 KB per SM) are on their way while two
 // are folded.  The K partials are combined as in gemv_mma.cuh.
