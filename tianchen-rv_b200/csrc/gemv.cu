@@ -7,6 +7,7 @@
 #include "gemv_mma_rows.cuh"
 #include "gemv_stream.cuh"
 #include "launchers.h"
+#include "strict_stream.cuh"
 
 namespace tcrv {
 
@@ -416,6 +417,13 @@ int launch_gemv(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t
       const int grid = static_cast<int>(nslots < static_cast<size_t>(sms) ? nslots : sms);
       return launch_stream<kQ8W>(args, static_cast<uint32_t>(nc), grid, fixed + nwarps * spw * slot, stream);
     }
+  }
+
+  // the reference's strict order at streaming speed: up to 8 columns against many aligned rows
+  if (strict) {
+    constexpr int kFormat = kQ8W ? 5 : 4;
+    if (const uint32_t rps = strict_stream_rows<kFormat>(nb, nr, nc, vx, bx))
+      return launch_strict_stream<kFormat>(n, s, vx, vy, by, nr, nc, bx, bs, rps, sm_count(), stream);
   }
 
   // generic path

@@ -1,0 +1,406 @@
+// Block dots in the reference's STRICT ascending block order at streaming speed: up to 8
+// activation columns against many weight rows, for Q4_0 / Q8_0 weights (x Q8_0) and the sibling
+// formats Q4_1 x Q8_1, Q5_0 x Q8_0, Q5_1 x Q8_1.
+//
+// A row's value is a chain of nb dependent fp32 operations, one per block; the streaming GEMV
+// kernels avoid that chain by summing in another order.  Here the chain stays, but it is taken
+// off the path of the weights: the integer work and the per-block scaling are done by many
+// threads in any order, and only the final one-operation-per-block fold is sequential.
+//
+// One persistent CTA per SM walks a contiguous range of weight rows in slots of `rps` rows,
+// double buffered: a slot arrives by the bulk copy engine while the previous one is worked on.
+//   * 16 worker warps compute the block terms of a slot (thread <-> one block of one row, all
+//     columns; consecutive threads on consecutive blocks, so the 18-, 20-, 22- and 34-byte
+//     strides are conflict-free or nearly so) into a shared-memory table term[column][row][block];
+//   * 4 folding warps fold the table, thread <-> (row, column), block after block in ascending
+//     order with exactly the operations of the general kernels, so an output has the sequential
+//     fold's bits.  They run one slot behind the workers (two tables); the first of them also
+//     requests the copies: a slot's buffer is free for the slot after next as soon as its
+//     table is complete.
+// The columns are converted once per CTA into word planes (word w of every block side by side);
+// with one column and a block count that divides the worker count, a thread meets the same
+// block in every row and keeps its activation words in registers.
+//
+// Folds (reference: lib/Conversion/RVV/RVVToEmitCBlockQuantLinear.cpp:322-356, 7538-7573,
+// 472-915, 916-1391, 6817-7263):
+//   Q4_0 x Q8_0:    sumf = fma((float)sumi * d_w, d_x, sumf)       table: (float)sumi * d_w
+//   Q8_0 x Q8_0:    sumf = fma((float)sumi, d_w * d_x, sumf)       tables: (float)sumi, d_w * d_x
+//   Q5_0 x Q8_0:    sumf = fma(d_w * d_x, (float)sumi, sumf)       tables: (float)sumi, d_w * d_x
+//   Q4_1, Q5_1:     sumf = sumf + fma(d_w * d_x, (float)sumi, m_w * s_x)   table: the whole term
+#pragma once
+
+#include <atomic>
+
+#include "async_copy.cuh"
+#include "tcrv_common.cuh"
+
+namespace tcrv {
+
+enum StrictFold { kFoldQ4 = 0, kFoldProduct = 1, kFoldMin = 2 };
+
+// Block layouts: weight / activation block bytes, offsets of the quants, of the fifth-bit word
+// (0: none), the constant subtracted from the unsigned weight codes, nibble-packed or int8
+// weights, and the fold.  Formats 1..3 are the C ABI's sibling format numbers.
+template <int kFormat>
+struct StrictFormat;
+template <>
+struct StrictFormat<1> {  // Q4_1 x Q8_1
+  static constexpr int kW = 20, kA = 36, kWq = 4, kAq = 4, kQh = 0, kBias = 0;
+  static constexpr bool kNibbles = true;
+  static constexpr StrictFold kFold = kFoldMin;
+};
+template <>
+struct StrictFormat<2> {  // Q5_0 x Q8_0
+  static constexpr int kW = 22, kA = 34, kWq = 6, kAq = 2, kQh = 2, kBias = 16;
+  static constexpr bool kNibbles = true;
+  static constexpr StrictFold kFold = kFoldProduct;
+};
+template <>
+struct StrictFormat<3> {  // Q5_1 x Q8_1
+  static constexpr int kW = 24, kA = 36, kWq = 8, kAq = 4, kQh = 4, kBias = 0;
+  static constexpr bool kNibbles = true;
+  static constexpr StrictFold kFold = kFoldMin;
+};
+template <>
+struct StrictFormat<4> {  // Q4_0 x Q8_0
+  static constexpr int kW = 18, kA = 34, kWq = 2, kAq = 2, kQh = 0, kBias = 8;
+  static constexpr bool kNibbles = true;
+  static constexpr StrictFold kFold = kFoldQ4;
+};
+template <>
+struct StrictFormat<5> {  // Q8_0 x Q8_0
+  static constexpr int kW = 34, kA = 34, kWq = 2, kAq = 2, kQh = 0, kBias = 0;
+  static constexpr bool kNibbles = false;
+  static constexpr StrictFold kFold = kFoldProduct;
+};
+
+// int32 dot of one block.  Nibble formats: `q[0..3]` are the four nibble words (bytes 4w..4w+3 in
+// word w), `qh` the fifth bits (0 where the format has none); int8 weights: `q[0..7]` are the
+// weight words.  `y` are the eight activation words.
+template <int kFormat>
+__device__ __forceinline__ int strict_sumi_words(const uint32_t (&q)[8], uint32_t qh, const uint32_t (&y)[8]) {
+  using F = StrictFormat<kFormat>;
+  int sumi = 0;
+  if constexpr (!F::kNibbles) {
+#pragma unroll
+    for (int w = 0; w < 8; ++w)
+      sumi = __dp4a(static_cast<int>(q[w]), static_cast<int>(y[w]), sumi);
+    return sumi;
+  } else {
+    int ysum = 0;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      uint32_t lo = q[w] & 0x0f0f0f0fu, hi = (q[w] >> 4) & 0x0f0f0f0fu;
+      if constexpr (F::kQh != 0) {
+        // bit j of qh -> bit 4 of byte j (low half), bit 16 + j -> bit 4 of byte j (high half).
+        // b * 0x02040810 puts copies of the 4-bit field b at bits 4, 11, 18 and 25 (they do not
+        // overlap, so nothing carries); bit j of the copy at 4 + 7j is bit 4 of byte j.
+        const uint32_t bl = (qh >> (4 * w)) & 0xfu, bh = (qh >> (16 + 4 * w)) & 0xfu;
+        lo |= (bl * 0x02040810u) & 0x10101010u;
+        hi |= (bh * 0x02040810u) & 0x10101010u;
+      }
+      const uint32_t ylo = y[w], yhi = y[4 + w];
+      sumi = __dp4a(static_cast<int>(lo), static_cast<int>(ylo), sumi);  // codes 0..31 as signed bytes
+      sumi = __dp4a(static_cast<int>(hi), static_cast<int>(yhi), sumi);
+      if constexpr (F::kBias != 0) {
+        ysum = __dp4a(0x01010101, static_cast<int>(ylo), ysum);
+        ysum = __dp4a(0x01010101, static_cast<int>(yhi), ysum);
+      }
+    }
+    if constexpr (F::kBias != 0)
+      sumi -= F::kBias * ysum;  // sum((v - bias) * y) = sum(v * y) - bias * sum(y)
+    return sumi;
+  }
+}
+
+constexpr int kStrictWorkers = 512;
+constexpr int kStrictFoldWarps = 4;
+constexpr int kStrictThreads = kStrictWorkers + 32 * kStrictFoldWarps;
+constexpr int kStrictMaxRows = 32;  // rows per slot
+constexpr int kStrictMaxCols = 8;
+constexpr size_t kStrictSmemCap = 227 * 1024;
+
+struct StrictStreamArgs {
+  const uint8_t *vx;
+  const uint8_t *vy;
+  float *s;
+  size_t bx, by, bs;
+  uint32_t nr, nc, nb, row_bytes, rps, contiguous;
+};
+
+// shared-memory pieces: word planes, scale and (Q8_1) sum of every column; the term tables
+__host__ __device__ inline size_t strict_x_bytes(uint32_t nb, uint32_t nc) { return static_cast<size_t>(nc) * nb * 10 * 4; }
+__host__ __device__ inline size_t strict_table_floats(uint32_t nb, uint32_t nc, uint32_t rps, bool two) {
+  return static_cast<size_t>(nc) * rps * (nb + 1) * (two ? 2 : 1);
+}
+__host__ __device__ inline size_t strict_slots_offset(uint32_t nb, uint32_t nc, uint32_t rps, bool two) {
+  return (128 + strict_x_bytes(nb, nc) + 2 * strict_table_floats(nb, nc, rps, two) * 4 + 127) / 128 * 128;
+}
+
+// the 4 bytes at byte offset `off` (a multiple of 2) of a word array
+__device__ __forceinline__ uint32_t strict_word_at(const uint32_t *words, uint32_t off) {
+  const uint32_t i = off >> 2;
+  if ((off & 2u) == 0)
+    return words[i];
+  return __funnelshift_r(words[i], words[i + 1], 16);
+}
+
+// kOneCol: a.nc == 1, known at compile time (the common decode case: no column loops).
+template <int kFormat, bool kOneCol>
+__global__ void __launch_bounds__(kStrictThreads, 1) strict_stream_kernel(const StrictStreamArgs a) {
+  using F = StrictFormat<kFormat>;
+  constexpr bool kTwo = F::kFold == kFoldProduct;  // (float)sumi and the scale product kept apart
+  constexpr int kQWords = F::kNibbles ? 4 : 8;
+  extern __shared__ __align__(128) uint8_t smem[];
+  uint64_t *full = reinterpret_cast<uint64_t *>(smem);  // [2] slot landed
+  uint64_t *tfull = full + 2;                            // [2] table written by the 16 worker warps
+  uint64_t *tempty = full + 4;                           // [2] table folded by the 4 folding warps
+  volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(full + 6);
+  const uint32_t nb = a.nb, nc = kOneCol ? 1u : a.nc, rps = a.rps;
+  uint32_t *xq = reinterpret_cast<uint32_t *>(smem + 128);  // [nc][8][nb]
+  float *xd = reinterpret_cast<float *>(xq + static_cast<size_t>(nc) * 8 * nb);  // [nc][nb]
+  float *xs = xd + static_cast<size_t>(nc) * nb;                                  // [nc][nb] (Q8_1: s = d * sum(q))
+  float *table = xs + static_cast<size_t>(nc) * nb;  // [2][kTwo ? 2 : 1][nc][rps][nb + 1]
+  const size_t plane = static_cast<size_t>(nc) * rps * (nb + 1);  // one table of one buffer
+  const size_t table_floats = plane * (kTwo ? 2 : 1);
+  uint8_t *slots = smem + strict_slots_offset(nb, nc, rps, kTwo);
+  const size_t slot_bytes = static_cast<size_t>(rps) * a.row_bytes;
+
+  const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
+  const uint32_t r0 = static_cast<uint32_t>(static_cast<uint64_t>(a.nr) * blockIdx.x / gridDim.x);
+  const uint32_t r1 = static_cast<uint32_t>(static_cast<uint64_t>(a.nr) * (blockIdx.x + 1) / gridDim.x);
+  const uint32_t nslots = (r1 - r0 + rps - 1) / rps;
+
+  if (tid == 0) {
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&full[b], 1);
+      mbar_init(&tfull[b], kStrictWorkers / 32);
+      mbar_init(&tempty[b], kStrictFoldWarps);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  __syncthreads();
+  auto fail = [&]() {
+    if (lane == 0 && *abort_flag == 0)
+      raise_device_error(kDevErrBarrierTimeout);
+    *abort_flag = 1;
+  };
+
+  if (warp >= kStrictWorkers / 32) {
+    // ---- folding warps; the first also requests the copies.  Lane 0 announces a slot's bytes,
+    // then lanes 0..7 copy an eighth of its rows each.
+    const uint32_t fw = warp - kStrictWorkers / 32;
+    auto issue = [&](uint32_t j) {
+      const uint32_t row = r0 + j * rps, rows = min(rps, r1 - row);
+      if (lane == 0)
+        mbar_arrive_expect_tx(&full[j & 1u], rows * a.row_bytes);
+      __syncwarp();
+      const uint32_t per = (rows + 7) / 8, first = lane * per;
+      if (lane < 8 && first < rows) {
+        const uint32_t mine = min(per, rows - first);
+        uint8_t *dst = slots + (j & 1u) * slot_bytes + static_cast<size_t>(first) * a.row_bytes;
+        const uint8_t *src = a.vx + static_cast<size_t>(row + first) * a.bx;
+        if (a.contiguous) {
+          bulk_copy_g2s(dst, src, mine * a.row_bytes, &full[j & 1u]);
+        } else {
+          for (uint32_t r = 0; r < mine; ++r)
+            bulk_copy_g2s(dst + static_cast<size_t>(r) * a.row_bytes, src + r * a.bx, a.row_bytes, &full[j & 1u]);
+        }
+      }
+    };
+    uint32_t issued = 0;
+    if (fw == 0)
+      for (; issued < min(2u, nslots); ++issued)
+        issue(issued);
+    uint32_t j = 0;
+    for (; j < nslots; ++j) {
+      const uint32_t row0 = r0 + j * rps, rows = min(rps, r1 - row0);
+      const float *ta = table + (j & 1u) * table_floats;  // first table of this slot's buffer
+      if (!mbar_wait_bounded(&tfull[j & 1u], (j >> 1) & 1u, abort_flag)) {
+        fail();
+        break;
+      }
+      // the workers have read the slot's rows: its buffer takes the slot after next
+      if (fw == 0 && issued < nslots) {
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        issue(issued++);
+      }
+      // chain = (row, column); this lane takes chains fw * 32 + lane, + 128, ...
+      for (uint32_t c = fw * 32 + lane; c < rows * nc; c += 32 * kStrictFoldWarps) {
+        const uint32_t r = c / nc, col = c - r * nc;
+        const float *t = ta + (static_cast<size_t>(col) * rps + r) * (nb + 1);
+        float acc = 0.0f;
+        if constexpr (F::kFold == kFoldMin) {
+#pragma unroll 8
+          for (uint32_t ib = 0; ib < nb; ++ib)
+            acc = __fadd_rn(acc, t[ib]);
+        } else if constexpr (F::kFold == kFoldProduct) {
+          const float *p = t + plane;  // d_w * d_x
+#pragma unroll 8
+          for (uint32_t ib = 0; ib < nb; ++ib)
+            acc = __fmaf_rn(t[ib], p[ib], acc);
+        } else {
+          const float *dx = xd + static_cast<size_t>(col) * nb;
+#pragma unroll 8
+          for (uint32_t ib = 0; ib < nb; ++ib)
+            acc = __fmaf_rn(t[ib], dx[ib], acc);
+        }
+        a.s[static_cast<size_t>(row0 + r) * a.bs + col] = acc;
+      }
+      __syncwarp();
+      if (lane == 0)
+        mbar_arrive(&tempty[j & 1u]);
+    }
+    if (fw == 0 && j < nslots && lane == 0) {
+      // leaving early: copies already requested must land before the CTA's memory goes away
+      for (uint32_t u = issued >= 2 ? issued - 2 : 0; u < issued; ++u)
+        (void)mbar_wait_bounded(&full[u & 1u], (u >> 1) & 1u);
+    }
+    return;
+  }
+
+  // ---- workers: the activation columns -> word planes
+  const bool y_even = (reinterpret_cast<uintptr_t>(a.vy) & 1u) == 0 && (a.by & 1u) == 0;  // block sizes are even
+  for (uint32_t idx = tid; idx < nc * nb; idx += kStrictWorkers) {
+    const uint32_t col = idx / nb, ib = idx - col * nb;
+    const uint8_t *yb = a.vy + col * a.by + static_cast<size_t>(ib) * F::kA;
+    auto half_at = [&](int off) -> uint32_t {
+      return y_even ? static_cast<uint32_t>(*reinterpret_cast<const unsigned short *>(yb + off)) : load_u16(yb + off);
+    };
+    xd[idx] = half_bits_to_float(static_cast<unsigned short>(half_at(0)));
+    xs[idx] = F::kFold == kFoldMin ? half_bits_to_float(static_cast<unsigned short>(half_at(2))) : 0.0f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w)
+      xq[(static_cast<size_t>(col) * 8 + w) * nb + ib] = half_at(F::kAq + 4 * w) | (half_at(F::kAq + 4 * w + 2) << 16);
+  }
+  asm volatile("bar.sync 1, %0;" ::"r"(kStrictWorkers) : "memory");  // the workers only
+
+  // one column and a block index that is the same in every row: the activation block lives in registers
+  const bool fixed = kOneCol && kStrictWorkers % nb == 0;
+  uint32_t yfix[8];
+  float dfix = 0.0f, sfix = 0.0f;
+  if (fixed) {
+    const uint32_t ib = tid % nb;
+#pragma unroll
+    for (int w = 0; w < 8; ++w)
+      yfix[w] = xq[w * nb + ib];
+    dfix = xd[ib], sfix = xs[ib];
+  }
+
+  for (uint32_t j = 0; j < nslots; ++j) {
+    const uint32_t row0 = r0 + j * rps, rows = min(rps, r1 - row0);
+    float *ta = table + (j & 1u) * table_floats;
+    if (!mbar_wait_bounded(&full[j & 1u], (j >> 1) & 1u, abort_flag) ||
+        (j >= 2 && !mbar_wait_bounded(&tempty[j & 1u], ((j >> 1) - 1) & 1u, abort_flag))) {
+      fail();
+      return;
+    }
+    const uint32_t *wslot = reinterpret_cast<const uint32_t *>(slots + (j & 1u) * slot_bytes);
+    for (uint32_t e = tid; e < rows * nb; e += kStrictWorkers) {
+      const uint32_t r = e / nb, ib = e - r * nb;
+      const uint32_t *wrow = wslot + static_cast<size_t>(r) * (a.row_bytes / 4);
+      const uint32_t off = ib * F::kW;  // a multiple of 2
+      const uint32_t head = strict_word_at(wrow, off);  // d (and m) of the block
+      uint32_t q[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+      for (int w = 0; w < kQWords; ++w)
+        q[w] = strict_word_at(wrow, off + F::kWq + 4 * w);
+      uint32_t qh = 0;
+      if constexpr (F::kQh != 0)
+        qh = strict_word_at(wrow, off + F::kQh);
+      const float dw = half_bits_to_float(static_cast<unsigned short>(head & 0xffffu));
+      [[maybe_unused]] const float mw = half_bits_to_float(static_cast<unsigned short>(head >> 16));
+      for (uint32_t col = 0; col < nc; ++col) {
+        uint32_t y[8];
+        float dy, sy;
+        if (fixed) {
+#pragma unroll
+          for (int w = 0; w < 8; ++w)
+            y[w] = yfix[w];
+          dy = dfix, sy = sfix;
+        } else {
+#pragma unroll
+          for (int w = 0; w < 8; ++w)
+            y[w] = xq[(static_cast<size_t>(col) * 8 + w) * nb + ib];
+          dy = xd[col * nb + ib], sy = xs[col * nb + ib];
+        }
+        const float fs = __int2float_rn(strict_sumi_words<kFormat>(q, qh, y));
+        float *t = ta + (static_cast<size_t>(col) * rps + r) * (nb + 1) + ib;
+        if constexpr (F::kFold == kFoldMin) {
+          *t = __fmaf_rn(__fmul_rn(dw, dy), fs, __fmul_rn(mw, sy));
+        } else if constexpr (F::kFold == kFoldProduct) {
+          t[0] = fs;
+          t[plane] = __fmul_rn(dw, dy);
+        } else {
+          *t = __fmul_rn(fs, dw);
+        }
+        (void)sy;
+      }
+    }
+    // this warp's share of the table is written and its reads of the slot are done
+    __syncwarp();
+    if (lane == 0)
+      mbar_arrive(&tfull[j & 1u]);
+  }
+}
+
+// Rows per slot of the streaming form for this call (0: it does not fit or does not apply).
+template <int kFormat>
+uint32_t strict_stream_rows(uint32_t nb, size_t nr, size_t nc, const uint8_t *vx, size_t bx) {
+  using F = StrictFormat<kFormat>;
+  if (nc == 0 || nc > kStrictMaxCols || nb == 0 || nb % 8 != 0 || nr < 64 ||
+      reinterpret_cast<uintptr_t>(vx) % 16 != 0 || bx % 16 != 0)
+    return 0;
+  const size_t row_bytes = static_cast<size_t>(nb) * F::kW;
+  const bool two = F::kFold == kFoldProduct;
+  for (uint32_t rps = kStrictMaxRows; rps >= 4; rps -= 4) {
+    const size_t need = strict_slots_offset(nb, static_cast<uint32_t>(nc), rps, two) + 2 * rps * row_bytes;
+    if (need <= kStrictSmemCap)
+      return rps;
+  }
+  return 0;
+}
+
+// Launches the streaming form; the caller has checked strict_stream_rows() != 0.
+template <int kFormat>
+int launch_strict_stream(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by, size_t nr, size_t nc,
+                         size_t bx, size_t bs, uint32_t rps, int sms, cudaStream_t stream) {
+  using F = StrictFormat<kFormat>;
+  const uint32_t nb = static_cast<uint32_t>(n / kQK);
+  StrictStreamArgs args;
+  args.vx = vx;
+  args.vy = vy;
+  args.s = s;
+  args.bx = bx;
+  args.by = by;
+  args.bs = bs;
+  args.nr = static_cast<uint32_t>(nr);
+  args.nc = static_cast<uint32_t>(nc);
+  args.nb = nb;
+  args.row_bytes = nb * F::kW;
+  args.rps = rps;
+  args.contiguous = bx == static_cast<size_t>(nb) * F::kW ? 1u : 0u;
+  const size_t smem = strict_slots_offset(nb, args.nc, rps, F::kFold == kFoldProduct) +
+                      2 * static_cast<size_t>(rps) * args.row_bytes;
+  static std::atomic<bool> configured[64];
+  int dev = 0;
+  TCRV_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    TCRV_CUDA_TRY(cudaFuncSetAttribute(strict_stream_kernel<kFormat, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(kStrictSmemCap)));
+    TCRV_CUDA_TRY(cudaFuncSetAttribute(strict_stream_kernel<kFormat, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(kStrictSmemCap)));
+    configured[dev] = true;
+  }
+  const size_t slots = (nr + rps - 1) / rps;
+  const size_t grid = slots < static_cast<size_t>(sms) ? slots : static_cast<size_t>(sms);
+  if (nc == 1)
+    strict_stream_kernel<kFormat, true><<<static_cast<int>(grid), kStrictThreads, smem, stream>>>(args);
+  else
+    strict_stream_kernel<kFormat, false><<<static_cast<int>(grid), kStrictThreads, smem, stream>>>(args);
+  TCRV_CUDA_TRY(cudaGetLastError());
+  return TCRV_CUDA_OK;
+}
+
+}  // namespace tcrv
