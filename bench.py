@@ -507,10 +507,12 @@ def measure_e2e(pkg, torch, layers, steps, dist):
         if st != 0:
             raise RuntimeError(f"host sync failed: {st}")
 
+    device_flags = [0]
+
     def check():
         # the resident path must agree with the device-pointer path
         for l, w_host, x_host, y_host in host:
-            pkg.gemv(l["w"][0], l["x"], out=l["y"])
+            pkg.gemv(l["w"][0], l["x"], out=l["y"], flags=device_flags[0])
             torch.cuda.synchronize()
             if not torch.equal(l["y"].cpu(), y_host):
                 raise RuntimeError("host-pointer path disagrees with the device-pointer path")
@@ -537,6 +539,13 @@ def measure_e2e(pkg, torch, layers, steps, dist):
     dt = timed(one_pass_queued)
     one_pass_queued()
     check()
+    # the same queued step in the entries' default, the reference's strict block order (every
+    # output byte-identical with the generated kernel's): the strict streaming kernel
+    L.tcrv_cuda_host_set_fold_order(0)
+    device_flags[0] = pkg.FLAG_STRICT_ORDER
+    dt_strict = timed(one_pass_queued)
+    one_pass_queued()
+    check()
     world = dist.get_world_size() if dist is not None else 1
     for l, w_host, x_host, y_host in host:
         L.tcrv_cuda_host_unregister_weights(w_host.ctypes.data)
@@ -554,6 +563,10 @@ def measure_e2e(pkg, torch, layers, steps, dist):
                                "ms_per_step": round(dt_blocking / steps * 1e3, 4),
                                "call": "tcrv_cuda_host_gemm_q4_0_q8_0 per layer (each call waits for its result)"},
             "fold_order": "TCRV_CUDA_HOST_FOLD_FAST (lane pairs), selected with tcrv_cuda_host_set_fold_order",
+            "reference_order": {"value": round(step_bytes * steps * world / dt_strict / 1e9, 2),
+                                "ms_per_step": round(dt_strict / steps * 1e3, 4),
+                                "call": "the same queued step with the entries' default TCRV_CUDA_HOST_FOLD_STRICT: "
+                                        "every output has the bits of the reference's ascending block order"},
             "weights": "registered once (resident); activations and outputs cross PCIe every step "
                        "(inputs by a copy from the pinned buffer, results stored by the kernel into the pinned "
                        "output through its device mapping)"}
@@ -623,6 +636,13 @@ def measure_other_kernels(pkg, torch):
     y8 = torch.empty((32000, 8), device="cuda")
     timed("gemv_q4_0_q8_0_batch8", lambda c: pkg.gemv(w4[c], x8, out=y8, flags=pkg.FLAG_STATIC_WEIGHTS), 5,
           gemv_bytes(32000, 4096, 8), "32000 x 4096, batch 8")
+    # the strict-order (reference order) GEMV on the same matrix, 1 and 8 columns
+    for cols in (1, 8):
+        xs_ = pkg.quantize_q8_0(torch.randn((cols, 4096), generator=gen, device="cuda"))
+        ys_ = torch.empty((32000, cols), device="cuda")
+        timed(f"gemv_q4_0_q8_0_strict_order_b{cols}",
+              lambda c, xs_=xs_, ys_=ys_: pkg.gemv(w4[c], xs_, out=ys_, flags=pkg.FLAG_STRICT_ORDER), 5,
+              32000 * 128 * 18 + cols * 128 * 34 + 4 * cols * 32000, f"32000 x 4096, batch {cols}, strict ascending block order")
     del w4
     # consumers of the 16-row interleaved layouts: decode GEMV over block_q4_0x16 / block_q8_0x16
     # (random bytes stand in for the weights: the timing does not depend on the values), and the
