@@ -41,7 +41,11 @@ typedef enum {
 /* flags for the GEMV / GEMM entry points */
 #define TCRV_CUDA_FLAG_NONE 0u
 /* fold every row's blocks in strict ascending order (bit-identical to the sequential
- * scalar kernel with the fused fold); slower, meant for verification */
+ * scalar kernel with the fused fold).  Up to 8 columns against at least 64 rows whose base and
+ * stride are multiples of 16 bytes (block count a multiple of 8) run on a streaming kernel that
+ * keeps that order (many threads compute the per-block terms, a few fold them block after
+ * block): about half the bandwidth of the default lane-parallel order for one column; anything
+ * else on a general warp-per-output kernel */
 #define TCRV_CUDA_FLAG_STRICT_ORDER 1u
 /* the weight buffer was not written by the work that immediately precedes this call on the
  * stream (model weights are static): the decode GEMV may then start streaming weights while
@@ -173,11 +177,11 @@ int tcrv_cuda_gemm_q4_0_q8_0_prepared(size_t n, float *s, const void *prepared_w
  *   Q4_1, Q5_1:  sumf = sumf + fma(d_x*d_y, (float)sumi, m_x*s_y),
  * i.e. bit-identical to the sequential fold.  `dot_rows` is the matrix form
  * (s[row*bs + col], strides as in tcrv_cuda_gemv_*); the vec_dot entries are the reference's
- * one-row kernels (ABI order n, s, vx, vy).  One column (nc == 1) against at least 64 rows whose
- * base and stride are multiples of 16 bytes, with a block count that is a multiple of 8, runs on
- * a streaming kernel (bulk copies, a table of block terms folded row by row in ascending
- * order); everything else on a general warp-per-output kernel.  Both perform the same
- * operations in the same order. */
+ * one-row kernels (ABI order n, s, vx, vy).  Up to 8 columns against at least 64 rows whose
+ * base and stride are multiples of 16 bytes, with a block count that is a multiple of 8, run on
+ * the streaming kernel of TCRV_CUDA_FLAG_STRICT_ORDER (bulk copies, a table of block terms
+ * folded row by row in ascending order); everything else on a general warp-per-output
+ * kernel.  Both perform the same operations in the same order. */
 #define TCRV_CUDA_FORMAT_Q4_1_Q8_1 1
 #define TCRV_CUDA_FORMAT_Q5_0_Q8_0 2
 #define TCRV_CUDA_FORMAT_Q5_1_Q8_1 3

@@ -38,7 +38,8 @@ int tcrv_cuda_host_release(void);
  *                               byte-identical to the generated RVV kernel's result
  *   TCRV_CUDA_HOST_FOLD_FAST    the streaming decode kernels' own orders (lane pairs, 16-way K
  *                               split, range/chain order; see tcrv_cuda_gemv_fold_order): same
- *                               integer block sums, rows within rel 1e-5, several times faster
+ *                               integer block sums, rows within rel 1e-5, about twice as fast
+ *                               for one column (the strict order runs on a streaming kernel too)
  * The GEMM with more than 8 columns and the block-dot / GEMM-tile entries are strict either
  * way.  Process-wide; returns the previous setting, or TCRV_CUDA_ERR_INVALID_ARGUMENT. */
 #define TCRV_CUDA_HOST_FOLD_STRICT 0
