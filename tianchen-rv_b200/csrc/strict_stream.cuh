@@ -137,26 +137,31 @@ __host__ __device__ inline size_t strict_slots_offset(uint32_t nb, uint32_t nc, 
   return (128 + strict_x_bytes(nb, nc) + 2 * strict_table_floats(nb, nc, rps, two) * 4 + 127) / 128 * 128;
 }
 
-// the 4 bytes at byte offset `off` (a multiple of 2) of a word array
-__device__ __forceinline__ uint32_t strict_word_at(const uint32_t *words, uint32_t off) {
-  const uint32_t i = off >> 2;
-  if ((off & 2u) == 0)
-    return words[i];
-  return __funnelshift_r(words[i], words[i + 1], 16);
-}
-
 // kOneCol: a.nc == 1, known at compile time (the common decode case: no column loops).
 template <int kFormat, bool kOneCol>
 __global__ void __launch_bounds__(kStrictThreads, 1) strict_stream_kernel(const StrictStreamArgs a) {
   using F = StrictFormat<kFormat>;
   constexpr bool kTwo = F::kFold == kFoldProduct;  // (float)sumi and the scale product kept apart
   constexpr int kQWords = F::kNibbles ? 4 : 8;
+  // Blocks of 18, 22 or 34 bytes start on a word boundary and in the middle of a word
+  // alternately: a work item is then a PAIR of blocks (36, 44 or 68 bytes, whole words), and which
+  // fields need re-aligning is known at compile time.  Blocks of 20 or 24 bytes are items of
+  // their own.  Everything kept per block (activation planes, scales, table rows) is laid out by
+  // item: the first blocks of all items, then the second blocks, so that consecutive threads
+  // touch consecutive words.
+  constexpr bool kPairs = F::kW % 4 != 0;
+  constexpr uint32_t kUnit = kPairs ? 2 : 1;         // blocks per work item
+  constexpr uint32_t kUnitWords = kUnit * F::kW / 4;  // 5, 6 / 9, 11, 17
+  static_assert(!kPairs || (F::kWq % 4 == 2 && (F::kQh == 0 || F::kQh % 4 == 2) && F::kFold != kFoldMin),
+                "pair handling assumes a 2-byte scale followed by the other fields");
   extern __shared__ __align__(128) uint8_t smem[];
   uint64_t *full = reinterpret_cast<uint64_t *>(smem);  // [2] slot landed
   uint64_t *tfull = full + 2;                            // [2] table written by the 16 worker warps
   uint64_t *tempty = full + 4;                           // [2] table folded by the 4 folding warps
   volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(full + 6);
   const uint32_t nb = a.nb, nc = kOneCol ? 1u : a.nc, rps = a.rps;
+  const uint32_t units = nb / kUnit;  // items per row (nb is a multiple of 8)
+  auto pos = [&](uint32_t ib) { return kPairs ? (ib & 1u) * units + (ib >> 1) : ib; };  // where block ib is kept
   uint32_t *xq = reinterpret_cast<uint32_t *>(smem + 128);  // [nc][8][nb]
   float *xd = reinterpret_cast<float *>(xq + static_cast<size_t>(nc) * 8 * nb);  // [nc][nb]
   float *xs = xd + static_cast<size_t>(nc) * nb;                                  // [nc][nb] (Q8_1: s = d * sum(q))
@@ -231,20 +236,27 @@ __global__ void __launch_bounds__(kStrictThreads, 1) strict_stream_kernel(const 
         const uint32_t r = c / nc, col = c - r * nc;
         const float *t = ta + (static_cast<size_t>(col) * rps + r) * (nb + 1);
         float acc = 0.0f;
+        // ascending block order: item k holds blocks kUnit * k + h at positions h * units + k
         if constexpr (F::kFold == kFoldMin) {
 #pragma unroll 8
-          for (uint32_t ib = 0; ib < nb; ++ib)
-            acc = __fadd_rn(acc, t[ib]);
+          for (uint32_t k = 0; k < units; ++k)
+#pragma unroll
+            for (uint32_t h = 0; h < kUnit; ++h)
+              acc = __fadd_rn(acc, t[h * units + k]);
         } else if constexpr (F::kFold == kFoldProduct) {
           const float *p = t + plane;  // d_w * d_x
 #pragma unroll 8
-          for (uint32_t ib = 0; ib < nb; ++ib)
-            acc = __fmaf_rn(t[ib], p[ib], acc);
+          for (uint32_t k = 0; k < units; ++k)
+#pragma unroll
+            for (uint32_t h = 0; h < kUnit; ++h)
+              acc = __fmaf_rn(t[h * units + k], p[h * units + k], acc);
         } else {
           const float *dx = xd + static_cast<size_t>(col) * nb;
 #pragma unroll 8
-          for (uint32_t ib = 0; ib < nb; ++ib)
-            acc = __fmaf_rn(t[ib], dx[ib], acc);
+          for (uint32_t k = 0; k < units; ++k)
+#pragma unroll
+            for (uint32_t h = 0; h < kUnit; ++h)
+              acc = __fmaf_rn(t[h * units + k], dx[h * units + k], acc);
         }
         a.s[static_cast<size_t>(row0 + r) * a.bs + col] = acc;
       }
@@ -268,24 +280,28 @@ __global__ void __launch_bounds__(kStrictThreads, 1) strict_stream_kernel(const 
     auto half_at = [&](int off) -> uint32_t {
       return y_even ? static_cast<uint32_t>(*reinterpret_cast<const unsigned short *>(yb + off)) : load_u16(yb + off);
     };
-    xd[idx] = half_bits_to_float(static_cast<unsigned short>(half_at(0)));
-    xs[idx] = F::kFold == kFoldMin ? half_bits_to_float(static_cast<unsigned short>(half_at(2))) : 0.0f;
+    const uint32_t at = pos(ib);
+    xd[col * nb + at] = half_bits_to_float(static_cast<unsigned short>(half_at(0)));
+    xs[col * nb + at] = F::kFold == kFoldMin ? half_bits_to_float(static_cast<unsigned short>(half_at(2))) : 0.0f;
 #pragma unroll
     for (int w = 0; w < 8; ++w)
-      xq[(static_cast<size_t>(col) * 8 + w) * nb + ib] = half_at(F::kAq + 4 * w) | (half_at(F::kAq + 4 * w + 2) << 16);
+      xq[(static_cast<size_t>(col) * 8 + w) * nb + at] = half_at(F::kAq + 4 * w) | (half_at(F::kAq + 4 * w + 2) << 16);
   }
   asm volatile("bar.sync 1, %0;" ::"r"(kStrictWorkers) : "memory");  // the workers only
 
-  // one column and a block index that is the same in every row: the activation block lives in registers
-  const bool fixed = kOneCol && kStrictWorkers % nb == 0;
-  uint32_t yfix[8];
-  float dfix = 0.0f, sfix = 0.0f;
+  // one column and an item index that is the same in every row: the activation blocks live in registers
+  const bool fixed = kOneCol && kStrictWorkers % units == 0;
+  uint32_t yfix[kUnit][8];
+  float dfix[kUnit], sfix[kUnit];
   if (fixed) {
-    const uint32_t ib = tid % nb;
 #pragma unroll
-    for (int w = 0; w < 8; ++w)
-      yfix[w] = xq[w * nb + ib];
-    dfix = xd[ib], sfix = xs[ib];
+    for (uint32_t h = 0; h < kUnit; ++h) {
+      const uint32_t at = h * units + tid % units;
+#pragma unroll
+      for (int w = 0; w < 8; ++w)
+        yfix[h][w] = xq[w * nb + at];
+      dfix[h] = xd[at], sfix[h] = xs[at];
+    }
   }
 
   for (uint32_t j = 0; j < nslots; ++j) {
@@ -297,36 +313,28 @@ __global__ void __launch_bounds__(kStrictThreads, 1) strict_stream_kernel(const 
       return;
     }
     const uint32_t *wslot = reinterpret_cast<const uint32_t *>(slots + (j & 1u) * slot_bytes);
-    for (uint32_t e = tid; e < rows * nb; e += kStrictWorkers) {
-      const uint32_t r = e / nb, ib = e - r * nb;
-      const uint32_t *wrow = wslot + static_cast<size_t>(r) * (a.row_bytes / 4);
-      const uint32_t off = ib * F::kW;  // a multiple of 2
-      const uint32_t head = strict_word_at(wrow, off);  // d (and m) of the block
-      uint32_t q[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-#pragma unroll
-      for (int w = 0; w < kQWords; ++w)
-        q[w] = strict_word_at(wrow, off + F::kWq + 4 * w);
-      uint32_t qh = 0;
-      if constexpr (F::kQh != 0)
-        qh = strict_word_at(wrow, off + F::kQh);
-      const float dw = half_bits_to_float(static_cast<unsigned short>(head & 0xffffu));
-      [[maybe_unused]] const float mw = half_bits_to_float(static_cast<unsigned short>(head >> 16));
+    // terms of one block (row r of the slot, kept at position `at`, the h-th block of its item) for every column
+    auto emit = [&](uint32_t r, uint32_t at, uint32_t h, uint32_t dbits, uint32_t mbits, const uint32_t (&q)[8],
+                    uint32_t qh) {
+      const float dw = half_bits_to_float(static_cast<unsigned short>(dbits));
+      [[maybe_unused]] const float mw = half_bits_to_float(static_cast<unsigned short>(mbits));
       for (uint32_t col = 0; col < nc; ++col) {
         uint32_t y[8];
-        float dy, sy;
+        float dy;
+        [[maybe_unused]] float sy;
         if (fixed) {
 #pragma unroll
           for (int w = 0; w < 8; ++w)
-            y[w] = yfix[w];
-          dy = dfix, sy = sfix;
+            y[w] = yfix[h][w];
+          dy = dfix[h], sy = sfix[h];
         } else {
 #pragma unroll
           for (int w = 0; w < 8; ++w)
-            y[w] = xq[(static_cast<size_t>(col) * 8 + w) * nb + ib];
-          dy = xd[col * nb + ib], sy = xs[col * nb + ib];
+            y[w] = xq[(static_cast<size_t>(col) * 8 + w) * nb + at];
+          dy = xd[col * nb + at], sy = xs[col * nb + at];
         }
         const float fs = __int2float_rn(strict_sumi_words<kFormat>(q, qh, y));
-        float *t = ta + (static_cast<size_t>(col) * rps + r) * (nb + 1) + ib;
+        float *t = ta + (static_cast<size_t>(col) * rps + r) * (nb + 1) + at;
         if constexpr (F::kFold == kFoldMin) {
           *t = __fmaf_rn(__fmul_rn(dw, dy), fs, __fmul_rn(mw, sy));
         } else if constexpr (F::kFold == kFoldProduct) {
@@ -335,7 +343,39 @@ __global__ void __launch_bounds__(kStrictThreads, 1) strict_stream_kernel(const 
         } else {
           *t = __fmul_rn(fs, dw);
         }
-        (void)sy;
+      }
+    };
+    for (uint32_t e = tid; e < rows * units; e += kStrictWorkers) {
+      const uint32_t r = e / units, iu = e - r * units;
+      const uint32_t *w = wslot + static_cast<size_t>(r) * (a.row_bytes / 4) + iu * kUnitWords;
+      uint32_t pw[kUnitWords];
+#pragma unroll
+      for (uint32_t k = 0; k < kUnitWords; ++k)
+        pw[k] = w[k];
+      uint32_t q[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      uint32_t qh = 0;
+      if constexpr (!kPairs) {
+#pragma unroll
+        for (int k = 0; k < kQWords; ++k)
+          q[k] = pw[F::kWq / 4 + k];
+        if constexpr (F::kQh != 0)
+          qh = pw[F::kQh / 4];
+        emit(r, iu, 0, pw[0] & 0xffffu, pw[0] >> 16, q, qh);
+      } else {
+        // even block: starts on a word boundary, its fields lie 2 bytes into a word
+#pragma unroll
+        for (int k = 0; k < kQWords; ++k)
+          q[k] = __funnelshift_r(pw[(F::kWq + 4 * k) / 4], pw[(F::kWq + 4 * k) / 4 + 1], 16);
+        if constexpr (F::kQh != 0)
+          qh = __funnelshift_r(pw[F::kQh / 4], pw[F::kQh / 4 + 1], 16);
+        emit(r, iu, 0, pw[0] & 0xffffu, 0, q, qh);
+        // odd block: starts 2 bytes into a word, its fields are word aligned
+#pragma unroll
+        for (int k = 0; k < kQWords; ++k)
+          q[k] = pw[(F::kW + F::kWq + 4 * k) / 4];
+        if constexpr (F::kQh != 0)
+          qh = pw[(F::kW + F::kQh) / 4];
+        emit(r, units + iu, 1, pw[F::kW / 4] >> 16, 0, q, qh);
       }
     }
     // this warp's share of the table is written and its reads of the slot are done
