@@ -826,7 +826,7 @@ def measure_gemm(pkg, torch, dist, rank, world):
     return results
 
 
-PROFILE_CASES = ["gemv", "gemv_q8", "gemm", "dequant", "quantize", "silu", "rms_norm", "repack_gemv", "repack_gemv_q8",
+PROFILE_CASES = ["gemv", "gemv_q8", "gemv_strict", "gemm", "dequant", "quantize", "silu", "rms_norm", "repack_gemv", "repack_gemv_q8",
                  "repack_gemm", "sibling_q4_1", "sibling_q5_0", "sibling_q5_1"]
 
 
@@ -845,16 +845,17 @@ def run_profile_case(args):
     pkg = entry.load_package()
     torch.cuda.set_device(0)
     gen = torch.Generator(device="cuda").manual_seed(7)
-    if args.case in ("gemv", "gemv_q8"):
+    if args.case in ("gemv", "gemv_q8", "gemv_strict"):
         rows = args.rows or 32000
         q8w = args.case == "gemv_q8"
+        flags = pkg.FLAG_STRICT_ORDER if args.case == "gemv_strict" else 0
         wf = torch.randn((rows, args.k), generator=gen, device="cuda") * 0.02
         w = pkg.quantize_q8_0(wf) if q8w else pkg.quantize_q4_0(wf)
         copies = [w] + [w.clone() for _ in range(max(2, (300 << 20) // w.numel()))]
         x = pkg.quantize_q8_0(torch.randn((args.cols, args.k), generator=gen, device="cuda"))
         y = torch.empty((rows, args.cols), dtype=torch.float32, device="cuda")
         for i in range(args.launches):
-            pkg.gemv(copies[i % len(copies)], x, q8_weights=q8w, out=y)
+            pkg.gemv(copies[i % len(copies)], x, q8_weights=q8w, out=y, flags=flags)
     elif args.case in ("repack_gemv", "repack_gemv_q8"):
         # random bytes stand in for the interleaved weights (timing and traffic do not depend on them)
         rows = args.rows or 32000
