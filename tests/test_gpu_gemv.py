@@ -220,3 +220,33 @@ def test_tensor_core_gemv_reports_and_follows_its_order(cuda, pkg, O, q8w, nr, k
     # the dp4a kernel (flags bit 12) still serves several columns, in lane-pair order
     alt = pkg.gemv(wd, xd, q8_weights=q8w, flags=0x1000).cpu().numpy()
     assert np.array_equal(alt[rows].view(np.uint32), O.gemv_lane_order(w[rows], x, q8w).view(np.uint32))
+
+
+@pytest.mark.parametrize("q8w", [False, True])
+@pytest.mark.parametrize("nr,k,nc", [(64, 256, 4), (97, 256, 6), (1000, 4096, 8), (333, 2048, 5), (1000, 4096, 1),
+                                     (500, 4096, 3), (257, 11008, 8), (70, 4096, 8)])
+def test_strict_order_streaming_kernels_are_bit_exact(cuda, pkg, O, q8w, nr, k, nc):
+    # At least 64 aligned rows take the strict streaming kernels (term table + sequential fold): the
+    # tensor-core form for 4..8 columns on rows of up to 4096 elements, the dp4a form otherwise.
+    # Every output must have the bits of the sequential fold; flags bit 13 (dp4a form) gives the same.
+    w, x = make(O, nr, k, nc, q8w, 2300 + nr + nc)
+    wd, xd = dev(cuda, w), dev(cuda, x)
+    want = O.gemm(w, x, q8_weights=q8w, fold=O.FOLD_FMA, threads=8)
+    got = pkg.gemv(wd, xd, q8_weights=q8w, flags=pkg.FLAG_STRICT_ORDER).cpu().numpy()
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    alt = pkg.gemv(wd, xd, q8_weights=q8w, flags=pkg.FLAG_STRICT_ORDER | 0x2000).cpu().numpy()
+    assert np.array_equal(alt.view(np.uint32), want.view(np.uint32))
+    # rows with a stride, the activation columns 2 bytes off a 16-byte boundary
+    L = pkg.lib()
+    wt = cuda.zeros((nr, w.shape[1] + 32), dtype=cuda.uint8, device="cuda")
+    wt[:, : w.shape[1]] = wd
+    xt = cuda.zeros((nc * (x.shape[1] + 10) + 2,), dtype=cuda.uint8, device="cuda")
+    xv = xt[2:].view(nc, x.shape[1] + 10)
+    xv[:, : x.shape[1]] = xd
+    out = cuda.full((nr, nc + 1), -1.0, dtype=cuda.float32, device="cuda")
+    fn = L.tcrv_cuda_gemv_q8_0_q8_0 if q8w else L.tcrv_cuda_gemv_q4_0_q8_0
+    assert fn(k, out.data_ptr(), wt.data_ptr(), xv.data_ptr(), xv.stride(0), nr, nc, wt.stride(0), nc + 1,
+              pkg.FLAG_STRICT_ORDER, cuda.cuda.current_stream().cuda_stream) == 0
+    pkg.check_device_errors()
+    res = out.cpu().numpy()
+    assert np.array_equal(res[:, :nc].view(np.uint32), want.view(np.uint32)) and np.all(res[:, nc] == -1.0)

@@ -5,6 +5,7 @@
 #include <atomic>
 #include "gemv_mma.cuh"
 #include "gemv_mma_rows.cuh"
+#include "gemv_mma_strict.cuh"
 #include "gemv_stream.cuh"
 #include "launchers.h"
 #include "strict_stream.cuh"
@@ -323,6 +324,68 @@ int launch_mma_rows(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, si
   return TCRV_CUDA_OK;
 }
 
+// The strict-order tensor-core GEMV (4..8 columns, rows of at most 16 chunks): ring depth in
+// 16-row units, 0 if it does not apply.
+template <bool kQ8W>
+size_t mma_strict_ring(uint32_t nb, size_t nr, size_t nc, const uint8_t *vx, size_t bx) {
+  if (nc < kMmaMinCols || nc > static_cast<size_t>(kRowsCols) || nb == 0 || nb % kMmaChunkBlocks != 0 ||
+      nb > static_cast<uint32_t>(kMmaWarps * kMmaChunkBlocks) || nr < 64 || !multiple_of(vx, 16) || bx % 16 != 0)
+    return 0;
+  const size_t unit = kRowsPairs * mma_rows_pair_pitch<kQ8W>(nb);
+  const size_t fixed = strict_mma_fixed_bytes(nb, kQ8W);
+  if (fixed + 2 * unit > kMaxDynamicSmem)
+    return 0;
+  const size_t ring = (kMaxDynamicSmem - fixed) / unit;
+  return ring > static_cast<size_t>(kStrictMmaMaxRing) ? static_cast<size_t>(kStrictMmaMaxRing) : ring;
+}
+
+template <bool kQ8W>
+int launch_mma_strict(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by, size_t nr, size_t nc,
+                      size_t bx, size_t bs, unsigned flags, size_t ring, cudaStream_t stream) {
+  constexpr int WB = WeightFormat<kQ8W>::kBlockBytes;
+  const uint32_t nb = static_cast<uint32_t>(n / kQK);
+  GemvRowsArgs args;
+  args.vx = vx;
+  args.vy = vy;
+  args.s = s;
+  args.bx = bx;
+  args.by = by;
+  args.bs = bs;
+  args.nr = static_cast<uint32_t>(nr);
+  args.nc = static_cast<uint32_t>(nc);
+  args.nb = nb;
+  args.row_bytes = nb * WB;
+  args.pair_pitch = static_cast<uint32_t>(mma_rows_pair_pitch<kQ8W>(nb));
+  args.ring = static_cast<uint32_t>(ring);
+  args.contiguous = bx == static_cast<size_t>(nb) * WB ? 1u : 0u;
+  args.static_weights = (flags & TCRV_CUDA_FLAG_STATIC_WEIGHTS) ? 1u : 0u;
+  args.x_aligned = multiple_of(vy, 16) && by % 16 == 0 ? 1u : 0u;
+  const size_t smem = strict_mma_fixed_bytes(nb, kQ8W) + ring * kRowsPairs * args.pair_pitch;
+  auto kernel = gemv_mma_strict_kernel<kQ8W>;
+  static std::atomic<bool> configured[64];
+  int dev = 0;
+  TCRV_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    TCRV_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(kMaxDynamicSmem)));
+    configured[dev] = true;
+  }
+  const size_t units = (nr + kMmaRows - 1) / kMmaRows;
+  const int sms = sm_count();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(units < static_cast<size_t>(sms) ? units : sms));
+  cfg.blockDim = dim3(kStrictMmaThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  TCRV_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, args));
+  return TCRV_CUDA_OK;
+}
+
 }  // namespace
 
 // 0 = strict ascending, 1 = lane pairs + butterfly, 2 = 16-way K split (see tcrv_cuda.h).
@@ -421,6 +484,10 @@ int launch_gemv(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t
 
   // the reference's strict order at streaming speed: up to 8 columns against many aligned rows
   if (strict) {
+    // 4..8 columns on short rows: the tensor-core form (flags bit 13 keeps the dp4a form: tuning)
+    if ((flags & 0x2000u) == 0)
+      if (const size_t ring = mma_strict_ring<kQ8W>(nb, nr, nc, vx, bx))
+        return launch_mma_strict<kQ8W>(n, s, vx, vy, by, nr, nc, bx, bs, flags, ring, stream);
     constexpr int kFormat = kQ8W ? 5 : 4;
     if (const uint32_t rps = strict_stream_rows<kFormat>(nb, nr, nc, vx, bx))
       return launch_strict_stream<kFormat>(n, s, vx, vy, by, nr, nc, bx, bs, rps, sm_count(), stream);

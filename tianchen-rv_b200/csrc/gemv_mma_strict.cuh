@@ -1,0 +1,308 @@
+// Decode GEMV for 4..8 activation columns in the reference's STRICT ascending block order, on
+// the tensor cores (rows of at most 128 blocks).
+//
+// The integer work is that of gemv_mma_rows.cuh: whole rows by bulk copies from a producer warp,
+// 16 MMA warps that split K 16 ways (warp w owns the 8 blocks of chunk w), one
+// mma.sync.m16n8k32.s8 per ggml block of a 16-row unit.  What differs is what happens to a
+// block's int32 tile: instead of folding it into a running K-partial (which fixes a 16-way
+// summation order), the warp scales it by the weight scale - the first, order-free half of the
+// reference's fold - and drops the 16 x 8 terms of the block into a shared-memory table
+// term[row][block][column].  Four folding warps then run the second half as the reference does:
+// thread <-> (row, column), block after block,
+//   Q4_0:  acc = fma(term, d_x, acc),            term = (float)sumi * d_w
+//   Q8_0:  acc = fma(term, d_w * d_x, acc),      term = (float)sumi
+// so every output has the bits of the sequential fold (lib/Conversion/RVV/
+// RVVToEmitCBlockQuantLinear.cpp:322-356, 7538-7573).  One table: the MMA warps fill it for unit
+// h + 1 when the folding warps have read unit h (the MMA phase is short, 8 MMAs per warp).
+//
+// Table layout: row slot rho (0..15), then block, then the 8 columns side by side.  Thread
+// (g = lane / 4, t = lane % 4) of an MMA warp holds rows 2g, 2g+1 x columns 2t, 2t+1 and writes
+// them as two 8-byte stores to slots g and g + 8; with an odd block pitch both the stores and
+// the folding warps' loads (lane <-> slot 4 * fw + lane / 8, column lane % 8) are conflict-free.
+#pragma once
+
+#include "gemv_mma_rows.cuh"
+
+namespace tcrv {
+
+constexpr int kStrictMmaFoldWarps = 4;
+constexpr int kStrictMmaThreads = (kMmaWarps + 1 + kStrictMmaFoldWarps) * 32;
+constexpr int kStrictMmaBarrierBytes = 256;  // full/empty per ring position, table full/empty, abort word
+constexpr int kStrictMmaMaxRing = 8;
+
+// bytes of the column-scale array, the term table (which also serves as the staging room of the
+// activation columns in the prologue) and, for Q8_0 weights, the weight-scale table
+__host__ __device__ inline size_t strict_mma_fixed_bytes(uint32_t nb, bool q8w) {
+  const size_t xd = static_cast<size_t>(nb) * kRowsCols * 4;
+  size_t table = static_cast<size_t>(kMmaRows) * (nb + 1) * kRowsCols * 4;
+  if (table < static_cast<size_t>(kMmaWarps) * kRowsStageWarpBytes)
+    table = static_cast<size_t>(kMmaWarps) * kRowsStageWarpBytes;
+  const size_t dwt = q8w ? static_cast<size_t>(kMmaRows) * (nb + 1) * 4 : 0;
+  return (kStrictMmaBarrierBytes + xd + table + dwt + 127) / 128 * 128;
+}
+
+template <bool kQ8W>
+__global__ void __launch_bounds__(kStrictMmaThreads, 1) gemv_mma_strict_kernel(const GemvRowsArgs a) {
+  using F = WeightFormat<kQ8W>;
+  constexpr int WB = F::kBlockBytes;
+  constexpr int CB = kMmaChunkBlocks * WB;  // chunk bytes per row: 144 or 272
+  extern __shared__ __align__(128) uint8_t smem[];
+  uint64_t *full = reinterpret_cast<uint64_t *>(smem);  // unit landed (8 pair copies)
+  uint64_t *empty = full + kStrictMmaMaxRing;           // unit read by all 16 MMA warps
+  uint64_t *tfull = empty + kStrictMmaMaxRing;          // table written by all 16 MMA warps
+  uint64_t *tempty = tfull + 1;                         // table folded by the 4 folding warps
+  volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(tempty + 1);
+  const uint32_t nb = a.nb, pitch = nb + 1;  // blocks of a row slot in the table (odd)
+  float *xd = reinterpret_cast<float *>(smem + kStrictMmaBarrierBytes);  // [nb][8]
+  float *table = xd + static_cast<size_t>(nb) * kRowsCols;               // [16][pitch][8]
+  size_t table_bytes = static_cast<size_t>(kMmaRows) * pitch * kRowsCols * 4;
+  if (table_bytes < static_cast<size_t>(kMmaWarps) * kRowsStageWarpBytes)
+    table_bytes = static_cast<size_t>(kMmaWarps) * kRowsStageWarpBytes;
+  [[maybe_unused]] float *dwt = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(table) + table_bytes);  // [16][pitch]
+  uint8_t *units = smem + strict_mma_fixed_bytes(nb, kQ8W);
+  const uint32_t ring = a.ring;
+  const uint32_t unit_bytes = kRowsPairs * a.pair_pitch;
+  const uint32_t units_addr = smem_addr(units);
+
+  const uint32_t warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const uint32_t all_units = (a.nr + kMmaRows - 1) / kMmaRows;
+  const uint32_t u0 = static_cast<uint32_t>(static_cast<uint64_t>(all_units) * blockIdx.x / gridDim.x);
+  const uint32_t u1 = static_cast<uint32_t>(static_cast<uint64_t>(all_units) * (blockIdx.x + 1) / gridDim.x);
+  const uint32_t nunits = u1 - u0;  // unit h of this CTA = rows 16 * (u0 + h) .., in ring position h % ring
+  const uint32_t nchunks = nb / kMmaChunkBlocks;
+
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  if (!a.static_weights)
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (threadIdx.x == 0) {
+    for (uint32_t r = 0; r < ring; ++r) {
+      mbar_init(&full[r], kRowsPairs);
+      mbar_init(&empty[r], kMmaWarps);
+    }
+    mbar_init(tfull, kMmaWarps);
+    mbar_init(tempty, kStrictMmaFoldWarps);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  __syncthreads();
+  auto fail = [&]() {
+    if (lane == 0 && *abort_flag == 0)
+      raise_device_error(kDevErrBarrierTimeout);
+    *abort_flag = 1;
+  };
+
+  if (warp == kMmaWarps) {
+    // ---- producer: lane p brings pair p of every unit
+    uint32_t issued = 0;
+    bool ok = true;
+    for (uint32_t h = 0; h < nunits && ok; ++h) {
+      const uint32_t pos = h % ring;
+      if (h >= ring)  // the position's previous unit must have been read by every MMA warp
+        ok = mbar_wait_bounded(&empty[pos], ((h / ring) - 1) & 1, abort_flag);
+      if (!ok)
+        break;
+      if (lane < kRowsPairs) {
+        const uint32_t row = (u0 + h) * kMmaRows + 2 * lane;
+        const uint32_t rows = row < a.nr ? min(2u, a.nr - row) : 0u;  // a ragged last unit has fewer
+        uint8_t *dst = units + static_cast<size_t>(pos) * unit_bytes + static_cast<size_t>(lane) * a.pair_pitch;
+        const uint8_t *src = a.vx + static_cast<size_t>(row) * a.bx;
+        if (rows == 0) {
+          mbar_arrive(&full[pos]);
+        } else {
+          // reads of the position by the MMA warps happened before their arrivals on `empty`
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          mbar_arrive_expect_tx(&full[pos], rows * a.row_bytes);
+          if (a.contiguous || rows == 1) {
+            bulk_copy_g2s(dst, src, rows * a.row_bytes, &full[pos]);
+          } else {
+            bulk_copy_g2s(dst, src, a.row_bytes, &full[pos]);
+            bulk_copy_g2s(dst + a.row_bytes, src + a.bx, a.row_bytes, &full[pos]);
+          }
+        }
+      }
+      issued = h + 1;
+    }
+    if (!ok && lane == 0) {
+      if (*abort_flag == 0)
+        raise_device_error(kDevErrBarrierTimeout);
+      *abort_flag = 1;
+      // copies already requested must land before the CTA's shared memory goes away
+      for (uint32_t h = issued > ring ? issued - ring : 0; h < issued; ++h)
+        (void)mbar_wait_bounded(&full[h % ring], (h / ring) & 1);
+    }
+    return;
+  }
+
+  if (warp > kMmaWarps) {
+    // ---- folding warps: lane <-> (row slot 4 * fw + lane / 8, column lane % 8)
+    const uint32_t fw = warp - kMmaWarps - 1;
+    const uint32_t rho = fw * 4 + (lane >> 3), col = lane & 7;
+    const uint32_t row_in_unit = rho < 8 ? 2 * rho : 2 * (rho - 8) + 1;
+    const float *tr = table + (static_cast<size_t>(rho) * pitch) * kRowsCols + col;
+    for (uint32_t h = 0; h < nunits; ++h) {
+      if (!mbar_wait_bounded(tfull, h & 1, abort_flag)) {
+        fail();
+        return;
+      }
+      float acc = 0.0f;
+      if constexpr (kQ8W) {
+        const float *dw = dwt + static_cast<size_t>(rho) * pitch;
+#pragma unroll 8
+        for (uint32_t ib = 0; ib < nb; ++ib)
+          acc = __fmaf_rn(tr[ib * kRowsCols], __fmul_rn(dw[ib], xd[ib * kRowsCols + col]), acc);
+      } else {
+#pragma unroll 8
+        for (uint32_t ib = 0; ib < nb; ++ib)
+          acc = __fmaf_rn(tr[ib * kRowsCols], xd[ib * kRowsCols + col], acc);
+      }
+      // this lane has read its part of the table
+      __syncwarp();
+      if (lane == 0)
+        mbar_arrive(tempty);
+      const uint32_t row = (u0 + h) * kMmaRows + row_in_unit;
+      if (row < a.nr && col < a.nc)
+        a.s[static_cast<size_t>(row) * a.bs + col] = acc;
+    }
+    return;
+  }
+
+  // ---- MMA warps
+  if (a.static_weights)
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+  // Activation fragments (see gemv_mma_rows.cuh): two quant words of column g, -8 * sum(q) of
+  // columns 2t and 2t+1; the column scales go to shared memory for the folding warps.
+  uint32_t xb0[kMmaChunkBlocks], xb1[kMmaChunkBlocks];
+  int2 xsx[kMmaChunkBlocks];
+  const bool active = warp < nchunks;
+  if (active) {
+    const bool col_ok = static_cast<uint32_t>(g) < a.nc;
+    float dcol[kMmaChunkBlocks];  // scale of column g
+    if (a.x_aligned) {
+      uint8_t *stage = reinterpret_cast<uint8_t *>(table) + warp * kRowsStageWarpBytes;
+      constexpr int kPieces = kRowsStageColBytes / 16;  // 17 per column
+      uint4 piece[(kRowsCols * kPieces + 31) / 32];
+#pragma unroll
+      for (int r = 0; r < (kRowsCols * kPieces + 31) / 32; ++r) {
+        const uint32_t idx = r * 32 + lane, c = idx / kPieces, k = idx - c * kPieces;
+        piece[r] = make_uint4(0, 0, 0, 0);
+        if (c < a.nc)
+          piece[r] = *reinterpret_cast<const uint4 *>(a.vy + c * a.by + static_cast<size_t>(warp) * kRowsStageColBytes +
+                                                      k * 16);
+      }
+#pragma unroll
+      for (int r = 0; r < (kRowsCols * kPieces + 31) / 32; ++r) {
+        const uint32_t idx = r * 32 + lane;
+        if (idx < kRowsCols * kPieces)
+          reinterpret_cast<uint4 *>(stage)[idx] = piece[r];
+      }
+      __syncwarp();
+      const uint32_t mine = smem_addr(stage) + g * kRowsStageColBytes;
+#pragma unroll
+      for (int bi = 0; bi < kMmaChunkBlocks; ++bi) {
+        const uint32_t blk = mine + bi * kQ8Block + 2 + 4 * t;
+        xb0[bi] = static_cast<uint32_t>(lds_u16(blk)) | (static_cast<uint32_t>(lds_u16(blk + 2)) << 16);
+        xb1[bi] = static_cast<uint32_t>(lds_u16(blk + 16)) | (static_cast<uint32_t>(lds_u16(blk + 18)) << 16);
+        dcol[bi] = half_bits_to_float(lds_u16(mine + bi * kQ8Block));
+      }
+    } else {
+#pragma unroll
+      for (int bi = 0; bi < kMmaChunkBlocks; ++bi) {
+        const size_t off = static_cast<size_t>(warp * kMmaChunkBlocks + bi) * kQ8Block;
+        const unsigned short *h = reinterpret_cast<const unsigned short *>(a.vy + g * a.by + off);
+        xb0[bi] = col_ok ? static_cast<uint32_t>(h[1 + 2 * t]) | (static_cast<uint32_t>(h[2 + 2 * t]) << 16) : 0u;
+        xb1[bi] = col_ok ? static_cast<uint32_t>(h[9 + 2 * t]) | (static_cast<uint32_t>(h[10 + 2 * t]) << 16) : 0u;
+        dcol[bi] = col_ok ? half_bits_to_float(h[0]) : 0.0f;
+      }
+    }
+#pragma unroll
+    for (int bi = 0; bi < kMmaChunkBlocks; ++bi) {
+      int sum = __dp4a(static_cast<int>(xb0[bi]), 0x01010101, __dp4a(static_cast<int>(xb1[bi]), 0x01010101, 0));
+      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+      xsx[bi].x = -8 * __shfl_sync(0xffffffffu, sum, 8 * t);
+      xsx[bi].y = -8 * __shfl_sync(0xffffffffu, sum, 8 * t + 4);
+      if (t == 0)  // one lane per column
+        xd[(warp * kMmaChunkBlocks + bi) * kRowsCols + g] = dcol[bi];
+    }
+  }
+  // the staging room becomes the term table: no warp may write a term before every warp has
+  // read its fragments (named barrier of the 16 MMA warps; the other roles are elsewhere)
+  asm volatile("bar.sync 1, %0;" ::"r"(kMmaWarps * 32) : "memory");
+
+  for (uint32_t h = 0; h < nunits; ++h) {
+    // the unit's rows have landed, and the folding warps have read the previous unit's terms
+    if (!mbar_wait_bounded(&full[h % ring], (h / ring) & 1, abort_flag) ||
+        (h >= 1 && !mbar_wait_bounded(tempty, (h - 1) & 1, abort_flag))) {
+      fail();
+      return;
+    }
+    if (active) {
+      const uint32_t row_lo = units_addr + (h % ring) * unit_bytes + g * a.pair_pitch + warp * CB;
+      const uint32_t row_hi = row_lo + a.row_bytes;
+      float *out_lo = table + (static_cast<size_t>(g) * pitch + warp * kMmaChunkBlocks) * kRowsCols + 2 * t;
+      float *out_hi = out_lo + static_cast<size_t>(8) * pitch * kRowsCols;
+#pragma unroll
+      for (int bi = 0; bi < kMmaChunkBlocks; ++bi) {
+        // bytes 2.. of a block are 4-byte aligned for odd bi and off by two for even bi
+        uint32_t afrag[4];
+        float dw_lo, dw_hi;
+        auto load_rows = [&](uint32_t row, uint32_t &k_lo, uint32_t &k_hi, float &dw) {
+          const uint32_t blk = row + bi * WB;
+          dw = half_bits_to_float(lds_u16(blk));
+          auto word_at = [&](int byte_off) -> uint32_t {  // the 4 bytes at blk + 2 + byte_off
+            if ((bi & 1) != 0)
+              return lds_u32(blk + 2 + byte_off);
+            return __funnelshift_r(lds_u32(blk + byte_off), lds_u32(blk + byte_off + 4), 16);
+          };
+          if constexpr (kQ8W) {
+            k_lo = word_at(4 * t);
+            k_hi = word_at(16 + 4 * t);
+          } else {
+            const uint32_t qw = word_at(4 * t);
+            k_lo = qw & 0x0f0f0f0fu;
+            k_hi = (qw >> 4) & 0x0f0f0f0fu;
+          }
+        };
+        load_rows(row_lo, afrag[0], afrag[2], dw_lo);
+        load_rows(row_hi, afrag[1], afrag[3], dw_hi);
+        int c[4];
+        // Q4_0: the nibbles enter unsigned; -8 * sum(x) of each column rides in as the MMA's C input
+        if constexpr (kQ8W)
+          mma_m16n8k32_s8(c, afrag, xb0[bi], xb1[bi], 0, 0);
+        else
+          mma_m16n8k32_s8(c, afrag, xb0[bi], xb1[bi], xsx[bi].x, xsx[bi].y);
+        // (float)sumi without a conversion instruction (see gemv_mma.cuh), then the order-free
+        // half of the fold: Q4_0 scales by d_w (one rounding), Q8_0 keeps the exact integer
+        const uint64_t b_lo = mma_pack2(__uint_as_float(static_cast<uint32_t>(c[0]) + kMmaMagicBits),
+                                        __uint_as_float(static_cast<uint32_t>(c[1]) + kMmaMagicBits));
+        const uint64_t b_hi = mma_pack2(__uint_as_float(static_cast<uint32_t>(c[2]) + kMmaMagicBits),
+                                        __uint_as_float(static_cast<uint32_t>(c[3]) + kMmaMagicBits));
+        uint64_t t_lo, t_hi;
+        if constexpr (kQ8W) {
+          const uint64_t neg = mma_pack2(-kMmaMagic, -kMmaMagic);
+          t_lo = mma_add2(b_lo, neg);
+          t_hi = mma_add2(b_hi, neg);
+          if (t == 0) {
+            dwt[static_cast<size_t>(g) * pitch + warp * kMmaChunkBlocks + bi] = dw_lo;
+            dwt[static_cast<size_t>(g + 8) * pitch + warp * kMmaChunkBlocks + bi] = dw_hi;
+          }
+        } else {
+          const float n_lo = __fmul_rn(-kMmaMagic, dw_lo), n_hi = __fmul_rn(-kMmaMagic, dw_hi);
+          t_lo = mma_fma2(b_lo, mma_pack2(dw_lo, dw_lo), mma_pack2(n_lo, n_lo));
+          t_hi = mma_fma2(b_hi, mma_pack2(dw_hi, dw_hi), mma_pack2(n_hi, n_hi));
+        }
+        *reinterpret_cast<uint64_t *>(out_lo + bi * kRowsCols) = t_lo;
+        *reinterpret_cast<uint64_t *>(out_hi + bi * kRowsCols) = t_hi;
+      }
+    }
+    // every lane has read its words of the unit and written its terms
+    __syncwarp();
+    if (lane == 0) {
+      mbar_arrive(&empty[h % ring]);
+      mbar_arrive(tfull);
+    }
+  }
+}
+
+}  // namespace tcrv
