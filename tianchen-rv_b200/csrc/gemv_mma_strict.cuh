@@ -12,8 +12,10 @@
 //   Q4_0:  acc = fma(term, d_x, acc),            term = (float)sumi * d_w
 //   Q8_0:  acc = fma(term, d_w * d_x, acc),      term = (float)sumi
 // so every output has the bits of the sequential fold (lib/Conversion/RVV/
-// RVVToEmitCBlockQuantLinear.cpp:322-356, 7538-7573).  One table: the MMA warps fill it for unit
-// h + 1 when the folding warps have read unit h (the MMA phase is short, 8 MMAs per warp).
+// RVVToEmitCBlockQuantLinear.cpp:322-356, 7538-7573).  One table, handed over in two halves of
+// K (blocks 0..63 by MMA warps 0..7, blocks 64..127 by warps 8..15): the folding warps start on
+// the first half while the second is still being written, and warps 0..7 refill their half for
+// the next unit while the fold runs through the second.
 //
 // Table layout: row slot rho (0..15), then block, then the 8 columns side by side.  Thread
 // (g = lane / 4, t = lane % 4) of an MMA warp holds rows 2g, 2g+1 x columns 2t, 2t+1 and writes
@@ -49,9 +51,10 @@ __global__ void __launch_bounds__(kStrictMmaThreads, 1) gemv_mma_strict_kernel(c
   extern __shared__ __align__(128) uint8_t smem[];
   uint64_t *full = reinterpret_cast<uint64_t *>(smem);  // unit landed (8 pair copies)
   uint64_t *empty = full + kStrictMmaMaxRing;           // unit read by all 16 MMA warps
-  uint64_t *tfull = empty + kStrictMmaMaxRing;          // table written by all 16 MMA warps
-  uint64_t *tempty = tfull + 1;                         // table folded by the 4 folding warps
-  volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(tempty + 1);
+  uint64_t *tfull = empty + kStrictMmaMaxRing;          // [2] half of the table written by its 8 MMA warps
+  uint64_t *tempty = tfull + 2;                         // [2] half of the table folded by the 4 folding warps
+  volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(tempty + 2);
+  constexpr uint32_t kHalfBlocks = kMmaWarps / 2 * kMmaChunkBlocks;  // 64
   const uint32_t nb = a.nb, pitch = nb + 1;  // blocks of a row slot in the table (odd)
   float *xd = reinterpret_cast<float *>(smem + kStrictMmaBarrierBytes);  // [nb][8]
   float *table = xd + static_cast<size_t>(nb) * kRowsCols;               // [16][pitch][8]
@@ -80,8 +83,10 @@ __global__ void __launch_bounds__(kStrictMmaThreads, 1) gemv_mma_strict_kernel(c
       mbar_init(&full[r], kRowsPairs);
       mbar_init(&empty[r], kMmaWarps);
     }
-    mbar_init(tfull, kMmaWarps);
-    mbar_init(tempty, kStrictMmaFoldWarps);
+    for (int x = 0; x < 2; ++x) {
+      mbar_init(&tfull[x], kMmaWarps / 2);
+      mbar_init(&tempty[x], kStrictMmaFoldWarps);
+    }
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -141,25 +146,29 @@ __global__ void __launch_bounds__(kStrictMmaThreads, 1) gemv_mma_strict_kernel(c
     const uint32_t row_in_unit = rho < 8 ? 2 * rho : 2 * (rho - 8) + 1;
     const float *tr = table + (static_cast<size_t>(rho) * pitch) * kRowsCols + col;
     for (uint32_t h = 0; h < nunits; ++h) {
-      if (!mbar_wait_bounded(tfull, h & 1, abort_flag)) {
-        fail();
-        return;
-      }
       float acc = 0.0f;
-      if constexpr (kQ8W) {
-        const float *dw = dwt + static_cast<size_t>(rho) * pitch;
+#pragma unroll
+      for (uint32_t x = 0; x < 2; ++x) {
+        if (!mbar_wait_bounded(&tfull[x], h & 1, abort_flag)) {
+          fail();
+          return;
+        }
+        const uint32_t b0 = x * kHalfBlocks, b1 = min(nb, b0 + kHalfBlocks);
+        if constexpr (kQ8W) {
+          const float *dw = dwt + static_cast<size_t>(rho) * pitch;
 #pragma unroll 8
-        for (uint32_t ib = 0; ib < nb; ++ib)
-          acc = __fmaf_rn(tr[ib * kRowsCols], __fmul_rn(dw[ib], xd[ib * kRowsCols + col]), acc);
-      } else {
+          for (uint32_t ib = b0; ib < b1; ++ib)
+            acc = __fmaf_rn(tr[ib * kRowsCols], __fmul_rn(dw[ib], xd[ib * kRowsCols + col]), acc);
+        } else {
 #pragma unroll 8
-        for (uint32_t ib = 0; ib < nb; ++ib)
-          acc = __fmaf_rn(tr[ib * kRowsCols], xd[ib * kRowsCols + col], acc);
+          for (uint32_t ib = b0; ib < b1; ++ib)
+            acc = __fmaf_rn(tr[ib * kRowsCols], xd[ib * kRowsCols + col], acc);
+        }
+        // this lane has read its part of the half
+        __syncwarp();
+        if (lane == 0)
+          mbar_arrive(&tempty[x]);
       }
-      // this lane has read its part of the table
-      __syncwarp();
-      if (lane == 0)
-        mbar_arrive(tempty);
       const uint32_t row = (u0 + h) * kMmaRows + row_in_unit;
       if (row < a.nr && col < a.nc)
         a.s[static_cast<size_t>(row) * a.bs + col] = acc;
@@ -231,9 +240,9 @@ __global__ void __launch_bounds__(kStrictMmaThreads, 1) gemv_mma_strict_kernel(c
   asm volatile("bar.sync 1, %0;" ::"r"(kMmaWarps * 32) : "memory");
 
   for (uint32_t h = 0; h < nunits; ++h) {
-    // the unit's rows have landed, and the folding warps have read the previous unit's terms
+    // the unit's rows have landed, and the folding warps have read this half of the previous unit's terms
     if (!mbar_wait_bounded(&full[h % ring], (h / ring) & 1, abort_flag) ||
-        (h >= 1 && !mbar_wait_bounded(tempty, (h - 1) & 1, abort_flag))) {
+        (h >= 1 && !mbar_wait_bounded(&tempty[warp / (kMmaWarps / 2)], (h - 1) & 1, abort_flag))) {
       fail();
       return;
     }
@@ -300,7 +309,7 @@ __global__ void __launch_bounds__(kStrictMmaThreads, 1) gemv_mma_strict_kernel(c
     __syncwarp();
     if (lane == 0) {
       mbar_arrive(&empty[h % ring]);
-      mbar_arrive(tfull);
+      mbar_arrive(&tfull[warp / (kMmaWarps / 2)]);
     }
   }
 }
