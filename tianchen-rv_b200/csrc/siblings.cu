@@ -31,7 +31,7 @@ __device__ __forceinline__ int sibling_sumi(const uint8_t *xb, const uint8_t *yb
     y[w] = load_u32_bytes(yb + F::kAq + 4 * w);
     y[4 + w] = load_u32_bytes(yb + F::kAq + 16 + 4 * w);
   }
-  return strict_sumi_words<kFormat>(q, qh, y);
+  return strict_sumi_words<kFormat>(q, qh, y, F::kBias != 0 ? strict_ysum(y) : 0);
 }
 
 template <int kFormat>

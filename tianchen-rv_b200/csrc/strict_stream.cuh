@@ -74,11 +74,22 @@ struct StrictFormat<5> {  // Q8_0 x Q8_0
   static constexpr StrictFold kFold = kFoldProduct;
 };
 
+// sum of the 32 activation quants of a block (what the weight codes' offset is multiplied with)
+__device__ __forceinline__ int strict_ysum(const uint32_t (&y)[8]) {
+  int ysum = 0;
+#pragma unroll
+  for (int w = 0; w < 8; ++w)
+    ysum = __dp4a(0x01010101, static_cast<int>(y[w]), ysum);
+  return ysum;
+}
+
 // int32 dot of one block.  Nibble formats: `q[0..3]` are the four nibble words (bytes 4w..4w+3 in
 // word w), `qh` the fifth bits (0 where the format has none); int8 weights: `q[0..7]` are the
-// weight words.  `y` are the eight activation words.
+// weight words.  `y` are the eight activation words, `ysum` their sum (used by the formats whose
+// codes carry an offset: sum((v - bias) * y) = sum(v * y) - bias * sum(y)).
 template <int kFormat>
-__device__ __forceinline__ int strict_sumi_words(const uint32_t (&q)[8], uint32_t qh, const uint32_t (&y)[8]) {
+__device__ __forceinline__ int strict_sumi_words(const uint32_t (&q)[8], uint32_t qh, const uint32_t (&y)[8],
+                                                 int ysum) {
   using F = StrictFormat<kFormat>;
   int sumi = 0;
   if constexpr (!F::kNibbles) {
@@ -87,7 +98,6 @@ __device__ __forceinline__ int strict_sumi_words(const uint32_t (&q)[8], uint32_
       sumi = __dp4a(static_cast<int>(q[w]), static_cast<int>(y[w]), sumi);
     return sumi;
   } else {
-    int ysum = 0;
 #pragma unroll
     for (int w = 0; w < 4; ++w) {
       uint32_t lo = q[w] & 0x0f0f0f0fu, hi = (q[w] >> 4) & 0x0f0f0f0fu;
@@ -99,16 +109,11 @@ __device__ __forceinline__ int strict_sumi_words(const uint32_t (&q)[8], uint32_
         lo |= (bl * 0x02040810u) & 0x10101010u;
         hi |= (bh * 0x02040810u) & 0x10101010u;
       }
-      const uint32_t ylo = y[w], yhi = y[4 + w];
-      sumi = __dp4a(static_cast<int>(lo), static_cast<int>(ylo), sumi);  // codes 0..31 as signed bytes
-      sumi = __dp4a(static_cast<int>(hi), static_cast<int>(yhi), sumi);
-      if constexpr (F::kBias != 0) {
-        ysum = __dp4a(0x01010101, static_cast<int>(ylo), ysum);
-        ysum = __dp4a(0x01010101, static_cast<int>(yhi), ysum);
-      }
+      sumi = __dp4a(static_cast<int>(lo), static_cast<int>(y[w]), sumi);  // codes 0..31 as signed bytes
+      sumi = __dp4a(static_cast<int>(hi), static_cast<int>(y[4 + w]), sumi);
     }
     if constexpr (F::kBias != 0)
-      sumi -= F::kBias * ysum;  // sum((v - bias) * y) = sum(v * y) - bias * sum(y)
+      sumi -= F::kBias * ysum;
     return sumi;
   }
 }
@@ -282,10 +287,18 @@ __global__ void __launch_bounds__(kStrictThreads, 1) strict_stream_kernel(const 
     };
     const uint32_t at = pos(ib);
     xd[col * nb + at] = half_bits_to_float(static_cast<unsigned short>(half_at(0)));
-    xs[col * nb + at] = F::kFold == kFoldMin ? half_bits_to_float(static_cast<unsigned short>(half_at(2))) : 0.0f;
+    uint32_t yw[8];
 #pragma unroll
-    for (int w = 0; w < 8; ++w)
-      xq[(static_cast<size_t>(col) * 8 + w) * nb + at] = half_at(F::kAq + 4 * w) | (half_at(F::kAq + 4 * w + 2) << 16);
+    for (int w = 0; w < 8; ++w) {
+      yw[w] = half_at(F::kAq + 4 * w) | (half_at(F::kAq + 4 * w + 2) << 16);
+      xq[(static_cast<size_t>(col) * 8 + w) * nb + at] = yw[w];
+    }
+    // the third plane: Q8_1's s = d * sum(q) for the formats with a minimum, the plain integer
+    // sum(q) (as bits) for the formats whose weight codes carry an offset
+    if constexpr (F::kFold == kFoldMin)
+      xs[col * nb + at] = half_bits_to_float(static_cast<unsigned short>(half_at(2)));
+    else
+      xs[col * nb + at] = __int_as_float(strict_ysum(yw));
   }
   asm volatile("bar.sync 1, %0;" ::"r"(kStrictWorkers) : "memory");  // the workers only
 
@@ -321,7 +334,7 @@ __global__ void __launch_bounds__(kStrictThreads, 1) strict_stream_kernel(const 
       for (uint32_t col = 0; col < nc; ++col) {
         uint32_t y[8];
         float dy;
-        [[maybe_unused]] float sy;
+        float sy;
         if (fixed) {
 #pragma unroll
           for (int w = 0; w < 8; ++w)
@@ -333,7 +346,7 @@ __global__ void __launch_bounds__(kStrictThreads, 1) strict_stream_kernel(const 
             y[w] = xq[(static_cast<size_t>(col) * 8 + w) * nb + at];
           dy = xd[col * nb + at], sy = xs[col * nb + at];
         }
-        const float fs = __int2float_rn(strict_sumi_words<kFormat>(q, qh, y));
+        const float fs = __int2float_rn(strict_sumi_words<kFormat>(q, qh, y, __float_as_int(sy)));
         float *t = ta + (static_cast<size_t>(col) * rps + r) * (nb + 1) + at;
         if constexpr (F::kFold == kFoldMin) {
           *t = __fmaf_rn(__fmul_rn(dw, dy), fs, __fmul_rn(mw, sy));
