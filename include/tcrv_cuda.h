@@ -44,7 +44,7 @@ typedef enum {
  * scalar kernel with the fused fold).  Up to 8 columns against at least 64 rows whose base and
  * stride are multiples of 16 bytes (block count a multiple of 8) run on a streaming kernel that
  * keeps that order (many threads compute the per-block terms, a few fold them block after
- * block; 4..8 columns on rows of up to 4096 elements use the tensor cores for the terms): about
+ * block; 3..8 columns on rows of up to 4096 elements use the tensor cores for the terms): about
  * two thirds of the bandwidth of the default orders; anything else on a general warp-per-output
  * kernel */
 #define TCRV_CUDA_FLAG_STRICT_ORDER 1u

@@ -227,7 +227,7 @@ def test_tensor_core_gemv_reports_and_follows_its_order(cuda, pkg, O, q8w, nr, k
                                      (500, 4096, 3), (257, 11008, 8), (70, 4096, 8)])
 def test_strict_order_streaming_kernels_are_bit_exact(cuda, pkg, O, q8w, nr, k, nc):
     # At least 64 aligned rows take the strict streaming kernels (term table + sequential fold): the
-    # tensor-core form for 4..8 columns on rows of up to 4096 elements, the dp4a form otherwise.
+    # tensor-core form for 3..8 columns on rows of up to 4096 elements, the dp4a form otherwise.
     # Every output must have the bits of the sequential fold; flags bit 13 (dp4a form) gives the same.
     w, x = make(O, nr, k, nc, q8w, 2300 + nr + nc)
     wd, xd = dev(cuda, w), dev(cuda, x)

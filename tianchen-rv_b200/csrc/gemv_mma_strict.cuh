@@ -1,4 +1,4 @@
-// Decode GEMV for 4..8 activation columns in the reference's STRICT ascending block order, on
+// Decode GEMV for 3..8 activation columns in the reference's STRICT ascending block order, on
 // the tensor cores (rows of at most 128 blocks).
 //
 // The integer work is that of gemv_mma_rows.cuh: whole rows by bulk copies from a producer warp,
