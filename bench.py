@@ -474,8 +474,9 @@ def measure_e2e(pkg, torch, layers, steps, dist):
     import ctypes
 
     L = pkg.lib()
-    # the entry's default is the reference's strict block order (a verification-grade path); a
-    # decoder opts in to the streaming kernels' own summation orders, as the device-timed arm does
+    # the entry's default is the reference's strict block order (timed below as `reference_order`); a
+    # decoder that accepts rel 1e-5 opts in to the streaming kernels' own summation orders, as the
+    # device-timed arm does
     previous_order = L.tcrv_cuda_host_set_fold_order(1)
     host = []
     for l in layers:
