@@ -72,6 +72,100 @@ __device__ __forceinline__ unsigned short lds_u16(uint32_t addr) {
   return v;
 }
 
+// Activation fragments of one MMA warp for its K chunk (blocks 8 * warp .. 8 * warp + 7): for
+// thread (g = lane / 4, t = lane % 4) the two quant words of column g (`b0`, `b1`: the MMA's B
+// operand), the scale of column g (`dcol`) and -8 * sum(q) of columns 2t and 2t+1 (`sx`: the
+// MMA's C operand for Q4_0, summed over the quad that holds column g and fetched from the quads
+// of columns 2t, 2t+1).  Columns beyond a.nc are zero.  With 16-byte aligned columns the warp's
+// share of them (272 contiguous bytes of each) is first copied to `stage` (2176 bytes of shared
+// memory, this warp's own) in 16-byte pieces, all requested at once: picking the 2-byte aligned
+// words out of global memory directly took 48 small loads per thread in several dependent
+// rounds (3 to 4 us per launch).
+struct RowsXFragments {
+  uint32_t b0[kMmaChunkBlocks], b1[kMmaChunkBlocks];
+  float dcol[kMmaChunkBlocks];
+  int2 sx[kMmaChunkBlocks];
+};
+
+__device__ __forceinline__ void rows_load_x_fragments(const GemvRowsArgs &a, uint32_t warp, int lane, uint8_t *stage,
+                                                      RowsXFragments &x) {
+  const int g = lane >> 2, t = lane & 3;
+  const bool col_ok = static_cast<uint32_t>(g) < a.nc;
+  if (a.x_aligned) {
+    constexpr int kPieces = kRowsStageColBytes / 16;  // 17 per column
+    uint4 piece[(kRowsCols * kPieces + 31) / 32];
+#pragma unroll
+    for (int r = 0; r < (kRowsCols * kPieces + 31) / 32; ++r) {
+      const uint32_t idx = r * 32 + lane, col = idx / kPieces, k = idx - col * kPieces;
+      piece[r] = make_uint4(0, 0, 0, 0);
+      if (col < a.nc)
+        piece[r] = *reinterpret_cast<const uint4 *>(a.vy + col * a.by + static_cast<size_t>(warp) * kRowsStageColBytes +
+                                                    k * 16);
+    }
+#pragma unroll
+    for (int r = 0; r < (kRowsCols * kPieces + 31) / 32; ++r) {
+      const uint32_t idx = r * 32 + lane;
+      if (idx < kRowsCols * kPieces)
+        reinterpret_cast<uint4 *>(stage)[idx] = piece[r];
+    }
+    __syncwarp();
+    const uint32_t mine = smem_addr(stage) + g * kRowsStageColBytes;
+#pragma unroll
+    for (int bi = 0; bi < kMmaChunkBlocks; ++bi) {
+      const uint32_t blk = mine + bi * kQ8Block + 2 + 4 * t;
+      x.b0[bi] = static_cast<uint32_t>(lds_u16(blk)) | (static_cast<uint32_t>(lds_u16(blk + 2)) << 16);
+      x.b1[bi] = static_cast<uint32_t>(lds_u16(blk + 16)) | (static_cast<uint32_t>(lds_u16(blk + 18)) << 16);
+      x.dcol[bi] = half_bits_to_float(lds_u16(mine + bi * kQ8Block));
+    }
+  } else {
+#pragma unroll
+    for (int bi = 0; bi < kMmaChunkBlocks; ++bi) {
+      const size_t off = static_cast<size_t>(warp * kMmaChunkBlocks + bi) * kQ8Block;
+      const unsigned short *h = reinterpret_cast<const unsigned short *>(a.vy + g * a.by + off);
+      x.b0[bi] = col_ok ? static_cast<uint32_t>(h[1 + 2 * t]) | (static_cast<uint32_t>(h[2 + 2 * t]) << 16) : 0u;
+      x.b1[bi] = col_ok ? static_cast<uint32_t>(h[9 + 2 * t]) | (static_cast<uint32_t>(h[10 + 2 * t]) << 16) : 0u;
+      x.dcol[bi] = col_ok ? half_bits_to_float(h[0]) : 0.0f;
+    }
+  }
+#pragma unroll
+  for (int bi = 0; bi < kMmaChunkBlocks; ++bi) {
+    int sum = __dp4a(static_cast<int>(x.b0[bi]), 0x01010101, __dp4a(static_cast<int>(x.b1[bi]), 0x01010101, 0));
+    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+    x.sx[bi].x = -8 * __shfl_sync(0xffffffffu, sum, 8 * t);
+    x.sx[bi].y = -8 * __shfl_sync(0xffffffffu, sum, 8 * t + 4);
+  }
+}
+
+// The MMA's A operand for block `bi` of a chunk: rows at shared-window addresses `row_lo` and
+// `row_hi` (the chunk's first byte in each), thread column t; also the two rows' block scales.
+// Bytes 2.. of a block are 4-byte aligned for odd bi and off by two for even bi (bi is a
+// constant after unrolling).  Q4_0 nibbles come out unsigned.
+template <bool kQ8W>
+__device__ __forceinline__ void rows_load_a_fragment(uint32_t row_lo, uint32_t row_hi, int bi, int t,
+                                                     uint32_t (&afrag)[4], float &dw_lo, float &dw_hi) {
+  constexpr int WB = WeightFormat<kQ8W>::kBlockBytes;
+  auto load_row = [&](uint32_t row, uint32_t &k_lo, uint32_t &k_hi, float &dw) {
+    const uint32_t blk = row + bi * WB;
+    dw = half_bits_to_float(lds_u16(blk));
+    auto word_at = [&](int byte_off) -> uint32_t {  // the 4 bytes at blk + 2 + byte_off
+      if ((bi & 1) != 0)
+        return lds_u32(blk + 2 + byte_off);
+      return __funnelshift_r(lds_u32(blk + byte_off), lds_u32(blk + byte_off + 4), 16);
+    };
+    if constexpr (kQ8W) {
+      k_lo = word_at(4 * t);
+      k_hi = word_at(16 + 4 * t);
+    } else {
+      const uint32_t qw = word_at(4 * t);
+      k_lo = qw & 0x0f0f0f0fu;
+      k_hi = (qw >> 4) & 0x0f0f0f0fu;
+    }
+  };
+  load_row(row_lo, afrag[0], afrag[2], dw_lo);
+  load_row(row_hi, afrag[1], afrag[3], dw_hi);
+}
+
 template <bool kQ8W, int kGroups>
 __global__ void __launch_bounds__(kRowsThreads, 1) gemv_mma_rows_kernel(const GemvRowsArgs a) {
   using F = WeightFormat<kQ8W>;
@@ -162,71 +256,16 @@ __global__ void __launch_bounds__(kRowsThreads, 1) gemv_mma_rows_kernel(const Ge
   // ---- consumers
   if (a.static_weights)
     asm volatile("griddepcontrol.wait;" ::: "memory");
-  // Activation fragments: this thread's two quant words of column g, the scales of columns 2t
-  // and 2t+1, and -8 * sum(q) of those columns (summed over the quad that holds column g and
-  // fetched from the quads of columns 2t, 2t+1).  The warp's share of the columns (272
-  // contiguous bytes of each) is first copied to shared memory in 16-byte pieces, all requested
-  // at once: picking the 2-byte aligned words out of global memory directly took 48 small loads
-  // per thread in several dependent rounds (3 to 4 us per launch).
-  uint32_t xb0[kMmaChunkBlocks], xb1[kMmaChunkBlocks];
+  // Activation fragments (see rows_load_x_fragments); the fold wants the scales of columns 2t and
+  // 2t+1 as a pair: they sit in the quads of those columns.
+  RowsXFragments xf;
   uint64_t xdx[kMmaChunkBlocks];
-  int2 xsx[kMmaChunkBlocks];
   const bool active = warp < nchunks;
   if (active) {
-    const bool col_ok = static_cast<uint32_t>(g) < a.nc;
-    const bool even_ok = static_cast<uint32_t>(2 * t) < a.nc, odd_ok = static_cast<uint32_t>(2 * t + 1) < a.nc;
-    if (a.x_aligned) {
-      uint8_t *stage = reinterpret_cast<uint8_t *>(partial) + warp * kRowsStageWarpBytes;
-      constexpr int kPieces = kRowsStageColBytes / 16;  // 17 per column
-      uint4 piece[(kRowsCols * kPieces + 31) / 32];
+    rows_load_x_fragments(a, warp, lane, reinterpret_cast<uint8_t *>(partial) + warp * kRowsStageWarpBytes, xf);
 #pragma unroll
-      for (int r = 0; r < (kRowsCols * kPieces + 31) / 32; ++r) {
-        const uint32_t idx = r * 32 + lane, col = idx / kPieces, k = idx - col * kPieces;
-        piece[r] = make_uint4(0, 0, 0, 0);
-        if (col < a.nc)
-          piece[r] = *reinterpret_cast<const uint4 *>(a.vy + col * a.by +
-                                                      static_cast<size_t>(warp) * kRowsStageColBytes + k * 16);
-      }
-#pragma unroll
-      for (int r = 0; r < (kRowsCols * kPieces + 31) / 32; ++r) {
-        const uint32_t idx = r * 32 + lane;
-        if (idx < kRowsCols * kPieces)
-          reinterpret_cast<uint4 *>(stage)[idx] = piece[r];
-      }
-      __syncwarp();
-      const uint32_t mine = smem_addr(stage) + g * kRowsStageColBytes;
-      const uint32_t even = smem_addr(stage) + (2 * t) * kRowsStageColBytes, odd = even + kRowsStageColBytes;
-#pragma unroll
-      for (int bi = 0; bi < kMmaChunkBlocks; ++bi) {
-        const uint32_t blk = mine + bi * kQ8Block + 2 + 4 * t;
-        xb0[bi] = static_cast<uint32_t>(lds_u16(blk)) | (static_cast<uint32_t>(lds_u16(blk + 2)) << 16);
-        xb1[bi] = static_cast<uint32_t>(lds_u16(blk + 16)) | (static_cast<uint32_t>(lds_u16(blk + 18)) << 16);
-        xdx[bi] = mma_pack2(half_bits_to_float(lds_u16(even + bi * kQ8Block)),
-                            half_bits_to_float(lds_u16(odd + bi * kQ8Block)));
-      }
-    } else {
-#pragma unroll
-      for (int bi = 0; bi < kMmaChunkBlocks; ++bi) {
-        const size_t off = static_cast<size_t>(warp * kMmaChunkBlocks + bi) * kQ8Block;
-        const unsigned short *h = reinterpret_cast<const unsigned short *>(a.vy + g * a.by + off);
-        xb0[bi] = col_ok ? static_cast<uint32_t>(h[1 + 2 * t]) | (static_cast<uint32_t>(h[2 + 2 * t]) << 16) : 0u;
-        xb1[bi] = col_ok ? static_cast<uint32_t>(h[9 + 2 * t]) | (static_cast<uint32_t>(h[10 + 2 * t]) << 16) : 0u;
-        const float d_even =
-            even_ok ? half_bits_to_float(*reinterpret_cast<const unsigned short *>(a.vy + (2 * t) * a.by + off)) : 0.0f;
-        const float d_odd =
-            odd_ok ? half_bits_to_float(*reinterpret_cast<const unsigned short *>(a.vy + (2 * t + 1) * a.by + off))
-                   : 0.0f;
-        xdx[bi] = mma_pack2(d_even, d_odd);
-      }
-    }
-#pragma unroll
-    for (int bi = 0; bi < kMmaChunkBlocks; ++bi) {
-      int sum = __dp4a(static_cast<int>(xb0[bi]), 0x01010101, __dp4a(static_cast<int>(xb1[bi]), 0x01010101, 0));
-      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-      xsx[bi].x = -8 * __shfl_sync(0xffffffffu, sum, 8 * t);
-      xsx[bi].y = -8 * __shfl_sync(0xffffffffu, sum, 8 * t + 4);
-    }
+    for (int bi = 0; bi < kMmaChunkBlocks; ++bi)
+      xdx[bi] = mma_pack2(__shfl_sync(0xffffffffu, xf.dcol[bi], 8 * t), __shfl_sync(0xffffffffu, xf.dcol[bi], 8 * t + 4));
   }
   // the staging room becomes the partial ring: no warp may write a partial before every warp
   // has read its fragments (named barrier of the 16 consumer warps; the producer is elsewhere)
@@ -258,34 +297,15 @@ __global__ void __launch_bounds__(kRowsThreads, 1) gemv_mma_rows_kernel(const Ge
           // shared-window addresses and explicit ld.shared: the loads must not become generic ones
           const uint32_t row_lo = units_addr + ((j * G + q) % ring) * unit_bytes + g * a.pair_pitch + warp * CB;
           const uint32_t row_hi = row_lo + a.row_bytes;
-          // bytes 2.. of a block are 4-byte aligned for odd bi and off by two for even bi
           uint32_t afrag[4];
           float dw_lo, dw_hi;
-          auto load_rows = [&](uint32_t row, uint32_t &k_lo, uint32_t &k_hi, float &dw) {
-            const uint32_t blk = row + bi * WB;
-            dw = half_bits_to_float(lds_u16(blk));
-            auto word_at = [&](int byte_off) -> uint32_t {  // the 4 bytes at blk + 2 + byte_off
-              if ((bi & 1) != 0)
-                return lds_u32(blk + 2 + byte_off);
-              return __funnelshift_r(lds_u32(blk + byte_off), lds_u32(blk + byte_off + 4), 16);
-            };
-            if constexpr (kQ8W) {
-              k_lo = word_at(4 * t);
-              k_hi = word_at(16 + 4 * t);
-            } else {
-              const uint32_t qw = word_at(4 * t);
-              k_lo = qw & 0x0f0f0f0fu;
-              k_hi = (qw >> 4) & 0x0f0f0f0fu;
-            }
-          };
-          load_rows(row_lo, afrag[0], afrag[2], dw_lo);
-          load_rows(row_hi, afrag[1], afrag[3], dw_hi);
+          rows_load_a_fragment<kQ8W>(row_lo, row_hi, bi, t, afrag, dw_lo, dw_hi);
           int c[4];
           // Q4_0: the nibbles enter unsigned; -8 * sum(x) of each column rides in as the MMA's C input
           if constexpr (kQ8W)
-            mma_m16n8k32_s8(c, afrag, xb0[bi], xb1[bi], 0, 0);
+            mma_m16n8k32_s8(c, afrag, xf.b0[bi], xf.b1[bi], 0, 0);
           else
-            mma_m16n8k32_s8(c, afrag, xb0[bi], xb1[bi], xsx[bi].x, xsx[bi].y);
+            mma_m16n8k32_s8(c, afrag, xf.b0[bi], xf.b1[bi], xf.sx[bi].x, xf.sx[bi].y);
           acc_lo[q] = mma_fold2<kQ8W>(acc_lo[q], c[0], c[1], dw_lo, xdx[bi]);
           acc_hi[q] = mma_fold2<kQ8W>(acc_hi[q], c[2], c[3], dw_hi, xdx[bi]);
         }

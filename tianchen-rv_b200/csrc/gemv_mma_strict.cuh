@@ -179,60 +179,16 @@ __global__ void __launch_bounds__(kStrictMmaThreads, 1) gemv_mma_strict_kernel(c
   // ---- MMA warps
   if (a.static_weights)
     asm volatile("griddepcontrol.wait;" ::: "memory");
-  // Activation fragments (see gemv_mma_rows.cuh): two quant words of column g, -8 * sum(q) of
-  // columns 2t and 2t+1; the column scales go to shared memory for the folding warps.
-  uint32_t xb0[kMmaChunkBlocks], xb1[kMmaChunkBlocks];
-  int2 xsx[kMmaChunkBlocks];
+  // Activation fragments (see rows_load_x_fragments); the column scales go to shared memory for
+  // the folding warps.
+  RowsXFragments xf;
   const bool active = warp < nchunks;
   if (active) {
-    const bool col_ok = static_cast<uint32_t>(g) < a.nc;
-    float dcol[kMmaChunkBlocks];  // scale of column g
-    if (a.x_aligned) {
-      uint8_t *stage = reinterpret_cast<uint8_t *>(table) + warp * kRowsStageWarpBytes;
-      constexpr int kPieces = kRowsStageColBytes / 16;  // 17 per column
-      uint4 piece[(kRowsCols * kPieces + 31) / 32];
+    rows_load_x_fragments(a, warp, lane, reinterpret_cast<uint8_t *>(table) + warp * kRowsStageWarpBytes, xf);
+    if (t == 0) {  // one lane per column
 #pragma unroll
-      for (int r = 0; r < (kRowsCols * kPieces + 31) / 32; ++r) {
-        const uint32_t idx = r * 32 + lane, c = idx / kPieces, k = idx - c * kPieces;
-        piece[r] = make_uint4(0, 0, 0, 0);
-        if (c < a.nc)
-          piece[r] = *reinterpret_cast<const uint4 *>(a.vy + c * a.by + static_cast<size_t>(warp) * kRowsStageColBytes +
-                                                      k * 16);
-      }
-#pragma unroll
-      for (int r = 0; r < (kRowsCols * kPieces + 31) / 32; ++r) {
-        const uint32_t idx = r * 32 + lane;
-        if (idx < kRowsCols * kPieces)
-          reinterpret_cast<uint4 *>(stage)[idx] = piece[r];
-      }
-      __syncwarp();
-      const uint32_t mine = smem_addr(stage) + g * kRowsStageColBytes;
-#pragma unroll
-      for (int bi = 0; bi < kMmaChunkBlocks; ++bi) {
-        const uint32_t blk = mine + bi * kQ8Block + 2 + 4 * t;
-        xb0[bi] = static_cast<uint32_t>(lds_u16(blk)) | (static_cast<uint32_t>(lds_u16(blk + 2)) << 16);
-        xb1[bi] = static_cast<uint32_t>(lds_u16(blk + 16)) | (static_cast<uint32_t>(lds_u16(blk + 18)) << 16);
-        dcol[bi] = half_bits_to_float(lds_u16(mine + bi * kQ8Block));
-      }
-    } else {
-#pragma unroll
-      for (int bi = 0; bi < kMmaChunkBlocks; ++bi) {
-        const size_t off = static_cast<size_t>(warp * kMmaChunkBlocks + bi) * kQ8Block;
-        const unsigned short *h = reinterpret_cast<const unsigned short *>(a.vy + g * a.by + off);
-        xb0[bi] = col_ok ? static_cast<uint32_t>(h[1 + 2 * t]) | (static_cast<uint32_t>(h[2 + 2 * t]) << 16) : 0u;
-        xb1[bi] = col_ok ? static_cast<uint32_t>(h[9 + 2 * t]) | (static_cast<uint32_t>(h[10 + 2 * t]) << 16) : 0u;
-        dcol[bi] = col_ok ? half_bits_to_float(h[0]) : 0.0f;
-      }
-    }
-#pragma unroll
-    for (int bi = 0; bi < kMmaChunkBlocks; ++bi) {
-      int sum = __dp4a(static_cast<int>(xb0[bi]), 0x01010101, __dp4a(static_cast<int>(xb1[bi]), 0x01010101, 0));
-      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-      xsx[bi].x = -8 * __shfl_sync(0xffffffffu, sum, 8 * t);
-      xsx[bi].y = -8 * __shfl_sync(0xffffffffu, sum, 8 * t + 4);
-      if (t == 0)  // one lane per column
-        xd[(warp * kMmaChunkBlocks + bi) * kRowsCols + g] = dcol[bi];
+      for (int bi = 0; bi < kMmaChunkBlocks; ++bi)
+        xd[(warp * kMmaChunkBlocks + bi) * kRowsCols + g] = xf.dcol[bi];
     }
   }
   // the staging room becomes the term table: no warp may write a term before every warp has
@@ -253,34 +209,15 @@ __global__ void __launch_bounds__(kStrictMmaThreads, 1) gemv_mma_strict_kernel(c
       float *out_hi = out_lo + static_cast<size_t>(8) * pitch * kRowsCols;
 #pragma unroll
       for (int bi = 0; bi < kMmaChunkBlocks; ++bi) {
-        // bytes 2.. of a block are 4-byte aligned for odd bi and off by two for even bi
         uint32_t afrag[4];
         float dw_lo, dw_hi;
-        auto load_rows = [&](uint32_t row, uint32_t &k_lo, uint32_t &k_hi, float &dw) {
-          const uint32_t blk = row + bi * WB;
-          dw = half_bits_to_float(lds_u16(blk));
-          auto word_at = [&](int byte_off) -> uint32_t {  // the 4 bytes at blk + 2 + byte_off
-            if ((bi & 1) != 0)
-              return lds_u32(blk + 2 + byte_off);
-            return __funnelshift_r(lds_u32(blk + byte_off), lds_u32(blk + byte_off + 4), 16);
-          };
-          if constexpr (kQ8W) {
-            k_lo = word_at(4 * t);
-            k_hi = word_at(16 + 4 * t);
-          } else {
-            const uint32_t qw = word_at(4 * t);
-            k_lo = qw & 0x0f0f0f0fu;
-            k_hi = (qw >> 4) & 0x0f0f0f0fu;
-          }
-        };
-        load_rows(row_lo, afrag[0], afrag[2], dw_lo);
-        load_rows(row_hi, afrag[1], afrag[3], dw_hi);
+        rows_load_a_fragment<kQ8W>(row_lo, row_hi, bi, t, afrag, dw_lo, dw_hi);
         int c[4];
         // Q4_0: the nibbles enter unsigned; -8 * sum(x) of each column rides in as the MMA's C input
         if constexpr (kQ8W)
-          mma_m16n8k32_s8(c, afrag, xb0[bi], xb1[bi], 0, 0);
+          mma_m16n8k32_s8(c, afrag, xf.b0[bi], xf.b1[bi], 0, 0);
         else
-          mma_m16n8k32_s8(c, afrag, xb0[bi], xb1[bi], xsx[bi].x, xsx[bi].y);
+          mma_m16n8k32_s8(c, afrag, xf.b0[bi], xf.b1[bi], xf.sx[bi].x, xf.sx[bi].y);
         // (float)sumi without a conversion instruction (see gemv_mma.cuh), then the order-free
         // half of the fold: Q4_0 scales by d_w (one rounding), Q8_0 keeps the exact integer
         const uint64_t b_lo = mma_pack2(__uint_as_float(static_cast<uint32_t>(c[0]) + kMmaMagicBits),
