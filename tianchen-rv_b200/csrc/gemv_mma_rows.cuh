@@ -72,6 +72,52 @@ __device__ __forceinline__ unsigned short lds_u16(uint32_t addr) {
   return v;
 }
 
+// The producer warp of the whole-row kernels: lane p brings row pair p of every 16-row unit
+// (units first_unit .. first_unit + nunits - 1 of the matrix) into ring position h % ring as soon
+// as all 16 consumer warps have handed the position back.  On a failed wait it raises the
+// device error, tells the other roles and waits for the copies it has already requested.
+__device__ __forceinline__ void rows_producer(const GemvRowsArgs &a, uint8_t *units, uint32_t unit_bytes, uint32_t ring,
+                                              uint32_t first_unit, uint32_t nunits, uint64_t *full, uint64_t *empty,
+                                              volatile uint32_t *abort_flag, int lane) {
+  uint32_t issued = 0;
+  bool ok = true;
+  for (uint32_t h = 0; h < nunits && ok; ++h) {
+    const uint32_t pos = h % ring;
+    if (h >= ring)  // the position's previous unit must have been read by every consumer warp
+      ok = mbar_wait_bounded(&empty[pos], ((h / ring) - 1) & 1, abort_flag);
+    if (!ok)
+      break;
+    if (lane < kRowsPairs) {
+      const uint32_t row = (first_unit + h) * kMmaRows + 2 * lane;
+      const uint32_t rows = row < a.nr ? min(2u, a.nr - row) : 0u;  // a ragged last unit has fewer
+      uint8_t *dst = units + static_cast<size_t>(pos) * unit_bytes + static_cast<size_t>(lane) * a.pair_pitch;
+      const uint8_t *src = a.vx + static_cast<size_t>(row) * a.bx;
+      if (rows == 0) {
+        mbar_arrive(&full[pos]);
+      } else {
+        // reads of the position by the consumers happened before their arrivals on `empty`
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        mbar_arrive_expect_tx(&full[pos], rows * a.row_bytes);
+        if (a.contiguous || rows == 1) {
+          bulk_copy_g2s(dst, src, rows * a.row_bytes, &full[pos]);
+        } else {
+          bulk_copy_g2s(dst, src, a.row_bytes, &full[pos]);
+          bulk_copy_g2s(dst + a.row_bytes, src + a.bx, a.row_bytes, &full[pos]);
+        }
+      }
+    }
+    issued = h + 1;
+  }
+  if (!ok && lane == 0) {
+    if (*abort_flag == 0)
+      raise_device_error(kDevErrBarrierTimeout);
+    *abort_flag = 1;
+    // copies already requested must land before the CTA's shared memory goes away
+    for (uint32_t h = issued > ring ? issued - ring : 0; h < issued; ++h)
+      (void)mbar_wait_bounded(&full[h % ring], (h / ring) & 1);
+  }
+}
+
 // Activation fragments of one MMA warp for its K chunk (blocks 8 * warp .. 8 * warp + 7): for
 // thread (g = lane / 4, t = lane % 4) the two quant words of column g (`b0`, `b1`: the MMA's B
 // operand), the scale of column g (`dcol`) and -8 * sum(q) of columns 2t and 2t+1 (`sx`: the
@@ -212,44 +258,7 @@ __global__ void __launch_bounds__(kRowsThreads, 1) gemv_mma_rows_kernel(const Ge
   __syncthreads();
 
   if (warp == kMmaWarps) {
-    // ---- producer: lane p brings pair p of every unit
-    uint32_t issued = 0;
-    bool ok = true;
-    for (uint32_t h = 0; h < nunits && ok; ++h) {
-      const uint32_t pos = h % ring;
-      if (h >= ring)  // the position's previous unit must have been folded by every warp
-        ok = mbar_wait_bounded(&empty[pos], ((h / ring) - 1) & 1, abort_flag);
-      if (!ok)
-        break;
-      if (lane < kRowsPairs) {
-        const uint32_t row = ((s0 + h / G) * G + h % G) * kMmaRows + 2 * lane;
-        const uint32_t rows = row < a.nr ? min(2u, a.nr - row) : 0u;  // a ragged last unit has fewer
-        uint8_t *dst = units + static_cast<size_t>(pos) * unit_bytes + static_cast<size_t>(lane) * a.pair_pitch;
-        const uint8_t *src = a.vx + static_cast<size_t>(row) * a.bx;
-        if (rows == 0) {
-          mbar_arrive(&full[pos]);
-        } else {
-          // reads of the position by the consumers happened before their arrivals on `empty`
-          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-          mbar_arrive_expect_tx(&full[pos], rows * a.row_bytes);
-          if (a.contiguous || rows == 1) {
-            bulk_copy_g2s(dst, src, rows * a.row_bytes, &full[pos]);
-          } else {
-            bulk_copy_g2s(dst, src, a.row_bytes, &full[pos]);
-            bulk_copy_g2s(dst + a.row_bytes, src + a.bx, a.row_bytes, &full[pos]);
-          }
-        }
-      }
-      issued = h + 1;
-    }
-    if (!ok && lane == 0) {
-      if (*abort_flag == 0)
-        raise_device_error(kDevErrBarrierTimeout);
-      *abort_flag = 1;
-      // copies already requested must land before the CTA's shared memory goes away
-      for (uint32_t h = issued > ring ? issued - ring : 0; h < issued; ++h)
-        (void)mbar_wait_bounded(&full[h % ring], (h / ring) & 1);
-    }
+    rows_producer(a, units, unit_bytes, ring, s0 * G, nunits, full, empty, abort_flag, lane);
     return;
   }
 

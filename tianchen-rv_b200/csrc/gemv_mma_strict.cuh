@@ -98,44 +98,7 @@ __global__ void __launch_bounds__(kStrictMmaThreads, 1) gemv_mma_strict_kernel(c
   };
 
   if (warp == kMmaWarps) {
-    // ---- producer: lane p brings pair p of every unit
-    uint32_t issued = 0;
-    bool ok = true;
-    for (uint32_t h = 0; h < nunits && ok; ++h) {
-      const uint32_t pos = h % ring;
-      if (h >= ring)  // the position's previous unit must have been read by every MMA warp
-        ok = mbar_wait_bounded(&empty[pos], ((h / ring) - 1) & 1, abort_flag);
-      if (!ok)
-        break;
-      if (lane < kRowsPairs) {
-        const uint32_t row = (u0 + h) * kMmaRows + 2 * lane;
-        const uint32_t rows = row < a.nr ? min(2u, a.nr - row) : 0u;  // a ragged last unit has fewer
-        uint8_t *dst = units + static_cast<size_t>(pos) * unit_bytes + static_cast<size_t>(lane) * a.pair_pitch;
-        const uint8_t *src = a.vx + static_cast<size_t>(row) * a.bx;
-        if (rows == 0) {
-          mbar_arrive(&full[pos]);
-        } else {
-          // reads of the position by the MMA warps happened before their arrivals on `empty`
-          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-          mbar_arrive_expect_tx(&full[pos], rows * a.row_bytes);
-          if (a.contiguous || rows == 1) {
-            bulk_copy_g2s(dst, src, rows * a.row_bytes, &full[pos]);
-          } else {
-            bulk_copy_g2s(dst, src, a.row_bytes, &full[pos]);
-            bulk_copy_g2s(dst + a.row_bytes, src + a.bx, a.row_bytes, &full[pos]);
-          }
-        }
-      }
-      issued = h + 1;
-    }
-    if (!ok && lane == 0) {
-      if (*abort_flag == 0)
-        raise_device_error(kDevErrBarrierTimeout);
-      *abort_flag = 1;
-      // copies already requested must land before the CTA's shared memory goes away
-      for (uint32_t h = issued > ring ? issued - ring : 0; h < issued; ++h)
-        (void)mbar_wait_bounded(&full[h % ring], (h / ring) & 1);
-    }
+    rows_producer(a, units, unit_bytes, ring, u0, nunits, full, empty, abort_flag, lane);
     return;
   }
 
