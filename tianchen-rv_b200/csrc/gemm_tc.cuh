@@ -33,9 +33,10 @@
 //               of the columns of every accumulator tile
 //   warp 16     TMA producer (one lane)
 //   warp 17     TMEM allocation + MMA issue (one lane)
-// Pipelines: shared-memory stages of 4 blocks each (full/empty mbarriers) and four TMEM stages
-// of one accumulator tile each (full/empty mbarriers), so the tensor core runs up to four
-// blocks ahead of the fold.
+// Pipelines: shared-memory stages of 4 blocks each (full/empty mbarriers) and two TMEM stages of
+// two accumulator tiles each, i.e. two consecutive blocks per hand-over (full/empty mbarriers),
+// so the tensor core runs up to four blocks ahead of the fold.  The epilogue warps wait on the
+// accumulator barriers only: a stage's scale tiles have landed when its first accumulator has.
 //
 // Work items: 128 x 128 tiles dealt round-robin to the CTAs; when the last round would leave
 // more than half of the CTAs idle its tiles are cut into two 128 x 64 items (same row order,
