@@ -1,7 +1,9 @@
 // Decode GEMV for several (4..8) activation columns on the tensor cores (legacy warp-level MMA,
 // mma.sync.m16n8k32.s8: 16 weight rows x 32 K x 8 columns is exactly one ggml block of a
 // 16-row group against all columns).  With several columns the dp4a kernel is issue-bound
-// long before HBM is; here one MMA replaces 16 x 8 x 8 dp4a.
+// long before HBM is; here one MMA replaces 16 x 8 x 8 dp4a.  This is the tiled-TMA form, which
+// the launcher uses for rows of more than 4096 elements; shorter rows take the whole-row form
+// in gemv_mma_rows.cuh (same arithmetic, same order).
 //
 // One persistent CTA per SM owns a contiguous range of 32-row slots (two 16-row MMA groups,
 // folded as two independent chains).  All 16 warps of the CTA work on the SAME slot and
