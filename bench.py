@@ -656,6 +656,11 @@ def measure_other_kernels(pkg, torch):
         timed("repack_gemv_q8_0x16" if q8w else "repack_gemv_q4_0x16",
               lambda c, wx=wx, yr=yr, rows=rows, q8w=q8w: pkg.repack_gemv(wx[c], x1r, rows, q8_weights=q8w, out=yr),
               copies, rows * 128 * (34 if q8w else 18) + 128 * 34 + 4 * rows, f"{rows} x 4096, batch 1")
+        timed(("repack_gemv_q8_0x16" if q8w else "repack_gemv_q4_0x16") + "_strict_order",
+              lambda c, wx=wx, yr=yr, rows=rows, q8w=q8w: pkg.repack_gemv(wx[c], x1r, rows, q8_weights=q8w, out=yr,
+                                                                          flags=pkg.FLAG_STRICT_ORDER),
+              copies, rows * 128 * (34 if q8w else 18) + 128 * 34 + 4 * rows,
+              f"{rows} x 4096, batch 1, the reference's one chain per row")
         del wx
     wx = torch.randint(0, 256, (11008 // 16 * 128 * 288,), dtype=torch.uint8, device="cuda", generator=gen)
     xx = torch.randint(0, 256, (GEMM_TOKENS // 4 * 128 * 136,), dtype=torch.uint8, device="cuda", generator=gen)

@@ -73,6 +73,17 @@ def test_repack_gemv_work_split_does_not_change_the_result(cuda, pkg, O, q8w):
             flags = (depth << 8) | (coop << 12) | (window << 16)
             got = pkg.repack_gemv(wd, xd, nc, q8_weights=q8w, flags=flags).cpu().numpy()
             assert np.array_equal(bits(got), bits(want)), (coop, depth, window)
+    # the same for the reference's order: one chain per row whether a warp has the group to
+    # itself (it folds step by step) or shares it (the first warp folds the group's term table)
+    for nc2, k2 in ((256, 4096), (160, 1312), (4096, 4096)):
+        wx, x = make_case(O, nc2, k2, q8w, 901 + nc2)
+        want = O.repack_gemv(wx, x[0], nc2, q8_weights=q8w)
+        wd, xd = dev(cuda, wx), dev(cuda, x[0])
+        for coop in (0, 1, 2, 4, 8):
+            for depth, window in ((0, 0), (2, 1), (4, 3)):
+                flags = pkg.FLAG_STRICT_ORDER | (depth << 8) | (coop << 12) | (window << 16)
+                got = pkg.repack_gemv(wd, xd, nc2, q8_weights=q8w, flags=flags).cpu().numpy()
+                assert np.array_equal(bits(got), bits(want)), (nc2, k2, coop, depth, window)
     pkg.check_device_errors()
 
 

@@ -28,6 +28,15 @@
 // warps (a divisor of `parts`) share a group, each folding parts/coop consecutive ranges, and
 // a CTA of 16 warps handles 16/coop groups per round.  Range sums meet in shared memory and
 // the first warp of the group adds them.
+//
+// With TCRV_CUDA_FLAG_STRICT_ORDER the same kernel (kStrict) keeps the reference's order, one
+// chain per row over blocks 0, 1, 2, ...: the lanes write their terms, (float)sumi and
+// d_w * d_a, into a table of [8 blocks][16 rows] per step, and the lower half of a warp
+// (lane = row) folds the 8 blocks of the step in ascending order onto the row's chain.  A
+// warp that has a group to itself folds after every step; warps that share a group (few
+// groups per CTA) fill one table per step and the first of them folds the whole row once they
+// have met.  The fold is off the weight stream's critical path, so the strict order costs
+// 0..15 % over the regrouped one.
 #include <atomic>
 #include "async_copy.cuh"
 #include "launchers.h"
@@ -68,6 +77,7 @@ struct RepackGemvArgs {
   uint32_t coop;    // warps sharing a group, divides parts
   uint32_t depth;   // ring slots per warp
   uint32_t window;  // copies a warp keeps in flight, < depth
+  uint32_t terms_bytes;  // strict order with coop > 1: room for the term tables of a round's groups
 };
 
 __host__ __device__ inline uint32_t rp_x_bytes(uint32_t nb) { return (nb * 36u + 15u) & ~15u; }
@@ -88,7 +98,7 @@ __device__ __forceinline__ float small_int_to_float(int v) {
   return __fadd_rn(__int_as_float(v + 0x4B400000), -12582912.0f);
 }
 
-template <bool kQ8W>
+template <bool kQ8W, bool kStrict>
 __global__ void __launch_bounds__(kRpThreads, 1) repack_gemv_kernel(const RepackGemvArgs a) {
   using F = X16<kQ8W>;
   extern __shared__ __align__(128) uint8_t smem[];
@@ -98,7 +108,7 @@ __global__ void __launch_bounds__(kRpThreads, 1) repack_gemv_kernel(const Repack
   const uint32_t nb = a.nb;
   uint4 *xq = reinterpret_cast<uint4 *>(smem + kRpFixedBytes);             // [nb][2] activation quants
   float *xd = reinterpret_cast<float *>(smem + kRpFixedBytes + nb * 32u);  // [nb] activation scales
-  uint8_t *slots = smem + kRpFixedBytes + rp_x_bytes(nb);
+  uint8_t *slots = smem + kRpFixedBytes + rp_x_bytes(nb) + a.terms_bytes;
 
   const uint32_t warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -171,6 +181,27 @@ __global__ void __launch_bounds__(kRpThreads, 1) repack_gemv_kernel(const Repack
   __syncthreads();
 
   float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+  // kStrict: the terms of a step, [8 blocks][16 rows] as a plane of (float)sumi and a plane of
+  // d_w * d_a, and the single chain of row `lane` in the lower half of a warp.  A warp that has
+  // a group to itself folds every step as it goes (one table per warp); warps that share a
+  // group (parts = coop, each a contiguous span of steps) fill a table per step of the group,
+  // and the first of them folds all of it once the group's warps have met.
+  float *terms = coop == 1 ? partial + warp * 256
+                           : reinterpret_cast<float *>(smem + kRpFixedBytes + rp_x_bytes(nb)) + wgroup * steps * 256;
+  float chain = 0.0f;
+  auto fold_step = [&](const float *t, uint32_t first) {
+    float f[kRpStepBlocks], sc[kRpStepBlocks];
+#pragma unroll
+    for (int k = 0; k < kRpStepBlocks; ++k) {
+      f[k] = t[16 * k + lane];
+      sc[k] = t[128 + 16 * k + lane];
+    }
+#pragma unroll
+    for (int k = 0; k < kRpStepBlocks; ++k) {
+      if (first + k < nb)
+        chain = __fmaf_rn(f[k], sc[k], chain);
+    }
+  };
   uint32_t step = s_begin, round = 0, pos = 0, phase = 0;
   uint32_t range = wpart * rpw, range_end = (range + 1) * steps / parts;
   bool dead = false;  // a wait of this warp expired: walk on without data (warp-uniform)
@@ -223,51 +254,90 @@ __global__ void __launch_bounds__(kRpThreads, 1) repack_gemv_kernel(const Repack
         }
         const float dw[4] = {half_bits_to_float(sc0 & 0xffffu), half_bits_to_float(sc0 >> 16),
                              half_bits_to_float(sc1 & 0xffffu), half_bits_to_float(sc1 >> 16)};
+        if constexpr (kStrict) {
+          float f[4], sc[4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int si = kQ8W ? sumi[j] : (sumi[j] >> 4);  // exact: the total is a multiple of 16
-          acc[j] = __fmaf_rn(small_int_to_float(si), __fmul_rn(dw[j], da), acc[j]);
+          for (int j = 0; j < 4; ++j) {
+            f[j] = small_int_to_float(kQ8W ? sumi[j] : (sumi[j] >> 4));
+            sc[j] = __fmul_rn(dw[j], da);
+          }
+          float *t = terms + (coop == 1 ? 0u : step * 256u);
+          reinterpret_cast<float4 *>(t)[lane] = make_float4(f[0], f[1], f[2], f[3]);
+          reinterpret_cast<float4 *>(t + 128)[lane] = make_float4(sc[0], sc[1], sc[2], sc[3]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int si = kQ8W ? sumi[j] : (sumi[j] >> 4);  // exact: the total is a multiple of 16
+            acc[j] = __fmaf_rn(small_int_to_float(si), __fmul_rn(dw[j], da), acc[j]);
+          }
         }
       }
-      ++step;
-      if (step == range_end) {
-        // a range is folded: add its 8 chains and hand the 16 sums over
-#pragma unroll
-        for (int off = 16; off >= 4; off >>= 1) {
-#pragma unroll
-          for (int j = 0; j < 4; ++j)
-            acc[j] = __fadd_rn(acc[j], __shfl_xor_sync(0xffffffffu, acc[j], off));
-        }
-        float *slot = partial + (((round & 1u) * kRpWarps + wgroup) * kRpMaxParts + range) * 16;
-        if (b == 0) {
-#pragma unroll
-          for (int j = 0; j < 4; ++j)
-            slot[4 * rq + j] = acc[j];
-        }
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-          acc[j] = 0.0f;
-        ++range;
-        range_end = (range + 1) * steps / parts;
-      }
-      if (step == s_end) {
-        // this warp's share of the group is done: the group's warps meet, the first one adds
-        // the range sums in ascending order
-        if (coop > 1)
-          asm volatile("bar.sync %0, %1;" ::"r"(1u + wgroup), "r"(coop * 32u) : "memory");
-        else
+      if constexpr (kStrict) {
+        if (coop == 1) {
+          // the 8 blocks of the step, in ascending order, onto the one chain of each row
           __syncwarp();
-        if (wpart == 0 && lane < 16 && !dead) {
-          const float *sums = partial + ((round & 1u) * kRpWarps + wgroup) * kRpMaxParts * 16;
-          float tot = sums[lane];
-          for (uint32_t j = 1; j < parts; ++j)
-            tot = __fadd_rn(tot, sums[j * 16 + lane]);
-          a.s[static_cast<size_t>(g0 + round * gpr + wgroup) * 16 + lane] = tot;
+          if (lane < 16 && !dead)
+            fold_step(terms, step * kRpStepBlocks);
+          __syncwarp();
         }
-        step = s_begin;
-        range = wpart * rpw;
-        range_end = (range + 1) * steps / parts;
-        ++round;
+        ++step;
+        if (step == s_end) {
+          if (coop > 1) {
+            asm volatile("bar.sync %0, %1;" ::"r"(1u + wgroup), "r"(coop * 32u) : "memory");
+            if (wpart == 0 && lane < 16 && !dead) {
+              for (uint32_t st = 0; st < steps; ++st)
+                fold_step(terms + st * 256u, st * kRpStepBlocks);
+            }
+            if (nrounds > 1)  // the tables are filled again in the next round
+              asm volatile("bar.sync %0, %1;" ::"r"(1u + wgroup), "r"(coop * 32u) : "memory");
+          }
+          if (wpart == 0 && lane < 16 && !dead)
+            a.s[static_cast<size_t>(g0 + round * gpr + wgroup) * 16 + lane] = chain;
+          chain = 0.0f;
+          step = s_begin;
+          ++round;
+        }
+      } else {
+        ++step;
+        if (step == range_end) {
+          // a range is folded: add its 8 chains and hand the 16 sums over
+#pragma unroll
+          for (int off = 16; off >= 4; off >>= 1) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              acc[j] = __fadd_rn(acc[j], __shfl_xor_sync(0xffffffffu, acc[j], off));
+          }
+          float *slot = partial + (((round & 1u) * kRpWarps + wgroup) * kRpMaxParts + range) * 16;
+          if (b == 0) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              slot[4 * rq + j] = acc[j];
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            acc[j] = 0.0f;
+          ++range;
+          range_end = (range + 1) * steps / parts;
+        }
+        if (step == s_end) {
+          // this warp's share of the group is done: the group's warps meet, the first one adds
+          // the range sums in ascending order
+          if (coop > 1)
+            asm volatile("bar.sync %0, %1;" ::"r"(1u + wgroup), "r"(coop * 32u) : "memory");
+          else
+            __syncwarp();
+          if (wpart == 0 && lane < 16 && !dead) {
+            const float *sums = partial + ((round & 1u) * kRpWarps + wgroup) * kRpMaxParts * 16;
+            float tot = sums[lane];
+            for (uint32_t j = 1; j < parts; ++j)
+              tot = __fadd_rn(tot, sums[j * 16 + lane]);
+            a.s[static_cast<size_t>(g0 + round * gpr + wgroup) * 16 + lane] = tot;
+          }
+          step = s_begin;
+          range = wpart * rpw;
+          range_end = (range + 1) * steps / parts;
+          ++round;
+        }
       }
     }  // steps of the slot
     if (++pos == depth) {
@@ -346,13 +416,15 @@ __global__ void __launch_bounds__(256) repack_gemv_generic_kernel(const uint8_t 
   }
 }
 
-// The reference's own order (TCRV_CUDA_FLAG_STRICT_ORDER): every output row folds its blocks
-// one after the other, acc = fma((float)sumi, d_w * d_a, acc) for block 0, 1, 2, ... from 0.0f,
-// which is what the lane-wise vfmacc chain of the RVV kernel computes
+// The reference's own order (TCRV_CUDA_FLAG_STRICT_ORDER) without bulk copies or shared memory,
+// for weight pointers that are not 16-byte aligned and for rows too long for the staged
+// activation column: every output row folds its blocks one after the other,
+// acc = fma((float)sumi, d_w * d_a, acc) for block 0, 1, 2, ... from 0.0f, which is what the
+// lane-wise vfmacc chain of the RVV kernel computes
 // (lib/Conversion/RVV/RVVToEmitCBlockQuantLinear.cpp:3262-3298).  One warp per row group: lane
 // 16*h + r owns row r and takes the integer sums of the blocks with index parity h; the two
-// halves exchange them so that the lower half folds block 2m and then block 2m+1.  A chain of
-// nb dependent FMAs per row cannot be fast; this path exists for byte-exact comparison.
+// halves exchange them so that the lower half folds block 2m and then block 2m+1.  Slow (every
+// load waits for the one before), and only there so that no argument is refused.
 template <bool kQ8W>
 __global__ void __launch_bounds__(256) repack_gemv_strict_kernel(const uint8_t *__restrict__ vx,
                                                                  const uint8_t *__restrict__ vy,
@@ -402,13 +474,7 @@ int launch_repack_gemv_impl(size_t n, float *s, const uint8_t *vx, const uint8_t
   const size_t nb = n / kQK, groups = nc / 16;
   if (nb == 0 || groups == 0)
     return TCRV_CUDA_OK;
-  if (flags & TCRV_CUDA_FLAG_STRICT_ORDER) {
-    const size_t want = (groups + 7) / 8, cap = static_cast<size_t>(sm_count()) * 16;
-    repack_gemv_strict_kernel<kQ8W><<<static_cast<int>(want < cap ? want : cap), 256, 0, stream>>>(
-        vx, vy, s, static_cast<uint32_t>(nb), static_cast<uint32_t>(groups));
-    TCRV_CUDA_TRY(cudaGetLastError());
-    return TCRV_CUDA_OK;
-  }
+  const bool strict = (flags & TCRV_CUDA_FLAG_STRICT_ORDER) != 0;
   RepackGemvArgs args = {};
   args.vx = vx;
   args.vy = vy;
@@ -420,44 +486,79 @@ int launch_repack_gemv_impl(size_t n, float *s, const uint8_t *vx, const uint8_t
   const uint32_t grid = args.groups < sms ? args.groups : sms;
   // warps per group: as many as keep a CTA's groups within one or few rounds of 16 warps
   const uint32_t groups_per_cta = (args.groups + grid - 1) / grid;
-  uint32_t coop = args.parts;
-  while (coop > 1 && groups_per_cta * coop > kRpWarps)
+  const uint32_t steps = (args.nb + kRpStepBlocks - 1) / kRpStepBlocks;
+  const size_t x_fixed = kRpFixedBytes + rp_x_bytes(args.nb);
+  // strict order, warps sharing a group: one table of 1 KB per step and group of the round
+  auto strict_terms = [&](uint32_t c) { return c == 1 ? size_t{0} : static_cast<size_t>(groups_per_cta) * steps * 1024; };
+  uint32_t coop = strict ? 8u : args.parts;
+  while (coop > 1 && (groups_per_cta * coop > kRpWarps ||
+                      (strict && (coop > steps || x_fixed + strict_terms(coop) + 2 * static_cast<size_t>(groups_per_cta) *
+                                                                                     coop * F::kSlotBytes >
+                                                      kRpSmemLimit))))
     coop /= 2;
-  if (const unsigned forced = (flags >> 12) & 0xfu)
-    coop = forced > args.parts ? args.parts : forced;
+  if (const unsigned forced = (flags >> 12) & 0xfu) {
+    if (!strict)
+      coop = forced > args.parts ? args.parts : forced;
+    else if (forced < coop)
+      coop = forced;  // powers of two only
+  }
+  if (strict) {
+    if ((coop & (coop - 1)) != 0)
+      return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+    args.parts = coop;  // one contiguous span of steps per warp, one chain per row
+    args.terms_bytes = static_cast<uint32_t>(strict_terms(coop));
+  }
   if (coop == 0 || args.parts % coop != 0)
     return TCRV_CUDA_ERR_INVALID_ARGUMENT;
   args.coop = coop;
-  const size_t fixed = kRpFixedBytes + rp_x_bytes(args.nb);
+  // warps that have a group at all: only their rings take shared memory
+  const uint32_t active = groups_per_cta * coop < kRpWarps ? groups_per_cta * coop : kRpWarps;
+  const uint32_t ring_warps = strict ? active : kRpWarps;
+  const size_t fixed = x_fixed + args.terms_bytes;
   if ((reinterpret_cast<uintptr_t>(vx) & 15u) != 0 ||
-      fixed + 2 * static_cast<size_t>(kRpWarps) * F::kSlotBytes > kRpSmemLimit) {
+      x_fixed + 2 * static_cast<size_t>(kRpWarps) * F::kSlotBytes > kRpSmemLimit) {
     // unaligned weights, or K beyond ~100k elements (the activation column no longer fits)
-    const size_t want = (groups + 7) / 8, cap = static_cast<size_t>(sm_count()) * 8;
-    repack_gemv_generic_kernel<kQ8W><<<static_cast<int>(want < cap ? want : cap), 256, 0, stream>>>(
-        vx, vy, s, args.nb, args.groups, args.parts);
+    if (strict) {
+      const size_t want = (groups + 7) / 8, cap = static_cast<size_t>(sm_count()) * 16;
+      repack_gemv_strict_kernel<kQ8W><<<static_cast<int>(want < cap ? want : cap), 256, 0, stream>>>(
+          vx, vy, s, args.nb, args.groups);
+    } else {
+      const size_t want = (groups + 7) / 8, cap = static_cast<size_t>(sm_count()) * 8;
+      repack_gemv_generic_kernel<kQ8W><<<static_cast<int>(want < cap ? want : cap), 256, 0, stream>>>(
+          vx, vy, s, args.nb, args.groups, args.parts);
+    }
     TCRV_CUDA_TRY(cudaGetLastError());
     return TCRV_CUDA_OK;
   }
-  size_t depth = (kRpSmemLimit - fixed) / (static_cast<size_t>(kRpWarps) * F::kSlotBytes);
+  size_t depth = (kRpSmemLimit - fixed) / (static_cast<size_t>(ring_warps) * F::kSlotBytes);
   depth = depth > kRpMaxDepth ? kRpMaxDepth : depth;
   if (const unsigned forced = (flags >> 8) & 0xfu)
     depth = forced < 2 ? 2 : (forced > depth ? depth : forced);
   args.depth = static_cast<uint32_t>(depth);
-  uint32_t window = 1;  // one copy (about 4.5 KB) in flight per warp
+  // copies (about 4.5 KB each) a warp keeps in flight: one when all 16 warps stream, more
+  // when few warps of the CTA have a group
+  uint32_t window = strict ? (kRpWarps / active < 4 ? kRpWarps / active : 4) : 1;
   if (const unsigned forced = (flags >> 16) & 0xfu)
     window = forced;
   args.window = window < args.depth ? window : args.depth - 1;
-  const size_t smem = fixed + static_cast<size_t>(kRpWarps) * args.depth * F::kSlotBytes;
+  const size_t smem = fixed + static_cast<size_t>(ring_warps) * args.depth * F::kSlotBytes;
 
   static std::atomic<bool> configured[64][2];
   int dev = 0;
   TCRV_CUDA_TRY(cudaGetDevice(&dev));
   if (dev < 64 && !configured[dev][kQ8W ? 1 : 0]) {
-    TCRV_CUDA_TRY(cudaFuncSetAttribute(repack_gemv_kernel<kQ8W>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    TCRV_CUDA_TRY(cudaFuncSetAttribute(repack_gemv_kernel<kQ8W, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(kRpSmemLimit)));
+    TCRV_CUDA_TRY(cudaFuncSetAttribute(repack_gemv_kernel<kQ8W, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(kRpSmemLimit)));
     configured[dev][kQ8W ? 1 : 0] = true;
   }
-  TCRV_CUDA_TRY(launch_pdl(repack_gemv_kernel<kQ8W>, static_cast<int>(grid), kRpThreads, smem, stream, args));
+  if (strict) {
+    TCRV_CUDA_TRY(launch_pdl(repack_gemv_kernel<kQ8W, true>, static_cast<int>(grid), kRpThreads, smem, stream, args));
+    TCRV_CUDA_TRY(cudaGetLastError());
+    return TCRV_CUDA_OK;
+  }
+  TCRV_CUDA_TRY(launch_pdl(repack_gemv_kernel<kQ8W, false>, static_cast<int>(grid), kRpThreads, smem, stream, args));
   TCRV_CUDA_TRY(cudaGetLastError());
   return TCRV_CUDA_OK;
 }
