@@ -832,7 +832,7 @@ def measure_gemm(pkg, torch, dist, rank, world):
     return results
 
 
-PROFILE_CASES = ["gemv", "gemv_q8", "gemv_strict", "gemm", "dequant", "quantize", "silu", "rms_norm", "repack_gemv", "repack_gemv_q8",
+PROFILE_CASES = ["gemv", "gemv_q8", "gemv_strict", "gemv_strict_cta", "gemm", "dequant", "quantize", "silu", "rms_norm", "repack_gemv", "repack_gemv_q8",
                  "repack_gemm", "sibling_q4_1", "sibling_q5_0", "sibling_q5_1"]
 
 
@@ -851,10 +851,12 @@ def run_profile_case(args):
     pkg = entry.load_package()
     torch.cuda.set_device(0)
     gen = torch.Generator(device="cuda").manual_seed(7)
-    if args.case in ("gemv", "gemv_q8", "gemv_strict"):
+    if args.case in ("gemv", "gemv_q8", "gemv_strict", "gemv_strict_cta"):
         rows = args.rows or 32000
         q8w = args.case == "gemv_q8"
-        flags = pkg.FLAG_STRICT_ORDER if args.case == "gemv_strict" else 0
+        # gemv_strict_cta: the strict order on the kernel with one term table per CTA (tuning
+        # bit 13), which serves 2 columns and the sibling formats by default
+        flags = {"gemv_strict": pkg.FLAG_STRICT_ORDER, "gemv_strict_cta": pkg.FLAG_STRICT_ORDER | 0x2000}.get(args.case, 0)
         wf = torch.randn((rows, args.k), generator=gen, device="cuda") * 0.02
         w = pkg.quantize_q8_0(wf) if q8w else pkg.quantize_q4_0(wf)
         copies = [w] + [w.clone() for _ in range(max(2, (300 << 20) // w.numel()))]

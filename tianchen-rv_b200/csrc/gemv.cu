@@ -123,9 +123,9 @@ __global__ void __launch_bounds__(256) block_sums_kernel(const uint8_t *__restri
 
 constexpr size_t kMaxDynamicSmem = 227 * 1024;
 
-template <bool kQ8W, int kCols, int kXRegPairs>
+template <bool kQ8W, int kCols, int kXRegPairs, bool kStrict = false>
 int launch_stream_instance(const GemvArgs &args, int grid, size_t smem, cudaStream_t stream) {
-  auto kernel = gemv_stream_kernel<kQ8W, kCols, kXRegPairs>;
+  auto kernel = gemv_stream_kernel<kQ8W, kCols, kXRegPairs, kStrict>;
   static std::atomic<bool> configured[64];
   int dev = 0;
   TCRV_CUDA_TRY(cudaGetDevice(&dev));
@@ -154,6 +154,13 @@ int launch_stream_instance(const GemvArgs &args, int grid, size_t smem, cudaStre
 template <bool kQ8W>
 int launch_stream(const GemvArgs &args, uint32_t nc, int grid, size_t smem, cudaStream_t stream) {
   const uint32_t npairs = args.nb / 2;
+  if (args.table_bytes != 0) {  // the reference's order, one column
+    if (nc != 1)
+      return TCRV_CUDA_ERR_UNSUPPORTED;
+    if (npairs <= 64)
+      return launch_stream_instance<kQ8W, 1, 2, true>(args, grid, smem, stream);
+    return launch_stream_instance<kQ8W, 1, 0, true>(args, grid, smem, stream);
+  }
   switch (nc) {
     case 1:
       if (npairs <= 64)
@@ -415,8 +422,54 @@ int launch_gemv(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t
   const bool strict = (flags & TCRV_CUDA_FLAG_STRICT_ORDER) != 0;
   const size_t row_bytes = static_cast<size_t>(nb) * WB;
 
-  if (!strict && nb > 0 && nb % 8 == 0 && nc <= kGemvMaxCols && multiple_of(vx, 16) && bx % 16 == 0 &&
-      multiple_of(vy, 2) && by % 2 == 0) {
+  const bool bulk = nb > 0 && nb % 8 == 0 && nc <= kGemvMaxCols && multiple_of(vx, 16) && bx % 16 == 0 &&
+                    multiple_of(vy, 2) && by % 2 == 0;
+  // One column in the reference's order: the streaming kernel with a term table per warp
+  // (flags bit 13 keeps the table-per-CTA kernel: tuning).
+  if (strict && bulk && nc == 1 && (flags & 0x2000u) == 0) {
+    const size_t fixed = kGemvBarrierBytes + gemv_xcol_bytes(nb);
+    // rows per slot (= chains folded side by side), measured: 4 up to 4 KB rows, 3 up to 4.5 KB
+    // (Q8_0 weights with K = 4096, Q4_0 with K = 8192), 2 beyond; flags bits 8..11 override (tuning)
+    size_t rps = row_bytes <= 4096 ? 4 : (row_bytes <= 4608 ? 3 : 2);
+    const unsigned forced = (flags >> 8) & 0xfu;
+    if (forced >= 1 && forced <= 4)
+      rps = forced;
+    auto per_warp = [&](size_t rows) { return 2 * rows * row_bytes + gemv_strict_table_bytes(nb, rows, kQ8W); };
+    while (rps > 1 && fixed + per_warp(rps) > kMaxDynamicSmem)
+      --rps;
+    if (fixed + per_warp(rps) <= kMaxDynamicSmem) {
+      const size_t slot = rps * row_bytes, table = gemv_strict_table_bytes(nb, static_cast<uint32_t>(rps), kQ8W);
+      size_t nwarps = (kMaxDynamicSmem - fixed) / per_warp(rps);
+      nwarps = nwarps > kGemvMaxConsumerWarps ? kGemvMaxConsumerWarps : nwarps;
+      size_t spw = ((kMaxDynamicSmem - fixed) / nwarps - table) / slot;
+      spw = spw > kGemvMaxSlotsPerWarp ? kGemvMaxSlotsPerWarp : spw;
+      GemvArgs args;
+      args.vx = vx;
+      args.vy = vy;
+      args.s = s;
+      args.bx = bx;
+      args.by = by;
+      args.bs = bs;
+      args.nr = static_cast<uint32_t>(nr);
+      args.nb = nb;
+      args.row_bytes = static_cast<uint32_t>(row_bytes);
+      args.nwarps = static_cast<uint32_t>(nwarps);
+      args.slots = static_cast<uint32_t>(spw);
+      args.contiguous = (bx == row_bytes) ? 1u : 0u;
+      args.rps = static_cast<uint32_t>(rps);
+      args.static_weights = (flags & TCRV_CUDA_FLAG_STATIC_WEIGHTS) ? 1u : 0u;
+      args.window = 1;
+      if (const unsigned wf = (flags >> 16) & 0xfu)
+        args.window = wf < spw ? wf : static_cast<uint32_t>(spw);
+      args.table_bytes = static_cast<uint32_t>(table);
+      const size_t nslots = (nr + rps - 1) / rps;
+      const int sms = sm_count();
+      const int grid = static_cast<int>(nslots < static_cast<size_t>(sms) ? nslots : sms);
+      return launch_stream<kQ8W>(args, 1, grid, fixed + nwarps * (spw * slot + table), stream);
+    }
+  }
+
+  if (!strict && bulk) {
     // Many activation columns: the tensor-core kernel (measured faster from about 4 columns
     // on; flags bit 12 keeps the dp4a kernel, bit 14 takes this one for any column count: tuning).
     if ((nc >= kMmaMinCols || (flags & 0x4000u) != 0) && (flags & 0x1000u) == 0) {
@@ -477,13 +530,15 @@ int launch_gemv(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t
         if (wf >= 1)
           args.window = wf < spw ? wf : static_cast<uint32_t>(spw);
       }
+      args.table_bytes = 0;
       const size_t nslots = (nr + rps - 1) / rps;
       const int grid = static_cast<int>(nslots < static_cast<size_t>(sms) ? nslots : sms);
       return launch_stream<kQ8W>(args, static_cast<uint32_t>(nc), grid, fixed + nwarps * spw * slot, stream);
     }
   }
 
-  // the reference's strict order at streaming speed: up to 8 columns against many aligned rows
+  // the reference's strict order at streaming speed for what the per-warp tables above do not
+  // cover: 2..8 columns against many aligned rows
   if (strict) {
     // 3..8 columns on short rows: the tensor-core form (flags bit 13 keeps the dp4a form: tuning)
     if ((flags & 0x2000u) == 0)

@@ -29,7 +29,8 @@
 //
 // fp32 order: lane l folds its pairs l, l+32, ... in ascending order (even block, then odd
 // block), starting from 0.0f, with the fused fold; the 32 partials are then combined by a
-// butterfly (xor 16, 8, 4, 2, 1).
+// butterfly (xor 16, 8, 4, 2, 1).  The kStrict instantiation (one column) keeps the reference's
+// sequential order instead: see pair_terms / gemv_rows_strict below.
 #pragma once
 
 #include "async_copy.cuh"
@@ -58,6 +59,7 @@ struct GemvArgs {
   uint32_t rps;        // rows per slot: 1, 2 or 4 (single column), 1 or 2 otherwise
   uint32_t static_weights;  // weights may be fetched before the preceding kernel has finished
   uint32_t window;     // copies a warp keeps in flight (1..slots); below `slots` a refill is issued on arrival
+  uint32_t table_bytes;  // strict order: bytes of a warp's term table (gemv_strict_table_bytes), else 0
 };
 
 template <bool kQ8W>
@@ -111,6 +113,102 @@ __device__ __forceinline__ float fold_pair(float acc, const uint32_t *w, const X
     acc = fold_q4(acc, q4_0_q8_0_sumi(o, x.q1, x.s1), dw1, x.d1);
   }
   return acc;
+}
+
+// The reference's order in this kernel (kStrict, one column): a lane does not fold its pairs
+// but writes their terms into the warp's table, term[row][block] with a row pitch of nb + 4
+// floats, and lane r then folds row r block after block from 0.0f:
+//   Q4_0 weights: term = (float)sumi * d_w,  acc = fma(term, d_x, acc)   (d_x from the staged column)
+//   Q8_0 weights: term = (float)sumi and, in a second plane, d_w * d_x,  acc = fma(term, product, acc)
+// which are the operations of the sequential fold.  The chain of nb dependent FMAs per row
+// runs in at most four lanes of the warp while the other warps of the CTA stream and compute.
+__host__ __device__ inline uint32_t gemv_strict_pitch(uint32_t nb) { return nb + 4u; }
+__host__ __device__ inline uint32_t gemv_strict_table_bytes(uint32_t nb, uint32_t rps, bool q8w) {
+  return rps * gemv_strict_pitch(nb) * 4u * (q8w ? 2u : 1u);
+}
+
+template <bool kQ8W>
+__device__ __forceinline__ void pair_terms(const uint32_t *w, const XBlockPair &x, float2 &term, float2 &prod) {
+  using F = WeightFormat<kQ8W>;
+  constexpr int QW = F::kQuantWords;
+  const float dw0 = half_bits_to_float(w[0] & 0xffffu);
+  const float dw1 = half_bits_to_float(w[QW] >> 16);
+  uint32_t e[QW], o[QW];
+#pragma unroll
+  for (int j = 0; j < QW; ++j) {
+    e[j] = __funnelshift_r(w[j], w[j + 1], 16);
+    o[j] = w[QW + 1 + j];
+  }
+  if constexpr (kQ8W) {
+    term = make_float2(__int2float_rn(q8_0_q8_0_sumi(e, x.q0)), __int2float_rn(q8_0_q8_0_sumi(o, x.q1)));
+    prod = make_float2(__fmul_rn(dw0, x.d0), __fmul_rn(dw1, x.d1));
+  } else {
+    term = make_float2(__fmul_rn(__int2float_rn(q4_0_q8_0_sumi(e, x.q0, x.s0)), dw0),
+                       __fmul_rn(__int2float_rn(q4_0_q8_0_sumi(o, x.q1, x.s1)), dw1));
+    prod = make_float2(0.0f, 0.0f);
+  }
+}
+
+// The rows of one slot against the one column in the reference's order; every lane gets the
+// kRows sums in `res`.
+template <bool kQ8W, int kXRegPairs, int kRows>
+__device__ __forceinline__ void gemv_rows_strict(const GemvArgs &a, const uint32_t *wrow0, const uint8_t *xsm,
+                                                 const XBlockPair *xr, float *table, int lane,
+                                                 float (&res)[kGemvMaxRowsPerSlot]) {
+  using F = WeightFormat<kQ8W>;
+  constexpr int PW = F::kPairWords;
+  const uint32_t nb = a.nb, npairs = nb / 2;
+  const uint32_t row_words = a.row_bytes / 4;
+  const uint32_t pitch = gemv_strict_pitch(nb);
+  float *products = table + a.rps * pitch;  // Q8_0 weights only
+  auto one_pair = [&](uint32_t p, const XBlockPair &x) {
+    uint32_t w[kRows][PW];
+#pragma unroll
+    for (int r = 0; r < kRows; ++r)
+#pragma unroll
+      for (int j = 0; j < PW; ++j)
+        w[r][j] = wrow0[r * row_words + p * PW + j];
+#pragma unroll
+    for (int r = 0; r < kRows; ++r) {
+      float2 term, prod;
+      pair_terms<kQ8W>(w[r], x, term, prod);
+      *reinterpret_cast<float2 *>(table + r * pitch + 2 * p) = term;
+      if constexpr (kQ8W)
+        *reinterpret_cast<float2 *>(products + r * pitch + 2 * p) = prod;
+    }
+  };
+  if constexpr (kXRegPairs > 0) {
+#pragma unroll
+    for (int i = 0; i < kXRegPairs; ++i) {
+      const uint32_t p = lane + 32u * i;
+      if (p < npairs)
+        one_pair(p, xr[i]);
+    }
+  } else {
+    for (uint32_t p = lane; p < npairs; p += 32) {
+      XBlockPair x;
+      load_xpair(x, xsm, npairs, nb, p);
+      one_pair(p, x);
+    }
+  }
+  __syncwarp();
+  float acc = 0.0f;
+  if (lane < kRows) {
+    const float4 *t = reinterpret_cast<const float4 *>(table + lane * pitch);
+    const float4 *m = kQ8W ? reinterpret_cast<const float4 *>(products + lane * pitch)
+                           : reinterpret_cast<const float4 *>(xsm + npairs * 64u);  // the column's scales
+#pragma unroll 4
+    for (uint32_t i = 0; i < nb / 4; ++i) {
+      const float4 tv = t[i], mv = m[i];
+      acc = __fmaf_rn(tv.x, mv.x, acc);
+      acc = __fmaf_rn(tv.y, mv.y, acc);
+      acc = __fmaf_rn(tv.z, mv.z, acc);
+      acc = __fmaf_rn(tv.w, mv.w, acc);
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < kRows; ++r)
+    res[r] = __shfl_sync(0xffffffffu, acc, r);  // the caller meets (__syncwarp) before the table is written again
 }
 
 // Folds all block pairs of `kRows` weight rows (the rows of one slot) against every
@@ -192,14 +290,16 @@ __device__ __forceinline__ void gemv_rows(const GemvArgs &a, const uint32_t *wro
 
 // kCols: activation columns (1..8).  kXRegPairs: when > 0 (single column only) the lane keeps
 // its activation pairs in registers for the whole kernel; requires npairs <= 32*kXRegPairs.
-template <bool kQ8W, int kCols, int kXRegPairs>
+template <bool kQ8W, int kCols, int kXRegPairs, bool kStrict = false>
 __global__ void __launch_bounds__(kGemvMaxThreads, 1) gemv_stream_kernel(const GemvArgs a) {
+  static_assert(!kStrict || kCols == 1, "the strict order of this kernel is built for one column");
   extern __shared__ __align__(128) uint8_t smem[];
   uint64_t *full = reinterpret_cast<uint64_t *>(smem);
   uint8_t *xsm = smem + kGemvBarrierBytes;
   const uint32_t nb = a.nb, npairs = nb / 2;
   const uint32_t xcol_bytes = gemv_xcol_bytes(nb);
-  uint8_t *slots = xsm + static_cast<size_t>(kCols) * xcol_bytes;
+  uint8_t *tables = xsm + static_cast<size_t>(kCols) * xcol_bytes;  // kStrict: one term table per warp
+  uint8_t *slots = tables + static_cast<size_t>(a.nwarps) * a.table_bytes;
   const uint32_t rps = a.rps;
   const uint32_t slot_bytes = rps * a.row_bytes;
   const uint32_t nwarps = a.nwarps, spw = a.slots;
@@ -306,7 +406,17 @@ __global__ void __launch_bounds__(kGemvMaxThreads, 1) gemv_stream_kernel(const G
     const uint32_t rows = slot_count(t);
     // all rows of the slot are folded together (independent accumulators hide latency)
     float res[kGemvMaxRowsPerSlot];
-    if (rows == 4) {
+    if constexpr (kStrict) {
+      float *table = reinterpret_cast<float *>(tables + static_cast<size_t>(warp) * a.table_bytes);
+      if (rows == 4)
+        gemv_rows_strict<kQ8W, kXRegPairs, 4>(a, wrow, xsm, xr, table, lane, res);
+      else if (rows == 3)
+        gemv_rows_strict<kQ8W, kXRegPairs, 3>(a, wrow, xsm, xr, table, lane, res);
+      else if (rows == 2)
+        gemv_rows_strict<kQ8W, kXRegPairs, 2>(a, wrow, xsm, xr, table, lane, res);
+      else
+        gemv_rows_strict<kQ8W, kXRegPairs, 1>(a, wrow, xsm, xr, table, lane, res);
+    } else if (rows == 4) {
       if constexpr (kCols == 1)
         gemv_rows<kQ8W, kCols, kXRegPairs, 4>(a, wrow, xsm, xcol_bytes, xr, row, lane, res);
     } else if (rows == 3) {
