@@ -225,11 +225,12 @@ def test_tensor_core_gemv_reports_and_follows_its_order(cuda, pkg, O, q8w, nr, k
 @pytest.mark.parametrize("q8w", [False, True])
 @pytest.mark.parametrize("nr,k,nc", [(64, 256, 4), (97, 256, 6), (1000, 4096, 8), (333, 2048, 5), (1000, 4096, 1),
                                      (500, 4096, 3), (257, 11008, 8), (70, 4096, 8), (20000, 4096, 1),
-                                     (4096, 11008, 1), (2048, 8192, 1), (150, 256, 1), (64, 8192, 2), (7, 4096, 1)])
+                                     (4096, 11008, 1), (2048, 8192, 1), (150, 256, 1), (64, 8192, 2), (7, 4096, 1), (4096, 4096, 2),
+                                     (1000, 11008, 3), (3000, 4096, 3)])
 def test_strict_order_streaming_kernels_are_bit_exact(cuda, pkg, O, q8w, nr, k, nc):
-    # Aligned rows take the strict streaming kernels (term table + sequential fold): one column the
-    # streaming kernel with a table per warp, 3..8 columns on rows of up to 4096 elements the
-    # tensor-core form, the rest (from 64 rows on) the dp4a form with a table per CTA.
+    # Aligned rows take the strict streaming kernels (term table + sequential fold): one or two
+    # columns the streaming kernel with a table per warp, 3..8 columns on rows of up to 4096 elements
+    # the tensor-core form, the rest (from 64 rows on) the dp4a form with a table per CTA.
     # Every output must have the bits of the sequential fold; flags bit 13 (table per CTA) gives the same.
     w, x = make(O, nr, k, nc, q8w, 2300 + nr + nc)
     wd, xd = dev(cuda, w), dev(cuda, x)
@@ -238,7 +239,10 @@ def test_strict_order_streaming_kernels_are_bit_exact(cuda, pkg, O, q8w, nr, k, 
     assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
     alt = pkg.gemv(wd, xd, q8_weights=q8w, flags=pkg.FLAG_STRICT_ORDER | 0x2000).cpu().numpy()
     assert np.array_equal(alt.view(np.uint32), want.view(np.uint32))
-    if nc == 1:
+    if nc <= 3:
+        # flags bit 14: the table-per-warp kernel for 3 columns too
+        alt = pkg.gemv(wd, xd, q8_weights=q8w, flags=pkg.FLAG_STRICT_ORDER | 0x4000).cpu().numpy()
+        assert np.array_equal(alt.view(np.uint32), want.view(np.uint32))
         # rows per slot and copies in flight of the table-per-warp kernel are scheduling choices only
         for rps, window in ((1, 1), (2, 2), (3, 1), (4, 3)):
             alt = pkg.gemv(wd, xd, q8_weights=q8w, flags=pkg.FLAG_STRICT_ORDER | (rps << 8) | (window << 16)).cpu().numpy()

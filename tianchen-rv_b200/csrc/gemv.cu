@@ -122,6 +122,7 @@ __global__ void __launch_bounds__(256) block_sums_kernel(const uint8_t *__restri
 }
 
 constexpr size_t kMaxDynamicSmem = 227 * 1024;
+constexpr size_t kStrictWarpTableCols = 2;  // strict order: columns served by the table-per-warp streaming kernel
 
 template <bool kQ8W, int kCols, int kXRegPairs, bool kStrict = false>
 int launch_stream_instance(const GemvArgs &args, int grid, size_t smem, cudaStream_t stream) {
@@ -154,12 +155,19 @@ int launch_stream_instance(const GemvArgs &args, int grid, size_t smem, cudaStre
 template <bool kQ8W>
 int launch_stream(const GemvArgs &args, uint32_t nc, int grid, size_t smem, cudaStream_t stream) {
   const uint32_t npairs = args.nb / 2;
-  if (args.table_bytes != 0) {  // the reference's order, one column
-    if (nc != 1)
-      return TCRV_CUDA_ERR_UNSUPPORTED;
-    if (npairs <= 64)
-      return launch_stream_instance<kQ8W, 1, 2, true>(args, grid, smem, stream);
-    return launch_stream_instance<kQ8W, 1, 0, true>(args, grid, smem, stream);
+  if (args.table_bytes != 0) {  // the reference's order, up to 3 columns
+    switch (nc) {
+      case 1:
+        if (npairs <= 64)
+          return launch_stream_instance<kQ8W, 1, 2, true>(args, grid, smem, stream);
+        return launch_stream_instance<kQ8W, 1, 0, true>(args, grid, smem, stream);
+      case 2:
+        return launch_stream_instance<kQ8W, 2, 0, true>(args, grid, smem, stream);
+      case 3:
+        return launch_stream_instance<kQ8W, 3, 0, true>(args, grid, smem, stream);
+      default:
+        return TCRV_CUDA_ERR_UNSUPPORTED;
+    }
   }
   switch (nc) {
     case 1:
@@ -424,21 +432,29 @@ int launch_gemv(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t
 
   const bool bulk = nb > 0 && nb % 8 == 0 && nc <= kGemvMaxCols && multiple_of(vx, 16) && bx % 16 == 0 &&
                     multiple_of(vy, 2) && by % 2 == 0;
-  // One column in the reference's order: the streaming kernel with a term table per warp
-  // (flags bit 13 keeps the table-per-CTA kernel: tuning).
-  if (strict && bulk && nc == 1 && (flags & 0x2000u) == 0) {
-    const size_t fixed = kGemvBarrierBytes + gemv_xcol_bytes(nb);
+  // One or two columns in the reference's order: the streaming kernel with a term table per
+  // warp; also three columns of Q4_0 weights on rows too long for the tensor-core form
+  // (4096x11008: 16.7 us against 20.7).  Flags bit 13 keeps the table-per-CTA / tensor-core
+  // kernels, bit 14 takes this one for any 3 columns: tuning.
+  const bool warp_tables =
+      nc <= kStrictWarpTableCols ||
+      (nc == 3 && ((flags & 0x4000u) != 0 || (!kQ8W && mma_strict_ring<kQ8W>(nb, nr, nc, vx, bx) == 0)));
+  if (strict && bulk && warp_tables && (flags & 0x2000u) == 0) {
+    const size_t fixed = kGemvBarrierBytes + nc * static_cast<size_t>(gemv_xcol_bytes(nb));
     // rows per slot (= chains folded side by side), measured: 4 up to 4 KB rows, 3 up to 4.5 KB
     // (Q8_0 weights with K = 4096, Q4_0 with K = 8192), 2 beyond; flags bits 8..11 override (tuning)
-    size_t rps = row_bytes <= 4096 ? 4 : (row_bytes <= 4608 ? 3 : 2);
+    size_t rps = nc > 1 ? 2 : (row_bytes <= 4096 ? 4 : (row_bytes <= 4608 ? 3 : 2));
     const unsigned forced = (flags >> 8) & 0xfu;
-    if (forced >= 1 && forced <= 4)
+    if (forced >= 1 && forced <= (nc > 1 ? 2u : 4u))
       rps = forced;
-    auto per_warp = [&](size_t rows) { return 2 * rows * row_bytes + gemv_strict_table_bytes(nb, rows, kQ8W); };
+    const uint32_t cols = static_cast<uint32_t>(nc);
+    auto per_warp = [&](size_t rows) {
+      return 2 * rows * row_bytes + gemv_strict_table_bytes(nb, static_cast<uint32_t>(rows), kQ8W, cols);
+    };
     while (rps > 1 && fixed + per_warp(rps) > kMaxDynamicSmem)
       --rps;
     if (fixed + per_warp(rps) <= kMaxDynamicSmem) {
-      const size_t slot = rps * row_bytes, table = gemv_strict_table_bytes(nb, static_cast<uint32_t>(rps), kQ8W);
+      const size_t slot = rps * row_bytes, table = gemv_strict_table_bytes(nb, static_cast<uint32_t>(rps), kQ8W, cols);
       size_t nwarps = (kMaxDynamicSmem - fixed) / per_warp(rps);
       nwarps = nwarps > kGemvMaxConsumerWarps ? kGemvMaxConsumerWarps : nwarps;
       size_t spw = ((kMaxDynamicSmem - fixed) / nwarps - table) / slot;
@@ -465,7 +481,7 @@ int launch_gemv(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t
       const size_t nslots = (nr + rps - 1) / rps;
       const int sms = sm_count();
       const int grid = static_cast<int>(nslots < static_cast<size_t>(sms) ? nslots : sms);
-      return launch_stream<kQ8W>(args, 1, grid, fixed + nwarps * (spw * slot + table), stream);
+      return launch_stream<kQ8W>(args, cols, grid, fixed + nwarps * (spw * slot + table), stream);
     }
   }
 

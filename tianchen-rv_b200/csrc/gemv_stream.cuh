@@ -115,16 +115,16 @@ __device__ __forceinline__ float fold_pair(float acc, const uint32_t *w, const X
   return acc;
 }
 
-// The reference's order in this kernel (kStrict, one column): a lane does not fold its pairs
-// but writes their terms into the warp's table, term[row][block] with a row pitch of nb + 4
-// floats, and lane r then folds row r block after block from 0.0f:
+// The reference's order in this kernel (kStrict, up to 3 columns): a lane does not fold its pairs
+// but writes their terms into the warp's table, term[column][row][block] with a row pitch of
+// nb + 4 floats, and lane (column, row) then folds its output block after block from 0.0f:
 //   Q4_0 weights: term = (float)sumi * d_w,  acc = fma(term, d_x, acc)   (d_x from the staged column)
 //   Q8_0 weights: term = (float)sumi and, in a second plane, d_w * d_x,  acc = fma(term, product, acc)
 // which are the operations of the sequential fold.  The chain of nb dependent FMAs per row
-// runs in at most four lanes of the warp while the other warps of the CTA stream and compute.
+// runs in at most six lanes of the warp while the other warps of the CTA stream and compute.
 __host__ __device__ inline uint32_t gemv_strict_pitch(uint32_t nb) { return nb + 4u; }
-__host__ __device__ inline uint32_t gemv_strict_table_bytes(uint32_t nb, uint32_t rps, bool q8w) {
-  return rps * gemv_strict_pitch(nb) * 4u * (q8w ? 2u : 1u);
+__host__ __device__ inline uint32_t gemv_strict_table_bytes(uint32_t nb, uint32_t rps, bool q8w, uint32_t cols) {
+  return cols * rps * gemv_strict_pitch(nb) * 4u * (q8w ? 2u : 1u);
 }
 
 template <bool kQ8W>
@@ -149,54 +149,65 @@ __device__ __forceinline__ void pair_terms(const uint32_t *w, const XBlockPair &
   }
 }
 
-// The rows of one slot against the one column in the reference's order; every lane gets the
-// kRows sums in `res`.
-template <bool kQ8W, int kXRegPairs, int kRows>
+// The rows of one slot against the columns in the reference's order.  One column: every lane
+// gets the kRows sums in `res`; several columns: the folding lanes store their outputs.
+template <bool kQ8W, int kCols, int kXRegPairs, int kRows>
 __device__ __forceinline__ void gemv_rows_strict(const GemvArgs &a, const uint32_t *wrow0, const uint8_t *xsm,
-                                                 const XBlockPair *xr, float *table, int lane,
-                                                 float (&res)[kGemvMaxRowsPerSlot]) {
+                                                 uint32_t xcol_bytes, const XBlockPair *xr, float *table, uint32_t row,
+                                                 int lane, float (&res)[kGemvMaxRowsPerSlot]) {
   using F = WeightFormat<kQ8W>;
   constexpr int PW = F::kPairWords;
   const uint32_t nb = a.nb, npairs = nb / 2;
   const uint32_t row_words = a.row_bytes / 4;
   const uint32_t pitch = gemv_strict_pitch(nb);
-  float *products = table + a.rps * pitch;  // Q8_0 weights only
-  auto one_pair = [&](uint32_t p, const XBlockPair &x) {
-    uint32_t w[kRows][PW];
+  float *products = table + kCols * a.rps * pitch;  // Q8_0 weights only
+  auto one_pair = [&](uint32_t p, const uint32_t (&w)[kRows][PW], const XBlockPair &x, int col) {
+#pragma unroll
+    for (int r = 0; r < kRows; ++r) {
+      float2 term, prod;
+      pair_terms<kQ8W>(w[r], x, term, prod);
+      *reinterpret_cast<float2 *>(table + (col * a.rps + r) * pitch + 2 * p) = term;
+      if constexpr (kQ8W)
+        *reinterpret_cast<float2 *>(products + (col * a.rps + r) * pitch + 2 * p) = prod;
+    }
+  };
+  auto load_w = [&](uint32_t p, uint32_t (&w)[kRows][PW]) {
 #pragma unroll
     for (int r = 0; r < kRows; ++r)
 #pragma unroll
       for (int j = 0; j < PW; ++j)
         w[r][j] = wrow0[r * row_words + p * PW + j];
-#pragma unroll
-    for (int r = 0; r < kRows; ++r) {
-      float2 term, prod;
-      pair_terms<kQ8W>(w[r], x, term, prod);
-      *reinterpret_cast<float2 *>(table + r * pitch + 2 * p) = term;
-      if constexpr (kQ8W)
-        *reinterpret_cast<float2 *>(products + r * pitch + 2 * p) = prod;
-    }
   };
   if constexpr (kXRegPairs > 0) {
 #pragma unroll
     for (int i = 0; i < kXRegPairs; ++i) {
       const uint32_t p = lane + 32u * i;
-      if (p < npairs)
-        one_pair(p, xr[i]);
+      if (p < npairs) {
+        uint32_t w[kRows][PW];
+        load_w(p, w);
+        one_pair(p, w, xr[i], 0);
+      }
     }
   } else {
     for (uint32_t p = lane; p < npairs; p += 32) {
-      XBlockPair x;
-      load_xpair(x, xsm, npairs, nb, p);
-      one_pair(p, x);
+      uint32_t w[kRows][PW];
+      load_w(p, w);
+#pragma unroll
+      for (int b = 0; b < kCols; ++b) {
+        XBlockPair x;
+        load_xpair(x, xsm + static_cast<size_t>(b) * xcol_bytes, npairs, nb, p);
+        one_pair(p, w, x, b);
+      }
     }
   }
   __syncwarp();
   float acc = 0.0f;
-  if (lane < kRows) {
-    const float4 *t = reinterpret_cast<const float4 *>(table + lane * pitch);
-    const float4 *m = kQ8W ? reinterpret_cast<const float4 *>(products + lane * pitch)
-                           : reinterpret_cast<const float4 *>(xsm + npairs * 64u);  // the column's scales
+  const int col = lane / kRows, r = lane - col * kRows;
+  if (lane < kRows * kCols) {
+    const float4 *t = reinterpret_cast<const float4 *>(table + (col * a.rps + r) * pitch);
+    const float4 *m = kQ8W ? reinterpret_cast<const float4 *>(products + (col * a.rps + r) * pitch)
+                           : reinterpret_cast<const float4 *>(xsm + static_cast<size_t>(col) * xcol_bytes +
+                                                              npairs * 64u);  // the column's scales
 #pragma unroll 4
     for (uint32_t i = 0; i < nb / 4; ++i) {
       const float4 tv = t[i], mv = m[i];
@@ -205,10 +216,15 @@ __device__ __forceinline__ void gemv_rows_strict(const GemvArgs &a, const uint32
       acc = __fmaf_rn(tv.z, mv.z, acc);
       acc = __fmaf_rn(tv.w, mv.w, acc);
     }
+    if constexpr (kCols > 1)
+      a.s[static_cast<size_t>(row + r) * a.bs + col] = acc;
   }
+  if constexpr (kCols == 1) {
 #pragma unroll
-  for (int r = 0; r < kRows; ++r)
-    res[r] = __shfl_sync(0xffffffffu, acc, r);  // the caller meets (__syncwarp) before the table is written again
+    for (int q = 0; q < kRows; ++q)
+      res[q] = __shfl_sync(0xffffffffu, acc, q);
+  }
+  // the caller meets (__syncwarp) before the table is written again
 }
 
 // Folds all block pairs of `kRows` weight rows (the rows of one slot) against every
@@ -292,7 +308,7 @@ __device__ __forceinline__ void gemv_rows(const GemvArgs &a, const uint32_t *wro
 // its activation pairs in registers for the whole kernel; requires npairs <= 32*kXRegPairs.
 template <bool kQ8W, int kCols, int kXRegPairs, bool kStrict = false>
 __global__ void __launch_bounds__(kGemvMaxThreads, 1) gemv_stream_kernel(const GemvArgs a) {
-  static_assert(!kStrict || kCols == 1, "the strict order of this kernel is built for one column");
+  static_assert(!kStrict || kCols <= 3, "the strict order of this kernel is built for up to 3 columns");
   extern __shared__ __align__(128) uint8_t smem[];
   uint64_t *full = reinterpret_cast<uint64_t *>(smem);
   uint8_t *xsm = smem + kGemvBarrierBytes;
@@ -408,14 +424,17 @@ __global__ void __launch_bounds__(kGemvMaxThreads, 1) gemv_stream_kernel(const G
     float res[kGemvMaxRowsPerSlot];
     if constexpr (kStrict) {
       float *table = reinterpret_cast<float *>(tables + static_cast<size_t>(warp) * a.table_bytes);
-      if (rows == 4)
-        gemv_rows_strict<kQ8W, kXRegPairs, 4>(a, wrow, xsm, xr, table, lane, res);
-      else if (rows == 3)
-        gemv_rows_strict<kQ8W, kXRegPairs, 3>(a, wrow, xsm, xr, table, lane, res);
-      else if (rows == 2)
-        gemv_rows_strict<kQ8W, kXRegPairs, 2>(a, wrow, xsm, xr, table, lane, res);
-      else
-        gemv_rows_strict<kQ8W, kXRegPairs, 1>(a, wrow, xsm, xr, table, lane, res);
+      if (rows == 4) {
+        if constexpr (kCols == 1)
+          gemv_rows_strict<kQ8W, kCols, kXRegPairs, 4>(a, wrow, xsm, xcol_bytes, xr, table, row, lane, res);
+      } else if (rows == 3) {
+        if constexpr (kCols == 1)
+          gemv_rows_strict<kQ8W, kCols, kXRegPairs, 3>(a, wrow, xsm, xcol_bytes, xr, table, row, lane, res);
+      } else if (rows == 2) {
+        gemv_rows_strict<kQ8W, kCols, kXRegPairs, 2>(a, wrow, xsm, xcol_bytes, xr, table, row, lane, res);
+      } else {
+        gemv_rows_strict<kQ8W, kCols, kXRegPairs, 1>(a, wrow, xsm, xcol_bytes, xr, table, row, lane, res);
+      }
     } else if (rows == 4) {
       if constexpr (kCols == 1)
         gemv_rows<kQ8W, kCols, kXRegPairs, 4>(a, wrow, xsm, xcol_bytes, xr, row, lane, res);
