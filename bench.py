@@ -470,7 +470,8 @@ def measure_e2e(pkg, torch, layers, steps, dist):
     call (`tcrv_cuda_host_gemm_q4_0_q8_0`, the int-returning twin of
     `tcrv_emitc_ggml_q4_0_q8_0_gemm_kernel_ggml_q4_0_q8_0_gemm`): activations start in pinned
     host memory and every step's outputs land in pinned host memory.  Weights are registered
-    once (resident, like model parameters) and are not re-uploaded per step."""
+    once (resident, like model parameters) and are not re-uploaded per step.  The timed loops run
+    in a C++ caller of the entries (examples/gpu/decode_loop.cpp) when its library has been built."""
     import ctypes
 
     L = pkg.lib()
@@ -508,6 +509,38 @@ def measure_e2e(pkg, torch, layers, steps, dist):
         if st != 0:
             raise RuntimeError(f"host sync failed: {st}")
 
+    # The timed loops run in a C++ caller of the same entries (examples/gpu/decode_loop.cpp, a
+    # shared library built beside the C-ABI library): what is timed is then the entries, not this
+    # interpreter's foreign-call overhead of five calls per step.  Without that library the loops
+    # below run here and the line says so.
+    loop = None
+    loop_path = os.path.join(os.path.dirname(pkg.LIB_PATH), "libtcrv_decode_loop.so")
+    if os.path.exists(loop_path):
+        class DecodeCall(ctypes.Structure):
+            _fields_ = [("n", ctypes.c_size_t), ("s", ctypes.c_void_p), ("vx", ctypes.c_void_p), ("vy", ctypes.c_void_p),
+                        ("by", ctypes.c_size_t), ("nr", ctypes.c_size_t), ("nc", ctypes.c_size_t),
+                        ("bx", ctypes.c_size_t), ("bs", ctypes.c_size_t)]
+
+        loop = ctypes.CDLL(loop_path)
+        loop.tcrv_decode_loop_run.argtypes = [ctypes.POINTER(DecodeCall), ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                                              ctypes.POINTER(ctypes.c_double)]
+        loop.tcrv_decode_loop_run.restype = ctypes.c_int
+        call_array = (DecodeCall * len(calls))(*[DecodeCall(*args) for args in calls])
+
+    def run_steps(one_pass, count):
+        """`count` decode steps; returns the elapsed wall time in seconds."""
+        if loop is not None:
+            seconds = ctypes.c_double(0.0)
+            st = loop.tcrv_decode_loop_run(call_array, len(calls), count, 1 if one_pass is one_pass_queued else 0,
+                                           ctypes.byref(seconds))
+            if st != 0:
+                raise RuntimeError(f"host gemv failed: {st}")
+            return seconds.value
+        t0 = time.perf_counter()
+        for _ in range(count):
+            one_pass()
+        return time.perf_counter() - t0
+
     device_flags = [0]
 
     def check():
@@ -524,12 +557,10 @@ def measure_e2e(pkg, torch, layers, steps, dist):
             one_pass()
         check()
         one_pass()
+        run_steps(one_pass, 3)
         if dist is not None:
             dist.barrier()
-        t0 = time.perf_counter()
-        for _ in range(steps):
-            one_pass()
-        dt = time.perf_counter() - t0
+        dt = run_steps(one_pass, steps)
         if dist is not None:
             t = torch.tensor([dt], dtype=torch.float64, device="cuda")
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -540,6 +571,15 @@ def measure_e2e(pkg, torch, layers, steps, dist):
     dt = timed(one_pass_queued)
     one_pass_queued()
     check()
+    # the same queued step called from this interpreter (five foreign calls per step)
+    dt_interp = None
+    if loop is not None:
+        for _ in range(3):
+            one_pass_queued()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            one_pass_queued()
+        dt_interp = time.perf_counter() - t0
     # the same queued step in the entries' default, the reference's strict block order (every
     # output byte-identical with the generated kernel's): the strict streaming kernel
     L.tcrv_cuda_host_set_fold_order(0)
@@ -560,6 +600,12 @@ def measure_e2e(pkg, torch, layers, steps, dist):
             "call": "tcrv_cuda_host_gemm_q4_0_q8_0_async per layer + tcrv_cuda_host_sync per step (one host round trip "
                     "per step; the library replays a repeated step as one graph: one fetch of the four layers' "
                     "activations, four GEMV kernels)",
+            "caller": ("a C++ loop over the entries (examples/gpu/decode_loop.cpp), wall clock around all steps"
+                       if loop is not None else "this interpreter (ctypes), wall clock around all steps"),
+            "interpreter_caller": (None if dt_interp is None else
+                                   {"value": round(step_bytes * steps / dt_interp / 1e9, 2),
+                                    "ms_per_step": round(dt_interp / steps * 1e3, 4),
+                                    "call": "the same queued step with the five calls made through ctypes (this rank)"}),
             "blocking_calls": {"value": round(step_bytes * steps * world / dt_blocking / 1e9, 2),
                                "ms_per_step": round(dt_blocking / steps * 1e3, 4),
                                "call": "tcrv_cuda_host_gemm_q4_0_q8_0 per layer (each call waits for its result)"},

@@ -30,6 +30,22 @@ def test_library_exports_every_declared_symbol(pkg):
     assert not missing, f"declared in include/*.h but not exported: {missing}"
 
 
+def test_decode_loop_helper_builds_and_exports_its_entry(pkg):
+    # the C++ caller of the host entries that the benchmark's end-to-end leg times (host compiler only)
+    import subprocess
+
+    pkg.build_library()
+    pkg_dir = os.path.dirname(pkg.LIB_PATH)
+    subprocess.run(["make", "-s", "-C", pkg_dir, "decode_loop"], check=True)
+    helper = ctypes.CDLL(os.path.join(pkg_dir, "libtcrv_decode_loop.so"))
+    assert hasattr(helper, "tcrv_decode_loop_run")
+    # zero steps of zero calls: no entry is called, the clock is read
+    helper.tcrv_decode_loop_run.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                                            ctypes.POINTER(ctypes.c_double)]
+    seconds = ctypes.c_double(-1.0)
+    assert helper.tcrv_decode_loop_run(None, 0, 0, 1, ctypes.byref(seconds)) == 0 and 0.0 <= seconds.value < 1.0
+
+
 def test_python_binding_table_matches_header(pkg):
     assert sorted(n for n in pkg.ABI if n.startswith("tcrv_cuda_")) == [
         n for n in declared_functions() if n.startswith("tcrv_cuda_")
