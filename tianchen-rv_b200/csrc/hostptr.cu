@@ -118,7 +118,30 @@ void drop_replays(HostContext &c) {
   c.sequences.clear();
 }
 
+// cuPointerGetAttribute of the driver, looked up once: asking for the memory type alone takes a
+// fraction of the time of cudaPointerGetAttributes, and a queued decode step asks eight times.
+using PointerAttributeFn = int (*)(void *data, int attribute, unsigned long long ptr);
+PointerAttributeFn pointer_attribute_fn() {
+  static const PointerAttributeFn fn = [] {
+    void *f = nullptr;
+    cudaDriverEntryPointQueryResult found = cudaDriverEntryPointSymbolNotFound;
+    if (cudaGetDriverEntryPoint("cuPointerGetAttribute", &f, cudaEnableDefault, &found) != cudaSuccess ||
+        found != cudaDriverEntryPointSuccess) {
+      (void)cudaGetLastError();
+      f = nullptr;
+    }
+    return reinterpret_cast<PointerAttributeFn>(f);
+  }();
+  return fn;
+}
+
 bool is_pinned_host(const void *p) {
+  if (const PointerAttributeFn fn = pointer_attribute_fn()) {
+    constexpr int kAttributeMemoryType = 2;  // CU_POINTER_ATTRIBUTE_MEMORY_TYPE
+    constexpr unsigned kMemoryTypeHost = 1;  // CU_MEMORYTYPE_HOST: page-locked host memory known to the driver
+    unsigned type = 0;
+    return fn(&type, kAttributeMemoryType, reinterpret_cast<unsigned long long>(p)) == 0 && type == kMemoryTypeHost;
+  }
   cudaPointerAttributes attr;
   if (cudaPointerGetAttributes(&attr, p) != cudaSuccess) {
     (void)cudaGetLastError();
