@@ -599,7 +599,7 @@ def measure_e2e(pkg, torch, layers, steps, dist):
             "ms_per_step": round(dt / steps * 1e3, 4), "steps": steps,
             "call": "tcrv_cuda_host_gemm_q4_0_q8_0_async per layer + tcrv_cuda_host_sync per step (one host round trip "
                     "per step; the library replays a repeated step as one graph: one fetch of the four layers' "
-                    "activations, four GEMV kernels)",
+                    "activations, then one grouped launch in which the four independent GEMVs stream at once)",
             "caller": ("a C++ loop over the entries (examples/gpu/decode_loop.cpp), wall clock around all steps"
                        if loop is not None else "this interpreter (ctypes), wall clock around all steps"),
             "interpreter_caller": (None if dt_interp is None else

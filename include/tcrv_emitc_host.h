@@ -82,8 +82,11 @@ int tcrv_cuda_host_gemm_q4_0_q8_0(size_t n, float *s, const uint8_t *vx, const u
  * calls, nothing else in between) that repeats between syncs with the same arguments - a decode
  * step - is recorded the first time, captured the second and from then on held back until the
  * sync (or the next other call) and launched as ONE graph: a single kernel fetches every call's
- * activations, the GEMVs follow back to back.  Results are those of the calls made one by one;
- * a run in which a call reads a buffer an earlier call of the run writes is never merged. */
+ * activations, the GEMVs follow back to back - or, when every call has one activation column
+ * and the same weight format, as one grouped launch in which the SMs are dealt out among the
+ * calls and all of them stream at once (the calls of such a run do not depend on one another).
+ * Results are those of the calls made one by one, bit for bit; a run in which a call reads a
+ * buffer an earlier call of the run writes is never merged. */
 int tcrv_cuda_host_gemm_q4_0_q8_0_async(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by, size_t nr,
                                         size_t nc, size_t bx, size_t bs);
 int tcrv_cuda_host_gemm_q8_0_q8_0_async(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by, size_t nr,

@@ -434,6 +434,48 @@ def test_a_repeated_run_of_queued_calls_is_replayed_as_one_sequence(cuda, pkg, O
         L.tcrv_cuda_host_release()
 
 
+@pytest.mark.parametrize("q8w", [False, True], ids=["q4_0", "q8_0"])
+@pytest.mark.parametrize("order", [0, 1], ids=["strict", "fast"])
+def test_a_replayed_step_of_one_column_calls_runs_as_one_grouped_launch(cuda, pkg, O, q8w, order):
+    # A replayed step whose calls all have one activation column and one weight format is issued as
+    # ONE grouped launch of the streaming kernel (the SMs dealt out among the calls): every call
+    # must still have the bits of its own blocking call, in either fold order, for rows of up to
+    # and beyond 4096 elements and for calls with fewer rows than a CTA's share.
+    L = pkg.lib()
+    previous = L.tcrv_cuda_host_set_fold_order(order)
+    shapes = [(700, 4096), (300, 11008), (5, 2048), (2000, 1024), (130, 8192)]
+    quant = O.quantize_q8_0 if q8w else O.quantize_q4_0
+    queue_fn = L.tcrv_cuda_host_gemm_q8_0_q8_0_async if q8w else L.tcrv_cuda_host_gemm_q4_0_q8_0_async
+    block_fn = L.tcrv_cuda_host_gemm_q8_0_q8_0 if q8w else L.tcrv_cuda_host_gemm_q4_0_q8_0
+    layers = []
+    for i, (nr, k) in enumerate(shapes):
+        wh = np.ascontiguousarray(quant(O.fill_normal(nr * k, 8800 + i, 0.0, 0.02).reshape(nr, k)))
+        xt = cuda.empty((1, k // 32 * 34), dtype=cuda.uint8).pin_memory()
+        yt = cuda.empty((nr, 1), dtype=cuda.float32).pin_memory()
+        assert L.tcrv_cuda_host_register_weights(wh.ctypes.data, wh.nbytes) == 0
+        layers.append((nr, k, wh, xt, yt))
+    try:
+        for rnd in range(5):
+            for j, (nr, k, wh, xt, yt) in enumerate(layers):
+                xt.copy_(cuda.from_numpy(O.quantize_q8_0(O.fill_normal(k, 8900 + 10 * rnd + j).reshape(1, k))))
+                yt.fill_(float("nan"))
+            for nr, k, wh, xt, yt in layers:
+                assert queue_fn(k, yt.data_ptr(), wh.ctypes.data, xt.data_ptr(), xt.stride(0), nr, 1, wh.strides[0], 1) == 0
+            assert L.tcrv_cuda_host_sync() == 0
+            for j, (nr, k, wh, xt, yt) in enumerate(layers):
+                ref = cuda.empty((nr, 1), dtype=cuda.float32)
+                assert block_fn(k, ref.data_ptr(), wh.ctypes.data, xt.data_ptr(), xt.stride(0), nr, 1, wh.strides[0], 1) == 0
+                assert np.array_equal(yt.numpy().view(np.uint32), ref.numpy().view(np.uint32)), (rnd, j)
+                if order == 0:  # the entries' default: the reference's ascending block order, bit for bit
+                    want = O.gemm(wh, xt.numpy(), q8_weights=q8w, fold=O.FOLD_FMA, threads=8)
+                    assert np.array_equal(yt.numpy().view(np.uint32), want.view(np.uint32)), (rnd, j)
+    finally:
+        for layer in layers:
+            L.tcrv_cuda_host_unregister_weights(layer[2].ctypes.data)
+        L.tcrv_cuda_host_release()
+        L.tcrv_cuda_host_set_fold_order(previous)
+
+
 def test_a_sequence_whose_call_reads_an_earlier_calls_output_keeps_call_order(cuda, pkg, O):
     # Call B's activations lie in the buffer call A writes its result to.  Fetching all inputs at
     # the start of a captured sequence would hand B the bytes from before A ran, so such a run

@@ -402,6 +402,112 @@ int launch_mma_strict(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, 
   return TCRV_CUDA_OK;
 }
 
+// A launch of the streaming kernel: its arguments, shared memory and grid.
+struct StreamPlan {
+  GemvArgs args;
+  size_t smem;
+  int grid;
+};
+
+template <bool kQ8W>
+void fill_stream_args(GemvArgs &args, uint32_t nb, float *s, const uint8_t *vx, const uint8_t *vy, size_t by, size_t nr,
+                      size_t bx, size_t bs, unsigned flags, size_t rps, size_t nwarps, size_t spw, size_t table) {
+  const size_t row_bytes = static_cast<size_t>(nb) * WeightFormat<kQ8W>::kBlockBytes;
+  args.vx = vx;
+  args.vy = vy;
+  args.s = s;
+  args.bx = bx;
+  args.by = by;
+  args.bs = bs;
+  args.nr = static_cast<uint32_t>(nr);
+  args.nb = nb;
+  args.row_bytes = static_cast<uint32_t>(row_bytes);
+  args.nwarps = static_cast<uint32_t>(nwarps);
+  args.slots = static_cast<uint32_t>(spw);
+  args.contiguous = (bx == row_bytes) ? 1u : 0u;
+  args.rps = static_cast<uint32_t>(rps);
+  args.static_weights = (flags & TCRV_CUDA_FLAG_STATIC_WEIGHTS) ? 1u : 0u;
+  // One copy in flight per warp (see the kernel's header); flags bits 16..19 set another
+  // window, up to the ring depth (tuning).
+  args.window = 1;
+  if (const unsigned wf = (flags >> 16) & 0xfu)
+    args.window = wf < spw ? wf : static_cast<uint32_t>(spw);
+  args.table_bytes = static_cast<uint32_t>(table);
+}
+
+// The reference's order on the streaming kernel with a term table per warp (1..3 columns).
+template <bool kQ8W>
+bool plan_stream_strict(uint32_t nb, float *s, const uint8_t *vx, const uint8_t *vy, size_t by, size_t nr, size_t nc,
+                        size_t bx, size_t bs, unsigned flags, StreamPlan &plan) {
+  const size_t row_bytes = static_cast<size_t>(nb) * WeightFormat<kQ8W>::kBlockBytes;
+  const size_t fixed = kGemvBarrierBytes + nc * static_cast<size_t>(gemv_xcol_bytes(nb));
+  // rows per slot (= chains folded side by side), measured: 4 up to 4 KB rows, 3 up to 4.5 KB
+  // (Q8_0 weights with K = 4096, Q4_0 with K = 8192), 2 beyond; flags bits 8..11 override (tuning)
+  size_t rps = nc > 1 ? 2 : (row_bytes <= 4096 ? 4 : (row_bytes <= 4608 ? 3 : 2));
+  const unsigned forced = (flags >> 8) & 0xfu;
+  if (forced >= 1 && forced <= (nc > 1 ? 2u : 4u))
+    rps = forced;
+  const uint32_t cols = static_cast<uint32_t>(nc);
+  auto per_warp = [&](size_t rows) {
+    return 2 * rows * row_bytes + gemv_strict_table_bytes(nb, static_cast<uint32_t>(rows), kQ8W, cols);
+  };
+  while (rps > 1 && fixed + per_warp(rps) > kMaxDynamicSmem)
+    --rps;
+  if (fixed + per_warp(rps) > kMaxDynamicSmem)
+    return false;
+  const size_t slot = rps * row_bytes, table = gemv_strict_table_bytes(nb, static_cast<uint32_t>(rps), kQ8W, cols);
+  size_t nwarps = (kMaxDynamicSmem - fixed) / per_warp(rps);
+  nwarps = nwarps > kGemvMaxConsumerWarps ? kGemvMaxConsumerWarps : nwarps;
+  size_t spw = ((kMaxDynamicSmem - fixed) / nwarps - table) / slot;
+  spw = spw > kGemvMaxSlotsPerWarp ? kGemvMaxSlotsPerWarp : spw;
+  fill_stream_args<kQ8W>(plan.args, nb, s, vx, vy, by, nr, bx, bs, flags, rps, nwarps, spw, table);
+  const size_t nslots = (nr + rps - 1) / rps;
+  const int sms = sm_count();
+  plan.grid = static_cast<int>(nslots < static_cast<size_t>(sms) ? nslots : sms);
+  plan.smem = fixed + nwarps * (spw * slot + table);
+  return true;
+}
+
+// The kernel's own order (lane pairs) on the streaming kernel, 1..8 columns.
+template <bool kQ8W>
+bool plan_stream_fast(uint32_t nb, float *s, const uint8_t *vx, const uint8_t *vy, size_t by, size_t nr, size_t nc,
+                      size_t bx, size_t bs, unsigned flags, StreamPlan &plan) {
+  const size_t row_bytes = static_cast<size_t>(nb) * WeightFormat<kQ8W>::kBlockBytes;
+  const size_t fixed = kGemvBarrierBytes + nc * static_cast<size_t>(gemv_xcol_bytes(nb));
+  // Rows per slot: a warp folds all rows of a slot together, and more independent rows per
+  // warp hide more latency (the kernel is issue/latency-bound); measured best is 4 rows for
+  // rows up to 4 KB and 2 rows beyond (registers), 2 rows with several activation columns.
+  // flags bits 8..11 override the choice (tuning).
+  size_t rps = nc == 1 ? (row_bytes <= 4096 ? 4 : 2) : 2;
+  const unsigned forced = (flags >> 8) & 0xfu;
+  if (forced == 1 || forced == 2 || (forced == 4 && nc == 1))
+    rps = forced;
+  const size_t smem_cap = kMaxDynamicSmem;
+  const size_t warp_cap = kGemvMaxConsumerWarps;
+  while (rps > 1 && fixed + 2 * rps * row_bytes > smem_cap)
+    rps /= 2;
+  const size_t slot = rps * row_bytes;
+  if (fixed + 2 * slot > smem_cap)
+    return false;
+  const size_t total_slots = (smem_cap - fixed) / slot;
+  size_t nwarps, spw;
+  if (total_slots >= 2 * warp_cap) {
+    nwarps = warp_cap;
+    spw = total_slots / nwarps;
+    if (spw > kGemvMaxSlotsPerWarp)
+      spw = kGemvMaxSlotsPerWarp;
+  } else {
+    nwarps = total_slots / 2;
+    spw = 2;
+  }
+  fill_stream_args<kQ8W>(plan.args, nb, s, vx, vy, by, nr, bx, bs, flags, rps, nwarps, spw, 0);
+  const size_t nslots = (nr + rps - 1) / rps;
+  const int sms = sm_count();
+  plan.grid = static_cast<int>(nslots < static_cast<size_t>(sms) ? nslots : sms);
+  plan.smem = fixed + nwarps * spw * slot;
+  return true;
+}
+
 }  // namespace
 
 // 0 = strict ascending, 1 = lane pairs + butterfly, 2 = 16-way K split (see tcrv_cuda.h).
@@ -425,10 +531,8 @@ int launch_gemv(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t
                 size_t bx, size_t bs, unsigned flags, cudaStream_t stream) {
   if (nr == 0 || nc == 0)
     return TCRV_CUDA_OK;
-  constexpr int WB = WeightFormat<kQ8W>::kBlockBytes;
   const uint32_t nb = static_cast<uint32_t>(n / kQK);
   const bool strict = (flags & TCRV_CUDA_FLAG_STRICT_ORDER) != 0;
-  const size_t row_bytes = static_cast<size_t>(nb) * WB;
 
   const bool bulk = nb > 0 && nb % 8 == 0 && nc <= kGemvMaxCols && multiple_of(vx, 16) && bx % 16 == 0 &&
                     multiple_of(vy, 2) && by % 2 == 0;
@@ -440,49 +544,9 @@ int launch_gemv(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t
       nc <= kStrictWarpTableCols ||
       (nc == 3 && ((flags & 0x4000u) != 0 || (!kQ8W && mma_strict_ring<kQ8W>(nb, nr, nc, vx, bx) == 0)));
   if (strict && bulk && warp_tables && (flags & 0x2000u) == 0) {
-    const size_t fixed = kGemvBarrierBytes + nc * static_cast<size_t>(gemv_xcol_bytes(nb));
-    // rows per slot (= chains folded side by side), measured: 4 up to 4 KB rows, 3 up to 4.5 KB
-    // (Q8_0 weights with K = 4096, Q4_0 with K = 8192), 2 beyond; flags bits 8..11 override (tuning)
-    size_t rps = nc > 1 ? 2 : (row_bytes <= 4096 ? 4 : (row_bytes <= 4608 ? 3 : 2));
-    const unsigned forced = (flags >> 8) & 0xfu;
-    if (forced >= 1 && forced <= (nc > 1 ? 2u : 4u))
-      rps = forced;
-    const uint32_t cols = static_cast<uint32_t>(nc);
-    auto per_warp = [&](size_t rows) {
-      return 2 * rows * row_bytes + gemv_strict_table_bytes(nb, static_cast<uint32_t>(rows), kQ8W, cols);
-    };
-    while (rps > 1 && fixed + per_warp(rps) > kMaxDynamicSmem)
-      --rps;
-    if (fixed + per_warp(rps) <= kMaxDynamicSmem) {
-      const size_t slot = rps * row_bytes, table = gemv_strict_table_bytes(nb, static_cast<uint32_t>(rps), kQ8W, cols);
-      size_t nwarps = (kMaxDynamicSmem - fixed) / per_warp(rps);
-      nwarps = nwarps > kGemvMaxConsumerWarps ? kGemvMaxConsumerWarps : nwarps;
-      size_t spw = ((kMaxDynamicSmem - fixed) / nwarps - table) / slot;
-      spw = spw > kGemvMaxSlotsPerWarp ? kGemvMaxSlotsPerWarp : spw;
-      GemvArgs args;
-      args.vx = vx;
-      args.vy = vy;
-      args.s = s;
-      args.bx = bx;
-      args.by = by;
-      args.bs = bs;
-      args.nr = static_cast<uint32_t>(nr);
-      args.nb = nb;
-      args.row_bytes = static_cast<uint32_t>(row_bytes);
-      args.nwarps = static_cast<uint32_t>(nwarps);
-      args.slots = static_cast<uint32_t>(spw);
-      args.contiguous = (bx == row_bytes) ? 1u : 0u;
-      args.rps = static_cast<uint32_t>(rps);
-      args.static_weights = (flags & TCRV_CUDA_FLAG_STATIC_WEIGHTS) ? 1u : 0u;
-      args.window = 1;
-      if (const unsigned wf = (flags >> 16) & 0xfu)
-        args.window = wf < spw ? wf : static_cast<uint32_t>(spw);
-      args.table_bytes = static_cast<uint32_t>(table);
-      const size_t nslots = (nr + rps - 1) / rps;
-      const int sms = sm_count();
-      const int grid = static_cast<int>(nslots < static_cast<size_t>(sms) ? nslots : sms);
-      return launch_stream<kQ8W>(args, cols, grid, fixed + nwarps * (spw * slot + table), stream);
-    }
+    StreamPlan plan;
+    if (plan_stream_strict<kQ8W>(nb, s, vx, vy, by, nr, nc, bx, bs, flags, plan))
+      return launch_stream<kQ8W>(plan.args, static_cast<uint32_t>(nc), plan.grid, plan.smem, stream);
   }
 
   if (!strict && bulk) {
@@ -496,61 +560,9 @@ int launch_gemv(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t
       if (slot_groups > 0)
         return launch_mma<kQ8W>(n, s, vx, vy, by, nr, nc, bx, bs, flags, slot_groups, stream);
     }
-    const size_t fixed = kGemvBarrierBytes + nc * static_cast<size_t>(gemv_xcol_bytes(nb));
-    // Rows per slot: a warp folds all rows of a slot together, and more independent rows per
-    // warp hide more latency (the kernel is issue/latency-bound); measured best is 4 rows for
-    // rows up to 4 KB and 2 rows beyond (registers), 2 rows with several activation columns.
-    // flags bits 8..11 override the choice (tuning).
-    const int sms = sm_count();
-    size_t rps = nc == 1 ? (row_bytes <= 4096 ? 4 : 2) : 2;
-    const unsigned forced = (flags >> 8) & 0xfu;
-    if (forced == 1 || forced == 2 || (forced == 4 && nc == 1))
-      rps = forced;
-    const size_t smem_cap = kMaxDynamicSmem;
-    const size_t warp_cap = kGemvMaxConsumerWarps;
-    while (rps > 1 && fixed + 2 * rps * row_bytes > smem_cap)
-      rps /= 2;
-    const size_t slot = rps * row_bytes;
-    if (fixed + 2 * slot <= smem_cap) {
-      const size_t total_slots = (smem_cap - fixed) / slot;
-      size_t nwarps, spw;
-      if (total_slots >= 2 * warp_cap) {
-        nwarps = warp_cap;
-        spw = total_slots / nwarps;
-        if (spw > kGemvMaxSlotsPerWarp)
-          spw = kGemvMaxSlotsPerWarp;
-      } else {
-        nwarps = total_slots / 2;
-        spw = 2;
-      }
-      GemvArgs args;
-      args.vx = vx;
-      args.vy = vy;
-      args.s = s;
-      args.bx = bx;
-      args.by = by;
-      args.bs = bs;
-      args.nr = static_cast<uint32_t>(nr);
-      args.nb = nb;
-      args.row_bytes = static_cast<uint32_t>(row_bytes);
-      args.nwarps = static_cast<uint32_t>(nwarps);
-      args.slots = static_cast<uint32_t>(spw);
-      args.contiguous = (bx == row_bytes) ? 1u : 0u;
-      args.rps = static_cast<uint32_t>(rps);
-      args.static_weights = (flags & TCRV_CUDA_FLAG_STATIC_WEIGHTS) ? 1u : 0u;
-      // One copy in flight per warp (see the kernel's header); flags bits 16..19 set another
-      // window, up to the ring depth (tuning).
-      args.window = 1;
-      {
-        const unsigned wf = (flags >> 16) & 0xfu;
-        if (wf >= 1)
-          args.window = wf < spw ? wf : static_cast<uint32_t>(spw);
-      }
-      args.table_bytes = 0;
-      const size_t nslots = (nr + rps - 1) / rps;
-      const int grid = static_cast<int>(nslots < static_cast<size_t>(sms) ? nslots : sms);
-      return launch_stream<kQ8W>(args, static_cast<uint32_t>(nc), grid, fixed + nwarps * spw * slot, stream);
-    }
+    StreamPlan plan;
+    if (plan_stream_fast<kQ8W>(nb, s, vx, vy, by, nr, nc, bx, bs, flags, plan))
+      return launch_stream<kQ8W>(plan.args, static_cast<uint32_t>(nc), plan.grid, plan.smem, stream);
   }
 
   // the reference's strict order at streaming speed for what the per-warp tables above do not
@@ -585,6 +597,115 @@ template int launch_gemv<false>(size_t, float *, const uint8_t *, const uint8_t 
                                 size_t, unsigned, cudaStream_t);
 template int launch_gemv<true>(size_t, float *, const uint8_t *, const uint8_t *, size_t, size_t, size_t, size_t,
                                size_t, unsigned, cudaStream_t);
+
+namespace {
+
+template <bool kQ8W>
+int launch_gemv_group_impl(const GemvGroupItem *items, size_t count, cudaStream_t stream) {
+  if (count < 2 || count > static_cast<size_t>(kGemvGroupMax))
+    return TCRV_CUDA_ERR_UNSUPPORTED;
+  const bool strict = (items[0].flags & TCRV_CUDA_FLAG_STRICT_ORDER) != 0;
+  constexpr unsigned kKnownFlags = TCRV_CUDA_FLAG_STRICT_ORDER | TCRV_CUDA_FLAG_STATIC_WEIGHTS;
+  GemvGroupArgs group = {};
+  group.count = static_cast<uint32_t>(count);
+  size_t smem = 0;
+  double cost[kGemvGroupMax], all_cost = 0.0;
+  uint32_t warps = 0;
+  int cap[kGemvGroupMax];
+  for (size_t i = 0; i < count; ++i) {
+    const GemvGroupItem &it = items[i];
+    const uint32_t nb = static_cast<uint32_t>(it.n / kQK);
+    // one column each, no tuning bits, the same order for all, operands the bulk copies accept
+    if (it.nc != 1 || it.nr == 0 || (it.flags & ~kKnownFlags) != 0 ||
+        ((it.flags & TCRV_CUDA_FLAG_STRICT_ORDER) != 0) != strict || it.n % kQK != 0 || nb == 0 || nb % 8 != 0 ||
+        !multiple_of(it.vx, 16) || it.bx % 16 != 0 || !multiple_of(it.vy, 2) || it.by % 2 != 0)
+      return TCRV_CUDA_ERR_UNSUPPORTED;
+    StreamPlan plan;
+    const bool ok = strict ? plan_stream_strict<kQ8W>(nb, it.s, it.vx, it.vy, it.by, it.nr, 1, it.bx, it.bs, it.flags, plan)
+                           : plan_stream_fast<kQ8W>(nb, it.s, it.vx, it.vy, it.by, it.nr, 1, it.bx, it.bs, it.flags, plan);
+    if (!ok)
+      return TCRV_CUDA_ERR_UNSUPPORTED;
+    group.problem[i] = plan.args;
+    cap[i] = plan.grid;
+    smem = plan.smem > smem ? plan.smem : smem;
+    warps = plan.args.nwarps > warps ? plan.args.nwarps : warps;
+    // What a problem costs an SM: its weight bytes, and more per byte where rows longer than
+    // 4.5 KB leave a CTA fewer warps and rows per slot (measured per-SM rates on 32000 x 4096
+    // against 4096 x 11008: 39 : 35 GB/s in the kernel's own order, 36 : 22 in the reference's).
+    const double per_byte = plan.args.row_bytes > 4608 ? (strict ? 1.5 : 1.1) : 1.0;
+    cost[i] = static_cast<double>(it.nr) * plan.args.row_bytes * per_byte;
+    all_cost += cost[i];
+  }
+  // One CTA per SM in all, dealt in proportion to that cost (every problem at least one, none
+  // more than it has slots of rows), so that all problems end at about the same time.
+  const uint32_t sms = static_cast<uint32_t>(sm_count());
+  if (count > sms)
+    return TCRV_CUDA_ERR_UNSUPPORTED;
+  uint32_t share[kGemvGroupMax], dealt = 0;
+  for (size_t i = 0; i < count; ++i) {
+    uint32_t want = static_cast<uint32_t>(cost[i] / all_cost * sms);
+    want = want < 1 ? 1 : want;
+    share[i] = want > static_cast<uint32_t>(cap[i]) ? static_cast<uint32_t>(cap[i]) : want;
+    dealt += share[i];
+  }
+  // rounding left SMs over (or took too many): give to the problem whose CTAs carry the most,
+  // take from the one whose CTAs would carry the least afterwards
+  while (dealt != sms) {
+    size_t pick = count;
+    double best = 0.0;
+    for (size_t i = 0; i < count; ++i) {
+      if (dealt < sms ? share[i] >= static_cast<uint32_t>(cap[i]) : share[i] <= 1)
+        continue;
+      const double load = dealt < sms ? cost[i] / share[i] : -cost[i] / (share[i] - 1);
+      if (pick == count || load > best) {
+        pick = i;
+        best = load;
+      }
+    }
+    if (pick == count)
+      break;  // every problem is at its cap: fewer CTAs than SMs
+    if (dealt < sms) {
+      ++share[pick];
+      ++dealt;
+    } else {
+      --share[pick];
+      --dealt;
+    }
+  }
+  group.first[0] = 0;
+  for (size_t i = 0; i < count; ++i)
+    group.first[i + 1] = group.first[i] + share[i];
+
+  auto kernel = strict ? gemv_stream_group_kernel<kQ8W, true> : gemv_stream_group_kernel<kQ8W, false>;
+  static std::atomic<bool> configured[64][2];
+  int dev = 0;
+  TCRV_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev >= 0 && dev < 64 && !configured[dev][strict ? 1 : 0]) {
+    TCRV_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(kMaxDynamicSmem)));
+    configured[dev][strict ? 1 : 0] = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(group.first[count]);
+  cfg.blockDim = dim3(warps * 32);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  TCRV_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, group));
+  TCRV_CUDA_TRY(cudaGetLastError());
+  return TCRV_CUDA_OK;
+}
+
+}  // namespace
+
+int launch_gemv_group(bool q8_weights, const GemvGroupItem *items, size_t count, cudaStream_t stream) {
+  return q8_weights ? launch_gemv_group_impl<true>(items, count, stream)
+                    : launch_gemv_group_impl<false>(items, count, stream);
+}
 
 template <bool kQ8W>
 int launch_block_sums(size_t n, int32_t *sumi, const uint8_t *vx, const uint8_t *vy, size_t by, size_t nr,

@@ -306,10 +306,12 @@ __device__ __forceinline__ void gemv_rows(const GemvArgs &a, const uint32_t *wro
 
 // kCols: activation columns (1..8).  kXRegPairs: when > 0 (single column only) the lane keeps
 // its activation pairs in registers for the whole kernel; requires npairs <= 32*kXRegPairs.
-template <bool kQ8W, int kCols, int kXRegPairs, bool kStrict = false>
-__global__ void __launch_bounds__(kGemvMaxThreads, 1) gemv_stream_kernel(const GemvArgs a) {
+// The kernel's body for CTA `cta` of the `nctas` that share the problem `a` (the whole grid for
+// the single-problem kernel, a share of it for the grouped one).  The block may have more
+// warps than a.nwarps: the spare ones only meet the others at the one block-wide barrier.
+template <bool kQ8W, int kCols, int kXRegPairs, bool kStrict>
+__device__ __forceinline__ void gemv_stream_body(const GemvArgs &a, uint32_t cta, uint32_t nctas, uint8_t *smem) {
   static_assert(!kStrict || kCols <= 3, "the strict order of this kernel is built for up to 3 columns");
-  extern __shared__ __align__(128) uint8_t smem[];
   uint64_t *full = reinterpret_cast<uint64_t *>(smem);
   uint8_t *xsm = smem + kGemvBarrierBytes;
   const uint32_t nb = a.nb, npairs = nb / 2;
@@ -319,15 +321,15 @@ __global__ void __launch_bounds__(kGemvMaxThreads, 1) gemv_stream_kernel(const G
   const uint32_t rps = a.rps;
   const uint32_t slot_bytes = rps * a.row_bytes;
   const uint32_t nwarps = a.nwarps, spw = a.slots;
-  const uint32_t nthreads = nwarps * 32;
 
   const uint32_t warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   // Contiguous, balanced row range of this CTA, split again into contiguous, balanced ranges
   // per warp (they differ by at most one row, so no warp does a whole slot more than the
   // others).  A warp walks its n rows in k = ceil(n / rps) slots of n/k or n/k + 1 rows.
-  const uint32_t r0 = static_cast<uint32_t>(static_cast<uint64_t>(a.nr) * blockIdx.x / gridDim.x);
-  const uint32_t r1 = static_cast<uint32_t>(static_cast<uint64_t>(a.nr) * (blockIdx.x + 1) / gridDim.x);
+  const bool spare = warp >= nwarps;  // a warp of a wider block than this problem uses
+  const uint32_t r0 = static_cast<uint32_t>(static_cast<uint64_t>(a.nr) * cta / nctas);
+  const uint32_t r1 = static_cast<uint32_t>(static_cast<uint64_t>(a.nr) * (cta + 1) / nctas);
   const uint32_t w0 = r0 + (r1 - r0) * warp / nwarps;
   const uint32_t wrows = r0 + (r1 - r0) * (warp + 1) / nwarps - w0;
   const uint32_t mine = (wrows + rps - 1) / rps;  // slots of this warp
@@ -359,7 +361,7 @@ __global__ void __launch_bounds__(kGemvMaxThreads, 1) gemv_stream_kernel(const G
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (!a.static_weights)
     asm volatile("griddepcontrol.wait;" ::: "memory");
-  if (lane == 0) {
+  if (lane == 0 && !spare) {
     for (uint32_t i = 0; i < spw; ++i)
       mbar_init(&full[warp * spw + i], 1);
     mbar_fence_init();
@@ -370,7 +372,7 @@ __global__ void __launch_bounds__(kGemvMaxThreads, 1) gemv_stream_kernel(const G
   if (a.static_weights)
     asm volatile("griddepcontrol.wait;" ::: "memory");
   // Convert the activation columns (plain block_q8_0, 2-byte aligned) into the lane layout.
-  for (uint32_t idx = threadIdx.x; idx < kCols * nb; idx += nthreads) {
+  for (uint32_t idx = threadIdx.x; idx < kCols * nb; idx += blockDim.x) {
     const uint32_t col = idx / nb, ib = idx - col * nb;
     const uint8_t *src = a.vy + col * a.by + static_cast<size_t>(ib) * kQ8Block;
     const unsigned short *h = reinterpret_cast<const unsigned short *>(src);
@@ -387,6 +389,8 @@ __global__ void __launch_bounds__(kGemvMaxThreads, 1) gemv_stream_kernel(const G
     reinterpret_cast<int *>(xcol + npairs * 64u + nb * 4u)[ib] = 8 * sum_s8x32(q);
   }
   __syncthreads();
+  if (spare)
+    return;
 
   XBlockPair xr[kXRegPairs > 0 ? kXRegPairs : 1];
   if constexpr (kXRegPairs > 0) {
@@ -474,6 +478,38 @@ __global__ void __launch_bounds__(kGemvMaxThreads, 1) gemv_stream_kernel(const G
     if (static_cast<uint32_t>(lane) < kept)
       a.s[static_cast<size_t>(kept_row + lane) * a.bs] = keep;
   }
+}
+
+template <bool kQ8W, int kCols, int kXRegPairs, bool kStrict = false>
+__global__ void __launch_bounds__(kGemvMaxThreads, 1) gemv_stream_kernel(const GemvArgs a) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  gemv_stream_body<kQ8W, kCols, kXRegPairs, kStrict>(a, blockIdx.x, gridDim.x, smem);
+}
+
+// Several independent one-column problems in ONE launch: CTAs first[i] .. first[i+1]-1 work on
+// problem i exactly as the single-problem kernel's grid would (same rows per warp rule, same
+// fp32 order, so the same bits), and all problems stream at the same time.  For callers that
+// have a batch of GEMVs with no dependencies among them (a replayed run of queued decode calls):
+// one prologue and one tail instead of one per problem.
+constexpr int kGemvGroupMax = 16;
+struct GemvGroupArgs {
+  GemvArgs problem[kGemvGroupMax];
+  uint32_t first[kGemvGroupMax + 1];  // first CTA of every problem; first[count] = grid size
+  uint32_t count;
+};
+
+template <bool kQ8W, bool kStrict>
+__global__ void __launch_bounds__(kGemvMaxThreads, 1) gemv_stream_group_kernel(const __grid_constant__ GemvGroupArgs g) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  uint32_t i = 0;
+  while (i + 1 < g.count && blockIdx.x >= g.first[i + 1])
+    ++i;
+  const GemvArgs &a = g.problem[i];
+  const uint32_t cta = blockIdx.x - g.first[i], nctas = g.first[i + 1] - g.first[i];
+  if (a.nb / 2 <= 64)
+    gemv_stream_body<kQ8W, 1, 2, kStrict>(a, cta, nctas, smem);
+  else
+    gemv_stream_body<kQ8W, 1, 0, kStrict>(a, cta, nctas, smem);
 }
 
 }  // namespace tcrv

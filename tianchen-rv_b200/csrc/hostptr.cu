@@ -695,7 +695,10 @@ cudaGraphExec_t capture_sequence(HostContext &c, const std::vector<ReplayKey> &k
   bool ok = true;
   fetch_rows_multi_kernel<<<static_cast<unsigned>(count), 512, 0, c.stream>>>(list);
   ok = cudaGetLastError() == cudaSuccess;
-  for (size_t i = 0; i < count && ok; ++i) {
+  // where every call's result goes: single-column results straight into the caller's buffer
+  std::vector<GemvGroupItem> launches(count);
+  bool one_format = true;
+  for (size_t i = 0; i < count; ++i) {
     const ReplayKey &k = keys[i];
     float *out = items[i].ds;
     size_t out_bs = k.nc;
@@ -709,12 +712,25 @@ cudaGraphExec_t capture_sequence(HostContext &c, const std::vector<ReplayKey> &k
         (void)cudaGetLastError();
       }
     }
-    const unsigned lf = k.flags | TCRV_CUDA_FLAG_STATIC_WEIGHTS;
-    const uint8_t *vy = items[i].dx;
-    const int st = k.q8 ? launch_gemv<true>(k.n, out, items[i].res->dev, vy, items[i].xrow, k.nr, k.nc, k.bx, out_bs, lf,
-                                            c.stream)
-                        : launch_gemv<false>(k.n, out, items[i].res->dev, vy, items[i].xrow, k.nr, k.nc, k.bx, out_bs,
-                                             lf, c.stream);
+    launches[i] = GemvGroupItem{k.n, out, items[i].res->dev, items[i].dx, items[i].xrow, k.nr, k.nc, k.bx, out_bs,
+                                k.flags | TCRV_CUDA_FLAG_STATIC_WEIGHTS};
+    one_format = one_format && k.q8 == keys[0].q8;
+  }
+  // The calls of a sequence do not depend on one another (checked above), so one-column calls of
+  // one weight format run as a single grouped launch: all of them stream at the same time and
+  // there is one prologue and one tail instead of one per call.  Anything else: one launch each.
+  bool grouped = false;
+  if (one_format) {
+    const int st = launch_gemv_group(keys[0].q8, launches.data(), count, c.stream);
+    grouped = st == TCRV_CUDA_OK;
+    ok = grouped || st == TCRV_CUDA_ERR_UNSUPPORTED;
+    if (!grouped)
+      (void)cudaGetLastError();
+  }
+  for (size_t i = 0; i < count && ok && !grouped; ++i) {
+    const GemvGroupItem &g = launches[i];
+    const int st = keys[i].q8 ? launch_gemv<true>(g.n, g.s, g.vx, g.vy, g.by, g.nr, g.nc, g.bx, g.bs, g.flags, c.stream)
+                              : launch_gemv<false>(g.n, g.s, g.vx, g.vy, g.by, g.nr, g.nc, g.bx, g.bs, g.flags, c.stream);
     ok = st == TCRV_CUDA_OK;
   }
   for (size_t i = 0; i < count && ok; ++i) {

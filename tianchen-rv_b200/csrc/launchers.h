@@ -44,6 +44,19 @@ int launch_quantize_row_q4_0(size_t n, const float *x, uint8_t *vx, cudaStream_t
 template <bool kQ8W>
 int launch_gemv(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by, size_t nr, size_t nc,
                 size_t bx, size_t bs, unsigned flags, cudaStream_t stream);
+// Several independent one-column GEMVs (the arguments of launch_gemv each) in ONE launch of the
+// streaming kernel: same weight format, same fold-order flag, no tuning bits; every output has
+// the bits launch_gemv gives.  TCRV_CUDA_ERR_UNSUPPORTED when the group does not qualify (the
+// caller then launches them one by one).
+struct GemvGroupItem {
+  size_t n;
+  float *s;
+  const uint8_t *vx;
+  const uint8_t *vy;
+  size_t by, nr, nc, bx, bs;
+  unsigned flags;
+};
+int launch_gemv_group(bool q8_weights, const GemvGroupItem *items, size_t count, cudaStream_t stream);
 template <bool kQ8W>
 int gemv_fold_order(size_t n, size_t nc, const void *vx, size_t bx, const void *vy, size_t by, unsigned flags);
 template <bool kQ8W>
