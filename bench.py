@@ -331,6 +331,7 @@ def run_ours(args):
         per_shape.append({"shape": f"{l['nr']}x{l['k']}", "us": round(us, 3), "gbs": round(l["bytes"] / us / 1e3, 1)})
 
     batch8 = measure_batch8(pkg, torch, layers, side, gen)
+    grouped = measure_grouped(pkg, torch, layers, side)
     e2e = measure_e2e(pkg, torch, layers, max(10, min(args.steps, 50)), dist)
     try:
         others = measure_other_kernels(pkg, torch) if (rank == 0 and not args.skip_gemm) else None
@@ -372,6 +373,14 @@ def run_ours(args):
                    "frac": round(b8_bytes / batch8["pass_us"] / 1e3 / peaks["hbm_gbs"], 4),
                    "per_shape": batch8["per_shape"],
                    "largest_shape_frac": round(batch8["per_shape"][-1]["gbs"] / peaks["hbm_gbs"], 4)},
+        "grouped_step": {"kernel": "gemv_stream_group_kernel<q4_0>: the step's four GEMVs as one launch "
+                                   "(tcrv_cuda_gemv_group_q4_0_q8_0), batch 1",
+                         "note": "not the headline: valid where the GEMVs do not depend on one another "
+                                 "(shared-input projections, experts, the queued host calls of a replayed step)",
+                         "us": grouped["own_order"], "gbs": round(step_bytes / grouped["own_order"] / 1e3, 1),
+                         "frac": round(step_bytes / grouped["own_order"] / 1e3 / peaks["hbm_gbs"], 4),
+                         "reference_order_us": grouped["reference_order"],
+                         "reference_order_frac": round(step_bytes / grouped["reference_order"] / 1e3 / peaks["hbm_gbs"], 4)},
         # prefill GEMM (the metric's second half): int8 TOP/s of the N-sharded GEMM on this many GPUs
         "gemm": gemm_summary(gemm),
     }
@@ -463,6 +472,41 @@ def measure_batch8(pkg, torch, layers, side, gen):
                           "gbs": round(gemv_bytes(l["nr"], l["k"], 8) / us / 1e3, 1)})
     pkg.check_device_errors()
     return {"pass_us": round(pass_us, 3), "per_shape": per_shape}
+
+
+def measure_grouped(pkg, torch, layers, side):
+    """The four layer shapes (batch 1) as ONE grouped launch per step (`tcrv_cuda_gemv_group_q4_0_q8_0`:
+    the SMs dealt out among the four problems, all streaming at once) over the same rotating weight
+    copies, in the kernel's own order and in the reference's.  Not the headline: the layers of a
+    model depend on one another; this is what callers with independent GEMVs (projections that
+    share an input, experts, the queued host calls of a replayed step) get."""
+    out = {}
+    for name, flags in (("own_order", pkg.FLAG_STATIC_WEIGHTS), ("reference_order", pkg.FLAG_STATIC_WEIGHTS | pkg.FLAG_STRICT_ORDER)):
+        groups = [pkg.gemv_group_calls([(l["w"][r], l["x"], l["y"]) for l in layers]) for r in range(ROTATION_SETS)]
+
+        def whole():
+            for calls in groups:
+                pkg.gemv_group(calls, flags=flags)
+
+        with torch.cuda.stream(side):
+            whole()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            whole()
+        for _ in range(3):
+            g.replay()
+        torch.cuda.synchronize()
+        reps = 10
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            g.replay()
+        b.record()
+        torch.cuda.synchronize()
+        out[name] = round(a.elapsed_time(b) * 1e3 / (reps * ROTATION_SETS), 3)
+    pkg.check_device_errors()
+    return out
 
 
 def measure_e2e(pkg, torch, layers, steps, dist):

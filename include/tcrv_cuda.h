@@ -134,6 +134,25 @@ int tcrv_cuda_gemv_fold_order(int q8_weights, size_t n, size_t nc, const void *v
 int tcrv_cuda_gemv_q4_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by,
                              size_t nr, size_t nc, size_t bx, size_t bs, unsigned flags,
                              tcrv_cuda_stream stream);
+/* Up to 16 GEMVs that do not depend on one another (no call's output is another's input: the
+ * projections that share an input, the experts of a layer) as one request.  Calls with one
+ * activation column whose operands the streaming kernel accepts run as ONE launch in which the
+ * SMs are dealt out among the calls by weight bytes and all of them stream at the same time -
+ * one prologue and one tail instead of one per call; any other group is launched call by call.
+ * Every output has the bits tcrv_cuda_gemv_* gives for that call with the same `flags` (0,
+ * TCRV_CUDA_FLAG_STRICT_ORDER, TCRV_CUDA_FLAG_STATIC_WEIGHTS).  The reference has one entry per
+ * operation and nothing like it; a caller keeps its per-call ABI and gains by batching. */
+typedef struct {
+  size_t n;          /* elements per row, as in tcrv_cuda_gemv_q4_0_q8_0 */
+  float *s;
+  const uint8_t *vx;
+  const uint8_t *vy;
+  size_t by, nr, nc, bx, bs;
+} tcrv_cuda_gemv_call;
+int tcrv_cuda_gemv_group_q4_0_q8_0(const tcrv_cuda_gemv_call *calls, size_t count, unsigned flags,
+                                   tcrv_cuda_stream stream);
+int tcrv_cuda_gemv_group_q8_0_q8_0(const tcrv_cuda_gemv_call *calls, size_t count, unsigned flags,
+                                   tcrv_cuda_stream stream);
 /* The same loop over the Q8_0 x Q8_0 block dot (fold fma((float)sumi, d_x*d_y, sumf)). */
 int tcrv_cuda_gemv_q8_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by,
                              size_t nr, size_t nc, size_t bx, size_t bs, unsigned flags,

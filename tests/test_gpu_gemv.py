@@ -261,3 +261,25 @@ def test_strict_order_streaming_kernels_are_bit_exact(cuda, pkg, O, q8w, nr, k, 
     pkg.check_device_errors()
     res = out.cpu().numpy()
     assert np.array_equal(res[:, :nc].view(np.uint32), want.view(np.uint32)) and np.all(res[:, nc] == -1.0)
+
+
+@pytest.mark.parametrize("q8w", [False, True])
+@pytest.mark.parametrize("strict", [False, True])
+def test_a_group_of_independent_gemvs_has_the_bits_of_the_single_calls(cuda, pkg, O, q8w, strict):
+    # tcrv_cuda_gemv_group_*: one-column calls run as ONE launch with the SMs dealt out among them;
+    # a group with a several-column call is launched call by call.  Either way every output has the
+    # bits of its own tcrv_cuda_gemv_* call.
+    flags = pkg.FLAG_STRICT_ORDER if strict else 0
+    shapes = [(3000, 4096, 1), (700, 11008, 1), (9, 1024, 1), (4096, 2048, 1), (257, 8192, 1)]
+    for variant in (shapes, shapes[:2] + [(500, 4096, 4)]):
+        problems, want = [], []
+        for i, (nr, k, nc) in enumerate(variant):
+            w, x = make(O, nr, k, nc, q8w, 4100 + i)
+            wd, xd = dev(cuda, w), dev(cuda, x)
+            out = cuda.full((nr, nc), float("nan"), dtype=cuda.float32, device="cuda")
+            problems.append((wd, xd, out))
+            want.append(pkg.gemv(wd, xd, q8_weights=q8w, flags=flags).cpu().numpy())
+        pkg.gemv_group(pkg.gemv_group_calls(problems, q8_weights=q8w), q8_weights=q8w, flags=flags)
+        pkg.check_device_errors()
+        for (wd, xd, out), ref in zip(problems, want):
+            assert np.array_equal(out.cpu().numpy().view(np.uint32), ref.view(np.uint32))

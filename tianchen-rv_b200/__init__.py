@@ -45,6 +45,8 @@ ABI = {
     "tcrv_cuda_vec_dot_q8_0_q8_0": [_sz, _p, _p, _p, _p],
     "tcrv_cuda_gemv_q4_0_q8_0": [_sz, _p, _p, _p, _sz, _sz, _sz, _sz, _sz, ctypes.c_uint, _p],
     "tcrv_cuda_gemv_q8_0_q8_0": [_sz, _p, _p, _p, _sz, _sz, _sz, _sz, _sz, ctypes.c_uint, _p],
+    "tcrv_cuda_gemv_group_q4_0_q8_0": [_p, _sz, ctypes.c_uint, _p],
+    "tcrv_cuda_gemv_group_q8_0_q8_0": [_p, _sz, ctypes.c_uint, _p],
     "tcrv_cuda_gemm_weights_bytes": [_sz, _sz],
     "tcrv_cuda_gemm_acts_workspace_bytes": [_sz, _sz],
     "tcrv_cuda_gemm_workspace_bytes": [_sz, _sz, _sz],
@@ -315,6 +317,30 @@ def gemv(w, x, q8_weights: bool = False, flags: int = FLAG_NONE, out=None):
     _check(fn(n, _dev(out, torch.float32), w.data_ptr(), x.data_ptr(), by, nr, nc, bx, out.stride(0), flags, _stream()),
            name)
     return out
+
+
+class GemvCall(ctypes.Structure):
+    """One call of a group: the arguments of tcrv_cuda_gemv_q4_0_q8_0 in ABI order (tcrv_cuda_gemv_call)."""
+
+    _fields_ = [("n", ctypes.c_size_t), ("s", ctypes.c_void_p), ("vx", ctypes.c_void_p), ("vy", ctypes.c_void_p),
+                ("by", ctypes.c_size_t), ("nr", ctypes.c_size_t), ("nc", ctypes.c_size_t), ("bx", ctypes.c_size_t),
+                ("bs", ctypes.c_size_t)]
+
+
+def gemv_group_calls(problems, q8_weights: bool = False):
+    """The ctypes array for `gemv_group`: problems is a sequence of (w, x, out) with out preallocated."""
+    wblock = Q8_0_BLOCK if q8_weights else Q4_0_BLOCK
+    calls = []
+    for w, x, out in problems:
+        n, nr, nc, bx, by, torch = _matrix_args(w, x, wblock)
+        calls.append(GemvCall(n, _dev(out, torch.float32), w.data_ptr(), x.data_ptr(), by, nr, nc, bx, out.stride(0)))
+    return (GemvCall * len(calls))(*calls)
+
+
+def gemv_group(calls, q8_weights: bool = False, flags: int = FLAG_NONE):
+    """Independent GEMVs as one request (tcrv_cuda_gemv_group_*): `calls` from gemv_group_calls."""
+    name = "tcrv_cuda_gemv_group_q8_0_q8_0" if q8_weights else "tcrv_cuda_gemv_group_q4_0_q8_0"
+    _check(getattr(lib(), name)(ctypes.addressof(calls), len(calls), flags, _stream()), name)
 
 
 def gemv_fold_order(w, x, q8_weights: bool = False, flags: int = FLAG_NONE) -> int:

@@ -181,6 +181,46 @@ int tcrv_cuda_gemv_q8_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_
   return launch_gemv<true>(n, s, vx, vy, by, nr, nc, bx, bs, flags, as_stream(stream));
 }
 
+namespace {
+int gemv_group(bool q8_weights, const tcrv_cuda_gemv_call *calls, size_t count, unsigned flags, tcrv_cuda_stream stream) {
+  if (count == 0)
+    return TCRV_CUDA_OK;
+  if (!calls || count > 16)
+    return TCRV_CUDA_ERR_INVALID_ARGUMENT;
+  GemvGroupItem items[16];
+  for (size_t i = 0; i < count; ++i) {
+    const tcrv_cuda_gemv_call &c = calls[i];
+    const int st = check_matrix_args(c.n, c.s, c.vx, c.vy, c.by, c.nr, c.nc, c.bx, c.bs,
+                                     q8_weights ? TCRV_Q8_0_BLOCK_BYTES : TCRV_Q4_0_BLOCK_BYTES);
+    if (st != TCRV_CUDA_OK)
+      return st;
+    items[i] = GemvGroupItem{c.n, c.s, c.vx, c.vy, c.by, c.nr, c.nc, c.bx, c.bs, flags};
+  }
+  const int st = launch_gemv_group(q8_weights, items, count, as_stream(stream));
+  if (st != TCRV_CUDA_ERR_UNSUPPORTED)
+    return st;
+  // not one launch (several columns, tuning bits, operands the bulk copies refuse): one after the other
+  for (size_t i = 0; i < count; ++i) {
+    const GemvGroupItem &g = items[i];
+    const int each = q8_weights ? launch_gemv<true>(g.n, g.s, g.vx, g.vy, g.by, g.nr, g.nc, g.bx, g.bs, g.flags, as_stream(stream))
+                                : launch_gemv<false>(g.n, g.s, g.vx, g.vy, g.by, g.nr, g.nc, g.bx, g.bs, g.flags, as_stream(stream));
+    if (each != TCRV_CUDA_OK)
+      return each;
+  }
+  return TCRV_CUDA_OK;
+}
+}  // namespace
+
+int tcrv_cuda_gemv_group_q4_0_q8_0(const tcrv_cuda_gemv_call *calls, size_t count, unsigned flags,
+                                   tcrv_cuda_stream stream) {
+  return gemv_group(false, calls, count, flags, stream);
+}
+
+int tcrv_cuda_gemv_group_q8_0_q8_0(const tcrv_cuda_gemv_call *calls, size_t count, unsigned flags,
+                                   tcrv_cuda_stream stream) {
+  return gemv_group(true, calls, count, flags, stream);
+}
+
 int tcrv_cuda_gemv_fold_order(int q8_weights, size_t n, size_t nc, const void *vx, size_t bx, const void *vy,
                               size_t by, unsigned flags) {
   return q8_weights ? gemv_fold_order<true>(n, nc, vx, bx, vy, by, flags)
