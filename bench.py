@@ -922,7 +922,7 @@ def measure_gemm(pkg, torch, dist, rank, world):
     return results
 
 
-PROFILE_CASES = ["gemv", "gemv_q8", "gemv_strict", "gemv_strict_cta", "gemm", "dequant", "quantize", "silu", "rms_norm", "repack_gemv", "repack_gemv_q8",
+PROFILE_CASES = ["gemv", "gemv_q8", "gemv_strict", "gemv_strict_cta", "gemv_group", "gemm", "dequant", "quantize", "silu", "rms_norm", "repack_gemv", "repack_gemv_q8",
                  "repack_gemm", "sibling_q4_1", "sibling_q5_0", "sibling_q5_1"]
 
 
@@ -954,6 +954,19 @@ def run_profile_case(args):
         y = torch.empty((rows, args.cols), dtype=torch.float32, device="cuda")
         for i in range(args.launches):
             pkg.gemv(copies[i % len(copies)], x, q8_weights=q8w, out=y, flags=flags)
+    elif args.case == "gemv_group":
+        # the four layer shapes of the decode step as one grouped launch, 3 rotating copies of each
+        problems = []
+        for r in range(3):
+            group = []
+            for nr, k in SHAPES:
+                w = pkg.quantize_q4_0(torch.randn((nr, k), generator=gen, device="cuda") * 0.02)
+                x = pkg.quantize_q8_0(torch.randn((1, k), generator=gen, device="cuda"))
+                group.append((w, x, torch.empty((nr, 1), dtype=torch.float32, device="cuda")))
+            problems.append(group)
+        calls = [pkg.gemv_group_calls(g) for g in problems]
+        for i in range(args.launches):
+            pkg.gemv_group(calls[i % len(calls)], flags=pkg.FLAG_STATIC_WEIGHTS)
     elif args.case in ("repack_gemv", "repack_gemv_q8"):
         # random bytes stand in for the interleaved weights (timing and traffic do not depend on them)
         rows = args.rows or 32000
