@@ -70,3 +70,11 @@ def test_argument_validation_without_gpu(pkg):
     assert L.tcrv_cuda_gemv_q4_0_q8_0(4096, 1, 1, 1, 100, 8, 2, 2304, 2, 0, None) == -1  # by < column bytes
     assert L.tcrv_cuda_gemv_q4_0_q8_0(4096, 1, 1, 1, 4352, 8, 2, 2304, 1, 0, None) == -1  # bs < nc
     assert L.tcrv_cuda_add_f32(None, None, None, 0, None) == 0  # empty input is a no-op
+    # the grouped GEMV entry: an empty group is a no-op, a null list, more than 16 calls and a
+    # call with a bad argument are refused before anything is launched
+    assert L.tcrv_cuda_gemv_group_q4_0_q8_0(None, 0, 0, None) == 0
+    assert L.tcrv_cuda_gemv_group_q4_0_q8_0(None, 2, 0, None) == -1
+    calls = (pkg.GemvCall * 17)(*[pkg.GemvCall(4096, 1, 1, 1, 4352, 8, 1, 2304, 1) for _ in range(17)])
+    assert L.tcrv_cuda_gemv_group_q4_0_q8_0(ctypes.addressof(calls), 17, 0, None) == -1
+    calls[1].n = 4100
+    assert L.tcrv_cuda_gemv_group_q8_0_q8_0(ctypes.addressof(calls), 2, 0, None) == -1

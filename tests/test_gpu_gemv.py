@@ -271,7 +271,7 @@ def test_a_group_of_independent_gemvs_has_the_bits_of_the_single_calls(cuda, pkg
     # bits of its own tcrv_cuda_gemv_* call.
     flags = pkg.FLAG_STRICT_ORDER if strict else 0
     shapes = [(3000, 4096, 1), (700, 11008, 1), (9, 1024, 1), (4096, 2048, 1), (257, 8192, 1)]
-    for variant in (shapes, shapes[:2] + [(500, 4096, 4)]):
+    for variant in (shapes, shapes[:2] + [(500, 4096, 4)], shapes[:1], shapes * 3 + shapes[:1]):  # also 1 and 16 calls
         problems, want = [], []
         for i, (nr, k, nc) in enumerate(variant):
             w, x = make(O, nr, k, nc, q8w, 4100 + i)
