@@ -134,8 +134,8 @@ int tcrv_cuda_gemv_fold_order(int q8_weights, size_t n, size_t nc, const void *v
 int tcrv_cuda_gemv_q4_0_q8_0(size_t n, float *s, const uint8_t *vx, const uint8_t *vy, size_t by,
                              size_t nr, size_t nc, size_t bx, size_t bs, unsigned flags,
                              tcrv_cuda_stream stream);
-/* Up to 16 GEMVs that do not depend on one another (no call's output is another's input: the
- * projections that share an input, the experts of a layer) as one request.  Calls with one
+/* Up to 16 GEMVs that do not depend on one another (no call's output overlaps another call's
+ * input or output: the projections that share an input, the experts of a layer) as one request.  Calls with one
  * activation column whose operands the streaming kernel accepts run as ONE launch in which the
  * SMs are dealt out among the calls by weight bytes and all of them stream at the same time -
  * one prologue and one tail instead of one per call; any other group is launched call by call.

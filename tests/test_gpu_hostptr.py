@@ -476,6 +476,40 @@ def test_a_replayed_step_of_one_column_calls_runs_as_one_grouped_launch(cuda, pk
         L.tcrv_cuda_host_set_fold_order(previous)
 
 
+def test_a_replayed_step_whose_calls_share_an_output_keeps_call_order(cuda, pkg, O):
+    # Two queued one-column calls that write the same floats: the later call's result must stand in
+    # every round, replayed ones included (such a step is not issued as one grouped launch).
+    L = pkg.lib()
+    nr, k = 600, 2048
+    layers = []
+    for i in range(3):
+        wh = np.ascontiguousarray(O.quantize_q4_0(O.fill_normal(nr * k, 9300 + i, 0.0, 0.02).reshape(nr, k)))
+        xt = cuda.empty((1, k // 32 * 34), dtype=cuda.uint8).pin_memory()
+        assert L.tcrv_cuda_host_register_weights(wh.ctypes.data, wh.nbytes) == 0
+        layers.append((wh, xt))
+    shared = cuda.empty((nr, 1), dtype=cuda.float32).pin_memory()
+    own = cuda.empty((nr, 1), dtype=cuda.float32).pin_memory()
+    outs = [shared, own, shared]  # calls 0 and 2 write the same buffer
+    try:
+        for rnd in range(5):
+            for j, (wh, xt) in enumerate(layers):
+                xt.copy_(cuda.from_numpy(O.quantize_q8_0(O.fill_normal(k, 9400 + 10 * rnd + j).reshape(1, k))))
+            shared.fill_(float("nan"))
+            for (wh, xt), yt in zip(layers, outs):
+                assert L.tcrv_cuda_host_gemm_q4_0_q8_0_async(k, yt.data_ptr(), wh.ctypes.data, xt.data_ptr(), xt.stride(0),
+                                                             nr, 1, wh.strides[0], 1) == 0
+            assert L.tcrv_cuda_host_sync() == 0
+            ref = cuda.empty((nr, 1), dtype=cuda.float32)
+            wh, xt = layers[2]
+            assert L.tcrv_cuda_host_gemm_q4_0_q8_0(k, ref.data_ptr(), wh.ctypes.data, xt.data_ptr(), xt.stride(0), nr, 1,
+                                                   wh.strides[0], 1) == 0
+            assert np.array_equal(shared.numpy().view(np.uint32), ref.numpy().view(np.uint32)), rnd
+    finally:
+        for wh, xt in layers:
+            L.tcrv_cuda_host_unregister_weights(wh.ctypes.data)
+        L.tcrv_cuda_host_release()
+
+
 def test_a_sequence_whose_call_reads_an_earlier_calls_output_keeps_call_order(cuda, pkg, O):
     # Call B's activations lie in the buffer call A writes its result to.  Fetching all inputs at
     # the start of a captured sequence would hand B the bytes from before A ran, so such a run

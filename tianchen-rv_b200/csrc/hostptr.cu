@@ -697,7 +697,7 @@ cudaGraphExec_t capture_sequence(HostContext &c, const std::vector<ReplayKey> &k
   ok = cudaGetLastError() == cudaSuccess;
   // where every call's result goes: single-column results straight into the caller's buffer
   std::vector<GemvGroupItem> launches(count);
-  bool one_format = true;
+  bool groupable = true;
   for (size_t i = 0; i < count; ++i) {
     const ReplayKey &k = keys[i];
     float *out = items[i].ds;
@@ -714,13 +714,18 @@ cudaGraphExec_t capture_sequence(HostContext &c, const std::vector<ReplayKey> &k
     }
     launches[i] = GemvGroupItem{k.n, out, items[i].res->dev, items[i].dx, items[i].xrow, k.nr, k.nc, k.bx, out_bs,
                                 k.flags | TCRV_CUDA_FLAG_STATIC_WEIGHTS};
-    one_format = one_format && k.q8 == keys[0].q8;
+    groupable = groupable && k.q8 == keys[0].q8;
+    // two calls that write the same floats must keep their order: no grouped launch for them
+    for (size_t j = 0; j < i; ++j)
+      groupable = groupable && !ranges_overlap(k.s, ((k.nr - 1) * k.bs + k.nc) * sizeof(float), keys[j].s,
+                                                 ((keys[j].nr - 1) * keys[j].bs + keys[j].nc) * sizeof(float));
   }
-  // The calls of a sequence do not depend on one another (checked above), so one-column calls of
-  // one weight format run as a single grouped launch: all of them stream at the same time and
+  // The calls of a sequence do not depend on one another (no call reads what an earlier one
+  // writes, checked above; none writes what another writes), so one-column calls of one weight
+  // format run as a single grouped launch: all of them stream at the same time and
   // there is one prologue and one tail instead of one per call.  Anything else: one launch each.
   bool grouped = false;
-  if (one_format) {
+  if (groupable) {
     const int st = launch_gemv_group(keys[0].q8, launches.data(), count, c.stream);
     grouped = st == TCRV_CUDA_OK;
     ok = grouped || st == TCRV_CUDA_ERR_UNSUPPORTED;
