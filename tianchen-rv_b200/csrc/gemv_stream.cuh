@@ -307,9 +307,9 @@ __device__ __forceinline__ void gemv_rows(const GemvArgs &a, const uint32_t *wro
 // kCols: activation columns (1..8).  kXRegPairs: when > 0 (single column only) the lane keeps
 // its activation pairs in registers for the whole kernel; requires npairs <= 32*kXRegPairs.
 // The kernel's body for CTA `cta` of the `nctas` that share the problem `a` (the whole grid for
-// the single-problem kernel, a share of it for the grouped one).  The block may have more
-// warps than a.nwarps: the spare ones only meet the others at the one block-wide barrier.
-template <bool kQ8W, int kCols, int kXRegPairs, bool kStrict>
+// the single-problem kernel, a share of it for the grouped one).  kWideBlock: the block may have
+// more warps than a.nwarps; the spare ones only meet the others at the one block-wide barrier.
+template <bool kQ8W, int kCols, int kXRegPairs, bool kStrict, bool kWideBlock>
 __device__ __forceinline__ void gemv_stream_body(const GemvArgs &a, uint32_t cta, uint32_t nctas, uint8_t *smem) {
   static_assert(!kStrict || kCols <= 3, "the strict order of this kernel is built for up to 3 columns");
   uint64_t *full = reinterpret_cast<uint64_t *>(smem);
@@ -327,7 +327,7 @@ __device__ __forceinline__ void gemv_stream_body(const GemvArgs &a, uint32_t cta
   // Contiguous, balanced row range of this CTA, split again into contiguous, balanced ranges
   // per warp (they differ by at most one row, so no warp does a whole slot more than the
   // others).  A warp walks its n rows in k = ceil(n / rps) slots of n/k or n/k + 1 rows.
-  const bool spare = warp >= nwarps;  // a warp of a wider block than this problem uses
+  const bool spare = kWideBlock && warp >= nwarps;  // a warp of a wider block than this problem uses
   const uint32_t r0 = static_cast<uint32_t>(static_cast<uint64_t>(a.nr) * cta / nctas);
   const uint32_t r1 = static_cast<uint32_t>(static_cast<uint64_t>(a.nr) * (cta + 1) / nctas);
   const uint32_t w0 = r0 + (r1 - r0) * warp / nwarps;
@@ -372,7 +372,7 @@ __device__ __forceinline__ void gemv_stream_body(const GemvArgs &a, uint32_t cta
   if (a.static_weights)
     asm volatile("griddepcontrol.wait;" ::: "memory");
   // Convert the activation columns (plain block_q8_0, 2-byte aligned) into the lane layout.
-  for (uint32_t idx = threadIdx.x; idx < kCols * nb; idx += blockDim.x) {
+  for (uint32_t idx = threadIdx.x; idx < kCols * nb; idx += (kWideBlock ? blockDim.x : nwarps * 32)) {
     const uint32_t col = idx / nb, ib = idx - col * nb;
     const uint8_t *src = a.vy + col * a.by + static_cast<size_t>(ib) * kQ8Block;
     const unsigned short *h = reinterpret_cast<const unsigned short *>(src);
@@ -483,7 +483,7 @@ __device__ __forceinline__ void gemv_stream_body(const GemvArgs &a, uint32_t cta
 template <bool kQ8W, int kCols, int kXRegPairs, bool kStrict = false>
 __global__ void __launch_bounds__(kGemvMaxThreads, 1) gemv_stream_kernel(const GemvArgs a) {
   extern __shared__ __align__(128) uint8_t smem[];
-  gemv_stream_body<kQ8W, kCols, kXRegPairs, kStrict>(a, blockIdx.x, gridDim.x, smem);
+  gemv_stream_body<kQ8W, kCols, kXRegPairs, kStrict, false>(a, blockIdx.x, gridDim.x, smem);
 }
 
 // Several independent one-column problems in ONE launch: CTAs first[i] .. first[i+1]-1 work on
@@ -507,9 +507,9 @@ __global__ void __launch_bounds__(kGemvMaxThreads, 1) gemv_stream_group_kernel(c
   const GemvArgs &a = g.problem[i];
   const uint32_t cta = blockIdx.x - g.first[i], nctas = g.first[i + 1] - g.first[i];
   if (a.nb / 2 <= 64)
-    gemv_stream_body<kQ8W, 1, 2, kStrict>(a, cta, nctas, smem);
+    gemv_stream_body<kQ8W, 1, 2, kStrict, true>(a, cta, nctas, smem);
   else
-    gemv_stream_body<kQ8W, 1, 0, kStrict>(a, cta, nctas, smem);
+    gemv_stream_body<kQ8W, 1, 0, kStrict, true>(a, cta, nctas, smem);
 }
 
 }  // namespace tcrv
